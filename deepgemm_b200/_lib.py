@@ -1,0 +1,74 @@
+"""ctypes binding of libdgb200.so (the C ABI declared in include/dgb200.h).
+
+The reference binds its host layer with pybind11 (csrc/python_api.cpp:17-28); here the boundary is a plain
+C ABI, so the same library can be bound from any host language. There is no CPU fallback: if the shared
+object is missing or fails to load, importing an operator raises.
+"""
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, 'libdgb200.so')
+
+_lib = None
+
+_i32, _i64, _ptr = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
+
+# name -> argtypes; every function returns int except where noted below
+_SIGNATURES = {
+    'dgb200_version': [],
+    'dgb200_set_num_sms': [ctypes.c_int],
+    'dgb200_get_num_sms': [],
+    'dgb200_device_status': [_ptr, _ptr],
+    'dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous': [
+        _ptr, _ptr, _i64, _ptr, _ptr, _i64, _i64, _ptr, _i64, _ptr,
+        _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_m_grouped_fp8_fp4_gemm_nt_masked': [
+        _ptr, _ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _ptr, _i64, _ptr,
+        _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+}
+
+
+def exported_symbols():
+    """Names of every entry point this binding expects the library to export."""
+    return ['dgb200_last_error'] + sorted(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the library on first use. Raises if it has not been built (``python -m deepgemm_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f'{LIB_PATH} is missing: build it with `python -m deepgemm_b200.build` (needs nvcc). '
+                'deepgemm_b200 has no CPU or PyTorch fallback.')
+        handle = ctypes.CDLL(LIB_PATH)
+        handle.dgb200_last_error.restype = ctypes.c_char_p
+        handle.dgb200_last_error.argtypes = []
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_int
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    """Raises RuntimeError with the library's message, as the reference's DGException surfaces in Python
+    (csrc/utils/exception.hpp:12-23)."""
+    if rc != 0:
+        raise RuntimeError(lib().dgb200_last_error().decode())
+
+
+def current_stream_ptr() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def device_status(raise_on_error: bool = True):
+    """Synchronises the current stream and returns the 8 status words; raises if a kernel reported a failure."""
+    words = (ctypes.c_int32 * 8)()
+    rc = lib().dgb200_device_status(ctypes.cast(words, ctypes.c_void_p), current_stream_ptr())
+    if rc != 0 and raise_on_error:
+        check(rc)
+    return list(words)

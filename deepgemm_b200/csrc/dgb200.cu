@@ -1,0 +1,524 @@
+// libdgb200.so: C-ABI entry points (declared in include/dgb200.h) and the single translation unit that holds
+// every sm_100a kernel of the Mega-MoE hot path. Host logic here plays the role of the reference's
+// csrc/apis/{gemm,mega,layout,runtime}.hpp argument checking and csrc/jit_kernels/impls/*.hpp launch glue;
+// there is no JIT: every kernel is compiled ahead of time for sm_100a.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "host_common.cuh"
+#include "gemm_kernel.cuh"
+#include "quant_kernels.cuh"
+#include "moe_kernels.cuh"
+
+namespace dgb {
+
+namespace {
+
+constexpr int kVersion = 100;
+
+template <int BLOCK_N, int kStages, int EPI>
+int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmParams& p, int grid, cudaStream_t stream) {
+    using L = GemmSmem<BLOCK_N, kStages>;
+    auto kernel = dgb200_grouped_gemm_kernel<BLOCK_N, kStages, EPI>;
+    static bool configured = false;  // per instantiation; the attribute is per device function, set on every device once
+    static int configured_device = -1;
+    int dev = 0;
+    DGB_CUDA(cudaGetDevice(&dev));
+    if (!configured || configured_device != dev) {
+        DGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+        configured = true;
+        configured_device = dev;
+    }
+    kernel<<<grid, 256, L::kDynamicBytes, stream>>>(tm_a, tm_b, p);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+struct GemmCall {
+    const void* a;
+    const void* b;
+    long long a_rows_total;  // rows of the flattened A
+    GemmParams p;
+    int b_is_fp4;
+    int epilogue;
+    int max_tiles;  // upper bound on tiles, <= 0 if unknown
+};
+
+int debug_b_tx_mode() {
+    static int mode = [] {
+        const char* s = std::getenv("DGB200_DEBUG_B_TX_SMEM_BYTES");
+        return (s != nullptr && s[0] == '1') ? 1 : 0;
+    }();
+    return mode;
+}
+
+int run_gemm(GemmCall& c, cudaStream_t stream) {
+    GemmParams& p = c.p;
+    DGB_REQUIRE(p.k > 0 && p.k % 128 == 0, "k (%d) must be a positive multiple of 128", p.k);
+    DGB_REQUIRE(p.n > 0 && p.n % 128 == 0, "n (%d) must be a positive multiple of 128", p.n);
+    DGB_REQUIRE(p.gran_a == 32 || p.gran_a == 128, "gran_k_a must be 32 or 128, got %d", p.gran_a);
+    DGB_REQUIRE(p.gran_b == 32 || p.gran_b == 128, "gran_k_b must be 32 or 128, got %d", p.gran_b);
+    DGB_REQUIRE(p.num_groups > 0, "num_groups must be positive");
+    DGB_REQUIRE(c.a != nullptr && c.b != nullptr && p.sfa != nullptr && p.sfb != nullptr && p.layout != nullptr,
+                "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.a) % 16 == 0, "a must be 16-byte aligned");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.b) % 32 == 0, "b must be 32-byte aligned");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(p.sfa) % 16 == 0 && reinterpret_cast<uintptr_t>(p.sfb) % 16 == 0,
+                "scale-factor tensors must be 16-byte aligned");
+    DGB_REQUIRE(p.sfa_k_stride % 4 == 0 && p.sfb_k_stride % 4 == 0 && p.sfa_group_stride % 4 == 0 &&
+                    p.sfb_group_stride % 4 == 0,
+                "packed scale-factor strides must be multiples of 4 ints (TMA-aligned MN stride)");
+    if (c.a_rows_total == 0) return 0;
+
+    CUtensorMap tm_a, tm_b;
+    int rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, static_cast<uint64_t>(p.k),
+                                static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.k), 128, 128,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint64_t b_rows = static_cast<uint64_t>(p.num_groups) * p.n;
+    constexpr int BLOCK_N = 128;
+    if (c.b_is_fp4) {
+        rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, c.b, static_cast<uint64_t>(p.k), b_rows,
+                                static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = kFmtE2M1_F8F6F4;
+        // Packed FP4 expands to one byte per element in shared memory; the mbarrier is credited with the
+        // bytes read from global memory (half the tile).
+        p.b_tx_bytes = debug_b_tx_mode() ? BLOCK_N * 128 : BLOCK_N * 64;
+    } else {
+        rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, static_cast<uint64_t>(p.k), b_rows,
+                                static_cast<uint64_t>(p.k), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = kFmtE4M3;
+        p.b_tx_bytes = BLOCK_N * 128;
+    }
+    if (rc) return rc;
+
+    int sms = 0;
+    rc = effective_num_sms(&sms);
+    if (rc) return rc;
+    int grid = sms;
+    if (c.max_tiles > 0) grid = std::min(grid, c.max_tiles);
+
+    constexpr int kStages = 6;
+    switch (c.epilogue) {
+        case kEpiBF16: return launch_gemm<BLOCK_N, kStages, kEpiBF16>(tm_a, tm_b, p, grid, stream);
+        case kEpiF32: return launch_gemm<BLOCK_N, kStages, kEpiF32>(tm_a, tm_b, p, grid, stream);
+        case kEpiSwiGLU: return launch_gemm<BLOCK_N, kStages, kEpiSwiGLU>(tm_a, tm_b, p, grid, stream);
+        case kEpiScatter: return launch_gemm<BLOCK_N, kStages, kEpiScatter>(tm_a, tm_b, p, grid, stream);
+        default: return fail(DGB200_EINVAL, "unknown epilogue %d", c.epilogue);
+    }
+}
+
+
+// --------------------------------------------------------------------------------------------------------------
+// Mega-MoE buffer layout. One flat buffer per rank holds the caller-written inputs and every intermediate of the
+// layer (the reference's counterpart: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155, and
+// deep_gemm/include/deep_gemm/layout/mega_moe.cuh:46-443). All regions start on 1024-byte boundaries.
+// --------------------------------------------------------------------------------------------------------------
+constexpr int kSegmentAlignment = 16;  // rows each expert segment is padded to in the expert-sorted buffers
+
+struct MegaLayout {
+    long long x, x_sf, topk_idx, topk_weights;                            // inputs, written by the caller
+    long long chunk_hist, expert_start, expert_end, total_rows, dest_row;  // dispatch plan
+    long long src_of_row, row_weight;
+    long long l1_acts, l1_sf, l2_acts, l2_sf, combine;
+    long long total;
+    long long max_rows;  // capacity of the expert-sorted buffers (rows), a multiple of 128
+    int num_chunks, num_local_experts;
+};
+
+int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, MegaLayout* out) {
+    DGB_REQUIRE(num_ranks >= 1 && num_ranks <= kMaxRanks, "num_ranks must be in [1, %d]", kMaxRanks);
+    DGB_REQUIRE(num_experts > 0 && num_experts % num_ranks == 0, "num_experts must be a positive multiple of num_ranks");
+    DGB_REQUIRE(max_tokens > 0 && topk > 0 && topk <= 32, "need max tokens > 0 and 0 < topk <= 32");
+    DGB_REQUIRE(hidden % 128 == 0 && inter % 128 == 0 && hidden > 0 && inter > 0,
+                "hidden and intermediate_hidden must be positive multiples of 128");
+    MegaLayout l{};
+    l.num_local_experts = num_experts / num_ranks;
+    const long long active_topk = std::min(topk, l.num_local_experts);
+    const long long routed = static_cast<long long>(max_tokens) * num_ranks * active_topk;
+    l.max_rows = (routed + static_cast<long long>(l.num_local_experts) * kSegmentAlignment + 127) / 128 * 128;
+    l.num_chunks = static_cast<int>((static_cast<long long>(max_tokens) * topk + kPlanChunk - 1) / kPlanChunk);
+    long long off = 0;
+    auto take = [&off](long long bytes) {
+        const long long at = off;
+        off += (bytes + 1023) / 1024 * 1024;
+        return at;
+    };
+    l.x = take(static_cast<long long>(max_tokens) * hidden);
+    l.x_sf = take(static_cast<long long>(max_tokens) * (hidden / 128) * 4);
+    l.topk_idx = take(static_cast<long long>(max_tokens) * topk * 8);
+    l.topk_weights = take(static_cast<long long>(max_tokens) * topk * 4);
+    l.chunk_hist = take(static_cast<long long>(l.num_chunks) * l.num_local_experts * 4);
+    l.expert_start = take(l.num_local_experts * 4ll);
+    l.expert_end = take(l.num_local_experts * 4ll);
+    l.total_rows = take(16);
+    l.dest_row = take(static_cast<long long>(max_tokens) * topk * 4);
+    l.src_of_row = take(l.max_rows * 4);
+    l.row_weight = take(l.max_rows * 4);
+    l.l1_acts = take(l.max_rows * hidden);
+    l.l1_sf = take(l.max_rows * (hidden / 128) * 4);
+    l.l2_acts = take(l.max_rows * inter);
+    l.l2_sf = take(l.max_rows * (inter / 128) * 4);
+    l.combine = take(static_cast<long long>(topk) * max_tokens * hidden * 2);
+    l.total = off;
+    *out = l;
+    return 0;
+}
+
+int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, int gran_k, void* q, long long q_row_stride,
+             float* sf_f32, void* sf_packed, long long sf_k_stride, cudaStream_t stream) {
+    DGB_REQUIRE(rows >= 0 && k > 0 && k % 16 == 0, "k (%d) must be a positive multiple of 16", k);
+    DGB_REQUIRE(gran_k == 32 || gran_k == 128, "gran_k must be 32 or 128, got %d", gran_k);
+    DGB_REQUIRE(x != nullptr && q != nullptr, "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0 && (x_row_stride * 2) % 16 == 0, "x rows must be 16-byte aligned");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(q) % 16 == 0 && q_row_stride % (fp4 ? 8 : 16) == 0, "q rows must be 16-byte aligned");
+    DGB_REQUIRE(sf_f32 != nullptr || sf_packed != nullptr, "at least one scale-factor output is required");
+    DGB_REQUIRE(sf_packed == nullptr || sf_k_stride >= rows, "packed scale-factor MN stride smaller than rows");
+    if (rows == 0) return 0;
+    CastParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.x_row_stride = x_row_stride;
+    p.q = q;
+    p.q_row_stride = q_row_stride;
+    p.sf_f32 = sf_f32;
+    p.sf_packed = static_cast<uint32_t*>(sf_packed);
+    p.sf_k_stride = sf_k_stride;
+    p.rows = rows;
+    p.k = k;
+    p.gran_k = gran_k;
+    const dim3 grid((k + 511) / 512, (rows + 31) / 32);
+    if (fp4)
+        dgb200_cast_rows_kernel<true><<<grid, 256, 0, stream>>>(p);
+    else
+        dgb200_cast_rows_kernel<false><<<grid, 256, 0, stream>>>(p);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+}  // namespace dgb
+
+using namespace dgb;
+
+extern "C" {
+
+const char* dgb200_last_error(void) { return last_error_storage().c_str(); }
+
+int dgb200_version(void) { return kVersion; }
+
+int dgb200_set_num_sms(int num_sms) {
+    DGB_REQUIRE(num_sms >= 0, "num_sms must be >= 0");
+    num_sms_setting() = num_sms;
+    return 0;
+}
+
+int dgb200_get_num_sms(void) {
+    int sms = 0;
+    if (effective_num_sms(&sms) != 0) return -1;
+    return sms;
+}
+
+int dgb200_device_status(int32_t* out_words, void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DGB_CUDA(cudaStreamSynchronize(s));
+    int words[8];
+    DGB_CUDA(cudaMemcpyFromSymbol(words, g_status, sizeof(words)));
+    if (out_words != nullptr) std::memcpy(out_words, words, sizeof(words));
+    if (words[0] != 0) {
+        const int zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        DGB_CUDA(cudaMemcpyToSymbol(g_status, zeros, sizeof(zeros)));
+        return fail(DGB200_EDEVICE, "device status: code %d at block %d (detail %d, %d)", words[0], words[1], words[2],
+                    words[3]);
+    }
+    return 0;
+}
+
+int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
+    const void* a, const void* sfa, int64_t sfa_k_stride,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
+    void* d, int64_t d_row_stride, const int32_t* grouped_layout,
+    int32_t m, int32_t n, int32_t k, int32_t num_groups,
+    int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
+    int32_t layout_kind, int32_t alignment, int32_t store_padding, void* stream) {
+    DGB_REQUIRE(m >= 0, "m must be >= 0");
+    DGB_REQUIRE(layout_kind == DGB200_LAYOUT_ROW_IDS || layout_kind == DGB200_LAYOUT_PSUM, "unknown layout kind %d",
+                layout_kind);
+    DGB_REQUIRE(alignment > 0 && alignment % 4 == 0, "alignment (%d) must be a positive multiple of 4", alignment);
+    DGB_REQUIRE(layout_kind == DGB200_LAYOUT_PSUM || alignment % 128 == 0,
+                "the row-id layout needs an M alignment that is a multiple of 128, got %d", alignment);
+    DGB_REQUIRE(d != nullptr || m == 0, "null output");
+    DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
+                "d row stride must cover n and keep rows 16-byte aligned");
+    DGB_REQUIRE(sfa_k_stride >= m, "sfa MN stride (%lld) smaller than m (%d)", static_cast<long long>(sfa_k_stride), m);
+    GemmCall c{};
+    c.a = a;
+    c.b = b;
+    c.a_rows_total = m;
+    c.b_is_fp4 = b_is_fp4;
+    c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
+    GemmParams& p = c.p;
+    p.sfa = static_cast<const uint32_t*>(sfa);
+    p.sfb = static_cast<const uint32_t*>(sfb);
+    p.sfa_k_stride = sfa_k_stride;
+    p.sfa_group_stride = 0;
+    p.sfa_rows = sfa_k_stride;
+    p.sfb_k_stride = sfb_k_stride;
+    p.sfb_group_stride = sfb_group_stride;
+    p.d = d;
+    p.d_row_stride = d_row_stride;
+    p.layout = grouped_layout;
+    p.mode = layout_kind == DGB200_LAYOUT_PSUM ? kModePsum : kModeRowIds;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.num_groups = num_groups;
+    p.alignment = alignment;
+    p.gran_a = gran_k_a;
+    p.gran_b = gran_k_b;
+    p.store_padding = store_padding;
+    const long long m_blocks = (static_cast<long long>(m) + 127) / 128 + (p.mode == kModePsum ? num_groups : 0);
+    c.max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
+    return run_gemm(c, static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
+    const void* a, const void* sfa, int64_t sfa_k_stride, int64_t sfa_group_stride,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
+    void* d, int64_t d_row_stride, const int32_t* masked_m,
+    int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
+    int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream) {
+    (void)expected_m;
+    DGB_REQUIRE(max_m > 0 && max_m % 4 == 0, "max_m (%d) must be a positive multiple of 4", max_m);
+    DGB_REQUIRE(d != nullptr, "null output");
+    DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
+                "d row stride must cover n and keep rows 16-byte aligned");
+    DGB_REQUIRE(sfa_k_stride >= max_m, "sfa MN stride smaller than max_m");
+    GemmCall c{};
+    c.a = a;
+    c.b = b;
+    c.a_rows_total = static_cast<long long>(num_groups) * max_m;
+    c.b_is_fp4 = b_is_fp4;
+    c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
+    GemmParams& p = c.p;
+    p.sfa = static_cast<const uint32_t*>(sfa);
+    p.sfb = static_cast<const uint32_t*>(sfb);
+    p.sfa_k_stride = sfa_k_stride;
+    p.sfa_group_stride = sfa_group_stride;
+    p.sfa_rows = sfa_k_stride;
+    p.sfb_k_stride = sfb_k_stride;
+    p.sfb_group_stride = sfb_group_stride;
+    p.d = d;
+    p.d_row_stride = d_row_stride;
+    p.layout = masked_m;
+    p.mode = kModeMasked;
+    p.m = max_m;
+    p.n = n;
+    p.k = k;
+    p.num_groups = num_groups;
+    p.alignment = 4;
+    p.gran_a = gran_k_a;
+    p.gran_b = gran_k_b;
+    p.store_padding = 0;
+    c.max_tiles = 0;
+    return run_gemm(c, static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_per_token_cast_to_fp8(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
+                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride, void* stream) {
+    return run_cast(false, x, x_row_stride, rows, k, gran_k, q, q_row_stride, sf_f32, sf_packed, sf_k_stride,
+                    static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_per_token_cast_to_fp4(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
+                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride, void* stream) {
+    return run_cast(true, x, x_row_stride, rows, k, gran_k, q, q_row_stride, sf_f32, sf_packed, sf_k_stride,
+                    static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, int64_t stride_mn, int64_t stride_k,
+                                             void* out, int32_t num_groups, int32_t mn, int32_t sf_k, int32_t gran_mn,
+                                             const int32_t* psum_layout, int32_t num_psum_groups,
+                                             int32_t psum_alignment, void* stream) {
+    DGB_REQUIRE(sf != nullptr && out != nullptr, "null tensor pointer");
+    DGB_REQUIRE(num_groups > 0 && mn >= 0 && sf_k > 0 && gran_mn > 0, "bad scale-factor shape");
+    DGB_REQUIRE(psum_layout == nullptr || (num_psum_groups > 0 && psum_alignment > 0), "bad psum layout");
+    if (mn == 0) return 0;
+    PackSfParams p{};
+    p.sf = sf;
+    p.in_stride_g = stride_g;
+    p.in_stride_mn = stride_mn;
+    p.in_stride_k = stride_k;
+    p.out = static_cast<uint32_t*>(out);
+    p.aligned_mn = (static_cast<long long>(mn) + 3) / 4 * 4;
+    p.num_groups = num_groups;
+    p.mn = mn;
+    p.sf_k = sf_k;
+    p.gran_mn = gran_mn;
+    p.psum_layout = psum_layout;
+    p.num_psum_groups = num_psum_groups;
+    p.psum_alignment = psum_alignment;
+    const long long total = static_cast<long long>(num_groups) * ((sf_k + 3) / 4) * mn;
+    const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+    dgb200_pack_sf_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int dgb200_get_token_alignment_for_mega_moe(void) { return 128; }
+
+int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                               int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                               int64_t* out) {
+    DGB_REQUIRE(out != nullptr, "null output");
+    MegaLayout l;
+    const int rc = make_mega_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
+    if (rc) return rc;
+    out[0] = l.total;
+    out[1] = l.x;
+    out[2] = l.x_sf;
+    out[3] = l.topk_idx;
+    out[4] = l.topk_weights;
+    out[5] = l.l1_acts;
+    out[6] = l.l1_sf;
+    out[7] = l.l2_acts;
+    out[8] = l.l2_sf;
+    out[9] = l.max_rows;
+    out[10] = l.dest_row;
+    out[11] = l.src_of_row;
+    out[12] = l.expert_start;
+    out[13] = l.expert_end;
+    out[14] = l.combine;
+    out[15] = l.row_weight;
+    return 0;
+}
+
+int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+                            int32_t* cumulative_local_expert_recv_stats, void* buffer, const uint64_t* peer_buffer_ptrs,
+                            int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
+                            int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                            float activation_clamp, int32_t fast_math, void* stream_) {
+    (void)fast_math;  // the SwiGLU epilogue always uses the fast exponential, as the reference does by default
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    MegaLayout l;
+    int rc = make_mega_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
+    if (rc) return rc;
+    DGB_REQUIRE(num_ranks == 1, "this entry point runs the single-rank layer; use dgb200_fp8_fp4_mega_moe_ep for %d ranks", num_ranks);
+    DGB_REQUIRE(rank == 0 && peer_buffer_ptrs != nullptr && peer_buffer_ptrs[0] == reinterpret_cast<uint64_t>(buffer),
+                "rank / peer pointer table do not describe this buffer");
+    DGB_REQUIRE(num_tokens >= 0 && num_tokens <= num_max_tokens_per_rank, "num_tokens (%d) exceeds the buffer capacity (%d)",
+                num_tokens, num_max_tokens_per_rank);
+    DGB_REQUIRE(y != nullptr && l1_w != nullptr && l1_w_sf != nullptr && l2_w != nullptr && l2_w_sf != nullptr && buffer != nullptr,
+                "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 1024 == 0, "buffer must be 1024-byte aligned");
+    DGB_REQUIRE((2 * intermediate_hidden) % 128 == 0 && intermediate_hidden % 64 == 0, "intermediate_hidden must be a multiple of 64");
+    if (num_tokens == 0) return 0;
+
+    uint8_t* base = static_cast<uint8_t*>(buffer);
+    const int E = l.num_local_experts;
+    const int entries = num_tokens * num_topk;
+    const int chunks = (entries + kPlanChunk - 1) / kPlanChunk;
+    int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
+    int* expert_start = reinterpret_cast<int*>(base + l.expert_start);
+    int* expert_end = reinterpret_cast<int*>(base + l.expert_end);
+    int* total_rows = reinterpret_cast<int*>(base + l.total_rows);
+    int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
+    int* src_of_row = reinterpret_cast<int*>(base + l.src_of_row);
+    float* row_weight = reinterpret_cast<float*>(base + l.row_weight);
+    const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
+    const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
+
+    // 1. dispatch plan: stable counting sort of the (token, k) entries by expert
+    DGB_CUDA(cudaMemsetAsync(src_of_row, 0xff, l.max_rows * 4, stream));
+    dgb200_moe_count_kernel<<<chunks, kPlanChunk, E * sizeof(int), stream>>>(topk_idx, entries, 0, E, chunk_hist);
+    dgb200_moe_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, E, kSegmentAlignment, expert_start, expert_end,
+                                                    total_rows, cumulative_local_expert_recv_stats);
+    dgb200_moe_assign_kernel<<<chunks, kPlanChunk, 32 * E, stream>>>(topk_idx, topk_weights, entries, 0, E, chunk_hist,
+                                                                    expert_start, dest_row, src_of_row, row_weight);
+    DGB_CUDA(cudaGetLastError());
+
+    // 2. gather FP8 rows + scales into expert-sorted order
+    const long long upper_rows = std::min<long long>(l.max_rows, static_cast<long long>(entries) + static_cast<long long>(E) * kSegmentAlignment);
+    const int gather_blocks = static_cast<int>((upper_rows + 31) / 32);
+    dgb200_moe_gather_kernel<<<gather_blocks, 256, (hidden / 128) * 33 * sizeof(unsigned), stream>>>(
+        base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk, hidden,
+        base + l.l1_acts, reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
+    DGB_CUDA(cudaGetLastError());
+
+    // 3. L1: gate/up GEMM with the fused SwiGLU + FP8 requant epilogue
+    {
+        GemmCall c{};
+        c.a = base + l.l1_acts;
+        c.b = l1_w;
+        c.a_rows_total = l.max_rows;
+        c.b_is_fp4 = 1;
+        c.epilogue = kEpiSwiGLU;
+        c.max_tiles = 0;
+        GemmParams& p = c.p;
+        p.sfa = reinterpret_cast<const uint32_t*>(base + l.l1_sf);
+        p.sfb = static_cast<const uint32_t*>(l1_w_sf);
+        p.sfa_k_stride = l.max_rows;
+        p.sfa_group_stride = 0;
+        p.sfa_rows = l.max_rows;
+        p.sfb_k_stride = 2 * intermediate_hidden;
+        p.sfb_group_stride = static_cast<long long>(hidden / 128) * 2 * intermediate_hidden;
+        p.layout = expert_end;
+        p.mode = kModePsum;
+        p.m = static_cast<int>(l.max_rows);
+        p.n = 2 * intermediate_hidden;
+        p.k = hidden;
+        p.num_groups = E;
+        p.alignment = kSegmentAlignment;
+        p.gran_a = 32;
+        p.gran_b = 32;
+        p.act_q = base + l.l2_acts;
+        p.act_sf = base + l.l2_sf;
+        p.act_q_row_stride = intermediate_hidden;
+        p.act_sf_k_stride = l.max_rows;
+        p.row_weight = row_weight;
+        p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
+        rc = run_gemm(c, stream);
+        if (rc) return rc;
+    }
+    // 4. L2: down GEMM, rows scattered to the combine slot of their (token, top-k slot)
+    {
+        GemmCall c{};
+        c.a = base + l.l2_acts;
+        c.b = l2_w;
+        c.a_rows_total = l.max_rows;
+        c.b_is_fp4 = 1;
+        c.epilogue = kEpiScatter;
+        c.max_tiles = 0;
+        GemmParams& p = c.p;
+        p.sfa = reinterpret_cast<const uint32_t*>(base + l.l2_sf);
+        p.sfb = static_cast<const uint32_t*>(l2_w_sf);
+        p.sfa_k_stride = l.max_rows;
+        p.sfa_group_stride = 0;
+        p.sfa_rows = l.max_rows;
+        p.sfb_k_stride = hidden;
+        p.sfb_group_stride = static_cast<long long>(intermediate_hidden / 128) * hidden;
+        p.layout = expert_end;
+        p.mode = kModePsum;
+        p.m = static_cast<int>(l.max_rows);
+        p.n = hidden;
+        p.k = intermediate_hidden;
+        p.num_groups = E;
+        p.alignment = kSegmentAlignment;
+        p.gran_a = 32;
+        p.gran_b = 32;
+        p.row_src = src_of_row;
+        p.combine_base[0] = base + l.combine;
+        p.combine_tokens = num_max_tokens_per_rank;
+        p.topk = num_topk;
+        rc = run_gemm(c, stream);
+        if (rc) return rc;
+    }
+    // 5. combine: y[t] = sum over the top-k slots
+    dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(int), stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(base + l.combine), dest_row, num_topk, num_max_tokens_per_rank, hidden,
+        static_cast<__nv_bfloat16*>(y));
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // extern "C"

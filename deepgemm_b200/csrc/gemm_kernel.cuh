@@ -1,0 +1,459 @@
+// Persistent, warp-specialised m-grouped GEMM for sm_100a:
+//   D[m, :] = A[m, :] . B[group(m)]^T,  A = E4M3 activations, B = packed E2M1 (MXFP4) or E4M3 weights,
+//   UE8M0 block scales applied inside tcgen05.mma (kind::mxf8f6f4.block_scale), FP32 accumulation in TMEM.
+//
+// Replaces, for the m-grouped contiguous / psum / masked layouts, the reference kernel
+// deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_gemm_1d1d.cuh:33-534 together with its scheduler
+// (deep_gemm/include/deep_gemm/scheduler/gemm.cuh:39-325) and epilogue
+// (deep_gemm/include/deep_gemm/epilogue/sm100_store_cd_swap_ab.cuh:23-142).
+//
+// Design differences from the reference (it is not a translation):
+//   * Tokens sit on the UMMA M side (TMEM lanes), weight channels on the N side (TMEM columns). One epilogue
+//     thread therefore owns one token row: stores are row-contiguous 16-byte vectors straight from registers,
+//     and the SwiGLU / amax / requant epilogue needs no shuffles or shared-memory exchange.
+//   * Scale factors arrive by 1-D bulk copies (no tensor maps), 512 B per 128 rows per packed K group.
+//   * Stores are clipped to the valid rows of a group, so a masked group never writes into its neighbour.
+//   * Every wait is bounded; a timeout unwinds the CTA and is reported through the status block.
+//
+// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator + scale-factor
+// transposer, warp 3 idle, warps 4-7 epilogue (TMEM lane quarter = warp index % 4).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+
+namespace dgb {
+
+enum GroupMode : int {
+    kModeRowIds = 0,  // layout[m] = group of row m, -1 on padding rows (segments aligned to `alignment`)
+    kModePsum = 1,    // layout[g] = end row of group g; group g starts at align(layout[g-1], alignment)
+    kModeMasked = 2,  // A/D are [G, max_m, *]; layout[g] = valid rows of group g
+};
+
+enum EpilogueKind : int {
+    kEpiBF16 = 0,    // D bf16
+    kEpiF32 = 1,     // D fp32 (raw accumulators; bring-up and tests)
+    kEpiSwiGLU = 2,  // gate/up -> silu(gate)*up*row_weight -> per-32 UE8M0 FP8 requant
+    kEpiScatter = 3, // D bf16, row r written to the combine slot of its source (rank, token, top-k slot)
+};
+
+constexpr int kMaxRanks = 8;
+
+struct GemmParams {
+    const uint32_t* sfa;  // packed UE8M0, MN-major: int index = group*sfa_group_stride + kp*sfa_k_stride + row
+    const uint32_t* sfb;  // same for B:            int index = group*sfb_group_stride + kp*sfb_k_stride + channel
+    long long sfa_k_stride, sfa_group_stride, sfa_rows;  // sfa_rows: addressable rows per group (multiple of 4)
+    long long sfb_k_stride, sfb_group_stride;
+    void* d;
+    long long d_row_stride;  // elements
+    const int* layout;
+    int mode, m, n, k, num_groups, alignment;
+    int gran_a, gran_b;      // 32 or 128
+    unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
+    unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
+    int store_padding;       // psum only: also write the rows between a group's end and its aligned end
+    // SwiGLU epilogue only
+    unsigned char* act_q;        // e4m3 [rows, n/2]
+    unsigned char* act_sf;       // packed UE8M0 bytes, MN-major ints: ((j/128)*act_sf_k_stride + row)*4 + (j/32)%4
+    long long act_q_row_stride;  // bytes
+    long long act_sf_k_stride;   // ints
+    const float* row_weight;     // per destination row, may be null (weight 1)
+    float clamp;                 // <= 0: no clamp
+    // Scatter epilogue only: row r belongs to entry e = row_src[r] % (combine_tokens * topk) of rank
+    // row_src[r] / (combine_tokens * topk); entry e = token * topk + slot lands in
+    // combine_base[rank][(slot * combine_tokens + token) * n + column].
+    const int* row_src;
+    void* combine_base[kMaxRanks];
+    int combine_tokens, topk;
+};
+
+struct Tile {
+    int row_start;     // first row in the flattened A / D
+    int sf_row_start;  // first row inside the group's SF block (masked) or global row (others)
+    int rows_store;    // rows of this tile to write
+    int group;
+    int n_block;
+};
+
+template <int BLOCK_N>
+struct TileScheduler {
+    const GemmParams& p;
+    int num_n_blocks;
+    int tile;  // next global tile index of this CTA
+    int g, tiles_before_g;
+
+    __device__ explicit TileScheduler(const GemmParams& params)
+        : p(params), num_n_blocks(params.n / BLOCK_N), tile(static_cast<int>(blockIdx.x)), g(0), tiles_before_g(0) {}
+
+    __device__ __forceinline__ void group_extent(int group, int& start, int& rows, int& rows_store) const {
+        if (p.mode == kModeMasked) {
+            start = group * p.m;
+            rows = min(__ldg(p.layout + group), p.m);
+            rows_store = rows;
+        } else {
+            const int prev_end = group == 0 ? 0 : __ldg(p.layout + group - 1);
+            start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
+            const int end = __ldg(p.layout + group);
+            rows = max(end - start, 0);
+            const int aligned_end = min((end + p.alignment - 1) / p.alignment * p.alignment, p.m);
+            rows_store = p.store_padding ? max(aligned_end - start, 0) : rows;
+        }
+    }
+
+    // Returns false when this CTA has no more tiles. A tile with group < 0 must be skipped by every role.
+    __device__ bool next(Tile& t) {
+        if (p.mode == kModeRowIds) {
+            const int num_m_blocks = (p.m + 127) / 128;
+            if (tile >= num_m_blocks * num_n_blocks) return false;
+            const int mb = tile / num_n_blocks;
+            t.n_block = tile - mb * num_n_blocks;
+            t.row_start = t.sf_row_start = mb * 128;
+            t.rows_store = min(128, p.m - t.row_start);
+            t.group = __ldg(p.layout + t.row_start);
+            tile += static_cast<int>(gridDim.x);
+            return true;
+        }
+        while (g < p.num_groups) {
+            int start, rows, rows_store;
+            group_extent(g, start, rows, rows_store);
+            const int m_blocks = (max(rows, rows_store) + 127) / 128;
+            const int tiles_g = m_blocks * num_n_blocks;
+            if (tile < tiles_before_g + tiles_g) {
+                const int local = tile - tiles_before_g;
+                const int mb = local / num_n_blocks;
+                t.n_block = local - mb * num_n_blocks;
+                t.row_start = start + mb * 128;
+                t.sf_row_start = p.mode == kModeMasked ? mb * 128 : t.row_start;
+                t.rows_store = min(128, rows_store - mb * 128);
+                t.group = g;
+                tile += static_cast<int>(gridDim.x);
+                return true;
+            }
+            tiles_before_g += tiles_g;
+            ++g;
+        }
+        return false;
+    }
+};
+
+template <int BLOCK_N, int kStages>
+struct GemmSmem {
+    static constexpr int kABytes = 128 * 128;
+    static constexpr int kBBytes = BLOCK_N * 128;
+    static constexpr int kSfaBytes = 128 * 4;
+    static constexpr int kSfbBytes = BLOCK_N * 4;
+    static constexpr int kOffA = 0;
+    static constexpr int kOffB = kOffA + kStages * kABytes;
+    static constexpr int kOffSfa = kOffB + kStages * kBBytes;
+    static constexpr int kOffSfb = kOffSfa + kStages * kSfaBytes;
+    static constexpr int kOffBar = kOffSfb + kStages * kSfbBytes;
+    static constexpr int kNumBars = 3 * kStages + 4;
+    static constexpr int kOffMisc = kOffBar + kNumBars * 8;
+    static constexpr int kTotal = kOffMisc + 16;
+    static constexpr int kDynamicBytes = kTotal + 1024;  // slack to align the base to 1024 B
+};
+
+// Smallest power of two >= amax/448, as (sf, 1/sf, biased exponent byte). Mirrors the reference's in-kernel
+// requant rule (deep_gemm/include/deep_gemm/common/math.cuh:83-99): exponent is bumped when the mantissa of
+// amax/448 is non-zero; no lower clamp other than the UE8M0 range.
+__device__ __forceinline__ void ue8m0_scale_for_amax(float amax, float& sf_inv, uint32_t& sf_byte) {
+    const float s = amax * (1.0f / 448.0f);
+    const uint32_t bits = __float_as_uint(s);
+    uint32_t e = (bits >> 23) & 0xffu;
+    if (bits & 0x7fffffu) ++e;
+    e = min(max(e, 1u), 254u);
+    sf_byte = e;
+    sf_inv = __uint_as_float((254u - e) << 23);  // 2^(127-e)
+}
+
+template <int BLOCK_N, int kStages, int EPI>
+__global__ void __launch_bounds__(256, 1)
+dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                           const __grid_constant__ GemmParams p) {
+    using L = GemmSmem<BLOCK_N, kStages>;
+    static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
+    constexpr uint32_t kAccumCols = BLOCK_N;
+    constexpr uint32_t kNumAccum = BLOCK_N == 128 ? 2 : 1;
+    constexpr uint32_t kSfaCol = kAccumCols * kNumAccum;
+    constexpr uint32_t kSfbCol = kSfaCol + 4;
+    constexpr uint32_t kTmemCols = 512;
+    static_assert(kSfbCol + BLOCK_N / 32 <= kTmemCols || kNumAccum == 1, "TMEM budget");
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + kStages;
+    uint64_t* sf_ready_bar = bars + 2 * kStages;
+    uint64_t* tmem_full_bar = bars + 3 * kStages;
+    uint64_t* tmem_empty_bar = bars + 3 * kStages + 2;
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffMisc + 4);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(full_bar + i, 1);
+            mbar_init(empty_bar + i, 1);
+            mbar_init(sf_ready_bar + i, 32);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(tmem_full_bar + i, 1);
+            mbar_init(tmem_empty_bar + i, 128);
+        }
+        fence_mbar_init();
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+    }
+    if (warp == 2) tmem_alloc(tmem_ptr_smem, kTmemCols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    const int num_kb = p.k / 128;
+    const int a_per = p.gran_a == 32 ? 1 : 4;  // K blocks covered by one packed SF int
+    const int b_per = p.gran_b == 32 ? 1 : 4;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            TileScheduler<BLOCK_N> sched(p);
+            Tile t;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            while (ok && sched.next(t)) {
+                if (t.group < 0) continue;
+                const long long sfa_base = static_cast<long long>(t.group) * p.sfa_group_stride + t.sf_row_start;
+                const uint32_t sfa_bytes =
+                    static_cast<uint32_t>(min(128ll, p.sfa_rows - t.sf_row_start)) * 4u;
+                const long long sfb_base =
+                    static_cast<long long>(t.group) * p.sfb_group_stride + static_cast<long long>(t.n_block) * BLOCK_N;
+                const int b_row = t.group * p.n + t.n_block * BLOCK_N;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
+                    if (!ok) break;
+                    const bool load_sfa = kb % a_per == 0, load_sfb = kb % b_per == 0;
+                    uint32_t bytes = L::kABytes + p.b_tx_bytes;
+                    if (load_sfa) bytes += sfa_bytes;
+                    if (load_sfb) bytes += L::kSfbBytes;
+                    mbar_arrive_expect_tx(full_bar + stage, bytes);
+                    tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128, t.row_start);
+                    tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
+                    if (load_sfa)
+                        bulk_load_1d(smem + L::kOffSfa + stage * L::kSfaBytes,
+                                     p.sfa + sfa_base + static_cast<long long>(kb / a_per) * p.sfa_k_stride,
+                                     sfa_bytes, full_bar + stage);
+                    if (load_sfb)
+                        bulk_load_1d(smem + L::kOffSfb + stage * L::kSfbBytes,
+                                     p.sfb + sfb_base + static_cast<long long>(kb / b_per) * p.sfb_k_stride,
+                                     L::kSfbBytes, full_bar + stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        TileScheduler<BLOCK_N> sched(p);
+        Tile t;
+        uint32_t stage = 0, phase = 0, iter = 0;
+        const uint32_t idesc = make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
+        const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
+        const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
+        bool ok = true;
+        while (ok && sched.next(t)) {
+            if (t.group < 0) continue;
+            const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
+            ++iter;
+            ok = mbar_wait(tmem_empty_bar + as, aphase ^ 1, abort_flag, kTimeoutTmemEmpty, static_cast<int>(iter));
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t tmem_acc = tmem_base + as * kAccumCols;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(sf_ready_bar + stage, phase, abort_flag, kTimeoutSfReady, kb);
+                if (!ok) break;
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    if (kb % a_per == 0)
+                        tcgen05_cp_32x128b_warpx4(tmem_base + kSfaCol, make_sf_desc(sfa_smem + stage * L::kSfaBytes));
+                    if (kb % b_per == 0) {
+#pragma unroll
+                        for (int i = 0; i < BLOCK_N / 128; ++i)
+                            tcgen05_cp_32x128b_warpx4(tmem_base + kSfbCol + i * 4,
+                                                      make_sf_desc(sfb_smem + stage * L::kSfbBytes + i * 512));
+                    }
+                    const uint64_t adesc = make_kmajor_sw128_desc(a_base + stage * L::kABytes);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < 4; ++k4) {
+                        const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
+                        const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
+                        // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
+                        tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
+                                             idesc_with_sf_ids(idesc, sfa_id, sfb_id),
+                                             tmem_base + kSfaCol, tmem_base + kSfbCol, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar + stage);
+                    if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- scale-factor transposer
+        // tcgen05.cp 32x128b wants, per 128 rows, 32 rows x 4 words with word j of row r = source row r + 32 j.
+        TileScheduler<BLOCK_N> sched(p);
+        Tile t;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        while (ok && sched.next(t)) {
+            if (t.group < 0) continue;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
+                if (!ok) break;
+                if (kb % a_per == 0) {
+                    uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
+                    const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
+                    __syncwarp();
+                    *reinterpret_cast<uint4*>(s + lane * 4) = make_uint4(v0, v1, v2, v3);
+                }
+                if (kb % b_per == 0) {
+#pragma unroll
+                    for (int i = 0; i < BLOCK_N / 128; ++i) {
+                        uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfb + stage * L::kSfbBytes) + i * 128;
+                        const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
+                        __syncwarp();
+                        *reinterpret_cast<uint4*>(s + lane * 4) = make_uint4(v0, v1, v2, v3);
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(sf_ready_bar + stage);
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- epilogue
+        TileScheduler<BLOCK_N> sched(p);
+        Tile t;
+        uint32_t iter = 0;
+        const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
+        const int r = static_cast<int>(q * 32 + lane);
+        bool ok = true;
+        while (ok && sched.next(t)) {
+            if (t.group < 0) continue;
+            const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
+            ++iter;
+            ok = mbar_wait(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16);
+            const bool store = r < t.rows_store;
+            const long long row = static_cast<long long>(t.row_start) + r;
+            if constexpr (EPI == kEpiBF16 || EPI == kEpiF32 || EPI == kEpiScatter) {
+                __nv_bfloat16* scatter_row = nullptr;
+                if constexpr (EPI == kEpiScatter) {
+                    if (store) {
+                        const int src = __ldg(p.row_src + row);
+                        const int per_rank = p.combine_tokens * p.topk;
+                        const int rank = src / per_rank, entry = src - rank * per_rank;
+                        const int token = entry / p.topk, slot = entry - token * p.topk;
+                        scatter_row = reinterpret_cast<__nv_bfloat16*>(p.combine_base[rank]) +
+                                      (static_cast<long long>(slot) * p.combine_tokens + token) * p.n;
+                    }
+                }
+#pragma unroll 1
+                for (int c = 0; c < BLOCK_N / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_row + c * 32, v);
+                    tmem_ld_wait();
+                    if (store) {
+                        const long long col = static_cast<long long>(t.n_block) * BLOCK_N + c * 32;
+                        if constexpr (EPI == kEpiBF16 || EPI == kEpiScatter) {
+                            __nv_bfloat16* dst = EPI == kEpiScatter
+                                ? scatter_row + col
+                                : reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                st_global_v4(dst + i * 8,
+                                             pack_bf16x2(__uint_as_float(v[i * 8 + 0]), __uint_as_float(v[i * 8 + 1])),
+                                             pack_bf16x2(__uint_as_float(v[i * 8 + 2]), __uint_as_float(v[i * 8 + 3])),
+                                             pack_bf16x2(__uint_as_float(v[i * 8 + 4]), __uint_as_float(v[i * 8 + 5])),
+                                             pack_bf16x2(__uint_as_float(v[i * 8 + 6]), __uint_as_float(v[i * 8 + 7])));
+                        } else {
+                            float* dst = reinterpret_cast<float*>(p.d) + row * p.d_row_stride + col;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                st_global_v4(dst + i * 4, v[i * 4 + 0], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+                        }
+                    }
+                }
+            } else {
+                // Columns of this tile: [gate j..j+31 | up j..j+31 | gate j+32..j+63 | up j+32..j+63] (and again
+                // for BLOCK_N == 256), j = n_block * BLOCK_N / 2. One 32-wide output group = one UE8M0 scale.
+                const float w = (store && p.row_weight != nullptr) ? __ldg(p.row_weight + row) : 1.0f;
+#pragma unroll 1
+                for (int c = 0; c < BLOCK_N / 64; ++c) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32b_x32(tmem_row + c * 64, g);
+                    tmem_ld_32x32b_x32(tmem_row + c * 64 + 32, u);
+                    tmem_ld_wait();
+                    float o[32];
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float gv = bf16_round(__uint_as_float(g[i]));
+                        float uv = bf16_round(__uint_as_float(u[i]));
+                        if (p.clamp > 0.0f) {
+                            gv = fminf(gv, p.clamp);
+                            uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                        }
+                        const float silu = gv / (1.0f + __expf(-gv));
+                        o[i] = silu * uv * w;
+                        amax = fmaxf(amax, fabsf(o[i]));
+                    }
+                    float sf_inv;
+                    uint32_t sf_byte;
+                    ue8m0_scale_for_amax(amax, sf_inv, sf_byte);
+                    if (store) {
+                        const int j = t.n_block * (BLOCK_N / 2) + c * 32;  // first output channel of the group
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const __nv_fp8x4_e4m3 q4(make_float4(o[i * 4 + 0] * sf_inv, o[i * 4 + 1] * sf_inv,
+                                                                 o[i * 4 + 2] * sf_inv, o[i * 4 + 3] * sf_inv));
+                            packed[i] = q4.__x;
+                        }
+                        unsigned char* dst = p.act_q + row * p.act_q_row_stride + j;
+                        st_global_v4(dst, packed[0], packed[1], packed[2], packed[3]);
+                        st_global_v4(dst + 16, packed[4], packed[5], packed[6], packed[7]);
+                        p.act_sf[(static_cast<long long>(j / 128) * p.act_sf_k_stride + row) * 4 + ((j / 32) & 3)] =
+                            static_cast<unsigned char>(sf_byte);
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            mbar_arrive(tmem_empty_bar + as);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        // Let copies and MMAs that were already issued land before shared and tensor memory are released.
+        __nanosleep(100000);
+        __syncthreads();
+    }
+    if (warp == 2) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace dgb

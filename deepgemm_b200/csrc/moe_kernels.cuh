@@ -1,0 +1,189 @@
+// Dispatch (count / slot assignment / gather) and combine kernels of the MoE layer. All HBM-bound integer and
+// byte work: coalesced 16-byte vectors, scale factors transposed through shared memory.
+//
+// Reference counterparts (inside the fused kernel deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh):
+//   count + slot assignment  :329-399   (atomics; arrival-order dependent)
+//   token pull into the L1 ring :461-599
+//   combine                  :1323-1452
+// Differences by design: slot assignment here is a deterministic stable sort of the (token, k) entries by expert
+// (entry order = token-major), so the permutation is reproducible bit for bit; and each expert segment is padded
+// only to `alignment` rows (4..128) instead of to a full M block, because the GEMM clips its stores per group.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+
+namespace dgb {
+
+constexpr int kPlanChunk = 1024;  // (token, k) entries per CTA in the count / assign kernels
+
+// chunk_hist[chunk][e] = number of entries of `chunk` routed to local expert e.
+// An entry is local when expert_lo <= topk_idx < expert_lo + num_local_experts.
+__global__ void __launch_bounds__(kPlanChunk)
+dgb200_moe_count_kernel(const long long* __restrict__ topk_idx, int num_entries, int expert_lo, int num_local_experts,
+                        int* __restrict__ chunk_hist) {
+    extern __shared__ int hist[];
+    for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * kPlanChunk + threadIdx.x;
+    if (i < num_entries) {
+        const long long e = topk_idx[i] - expert_lo;
+        if (e >= 0 && e < num_local_experts) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x)
+        chunk_hist[static_cast<long long>(blockIdx.x) * num_local_experts + e] = hist[e];
+}
+
+// One CTA. Turns chunk_hist into exclusive per-chunk bases, and produces per expert: count, aligned segment start,
+// segment end (the psum layout the grouped GEMM walks). total_rows[0] = end of the last segment.
+__global__ void __launch_bounds__(1024)
+dgb200_moe_scan_kernel(int* __restrict__ chunk_hist, int num_chunks, int num_local_experts, int alignment,
+                       int* __restrict__ expert_start, int* __restrict__ expert_end, int* __restrict__ total_rows,
+                       int* __restrict__ cumulative_stats) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < num_local_experts; base += 1024) {
+        const int e = base + static_cast<int>(threadIdx.x);
+        int count = 0;
+        if (e < num_local_experts) {
+            for (int c = 0; c < num_chunks; ++c) {
+                int* slot = chunk_hist + static_cast<long long>(c) * num_local_experts + e;
+                const int t = *slot;
+                *slot = count;
+                count += t;
+            }
+            if (cumulative_stats != nullptr) cumulative_stats[e] += count;
+        }
+        const int padded = (count + alignment - 1) / alignment * alignment;
+        // block-wide exclusive scan of `padded`
+        int incl = padded;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        for (int off = 1; off < 32; off <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += n;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+            for (int off = 1; off < 32; off <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, w, off);
+                if (lane >= off) w += n;
+            }
+            warp_sums[lane] = w;
+        }
+        __syncthreads();
+        const int start = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - padded;
+        if (e < num_local_experts) {
+            expert_start[e] = start;
+            expert_end[e] = start + count;
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = start + padded;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) total_rows[0] = carry;
+}
+
+// dest_row[entry] = expert_start[e] + (entries of the same expert that precede it), or -1 when not local;
+// src_of_row[dest] = entry; row_weight[dest] = topk_weights[entry].
+__global__ void __launch_bounds__(kPlanChunk)
+dgb200_moe_assign_kernel(const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights, int num_entries,
+                         int expert_lo, int num_local_experts, const int* __restrict__ chunk_hist,
+                         const int* __restrict__ expert_start, int* __restrict__ dest_row, int* __restrict__ src_of_row,
+                         float* __restrict__ row_weight) {
+    extern __shared__ unsigned char warp_hist[];  // [32 warps][num_local_experts], counts <= 32
+    for (int i = threadIdx.x; i < 32 * num_local_experts; i += blockDim.x) warp_hist[i] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * kPlanChunk + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int e = -1;
+    if (i < num_entries) {
+        const long long g = topk_idx[i] - expert_lo;
+        if (g >= 0 && g < num_local_experts) e = static_cast<int>(g);
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_hist[warp * num_local_experts + e] = static_cast<unsigned char>(__popc(peers));
+    __syncthreads();
+    if (i >= num_entries) return;
+    if (e < 0) {
+        dest_row[i] = -1;
+        return;
+    }
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_hist[w * num_local_experts + e];
+    const int dest = expert_start[e] + chunk_hist[static_cast<long long>(blockIdx.x) * num_local_experts + e] + before +
+                     rank_in_warp;
+    dest_row[i] = dest;
+    src_of_row[dest] = i;
+    row_weight[dest] = topk_weights[i];
+}
+
+// Gathers FP8 token rows and their packed scales into expert-sorted order. One CTA per 32 destination rows.
+//   x      e4m3 [tokens, hidden]           x_sf  int32 [tokens, hidden / 128] (token-major, 4 UE8M0 bytes per int)
+//   acts   e4m3 [rows, hidden]             acts_sf int32 MN-major: int (kp, row) at acts_sf[kp * sf_k_stride + row]
+// Rows whose src_of_row is negative (segment padding) are left untouched.
+__global__ void __launch_bounds__(256)
+dgb200_moe_gather_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
+                         const int* __restrict__ src_of_row, const int* __restrict__ total_rows, int topk, int hidden,
+                         unsigned char* __restrict__ acts, unsigned* __restrict__ acts_sf, long long sf_k_stride) {
+    extern __shared__ unsigned sf_tile[];  // [hidden / 128][33]
+    const int row0 = blockIdx.x * 32;
+    if (row0 >= total_rows[0]) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sf_per_row = hidden / 128;
+    for (int rr = 0; rr < 4; ++rr) {
+        const int r = warp * 4 + rr;
+        const int src = src_of_row[row0 + r];
+        if (src < 0) continue;
+        const int token = src / topk;
+        const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * hidden);
+        uint4* to = reinterpret_cast<uint4*>(acts + static_cast<long long>(row0 + r) * hidden);
+        for (int c = lane; c < hidden / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
+        for (int c = lane; c < sf_per_row; c += 32) sf_tile[c * 33 + r] = x_sf[static_cast<long long>(token) * sf_per_row + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < sf_per_row * 32; i += 256) {
+        const int c = i >> 5, r = i & 31;
+        if (src_of_row[row0 + r] >= 0) acts_sf[static_cast<long long>(c) * sf_k_stride + row0 + r] = sf_tile[c * 33 + r];
+    }
+}
+
+// y[t, :] = bf16( sum over valid k, in ascending k, of float(combine[k][t, :]) ); slot k of token t is valid when
+// dest_row[t * topk + k] >= 0. combine is bf16 [topk][combine_tokens][hidden].
+// One CTA per token; a thread owns 8 consecutive channels (one 16-byte vector per slot).
+__global__ void __launch_bounds__(128)
+dgb200_moe_combine_kernel(const __nv_bfloat16* __restrict__ combine, const int* __restrict__ dest_row, int topk,
+                          int combine_tokens, int hidden, __nv_bfloat16* __restrict__ y) {
+    const int t = blockIdx.x;
+    extern __shared__ int valid[];
+    if (threadIdx.x < topk) valid[threadIdx.x] = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
+    __syncthreads();
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int k = 0; k < topk; ++k) {
+            if (valid[k] < 0) continue;
+            const __nv_bfloat16* row = combine + (static_cast<long long>(k) * combine_tokens + t) * hidden;
+            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(row) + c);
+            const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += __uint_as_float(w[i] << 16);
+                acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        reinterpret_cast<uint4*>(y + static_cast<long long>(t) * hidden)[c] = o;
+    }
+}
+
+}  // namespace dgb

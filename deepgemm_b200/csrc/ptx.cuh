@@ -1,0 +1,320 @@
+// Hand-written PTX wrappers for sm_100a: mbarrier, TMA (tiled and 1-D bulk), tcgen05
+// (TMEM alloc, block-scaled MMA, smem->TMEM copy, TMEM load, commit) and the shared-memory /
+// instruction descriptors they consume.
+//
+// Behavioural counterparts in the reference: deep_gemm/include/deep_gemm/ptx/{tcgen05,tma,ld_st,utils}.cuh
+// and deep_gemm/include/deep_gemm/mma/sm100.cuh:14-165 (descriptor builders). The reference obtains
+// its descriptor bitfields from CuTe; here they are built with plain shifts from the PTX ISA tables.
+//
+// Every wait in this file is bounded: a wait that runs out records a code in the device status
+// block and returns false, so a kernel can unwind (free TMEM, return) instead of hanging the GPU.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace dgb {
+
+// ----------------------------------------------------------------------------------------------
+// Device status block: one per device that loads the library (the library is a single translation
+// unit, so the definition lives here).
+// word 0: first error code (0 = OK), word 1: block index, word 2: detail a, word 3: detail b.
+// ----------------------------------------------------------------------------------------------
+__device__ int g_status[8];
+
+enum StatusCode : int {
+    kOk = 0,
+    kTimeoutFull = 1,       // consumer waited for TMA data
+    kTimeoutEmpty = 2,      // producer waited for a free stage
+    kTimeoutSfReady = 3,    // MMA warp waited for the scale-factor transposer
+    kTimeoutTmemFull = 4,   // epilogue waited for the accumulator
+    kTimeoutTmemEmpty = 5,  // MMA warp waited for the epilogue to drain the accumulator
+    kBadArgument = 6,
+    kTimeoutPeer = 7,       // waited for a flag another rank writes
+    kTimeoutGrid = 8,       // waited for a flag another CTA of this grid writes
+};
+
+__device__ __forceinline__ void report_error(int code, int a, int b) {
+    if (atomicCAS(&g_status[0], 0, code) == 0) {
+        g_status[1] = static_cast<int>(blockIdx.x);
+        g_status[2] = a;
+        g_status[3] = b;
+    }
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint32_t lane_id() {
+    uint32_t l;
+    asm volatile("mov.u32 %0, %%laneid;" : "=r"(l));
+    return l;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n" : "=r"(pred));
+    return pred != 0;
+}
+
+// ----------------------------------------------------------------------------------------------
+// mbarrier
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                 :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Budget of one wait. Two seconds is several orders of magnitude above any legitimate stage wait.
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+
+// Bounded wait. `abort_flag` is a CTA-shared word: once any role of the CTA gives up, the others
+// stop at their next poll instead of each burning their own budget.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          int code, int detail) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (((++spins) & 0xffu) == 0) {
+            if (*abort_flag != 0) return false;
+            if (global_timer_ns() - t0 > kWaitBudgetNs) {
+                *abort_flag = static_cast<uint32_t>(code);
+                report_error(code, detail, static_cast<int>(parity));
+                return false;
+            }
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// TMA: tiled 2-D load (CTA-local destination, completion on a CTA-local mbarrier) and 1-D bulk load
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// `bytes` must be a multiple of 16; both addresses 16-byte aligned.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        :: "r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// ----------------------------------------------------------------------------------------------
+// tcgen05: tensor memory management
+// ----------------------------------------------------------------------------------------------
+// Warp-collective. `num_cols` is a power of two in [32, 512]. The base address lands in `*smem_dst`.
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t num_cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(smem_dst)), "r"(num_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t tmem_addr, uint32_t num_cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_addr), "r"(num_cols) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// All previously issued tcgen05.mma / tcgen05.cp of this thread arrive on `bar` when they retire.
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 :: "r"(smem_u32(bar)) : "memory");
+}
+
+// ----------------------------------------------------------------------------------------------
+// Descriptors
+// ----------------------------------------------------------------------------------------------
+// 64-bit shared-memory matrix descriptor (PTX ISA, tcgen05 "shared memory descriptor"):
+//   [0,14)  start address >> 4          [16,30) leading-dimension byte offset >> 4
+//   [32,46) stride-dimension byte offset >> 4   [46,48) descriptor version (1 on sm_100)
+//   [49,52) base offset                 [52]    LBO mode          [61,64) swizzle mode
+// Swizzle codes: 0 none, 1 128B with 32B atoms, 2 128B, 4 64B, 6 32B.
+constexpr uint64_t kSwizzleNone = 0, kSwizzle128B = 2;
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes, uint64_t swizzle) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>(sbo_bytes >> 4) << 32;
+    d |= 1ull << 46;
+    d |= swizzle << 61;
+    return d;
+}
+
+// K-major operand tile whose rows are exactly one 128-byte swizzle span: 8-row groups are 1024 B apart.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    return make_smem_desc(smem_addr, 1024, kSwizzle128B);
+}
+
+// Scale-factor block for tcgen05.cp 32x128b: 32 rows of 16 bytes, contiguous; 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+    return make_smem_desc(smem_addr, 128, kSwizzleNone);
+}
+
+// 32-bit instruction descriptor of the block-scaled kinds (PTX ISA, tcgen05 "instruction descriptor"):
+//   [4,6) B scale-factor id   [7,10) A format   [10,13) B format   [13] negate A  [14] negate B
+//   [15] A MN-major  [16] B MN-major  [17,23) N >> 3   [23] scale type (0 UE4M3, 1 UE8M0)
+//   [24,29) M >> 4   [29,31) A scale-factor id
+// Element format codes: kind::mxf8f6f4 -> E4M3 0, E5M2 1, E2M3 3, E3M2 4, E2M1 5; kind::mxf4* -> E2M1 1.
+constexpr uint32_t kFmtE4M3 = 0, kFmtE2M1_F8F6F4 = 5, kFmtE2M1_MXF4 = 1;
+constexpr uint32_t kScaleUE4M3 = 0, kScaleUE8M0 = 1;
+
+__host__ __device__ constexpr uint32_t make_idesc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                               uint32_t scale_type) {
+    return (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (scale_type << 23) | ((m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t idesc_with_sf_ids(uint32_t idesc, uint32_t a_sf_id, uint32_t b_sf_id) {
+    return idesc | (a_sf_id << 29) | (b_sf_id << 4);
+}
+
+// ----------------------------------------------------------------------------------------------
+// tcgen05: data movement and MMA
+// ----------------------------------------------------------------------------------------------
+// Copies 32 rows x 16 B from shared memory into 4 TMEM columns, replicated to all four 32-lane quarters.
+__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4(uint32_t tmem_addr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(tmem_addr), "l"(sdesc) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T with per-block scales; FP8/FP6/FP4 operands, one UE8M0 scale per 32 K.
+__device__ __forceinline__ void tcgen05_mma_mxf8f6f4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// Packed E2M1 x E2M1, K = 64 per instruction, one UE4M3 scale per 16 K (NVFP4).
+__device__ __forceinline__ void tcgen05_mma_mxf4nvf4_4x(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                        uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// Packed E2M1 x E2M1, K = 64 per instruction, one UE8M0 scale per 32 K (MXFP4 on both sides).
+__device__ __forceinline__ void tcgen05_mma_mxf4_2x(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// Each lane reads 32 consecutive 32-bit columns of its own TMEM lane (lane quarter = warp index % 4).
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t tmem_addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(tmem_addr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------------------------
+// Global-memory helpers
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" :: "l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_global_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float bf16_round(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+// Programmatic dependent launch: wait for the preceding kernel's memory to be visible / let the next one start.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+}  // namespace dgb
