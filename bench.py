@@ -1,0 +1,374 @@
+"""Benchmark of the Mega-MoE hot path: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
+
+Metric (BASELINE.json): MoE layer tokens/s (whole job) with the fraction of the B200 roofline that explains it.
+One "step" = one pass of the layer over one batch of synthetic tokens:
+    router (sigmoid, top-8, renormalise) -> BF16->FP8 per-32 quantisation -> dispatch -> L1 GEMM + SwiGLU + FP8 requant
+    -> L2 GEMM -> weighted top-k combine.
+N = 1 runs BASELINE config 3 (4096 tokens, hidden 7168, 256 MXFP4 experts, top-8, intermediate 2048).
+Prints ONE JSON line (rank 0). `value` is timed with inputs resident in HBM; `e2e` includes the per-step
+host->device copy of the inputs (pinned memory) and the device->host copy of y.
+`--impl reference` times the CPU restatement of the reference arithmetic (oracle/) on the host cores instead.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONFIG3 = dict(tokens=4096, hidden=7168, inter=2048, experts=256, topk=8)
+METRIC = 'mega_moe_layer_tokens_per_s'
+CPU_SAMPLE_EXPERTS = 4  # experts whose routed rows the CPU legs evaluate per pass
+FP4_DENSE_PEAK_TFLOPS_NOMINAL = 9000.0
+FP8_DENSE_PEAK_TFLOPS_NOMINAL = 4500.0
+# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture, or None while unmeasured.
+L1_KERNEL_DRAM_TRAFFIC_BYTES = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--tokens', type=int, default=0, help='override tokens per rank (debugging only)')
+    ap.add_argument('--skip-cpu-baseline', action='store_true')
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+              'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.file = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
+                                          '-lms', '100', '-i', str(self.gpu_index)], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.proc.wait()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, max_clock, reasons = [], None, set()
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), parts[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        clocks.sort()
+        return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None, 'sm_max_mhz': max_clock,
+                'samples': len(clocks), 'reasons': sorted(reasons)}
+
+
+def cpu_sample_pass(sample):
+    """One pass of the oracle over the sampled experts: dequantise weights on the fly, L1, SwiGLU + requant, L2.
+    Returns the number of routed rows processed."""
+    import torch
+    from oracle import moe as omoe
+    from oracle import quant
+    rows = 0
+    for e in range(len(sample['l1_q'])):
+        x_q, x_sf, w = sample['x_q'][e], sample['x_sf'][e], sample['w'][e]
+        if x_q.shape[0] == 0:
+            continue
+        acc1 = quant.dequantize_fp8(x_q, x_sf, 32) @ quant.dequantize_fp4(sample['l1_q'][e], sample['l1_sf'][e], 32).T
+        a2_q, a2_sf = omoe.swiglu_requant(acc1, w, None)
+        acc2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(sample['l2_q'][e], sample['l2_sf'][e], 32).T
+        sample['out'] = acc2.to(torch.bfloat16)
+        rows += x_q.shape[0]
+    return rows
+
+
+def time_cpu_sample(sample, steps, warmup):
+    import torch
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows = 0
+    for _ in range(warmup):
+        rows = cpu_sample_pass(sample)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        rows = cpu_sample_pass(sample)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return rows, dt, torch.get_num_threads()
+
+
+def make_cpu_sample_on_cpu(cfg, seed=0):
+    """Seeded CPU-only inputs for the reference arm: all tokens routed over all experts, rows of the first
+    CPU_SAMPLE_EXPERTS experts kept; their weights drawn ~N(0, 0.02) and quantised to MXFP4 by the oracle."""
+    import torch
+    from oracle import moe as omoe
+    from oracle import quant
+    torch.manual_seed(seed)
+    x = torch.randn(cfg['tokens'], cfg['hidden']).bfloat16()
+    idx, w = omoe.route_sigmoid_topk(torch.randn(cfg['tokens'], cfg['experts']), cfg['topk'])
+    x_q, x_sf = quant.quantize_fp8_per_token(x, 32)
+    sample = {k: [] for k in ('x_q', 'x_sf', 'w', 'l1_q', 'l1_sf', 'l2_q', 'l2_sf')}
+    for e in range(CPU_SAMPLE_EXPERTS):
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        sample['x_q'].append(x_q[tok])
+        sample['x_sf'].append(x_sf[tok])
+        sample['w'].append(w[tok, slot])
+        q, sf = quant.quantize_fp4_per_token((torch.randn(2 * cfg['inter'], cfg['hidden']) * 0.02).bfloat16(), 32)
+        sample['l1_q'].append(q)
+        sample['l1_sf'].append(sf)
+        q, sf = quant.quantize_fp4_per_token((torch.randn(cfg['hidden'], cfg['inter']) * 0.02).bfloat16(), 32)
+        sample['l2_q'].append(q)
+        sample['l2_sf'].append(sf)
+    return sample
+
+
+def sample_description(cfg, rows):
+    return (f'routed rows of experts 0..{CPU_SAMPLE_EXPERTS - 1} of the same workload ({rows} of '
+            f'{cfg["tokens"] * cfg["topk"]} rows), weights dequantised on the fly, torch fp32 matmul')
+
+
+def run_reference(args, cfg, rank, world):
+    """CPU restatement of the reference arithmetic (oracle/), all host threads, on a bounded sample."""
+    if rank != 0:
+        return
+    sample = make_cpu_sample_on_cpu(cfg)
+    rows, dt, cores = time_cpu_sample(sample, args.steps, args.warmup)
+    value = rows / cfg['topk'] / dt
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8xfp4 (fp32 accumulate)', 'data': 'synthetic',
+        'config': workload_config(cfg, args.gpus),
+        'cpu_baseline': {'value': value, 'unit': 'tokens/s', 'cores': cores, 'kind': 'port',
+                         'sample': sample_description(cfg, rows)},
+        'e2e': {'value': value, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, gpus):
+    name = ('single-GPU full MoE layer, MXFP4 weights (BASELINE config 3)' if gpus == 1 else
+            f'{gpus}-GPU expert-parallel MoE layer, MXFP4 weights (BASELINE config 5)')
+    return {'workload': name, 'tokens_per_rank': cfg['tokens'], 'hidden': cfg['hidden'],
+            'intermediate': cfg['inter'], 'experts': cfg['experts'], 'topk': cfg['topk'],
+            'activations': 'fp8 e4m3, 1x32 ue8m0', 'weights': 'mxfp4 e2m1, 1x32 ue8m0',
+            'l2_policy': 'inputs larger than L2 (about 6 GB of expert weights streamed every step)'}
+
+
+def build_layer(dg, cfg, keep_cpu_experts):
+    """Random expert weights ~N(0, 0.02), quantised to MXFP4 on the GPU expert by expert (bounds memory), packed and
+    transformed for the layer. Returns (l1, l2, cpu copies of the first `keep_cpu_experts` experts' quantised weights)."""
+    import torch
+    e, h, i = cfg['local_experts'], cfg['hidden'], cfg['inter']
+    l1_q = torch.empty((e, 2 * i, h // 2), dtype=torch.int8, device='cuda')
+    l1_sf = torch.empty((e, 2 * i, h // 32), dtype=torch.float32, device='cuda')
+    l2_q = torch.empty((e, h, i // 2), dtype=torch.int8, device='cuda')
+    l2_sf = torch.empty((e, h, i // 32), dtype=torch.float32, device='cuda')
+    for g in range(e):
+        w = torch.randn(2 * i, h, device='cuda', dtype=torch.bfloat16) * 0.02
+        l1_q[g], l1_sf[g] = dg.utils.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+        w = torch.randn(h, i, device='cuda', dtype=torch.bfloat16) * 0.02
+        l2_q[g], l2_sf[g] = dg.utils.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+    cpu = {k: [t[g].cpu() for g in range(keep_cpu_experts)]
+           for k, t in (('l1_q', l1_q), ('l1_sf', l1_sf), ('l2_q', l2_q), ('l2_sf', l2_sf))}
+    l1_sf_p = dg.transform_sf_into_required_layout(l1_sf, 2 * i, h, (1, 32), e)
+    l2_sf_p = dg.transform_sf_into_required_layout(l2_sf, h, i, (1, 32), e)
+    del l1_sf, l2_sf
+    l1, l2 = dg.transform_weights_for_mega_moe((l1_q, l1_sf_p), (l2_q, l2_sf_p))
+    del l1_q, l1_sf_p
+    torch.cuda.empty_cache()
+    return l1, l2, cpu
+
+
+def run_ours(args, cfg, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+
+    if world > 1:
+        raise SystemExit('the expert-parallel (multi-GPU) layer is not built yet')
+    torch.cuda.set_device(local_rank)
+    torch.manual_seed(1234 + rank)
+    t, h, i, e, k = cfg['tokens'], cfg['hidden'], cfg['inter'], cfg['experts'], cfg['topk']
+    cfg['local_experts'] = e // world
+    l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 else 0)
+    buf = dg.get_symm_buffer_for_mega_moe(None, e, t, k, h, i)
+    x_host = torch.randn(t, h).bfloat16().pin_memory()
+    logits_host = torch.randn(t, e).pin_memory()
+    y_host = torch.empty((t, h), dtype=torch.bfloat16).pin_memory()
+    x = x_host.cuda()
+    logits = logits_host.cuda()
+    y = torch.empty((t, h), dtype=torch.bfloat16, device='cuda')
+    lib = _lib.lib()
+    kernels_per_step = 9  # router, cast, count, scan, assign, gather, L1, L2, combine (the one memset is not a kernel of ours)
+
+    def step(events=None):
+        dg.route_sigmoid_topk(logits, k, buf.topk_idx, buf.topk_weights)
+        dg.utils.per_token_cast_to_fp8_into(x, buf.x, buf.x_sf, gran_k=32)
+        if events is not None:
+            arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
+            _lib.check(lib.dgb200_set_mega_moe_stage_events(ctypes.cast(arr, ctypes.c_void_p), len(events)))
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    status = _lib.device_status()
+    stage_events = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(args.steps)]
+    for evs in stage_events:  # create the underlying handles before they are handed to the library
+        for ev in evs:
+            ev.record()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for s in range(args.steps):
+        step(stage_events[s])
+    t1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_per_step = t0.elapsed_time(t1) / args.steps
+    status = _lib.device_status()
+    stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_events) / args.steps for j in range(5)]
+
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        logits.copy_(logits_host, non_blocking=True)
+        step()
+        y_host.copy_(y, non_blocking=True)
+    for _ in range(max(args.warmup, 3)):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    _lib.device_status()
+
+    # ---- algorithmic work of this batch
+    lay = buf.layout
+    ends = buf.buffer[lay['expert_end']:lay['expert_end'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
+    starts = buf.buffer[lay['expert_start']:lay['expert_start'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
+    rows = int((ends - starts).sum())
+    touched = int(((ends - starts) > 0).sum())
+    flops = 2.0 * rows * h * i * 3
+    l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 32) + rows * (h + h // 32) + rows * (i + i // 32)
+    l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
+    times = torch.tensor([ms_per_step, e2e_ms] + stage_ms, dtype=torch.float64, device='cuda')
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_per_step, e2e_ms = float(times[0]), float(times[1])
+    stage_ms = [float(v) for v in times[2:]]
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    l1_gbs = l1_bytes / (stage_ms[2] * 1e-3) / 1e9
+    tflops = flops / (ms_per_step * 1e-3) / 1e12
+    line = {
+        'metric': METRIC, 'value': t * world / (ms_per_step * 1e-3), 'unit': 'tokens/s', 'n_gpus': world,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8xfp4 (fp32 accumulate)', 'data': 'synthetic',
+        'config': workload_config(cfg, world),
+        'e2e': {'value': t * world / (e2e_ms * 1e-3), 'unit': 'tokens/s', 'ms_per_step': e2e_ms,
+                'h2d_bytes_per_step': x_host.numel() * 2 + logits_host.numel() * 4, 'd2h_bytes_per_step': y_host.numel() * 2},
+        'gpu_launches': kernels_per_step * args.steps,
+        'clocks': clocks,
+        'roofline': {'kernel': 'dgb200_grouped_gemm_kernel (L1: gate/up GEMM + SwiGLU + FP8 requant)', 'bound': 'hbm',
+                     'achieved': l1_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': l1_gbs / peak, 'peak_source': peak_kind,
+                     'traffic': L1_KERNEL_DRAM_TRAFFIC_BYTES, 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]},
+        'stages_ms': {'plan': stage_ms[0], 'gather': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
+                      'l2_gemm_scatter': stage_ms[3], 'combine': stage_ms[4]},
+        'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9,
+        'tflops': tflops,
+        'frac_fp4_dense_peak_nominal': tflops / FP4_DENSE_PEAK_TFLOPS_NOMINAL,
+        'frac_fp8_rate_peak_nominal': tflops / FP8_DENSE_PEAK_TFLOPS_NOMINAL,
+        'routed_rows': rows,
+    }
+    if world == 1 and not args.skip_cpu_baseline:
+        idx, w = buf.topk_idx[:t].cpu(), buf.topk_weights[:t].cpu()
+        from oracle import quant
+        x_q_c, x_sf_c = buf.x[:t].cpu(), quant.unpack_ue8m0(buf.x_sf[:t].cpu())
+        sample = dict(cpu_weights)
+        sample.update({'x_q': [], 'x_sf': [], 'w': []})
+        for g in range(CPU_SAMPLE_EXPERTS):
+            tok, slot = torch.nonzero(idx == g, as_tuple=True)
+            sample['x_q'].append(x_q_c[tok])
+            sample['x_sf'].append(x_sf_c[tok])
+            sample['w'].append(w[tok, slot])
+        srows, dt, cores = time_cpu_sample(sample, 3, 1)
+        line['cpu_baseline'] = {'value': srows / k / dt, 'unit': 'tokens/s', 'cores': cores, 'kind': 'port',
+                                'sample': sample_description(cfg, srows)}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    cfg = dict(CONFIG3)
+    if args.gpus > 1:
+        cfg['tokens'] = 8192
+    if args.tokens:
+        cfg['tokens'] = args.tokens
+    if args.impl == 'reference':
+        run_reference(args, cfg, rank, world)
+        return
+    if world != args.gpus:
+        raise SystemExit(f'--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)')
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl')
+    run_ours(args, cfg, rank, world, local_rank)
+
+
+if __name__ == '__main__':
+    main()

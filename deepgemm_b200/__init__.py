@@ -1,0 +1,45 @@
+"""deepgemm_b200: the Mega-MoE hot path of DeepGEMM rebuilt for B200 (sm_100a).
+
+Same operator names and argument conventions as the reference package (deep_gemm/__init__.py:17-97) for the
+path it covers; use ``import deepgemm_b200 as deep_gemm``. Every operator calls libdgb200.so through its C ABI
+(include/dgb200.h); there is no CPU or PyTorch fallback.
+"""
+from . import _lib, testing, utils  # noqa: F401
+from .gemm import (  # noqa: F401
+    m_grouped_fp8_fp4_gemm_nn_contiguous,
+    m_grouped_fp8_fp4_gemm_nt_contiguous,
+    m_grouped_fp8_fp4_gemm_nt_masked,
+    m_grouped_fp8_gemm_nn_contiguous,
+    m_grouped_fp8_gemm_nt_contiguous,
+    m_grouped_fp8_gemm_nt_masked,
+)
+from .layout import (  # noqa: F401
+    get_mn_major_tma_aligned_packed_ue8m0_tensor,
+    get_tma_aligned_size,
+    transform_sf_into_required_layout,
+)
+from .mega import (  # noqa: F401
+    SymmBuffer,
+    fp8_fp4_mega_moe,
+    get_block_m_for_mega_moe,
+    get_symm_buffer_for_mega_moe,
+    get_token_alignment_for_mega_moe,
+    route_sigmoid_topk,
+    transform_weights_for_mega_moe,
+)
+from .runtime import (  # noqa: F401
+    get_mk_alignment_for_contiguous_layout,
+    get_num_sms,
+    get_pdl,
+    get_tc_util,
+    get_theoretical_mk_alignment_for_contiguous_layout,
+    init,
+    set_block_size_multiple_of,
+    set_ignore_compile_dims,
+    set_mk_alignment_for_contiguous_layout,
+    set_num_sms,
+    set_pdl,
+    set_tc_util,
+)
+
+__version__ = '0.1.0'

@@ -45,14 +45,6 @@ struct GemmCall {
     int max_tiles;  // upper bound on tiles, <= 0 if unknown
 };
 
-int debug_b_tx_mode() {
-    static int mode = [] {
-        const char* s = std::getenv("DGB200_DEBUG_B_TX_SMEM_BYTES");
-        return (s != nullptr && s[0] == '1') ? 1 : 0;
-    }();
-    return mode;
-}
-
 int run_gemm(GemmCall& c, cudaStream_t stream) {
     GemmParams& p = c.p;
     DGB_REQUIRE(p.k > 0 && p.k % 128 == 0, "k (%d) must be a positive multiple of 128", p.k);
@@ -84,7 +76,7 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
         p.b_fmt = kFmtE2M1_F8F6F4;
         // Packed FP4 expands to one byte per element in shared memory; the mbarrier is credited with the
         // bytes read from global memory (half the tile).
-        p.b_tx_bytes = debug_b_tx_mode() ? BLOCK_N * 128 : BLOCK_N * 64;
+        p.b_tx_bytes = BLOCK_N * 64;
     } else {
         rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, static_cast<uint64_t>(p.k), b_rows,
                                 static_cast<uint64_t>(p.k), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -115,7 +107,17 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 // layer (the reference's counterpart: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155, and
 // deep_gemm/include/deep_gemm/layout/mega_moe.cuh:46-443). All regions start on 1024-byte boundaries.
 // --------------------------------------------------------------------------------------------------------------
-constexpr int kSegmentAlignment = 16;  // rows each expert segment is padded to in the expert-sorted buffers
+constexpr int kSegmentAlignment = 16;
+
+// Optional CUDA events the next mega-MoE call records at its stage boundaries (set per host thread, used once).
+constexpr int kNumStageEvents = 6;
+thread_local cudaEvent_t g_stage_events[kNumStageEvents];
+thread_local int g_num_stage_events = 0;
+
+int record_stage(int index, cudaStream_t stream) {
+    if (index < g_num_stage_events) DGB_CUDA(cudaEventRecord(g_stage_events[index], stream));
+    return 0;
+}  // rows each expert segment is padded to in the expert-sorted buffers
 
 struct MegaLayout {
     long long x, x_sf, topk_idx, topk_weights;                            // inputs, written by the caller
@@ -167,14 +169,16 @@ int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, i
 }
 
 int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, int gran_k, void* q, long long q_row_stride,
-             float* sf_f32, void* sf_packed, long long sf_k_stride, cudaStream_t stream) {
+             float* sf_f32, void* sf_packed, long long sf_k_stride, long long sf_row_stride, cudaStream_t stream) {
     DGB_REQUIRE(rows >= 0 && k > 0 && k % 16 == 0, "k (%d) must be a positive multiple of 16", k);
     DGB_REQUIRE(gran_k == 32 || gran_k == 128, "gran_k must be 32 or 128, got %d", gran_k);
     DGB_REQUIRE(x != nullptr && q != nullptr, "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0 && (x_row_stride * 2) % 16 == 0, "x rows must be 16-byte aligned");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(q) % 16 == 0 && q_row_stride % (fp4 ? 8 : 16) == 0, "q rows must be 16-byte aligned");
     DGB_REQUIRE(sf_f32 != nullptr || sf_packed != nullptr, "at least one scale-factor output is required");
-    DGB_REQUIRE(sf_packed == nullptr || sf_k_stride >= rows, "packed scale-factor MN stride smaller than rows");
+    DGB_REQUIRE(sf_packed == nullptr || (sf_row_stride == 1 && sf_k_stride >= rows) ||
+                    (sf_k_stride == 1 && sf_row_stride >= (k + gran_k * 4 - 1) / (gran_k * 4)),
+                "packed scale-factor strides must be (k stride >= rows, row stride 1) or (k stride 1, row stride >= packed k)");
     if (rows == 0) return 0;
     CastParams p{};
     p.x = static_cast<const __nv_bfloat16*>(x);
@@ -184,6 +188,7 @@ int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, i
     p.sf_f32 = sf_f32;
     p.sf_packed = static_cast<uint32_t*>(sf_packed);
     p.sf_k_stride = sf_k_stride;
+    p.sf_row_stride = sf_row_stride;
     p.rows = rows;
     p.k = k;
     p.gran_k = gran_k;
@@ -325,14 +330,16 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
 }
 
 int dgb200_per_token_cast_to_fp8(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
-                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride, void* stream) {
-    return run_cast(false, x, x_row_stride, rows, k, gran_k, q, q_row_stride, sf_f32, sf_packed, sf_k_stride,
+                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride,
+                                 int64_t sf_row_stride, void* stream) {
+    return run_cast(false, x, x_row_stride, rows, k, gran_k, q, q_row_stride, sf_f32, sf_packed, sf_k_stride, sf_row_stride,
                     static_cast<cudaStream_t>(stream));
 }
 
 int dgb200_per_token_cast_to_fp4(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
-                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride, void* stream) {
-    return run_cast(true, x, x_row_stride, rows, k, gran_k, q, q_row_stride, sf_f32, sf_packed, sf_k_stride,
+                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride,
+                                 int64_t sf_row_stride, void* stream) {
+    return run_cast(true, x, x_row_stride, rows, k, gran_k, q, q_row_stride, sf_f32, sf_packed, sf_k_stride, sf_row_stride,
                     static_cast<cudaStream_t>(stream));
 }
 
@@ -361,6 +368,23 @@ int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, 
     const long long total = static_cast<long long>(num_groups) * ((sf_k + 3) / 4) * mn;
     const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
     dgb200_pack_sf_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t experts, int32_t topk, int64_t* topk_idx,
+                              float* topk_weights, void* stream) {
+    DGB_REQUIRE(logits != nullptr && topk_idx != nullptr && topk_weights != nullptr, "null tensor pointer");
+    DGB_REQUIRE(tokens >= 0 && experts > 0 && experts <= 1024, "experts must be in [1, 1024]");
+    DGB_REQUIRE(topk > 0 && topk <= 32 && topk <= experts, "topk must be in [1, min(32, experts)]");
+    if (tokens == 0) return 0;
+    const int grid = (tokens + 7) / 8;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    long long* idx = reinterpret_cast<long long*>(topk_idx);
+    if (experts <= 256)
+        dgb200_route_sigmoid_topk_kernel<8><<<grid, 256, 0, s>>>(logits, tokens, experts, topk, idx, topk_weights);
+    else
+        dgb200_route_sigmoid_topk_kernel<32><<<grid, 256, 0, s>>>(logits, tokens, experts, topk, idx, topk_weights);
     DGB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -428,6 +452,8 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
     const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
     const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
 
+    struct ClearEvents { ~ClearEvents() { g_num_stage_events = 0; } } clear_events_on_exit;
+    if ((rc = record_stage(0, stream))) return rc;
     // 1. dispatch plan: stable counting sort of the (token, k) entries by expert
     DGB_CUDA(cudaMemsetAsync(src_of_row, 0xff, l.max_rows * 4, stream));
     dgb200_moe_count_kernel<<<chunks, kPlanChunk, E * sizeof(int), stream>>>(topk_idx, entries, 0, E, chunk_hist);
@@ -437,6 +463,7 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                                                                     expert_start, dest_row, src_of_row, row_weight);
     DGB_CUDA(cudaGetLastError());
 
+    if ((rc = record_stage(1, stream))) return rc;
     // 2. gather FP8 rows + scales into expert-sorted order
     const long long upper_rows = std::min<long long>(l.max_rows, static_cast<long long>(entries) + static_cast<long long>(E) * kSegmentAlignment);
     const int gather_blocks = static_cast<int>((upper_rows + 31) / 32);
@@ -445,6 +472,7 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
         base + l.l1_acts, reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
     DGB_CUDA(cudaGetLastError());
 
+    if ((rc = record_stage(2, stream))) return rc;
     // 3. L1: gate/up GEMM with the fused SwiGLU + FP8 requant epilogue
     {
         GemmCall c{};
@@ -480,6 +508,7 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
         rc = run_gemm(c, stream);
         if (rc) return rc;
     }
+    if ((rc = record_stage(3, stream))) return rc;
     // 4. L2: down GEMM, rows scattered to the combine slot of their (token, top-k slot)
     {
         GemmCall c{};
@@ -513,11 +542,20 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
         rc = run_gemm(c, stream);
         if (rc) return rc;
     }
+    if ((rc = record_stage(4, stream))) return rc;
     // 5. combine: y[t] = sum over the top-k slots
     dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(int), stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(base + l.combine), dest_row, num_topk, num_max_tokens_per_rank, hidden,
         static_cast<__nv_bfloat16*>(y));
     DGB_CUDA(cudaGetLastError());
+    return record_stage(5, stream);
+}
+
+int dgb200_set_mega_moe_stage_events(void* const* events, int32_t count) {
+    DGB_REQUIRE(count >= 0 && count <= kNumStageEvents, "count must be in [0, %d]", kNumStageEvents);
+    DGB_REQUIRE(count == 0 || events != nullptr, "null event array");
+    for (int i = 0; i < count; ++i) g_stage_events[i] = static_cast<cudaEvent_t>(events[i]);
+    g_num_stage_events = count;
     return 0;
 }
 

@@ -154,6 +154,51 @@ dgb200_moe_gather_kernel(const unsigned char* __restrict__ x, const unsigned* __
     }
 }
 
+// Router of the benchmark layer: per token, the `topk` largest logits (descending; ties -> lower expert index),
+// weights = sigmoid(logit) renormalised to sum to one. One warp per token, expert e held by lane e % 32.
+// The reference leaves routing to the caller (tests/test_mega_moe.py:124-125 uses torch.topk).
+template <int kMaxPerLane>
+__global__ void __launch_bounds__(256)
+dgb200_route_sigmoid_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int topk,
+                                 long long* __restrict__ topk_idx, float* __restrict__ topk_weights) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    float v[kMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = e < experts ? logits[static_cast<long long>(t) * experts + e] : -INFINITY;
+    }
+    float my_score = 0.0f, sum = 0.0f;
+    int my_idx = 0;
+    for (int k = 0; k < topk; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i)
+            if (v[i] > best) { best = v[i]; best_e = i * 32 + lane; }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if ((best_e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < kMaxPerLane; ++i)
+                if (i == (best_e >> 5)) v[i] = -INFINITY;
+        }
+        const float score = 1.0f / (1.0f + expf(-best));
+        sum += score;
+        if (lane == k) { my_score = score; my_idx = best_e; }
+    }
+    if (lane < topk) {
+        topk_idx[static_cast<long long>(t) * topk + lane] = my_idx;
+        topk_weights[static_cast<long long>(t) * topk + lane] = my_score / sum;
+    }
+}
+
 // y[t, :] = bf16( sum over valid k, in ascending k, of float(combine[k][t, :]) ); slot k of token t is valid when
 // dest_row[t * topk + k] >= 0. combine is bf16 [topk][combine_tokens][hidden].
 // One CTA per token; a thread owns 8 consecutive channels (one 16-byte vector per slot).

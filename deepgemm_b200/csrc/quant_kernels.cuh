@@ -42,8 +42,8 @@ struct CastParams {
     void* q;
     long long q_row_stride;  // bytes
     float* sf_f32;           // [rows, ceil(k / gran)] row-major, or null
-    uint32_t* sf_packed;     // int (kp, row) at sf_packed[kp * sf_k_stride + row], or null
-    long long sf_k_stride;
+    uint32_t* sf_packed;     // int (kp, row) at sf_packed[kp * sf_k_stride + row * sf_row_stride], or null
+    long long sf_k_stride, sf_row_stride;  // (aligned rows, 1) = MN-major for the GEMM; (1, packed k) = token-major
     int rows, k, gran_k;
 };
 
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(256) dgb200_cast_rows_kernel(const CastParams 
         const int kp_local = i >> 5, r = i & 31;
         const int kp = col0 / (p.gran_k * 4) + kp_local;
         if (row0 + r < p.rows && kp < num_packed)
-            p.sf_packed[static_cast<long long>(kp) * p.sf_k_stride + row0 + r] =
+            p.sf_packed[static_cast<long long>(kp) * p.sf_k_stride + static_cast<long long>(row0 + r) * p.sf_row_stride] =
                 *reinterpret_cast<const uint32_t*>(&sf_stage[r][kp_local * 4]);
     }
 }

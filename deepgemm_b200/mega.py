@@ -1,0 +1,188 @@
+"""Mega-MoE entry points with the reference's Python surface (deep_gemm/mega/__init__.py:18-176):
+``get_symm_buffer_for_mega_moe`` -> ``SymmBuffer`` (the caller copies x / x_sf / topk_idx / topk_weights into its
+views), ``transform_weights_for_mega_moe`` and ``fp8_fp4_mega_moe``. The layer itself runs in libdgb200.so."""
+import ctypes
+import types
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .utils.math import align
+
+_NUM_LAYOUT_WORDS = 16
+_GATE_UP_INTERLEAVE = 32  # rows: [gate 0..31 | up 0..31 | gate 32..63 | ...], the order the L1 epilogue consumes
+
+
+def get_token_alignment_for_mega_moe() -> int:
+    """Reference: csrc/apis/mega.hpp:19-21."""
+    return _lib.lib().dgb200_get_token_alignment_for_mega_moe()
+
+
+def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_tokens: int,
+                             num_topk: int, mma_type: str = 'fp8xfp4') -> int:
+    """Rows of one M tile. The reference picks 16..192 by expected rows per expert (csrc/apis/mega.hpp:23-32);
+    this kernel always tiles tokens by 128 and clips per expert."""
+    del num_ranks, num_experts, num_max_tokens_per_rank, num_tokens, num_topk, mma_type
+    return 128
+
+
+def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden):
+    words = (ctypes.c_int64 * _NUM_LAYOUT_WORDS)()
+    _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe(
+        num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+        ctypes.cast(words, ctypes.c_void_p)))
+    keys = ['total', 'x', 'x_sf', 'topk_idx', 'topk_weights', 'l1_acts', 'l1_sf', 'l2_acts', 'l2_sf', 'max_rows',
+            'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'combine', 'row_weight']
+    return dict(zip(keys, list(words)))
+
+
+class SymmBuffer:
+    """One flat buffer per rank: caller-written inputs first, the layer's private workspace after them.
+    Reference: SymmBuffer, deep_gemm/mega/__init__.py:18-66."""
+
+    def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
+                 intermediate_hidden: int, num_shared_experts: int = 0, mma_type: str = 'fp8xfp4',
+                 activation: str = 'swiglu'):
+        if activation != 'swiglu':
+            raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
+        if mma_type != 'fp8xfp4':
+            raise RuntimeError(f'Only the `fp8xfp4` MMA type is built, got `{mma_type}`')
+        if num_shared_experts != 0:
+            raise RuntimeError('shared experts are not built')
+        self.group = group
+        self.num_ranks = 1 if group is None else group.size()
+        self.rank = 0 if group is None else group.rank()
+        self.num_experts, self.num_topk = num_experts, num_topk
+        self.num_max_tokens_per_rank = num_max_tokens_per_rank
+        self.hidden, self.intermediate_hidden = hidden, intermediate_hidden
+        self.layout = _buffer_layout(self.num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                                     intermediate_hidden)
+        num_bytes = self.layout['total']
+        if self.num_ranks == 1:
+            self.buffer = torch.empty(num_bytes, dtype=torch.int8, device='cuda')
+            self.handle = types.SimpleNamespace(buffer_ptrs=[self.buffer.data_ptr()])
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buffer = symm_mem.empty(num_bytes, dtype=torch.int8, device='cuda')
+            self.handle = symm_mem.rendezvous(self.buffer, group=group)
+        self.buffer.zero_()
+        if group is not None:
+            group.barrier()
+        torch.cuda.synchronize()
+
+        t, lay = num_max_tokens_per_rank, self.layout
+        def view(offset, nbytes, dtype, shape):
+            return self.buffer[offset:offset + nbytes].view(dtype).view(shape)
+        self.x = view(lay['x'], t * hidden, torch.float8_e4m3fn, (t, hidden))
+        self.x_sf = view(lay['x_sf'], t * (hidden // 128) * 4, torch.int32, (t, hidden // 128))
+        self.topk_idx = view(lay['topk_idx'], t * num_topk * 8, torch.int64, (t, num_topk))
+        self.topk_weights = view(lay['topk_weights'], t * num_topk * 4, torch.float32, (t, num_topk))
+
+    def destroy(self):
+        self.handle = self.buffer = self.group = None
+        self.x = self.x_sf = self.topk_idx = self.topk_weights = None
+
+
+def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
+                                 intermediate_hidden: int, num_shared_experts: int = 0,
+                                 use_fp8_dispatch: Optional[bool] = None, mma_type: str = 'fp8xfp4',
+                                 activation: str = 'swiglu') -> SymmBuffer:
+    """Reference: get_symm_buffer_for_mega_moe, deep_gemm/mega/__init__.py:69-94. ``group`` may be None for a
+    single process."""
+    num_max_tokens_per_rank = align(num_max_tokens_per_rank, get_token_alignment_for_mega_moe())
+    if use_fp8_dispatch is not None and use_fp8_dispatch != (mma_type.split('x')[0] == 'fp8'):
+        raise RuntimeError('use_fp8_dispatch contradicts mma_type')
+    return SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+                      num_shared_experts, mma_type=mma_type, activation=activation)
+
+
+def _interleave_rows(t: torch.Tensor, gran: int) -> torch.Tensor:
+    """[G, N, ...] with rows [gate | up] -> blocks of `gran` gate rows followed by the matching up rows. Strides of
+    the result equal those of the input (packed scale factors stay MN-major)."""
+    n = t.shape[1]
+    half = n // 2
+    if half % gran != 0:
+        raise RuntimeError(f'intermediate size {half} must be a multiple of {gran}')
+    r = torch.arange(n, device=t.device)
+    src = torch.where(r % (2 * gran) < gran, gran * (r // (2 * gran)) + r % gran,
+                      half + gran * (r // (2 * gran)) + r % gran - gran)
+    out = torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device)
+    out.copy_(t.index_select(1, src))
+    return out
+
+
+def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                                   l2_weights: Tuple[torch.Tensor, torch.Tensor], activation: str = 'swiglu'):
+    """Reorders the L1 weights (and their packed scale factors) so that every 64-column slice of an L1 output tile
+    holds 32 gate channels and their 32 up channels. L2 is returned unchanged. The transformed tensors are opaque
+    to the caller, as in the reference (transform_weights_for_mega_moe, deep_gemm/mega/__init__.py:131-149, which
+    interleaves by 8 and pre-transposes scale factors for its own kernel)."""
+    if activation != 'swiglu':
+        raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
+    if not isinstance(l1_weights, tuple):
+        raise RuntimeError('BF16 weights are not built; pass (packed FP4 weights, packed UE8M0 scale factors)')
+    return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), _interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE)), \
+        (l2_weights[0], l2_weights[1])
+
+
+def _check_weight(w, sf, num_groups, n, k, name):
+    if not (w.is_cuda and w.dtype == torch.int8 and w.is_contiguous() and tuple(w.shape) == (num_groups, n, k // 2)):
+        raise RuntimeError(f'{name} must be a contiguous CUDA int8 tensor of shape {(num_groups, n, k // 2)}')
+    if not (sf.dtype == torch.int32 and tuple(sf.shape) == (num_groups, n, k // 128) and sf.stride(1) == 1 and
+            sf.stride(2) == align(n, 4) and sf.stride(0) == sf.stride(2) * sf.shape[2]):
+        raise RuntimeError(f'{name} scale factors must be packed UE8M0 int32 {(num_groups, n, k // 128)}, MN-major '
+                           '(use transform_sf_into_required_layout)')
+
+
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                     l2_weights: Tuple[torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
+                     shared_l1_weights=None, shared_l2_weights=None,
+                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                     recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
+                     activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
+    """y[t] = sum_k w[t,k] * Expert_{idx[t,k]}(x[t]) over the inputs the caller placed in ``sym_buffer``.
+    Reference: fp8_fp4_mega_moe, deep_gemm/mega/__init__.py:153-176 and csrc/apis/mega.hpp:157-286."""
+    if tuple(recipe) != (1, 1, 32):
+        raise RuntimeError('recipe must be (1, 1, 32)')
+    if activation != 'swiglu':
+        raise RuntimeError('activation must be `swiglu`')
+    if shared_l1_weights is not None or shared_l2_weights is not None:
+        raise RuntimeError('shared experts are not built')
+    b = sym_buffer
+    num_local = b.num_experts // b.num_ranks
+    _check_weight(l1_weights[0], l1_weights[1], num_local, 2 * b.intermediate_hidden, b.hidden, 'l1_weights')
+    _check_weight(l2_weights[0], l2_weights[1], num_local, b.hidden, b.intermediate_hidden, 'l2_weights')
+    if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
+        raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
+    stats = cumulative_local_expert_recv_stats
+    if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == num_local and stats.is_contiguous()):
+        raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
+    ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.lib().dgb200_fp8_fp4_mega_moe(
+            p(y), p(l1_weights[0]), p(l1_weights[1]), p(l2_weights[0]), p(l2_weights[1]), p(stats), p(b.buffer),
+            ctypes.cast(ptrs, ctypes.c_void_p), b.rank, b.num_ranks, y.size(0), b.num_max_tokens_per_rank,
+            b.num_experts, b.num_topk, b.hidden, b.intermediate_hidden,
+            float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
+            _lib.current_stream_ptr()))
+
+
+def route_sigmoid_topk(logits: torch.Tensor, num_topk: int, topk_idx: Optional[torch.Tensor] = None,
+                       topk_weights: Optional[torch.Tensor] = None):
+    """Router of the benchmark layer (no reference counterpart; the reference's tests call torch.topk):
+    top-k of the logits, weights = renormalised sigmoid scores. Writes into the given views (e.g. the buffer's)."""
+    if not (logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()):
+        raise RuntimeError('logits must be a contiguous CUDA float32 [tokens, experts] tensor')
+    t, e = logits.shape
+    if topk_idx is None:
+        topk_idx = torch.empty((t, num_topk), dtype=torch.int64, device=logits.device)
+    if topk_weights is None:
+        topk_weights = torch.empty((t, num_topk), dtype=torch.float32, device=logits.device)
+    assert topk_idx.is_contiguous() and topk_weights.is_contiguous()
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.lib().dgb200_route_sigmoid_topk(
+            ctypes.c_void_p(logits.data_ptr()), t, e, num_topk, ctypes.c_void_p(topk_idx.data_ptr()),
+            ctypes.c_void_p(topk_weights.data_ptr()), _lib.current_stream_ptr()))
+    return topk_idx, topk_weights

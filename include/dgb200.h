@@ -78,6 +78,79 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
     int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
     int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream);
 
+/* BF16 rows -> E4M3 + one UE8M0 scale per gran_k (32 or 128) elements: sf = 2^ceil(log2(max(amax, 1e-4) / 448)),
+ * q = e4m3_rn(x / sf). Reference: per_token_cast_to_fp8(use_ue8m0=True), deep_gemm/utils/math.py:26-49 (a torch
+ * helper there; one fused kernel here).
+ *   x  bf16 [rows, k], row stride x_row_stride elements; k % 16 == 0.   q  e4m3 [rows, k], row stride in bytes.
+ *   sf_f32     optional float [rows, ceil(k / gran_k)] row-major.
+ *   sf_packed  optional int32, 4 scales per int (missing K blocks pack as 2^0); int (kp, row) is written at
+ *              sf_packed[kp * sf_k_stride + row * sf_row_stride]: (align(rows, 4), 1) gives the MN-major layout of
+ *              dgb200_transform_sf_into_required_layout, (1, packed k) the token-major one of
+ *              per_token_cast_to_fp8(use_packed_ue8m0=True). */
+int dgb200_per_token_cast_to_fp8(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
+                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride,
+                                 int64_t sf_row_stride, void* stream);
+
+/* BF16 rows -> packed E2M1 (two codes per byte, even K index in the low nibble) + UE8M0 scales:
+ * sf = 2^ceil(log2(max(amax, 1e-4) / 6)); thresholds .25 .75 1.25 1.75 2.5 3.5 5 with ties rounding down.
+ * Reference: per_token_cast_to_fp4(use_ue8m0=True), deep_gemm/utils/math.py:84-122.  q int8 [rows, k / 2]. */
+int dgb200_per_token_cast_to_fp4(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
+                                 int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride,
+                                 int64_t sf_row_stride, void* stream);
+
+/* FP32 power-of-two scales -> packed UE8M0 int32, MN-major, MN stride align(mn, 4):
+ * out[g * packed_k * align(mn, 4) + kp * align(mn, 4) + row], byte j of an int = K block 4 kp + j.
+ * Reference: transform_sf_into_required_layout, csrc/apis/layout.hpp:14-61 ->
+ * get_mn_major_tma_aligned_packed_ue8m0_tensor, csrc/jit_kernels/impls/smxx_layout.hpp:180-253.
+ *   sf element (g, r, c) at sf[g * stride_g + r * stride_mn + c * stride_k]; row r of the output reads input row
+ *   r / gran_mn. psum_layout (optional, device int32 [num_psum_groups]): rows that fall in the gap between one
+ *   group's end and the next group's aligned start pack as 0 instead of being read. A scale that is not a positive
+ *   power of two sets the device status (the reference traps). */
+int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, int64_t stride_mn, int64_t stride_k,
+                                             void* out, int32_t num_groups, int32_t mn, int32_t sf_k, int32_t gran_mn,
+                                             const int32_t* psum_layout, int32_t num_psum_groups,
+                                             int32_t psum_alignment, void* stream);
+
+/* Router used by the benchmark layer: top-k of the logits (descending, ties to the lower expert index), weights =
+ * sigmoid(logit) renormalised to sum to one. No reference counterpart (its tests call torch.topk,
+ * tests/test_mega_moe.py:124-125).  logits float [tokens, experts]; topk_idx int64, topk_weights float [tokens, topk]. */
+int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t experts, int32_t topk, int64_t* topk_idx,
+                              float* topk_weights, void* stream);
+
+/* Token-count granularity of the mega-MoE buffer. Reference: get_token_alignment_for_mega_moe, csrc/apis/mega.hpp:19-21. */
+int dgb200_get_token_alignment_for_mega_moe(void);
+
+/* Byte layout of the per-rank mega-MoE buffer. Reference: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155.
+ * out[16] = {total bytes, x, x_sf, topk_idx, topk_weights, l1_acts, l1_sf, l2_acts, l2_sf, max_rows (rows, not bytes),
+ *            dest_row, src_of_row, expert_start, expert_end, combine, row_weight}; all but out[0], out[9] are byte
+ * offsets. The caller writes x (e4m3 [T, hidden]), x_sf (int32 [T, hidden / 128], per-32 UE8M0, token-major),
+ * topk_idx (int64 [T, topk], -1 = masked) and topk_weights (float [T, topk]) before each call; the rest is private. */
+int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                               int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                               int64_t* out);
+
+/* The MoE layer: dispatch -> L1 (gate/up GEMM + SwiGLU + FP8 requant) -> L2 (down GEMM) -> weighted top-k combine.
+ * Reference: fp8_fp4_mega_moe, csrc/apis/mega.hpp:157-286 (host) and
+ * deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:55-1458 (kernel).
+ *   y        bf16 [num_tokens, hidden], written.
+ *   l1_w     packed e2m1 [E_local, 2 * inter, hidden / 2], rows gate/up-interleaved by 32;
+ *   l1_w_sf  packed UE8M0 int32 (per-32), MN-major [E_local][hidden / 128][2 * inter], same row order.
+ *   l2_w     packed e2m1 [E_local, hidden, inter / 2]; l2_w_sf int32 [E_local][inter / 128][hidden].
+ *   cumulative_local_expert_recv_stats  optional int32 [E_local], incremented by the rows each expert received.
+ *   buffer / peer_buffer_ptrs  this rank's buffer and the host array of all ranks' buffer addresses.
+ *   activation_clamp <= 0 disables the clamp. */
+int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+                            int32_t* cumulative_local_expert_recv_stats, void* buffer, const uint64_t* peer_buffer_ptrs,
+                            int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
+                            int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                            float activation_clamp, int32_t fast_math, void* stream);
+
+/* Measurement hook: the NEXT dgb200_fp8_fp4_mega_moe call of this host thread records events[i] (cudaEvent_t
+ * handles) on its stream at stage boundary i: 0 entry, 1 after the dispatch plan, 2 after the gather, 3 after L1,
+ * 4 after L2, 5 after the combine. The setting is consumed by that call. No reference counterpart (the reference
+ * times its kernel from outside with kineto, deep_gemm/testing/bench.py:79-146). */
+int dgb200_set_mega_moe_stage_events(void* const* events, int32_t count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,10 +4,20 @@ import torch
 from .quant import align, ceil_div, ue8m0_bytes
 
 
+def pack_sf_dense(sf: torch.Tensor) -> torch.Tensor:
+    """fp32 power-of-two scales [G, MN, SFK] -> contiguous int32 [G, ceil(SFK / 4), align(MN, 4)]: the memory image
+    of the packed MN-major tensor (byte j of an int = K block 4i + j; K blocks and rows beyond the input pack as 0)."""
+    g, mn, sfk = sf.shape
+    packed_k, aligned_mn = ceil_div(sfk, 4), align(mn, 4)
+    raw = torch.zeros((g, packed_k * 4, aligned_mn), dtype=torch.uint8)
+    raw[:, :sfk, :mn] = ue8m0_bytes(sf).transpose(1, 2)
+    ints = raw.view(g, packed_k, 4, aligned_mn).permute(0, 1, 3, 2).contiguous().view(torch.int32)
+    return ints.view(g, packed_k, aligned_mn)
+
+
 def pack_sf_mn_major(sf: torch.Tensor) -> torch.Tensor:
     """fp32 power-of-two scales [G?, MN, SFK] -> packed UE8M0 int32 [G?, MN, ceil(SFK / 4)] whose memory is
     MN-major with the MN stride padded to 4 ints: strides (packed_k * align(MN, 4), 1, align(MN, 4)).
-    K blocks beyond SFK pack as byte 0.
 
     Follows ``get_mn_major_tma_aligned_packed_ue8m0_tensor`` (csrc/jit_kernels/impls/smxx_layout.hpp:180-253)
     and its kernel ``transpose_and_pack_fp32_into_ue8m0`` (deep_gemm/include/deep_gemm/impls/smxx_layout.cuh:56-144),
@@ -15,14 +25,7 @@ def pack_sf_mn_major(sf: torch.Tensor) -> torch.Tensor:
     squeeze = sf.dim() == 2
     if squeeze:
         sf = sf.unsqueeze(0)
-    g, mn, sfk = sf.shape
-    packed_k, aligned_mn = ceil_div(sfk, 4), align(mn, 4)
-    raw = torch.zeros((g, packed_k * 4, aligned_mn), dtype=torch.uint8)
-    raw[:, :sfk, :mn] = ue8m0_bytes(sf).transpose(1, 2)
-    # [g, packed_k, 4, aligned_mn] -> ints [g, packed_k, aligned_mn] with byte j = K block 4i + j
-    ints = raw.view(g, packed_k, 4, aligned_mn).permute(0, 1, 3, 2).contiguous().view(torch.int32)
-    ints = ints.view(g, packed_k, aligned_mn)
-    out = ints.transpose(1, 2)[:, :mn, :]  # logical [g, mn, packed_k], memory MN-major
+    out = pack_sf_dense(sf).transpose(1, 2)[:, : sf.shape[1], :]  # logical [g, mn, packed_k]
     return out[0] if squeeze else out
 
 

@@ -1,0 +1,107 @@
+"""CPU oracle: routing, dispatch permutation and the full MoE layer. TEST INFRASTRUCTURE ONLY (see quant.py).
+
+The reference has no torch implementation of the whole layer (its test compares the fused kernel bitwise against
+DeepEP + grouped GEMM + a TileLang SwiGLU kernel, tests/test_mega_moe.py:281-329). This file composes the
+reference's own arithmetic into the layer, step by step as the fused kernel performs it
+(deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh): the cited lines give each step's source.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from .quant import align, dequantize_fp4, dequantize_fp8, ue8m0_ceil
+
+
+def route_sigmoid_topk(logits: torch.Tensor, topk: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router of the benchmark configurations: scores = sigmoid(logits); the ``topk`` largest per token (ties go to
+    the lower expert index, listed in descending score order); weights renormalised to sum to 1.
+    Returns (topk_idx int64 [T, topk], topk_weights fp32 [T, topk])."""
+    order = torch.sort(logits.float(), dim=1, descending=True, stable=True).indices[:, :topk]
+    scores = torch.sigmoid(logits.float()).gather(1, order)
+    return order.contiguous(), (scores / scores.sum(dim=1, keepdim=True)).contiguous()
+
+
+def dispatch_plan(topk_idx: torch.Tensor, num_experts: int, alignment: int, expert_lo: int = 0):
+    """Deterministic dispatch permutation: the (token, k) entries, in token-major order, stably sorted by expert;
+    expert e occupies rows [start[e], end[e]) with start[e] = align(end[e-1], alignment). Entries whose expert is
+    outside [expert_lo, expert_lo + num_experts) (or negative = masked, tests/test_mega_moe.py:131-134) get -1.
+
+    The reference assigns slots with atomics (sm100_fp8_fp4_mega_moe.cuh:363-377), so its order inside an expert
+    depends on arrival; this stable order is the definition the CUDA path is held to bit for bit.
+    Returns (dest_row int32 [T * topk], src_of_row int32 [total_rows], expert_start, expert_end int32 [E])."""
+    flat = topk_idx.reshape(-1).to(torch.int64) - expert_lo
+    local = (flat >= 0) & (flat < num_experts)
+    counts = torch.bincount(flat[local], minlength=num_experts)
+    start = torch.zeros(num_experts, dtype=torch.int64)
+    end = torch.zeros(num_experts, dtype=torch.int64)
+    cursor = 0
+    for e in range(num_experts):
+        start[e] = cursor
+        end[e] = cursor + int(counts[e])
+        cursor = align(int(end[e]), alignment)
+    total_rows = cursor
+    dest = torch.full((flat.numel(),), -1, dtype=torch.int64)
+    src = torch.full((total_rows,), -1, dtype=torch.int64)
+    entries = torch.nonzero(local).reshape(-1)
+    order = torch.sort(flat[entries], stable=True).indices
+    sorted_entries = entries[order]
+    sorted_experts = flat[sorted_entries]
+    rank_in_expert = torch.arange(sorted_entries.numel()) - torch.cumsum(counts, 0)[sorted_experts] + counts[sorted_experts]
+    rows = start[sorted_experts] + rank_in_expert
+    dest[sorted_entries] = rows
+    src[rows] = sorted_entries
+    return dest.to(torch.int32), src.to(torch.int32), start.to(torch.int32), end.to(torch.int32)
+
+
+def swiglu_requant(gate_up: torch.Tensor, weight: torch.Tensor, clamp: Optional[float]):
+    """L1 epilogue on fp32 accumulators [rows, 2I] laid out [gate | up]:
+    round to bf16 -> clamp (gate <= c, |up| <= c) -> silu(gate) * up * weight in fp32 -> per-32 amax ->
+    sf = 2^ceil(log2(amax * (1/448))) -> e4m3(value / sf).
+    Follows sm100_fp8_fp4_mega_moe.cuh:1046-1126 with math::get_e4m3_sf_and_sf_inv
+    (deep_gemm/include/deep_gemm/common/math.cuh:83-99); the formula is the TileLang baseline's
+    (third-party/tilelang_ops/swiglu_apply_weight_to_fp8.py:89-94). Returns (q e4m3 [rows, I], sf fp32 [rows, I/32])."""
+    half = gate_up.shape[1] // 2
+    gate = gate_up[:, :half].bfloat16().float()
+    up = gate_up[:, half:].bfloat16().float()
+    if clamp is not None:
+        gate = gate.clamp(max=clamp)
+        up = up.clamp(min=-clamp, max=clamp)
+    act = gate / (1.0 + torch.exp(-gate)) * up * weight.float().unsqueeze(1)
+    amax = act.view(act.shape[0], -1, 32).abs().amax(dim=2)
+    sf = ue8m0_ceil(amax * torch.tensor(1.0 / 448.0, dtype=torch.float32))
+    q = (act.view(act.shape[0], -1, 32) * (1.0 / sf.unsqueeze(2))).to(torch.float8_e4m3fn).view(act.shape)
+    return q, sf
+
+
+def moe_layer(x_q: torch.Tensor, x_sf: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+              l1_q: torch.Tensor, l1_sf: torch.Tensor, l2_q: torch.Tensor, l2_sf: torch.Tensor,
+              clamp: Optional[float] = None, return_intermediates: bool = False):
+    """Whole layer on one rank holding every expert.
+
+    x_q e4m3 [T, H] with x_sf fp32 [T, H/32] (per-32 UE8M0, tests/test_mega_moe.py:53-59);
+    l1_q int8 [E, 2I, H/2] rows [gate | up] with l1_sf fp32 [E, 2I, H/32]; l2_q int8 [E, H, I/2], l2_sf [E, H, I/32].
+    Per expert: acc1 = deq(x) @ deq(W1).T (fp32) -> swiglu_requant -> acc2 = deq(a2) @ deq(W2).T -> bf16 row;
+    y[t] = bf16(sum over valid slots k, ascending, of fp32(row(t, k))) (sm100_fp8_fp4_mega_moe.cuh:1378-1430)."""
+    tokens, hidden = x_q.shape
+    num_experts, topk = l1_q.shape[0], topk_idx.shape[1]
+    x = dequantize_fp8(x_q, x_sf, 32)
+    slot_rows = torch.zeros((tokens, topk, hidden), dtype=torch.bfloat16)
+    inter = {}
+    for e in range(num_experts):
+        tok, slot = torch.nonzero(topk_idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        w1 = dequantize_fp4(l1_q[e], l1_sf[e], 32)
+        acc1 = x[tok] @ w1.T
+        a2_q, a2_sf = swiglu_requant(acc1, topk_weights[tok, slot], clamp)
+        w2 = dequantize_fp4(l2_q[e], l2_sf[e], 32)
+        acc2 = dequantize_fp8(a2_q, a2_sf, 32) @ w2.T
+        slot_rows[tok, slot] = acc2.bfloat16()
+        if return_intermediates:
+            inter[e] = (tok, slot, acc1, a2_q, a2_sf, acc2)
+    valid = (topk_idx >= 0) & (topk_idx < num_experts)
+    y = torch.zeros((tokens, hidden), dtype=torch.float32)
+    for k in range(topk):
+        y += torch.where(valid[:, k, None], slot_rows[:, k].float(), torch.zeros(()))
+    y = y.bfloat16()
+    return (y, inter) if return_intermediates else y

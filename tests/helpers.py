@@ -1,0 +1,61 @@
+"""Shared input builders for the parity tests: seeded CPU tensors quantised by the oracle."""
+import random
+
+import torch
+
+from oracle import quant
+
+
+def quantize_groups(t: torch.Tensor, gran_k: int, fp4: bool):
+    """[G, R, K] bf16 -> (stacked q, stacked fp32 sf) with the oracle's quantisers."""
+    qs, sfs = [], []
+    for g in range(t.shape[0]):
+        q, sf = (quant.quantize_fp4_per_token if fp4 else quant.quantize_fp8_per_token)(t[g], gran_k)
+        qs.append(q)
+        sfs.append(sf)
+    return torch.stack(qs), torch.stack(sfs)
+
+
+def contiguous_case(num_groups, n, k, m_lo, m_hi, seed, alignment=128, gran_a=128, gran_b=32, b_fp4=True):
+    """BASELINE-style m-grouped contiguous inputs: rows per group uniform in [m_lo, m_hi], segments padded to
+    `alignment` with zero rows; A ~ N(0,1), B ~ N(0,0.02)."""
+    rng = random.Random(seed)
+    torch.manual_seed(seed)
+    ms = [rng.randint(m_lo, m_hi) for _ in range(num_groups)]
+    aligned = [-(-x // alignment) * alignment for x in ms]
+    m = sum(aligned)
+    a = torch.randn(m, k).bfloat16()
+    b = (torch.randn(num_groups, n, k) * 0.02).bfloat16()
+    row_ids = torch.full((m,), -1, dtype=torch.int32)
+    ends, start = [], 0
+    for g in range(num_groups):
+        row_ids[start:start + ms[g]] = g
+        a[start + ms[g]:start + aligned[g]] = 0
+        ends.append(start + ms[g])
+        start += aligned[g]
+    a_q, a_sf = quant.quantize_fp8_per_token(a, gran_a)
+    b_q, b_sf = quantize_groups(b, gran_b, b_fp4)
+    return dict(m=m, ms=ms, a_q=a_q, a_sf=a_sf, b_q=b_q, b_sf=b_sf, row_ids=row_ids,
+                psum=torch.tensor(ends, dtype=torch.int32))
+
+
+def moe_case(tokens, hidden, inter, experts, topk, seed, masked_ratio=0.0, empty_experts=()):
+    """Small MoE layer inputs: x ~ N(0,1) -> FP8 per-32, weights ~ N(0,0.02) -> MXFP4 per-32, sigmoid/top-k router."""
+    from oracle import moe as omoe
+    torch.manual_seed(seed)
+    x = torch.randn(tokens, hidden).bfloat16()
+    x_q, x_sf = quant.quantize_fp8_per_token(x, 32)
+    w1 = (torch.randn(experts, 2 * inter, hidden) * 0.02).bfloat16()
+    w2 = (torch.randn(experts, hidden, inter) * 0.02).bfloat16()
+    l1_q, l1_sf = quantize_groups(w1, 32, True)
+    l2_q, l2_sf = quantize_groups(w2, 32, True)
+    logits = torch.randn(tokens, experts)
+    for e in empty_experts:
+        logits[:, e] = -1e9
+    idx, w = omoe.route_sigmoid_topk(logits, topk)
+    if masked_ratio > 0:
+        mask = torch.rand(idx.shape) < masked_ratio
+        idx = idx.masked_fill(mask, -1)
+        w = w.masked_fill(mask, 0.0)
+    return dict(x=x, x_q=x_q, x_sf=x_sf, l1_q=l1_q, l1_sf=l1_sf, l2_q=l2_q, l2_sf=l2_sf, logits=logits,
+                topk_idx=idx, topk_weights=w)

@@ -1,0 +1,152 @@
+"""Parity of the MoE layer (dispatch -> L1 + SwiGLU/requant -> L2 -> combine) against the CPU oracle.
+Routing indices and the dispatch permutation must be bit-exact; y within calc_diff <= 2e-3 (FP4 weights)."""
+import pytest
+import torch
+
+from oracle import layout as olay
+from oracle import moe as omoe
+from oracle import quant
+from tests.helpers import moe_case
+
+pytestmark = pytest.mark.gpu
+FP4_TOL = 2e-3
+
+
+@pytest.fixture(scope='module')
+def dg():
+    import deepgemm_b200
+    return deepgemm_b200
+
+
+def _device_weights(dg, c):
+    """oracle-quantised weights -> the packed layouts the public API takes -> transform_weights_for_mega_moe"""
+    e, n1, h = c['l1_sf'].shape[0], c['l1_q'].shape[1], c['l1_q'].shape[2] * 2
+    l1_sf = dg.transform_sf_into_required_layout(c['l1_sf'].cuda(), n1, h, (1, 32), e)
+    l2_sf = dg.transform_sf_into_required_layout(c['l2_sf'].cuda(), c['l2_q'].shape[1], c['l2_q'].shape[2] * 2, (1, 32), e)
+    return dg.transform_weights_for_mega_moe((c['l1_q'].cuda(), l1_sf), (c['l2_q'].cuda(), l2_sf))
+
+
+def _run_layer(dg, c, tokens, hidden, inter, experts, topk, clamp=None, stats=None, buf=None):
+    buf = buf or dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    buf.x[:tokens].copy_(c['x_q'].cuda())
+    buf.x_sf[:tokens].copy_(quant.pack_ue8m0(c['x_sf']).cuda())
+    buf.topk_idx[:tokens].copy_(c['topk_idx'].cuda())
+    buf.topk_weights[:tokens].copy_(c['topk_weights'].cuda())
+    l1, l2 = _device_weights(dg, c)
+    y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+    dg.fp8_fp4_mega_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp)
+    from deepgemm_b200 import _lib
+    assert _lib.device_status()[0] == 0
+    return y.cpu(), buf
+
+
+def _plan_views(buf, tokens, topk, experts):
+    lay = buf.layout
+    raw = buf.buffer
+    dest = raw[lay['dest_row']:lay['dest_row'] + tokens * topk * 4].view(torch.int32).cpu()
+    end = raw[lay['expert_end']:lay['expert_end'] + experts * 4].view(torch.int32).cpu()
+    start = raw[lay['expert_start']:lay['expert_start'] + experts * 4].view(torch.int32).cpu()
+    return dest, start, end
+
+
+@pytest.mark.parametrize('tokens,hidden,inter,experts,topk', [
+    (200, 512, 256, 8, 2),
+    (77, 1024, 128, 16, 4),
+    (1, 256, 128, 4, 1),
+    (300, 256, 384, 5, 3),
+])
+def test_small_layer_matches_oracle(dg, tokens, hidden, inter, experts, topk):
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=tokens)
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+    stats = torch.full((experts,), 5, dtype=torch.int32, device='cuda')
+    got, buf = _run_layer(dg, c, tokens, hidden, inter, experts, topk, stats=stats)
+    dest, start, end = _plan_views(buf, tokens, topk, experts)
+    want_dest, _, want_start, want_end = omoe.dispatch_plan(c['topk_idx'], experts, 16)
+    assert torch.equal(dest, want_dest), 'dispatch permutation must be bit-exact'
+    assert torch.equal(start, want_start) and torch.equal(end, want_end)
+    assert torch.equal(stats.cpu(), 5 + (want_end - want_start))
+    assert not torch.isnan(got.float()).any()
+    assert quant.calc_diff(got, want) <= FP4_TOL
+
+
+def test_masked_slots_empty_experts_and_clamp(dg):
+    """topk_idx = -1 slots are skipped (reference: tests/test_mega_moe.py:131-134), two experts get no token,
+    and the activation clamp is applied before SwiGLU."""
+    tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 3
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=9, masked_ratio=0.3, empty_experts=(2, 5))
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'],
+                          c['l2_sf'], clamp=0.05)
+    got, buf = _run_layer(dg, c, tokens, hidden, inter, experts, topk, clamp=0.05)
+    dest, _, end = _plan_views(buf, tokens, topk, experts)
+    want_dest, _, _, want_end = omoe.dispatch_plan(c['topk_idx'], experts, 16)
+    assert torch.equal(dest, want_dest) and torch.equal(end, want_end)
+    assert (dest[c['topk_idx'].reshape(-1) < 0] == -1).all()
+    assert quant.calc_diff(got, want) <= FP4_TOL
+    fully_masked = (c['topk_idx'] < 0).all(dim=1)
+    assert (got[fully_masked] == 0).all()
+
+
+def test_buffer_is_reusable_and_deterministic(dg):
+    """Two calls on one buffer (fewer tokens the second time) give the same bits as fresh buffers: nothing of a
+    previous call leaks into the next (the reference cleans its workspace in-kernel, sm100_fp8_fp4_mega_moe.cuh:601-659)."""
+    hidden, inter, experts, topk = 512, 256, 8, 2
+    big = moe_case(256, hidden, inter, experts, topk, seed=21)
+    small = moe_case(100, hidden, inter, experts, topk, seed=22)
+    y_big, buf = _run_layer(dg, big, 256, hidden, inter, experts, topk)
+    y_small_reused, _ = _run_layer(dg, small, 100, hidden, inter, experts, topk, buf=buf)
+    y_small_fresh, _ = _run_layer(dg, small, 100, hidden, inter, experts, topk)
+    assert torch.equal(y_small_reused, y_small_fresh)
+    y_big_again, _ = _run_layer(dg, big, 256, hidden, inter, experts, topk, buf=buf)
+    assert torch.equal(y_big, y_big_again)
+
+
+def test_full_config_permutation_and_sampled_tokens(dg):
+    """BASELINE single-GPU layer at full size: 4096 tokens, hidden 7168, 256 experts, top-8, inter 2048.
+    Weights are drawn and quantised on the GPU expert by expert. Checked: routing + permutation bit-exact against
+    the oracle for all 32768 entries; y of sampled tokens against the oracle computed from the same quantised bits."""
+    tokens, hidden, inter, experts, topk = 4096, 7168, 2048, 256, 8
+    torch.manual_seed(0)
+    x = torch.randn(tokens, hidden, device='cuda', dtype=torch.bfloat16)
+    logits = torch.randn(tokens, experts, device='cuda')
+    l1_q = torch.empty((experts, 2 * inter, hidden // 2), dtype=torch.int8, device='cuda')
+    l1_sf = torch.empty((experts, 2 * inter, hidden // 32), dtype=torch.float32, device='cuda')
+    l2_q = torch.empty((experts, hidden, inter // 2), dtype=torch.int8, device='cuda')
+    l2_sf = torch.empty((experts, hidden, inter // 32), dtype=torch.float32, device='cuda')
+    for e in range(experts):
+        w = torch.randn(2 * inter, hidden, device='cuda', dtype=torch.bfloat16) * 0.02
+        l1_q[e], l1_sf[e] = dg.utils.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+        w = torch.randn(hidden, inter, device='cuda', dtype=torch.bfloat16) * 0.02
+        l2_q[e], l2_sf[e] = dg.utils.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+    l1_sf_p = dg.transform_sf_into_required_layout(l1_sf, 2 * inter, hidden, (1, 32), experts)
+    l2_sf_p = dg.transform_sf_into_required_layout(l2_sf, hidden, inter, (1, 32), experts)
+    l1, l2 = dg.transform_weights_for_mega_moe((l1_q, l1_sf_p), (l2_q, l2_sf_p))
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    x_q, x_sf = dg.utils.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32, use_packed_ue8m0=True)
+    buf.x.copy_(x_q)
+    buf.x_sf.copy_(x_sf)
+    dg.route_sigmoid_topk(logits, topk, buf.topk_idx, buf.topk_weights)
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
+    dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+    from deepgemm_b200 import _lib
+    assert _lib.device_status()[0] == 0
+
+    want_idx, want_w = omoe.route_sigmoid_topk(logits.cpu(), topk)
+    idx = buf.topk_idx.cpu()
+    assert torch.equal(idx, want_idx)
+    dest, start, end = _plan_views(buf, tokens, topk, experts)
+    want_dest, _, want_start, want_end = omoe.dispatch_plan(idx, experts, 16)
+    assert torch.equal(dest, want_dest) and torch.equal(end, want_end)
+    assert not torch.isnan(y.float()).any()
+
+    sample = [0, 1777, 4095]
+    w = buf.topk_weights.cpu()
+    x_q_c, x_sf_c = x_q.cpu(), quant.unpack_ue8m0(x_sf.cpu())
+    for t in sample:
+        acc = torch.zeros(hidden)
+        for k in range(topk):
+            e = int(idx[t, k])
+            a1 = quant.dequantize_fp8(x_q_c[t:t + 1], x_sf_c[t:t + 1], 32) @ quant.dequantize_fp4(l1_q[e].cpu(), l1_sf[e].cpu(), 32).T
+            a2_q, a2_sf = omoe.swiglu_requant(a1, w[t:t + 1, k], None)
+            a2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(l2_q[e].cpu(), l2_sf[e].cpu(), 32).T
+            acc += a2.bfloat16().float()[0]
+        assert quant.calc_diff(y[t].cpu(), acc.bfloat16()) <= FP4_TOL

@@ -1,0 +1,74 @@
+"""CPU tests of the oracle's own logic (dispatch plan, layer composition, layouts) on small seeded cases."""
+import torch
+
+from oracle import gemm as ogemm
+from oracle import moe as omoe
+from oracle import quant
+from tests.helpers import contiguous_case, moe_case
+
+
+def test_dispatch_plan_is_a_stable_sort_by_expert():
+    torch.manual_seed(0)
+    idx = torch.randint(-1, 6, (50, 3))
+    dest, src, start, end = omoe.dispatch_plan(idx, 6, 16)
+    flat = idx.reshape(-1)
+    assert (dest[flat < 0] == -1).all()
+    valid = torch.nonzero(flat >= 0).reshape(-1)
+    assert len(set(dest[valid].tolist())) == valid.numel()
+    for e in range(6):
+        entries = torch.nonzero(flat == e).reshape(-1)
+        rows = dest[entries]
+        assert rows.tolist() == list(range(int(start[e]), int(end[e])))  # stable: entry order preserved
+        assert int(start[e]) % 16 == 0
+    assert torch.equal(src[dest[valid].long()].long(), valid)
+    assert (src[src >= 0].numel()) == valid.numel()
+
+
+def test_dispatch_plan_expert_window():
+    idx = torch.tensor([[0, 5], [4, 7], [6, 1]])
+    dest, src, start, end = omoe.dispatch_plan(idx, 4, 4, expert_lo=4)
+    assert dest.tolist() == [-1, 4, 0, 12, 8, -1]
+    assert (end - start).tolist() == [1, 1, 1, 1]
+
+
+def test_layer_equals_per_token_evaluation():
+    c = moe_case(12, 256, 128, 4, 2, seed=3)
+    y = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+    x = quant.dequantize_fp8(c['x_q'], c['x_sf'], 32)
+    for t in range(12):
+        acc = torch.zeros(256)
+        for k in range(2):
+            e = int(c['topk_idx'][t, k])
+            a1 = x[t:t + 1] @ quant.dequantize_fp4(c['l1_q'][e], c['l1_sf'][e], 32).T
+            q, sf = omoe.swiglu_requant(a1, c['topk_weights'][t:t + 1, k], None)
+            a2 = quant.dequantize_fp8(q, sf, 32) @ quant.dequantize_fp4(c['l2_q'][e], c['l2_sf'][e], 32).T
+            acc += a2.bfloat16().float()[0]
+        assert quant.calc_diff(y[t], acc.bfloat16()) < 1e-6
+
+
+def test_swiglu_requant_scale_rule():
+    acc = torch.zeros(2, 128)
+    acc[0, :64] = 3.0      # gate
+    acc[0, 64:] = 2.0      # up
+    q, sf = omoe.swiglu_requant(acc, torch.tensor([0.5, 1.0]), None)
+    value = 3.0 / (1 + torch.exp(torch.tensor(-3.0))) * 2.0 * 0.5
+    expect_sf = quant.ue8m0_ceil(value * torch.tensor(1.0 / 448.0))
+    assert torch.equal(sf[0], expect_sf.expand(2))
+    assert float(sf[1, 0]) == 2.0 ** -126  # all-zero group: smallest UE8M0 scale, no 1e-4 clamp
+    clamped, _ = omoe.swiglu_requant(acc * 100, torch.ones(2), 1.0)
+    assert torch.isfinite(clamped.float()).all()
+
+
+def test_router_renormalises_and_breaks_ties_low():
+    logits = torch.tensor([[0.0, 1.0, 1.0, -2.0], [3.0, 3.0, 3.0, 3.0]])
+    idx, w = omoe.route_sigmoid_topk(logits, 2)
+    assert idx.tolist() == [[1, 2], [0, 1]]
+    assert torch.allclose(w.sum(dim=1), torch.ones(2))
+
+
+def test_contiguous_and_psum_oracles_agree():
+    c = contiguous_case(3, 128, 256, 5, 40, seed=1)
+    d1, m1 = ogemm.grouped_gemm_contiguous(c['a_q'], c['a_sf'], c['b_q'], c['b_sf'], c['row_ids'])
+    d2, m2 = ogemm.grouped_gemm_contiguous(c['a_q'], c['a_sf'], c['b_q'], c['b_sf'], c['psum'], use_psum_layout=True)
+    assert torch.equal(m1, m2) and torch.equal(d1[m1], d2[m2])
+    assert int(m1.sum()) == sum(c['ms'])
