@@ -18,7 +18,8 @@ namespace {
 constexpr int kVersion = 100;
 
 template <int BLOCK_N, int kStages, int EPI>
-int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmParams& p, int grid, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_sfa, const CUtensorMap& tm_sfb,
+                const GemmParams& p, int grid, cudaStream_t stream) {
     using L = GemmSmem<BLOCK_N, kStages>;
     auto kernel = dgb200_grouped_gemm_kernel<BLOCK_N, kStages, EPI>;
     static bool configured = false;  // per instantiation; the attribute is per device function, set on every device once
@@ -30,7 +31,7 @@ int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmPara
         configured = true;
         configured_device = dev;
     }
-    kernel<<<grid, 256, L::kDynamicBytes, stream>>>(tm_a, tm_b, p);
+    kernel<<<grid, 256, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, p);
     DGB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -38,12 +39,36 @@ int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmPara
 struct GemmCall {
     const void* a;
     const void* b;
+    const void* sfa;  // packed UE8M0 int32: int (group, kp, row) at sfa[group * sfa_group_stride + kp * sfa_k_stride + row]
+    const void* sfb;
+    long long sfa_k_stride, sfa_group_stride, sfb_k_stride, sfb_group_stride;
+    int num_groups_a;  // groups of A's scale factors: 1 for the contiguous layouts, num_groups for the masked one
     long long a_rows_total;  // rows of the flattened A
     GemmParams p;
     int b_is_fp4;
     int epilogue;
     int max_tiles;  // upper bound on tiles, <= 0 if unknown
 };
+
+// Tuning knobs read once from the environment (defaults are the measured best on B200).
+struct Tuning {
+    int prefetch_distance = 0;
+    int prefetch_mask = 7;
+    int block_n = 0;  // 0 = automatic
+    int debug_skip = 0;
+    long long* trace = nullptr;  // debugging: per-role clock64() samples of CTA 0 (8 roles x trace_cap)
+    int trace_cap = 0;
+};
+
+Tuning& tuning() {
+    static Tuning t = [] {
+        Tuning v;
+        if (const char* s = std::getenv("DGB200_PREFETCH_DISTANCE")) v.prefetch_distance = std::max(0, std::atoi(s));
+        if (const char* s = std::getenv("DGB200_PREFETCH_MASK")) v.prefetch_mask = std::atoi(s) & 7;
+        return v;
+    }();
+    return t;
+}
 
 int run_gemm(GemmCall& c, cudaStream_t stream) {
     GemmParams& p = c.p;
@@ -52,24 +77,41 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     DGB_REQUIRE(p.gran_a == 32 || p.gran_a == 128, "gran_k_a must be 32 or 128, got %d", p.gran_a);
     DGB_REQUIRE(p.gran_b == 32 || p.gran_b == 128, "gran_k_b must be 32 or 128, got %d", p.gran_b);
     DGB_REQUIRE(p.num_groups > 0, "num_groups must be positive");
-    DGB_REQUIRE(c.a != nullptr && c.b != nullptr && p.sfa != nullptr && p.sfb != nullptr && p.layout != nullptr,
+    DGB_REQUIRE(c.a != nullptr && c.b != nullptr && c.sfa != nullptr && c.sfb != nullptr && p.layout != nullptr,
                 "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.a) % 16 == 0, "a must be 16-byte aligned");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.b) % 32 == 0, "b must be 32-byte aligned");
-    DGB_REQUIRE(reinterpret_cast<uintptr_t>(p.sfa) % 16 == 0 && reinterpret_cast<uintptr_t>(p.sfb) % 16 == 0,
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.sfa) % 16 == 0 && reinterpret_cast<uintptr_t>(c.sfb) % 16 == 0,
                 "scale-factor tensors must be 16-byte aligned");
-    DGB_REQUIRE(p.sfa_k_stride % 4 == 0 && p.sfb_k_stride % 4 == 0 && p.sfa_group_stride % 4 == 0 &&
-                    p.sfb_group_stride % 4 == 0,
-                "packed scale-factor strides must be multiples of 4 ints (TMA-aligned MN stride)");
+    DGB_REQUIRE(c.sfa_k_stride % 4 == 0 && c.sfb_k_stride % 4 == 0 && c.sfa_k_stride > 0 && c.sfb_k_stride >= p.n,
+                "packed scale-factor MN strides must be positive multiples of 4 ints (TMA-aligned) that cover MN");
+    const int packed_k_a = (p.k / p.gran_a + 3) / 4, packed_k_b = (p.k / p.gran_b + 3) / 4;
+    DGB_REQUIRE(c.num_groups_a == 1 || c.sfa_group_stride == packed_k_a * c.sfa_k_stride,
+                "scale factors of A: group stride must equal packed K x MN stride");
+    DGB_REQUIRE(p.num_groups == 1 || c.sfb_group_stride == packed_k_b * c.sfb_k_stride,
+                "scale factors of B: group stride must equal packed K x MN stride");
+    p.sfa_group_rows = c.num_groups_a > 1 ? packed_k_a : 0;
+    p.sfb_packed_k = packed_k_b;
     if (c.a_rows_total == 0) return 0;
 
-    CUtensorMap tm_a, tm_b;
-    int rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, static_cast<uint64_t>(p.k),
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+    int rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
+                                static_cast<uint64_t>(packed_k_a) * c.num_groups_a,
+                                static_cast<uint64_t>(c.sfa_k_stride) * 4, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    // Wide N tiles give each tcgen05.mma enough work (128 x 256 x 32) to cover the per-K-block issue chain.
+    const int block_n = tuning().block_n != 0 ? tuning().block_n : (p.n % 256 == 0 ? 256 : 128);
+    DGB_REQUIRE((block_n == 128 || block_n == 256) && p.n % block_n == 0, "block_n %d does not divide n %d", block_n, p.n);
+    rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
+                            static_cast<uint64_t>(packed_k_b) * p.num_groups, static_cast<uint64_t>(c.sfb_k_stride) * 4,
+                            static_cast<uint32_t>(block_n), 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, static_cast<uint64_t>(p.k),
                                 static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.k), 128, 128,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     const uint64_t b_rows = static_cast<uint64_t>(p.num_groups) * p.n;
-    constexpr int BLOCK_N = 128;
+    const uint32_t BLOCK_N = static_cast<uint32_t>(block_n);
     if (c.b_is_fp4) {
         rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, c.b, static_cast<uint64_t>(p.k), b_rows,
                                 static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -85,20 +127,30 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     }
     if (rc) return rc;
 
+    p.prefetch_distance = tuning().prefetch_distance;
+    p.prefetch_mask = tuning().prefetch_mask;
+    p.debug_skip = tuning().debug_skip;
+    p.trace = tuning().trace;
+    p.trace_cap = tuning().trace_cap;
+
     int sms = 0;
     rc = effective_num_sms(&sms);
     if (rc) return rc;
     int grid = sms;
     if (c.max_tiles > 0) grid = std::min(grid, c.max_tiles);
 
-    constexpr int kStages = 6;
+    if (c.max_tiles > 0 && block_n == 256) grid = std::min(grid, std::max(1, c.max_tiles / 2));
+#define DGB_LAUNCH(EPI)                                                                                        \
+    return block_n == 256 ? launch_gemm<256, 4, EPI>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)              \
+                          : launch_gemm<128, 6, EPI>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)
     switch (c.epilogue) {
-        case kEpiBF16: return launch_gemm<BLOCK_N, kStages, kEpiBF16>(tm_a, tm_b, p, grid, stream);
-        case kEpiF32: return launch_gemm<BLOCK_N, kStages, kEpiF32>(tm_a, tm_b, p, grid, stream);
-        case kEpiSwiGLU: return launch_gemm<BLOCK_N, kStages, kEpiSwiGLU>(tm_a, tm_b, p, grid, stream);
-        case kEpiScatter: return launch_gemm<BLOCK_N, kStages, kEpiScatter>(tm_a, tm_b, p, grid, stream);
+        case kEpiBF16: DGB_LAUNCH(kEpiBF16);
+        case kEpiF32: DGB_LAUNCH(kEpiF32);
+        case kEpiSwiGLU: DGB_LAUNCH(kEpiSwiGLU);
+        case kEpiScatter: DGB_LAUNCH(kEpiScatter);
         default: return fail(DGB200_EINVAL, "unknown epilogue %d", c.epilogue);
     }
+#undef DGB_LAUNCH
 }
 
 
@@ -218,6 +270,30 @@ int dgb200_set_num_sms(int num_sms) {
     return 0;
 }
 
+int dgb200_set_tuning(const char* name, int32_t value) {
+    DGB_REQUIRE(name != nullptr, "null name");
+    if (std::strcmp(name, "prefetch_distance") == 0) {
+        DGB_REQUIRE(value >= 0 && value <= 4096, "prefetch_distance must be in [0, 4096]");
+        tuning().prefetch_distance = value;
+    } else if (std::strcmp(name, "prefetch_mask") == 0) {
+        tuning().prefetch_mask = value & 7;
+    } else if (std::strcmp(name, "block_n") == 0) {
+        DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
+        tuning().block_n = value;
+    } else if (std::strcmp(name, "debug_skip") == 0) {
+        tuning().debug_skip = value;
+    } else {
+        return fail(DGB200_EINVAL, "unknown tuning knob '%s'", name);
+    }
+    return 0;
+}
+
+int dgb200_debug_set_trace(void* device_buffer, int32_t capacity_per_role) {
+    tuning().trace = static_cast<long long*>(device_buffer);
+    tuning().trace_cap = device_buffer != nullptr ? capacity_per_role : 0;
+    return 0;
+}
+
 int dgb200_get_num_sms(void) {
     int sms = 0;
     if (effective_num_sms(&sms) != 0) return -1;
@@ -263,13 +339,13 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
     c.b_is_fp4 = b_is_fp4;
     c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
     GemmParams& p = c.p;
-    p.sfa = static_cast<const uint32_t*>(sfa);
-    p.sfb = static_cast<const uint32_t*>(sfb);
-    p.sfa_k_stride = sfa_k_stride;
-    p.sfa_group_stride = 0;
-    p.sfa_rows = sfa_k_stride;
-    p.sfb_k_stride = sfb_k_stride;
-    p.sfb_group_stride = sfb_group_stride;
+    c.sfa = sfa;
+    c.sfb = sfb;
+    c.sfa_k_stride = sfa_k_stride;
+    c.sfa_group_stride = 0;
+    c.num_groups_a = 1;
+    c.sfb_k_stride = sfb_k_stride;
+    c.sfb_group_stride = sfb_group_stride;
     p.d = d;
     p.d_row_stride = d_row_stride;
     p.layout = grouped_layout;
@@ -306,13 +382,13 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
     c.b_is_fp4 = b_is_fp4;
     c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
     GemmParams& p = c.p;
-    p.sfa = static_cast<const uint32_t*>(sfa);
-    p.sfb = static_cast<const uint32_t*>(sfb);
-    p.sfa_k_stride = sfa_k_stride;
-    p.sfa_group_stride = sfa_group_stride;
-    p.sfa_rows = sfa_k_stride;
-    p.sfb_k_stride = sfb_k_stride;
-    p.sfb_group_stride = sfb_group_stride;
+    c.sfa = sfa;
+    c.sfb = sfb;
+    c.sfa_k_stride = sfa_k_stride;
+    c.sfa_group_stride = sfa_group_stride;
+    c.num_groups_a = num_groups;
+    c.sfb_k_stride = sfb_k_stride;
+    c.sfb_group_stride = sfb_group_stride;
     p.d = d;
     p.d_row_stride = d_row_stride;
     p.layout = masked_m;
@@ -434,7 +510,7 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                 num_tokens, num_max_tokens_per_rank);
     DGB_REQUIRE(y != nullptr && l1_w != nullptr && l1_w_sf != nullptr && l2_w != nullptr && l2_w_sf != nullptr && buffer != nullptr,
                 "null tensor pointer");
-    DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 1024 == 0, "buffer must be 1024-byte aligned");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 256 == 0, "buffer must be 256-byte aligned");
     DGB_REQUIRE((2 * intermediate_hidden) % 128 == 0 && intermediate_hidden % 64 == 0, "intermediate_hidden must be a multiple of 64");
     if (num_tokens == 0) return 0;
 
@@ -483,13 +559,13 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
         c.epilogue = kEpiSwiGLU;
         c.max_tiles = 0;
         GemmParams& p = c.p;
-        p.sfa = reinterpret_cast<const uint32_t*>(base + l.l1_sf);
-        p.sfb = static_cast<const uint32_t*>(l1_w_sf);
-        p.sfa_k_stride = l.max_rows;
-        p.sfa_group_stride = 0;
-        p.sfa_rows = l.max_rows;
-        p.sfb_k_stride = 2 * intermediate_hidden;
-        p.sfb_group_stride = static_cast<long long>(hidden / 128) * 2 * intermediate_hidden;
+        c.sfa = base + l.l1_sf;
+        c.sfb = l1_w_sf;
+        c.sfa_k_stride = l.max_rows;
+        c.sfa_group_stride = 0;
+        c.num_groups_a = 1;
+        c.sfb_k_stride = 2 * intermediate_hidden;
+        c.sfb_group_stride = static_cast<long long>(hidden / 128) * 2 * intermediate_hidden;
         p.layout = expert_end;
         p.mode = kModePsum;
         p.m = static_cast<int>(l.max_rows);
@@ -519,13 +595,13 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
         c.epilogue = kEpiScatter;
         c.max_tiles = 0;
         GemmParams& p = c.p;
-        p.sfa = reinterpret_cast<const uint32_t*>(base + l.l2_sf);
-        p.sfb = static_cast<const uint32_t*>(l2_w_sf);
-        p.sfa_k_stride = l.max_rows;
-        p.sfa_group_stride = 0;
-        p.sfa_rows = l.max_rows;
-        p.sfb_k_stride = hidden;
-        p.sfb_group_stride = static_cast<long long>(intermediate_hidden / 128) * hidden;
+        c.sfa = base + l.l2_sf;
+        c.sfb = l2_w_sf;
+        c.sfa_k_stride = l.max_rows;
+        c.sfa_group_stride = 0;
+        c.num_groups_a = 1;
+        c.sfb_k_stride = hidden;
+        c.sfb_group_stride = static_cast<long long>(intermediate_hidden / 128) * hidden;
         p.layout = expert_end;
         p.mode = kModePsum;
         p.m = static_cast<int>(l.max_rows);

@@ -42,10 +42,10 @@ enum EpilogueKind : int {
 constexpr int kMaxRanks = 8;
 
 struct GemmParams {
-    const uint32_t* sfa;  // packed UE8M0, MN-major: int index = group*sfa_group_stride + kp*sfa_k_stride + row
-    const uint32_t* sfb;  // same for B:            int index = group*sfb_group_stride + kp*sfb_k_stride + channel
-    long long sfa_k_stride, sfa_group_stride, sfa_rows;  // sfa_rows: addressable rows per group (multiple of 4)
-    long long sfb_k_stride, sfb_group_stride;
+    // Scale factors are read through tensor maps over int32 [groups * packed_k, aligned MN] (packed UE8M0, MN-major):
+    // int (group, kp, row) sits at outer coordinate group * packed_k + kp, inner coordinate row.
+    int sfa_group_rows;  // packed K ints per group of A's scale factors (0 when A is not grouped)
+    int sfb_packed_k;    // packed K ints per group of B's scale factors
     void* d;
     long long d_row_stride;  // elements
     const int* layout;
@@ -54,6 +54,12 @@ struct GemmParams {
     unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
     unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
     int store_padding;       // psum only: also write the rows between a group's end and its aligned end
+    int prefetch_distance;   // K blocks the producer's L2 prefetch cursor runs ahead of its loads (0 = off)
+    int prefetch_mask;       // bit 0: B tiles, bit 1: A tiles, bit 2: scale factors
+    int debug_skip;          // timing experiments only (results become garbage): bit 0 no A loads, 1 no B loads,
+                             // 2 no scale-factor loads, 3 no MMA instructions, 4 no scale-factor TMEM copies
+    long long* trace;        // optional: CTA 0 records clock64() per role and K block at trace[role * trace_cap + i]
+    int trace_cap;
     // SwiGLU epilogue only
     unsigned char* act_q;        // e4m3 [rows, n/2]
     unsigned char* act_sf;       // packed UE8M0 bytes, MN-major ints: ((j/128)*act_sf_k_stride + row)*4 + (j/32)%4
@@ -168,9 +174,22 @@ __device__ __forceinline__ void ue8m0_scale_for_amax(float amax, float& sf_inv, 
     sf_inv = __uint_as_float((254u - e) << 23);  // 2^(127-e)
 }
 
+// Instrumentation (per-role clock samples, load / MMA skipping for timing experiments) is compiled in only with
+// -DDGB200_INSTRUMENT: even a never-taken branch is measurable in the single-thread issue loops below.
+#ifdef DGB200_INSTRUMENT
+__device__ __forceinline__ void trace_point(const GemmParams& p, int role, int index) {
+    if (p.trace != nullptr && blockIdx.x == 0 && index < p.trace_cap) p.trace[role * p.trace_cap + index] = clock64();
+}
+#define DGB_SKIP(p, bit) (((p).debug_skip & (bit)) != 0)
+#else
+__device__ __forceinline__ void trace_point(const GemmParams&, int, int) {}
+#define DGB_SKIP(p, bit) false
+#endif
+
 template <int BLOCK_N, int kStages, int EPI>
 __global__ void __launch_bounds__(256, 1)
 dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                           const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                            const __grid_constant__ GemmParams p) {
     using L = GemmSmem<BLOCK_N, kStages>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
@@ -209,6 +228,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         fence_mbar_init();
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
+        prefetch_tensormap(&tm_sfa);
+        prefetch_tensormap(&tm_sfb);
     }
     if (warp == 2) tmem_alloc(tmem_ptr_smem, kTmemCols);
     tcgen05_fence_before();
@@ -227,32 +248,68 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            int trace_i = 0;
+
+            // L2 prefetch cursor: walks the same (tile, K block) sequence `prefetch_distance` blocks ahead of the
+            // loads, so that HBM latency is covered by requests in flight to L2 rather than by shared-memory stages
+            // (a stage holds only 8 KB of packed FP4 weights).
+            TileScheduler<BLOCK_N> pf_sched(p);
+            Tile pt;
+            int pf_kb = 0;
+            bool pf_valid = false;
+            auto pf_next_tile = [&]() {
+                pf_valid = false;
+                while (pf_sched.next(pt)) {
+                    if (pt.group >= 0) { pf_valid = true; break; }
+                }
+                pf_kb = 0;
+            };
+            auto pf_advance = [&]() {
+                if (!pf_valid) return;
+                if (p.prefetch_mask & 1)
+                    tma_prefetch_2d(&tm_b, pf_kb * 128, pt.group * p.n + pt.n_block * BLOCK_N);
+                if (p.prefetch_mask & 2) tma_prefetch_2d(&tm_a, pf_kb * 128, pt.row_start);
+                if (p.prefetch_mask & 4) {
+                    if (pf_kb % b_per == 0)
+                        tma_prefetch_2d(&tm_sfb, pt.n_block * BLOCK_N, pt.group * p.sfb_packed_k + pf_kb / b_per);
+                    if (pf_kb % a_per == 0)
+                        tma_prefetch_2d(&tm_sfa, pt.sf_row_start, pt.group * p.sfa_group_rows + pf_kb / a_per);
+                }
+                if (++pf_kb == num_kb) pf_next_tile();
+            };
+            if (p.prefetch_distance > 0) {
+                pf_next_tile();
+                for (int i = 0; i < p.prefetch_distance; ++i) pf_advance();
+            }
+
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
-                const long long sfa_base = static_cast<long long>(t.group) * p.sfa_group_stride + t.sf_row_start;
-                const uint32_t sfa_bytes =
-                    static_cast<uint32_t>(min(128ll, p.sfa_rows - t.sf_row_start)) * 4u;
-                const long long sfb_base =
-                    static_cast<long long>(t.group) * p.sfb_group_stride + static_cast<long long>(t.n_block) * BLOCK_N;
                 const int b_row = t.group * p.n + t.n_block * BLOCK_N;
+                const int sfa_y = t.group * p.sfa_group_rows, sfb_y = t.group * p.sfb_packed_k;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfa = kb % a_per == 0, load_sfb = kb % b_per == 0;
-                    uint32_t bytes = L::kABytes + p.b_tx_bytes;
-                    if (load_sfa) bytes += sfa_bytes;
+                    trace_point(p, 0, trace_i);
+                    const bool skip_sf = DGB_SKIP(p, 4);
+                    const bool load_sfa = kb % a_per == 0 && !skip_sf, load_sfb = kb % b_per == 0 && !skip_sf;
+                    uint32_t bytes = 0;
+                    if (!DGB_SKIP(p, 1)) bytes += L::kABytes;
+                    if (!DGB_SKIP(p, 2)) bytes += p.b_tx_bytes;
+                    if (load_sfa) bytes += L::kSfaBytes;
                     if (load_sfb) bytes += L::kSfbBytes;
                     mbar_arrive_expect_tx(full_bar + stage, bytes);
-                    tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128, t.row_start);
-                    tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
+                    if (!DGB_SKIP(p, 1))
+                        tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128, t.row_start);
+                    if (!DGB_SKIP(p, 2))
+                        tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
                     if (load_sfa)
-                        bulk_load_1d(smem + L::kOffSfa + stage * L::kSfaBytes,
-                                     p.sfa + sfa_base + static_cast<long long>(kb / a_per) * p.sfa_k_stride,
-                                     sfa_bytes, full_bar + stage);
+                        tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage, t.sf_row_start,
+                                    sfa_y + kb / a_per);
                     if (load_sfb)
-                        bulk_load_1d(smem + L::kOffSfb + stage * L::kSfbBytes,
-                                     p.sfb + sfb_base + static_cast<long long>(kb / b_per) * p.sfb_k_stride,
-                                     L::kSfbBytes, full_bar + stage);
+                        tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
+                                    t.n_block * BLOCK_N, sfb_y + kb / b_per);
+                    if (p.prefetch_distance > 0) pf_advance();
+                    trace_point(p, 1, trace_i++);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -262,6 +319,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         TileScheduler<BLOCK_N> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
+        int trace_i = 0;
         const uint32_t idesc = make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
@@ -279,9 +337,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 if (!ok) break;
                 tcgen05_fence_after();
                 if (lane == 0) {
-                    if (kb % a_per == 0)
+                    trace_point(p, 4, trace_i);
+                    if (kb % a_per == 0 && !DGB_SKIP(p, 16))
                         tcgen05_cp_32x128b_warpx4(tmem_base + kSfaCol, make_sf_desc(sfa_smem + stage * L::kSfaBytes));
-                    if (kb % b_per == 0) {
+                    if (kb % b_per == 0 && !DGB_SKIP(p, 16)) {
 #pragma unroll
                         for (int i = 0; i < BLOCK_N / 128; ++i)
                             tcgen05_cp_32x128b_warpx4(tmem_base + kSfbCol + i * 4,
@@ -294,14 +353,17 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                         const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
+                        if (DGB_SKIP(p, 8)) continue;
                         tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
                                              idesc_with_sf_ids(idesc, sfa_id, sfb_id),
                                              tmem_base + kSfaCol, tmem_base + kSfbCol, (kb | k4) != 0 ? 1u : 0u);
                     }
                     tcgen05_commit(empty_bar + stage);
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
+                    trace_point(p, 5, trace_i);
                 }
                 __syncwarp();
+                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -311,12 +373,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         TileScheduler<BLOCK_N> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
+        int trace_i = 0;
         bool ok = true;
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
+                if (lane == 0) trace_point(p, 2, trace_i);
                 if (kb % a_per == 0) {
                     uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
                     const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
@@ -334,6 +398,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(sf_ready_bar + stage);
+                if (lane == 0) trace_point(p, 3, trace_i);
+                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -352,6 +418,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             ok = mbar_wait(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
             if (!ok) break;
             tcgen05_fence_after();
+            if (threadIdx.x == 128) trace_point(p, 6, static_cast<int>(iter) - 1);
             const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16);
             const bool store = r < t.rows_store;
             const long long row = static_cast<long long>(t.row_start) + r;
@@ -439,6 +506,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             }
             tcgen05_fence_before();
             mbar_arrive(tmem_empty_bar + as);
+            if (threadIdx.x == 128) trace_point(p, 7, static_cast<int>(iter) - 1);
         }
     }
 

@@ -107,21 +107,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Budget of one wait. Two seconds is several orders of magnitude above any legitimate stage wait.
-constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+// Budget of one wait in SM clock cycles: about two seconds at 2 GHz, several orders of magnitude above any
+// legitimate stage wait. The SM-local clock is used because reading %globaltimer costs hundreds of cycles.
+constexpr long long kWaitBudgetCycles = 4000000000ll;
 
 // Bounded wait. `abort_flag` is a CTA-shared word: once any role of the CTA gives up, the others
 // stop at their next poll instead of each burning their own budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           int code, int detail) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (((++spins) & 0xffu) == 0) {
+        if (((++spins) & 0x3ffu) == 0) {
             if (*abort_flag != 0) return false;
-            if (global_timer_ns() - t0 > kWaitBudgetNs) {
+            const long long now = clock64();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitBudgetCycles) {
                 *abort_flag = static_cast<uint32_t>(code);
                 report_error(code, detail, static_cast<int>(parity));
                 return false;
@@ -142,6 +146,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// L2 prefetch of one tile / one span: starts the HBM read early without occupying shared memory.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 :: "l"(map), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void bulk_prefetch_1d(const void* gmem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gmem_src), "r"(bytes) : "memory");
 }
 
 // `bytes` must be a multiple of 16; both addresses 16-byte aligned.

@@ -105,8 +105,8 @@ def _interleave_rows(t: torch.Tensor, gran: int) -> torch.Tensor:
     if half % gran != 0:
         raise RuntimeError(f'intermediate size {half} must be a multiple of {gran}')
     r = torch.arange(n, device=t.device)
-    src = torch.where(r % (2 * gran) < gran, gran * (r // (2 * gran)) + r % gran,
-                      half + gran * (r // (2 * gran)) + r % gran - gran)
+    block, within = r // (2 * gran), r % (2 * gran)
+    src = torch.where(within < gran, gran * block + within, half + gran * block + within - gran)
     out = torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device)
     out.copy_(t.index_select(1, src))
     return out

@@ -37,6 +37,17 @@ int dgb200_version(void);
 int dgb200_set_num_sms(int num_sms);
 int dgb200_get_num_sms(void);
 
+/* Process-wide tuning knobs of the GEMM kernels: "prefetch_distance" (K blocks the L2 prefetch cursor runs ahead,
+ * 0 = off; also DGB200_PREFETCH_DISTANCE in the environment) and "prefetch_mask" (bit 0 weights, bit 1 activations,
+ * bit 2 scale factors; DGB200_PREFETCH_MASK). Plays the role of the reference's heuristics overrides
+ * (csrc/apis/runtime.hpp:21-41). */
+int dgb200_set_tuning(const char* name, int32_t value);
+
+/* Debugging aid: while set, CTA 0 of every GEMM launch records clock64() per warp role and K block into
+ * device_buffer (int64 [8][capacity_per_role]; roles: 0/1 producer before/after issue, 2/3 scale-factor transposer,
+ * 4/5 MMA issuer, 6/7 epilogue per tile). NULL switches it off. No reference counterpart. */
+int dgb200_debug_set_trace(void* device_buffer, int32_t capacity_per_role);
+
 /* Synchronises `stream`, copies the 8-word device status block to `out_words` (may be NULL) and clears it.
  * Returns DGB200_EDEVICE when word 0 is non-zero. Words: {code, block, detail a, detail b, 0, 0, 0, 0}.
  * Replaces the reference's device-side printf + trap (deep_gemm/include/deep_gemm/comm/barrier.cuh:36-41,
