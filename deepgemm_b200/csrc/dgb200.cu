@@ -31,7 +31,7 @@ int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensor
         configured = true;
         configured_device = dev;
     }
-    kernel<<<grid, 256, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, p);
+    kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, p);
     DGB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -498,7 +498,6 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                             int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
                             int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                             float activation_clamp, int32_t fast_math, void* stream_) {
-    (void)fast_math;  // the SwiGLU epilogue always uses the fast exponential, as the reference does by default
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     MegaLayout l;
     int rc = make_mega_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
@@ -581,6 +580,7 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
         p.act_sf_k_stride = l.max_rows;
         p.row_weight = row_weight;
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
+        p.fast_math = fast_math;
         rc = run_gemm(c, stream);
         if (rc) return rc;
     }

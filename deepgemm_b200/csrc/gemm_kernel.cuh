@@ -15,8 +15,10 @@
 //   * Stores are clipped to the valid rows of a group, so a masked group never writes into its neighbour.
 //   * Every wait is bounded; a timeout unwinds the CTA and is reported through the status block.
 //
-// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator + scale-factor
-// transposer, warp 3 idle, warps 4-7 epilogue (TMEM lane quarter = warp index % 4).
+// Warp roles (384 threads): warp 0 loads A tiles and both scale-factor rows, warp 3 loads the weight tiles and runs the
+// L2 prefetch cursor, warp 1 issues the MMAs, warp 2 allocates TMEM and transposes scale factors for tcgen05.cp,
+// warps 4-11 are the epilogue (TMEM lane quarter = warp index % 4, two warps per quarter splitting the columns).
+// The control warpgroup hands registers to the epilogue warpgroups with setmaxnreg.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -67,6 +69,7 @@ struct GemmParams {
     long long act_sf_k_stride;   // ints
     const float* row_weight;     // per destination row, may be null (weight 1)
     float clamp;                 // <= 0: no clamp
+    int fast_math;               // SwiGLU: approximate exp / reciprocal (the reference's default) or IEEE expf and division
     // Scatter epilogue only: row r belongs to entry e = row_src[r] % (combine_tokens * topk) of rank
     // row_src[r] / (combine_tokens * topk); entry e = token * topk + slot lands in
     // combine_base[rank][(slot * combine_tokens + token) * n + column].
@@ -186,8 +189,12 @@ __device__ __forceinline__ void trace_point(const GemmParams&, int, int) {}
 #define DGB_SKIP(p, bit) false
 #endif
 
+constexpr int kGemmThreads = 384;       // warps 0-3: loaders / MMA / transposer; warps 4-11: epilogue
+constexpr int kRegsControlWarps = 96;   // after setmaxnreg: the control warpgroup gives registers away ...
+constexpr int kRegsEpilogueWarps = 200; // ... to the two epilogue warpgroups, which hold a drained accumulator
+
 template <int BLOCK_N, int kStages, int EPI>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                            const __grid_constant__ GemmParams p) {
@@ -198,7 +205,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     constexpr uint32_t kSfaCol = kAccumCols * kNumAccum;
     constexpr uint32_t kSfbCol = kSfaCol + 4;
     constexpr uint32_t kTmemCols = 512;
-    static_assert(kSfbCol + BLOCK_N / 32 <= kTmemCols || kNumAccum == 1, "TMEM budget");
+    static_assert(kSfbCol + BLOCK_N / 32 <= kTmemCols, "TMEM budget");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -217,13 +224,13 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(full_bar + i, 1);
-            mbar_init(empty_bar + i, 1);
-            mbar_init(sf_ready_bar + i, 32);
+            mbar_init(full_bar + i, 2);       // the A-side loader and the B-side loader
+            mbar_init(empty_bar + i, 1);      // tcgen05.commit of the MMA issuer
+            mbar_init(sf_ready_bar + i, 32);  // every lane of the transposer warp
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(tmem_full_bar + i, 1);
-            mbar_init(tmem_empty_bar + i, 128);
+            mbar_init(tmem_empty_bar + i, 8);  // lane 0 of each epilogue warp
         }
         fence_mbar_init();
         prefetch_tensormap(&tm_a);
@@ -241,18 +248,53 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     const int a_per = p.gran_a == 32 ? 1 : 4;  // K blocks covered by one packed SF int
     const int b_per = p.gran_b == 32 ? 1 : 4;
 
+    // Register re-balancing: each setmaxnreg dominates the code of its warpgroups, so that the compiler allocates
+    // the epilogue (which holds half an accumulator row in registers) under the raised limit.
+    if (warp < 4) {
+    setmaxnreg_dec<kRegsControlWarps>();
     if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer
+        // ---------------------------------------------------------------- loader: A tile + both scale-factor rows
+        // TMA instructions cost on the order of 100 cycles each in the issuing thread, so the loads of one stage are
+        // split over two threads (this one and warp 3); both arrive on the stage's full barrier with their own bytes.
         if (lane == 0) {
             TileScheduler<BLOCK_N> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int trace_i = 0;
+            while (ok && sched.next(t)) {
+                if (t.group < 0) continue;
+                const int sfa_y = t.group * p.sfa_group_rows, sfb_y = t.group * p.sfb_packed_k;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
+                    if (!ok) break;
+                    trace_point(p, 0, trace_i);
+                    const bool load_sfa = kb % a_per == 0, load_sfb = kb % b_per == 0;
+                    mbar_arrive_expect_tx(full_bar + stage, L::kABytes + (load_sfa ? L::kSfaBytes : 0) +
+                                                                (load_sfb ? L::kSfbBytes : 0));
+                    tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128, t.row_start);
+                    if (load_sfa)
+                        tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage, t.sf_row_start,
+                                    sfa_y + kb / a_per);
+                    if (load_sfb)
+                        tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
+                                    t.n_block * BLOCK_N, sfb_y + kb / b_per);
+                    trace_point(p, 1, trace_i++);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 3) {
+        // ---------------------------------------------------------------- loader: B (weight) tile + L2 prefetch
+        if (lane == 0) {
+            TileScheduler<BLOCK_N> sched(p);
+            Tile t;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
 
             // L2 prefetch cursor: walks the same (tile, K block) sequence `prefetch_distance` blocks ahead of the
-            // loads, so that HBM latency is covered by requests in flight to L2 rather than by shared-memory stages
-            // (a stage holds only 8 KB of packed FP4 weights).
+            // loads. A stage holds only 8 or 16 KB of packed FP4 weights and shared memory bounds the number of
+            // stages, so HBM latency is covered by prefetches in flight to L2 instead of by more stages.
             TileScheduler<BLOCK_N> pf_sched(p);
             Tile pt;
             int pf_kb = 0;
@@ -266,15 +308,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             };
             auto pf_advance = [&]() {
                 if (!pf_valid) return;
-                if (p.prefetch_mask & 1)
-                    tma_prefetch_2d(&tm_b, pf_kb * 128, pt.group * p.n + pt.n_block * BLOCK_N);
-                if (p.prefetch_mask & 2) tma_prefetch_2d(&tm_a, pf_kb * 128, pt.row_start);
-                if (p.prefetch_mask & 4) {
-                    if (pf_kb % b_per == 0)
-                        tma_prefetch_2d(&tm_sfb, pt.n_block * BLOCK_N, pt.group * p.sfb_packed_k + pf_kb / b_per);
-                    if (pf_kb % a_per == 0)
-                        tma_prefetch_2d(&tm_sfa, pt.sf_row_start, pt.group * p.sfa_group_rows + pf_kb / a_per);
-                }
+                if (p.prefetch_mask & 1) tma_prefetch_2d(&tm_b, pf_kb * 128, pt.group * p.n + pt.n_block * BLOCK_N);
+                if ((p.prefetch_mask & 4) && pf_kb % b_per == 0)
+                    tma_prefetch_2d(&tm_sfb, pt.n_block * BLOCK_N, pt.group * p.sfb_packed_k + pf_kb / b_per);
                 if (++pf_kb == num_kb) pf_next_tile();
             };
             if (p.prefetch_distance > 0) {
@@ -285,31 +321,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int b_row = t.group * p.n + t.n_block * BLOCK_N;
-                const int sfa_y = t.group * p.sfa_group_rows, sfb_y = t.group * p.sfb_packed_k;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    trace_point(p, 0, trace_i);
-                    const bool skip_sf = DGB_SKIP(p, 4);
-                    const bool load_sfa = kb % a_per == 0 && !skip_sf, load_sfb = kb % b_per == 0 && !skip_sf;
-                    uint32_t bytes = 0;
-                    if (!DGB_SKIP(p, 1)) bytes += L::kABytes;
-                    if (!DGB_SKIP(p, 2)) bytes += p.b_tx_bytes;
-                    if (load_sfa) bytes += L::kSfaBytes;
-                    if (load_sfb) bytes += L::kSfbBytes;
-                    mbar_arrive_expect_tx(full_bar + stage, bytes);
-                    if (!DGB_SKIP(p, 1))
-                        tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128, t.row_start);
-                    if (!DGB_SKIP(p, 2))
-                        tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
-                    if (load_sfa)
-                        tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage, t.sf_row_start,
-                                    sfa_y + kb / a_per);
-                    if (load_sfb)
-                        tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
-                                    t.n_block * BLOCK_N, sfb_y + kb / b_per);
+                    mbar_arrive_expect_tx(full_bar + stage, p.b_tx_bytes);
+                    tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
                     if (p.prefetch_distance > 0) pf_advance();
-                    trace_point(p, 1, trace_i++);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -338,9 +355,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 tcgen05_fence_after();
                 if (lane == 0) {
                     trace_point(p, 4, trace_i);
-                    if (kb % a_per == 0 && !DGB_SKIP(p, 16))
+                    if (kb % a_per == 0)
                         tcgen05_cp_32x128b_warpx4(tmem_base + kSfaCol, make_sf_desc(sfa_smem + stage * L::kSfaBytes));
-                    if (kb % b_per == 0 && !DGB_SKIP(p, 16)) {
+                    if (kb % b_per == 0) {
 #pragma unroll
                         for (int i = 0; i < BLOCK_N / 128; ++i)
                             tcgen05_cp_32x128b_warpx4(tmem_base + kSfbCol + i * 4,
@@ -353,7 +370,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                         const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
-                        if (DGB_SKIP(p, 8)) continue;
                         tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
                                              idesc_with_sf_ids(idesc, sfa_id, sfb_id),
                                              tmem_base + kSfaCol, tmem_base + kSfbCol, (kb | k4) != 0 ? 1u : 0u);
@@ -362,8 +378,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
                     trace_point(p, 5, trace_i);
                 }
-                __syncwarp();
                 ++trace_i;
+                __syncwarp();
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -373,14 +389,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         TileScheduler<BLOCK_N> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
-        int trace_i = 0;
         bool ok = true;
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
-                if (lane == 0) trace_point(p, 2, trace_i);
                 if (kb % a_per == 0) {
                     uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
                     const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
@@ -398,17 +412,21 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(sf_ready_bar + stage);
-                if (lane == 0) trace_point(p, 3, trace_i);
-                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp >= 4) {
-        // ---------------------------------------------------------------- epilogue
+    }
+    } else {
+        setmaxnreg_inc<kRegsEpilogueWarps>();
+        // ---------------------------------------------------------------- epilogue (8 warps)
+        // Warp w may read TMEM lanes [32 (w % 4), +32): two warps share a lane quarter and split the columns.
+        // Each thread first drains its half row of the accumulator into registers and releases the accumulator, so
+        // the MMA issuer can start the next tile while the arithmetic and the stores below run.
+        constexpr int kCols = BLOCK_N / 2;  // accumulator columns per thread
         TileScheduler<BLOCK_N> sched(p);
         Tile t;
         uint32_t iter = 0;
-        const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
+        const uint32_t q = warp & 3, half = (warp - 4) >> 2;
         const int r = static_cast<int>(q * 32 + lane);
         bool ok = true;
         while (ok && sched.next(t)) {
@@ -418,77 +436,74 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             ok = mbar_wait(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
             if (!ok) break;
             tcgen05_fence_after();
+            const bool warp_has_rows = static_cast<int>(q * 32) < t.rows_store;
+            uint32_t acc[kCols];
+            if (warp_has_rows) {
+                const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16) + half * kCols;
+#pragma unroll
+                for (int c = 0; c < kCols / 32; ++c) tmem_ld_32x32b_x32(tmem_row + c * 32, acc + c * 32);
+                tmem_ld_wait();
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar + as);
             if (threadIdx.x == 128) trace_point(p, 6, static_cast<int>(iter) - 1);
-            const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16);
-            const bool store = r < t.rows_store;
+
+            const bool store = r < t.rows_store && !DGB_SKIP(p, 32);
             const long long row = static_cast<long long>(t.row_start) + r;
-            if constexpr (EPI == kEpiBF16 || EPI == kEpiF32 || EPI == kEpiScatter) {
-                __nv_bfloat16* scatter_row = nullptr;
-                if constexpr (EPI == kEpiScatter) {
-                    if (store) {
-                        const int src = __ldg(p.row_src + row);
-                        const int per_rank = p.combine_tokens * p.topk;
-                        const int rank = src / per_rank, entry = src - rank * per_rank;
-                        const int token = entry / p.topk, slot = entry - token * p.topk;
-                        scatter_row = reinterpret_cast<__nv_bfloat16*>(p.combine_base[rank]) +
-                                      (static_cast<long long>(slot) * p.combine_tokens + token) * p.n;
-                    }
-                }
-#pragma unroll 1
-                for (int c = 0; c < BLOCK_N / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(tmem_row + c * 32, v);
-                    tmem_ld_wait();
-                    if (store) {
-                        const long long col = static_cast<long long>(t.n_block) * BLOCK_N + c * 32;
-                        if constexpr (EPI == kEpiBF16 || EPI == kEpiScatter) {
-                            __nv_bfloat16* dst = EPI == kEpiScatter
-                                ? scatter_row + col
-                                : reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col;
+            if (store) {
+                if constexpr (EPI == kEpiBF16 || EPI == kEpiF32 || EPI == kEpiScatter) {
+                    const long long col0 = static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
+                    if constexpr (EPI == kEpiF32) {
+                        float* dst = reinterpret_cast<float*>(p.d) + row * p.d_row_stride + col0;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                st_global_v4(dst + i * 8,
-                                             pack_bf16x2(__uint_as_float(v[i * 8 + 0]), __uint_as_float(v[i * 8 + 1])),
-                                             pack_bf16x2(__uint_as_float(v[i * 8 + 2]), __uint_as_float(v[i * 8 + 3])),
-                                             pack_bf16x2(__uint_as_float(v[i * 8 + 4]), __uint_as_float(v[i * 8 + 5])),
-                                             pack_bf16x2(__uint_as_float(v[i * 8 + 6]), __uint_as_float(v[i * 8 + 7])));
+                        for (int i = 0; i < kCols / 4; ++i)
+                            st_global_v4(dst + i * 4, acc[i * 4 + 0], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]);
+                    } else {
+                        __nv_bfloat16* dst;
+                        if constexpr (EPI == kEpiScatter) {
+                            const int src = __ldg(p.row_src + row);
+                            const int per_rank = p.combine_tokens * p.topk;
+                            const int rank = src / per_rank, entry = src - rank * per_rank;
+                            const int token = entry / p.topk, slot = entry - token * p.topk;
+                            dst = reinterpret_cast<__nv_bfloat16*>(p.combine_base[rank]) +
+                                  (static_cast<long long>(slot) * p.combine_tokens + token) * p.n + col0;
                         } else {
-                            float* dst = reinterpret_cast<float*>(p.d) + row * p.d_row_stride + col;
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                st_global_v4(dst + i * 4, v[i * 4 + 0], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+                            dst = reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col0;
                         }
-                    }
-                }
-            } else {
-                // Columns of this tile: [gate j..j+31 | up j..j+31 | gate j+32..j+63 | up j+32..j+63] (and again
-                // for BLOCK_N == 256), j = n_block * BLOCK_N / 2. One 32-wide output group = one UE8M0 scale.
-                const float w = (store && p.row_weight != nullptr) ? __ldg(p.row_weight + row) : 1.0f;
-#pragma unroll 1
-                for (int c = 0; c < BLOCK_N / 64; ++c) {
-                    uint32_t g[32], u[32];
-                    tmem_ld_32x32b_x32(tmem_row + c * 64, g);
-                    tmem_ld_32x32b_x32(tmem_row + c * 64 + 32, u);
-                    tmem_ld_wait();
-                    float o[32];
-                    float amax = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float gv = bf16_round(__uint_as_float(g[i]));
-                        float uv = bf16_round(__uint_as_float(u[i]));
-                        if (p.clamp > 0.0f) {
-                            gv = fminf(gv, p.clamp);
-                            uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
-                        }
-                        const float silu = gv / (1.0f + __expf(-gv));
-                        o[i] = silu * uv * w;
-                        amax = fmaxf(amax, fabsf(o[i]));
+                        for (int i = 0; i < kCols / 8; ++i)
+                            st_global_v4(dst + i * 8,
+                                         pack_bf16x2(__uint_as_float(acc[i * 8 + 0]), __uint_as_float(acc[i * 8 + 1])),
+                                         pack_bf16x2(__uint_as_float(acc[i * 8 + 2]), __uint_as_float(acc[i * 8 + 3])),
+                                         pack_bf16x2(__uint_as_float(acc[i * 8 + 4]), __uint_as_float(acc[i * 8 + 5])),
+                                         pack_bf16x2(__uint_as_float(acc[i * 8 + 6]), __uint_as_float(acc[i * 8 + 7])));
                     }
-                    float sf_inv;
-                    uint32_t sf_byte;
-                    ue8m0_scale_for_amax(amax, sf_inv, sf_byte);
-                    if (store) {
-                        const int j = t.n_block * (BLOCK_N / 2) + c * 32;  // first output channel of the group
+                } else {
+                    // Columns of a tile: [gate j..j+31 | up j..j+31 | gate j+32.. | up j+32.. | ...]; this thread holds
+                    // kCols / 64 such gate/up pairs. One 32-wide output group = one UE8M0 scale.
+                    const float w = p.row_weight != nullptr ? __ldg(p.row_weight + row) : 1.0f;
+#pragma unroll
+                    for (int c = 0; c < kCols / 64; ++c) {
+                        float o[32];
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float gv = bf16_round(__uint_as_float(acc[c * 64 + i]));
+                            float uv = bf16_round(__uint_as_float(acc[c * 64 + 32 + i]));
+                            if (p.clamp > 0.0f) {
+                                gv = fminf(gv, p.clamp);
+                                uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                            }
+                            const float silu = p.fast_math ? gv * rcp_approx(1.0f + __expf(-gv))
+                                                           : gv / (1.0f + expf(-gv));
+                            o[i] = silu * uv * w;
+                            amax = fmaxf(amax, fabsf(o[i]));
+                        }
+                        float sf_inv;
+                        uint32_t sf_byte;
+                        ue8m0_scale_for_amax(amax, sf_inv, sf_byte);
+                        const int j = t.n_block * (BLOCK_N / 2) + static_cast<int>(half) * (kCols / 2) + c * 32;
                         uint32_t packed[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -504,8 +519,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     }
                 }
             }
-            tcgen05_fence_before();
-            mbar_arrive(tmem_empty_bar + as);
             if (threadIdx.x == 128) trace_point(p, 7, static_cast<int>(iter) - 1);
         }
     }

@@ -284,7 +284,7 @@ __device__ __forceinline__ void tcgen05_mma_mxf4_2x(uint32_t tmem_d, uint64_t ad
 }
 
 // Each lane reads 32 consecutive 32-bit columns of its own TMEM lane (lane quarter = warp index % 4).
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t tmem_addr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t tmem_addr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -321,6 +321,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 __device__ __forceinline__ float bf16_round(float x) {
     return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+// Register re-balancing between warpgroups (all warps of a warpgroup execute the same instruction).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kRegs));
+}
+
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
 }
 
 // Programmatic dependent launch: wait for the preceding kernel's memory to be visible / let the next one start.
