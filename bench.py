@@ -37,7 +37,8 @@ def parse_args():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--tokens', type=int, default=0, help='override tokens per rank (debugging only)')
+    ap.add_argument('--tokens', type=int, default=0, help='override tokens per rank (profiling small cases only)')
+    ap.add_argument('--experts', type=int, default=0, help='override the expert count (profiling small cases only)')
     ap.add_argument('--skip-cpu-baseline', action='store_true')
     return ap.parse_args()
 
@@ -226,7 +227,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     torch.manual_seed(1234 + rank)
     t, h, i, e, k = cfg['tokens'], cfg['hidden'], cfg['inter'], cfg['experts'], cfg['topk']
     cfg['local_experts'] = e // world
-    l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 else 0)
+    l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 and not args.skip_cpu_baseline else 0)
     buf = dg.get_symm_buffer_for_mega_moe(None, e, t, k, h, i)
     x_host = torch.randn(t, h).bfloat16().pin_memory()
     logits_host = torch.randn(t, e).pin_memory()
@@ -358,6 +359,8 @@ def main():
         cfg['tokens'] = 8192
     if args.tokens:
         cfg['tokens'] = args.tokens
+    if args.experts:
+        cfg['experts'] = args.experts
     if args.impl == 'reference':
         run_reference(args, cfg, rank, world)
         return

@@ -202,10 +202,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
     constexpr uint32_t kAccumCols = BLOCK_N;
     constexpr uint32_t kNumAccum = BLOCK_N == 128 ? 2 : 1;
-    constexpr uint32_t kSfaCol = kAccumCols * kNumAccum;
-    constexpr uint32_t kSfbCol = kSfaCol + 4;
+    // Scale factors get their own TMEM columns per pipeline stage: with a single region every tcgen05.cp would have
+    // to wait for the previous K block's MMAs to finish reading it, which serialises copy and MMA.
+    constexpr uint32_t kSfColsPerStage = 4 + BLOCK_N / 32;
+    constexpr uint32_t kSfCol0 = kAccumCols * kNumAccum;
     constexpr uint32_t kTmemCols = 512;
-    static_assert(kSfbCol + BLOCK_N / 32 <= kTmemCols, "TMEM budget");
+    static_assert(kSfCol0 + kStages * kSfColsPerStage <= kTmemCols, "TMEM budget");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -256,7 +258,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // ---------------------------------------------------------------- loader: A tile + both scale-factor rows
         // TMA instructions cost on the order of 100 cycles each in the issuing thread, so the loads of one stage are
         // split over two threads (this one and warp 3); both arrive on the stage's full barrier with their own bytes.
-        if (lane == 0) {
+        // The whole warp walks the schedule with warp-uniform values and one elected lane issues: TMA and tcgen05
+        // instructions take their descriptors from uniform registers, which a single-lane (divergent) loop would
+        // have to refill through slow register-to-uniform moves for every instruction.
+        {
             TileScheduler<BLOCK_N> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0;
@@ -268,33 +273,41 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    trace_point(p, 0, trace_i);
                     const bool load_sfa = kb % a_per == 0, load_sfb = kb % b_per == 0;
-                    mbar_arrive_expect_tx(full_bar + stage, L::kABytes + (load_sfa ? L::kSfaBytes : 0) +
-                                                                (load_sfb ? L::kSfbBytes : 0));
-                    tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128, t.row_start);
-                    if (load_sfa)
-                        tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage, t.sf_row_start,
-                                    sfa_y + kb / a_per);
-                    if (load_sfb)
-                        tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
-                                    t.n_block * BLOCK_N, sfb_y + kb / b_per);
-                    trace_point(p, 1, trace_i++);
+                    if (elect_one()) {
+                        trace_point(p, 0, trace_i);
+                        mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) +
+                                                                    (load_sfa ? L::kSfaBytes : 0) +
+                                                                    (load_sfb ? L::kSfbBytes : 0));
+                        if (!DGB_SKIP(p, 1))
+                            tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128,
+                                        t.row_start);
+                        if (load_sfa)
+                            tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage,
+                                        t.sf_row_start, sfa_y + kb / a_per);
+                        if (load_sfb)
+                            tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
+                                        t.n_block * BLOCK_N, sfb_y + kb / b_per);
+                        trace_point(p, 1, trace_i);
+                    }
+                    __syncwarp();
+                    ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 3) {
         // ---------------------------------------------------------------- loader: B (weight) tile + L2 prefetch
-        if (lane == 0) {
+        {
             TileScheduler<BLOCK_N> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            int trace_i = 0;
 
             // L2 prefetch cursor: walks the same (tile, K block) sequence `prefetch_distance` blocks ahead of the
             // loads. A stage holds only 8 or 16 KB of packed FP4 weights and shared memory bounds the number of
-            // stages, so HBM latency is covered by prefetches in flight to L2 instead of by more stages.
+            // stages, so HBM latency can be covered by prefetches in flight to L2 instead of by more stages.
             TileScheduler<BLOCK_N> pf_sched(p);
             Tile pt;
             int pf_kb = 0;
@@ -308,9 +321,13 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             };
             auto pf_advance = [&]() {
                 if (!pf_valid) return;
-                if (p.prefetch_mask & 1) tma_prefetch_2d(&tm_b, pf_kb * 128, pt.group * p.n + pt.n_block * BLOCK_N);
-                if ((p.prefetch_mask & 4) && pf_kb % b_per == 0)
-                    tma_prefetch_2d(&tm_sfb, pt.n_block * BLOCK_N, pt.group * p.sfb_packed_k + pf_kb / b_per);
+                if (elect_one()) {
+                    if (p.prefetch_mask & 1)
+                        tma_prefetch_2d(&tm_b, pf_kb * 128, pt.group * p.n + pt.n_block * BLOCK_N);
+                    if ((p.prefetch_mask & 4) && pf_kb % b_per == 0)
+                        tma_prefetch_2d(&tm_sfb, pt.n_block * BLOCK_N, pt.group * p.sfb_packed_k + pf_kb / b_per);
+                }
+                __syncwarp();
                 if (++pf_kb == num_kb) pf_next_tile();
             };
             if (p.prefetch_distance > 0) {
@@ -324,15 +341,24 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(full_bar + stage, p.b_tx_bytes);
-                    tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
+                    if (elect_one()) {
+                        trace_point(p, 9, trace_i);
+                        mbar_arrive_expect_tx(full_bar + stage, DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes);
+                        if (!DGB_SKIP(p, 2))
+                            tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
+                        trace_point(p, 10, trace_i);
+                    }
+                    __syncwarp();
                     if (p.prefetch_distance > 0) pf_advance();
+                    ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
+        // Warp-uniform loop, one elected lane issues (see the loader above).
+        {
         TileScheduler<BLOCK_N> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
@@ -340,6 +366,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         const uint32_t idesc = make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
+        uint32_t tmem_sfa = 0, tmem_sfb = 0;  // TMEM columns holding the scale factors of the current K block
         bool ok = true;
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
@@ -353,14 +380,18 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 ok = mbar_wait(sf_ready_bar + stage, phase, abort_flag, kTimeoutSfReady, kb);
                 if (!ok) break;
                 tcgen05_fence_after();
-                if (lane == 0) {
+                if (elect_one()) {
                     trace_point(p, 4, trace_i);
-                    if (kb % a_per == 0)
-                        tcgen05_cp_32x128b_warpx4(tmem_base + kSfaCol, make_sf_desc(sfa_smem + stage * L::kSfaBytes));
+                    const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
+                    if (kb % a_per == 0) {
+                        tmem_sfa = sf_cols;
+                        tcgen05_cp_32x128b_warpx4(tmem_sfa, make_sf_desc(sfa_smem + stage * L::kSfaBytes));
+                    }
                     if (kb % b_per == 0) {
+                        tmem_sfb = sf_cols + 4;
 #pragma unroll
                         for (int i = 0; i < BLOCK_N / 128; ++i)
-                            tcgen05_cp_32x128b_warpx4(tmem_base + kSfbCol + i * 4,
+                            tcgen05_cp_32x128b_warpx4(tmem_sfb + i * 4,
                                                       make_sf_desc(sfb_smem + stage * L::kSfbBytes + i * 512));
                     }
                     const uint64_t adesc = make_kmajor_sw128_desc(a_base + stage * L::kABytes);
@@ -370,18 +401,20 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                         const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
+                        if (DGB_SKIP(p, 8)) continue;
                         tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
-                                             idesc_with_sf_ids(idesc, sfa_id, sfb_id),
-                                             tmem_base + kSfaCol, tmem_base + kSfbCol, (kb | k4) != 0 ? 1u : 0u);
+                                             idesc_with_sf_ids(idesc, sfa_id, sfb_id), tmem_sfa, tmem_sfb,
+                                             (kb | k4) != 0 ? 1u : 0u);
                     }
                     tcgen05_commit(empty_bar + stage);
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
                     trace_point(p, 5, trace_i);
                 }
-                ++trace_i;
                 __syncwarp();
+                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
+        }
         }
     } else if (warp == 2) {
         // ---------------------------------------------------------------- scale-factor transposer
@@ -389,12 +422,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         TileScheduler<BLOCK_N> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
+        int trace_i = 0;
         bool ok = true;
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
+                ok = mbar_wait_warp(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
+                if (lane == 0) trace_point(p, 2, trace_i);
                 if (kb % a_per == 0) {
                     uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
                     const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
@@ -412,6 +447,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(sf_ready_bar + stage);
+                if (lane == 0) trace_point(p, 3, trace_i);
+                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -433,7 +470,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             if (t.group < 0) continue;
             const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
             ++iter;
-            ok = mbar_wait(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
+            ok = mbar_wait_warp<32>(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
             if (!ok) break;
             tcgen05_fence_after();
             const bool warp_has_rows = static_cast<int>(q * 32) < t.rows_store;

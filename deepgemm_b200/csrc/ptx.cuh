@@ -113,12 +113,16 @@ constexpr long long kWaitBudgetCycles = 4000000000ll;
 
 // Bounded wait. `abort_flag` is a CTA-shared word: once any role of the CTA gives up, the others
 // stop at their next poll instead of each burning their own budget.
+// kBackoffNs > 0 makes the caller sleep between polls: for waits that last a whole tile, so that the polling does
+// not compete with the issue threads for the shared-memory pipeline.
+template <int kBackoffNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           int code, int detail) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
+        if (kBackoffNs > 0) __nanosleep(kBackoffNs);
         if (mbar_try_wait(bar, parity)) return true;
         if (((++spins) & 0x3ffu) == 0) {
             if (*abort_flag != 0) return false;
@@ -132,6 +136,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             }
         }
     }
+}
+
+// One lane polls for the whole warp; every lane gets the outcome.
+template <int kBackoffNs = 0>
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               int code, int detail) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait<kBackoffNs>(bar, parity, abort_flag, code, detail) ? 1u : 0u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ----------------------------------------------------------------------------------------------
