@@ -127,6 +127,16 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     }
     if (rc) return rc;
 
+    p.a_ptr = static_cast<const unsigned char*>(c.a);
+    p.b_ptr = static_cast<const unsigned char*>(c.b);
+    p.sfa_ptr = static_cast<const unsigned char*>(c.sfa);
+    p.sfb_ptr = static_cast<const unsigned char*>(c.sfb);
+    p.a_rows = c.a_rows_total;
+    p.a_row_bytes = p.k;
+    p.b_row_bytes = c.b_is_fp4 ? p.k / 2 : p.k;
+    p.b_kb_bytes = c.b_is_fp4 ? 64 : 128;
+    p.sfa_kp_bytes = c.sfa_k_stride * 4;
+    p.sfb_kp_bytes = c.sfb_k_stride * 4;
     p.prefetch_distance = tuning().prefetch_distance;
     p.prefetch_mask = tuning().prefetch_mask;
     p.debug_skip = tuning().debug_skip;

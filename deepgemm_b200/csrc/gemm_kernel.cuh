@@ -56,8 +56,17 @@ struct GemmParams {
     unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
     unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
     int store_padding;       // psum only: also write the rows between a group's end and its aligned end
-    int prefetch_distance;   // K blocks the producer's L2 prefetch cursor runs ahead of its loads (0 = off)
+    int prefetch_distance;   // K blocks the loaders' L2 prefetch cursors run ahead of their loads (0 = off)
     int prefetch_mask;       // bit 0: B tiles, bit 1: A tiles, bit 2: scale factors
+    // raw views of the operands for the prefetch cursors (the loads themselves go through the tensor maps)
+    const unsigned char* a_ptr;
+    const unsigned char* b_ptr;
+    const unsigned char* sfa_ptr;
+    const unsigned char* sfb_ptr;
+    long long a_rows;                      // rows of the flattened A (prefetches stay inside the tensor)
+    long long a_row_bytes, b_row_bytes;    // row pitch of A and B in bytes
+    long long sfa_kp_bytes, sfb_kp_bytes;  // pitch between packed K groups of the scale factors in bytes
+    int b_kb_bytes;                        // bytes of one B row inside one K block: 64 (packed FP4) or 128 (FP8)
     int debug_skip;          // timing experiments only (results become garbage): bit 0 no A loads, 1 no B loads,
                              // 2 no scale-factor loads, 3 no MMA instructions, 4 no scale-factor TMEM copies
     long long* trace;        // optional: CTA 0 records clock64() per role and K block at trace[role * trace_cap + i]
@@ -228,7 +237,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         for (int i = 0; i < kStages; ++i) {
             mbar_init(full_bar + i, 2);       // the A-side loader and the B-side loader
             mbar_init(empty_bar + i, 1);      // tcgen05.commit of the MMA issuer
-            mbar_init(sf_ready_bar + i, 32);  // every lane of the transposer warp
+            mbar_init(sf_ready_bar + i, 1);   // one lane of the transposer warp, after a warp barrier
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(tmem_full_bar + i, 1);
@@ -267,13 +276,45 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int trace_i = 0;
+            // L2 prefetch cursor for the A rows and their scale factors (see the weight loader below)
+            TileScheduler<BLOCK_N> pf_sched(p);
+            Tile pt;
+            int pf_kb = 0;
+            bool pf_valid = false;
+            auto pf_next_tile = [&]() {
+                pf_valid = false;
+                while (pf_sched.next(pt)) {
+                    if (pt.group >= 0) { pf_valid = true; break; }
+                }
+                pf_kb = 0;
+            };
+            auto pf_advance = [&]() {
+                if (!pf_valid) return;
+                if (p.prefetch_mask & 2) {
+                    const unsigned char* base = p.a_ptr + (static_cast<long long>(pt.row_start) + lane) * p.a_row_bytes +
+                                                static_cast<long long>(pf_kb) * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (pt.row_start + static_cast<int>(lane) + j * 32 < p.a_rows) prefetch_l2(base + j * 32 * p.a_row_bytes);
+                }
+                if ((p.prefetch_mask & 4) && pf_kb % a_per == 0 && lane < 4 &&
+                    (pt.sf_row_start + static_cast<int>(lane) * 32) * 4ll < p.sfa_kp_bytes)
+                    prefetch_l2(p.sfa_ptr + (static_cast<long long>(pt.group) * p.sfa_group_rows + pf_kb / a_per) * p.sfa_kp_bytes +
+                                static_cast<long long>(pt.sf_row_start) * 4 + lane * 128);
+                if (++pf_kb == num_kb) pf_next_tile();
+            };
+            if (p.prefetch_distance > 0 && (p.prefetch_mask & 6)) {
+                pf_next_tile();
+                for (int i = 0; i < p.prefetch_distance; ++i) pf_advance();
+            }
+
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int sfa_y = t.group * p.sfa_group_rows, sfb_y = t.group * p.sfb_packed_k;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfa = kb % a_per == 0, load_sfb = kb % b_per == 0;
+                    const bool load_sfa = kb % a_per == 0 && !DGB_SKIP(p, 4), load_sfb = kb % b_per == 0 && !DGB_SKIP(p, 4);
                     if (elect_one()) {
                         trace_point(p, 0, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) +
@@ -291,6 +332,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         trace_point(p, 1, trace_i);
                     }
                     __syncwarp();
+                    if (p.prefetch_distance > 0 && (p.prefetch_mask & 6)) pf_advance();
                     ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -321,13 +363,17 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             };
             auto pf_advance = [&]() {
                 if (!pf_valid) return;
-                if (elect_one()) {
-                    if (p.prefetch_mask & 1)
-                        tma_prefetch_2d(&tm_b, pf_kb * 128, pt.group * p.n + pt.n_block * BLOCK_N);
-                    if ((p.prefetch_mask & 4) && pf_kb % b_per == 0)
-                        tma_prefetch_2d(&tm_sfb, pt.n_block * BLOCK_N, pt.group * p.sfb_packed_k + pf_kb / b_per);
+                // every lane prefetches the 128-byte lines of its rows (plain prefetches: the TMA unit stays free)
+                const long long col = static_cast<long long>(pf_kb) * p.b_kb_bytes;
+                if ((p.prefetch_mask & 1) && (col & 127) == 0) {
+                    const unsigned char* base =
+                        p.b_ptr + (static_cast<long long>(pt.group) * p.n + pt.n_block * BLOCK_N + lane) * p.b_row_bytes + col;
+#pragma unroll
+                    for (int j = 0; j < BLOCK_N / 32; ++j) prefetch_l2(base + j * 32 * p.b_row_bytes);
                 }
-                __syncwarp();
+                if ((p.prefetch_mask & 4) && pf_kb % b_per == 0 && lane < BLOCK_N / 32)
+                    prefetch_l2(p.sfb_ptr + (static_cast<long long>(pt.group) * p.sfb_packed_k + pf_kb / b_per) * p.sfb_kp_bytes +
+                                static_cast<long long>(pt.n_block) * BLOCK_N * 4 + lane * 128);
                 if (++pf_kb == num_kb) pf_next_tile();
             };
             if (p.prefetch_distance > 0) {
@@ -427,26 +473,35 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = mbar_wait_warp(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
+                ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
                 if (lane == 0) trace_point(p, 2, trace_i);
-                if (kb % a_per == 0) {
-                    uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
-                    const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
-                    __syncwarp();
-                    *reinterpret_cast<uint4*>(s + lane * 4) = make_uint4(v0, v1, v2, v3);
-                }
-                if (kb % b_per == 0) {
+                // All reads first, one warp barrier, then all writes: this warp serves every K block in turn, so its
+                // service time bounds the whole pipeline.
+                const bool do_a = kb % a_per == 0, do_b = kb % b_per == 0;
+                uint32_t* sa = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
+                uint32_t* sb = reinterpret_cast<uint32_t*>(smem + L::kOffSfb + stage * L::kSfbBytes);
+                uint32_t va[4], vb[BLOCK_N / 128][4];
+                if (do_a) {
 #pragma unroll
-                    for (int i = 0; i < BLOCK_N / 128; ++i) {
-                        uint32_t* s = reinterpret_cast<uint32_t*>(smem + L::kOffSfb + stage * L::kSfbBytes) + i * 128;
-                        const uint32_t v0 = s[lane], v1 = s[32 + lane], v2 = s[64 + lane], v3 = s[96 + lane];
-                        __syncwarp();
-                        *reinterpret_cast<uint4*>(s + lane * 4) = make_uint4(v0, v1, v2, v3);
-                    }
+                    for (int j = 0; j < 4; ++j) va[j] = sa[j * 32 + lane];
+                }
+                if (do_b) {
+#pragma unroll
+                    for (int i = 0; i < BLOCK_N / 128; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) vb[i][j] = sb[i * 128 + j * 32 + lane];
+                }
+                __syncwarp();
+                if (do_a) *reinterpret_cast<uint4*>(sa + lane * 4) = make_uint4(va[0], va[1], va[2], va[3]);
+                if (do_b) {
+#pragma unroll
+                    for (int i = 0; i < BLOCK_N / 128; ++i)
+                        *reinterpret_cast<uint4*>(sb + i * 128 + lane * 4) = make_uint4(vb[i][0], vb[i][1], vb[i][2], vb[i][3]);
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(sf_ready_bar + stage);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sf_ready_bar + stage);
                 if (lane == 0) trace_point(p, 3, trace_i);
                 ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -470,7 +525,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             if (t.group < 0) continue;
             const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
             ++iter;
-            ok = mbar_wait_warp<32>(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
+            ok = mbar_wait<32>(tmem_full_bar + as, aphase, abort_flag, kTimeoutTmemFull, static_cast<int>(iter));
             if (!ok) break;
             tcgen05_fence_after();
             const bool warp_has_rows = static_cast<int>(q * 32) < t.rows_store;

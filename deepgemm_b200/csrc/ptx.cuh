@@ -101,7 +101,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
+#ifdef DGB200_TEST_WAIT
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
@@ -169,6 +173,11 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t 
 
 __device__ __forceinline__ void bulk_prefetch_1d(const void* gmem_src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+// Plain L2 prefetch of the cache line holding `p` (issued from ordinary lanes, so it does not occupy the TMA unit).
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" :: "l"(p));
 }
 
 // `bytes` must be a multiple of 16; both addresses 16-byte aligned.
