@@ -66,7 +66,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
-                                          '-lms', '100', '-i', str(self.gpu_index)], stdout=self.file,
+                                          '-lms', '20', '-i', str(self.gpu_index)], stdout=self.file,
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -221,16 +221,21 @@ def run_ours(args, cfg, rank, world, local_rank):
     import deepgemm_b200 as dg
     from deepgemm_b200 import _lib
 
-    if world > 1:
-        raise SystemExit('the expert-parallel (multi-GPU) layer is not built yet')
     torch.cuda.set_device(local_rank)
     torch.manual_seed(1234 + rank)
     t, h, i, e, k = cfg['tokens'], cfg['hidden'], cfg['inter'], cfg['experts'], cfg['topk']
     cfg['local_experts'] = e // world
     l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 and not args.skip_cpu_baseline else 0)
-    buf = dg.get_symm_buffer_for_mega_moe(None, e, t, k, h, i)
+    buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD if world > 1 else None, e, t, k, h, i)
     x_host = torch.randn(t, h).bfloat16().pin_memory()
-    logits_host = torch.randn(t, e).pin_memory()
+    logits = torch.randn(t, e)
+    if world > 1:
+        # expert popularity ~ Zipf(s = 1): rank r of a seeded random permutation of the experts has weight 1 / (r + 1)
+        g = torch.Generator().manual_seed(2024)
+        popularity = torch.empty(e)
+        popularity[torch.randperm(e, generator=g)] = 1.0 / torch.arange(1, e + 1, dtype=torch.float32)
+        logits = logits + torch.log(popularity / popularity.sum())
+    logits_host = logits.pin_memory()
     y_host = torch.empty((t, h), dtype=torch.bfloat16).pin_memory()
     x = x_host.cuda()
     logits = logits_host.cuda()
@@ -252,6 +257,7 @@ def run_ours(args, cfg, rank, world, local_rank):
         torch.cuda.synchronize()
 
     # ---- device-resident timing
+    barrier()
     for _ in range(args.warmup):
         step()
     barrier()
@@ -298,8 +304,13 @@ def run_ours(args, cfg, rank, world, local_rank):
     ends = buf.buffer[lay['expert_end']:lay['expert_end'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
     starts = buf.buffer[lay['expert_start']:lay['expert_start'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
     rows = int((ends - starts).sum())
+    rows_all = torch.tensor([float(rows)], device='cuda')
+    rows_max = rows_all.clone()
+    if world > 1:
+        dist.all_reduce(rows_all)
+        dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
     touched = int(((ends - starts) > 0).sum())
-    flops = 2.0 * rows * h * i * 3
+    flops = 2.0 * float(rows_all) * h * i * 3
     l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 32) + rows * (h + h // 32) + rows * (i + i // 32)
     l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
     times = torch.tensor([ms_per_step, e2e_ms] + stage_ms, dtype=torch.float64, device='cuda')
@@ -328,9 +339,10 @@ def run_ours(args, cfg, rank, world, local_rank):
                       'l2_gemm_scatter': stage_ms[3], 'combine': stage_ms[4]},
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9,
         'tflops': tflops,
-        'frac_fp4_dense_peak_nominal': tflops / FP4_DENSE_PEAK_TFLOPS_NOMINAL,
-        'frac_fp8_rate_peak_nominal': tflops / FP8_DENSE_PEAK_TFLOPS_NOMINAL,
+        'frac_fp4_dense_peak_nominal': tflops / (FP4_DENSE_PEAK_TFLOPS_NOMINAL * world),
+        'frac_fp8_rate_peak_nominal': tflops / (FP8_DENSE_PEAK_TFLOPS_NOMINAL * world),
         'routed_rows': rows,
+        'load_imbalance_max_over_mean': float(rows_max) / (float(rows_all) / world) if float(rows_all) > 0 else None,
     }
     if world == 1 and not args.skip_cpu_baseline:
         idx, w = buf.topk_idx[:t].cpu(), buf.topk_weights[:t].cpu()
@@ -367,10 +379,16 @@ def main():
     if world != args.gpus:
         raise SystemExit(f'--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)')
     if world > 1:
+        import torch
         import torch.distributed as dist
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-        dist.init_process_group('nccl')
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
     run_ours(args, cfg, rank, world, local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == '__main__':

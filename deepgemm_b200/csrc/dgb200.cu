@@ -5,6 +5,8 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 #include "host_common.cuh"
 #include "gemm_kernel.cuh"
@@ -185,6 +187,7 @@ struct MegaLayout {
     long long x, x_sf, topk_idx, topk_weights;                            // inputs, written by the caller
     long long chunk_hist, expert_start, expert_end, total_rows, dest_row;  // dispatch plan
     long long src_of_row, row_weight;
+    long long all_counts, my_base, flags;  // expert-parallel exchange: counts of every rank, this rank's bases, barrier flags
     long long l1_acts, l1_sf, l2_acts, l2_sf, combine;
     long long total;
     long long max_rows;  // capacity of the expert-sorted buffers (rows), a multiple of 128
@@ -213,7 +216,10 @@ int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, i
     l.x_sf = take(static_cast<long long>(max_tokens) * (hidden / 128) * 4);
     l.topk_idx = take(static_cast<long long>(max_tokens) * topk * 8);
     l.topk_weights = take(static_cast<long long>(max_tokens) * topk * 4);
-    l.chunk_hist = take(static_cast<long long>(l.num_chunks) * l.num_local_experts * 4);
+    l.chunk_hist = take(static_cast<long long>(l.num_chunks) * num_experts * 4);
+    l.all_counts = take(static_cast<long long>(num_ranks) * num_experts * 4);
+    l.my_base = take(num_experts * 4ll);
+    l.flags = take(4 * kMaxEpRanks * 4);
     l.expert_start = take(l.num_local_experts * 4ll);
     l.expert_end = take(l.num_local_experts * 4ll);
     l.total_rows = take(16);
@@ -261,6 +267,153 @@ int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, i
         dgb200_cast_rows_kernel<false><<<grid, 256, 0, stream>>>(p);
     DGB_CUDA(cudaGetLastError());
     return 0;
+}
+
+
+// The two grouped GEMMs of the layer over this rank's expert-sorted rows (shared by the single-rank and the
+// expert-parallel paths). `combine_bases[r]` = rank r's combine buffer as mapped here.
+int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
+                    const void* l2_w_sf, void* const* combine_bases, int num_ranks, int num_max_tokens_per_rank,
+                    int num_topk, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
+                    cudaStream_t stream, int stage_event_base) {
+    const int E = l.num_local_experts;
+    const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
+    int rc = 0;
+    {
+        GemmCall c{};
+        c.a = base + l.l1_acts;
+        c.b = l1_w;
+        c.a_rows_total = l.max_rows;
+        c.b_is_fp4 = 1;
+        c.epilogue = kEpiSwiGLU;
+        c.max_tiles = 0;
+        c.sfa = base + l.l1_sf;
+        c.sfb = l1_w_sf;
+        c.sfa_k_stride = l.max_rows;
+        c.sfa_group_stride = 0;
+        c.num_groups_a = 1;
+        c.sfb_k_stride = 2 * intermediate_hidden;
+        c.sfb_group_stride = static_cast<long long>(hidden / 128) * 2 * intermediate_hidden;
+        GemmParams& p = c.p;
+        p.layout = expert_end;
+        p.mode = kModePsum;
+        p.m = static_cast<int>(l.max_rows);
+        p.n = 2 * intermediate_hidden;
+        p.k = hidden;
+        p.num_groups = E;
+        p.alignment = kSegmentAlignment;
+        p.gran_a = 32;
+        p.gran_b = 32;
+        p.act_q = base + l.l2_acts;
+        p.act_sf = base + l.l2_sf;
+        p.act_q_row_stride = intermediate_hidden;
+        p.act_sf_k_stride = l.max_rows;
+        p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
+        p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
+        p.fast_math = fast_math;
+        if ((rc = run_gemm(c, stream))) return rc;
+    }
+    if ((rc = record_stage(stage_event_base, stream))) return rc;
+    {
+        GemmCall c{};
+        c.a = base + l.l2_acts;
+        c.b = l2_w;
+        c.a_rows_total = l.max_rows;
+        c.b_is_fp4 = 1;
+        c.epilogue = kEpiScatter;
+        c.max_tiles = 0;
+        c.sfa = base + l.l2_sf;
+        c.sfb = l2_w_sf;
+        c.sfa_k_stride = l.max_rows;
+        c.sfa_group_stride = 0;
+        c.num_groups_a = 1;
+        c.sfb_k_stride = hidden;
+        c.sfb_group_stride = static_cast<long long>(intermediate_hidden / 128) * hidden;
+        GemmParams& p = c.p;
+        p.layout = expert_end;
+        p.mode = kModePsum;
+        p.m = static_cast<int>(l.max_rows);
+        p.n = hidden;
+        p.k = intermediate_hidden;
+        p.num_groups = E;
+        p.alignment = kSegmentAlignment;
+        p.gran_a = 32;
+        p.gran_b = 32;
+        p.row_src = reinterpret_cast<const int*>(base + l.src_of_row);
+        for (int r = 0; r < num_ranks; ++r) p.combine_base[r] = combine_bases[r];
+        p.combine_tokens = num_max_tokens_per_rank;
+        p.topk = num_topk;
+        if ((rc = run_gemm(c, stream))) return rc;
+    }
+    return record_stage(stage_event_base + 1, stream);
+}
+
+// Epoch counter of the cross-rank barriers, one per buffer (all ranks call in lockstep, so the counters agree).
+uint32_t next_barrier_epoch(const void* buffer) {
+    static std::mutex mu;
+    static std::unordered_map<const void*, uint32_t> epochs;
+    std::lock_guard<std::mutex> lock(mu);
+    return ++epochs[buffer];
+}
+
+constexpr long long kPeerWaitBudgetCycles = 20000000000ll;  // about 10 s: ranks may reach their first call seconds apart
+
+int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+                    int32_t* stats, uint8_t* base, const uint64_t* peer_buffer_ptrs, int rank, int num_ranks, int num_tokens,
+                    int num_max_tokens_per_rank, int num_experts, int num_topk, int hidden, int intermediate_hidden,
+                    float activation_clamp, int fast_math, cudaStream_t stream) {
+    PeerTable peers{};
+    void* combine_bases[kMaxRanks];
+    for (int r = 0; r < num_ranks; ++r) {
+        DGB_REQUIRE(peer_buffer_ptrs[r] != 0, "peer buffer %d is not mapped", r);
+        peers.p[r] = peer_buffer_ptrs[r];
+        combine_bases[r] = reinterpret_cast<void*>(peer_buffer_ptrs[r] + l.combine);
+    }
+    const int entries = num_tokens * num_topk;
+    const int chunks = std::max(1, (entries + kPlanChunk - 1) / kPlanChunk);
+    const int entries_per_rank = num_max_tokens_per_rank * num_topk;
+    int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
+    int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
+    const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
+    const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
+    const uint32_t epoch0 = next_barrier_epoch(base) * 4;
+    int rc = 0;
+    if ((rc = record_stage(0, stream))) return rc;
+
+    // count this rank's entries per (global) expert and publish the totals to every rank
+    dgb200_moe_count_kernel<<<chunks, kPlanChunk, num_experts * sizeof(int), stream>>>(topk_idx, entries, 0, num_experts, chunk_hist);
+    dgb200_ep_share_counts_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, num_experts, rank, num_ranks, peers, l.all_counts);
+    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 0, rank, num_ranks, static_cast<int>(epoch0 + 1), kPeerWaitBudgetCycles);
+    // the same global plan on every rank, then push rows to their owners
+    dgb200_ep_plan_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
+                                                   kSegmentAlignment, reinterpret_cast<int*>(base + l.my_base),
+                                                   reinterpret_cast<int*>(base + l.expert_start),
+                                                   reinterpret_cast<int*>(base + l.expert_end),
+                                                   reinterpret_cast<int*>(base + l.total_rows), stats);
+    if (entries > 0) {
+        dgb200_ep_assign_kernel<<<chunks, kPlanChunk, 32 * num_experts, stream>>>(topk_idx, entries, num_experts, chunk_hist,
+                                                                              reinterpret_cast<const int*>(base + l.my_base), dest_row);
+        if ((rc = record_stage(1, stream))) return rc;
+        dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
+            base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
+            hidden, l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row);
+    } else if ((rc = record_stage(1, stream))) {
+        return rc;
+    }
+    DGB_CUDA(cudaGetLastError());
+    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
+    if ((rc = record_stage(2, stream))) return rc;
+
+    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, combine_bases, num_ranks, num_max_tokens_per_rank, num_topk, hidden,
+                         intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    if (rc) return rc;
+    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, static_cast<int>(epoch0 + 3), kPeerWaitBudgetCycles);
+    if (num_tokens > 0)
+        dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(int), stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(base + l.combine), dest_row, num_topk, num_max_tokens_per_rank, hidden,
+            static_cast<__nv_bfloat16*>(y));
+    DGB_CUDA(cudaGetLastError());
+    return record_stage(5, stream);
 }
 
 }  // namespace
@@ -512,8 +665,8 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
     MegaLayout l;
     int rc = make_mega_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
     if (rc) return rc;
-    DGB_REQUIRE(num_ranks == 1, "this entry point runs the single-rank layer; use dgb200_fp8_fp4_mega_moe_ep for %d ranks", num_ranks);
-    DGB_REQUIRE(rank == 0 && peer_buffer_ptrs != nullptr && peer_buffer_ptrs[0] == reinterpret_cast<uint64_t>(buffer),
+    DGB_REQUIRE(rank >= 0 && rank < num_ranks && peer_buffer_ptrs != nullptr &&
+                    peer_buffer_ptrs[rank] == reinterpret_cast<uint64_t>(buffer),
                 "rank / peer pointer table do not describe this buffer");
     DGB_REQUIRE(num_tokens >= 0 && num_tokens <= num_max_tokens_per_rank, "num_tokens (%d) exceeds the buffer capacity (%d)",
                 num_tokens, num_max_tokens_per_rank);
@@ -521,7 +674,7 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                 "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 256 == 0, "buffer must be 256-byte aligned");
     DGB_REQUIRE((2 * intermediate_hidden) % 128 == 0 && intermediate_hidden % 64 == 0, "intermediate_hidden must be a multiple of 64");
-    if (num_tokens == 0) return 0;
+    if (num_tokens == 0 && num_ranks == 1) return 0;
 
     uint8_t* base = static_cast<uint8_t*>(buffer);
     const int E = l.num_local_experts;
@@ -539,6 +692,11 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
 
     struct ClearEvents { ~ClearEvents() { g_num_stage_events = 0; } } clear_events_on_exit;
     if ((rc = record_stage(0, stream))) return rc;
+    if (num_ranks > 1)
+        return run_mega_moe_ep(l, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, base, peer_buffer_ptrs, rank,
+                               num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden,
+                               intermediate_hidden, activation_clamp, fast_math, stream);
+
     // 1. dispatch plan: stable counting sort of the (token, k) entries by expert
     DGB_CUDA(cudaMemsetAsync(src_of_row, 0xff, l.max_rows * 4, stream));
     dgb200_moe_count_kernel<<<chunks, kPlanChunk, E * sizeof(int), stream>>>(topk_idx, entries, 0, E, chunk_hist);
@@ -558,77 +716,11 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
     DGB_CUDA(cudaGetLastError());
 
     if ((rc = record_stage(2, stream))) return rc;
-    // 3. L1: gate/up GEMM with the fused SwiGLU + FP8 requant epilogue
-    {
-        GemmCall c{};
-        c.a = base + l.l1_acts;
-        c.b = l1_w;
-        c.a_rows_total = l.max_rows;
-        c.b_is_fp4 = 1;
-        c.epilogue = kEpiSwiGLU;
-        c.max_tiles = 0;
-        GemmParams& p = c.p;
-        c.sfa = base + l.l1_sf;
-        c.sfb = l1_w_sf;
-        c.sfa_k_stride = l.max_rows;
-        c.sfa_group_stride = 0;
-        c.num_groups_a = 1;
-        c.sfb_k_stride = 2 * intermediate_hidden;
-        c.sfb_group_stride = static_cast<long long>(hidden / 128) * 2 * intermediate_hidden;
-        p.layout = expert_end;
-        p.mode = kModePsum;
-        p.m = static_cast<int>(l.max_rows);
-        p.n = 2 * intermediate_hidden;
-        p.k = hidden;
-        p.num_groups = E;
-        p.alignment = kSegmentAlignment;
-        p.gran_a = 32;
-        p.gran_b = 32;
-        p.act_q = base + l.l2_acts;
-        p.act_sf = base + l.l2_sf;
-        p.act_q_row_stride = intermediate_hidden;
-        p.act_sf_k_stride = l.max_rows;
-        p.row_weight = row_weight;
-        p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
-        p.fast_math = fast_math;
-        rc = run_gemm(c, stream);
-        if (rc) return rc;
-    }
-    if ((rc = record_stage(3, stream))) return rc;
-    // 4. L2: down GEMM, rows scattered to the combine slot of their (token, top-k slot)
-    {
-        GemmCall c{};
-        c.a = base + l.l2_acts;
-        c.b = l2_w;
-        c.a_rows_total = l.max_rows;
-        c.b_is_fp4 = 1;
-        c.epilogue = kEpiScatter;
-        c.max_tiles = 0;
-        GemmParams& p = c.p;
-        c.sfa = base + l.l2_sf;
-        c.sfb = l2_w_sf;
-        c.sfa_k_stride = l.max_rows;
-        c.sfa_group_stride = 0;
-        c.num_groups_a = 1;
-        c.sfb_k_stride = hidden;
-        c.sfb_group_stride = static_cast<long long>(intermediate_hidden / 128) * hidden;
-        p.layout = expert_end;
-        p.mode = kModePsum;
-        p.m = static_cast<int>(l.max_rows);
-        p.n = hidden;
-        p.k = intermediate_hidden;
-        p.num_groups = E;
-        p.alignment = kSegmentAlignment;
-        p.gran_a = 32;
-        p.gran_b = 32;
-        p.row_src = src_of_row;
-        p.combine_base[0] = base + l.combine;
-        p.combine_tokens = num_max_tokens_per_rank;
-        p.topk = num_topk;
-        rc = run_gemm(c, stream);
-        if (rc) return rc;
-    }
-    if ((rc = record_stage(4, stream))) return rc;
+    // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
+    void* combine_bases[1] = {base + l.combine};
+    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, combine_bases, 1, num_max_tokens_per_rank, num_topk, hidden,
+                         intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    if (rc) return rc;
     // 5. combine: y[t] = sum over the top-k slots
     dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(int), stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(base + l.combine), dest_row, num_topk, num_max_tokens_per_rank, hidden,

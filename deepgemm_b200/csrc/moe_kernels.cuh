@@ -231,4 +231,187 @@ dgb200_moe_combine_kernel(const __nv_bfloat16* __restrict__ combine, const int* 
     }
 }
 
+constexpr int kMaxEpRanks = 8;
+struct PeerTable {
+    unsigned long long p[kMaxEpRanks];  // address of every rank's buffer as mapped into this process
+};
+
+// ==================================================================================================================
+// Expert-parallel dispatch: ranks own contiguous blocks of experts (expert e lives on rank e / experts_per_rank, as
+// in the reference: deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:372,389). Every rank holds one
+// buffer with the same layout; `peers[r]` is the address of rank r's buffer as mapped into this process.
+// Protocol of one layer call (all ranks in lockstep, each phase a kernel on the caller's stream):
+//   count  -> per-chunk histogram of this rank's entries over ALL experts
+//   share  -> per expert: this rank's entry count, written into every rank's all_counts[this rank][expert]
+//   barrier
+//   plan   -> every rank derives the same global layout from all_counts: rows of expert e on its owner are ordered
+//             by (source rank, entry), segments padded to `alignment`
+//   push   -> each entry's FP8 row, packed scales, routing weight and source id are stored straight into the owner's
+//             expert-sorted buffers (P2P stores; the reference pulls instead, :461-599)
+//   barrier -> L1 GEMM -> L2 GEMM (epilogue stores rows into the source rank's combine slots) -> barrier -> combine
+// ==================================================================================================================
+
+// One CTA. chunk_hist[chunk][e] (counts) -> exclusive bases over chunks; per-expert totals go to all ranks.
+__global__ void __launch_bounds__(1024)
+dgb200_ep_share_counts_kernel(int* __restrict__ chunk_hist, int num_chunks, int num_experts, int my_rank, int num_ranks,
+                              const PeerTable peers, long long all_counts_offset) {
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int count = 0;
+        for (int c = 0; c < num_chunks; ++c) {
+            int* slot = chunk_hist + static_cast<long long>(c) * num_experts + e;
+            const int t = *slot;
+            *slot = count;
+            count += t;
+        }
+        for (int r = 0; r < num_ranks; ++r) {
+            int* dst = reinterpret_cast<int*>(peers.p[r] + all_counts_offset) + static_cast<long long>(my_rank) * num_experts + e;
+            *dst = count;
+        }
+    }
+}
+
+// Cross-rank barrier: one warp; lane r signals rank r and waits for rank r's signal. Flags only grow (epoch), so they
+// never need a reset. Bounded: a peer that does not show up within the budget is reported, not waited for forever.
+__global__ void __launch_bounds__(32)
+dgb200_ep_barrier_kernel(const PeerTable peers, long long flags_offset, int which, int my_rank,
+                         int num_ranks, int epoch, long long budget_cycles) {
+    const int lane = threadIdx.x;
+    __threadfence_system();
+    if (lane < num_ranks) {
+        int* remote = reinterpret_cast<int*>(peers.p[lane] + flags_offset) + which * kMaxEpRanks + my_rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(remote), "r"(epoch) : "memory");
+        const int* mine = reinterpret_cast<const int*>(peers.p[my_rank] + flags_offset) + which * kMaxEpRanks + lane;
+        const long long t0 = clock64();
+        while (true) {
+            int seen;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (seen - epoch >= 0) break;
+            if (clock64() - t0 > budget_cycles) {
+                report_error(kTimeoutPeer, lane, seen);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __threadfence_system();
+}
+
+// One CTA. From all_counts[source rank][expert] derives, identically on every rank:
+//   my_base[e]   first row, on the owner of expert e, of THIS rank's entries for e
+//   expert_start / expert_end for the local experts (the psum layout the local GEMMs walk), total_rows, stats.
+__global__ void __launch_bounds__(1024)
+dgb200_ep_plan_kernel(const int* __restrict__ all_counts, int num_experts, int num_ranks, int my_rank, int alignment,
+                      int* __restrict__ my_base, int* __restrict__ expert_start, int* __restrict__ expert_end,
+                      int* __restrict__ total_rows, int* __restrict__ cumulative_stats) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    const int per_rank = num_experts / num_ranks;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int owner = 0; owner < num_ranks; ++owner) {
+        if (threadIdx.x == 0) carry = 0;
+        __syncthreads();
+        for (int base = 0; base < per_rank; base += 1024) {
+            const int local = base + static_cast<int>(threadIdx.x);
+            const int e = owner * per_rank + local;
+            int total = 0, before_me = 0;
+            if (local < per_rank) {
+                for (int s = 0; s < num_ranks; ++s) {
+                    const int c = all_counts[static_cast<long long>(s) * num_experts + e];
+                    if (s < my_rank) before_me += c;
+                    total += c;
+                }
+            }
+            const int padded = (total + alignment - 1) / alignment * alignment;
+            int incl = padded;
+            for (int off = 1; off < 32; off <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += n;
+            }
+            if (lane == 31) warp_sums[warp] = incl;
+            __syncthreads();
+            if (warp == 0) {
+                int w = warp_sums[lane];
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, w, off);
+                    if (lane >= off) w += n;
+                }
+                warp_sums[lane] = w;
+            }
+            __syncthreads();
+            const int start = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - padded;
+            if (local < per_rank) {
+                my_base[e] = start + before_me;
+                if (owner == my_rank) {
+                    expert_start[local] = start;
+                    expert_end[local] = start + total;
+                    if (cumulative_stats != nullptr) cumulative_stats[local] += total;
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 1023) carry = start + padded;
+            __syncthreads();
+        }
+        if (owner == my_rank && threadIdx.x == 0) total_rows[0] = carry;
+        __syncthreads();
+    }
+}
+
+// dest_row[entry] = row on the owner rank (my_base[e] + stable rank of the entry among this rank's entries for e).
+__global__ void __launch_bounds__(kPlanChunk)
+dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries, int num_experts,
+                        const int* __restrict__ chunk_hist, const int* __restrict__ my_base, int* __restrict__ dest_row) {
+    extern __shared__ unsigned char warp_hist[];  // [32 warps][num_experts]
+    for (int i = threadIdx.x; i < 32 * num_experts; i += blockDim.x) warp_hist[i] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * kPlanChunk + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int e = -1;
+    if (i < num_entries) {
+        const long long g = topk_idx[i];
+        if (g >= 0 && g < num_experts) e = static_cast<int>(g);
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_hist[warp * num_experts + e] = static_cast<unsigned char>(__popc(peers));
+    __syncthreads();
+    if (i >= num_entries) return;
+    if (e < 0) {
+        dest_row[i] = -1;
+        return;
+    }
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_hist[w * num_experts + e];
+    dest_row[i] = my_base[e] + chunk_hist[static_cast<long long>(blockIdx.x) * num_experts + e] + before + rank_in_warp;
+}
+
+// One warp per entry: stores the token's FP8 row, its packed scales (into the owner's MN-major scale buffer), the routing
+// weight and the source id into the owner rank's buffers.
+__global__ void __launch_bounds__(256)
+dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
+                      const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights,
+                      const int* __restrict__ dest_row, int num_entries, int topk, int hidden, int experts_per_rank,
+                      int my_rank, int entries_per_rank, const PeerTable peers,
+                      long long acts_offset, long long sf_offset, long long sf_k_stride, long long weight_offset,
+                      long long src_offset) {
+    const int lane = threadIdx.x & 31;
+    const int entry = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (entry >= num_entries) return;
+    const int dest = dest_row[entry];
+    if (dest < 0) return;
+    const int owner = static_cast<int>(topk_idx[entry]) / experts_per_rank;
+    const int token = entry / topk;
+    const unsigned long long base = peers.p[owner];
+    const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * hidden);
+    uint4* to = reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * hidden);
+    for (int c = lane; c < hidden / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
+    unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
+    const int sf_per_row = hidden / 128;
+    for (int c = lane; c < sf_per_row; c += 32)
+        sf[static_cast<long long>(c) * sf_k_stride + dest] = x_sf[static_cast<long long>(token) * sf_per_row + c];
+    if (lane == 0) {
+        reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
+        reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;
+    }
+}
+
 }  // namespace dgb

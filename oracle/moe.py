@@ -105,3 +105,43 @@ def moe_layer(x_q: torch.Tensor, x_sf: torch.Tensor, topk_idx: torch.Tensor, top
         y += torch.where(valid[:, k, None], slot_rows[:, k].float(), torch.zeros(()))
     y = y.bfloat16()
     return (y, inter) if return_intermediates else y
+
+
+def ep_counts(topk_idx: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Entries of one rank per (global) expert, masked slots (-1) excluded: the vector each rank publishes."""
+    flat = topk_idx.reshape(-1)
+    return torch.bincount(flat[(flat >= 0) & (flat < num_experts)], minlength=num_experts)
+
+
+def ep_plan(all_counts: torch.Tensor, rank: int, alignment: int):
+    """Expert-parallel dispatch plan, computed identically by every rank from all_counts [ranks, experts].
+
+    Expert e lives on rank e // (experts / ranks) (sm100_fp8_fp4_mega_moe.cuh:372,389). On its owner, the rows of
+    expert e are ordered by (source rank, entry) and the experts' segments are padded to ``alignment``.
+    Returns (my_base int64 [experts]: first row on the owner of this rank's entries for e,
+             expert_start, expert_end int64 [experts_per_rank] of this rank's own experts)."""
+    ranks, experts = all_counts.shape
+    per_rank = experts // ranks
+    total = all_counts.sum(dim=0)
+    before_me = all_counts[:rank].sum(dim=0)
+    owner_start = torch.zeros(experts, dtype=torch.int64)
+    for owner in range(ranks):
+        cursor = 0
+        for e in range(owner * per_rank, (owner + 1) * per_rank):
+            owner_start[e] = cursor
+            cursor = align(cursor + int(total[e]), alignment)
+    mine = slice(rank * per_rank, (rank + 1) * per_rank)
+    return owner_start + before_me, owner_start[mine].clone(), (owner_start + total)[mine].clone()
+
+
+def ep_dest_rows(topk_idx: torch.Tensor, my_base: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Row, on the owner rank, of each of this rank's (token, k) entries: my_base[e] + the number of earlier entries
+    of this rank with the same expert; -1 for masked slots."""
+    flat = topk_idx.reshape(-1)
+    dest = torch.full_like(flat, -1)
+    seen = torch.zeros(num_experts, dtype=torch.int64)
+    for i, e in enumerate(flat.tolist()):
+        if 0 <= e < num_experts:
+            dest[i] = int(my_base[e]) + int(seen[e])
+            seen[e] += 1
+    return dest
