@@ -159,7 +159,6 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
         case kEpiBF16: DGB_LAUNCH(kEpiBF16);
         case kEpiF32: DGB_LAUNCH(kEpiF32);
         case kEpiSwiGLU: DGB_LAUNCH(kEpiSwiGLU);
-        case kEpiScatter: DGB_LAUNCH(kEpiScatter);
         default: return fail(DGB200_EINVAL, "unknown epilogue %d", c.epilogue);
     }
 #undef DGB_LAUNCH
@@ -188,7 +187,7 @@ struct MegaLayout {
     long long chunk_hist, expert_start, expert_end, total_rows, dest_row;  // dispatch plan
     long long src_of_row, row_weight;
     long long all_counts, my_base, flags;  // expert-parallel exchange: counts of every rank, this rank's bases, barrier flags
-    long long l1_acts, l1_sf, l2_acts, l2_sf, combine;
+    long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
     long long total;
     long long max_rows;  // capacity of the expert-sorted buffers (rows), a multiple of 128
     int num_chunks, num_local_experts;
@@ -230,7 +229,7 @@ int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, i
     l.l1_sf = take(l.max_rows * (hidden / 128) * 4);
     l.l2_acts = take(l.max_rows * inter);
     l.l2_sf = take(l.max_rows * (inter / 128) * 4);
-    l.combine = take(static_cast<long long>(topk) * max_tokens * hidden * 2);
+    l.l2_out = take(l.max_rows * hidden * 2);
     l.total = off;
     *out = l;
     return 0;
@@ -271,10 +270,9 @@ int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, i
 
 
 // The two grouped GEMMs of the layer over this rank's expert-sorted rows (shared by the single-rank and the
-// expert-parallel paths). `combine_bases[r]` = rank r's combine buffer as mapped here.
+// expert-parallel paths): L1 writes FP8 activations + scales, L2 writes BF16 rows into l2_out in the same row order.
 int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
-                    const void* l2_w_sf, void* const* combine_bases, int num_ranks, int num_max_tokens_per_rank,
-                    int num_topk, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
+                    const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
                     cudaStream_t stream, int stage_event_base) {
     const int E = l.num_local_experts;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
@@ -320,7 +318,7 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
         c.b = l2_w;
         c.a_rows_total = l.max_rows;
         c.b_is_fp4 = 1;
-        c.epilogue = kEpiScatter;
+        c.epilogue = kEpiBF16;
         c.max_tiles = 0;
         c.sfa = base + l.l2_sf;
         c.sfb = l2_w_sf;
@@ -339,10 +337,8 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
         p.alignment = kSegmentAlignment;
         p.gran_a = 32;
         p.gran_b = 32;
-        p.row_src = reinterpret_cast<const int*>(base + l.src_of_row);
-        for (int r = 0; r < num_ranks; ++r) p.combine_base[r] = combine_bases[r];
-        p.combine_tokens = num_max_tokens_per_rank;
-        p.topk = num_topk;
+        p.d = base + l.l2_out;
+        p.d_row_stride = hidden;
         if ((rc = run_gemm(c, stream))) return rc;
     }
     return record_stage(stage_event_base + 1, stream);
@@ -363,11 +359,9 @@ int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* 
                     int num_max_tokens_per_rank, int num_experts, int num_topk, int hidden, int intermediate_hidden,
                     float activation_clamp, int fast_math, cudaStream_t stream) {
     PeerTable peers{};
-    void* combine_bases[kMaxRanks];
     for (int r = 0; r < num_ranks; ++r) {
         DGB_REQUIRE(peer_buffer_ptrs[r] != 0, "peer buffer %d is not mapped", r);
         peers.p[r] = peer_buffer_ptrs[r];
-        combine_bases[r] = reinterpret_cast<void*>(peer_buffer_ptrs[r] + l.combine);
     }
     const int entries = num_tokens * num_topk;
     const int chunks = std::max(1, (entries + kPlanChunk - 1) / kPlanChunk);
@@ -404,14 +398,12 @@ int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* 
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
     if ((rc = record_stage(2, stream))) return rc;
 
-    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, combine_bases, num_ranks, num_max_tokens_per_rank, num_topk, hidden,
-                         intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
     if (rc) return rc;
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, static_cast<int>(epoch0 + 3), kPeerWaitBudgetCycles);
     if (num_tokens > 0)
-        dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(int), stream>>>(
-            reinterpret_cast<const __nv_bfloat16*>(base + l.combine), dest_row, num_topk, num_max_tokens_per_rank, hidden,
-            static_cast<__nv_bfloat16*>(y));
+        dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
+            peers, l.l2_out, topk_idx, dest_row, num_topk, l.num_local_experts, hidden, static_cast<__nv_bfloat16*>(y));
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }
@@ -651,7 +643,7 @@ int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_ex
     out[11] = l.src_of_row;
     out[12] = l.expert_start;
     out[13] = l.expert_end;
-    out[14] = l.combine;
+    out[14] = l.l2_out;
     out[15] = l.row_weight;
     return 0;
 }
@@ -717,14 +709,13 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
 
     if ((rc = record_stage(2, stream))) return rc;
     // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
-    void* combine_bases[1] = {base + l.combine};
-    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, combine_bases, 1, num_max_tokens_per_rank, num_topk, hidden,
-                         intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
     if (rc) return rc;
-    // 5. combine: y[t] = sum over the top-k slots
-    dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(int), stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(base + l.combine), dest_row, num_topk, num_max_tokens_per_rank, hidden,
-        static_cast<__nv_bfloat16*>(y));
+    // 5. combine: y[t] = sum over the top-k slots of the rows the L2 GEMM wrote
+    PeerTable self{};
+    self.p[0] = reinterpret_cast<unsigned long long>(base);
+    dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
+        self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden, static_cast<__nv_bfloat16*>(y));
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }

@@ -38,7 +38,6 @@ enum EpilogueKind : int {
     kEpiBF16 = 0,    // D bf16
     kEpiF32 = 1,     // D fp32 (raw accumulators; bring-up and tests)
     kEpiSwiGLU = 2,  // gate/up -> silu(gate)*up*row_weight -> per-32 UE8M0 FP8 requant
-    kEpiScatter = 3, // D bf16, row r written to the combine slot of its source (rank, token, top-k slot)
 };
 
 constexpr int kMaxRanks = 8;
@@ -79,12 +78,6 @@ struct GemmParams {
     const float* row_weight;     // per destination row, may be null (weight 1)
     float clamp;                 // <= 0: no clamp
     int fast_math;               // SwiGLU: approximate exp / reciprocal (the reference's default) or IEEE expf and division
-    // Scatter epilogue only: row r belongs to entry e = row_src[r] % (combine_tokens * topk) of rank
-    // row_src[r] / (combine_tokens * topk); entry e = token * topk + slot lands in
-    // combine_base[rank][(slot * combine_tokens + token) * n + column].
-    const int* row_src;
-    void* combine_base[kMaxRanks];
-    int combine_tokens, topk;
 };
 
 struct Tile {
@@ -544,7 +537,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             const bool store = r < t.rows_store && !DGB_SKIP(p, 32);
             const long long row = static_cast<long long>(t.row_start) + r;
             if (store) {
-                if constexpr (EPI == kEpiBF16 || EPI == kEpiF32 || EPI == kEpiScatter) {
+                if constexpr (EPI == kEpiBF16 || EPI == kEpiF32) {
                     const long long col0 = static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
                     if constexpr (EPI == kEpiF32) {
                         float* dst = reinterpret_cast<float*>(p.d) + row * p.d_row_stride + col0;
@@ -552,17 +545,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         for (int i = 0; i < kCols / 4; ++i)
                             st_global_v4(dst + i * 4, acc[i * 4 + 0], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]);
                     } else {
-                        __nv_bfloat16* dst;
-                        if constexpr (EPI == kEpiScatter) {
-                            const int src = __ldg(p.row_src + row);
-                            const int per_rank = p.combine_tokens * p.topk;
-                            const int rank = src / per_rank, entry = src - rank * per_rank;
-                            const int token = entry / p.topk, slot = entry - token * p.topk;
-                            dst = reinterpret_cast<__nv_bfloat16*>(p.combine_base[rank]) +
-                                  (static_cast<long long>(slot) * p.combine_tokens + token) * p.n + col0;
-                        } else {
-                            dst = reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col0;
-                        }
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col0;
 #pragma unroll
                         for (int i = 0; i < kCols / 8; ++i)
                             st_global_v4(dst + i * 8,

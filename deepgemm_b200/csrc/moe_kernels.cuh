@@ -199,22 +199,38 @@ dgb200_route_sigmoid_topk_kernel(const float* __restrict__ logits, int tokens, i
     }
 }
 
-// y[t, :] = bf16( sum over valid k, in ascending k, of float(combine[k][t, :]) ); slot k of token t is valid when
-// dest_row[t * topk + k] >= 0. combine is bf16 [topk][combine_tokens][hidden].
-// One CTA per token; a thread owns 8 consecutive channels (one 16-byte vector per slot).
+constexpr int kMaxEpRanks = 8;
+struct PeerTable {
+    unsigned long long p[kMaxEpRanks];  // address of every rank's buffer as mapped into this process
+};
+
+// y[t, :] = bf16( sum over valid k, in ascending k, of float(row(t, k)[:]) ), where row(t, k) is the L2 GEMM's output
+// row for entry (t, k): row dest_row[t * topk + k] of the `rows` buffer of the rank that owns expert topk_idx[t, k]
+// (read in place over NVLink when that is another rank: the combine pulls, nothing is pushed). Slots with
+// dest_row < 0 are skipped. One CTA per token; a thread owns 8 consecutive channels (one 16-byte vector per slot).
+// Reference: the combine of the fused kernel, deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:1323-1452.
 __global__ void __launch_bounds__(128)
-dgb200_moe_combine_kernel(const __nv_bfloat16* __restrict__ combine, const int* __restrict__ dest_row, int topk,
-                          int combine_tokens, int hidden, __nv_bfloat16* __restrict__ y) {
+dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
+                          const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
+                          __nv_bfloat16* __restrict__ y) {
     const int t = blockIdx.x;
-    extern __shared__ int valid[];
-    if (threadIdx.x < topk) valid[threadIdx.x] = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
+    extern __shared__ unsigned long long slot_rows[];  // address of each slot's row, 0 = skip
+    if (threadIdx.x < topk) {
+        const int d = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
+        unsigned long long addr = 0;
+        if (d >= 0) {
+            const int owner = static_cast<int>(topk_idx[static_cast<long long>(t) * topk + threadIdx.x]) / experts_per_rank;
+            addr = peers.p[owner] + rows_offset + static_cast<unsigned long long>(d) * hidden * 2;
+        }
+        slot_rows[threadIdx.x] = addr;
+    }
     __syncthreads();
     for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int k = 0; k < topk; ++k) {
-            if (valid[k] < 0) continue;
-            const __nv_bfloat16* row = combine + (static_cast<long long>(k) * combine_tokens + t) * hidden;
-            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(row) + c);
+            const unsigned long long addr = slot_rows[k];
+            if (addr == 0) continue;
+            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(addr) + c);
             const unsigned w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -230,11 +246,6 @@ dgb200_moe_combine_kernel(const __nv_bfloat16* __restrict__ combine, const int* 
         reinterpret_cast<uint4*>(y + static_cast<long long>(t) * hidden)[c] = o;
     }
 }
-
-constexpr int kMaxEpRanks = 8;
-struct PeerTable {
-    unsigned long long p[kMaxEpRanks];  // address of every rank's buffer as mapped into this process
-};
 
 // ==================================================================================================================
 // Expert-parallel dispatch: ranks own contiguous blocks of experts (expert e lives on rank e / experts_per_rank, as

@@ -33,7 +33,7 @@ def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hi
         num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
         ctypes.cast(words, ctypes.c_void_p)))
     keys = ['total', 'x', 'x_sf', 'topk_idx', 'topk_weights', 'l1_acts', 'l1_sf', 'l2_acts', 'l2_sf', 'max_rows',
-            'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'combine', 'row_weight']
+            'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'l2_out', 'row_weight']
     return dict(zip(keys, list(words)))
 
 

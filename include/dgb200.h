@@ -133,7 +133,7 @@ int dgb200_get_token_alignment_for_mega_moe(void);
 
 /* Byte layout of the per-rank mega-MoE buffer. Reference: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155.
  * out[16] = {total bytes, x, x_sf, topk_idx, topk_weights, l1_acts, l1_sf, l2_acts, l2_sf, max_rows (rows, not bytes),
- *            dest_row, src_of_row, expert_start, expert_end, combine, row_weight}; all but out[0], out[9] are byte
+ *            dest_row, src_of_row, expert_start, expert_end, l2_out, row_weight}; all but out[0], out[9] are byte
  * offsets. The caller writes x (e4m3 [T, hidden]), x_sf (int32 [T, hidden / 128], per-32 UE8M0, token-major),
  * topk_idx (int64 [T, topk], -1 = masked) and topk_weights (float [T, topk]) before each call; the rest is private. */
 int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
