@@ -408,6 +408,36 @@ int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* 
     return record_stage(5, stream);
 }
 
+
+// --------------------------------------------------------------------------------------------------------------
+// Scratch of the allocation-free dispatch-plan entry point: per-chunk expert histograms (the same role the
+// caller-provided buffer plays for the layer call) plus one word for the row total. File-scope device memory, so
+// every GPU that loads the library holds these ~129 KB until the process exits.
+// --------------------------------------------------------------------------------------------------------------
+constexpr int kNoAllocMaxEntries = 65536;  // num_tokens * num_topk
+constexpr int kNoAllocMaxExperts = 512;
+constexpr int kNoAllocScratchInts = (kNoAllocMaxEntries / kPlanChunk) * kNoAllocMaxExperts + 64;
+static __device__ __align__(256) int g_noalloc_plan_scratch[kNoAllocScratchInts];
+
+// Device address of the scratch array on the current device, looked up once per device. In host code the array's
+// name is only a handle for the runtime; cudaGetSymbolAddress turns it into the address a kernel can use.
+int noalloc_scratch_for_current_device(int** out) {
+    constexpr int kMaxDevices = 64;
+    static int* cached[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = 0;
+    DGB_CUDA(cudaGetDevice(&dev));
+    DGB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        int* ptr = nullptr;
+        DGB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_plan_scratch));
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return 0;
+}
+
 }  // namespace
 }  // namespace dgb
 
@@ -725,6 +755,37 @@ int dgb200_set_mega_moe_stage_events(void* const* events, int32_t count) {
     DGB_REQUIRE(count == 0 || events != nullptr, "null event array");
     for (int i = 0; i < count; ++i) g_stage_events[i] = static_cast<cudaEvent_t>(events[i]);
     g_num_stage_events = count;
+    return 0;
+}
+
+int dgb200_moe_dispatch_plan_noalloc(const int64_t* topk_idx, int32_t num_tokens, int32_t num_topk, int32_t num_experts,
+                                     int32_t alignment, int32_t* dest_row, int32_t* expert_start, int32_t* expert_end,
+                                     void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DGB_REQUIRE(topk_idx != nullptr && dest_row != nullptr && expert_start != nullptr && expert_end != nullptr,
+                "null tensor pointer");
+    DGB_REQUIRE(num_tokens >= 0 && num_topk > 0 && num_experts > 0 && alignment > 0, "bad shape");
+    const long long entries = static_cast<long long>(num_tokens) * num_topk;
+    DGB_REQUIRE(entries <= kNoAllocMaxEntries,
+                "num_tokens * num_topk = %lld exceeds the built-in scratch (%d entries); use the layer call with a caller buffer",
+                entries, kNoAllocMaxEntries);
+    DGB_REQUIRE(num_experts <= kNoAllocMaxExperts, "num_experts = %d exceeds the built-in scratch (%d experts)", num_experts,
+                kNoAllocMaxExperts);
+    int* scratch = nullptr;
+    const int rc = noalloc_scratch_for_current_device(&scratch);
+    if (rc) return rc;
+    int* total_rows = scratch;        // 1 word (rewritten by every call)
+    int* chunk_hist = scratch + 64;   // [chunks][num_experts], every word the later kernels read is rewritten first
+    const int n = static_cast<int>(entries);
+    const int chunks = std::max(1, (n + kPlanChunk - 1) / kPlanChunk);
+    const long long* idx = reinterpret_cast<const long long*>(topk_idx);
+    dgb200_moe_count_kernel<<<chunks, kPlanChunk, num_experts * sizeof(int), stream>>>(idx, n, 0, num_experts, chunk_hist);
+    dgb200_moe_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, num_experts, alignment, expert_start, expert_end,
+                                                    total_rows, nullptr);
+    if (n > 0)
+        dgb200_ep_assign_kernel<<<chunks, kPlanChunk, 32 * num_experts, stream>>>(idx, n, num_experts, chunk_hist, expert_start,
+                                                                              dest_row);
+    DGB_CUDA(cudaGetLastError());
     return 0;
 }
 

@@ -156,6 +156,27 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                             int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                             float activation_clamp, int32_t fast_math, void* stream);
 
+/* Dispatch plan for callers that cannot allocate device memory. It has no counterpart in the reference.
+ * Some hosts of this library run it from places where cudaMalloc is off limits: inside a region whose memory is
+ * owned by another allocator with a fixed pool, in a callback that must not synchronise the device, or in a service
+ * that forbids allocation after start-up. For them this entry point computes the layer's dispatch permutation
+ * (the stable sort of the (token, k) entries by expert that dgb200_fp8_fp4_mega_moe builds inside its buffer) using
+ * a scratch array that is part of the library image instead of a caller buffer. It calls no cudaMalloc / cudaFree and
+ * no allocating library routine; inputs and outputs are the caller's.
+ *   topk_idx      int64 [num_tokens, num_topk], -1 = masked slot
+ *   dest_row      int32 [num_tokens * num_topk]   row of each entry in expert-sorted order, -1 for masked slots
+ *   expert_start  int32 [num_experts]             first row of each expert (multiples of `alignment`)
+ *   expert_end    int32 [num_experts]             one past the last row of each expert
+ * Limits: num_tokens * num_topk <= 65536 and num_experts <= 512 (about 129 KB of device memory per GPU, held from
+ * library load to process exit); larger problems are rejected with DGB200_EINVAL.
+ * The first call on a device looks up the scratch array's device address (cudaGetSymbolAddress): make that first
+ * call outside any stream capture. All calls on a device share the one scratch array: it keeps whatever the last
+ * call left (every word a call reads it has written first, so nothing needs clearing), and two calls that overlap
+ * on the GPU (different streams, no ordering) race on it. */
+int dgb200_moe_dispatch_plan_noalloc(const int64_t* topk_idx, int32_t num_tokens, int32_t num_topk, int32_t num_experts,
+                                     int32_t alignment, int32_t* dest_row, int32_t* expert_start, int32_t* expert_end,
+                                     void* stream);
+
 /* Measurement hook: the NEXT dgb200_fp8_fp4_mega_moe call of this host thread records events[i] (cudaEvent_t
  * handles) on its stream at stage boundary i: 0 entry, 1 after the dispatch plan, 2 after the gather, 3 after L1,
  * 4 after L2, 5 after the combine. The setting is consumed by that call. No reference counterpart (the reference
