@@ -27,8 +27,9 @@ METRIC = 'mega_moe_layer_tokens_per_s'
 CPU_SAMPLE_EXPERTS = 4  # experts whose routed rows the CPU legs evaluate per pass
 FP4_DENSE_PEAK_TFLOPS_NOMINAL = 9000.0
 FP8_DENSE_PEAK_TFLOPS_NOMINAL = 4500.0
-# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture, or None while unmeasured.
-L1_KERNEL_DRAM_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu capture summarised in
+# profiles/grouped_gemm_small_layer_ncu_full.md (small case, scaled by the units processed).
+L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.03
 
 
 def parse_args():
@@ -334,7 +335,7 @@ def run_ours(args, cfg, rank, world, local_rank):
         'clocks': clocks,
         'roofline': {'kernel': 'dgb200_grouped_gemm_kernel (L1: gate/up GEMM + SwiGLU + FP8 requant)', 'bound': 'hbm',
                      'achieved': l1_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': l1_gbs / peak, 'peak_source': peak_kind,
-                     'traffic': L1_KERNEL_DRAM_TRAFFIC_BYTES, 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]},
+                     'traffic': int(L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * l1_bytes), 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]},
         'stages_ms': {'plan': stage_ms[0], 'gather': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
                       'l2_gemm_scatter': stage_ms[3], 'combine': stage_ms[4]},
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9,
