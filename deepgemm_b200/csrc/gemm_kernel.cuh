@@ -88,25 +88,30 @@ struct Tile {
     int n_block;
 };
 
+constexpr int kMaxCachedGroups = 1024;  // group extents of up to this many groups are staged in shared memory
+
 template <int BLOCK_N>
 struct TileScheduler {
     const GemmParams& p;
+    const int* lay;  // per-group extents (psum ends / masked counts): the shared-memory copy when it fits, else global.
+                     // A dependent global load costs several hundred cycles and every role walks the groups per tile.
     int num_n_blocks;
     int tile;  // next global tile index of this CTA
     int g, tiles_before_g;
 
-    __device__ explicit TileScheduler(const GemmParams& params)
-        : p(params), num_n_blocks(params.n / BLOCK_N), tile(static_cast<int>(blockIdx.x)), g(0), tiles_before_g(0) {}
+    __device__ TileScheduler(const GemmParams& params, const int* group_layout)
+        : p(params), lay(group_layout), num_n_blocks(params.n / BLOCK_N), tile(static_cast<int>(blockIdx.x)), g(0),
+          tiles_before_g(0) {}
 
     __device__ __forceinline__ void group_extent(int group, int& start, int& rows, int& rows_store) const {
         if (p.mode == kModeMasked) {
             start = group * p.m;
-            rows = min(__ldg(p.layout + group), p.m);
+            rows = min(lay[group], p.m);
             rows_store = rows;
         } else {
-            const int prev_end = group == 0 ? 0 : __ldg(p.layout + group - 1);
+            const int prev_end = group == 0 ? 0 : lay[group - 1];
             start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
-            const int end = __ldg(p.layout + group);
+            const int end = lay[group];
             rows = max(end - start, 0);
             const int aligned_end = min((end + p.alignment - 1) / p.alignment * p.alignment, p.m);
             rows_store = p.store_padding ? max(aligned_end - start, 0) : rows;
@@ -162,7 +167,8 @@ struct GemmSmem {
     static constexpr int kOffBar = kOffSfb + kStages * kSfbBytes;
     static constexpr int kNumBars = 3 * kStages + 4;
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;
-    static constexpr int kTotal = kOffMisc + 16;
+    static constexpr int kOffGroups = kOffMisc + 16;
+    static constexpr int kTotal = kOffGroups + kMaxCachedGroups * 4;
     static constexpr int kDynamicBytes = kTotal + 1024;  // slack to align the base to 1024 B
 };
 
@@ -242,6 +248,11 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         prefetch_tensormap(&tm_sfa);
         prefetch_tensormap(&tm_sfb);
     }
+    int* group_cache = reinterpret_cast<int*>(smem + L::kOffGroups);
+    const bool cache_groups = p.mode != kModeRowIds && p.num_groups <= kMaxCachedGroups;
+    if (cache_groups)
+        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) group_cache[i] = __ldg(p.layout + i);
+    const int* group_layout = cache_groups ? group_cache : p.layout;
     if (warp == 2) tmem_alloc(tmem_ptr_smem, kTmemCols);
     tcgen05_fence_before();
     __syncthreads();
@@ -264,13 +275,13 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // instructions take their descriptors from uniform registers, which a single-lane (divergent) loop would
         // have to refill through slow register-to-uniform moves for every instruction.
         {
-            TileScheduler<BLOCK_N> sched(p);
+            TileScheduler<BLOCK_N> sched(p, group_layout);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int trace_i = 0;
             // L2 prefetch cursor for the A rows and their scale factors (see the weight loader below)
-            TileScheduler<BLOCK_N> pf_sched(p);
+            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
             Tile pt;
             int pf_kb = 0;
             bool pf_valid = false;
@@ -334,7 +345,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     } else if (warp == 3) {
         // ---------------------------------------------------------------- loader: B (weight) tile + L2 prefetch
         {
-            TileScheduler<BLOCK_N> sched(p);
+            TileScheduler<BLOCK_N> sched(p, group_layout);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -343,7 +354,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             // L2 prefetch cursor: walks the same (tile, K block) sequence `prefetch_distance` blocks ahead of the
             // loads. A stage holds only 8 or 16 KB of packed FP4 weights and shared memory bounds the number of
             // stages, so HBM latency can be covered by prefetches in flight to L2 instead of by more stages.
-            TileScheduler<BLOCK_N> pf_sched(p);
+            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
             Tile pt;
             int pf_kb = 0;
             bool pf_valid = false;
@@ -398,7 +409,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // ---------------------------------------------------------------- MMA issuer
         // Warp-uniform loop, one elected lane issues (see the loader above).
         {
-        TileScheduler<BLOCK_N> sched(p);
+        TileScheduler<BLOCK_N> sched(p, group_layout);
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
         int trace_i = 0;
@@ -458,7 +469,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     } else if (warp == 2) {
         // ---------------------------------------------------------------- scale-factor transposer
         // tcgen05.cp 32x128b wants, per 128 rows, 32 rows x 4 words with word j of row r = source row r + 32 j.
-        TileScheduler<BLOCK_N> sched(p);
+        TileScheduler<BLOCK_N> sched(p, group_layout);
         Tile t;
         uint32_t stage = 0, phase = 0;
         int trace_i = 0;
@@ -508,7 +519,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // Each thread first drains its half row of the accumulator into registers and releases the accumulator, so
         // the MMA issuer can start the next tile while the arithmetic and the stores below run.
         constexpr int kCols = BLOCK_N / 2;  // accumulator columns per thread
-        TileScheduler<BLOCK_N> sched(p);
+        TileScheduler<BLOCK_N> sched(p, group_layout);
         Tile t;
         uint32_t iter = 0;
         const uint32_t q = warp & 3, half = (warp - 4) >> 2;
