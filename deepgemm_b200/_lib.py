@@ -32,6 +32,11 @@ _SIGNATURES = {
     'dgb200_per_token_cast_to_fp4': [_ptr, _i64, _i32, _i32, _i32, _ptr, _i64, _ptr, _ptr, _i64, _i64, _ptr],
     'dgb200_transform_sf_into_required_layout': [
         _ptr, _i64, _i64, _i64, _ptr, _i32, _i32, _i32, _i32, _ptr, _i32, _i32, _ptr],
+    'dgb200_nvfp4_tensor_scale': [_ptr, _i64, _i32, _i32, _ptr, _ptr],
+    'dgb200_per_token_cast_to_nvfp4': [_ptr, _i64, _i32, _i32, _ptr, _ptr, _i64, _ptr, _i64, _i64, _ptr],
+    'dgb200_m_grouped_nvfp4_gemm_nt_contiguous': [
+        _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _i64, _i64, _ptr, _ptr, _i64, _ptr,
+        _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_route_sigmoid_topk': [_ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr],
     'dgb200_get_token_alignment_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],

@@ -19,11 +19,11 @@ namespace {
 
 constexpr int kVersion = 100;
 
-template <int BLOCK_N, int kStages, int EPI>
+template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
 int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_sfa, const CUtensorMap& tm_sfb,
                 const GemmParams& p, int grid, cudaStream_t stream) {
-    using L = GemmSmem<BLOCK_N, kStages>;
-    auto kernel = dgb200_grouped_gemm_kernel<BLOCK_N, kStages, EPI>;
+    using L = GemmSmem<BLOCK_N, kStages, kKind>;
+    auto kernel = dgb200_grouped_gemm_kernel<BLOCK_N, kStages, EPI, kKind>;
     static bool configured = false;  // per instantiation; the attribute is per device function, set on every device once
     static int configured_device = -1;
     int dev = 0;
@@ -45,6 +45,7 @@ struct GemmCall {
     const void* sfb;
     long long sfa_k_stride, sfa_group_stride, sfb_k_stride, sfb_group_stride;
     int num_groups_a;  // groups of A's scale factors: 1 for the contiguous layouts, num_groups for the masked one
+    int kind;          // kKindFp8Fp4 (default) or kKindNvfp4
     long long a_rows_total;  // rows of the flattened A
     GemmParams p;
     int b_is_fp4;
@@ -74,7 +75,9 @@ Tuning& tuning() {
 
 int run_gemm(GemmCall& c, cudaStream_t stream) {
     GemmParams& p = c.p;
-    DGB_REQUIRE(p.k > 0 && p.k % 128 == 0, "k (%d) must be a positive multiple of 128", p.k);
+    const bool nvfp4 = c.kind == kKindNvfp4;
+    DGB_REQUIRE(p.k > 0 && p.k % (nvfp4 ? 256 : 128) == 0, "k (%d) must be a positive multiple of %d", p.k, nvfp4 ? 256 : 128);
+    if (nvfp4) p.gran_a = p.gran_b = 32;  // unused by this kind; keeps the checks below uniform
     DGB_REQUIRE(p.n > 0 && p.n % 128 == 0, "n (%d) must be a positive multiple of 128", p.n);
     DGB_REQUIRE(p.gran_a == 32 || p.gran_a == 128, "gran_k_a must be 32 or 128, got %d", p.gran_a);
     DGB_REQUIRE(p.gran_b == 32 || p.gran_b == 128, "gran_k_b must be 32 or 128, got %d", p.gran_b);
@@ -87,7 +90,9 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
                 "scale-factor tensors must be 16-byte aligned");
     DGB_REQUIRE(c.sfa_k_stride % 4 == 0 && c.sfb_k_stride % 4 == 0 && c.sfa_k_stride > 0 && c.sfb_k_stride >= p.n,
                 "packed scale-factor MN strides must be positive multiples of 4 ints (TMA-aligned) that cover MN");
-    const int packed_k_a = (p.k / p.gran_a + 3) / 4, packed_k_b = (p.k / p.gran_b + 3) / 4;
+    const int packed_k_a = nvfp4 ? p.k / 64 : (p.k / p.gran_a + 3) / 4;
+    const int packed_k_b = nvfp4 ? p.k / 64 : (p.k / p.gran_b + 3) / 4;
+    const uint32_t sf_box_rows = nvfp4 ? 4 : 1;  // packed scale ints per row per K block
     DGB_REQUIRE(c.num_groups_a == 1 || c.sfa_group_stride == packed_k_a * c.sfa_k_stride,
                 "scale factors of A: group stride must equal packed K x MN stride");
     DGB_REQUIRE(p.num_groups == 1 || c.sfb_group_stride == packed_k_b * c.sfb_k_stride,
@@ -99,22 +104,29 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
                                 static_cast<uint64_t>(packed_k_a) * c.num_groups_a,
-                                static_cast<uint64_t>(c.sfa_k_stride) * 4, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+                                static_cast<uint64_t>(c.sfa_k_stride) * 4, 128, sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     // Wide N tiles give each tcgen05.mma enough work (128 x 256 x 32) to cover the per-K-block issue chain.
     const int block_n = tuning().block_n != 0 ? tuning().block_n : (p.n % 256 == 0 ? 256 : 128);
     DGB_REQUIRE((block_n == 128 || block_n == 256) && p.n % block_n == 0, "block_n %d does not divide n %d", block_n, p.n);
     rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
                             static_cast<uint64_t>(packed_k_b) * p.num_groups, static_cast<uint64_t>(c.sfb_k_stride) * 4,
-                            static_cast<uint32_t>(block_n), 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+                            static_cast<uint32_t>(block_n), sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, static_cast<uint64_t>(p.k),
-                                static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.k), 128, 128,
+    const uint64_t a_row_bytes = nvfp4 ? p.k / 2 : p.k;  // packed E2M1 or E4M3
+    rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, a_row_bytes,
+                                static_cast<uint64_t>(c.a_rows_total), a_row_bytes, 128, 128,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     const uint64_t b_rows = static_cast<uint64_t>(p.num_groups) * p.n;
     const uint32_t BLOCK_N = static_cast<uint32_t>(block_n);
-    if (c.b_is_fp4) {
+    if (nvfp4) {
+        // both operands stay packed in shared memory (two E2M1 per byte): plain byte tensors
+        rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, static_cast<uint64_t>(p.k / 2), b_rows,
+                                static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = kFmtE2M1_MXF4;
+        p.b_tx_bytes = BLOCK_N * 128;
+    } else if (c.b_is_fp4) {
         rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, c.b, static_cast<uint64_t>(p.k), b_rows,
                                 static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
         p.b_fmt = kFmtE2M1_F8F6F4;
@@ -134,9 +146,9 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     p.sfa_ptr = static_cast<const unsigned char*>(c.sfa);
     p.sfb_ptr = static_cast<const unsigned char*>(c.sfb);
     p.a_rows = c.a_rows_total;
-    p.a_row_bytes = p.k;
-    p.b_row_bytes = c.b_is_fp4 ? p.k / 2 : p.k;
-    p.b_kb_bytes = c.b_is_fp4 ? 64 : 128;
+    p.a_row_bytes = static_cast<long long>(a_row_bytes);
+    p.b_row_bytes = (nvfp4 || c.b_is_fp4) ? p.k / 2 : p.k;
+    p.b_kb_bytes = (c.b_is_fp4 && !nvfp4) ? 64 : 128;
     p.sfa_kp_bytes = c.sfa_k_stride * 4;
     p.sfb_kp_bytes = c.sfb_k_stride * 4;
     p.prefetch_distance = tuning().prefetch_distance;
@@ -152,13 +164,21 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     if (c.max_tiles > 0) grid = std::min(grid, c.max_tiles);
 
     if (c.max_tiles > 0 && block_n == 256) grid = std::min(grid, std::max(1, c.max_tiles / 2));
-#define DGB_LAUNCH(EPI)                                                                                        \
-    return block_n == 256 ? launch_gemm<256, 4, EPI>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)              \
-                          : launch_gemm<128, 6, EPI>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)
+#define DGB_LAUNCH(EPI, KIND)                                                                                   \
+    return block_n == 256 ? launch_gemm<256, 4, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)            \
+                          : launch_gemm<128, 6, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)
+    if (nvfp4) {
+        switch (c.epilogue) {
+            case kEpiBF16: DGB_LAUNCH(kEpiBF16, kKindNvfp4);
+            case kEpiF32: DGB_LAUNCH(kEpiF32, kKindNvfp4);
+            case kEpiSwiGLUNvfp4: DGB_LAUNCH(kEpiSwiGLUNvfp4, kKindNvfp4);
+            default: return fail(DGB200_EINVAL, "unknown epilogue %d for the NVFP4 kind", c.epilogue);
+        }
+    }
     switch (c.epilogue) {
-        case kEpiBF16: DGB_LAUNCH(kEpiBF16);
-        case kEpiF32: DGB_LAUNCH(kEpiF32);
-        case kEpiSwiGLU: DGB_LAUNCH(kEpiSwiGLU);
+        case kEpiBF16: DGB_LAUNCH(kEpiBF16, kKindFp8Fp4);
+        case kEpiF32: DGB_LAUNCH(kEpiF32, kKindFp8Fp4);
+        case kEpiSwiGLU: DGB_LAUNCH(kEpiSwiGLU, kKindFp8Fp4);
         default: return fail(DGB200_EINVAL, "unknown epilogue %d", c.epilogue);
     }
 #undef DGB_LAUNCH
@@ -787,6 +807,94 @@ int dgb200_moe_dispatch_plan_noalloc(const int64_t* topk_idx, int32_t num_tokens
                                                                               dest_row);
     DGB_CUDA(cudaGetLastError());
     return 0;
+}
+
+int dgb200_nvfp4_tensor_scale(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, float* out_scale, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DGB_REQUIRE(x != nullptr && out_scale != nullptr, "null tensor pointer");
+    DGB_REQUIRE(rows >= 0 && k > 0 && k % 8 == 0 && (x_row_stride * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0,
+                "x rows must be 16-byte aligned and k a multiple of 8");
+    DGB_CUDA(cudaMemsetAsync(out_scale, 0, sizeof(float), stream));
+    if (rows > 0) {
+        const long long vecs = static_cast<long long>(rows) * (k / 8);
+        const int grid = static_cast<int>(std::min<long long>((vecs + 255) / 256, 148 * 8));
+        dgb200_amax_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride, rows, k, out_scale);
+    }
+    dgb200_finish_tensor_scale_kernel<<<1, 1, 0, stream>>>(out_scale);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int dgb200_per_token_cast_to_nvfp4(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, const float* tensor_scale,
+                                   void* q, int64_t q_row_stride, void* sf_packed, int64_t sf_k_stride,
+                                   int64_t sf_row_stride, void* stream) {
+    DGB_REQUIRE(x != nullptr && q != nullptr && sf_packed != nullptr && tensor_scale != nullptr, "null tensor pointer");
+    DGB_REQUIRE(rows >= 0 && k > 0 && k % 64 == 0, "k (%d) must be a positive multiple of 64", k);
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0 && (x_row_stride * 2) % 16 == 0, "x rows must be 16-byte aligned");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(q) % 8 == 0 && q_row_stride % 8 == 0, "q rows must be 8-byte aligned");
+    DGB_REQUIRE((sf_row_stride == 1 && sf_k_stride >= rows) || (sf_k_stride == 1 && sf_row_stride >= k / 64),
+                "packed scale-factor strides must be (k stride >= rows, row stride 1) or (k stride 1, row stride >= k / 64)");
+    if (rows == 0) return 0;
+    CastNvfp4Params p{};
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.x_row_stride = x_row_stride;
+    p.q = static_cast<unsigned char*>(q);
+    p.q_row_stride = q_row_stride;
+    p.tensor_scale = tensor_scale;
+    p.sf_packed = static_cast<uint32_t*>(sf_packed);
+    p.sf_k_stride = sf_k_stride;
+    p.sf_row_stride = sf_row_stride;
+    p.rows = rows;
+    p.k = k;
+    const dim3 grid((k + 511) / 512, (rows + 31) / 32);
+    dgb200_cast_rows_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int dgb200_m_grouped_nvfp4_gemm_nt_contiguous(
+    const void* a, const void* sfa, int64_t sfa_k_stride, const float* a_scale,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride, const float* b_scales,
+    void* d, int64_t d_row_stride, const int32_t* grouped_layout,
+    int32_t m, int32_t n, int32_t k, int32_t num_groups, int32_t d_is_fp32,
+    int32_t layout_kind, int32_t alignment, void* stream) {
+    DGB_REQUIRE(m >= 0, "m must be >= 0");
+    DGB_REQUIRE(layout_kind == DGB200_LAYOUT_ROW_IDS || layout_kind == DGB200_LAYOUT_PSUM, "unknown layout kind %d", layout_kind);
+    DGB_REQUIRE(alignment > 0 && alignment % 4 == 0, "alignment (%d) must be a positive multiple of 4", alignment);
+    DGB_REQUIRE(layout_kind == DGB200_LAYOUT_PSUM || alignment % 128 == 0,
+                "the row-id layout needs an M alignment that is a multiple of 128, got %d", alignment);
+    DGB_REQUIRE(d != nullptr || m == 0, "null output");
+    DGB_REQUIRE(a_scale != nullptr && b_scales != nullptr, "null per-tensor scale pointer");
+    DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
+                "d row stride must cover n and keep rows 16-byte aligned");
+    DGB_REQUIRE(sfa_k_stride >= m, "sfa MN stride smaller than m");
+    GemmCall c{};
+    c.kind = kKindNvfp4;
+    c.a = a;
+    c.b = b;
+    c.a_rows_total = m;
+    c.b_is_fp4 = 1;
+    c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
+    c.sfa = sfa;
+    c.sfb = sfb;
+    c.sfa_k_stride = sfa_k_stride;
+    c.num_groups_a = 1;
+    c.sfb_k_stride = sfb_k_stride;
+    c.sfb_group_stride = sfb_group_stride;
+    GemmParams& p = c.p;
+    p.d = d;
+    p.d_row_stride = d_row_stride;
+    p.layout = grouped_layout;
+    p.mode = layout_kind == DGB200_LAYOUT_PSUM ? kModePsum : kModeRowIds;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.num_groups = num_groups;
+    p.alignment = alignment;
+    p.a_scale = a_scale;
+    p.b_scales = b_scales;
+    c.max_tiles = 0;
+    return run_gemm(c, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

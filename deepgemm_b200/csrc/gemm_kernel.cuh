@@ -38,6 +38,12 @@ enum EpilogueKind : int {
     kEpiBF16 = 0,    // D bf16
     kEpiF32 = 1,     // D fp32 (raw accumulators; bring-up and tests)
     kEpiSwiGLU = 2,  // gate/up -> silu(gate)*up*row_weight -> per-32 UE8M0 FP8 requant
+    kEpiSwiGLUNvfp4 = 3,  // gate/up -> silu(gate)*up*row_weight -> NVFP4 (per-16 UE4M3 scales, given per-tensor scale)
+};
+
+enum MmaKind : int {
+    kKindFp8Fp4 = 0,  // kind::mxf8f6f4: E4M3 activations x E2M1 (unpacked in smem) or E4M3 weights, UE8M0 scales, K block 128
+    kKindNvfp4 = 1,   // kind::mxf4nvf4 scale_vec::4X: packed E2M1 x packed E2M1, UE4M3 scale per 16, K block 256
 };
 
 constexpr int kMaxRanks = 8;
@@ -78,6 +84,11 @@ struct GemmParams {
     const float* row_weight;     // per destination row, may be null (weight 1)
     float clamp;                 // <= 0: no clamp
     int fast_math;               // SwiGLU: approximate exp / reciprocal (the reference's default) or IEEE expf and division
+    // NVFP4 only: FP32 per-tensor scales. The accumulator is multiplied by a_scale[0] * b_scales[group]; the SwiGLU
+    // epilogue requantises with the given (calibrated) out_scale[0].
+    const float* a_scale;
+    const float* b_scales;
+    const float* out_scale;
 };
 
 struct Tile {
@@ -154,12 +165,13 @@ struct TileScheduler {
     }
 };
 
-template <int BLOCK_N, int kStages>
+template <int BLOCK_N, int kStages, int kKind = kKindFp8Fp4>
 struct GemmSmem {
+    static constexpr int kSfIntsPerRow = kKind == kKindNvfp4 ? 4 : 1;  // packed scale ints per row per K block
     static constexpr int kABytes = 128 * 128;
     static constexpr int kBBytes = BLOCK_N * 128;
-    static constexpr int kSfaBytes = 128 * 4;
-    static constexpr int kSfbBytes = BLOCK_N * 4;
+    static constexpr int kSfaBytes = 128 * 4 * kSfIntsPerRow;
+    static constexpr int kSfbBytes = BLOCK_N * 4 * kSfIntsPerRow;
     static constexpr int kOffA = 0;
     static constexpr int kOffB = kOffA + kStages * kABytes;
     static constexpr int kOffSfa = kOffB + kStages * kBBytes;
@@ -201,18 +213,22 @@ constexpr int kGemmThreads = 384;       // warps 0-3: loaders / MMA / transposer
 constexpr int kRegsControlWarps = 96;   // after setmaxnreg: the control warpgroup gives registers away ...
 constexpr int kRegsEpilogueWarps = 200; // ... to the two epilogue warpgroups, which hold a drained accumulator
 
-template <int BLOCK_N, int kStages, int EPI>
+template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                            const __grid_constant__ GemmParams p) {
-    using L = GemmSmem<BLOCK_N, kStages>;
+    using L = GemmSmem<BLOCK_N, kStages, kKind>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
+    constexpr int kSfInts = L::kSfIntsPerRow;          // scale ints per row per K block = tcgen05.cp blocks per 128 rows
+    constexpr int kSfBlocksA = kSfInts;                // 512-byte blocks of A scales per stage
+    constexpr int kSfBlocksB = kSfInts * BLOCK_N / 128;
+    constexpr int kBlockK = kKind == kKindNvfp4 ? 256 : 128;  // K elements per stage (128 bytes per row either way)
     constexpr uint32_t kAccumCols = BLOCK_N;
     constexpr uint32_t kNumAccum = BLOCK_N == 128 ? 2 : 1;
     // Scale factors get their own TMEM columns per pipeline stage: with a single region every tcgen05.cp would have
     // to wait for the previous K block's MMAs to finish reading it, which serialises copy and MMA.
-    constexpr uint32_t kSfColsPerStage = 4 + BLOCK_N / 32;
+    constexpr uint32_t kSfColsPerStage = 4 * (kSfBlocksA + kSfBlocksB);
     constexpr uint32_t kSfCol0 = kAccumCols * kNumAccum;
     constexpr uint32_t kTmemCols = 512;
     static_assert(kSfCol0 + kStages * kSfColsPerStage <= kTmemCols, "TMEM budget");
@@ -259,9 +275,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
-    const int num_kb = p.k / 128;
-    const int a_per = p.gran_a == 32 ? 1 : 4;  // K blocks covered by one packed SF int
-    const int b_per = p.gran_b == 32 ? 1 : 4;
+    const int num_kb = p.k / kBlockK;
+    const int a_per = (kKind == kKindNvfp4 || p.gran_a == 32) ? 1 : 4;  // K blocks covered by one packed SF int
+    const int b_per = (kKind == kKindNvfp4 || p.gran_b == 32) ? 1 : 4;
 
     // Register re-balancing: each setmaxnreg dominates the code of its warpgroups, so that the compiler allocates
     // the epilogue (which holds half an accumulator row in registers) under the raised limit.
@@ -329,10 +345,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                         t.row_start);
                         if (load_sfa)
                             tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage,
-                                        t.sf_row_start, sfa_y + kb / a_per);
+                                        t.sf_row_start, sfa_y + kb * kSfInts / a_per);
                         if (load_sfb)
                             tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
-                                        t.n_block * BLOCK_N, sfb_y + kb / b_per);
+                                        t.n_block * BLOCK_N, sfb_y + kb * kSfInts / b_per);
                         trace_point(p, 1, trace_i);
                     }
                     __syncwarp();
@@ -413,7 +429,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
         int trace_i = 0;
-        const uint32_t idesc = make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
+        const uint32_t idesc = kKind == kKindNvfp4
+            ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
+            : make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
         uint32_t tmem_sfa = 0, tmem_sfb = 0;  // TMEM columns holding the scale factors of the current K block
@@ -432,29 +450,37 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 tcgen05_fence_after();
                 if (elect_one()) {
                     trace_point(p, 4, trace_i);
+                    // One tcgen05.cp moves the scales of 128 rows for one MMA (one packed int per row) into 4 TMEM columns.
                     const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
                     if (kb % a_per == 0) {
                         tmem_sfa = sf_cols;
-                        tcgen05_cp_32x128b_warpx4(tmem_sfa, make_sf_desc(sfa_smem + stage * L::kSfaBytes));
+#pragma unroll
+                        for (int b = 0; b < kSfBlocksA; ++b)
+                            tcgen05_cp_32x128b_warpx4(tmem_sfa + b * 4, make_sf_desc(sfa_smem + stage * L::kSfaBytes + b * 512));
                     }
                     if (kb % b_per == 0) {
-                        tmem_sfb = sf_cols + 4;
+                        tmem_sfb = sf_cols + 4 * kSfBlocksA;
 #pragma unroll
-                        for (int i = 0; i < BLOCK_N / 128; ++i)
-                            tcgen05_cp_32x128b_warpx4(tmem_sfb + i * 4,
-                                                      make_sf_desc(sfb_smem + stage * L::kSfbBytes + i * 512));
+                        for (int b = 0; b < kSfBlocksB; ++b)
+                            tcgen05_cp_32x128b_warpx4(tmem_sfb + b * 4, make_sf_desc(sfb_smem + stage * L::kSfbBytes + b * 512));
                     }
                     const uint64_t adesc = make_kmajor_sw128_desc(a_base + stage * L::kABytes);
                     const uint64_t bdesc = make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
-                        const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
-                        const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
-                        // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
                         if (DGB_SKIP(p, 8)) continue;
-                        tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
-                                             idesc_with_sf_ids(idesc, sfa_id, sfb_id), tmem_sfa, tmem_sfb,
-                                             (kb | k4) != 0 ? 1u : 0u);
+                        // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
+                        if constexpr (kKind == kKindNvfp4) {
+                            // K = 64 per MMA; its 4 scales per row are the 4 bytes of packed int k4 of the stage
+                            tcgen05_mma_mxf4nvf4_4x(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2, idesc, tmem_sfa + k4 * 4,
+                                                    tmem_sfb + k4 * (BLOCK_N / 32), (kb | k4) != 0 ? 1u : 0u);
+                        } else {
+                            const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
+                            const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
+                            tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
+                                                 idesc_with_sf_ids(idesc, sfa_id, sfb_id), tmem_sfa, tmem_sfb,
+                                                 (kb | k4) != 0 ? 1u : 0u);
+                        }
                     }
                     tcgen05_commit(empty_bar + stage);
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
@@ -485,23 +511,29 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 const bool do_a = kb % a_per == 0, do_b = kb % b_per == 0;
                 uint32_t* sa = reinterpret_cast<uint32_t*>(smem + L::kOffSfa + stage * L::kSfaBytes);
                 uint32_t* sb = reinterpret_cast<uint32_t*>(smem + L::kOffSfb + stage * L::kSfbBytes);
-                uint32_t va[4], vb[BLOCK_N / 128][4];
+                uint32_t va[kSfBlocksA][4], vb[kSfBlocksB][4];
                 if (do_a) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) va[j] = sa[j * 32 + lane];
+                    for (int b = 0; b < kSfBlocksA; ++b)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) va[b][j] = sa[b * 128 + j * 32 + lane];
                 }
                 if (do_b) {
 #pragma unroll
-                    for (int i = 0; i < BLOCK_N / 128; ++i)
+                    for (int b = 0; b < kSfBlocksB; ++b)
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) vb[i][j] = sb[i * 128 + j * 32 + lane];
+                        for (int j = 0; j < 4; ++j) vb[b][j] = sb[b * 128 + j * 32 + lane];
                 }
                 __syncwarp();
-                if (do_a) *reinterpret_cast<uint4*>(sa + lane * 4) = make_uint4(va[0], va[1], va[2], va[3]);
+                if (do_a) {
+#pragma unroll
+                    for (int b = 0; b < kSfBlocksA; ++b)
+                        *reinterpret_cast<uint4*>(sa + b * 128 + lane * 4) = make_uint4(va[b][0], va[b][1], va[b][2], va[b][3]);
+                }
                 if (do_b) {
 #pragma unroll
-                    for (int i = 0; i < BLOCK_N / 128; ++i)
-                        *reinterpret_cast<uint4*>(sb + i * 128 + lane * 4) = make_uint4(vb[i][0], vb[i][1], vb[i][2], vb[i][3]);
+                    for (int b = 0; b < kSfBlocksB; ++b)
+                        *reinterpret_cast<uint4*>(sb + b * 128 + lane * 4) = make_uint4(vb[b][0], vb[b][1], vb[b][2], vb[b][3]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -548,6 +580,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             const bool store = r < t.rows_store && !DGB_SKIP(p, 32);
             const long long row = static_cast<long long>(t.row_start) + r;
             if (store) {
+                if constexpr (kKind == kKindNvfp4) {
+                    // fold the two FP32 per-tensor scales into the accumulator
+                    const float alpha = __ldg(p.a_scale) * __ldg(p.b_scales + t.group);
+#pragma unroll
+                    for (int i = 0; i < kCols; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+                }
                 if constexpr (EPI == kEpiBF16 || EPI == kEpiF32) {
                     const long long col0 = static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
                     if constexpr (EPI == kEpiF32) {
@@ -564,6 +602,49 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 2]), __uint_as_float(acc[i * 8 + 3])),
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 4]), __uint_as_float(acc[i * 8 + 5])),
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 6]), __uint_as_float(acc[i * 8 + 7])));
+                    }
+                } else if constexpr (EPI == kEpiSwiGLUNvfp4) {
+                    // Same column order as below; the 32 outputs of a gate/up pair are requantised to NVFP4: two
+                    // UE4M3 block scales (16 outputs each) against the calibrated per-tensor scale out_scale[0].
+                    const float w = p.row_weight != nullptr ? __ldg(p.row_weight + row) : 1.0f;
+                    const float s_out = __ldg(p.out_scale);
+#pragma unroll
+                    for (int c = 0; c < kCols / 64; ++c) {
+                        float o[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float gv = bf16_round(__uint_as_float(acc[c * 64 + i]));
+                            float uv = bf16_round(__uint_as_float(acc[c * 64 + 32 + i]));
+                            if (p.clamp > 0.0f) {
+                                gv = fminf(gv, p.clamp);
+                                uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                            }
+                            const float silu = p.fast_math ? gv * rcp_approx(1.0f + __expf(-gv))
+                                                           : gv / (1.0f + expf(-gv));
+                            o[i] = silu * uv * w;
+                        }
+                        const int j = t.n_block * (BLOCK_N / 2) + static_cast<int>(half) * (kCols / 2) + c * 32;
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            float amax = 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(o[h * 16 + i]));
+                            const uint32_t sf_byte = e4m3_byte(amax / 6.0f / s_out);
+                            const float factor = e4m3_to_float(sf_byte) * s_out;
+                            uint32_t lo = 0, hi = 0;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                lo |= (factor > 0.0f ? e2m1_code(o[h * 16 + i] / factor) : 0u) << (4 * i);
+                                hi |= (factor > 0.0f ? e2m1_code(o[h * 16 + 8 + i] / factor) : 0u) << (4 * i);
+                            }
+                            packed[h * 2] = lo;
+                            packed[h * 2 + 1] = hi;
+                            const int jb = j + h * 16;
+                            p.act_sf[(static_cast<long long>(jb / 64) * p.act_sf_k_stride + row) * 4 + ((jb / 16) & 3)] =
+                                static_cast<unsigned char>(sf_byte);
+                        }
+                        st_global_v4(p.act_q + row * p.act_q_row_stride + j / 2, packed[0], packed[1], packed[2], packed[3]);
                     }
                 } else {
                     // Columns of a tile: [gate j..j+31 | up j..j+31 | gate j+32.. | up j+32.. | ...]; this thread holds

@@ -13,6 +13,8 @@
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 namespace dgb {
@@ -359,6 +361,23 @@ __device__ __forceinline__ float rcp_approx(float x) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
+}
+
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+    // thresholds between {0, .5, 1, 1.5, 2, 3, 4, 6}; a value on a threshold rounds down; -0 encodes as +0
+    const float a = fabsf(v);
+    uint32_t code = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+    if (v < 0.0f && code != 0) code |= 8u;
+    return code;
+}
+
+// E4M3 round-to-nearest-even with saturation at 448, as a byte and back (UE4M3 block scales are non-negative E4M3).
+__device__ __forceinline__ uint32_t e4m3_byte(float x) {
+    return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+    return __half2float(__half(h));
 }
 
 // Programmatic dependent launch: wait for the preceding kernel's memory to be visible / let the next one start.

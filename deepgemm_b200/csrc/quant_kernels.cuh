@@ -28,14 +28,6 @@ __device__ __forceinline__ uint32_t ue8m0_ceil_bits(float x) {
     return min(max(e, 1u), 254u);
 }
 
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-    // thresholds between {0, .5, 1, 1.5, 2, 3, 4, 6}; a value on a threshold rounds down; -0 encodes as +0
-    const float a = fabsf(v);
-    uint32_t code = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
-    if (v < 0.0f && code != 0) code |= 8u;
-    return code;
-}
-
 struct CastParams {
     const __nv_bfloat16* x;
     long long x_row_stride;  // elements
@@ -163,6 +155,100 @@ __global__ void __launch_bounds__(256) dgb200_pack_sf_kernel(const PackSfParams 
             }
         }
         p.out[(static_cast<long long>(g) * packed_k + kp) * p.aligned_mn + row] = packed;
+    }
+}
+
+}  // namespace dgb
+
+namespace dgb {
+
+// ------------------------------------------------------------------------------------------------------------------
+// NVFP4 quantisation (no reference counterpart: the reference has no NVFP4 code; format and rounding rules are stated
+// in oracle/nvfp4.py): value = e2m1 * ue4m3(block of 16) * fp32 per-tensor scale.
+// ------------------------------------------------------------------------------------------------------------------
+
+// out[0] (as int bits of a non-negative float) = max(out[0], amax of this CTA's elements); out must start at 0.
+__global__ void __launch_bounds__(256)
+dgb200_amax_kernel(const __nv_bfloat16* __restrict__ x, long long row_stride, int rows, int k, float* out) {
+    float amax = 0.0f;
+    const long long vec_per_row = k / 8;
+    const long long total = static_cast<long long>(rows) * vec_per_row;
+    for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
+        const long long r = i / vec_per_row, c = i - r * vec_per_row;
+        const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(x + r * row_stride) + c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            amax = fmaxf(amax, fabsf(__uint_as_float(w[j] << 16)));
+            amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xffff0000u)));
+        }
+    }
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(amax));
+}
+
+// amax -> per-tensor scale amax / (6 * 448), 1 for an all-zero tensor
+__global__ void dgb200_finish_tensor_scale_kernel(float* out) {
+    const float amax = out[0];
+    out[0] = amax > 0.0f ? amax / (6.0f * 448.0f) : 1.0f;
+}
+
+struct CastNvfp4Params {
+    const __nv_bfloat16* x;
+    long long x_row_stride;     // elements
+    unsigned char* q;           // packed e2m1 [rows, k / 2]
+    long long q_row_stride;     // bytes
+    const float* tensor_scale;  // device scalar
+    uint32_t* sf_packed;        // int (kq, row) at sf_packed[kq * sf_k_stride + row * sf_row_stride]; kq = K / 64 index,
+    long long sf_k_stride, sf_row_stride;  // byte j of an int = the UE4M3 scale of K block (16 elements) 4 kq + j
+    int rows, k;
+};
+
+// Same tiling as dgb200_cast_rows_kernel: 32 rows x 512 columns per CTA, a lane owns 16 consecutive elements, which is
+// exactly one NVFP4 block.
+__global__ void __launch_bounds__(256) dgb200_cast_rows_nvfp4_kernel(const CastNvfp4Params p) {
+    __shared__ uint8_t sf_stage[32][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = blockIdx.x * 512, row0 = blockIdx.y * 32;
+    const int col = col0 + lane * 16;
+    const float s_t = __ldg(p.tensor_scale);
+    for (int i = threadIdx.x; i < 32 * 32; i += 256) (&sf_stage[0][0])[i] = 0;
+    __syncthreads();
+#pragma unroll 1
+    for (int rr = 0; rr < 4; ++rr) {
+        const int row = row0 + warp * 4 + rr;
+        if (row >= p.rows) break;
+        if (col >= p.k) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.x_row_stride + col);
+        const uint4 r0 = ld_global_nc_v4(src), r1 = ld_global_nc_v4(src + 1);
+        const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        float v[16];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+        }
+        const uint32_t sf_byte = e4m3_byte(amax / 6.0f / s_t);
+        const float factor = e4m3_to_float(sf_byte) * s_t;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo |= (factor > 0.0f ? e2m1_code(v[i] / factor) : 0u) << (4 * i);
+            hi |= (factor > 0.0f ? e2m1_code(v[8 + i] / factor) : 0u) << (4 * i);
+        }
+        *reinterpret_cast<uint2*>(p.q + static_cast<long long>(row) * p.q_row_stride + col / 2) = make_uint2(lo, hi);
+        sf_stage[warp * 4 + rr][lane] = static_cast<uint8_t>(sf_byte);
+    }
+    __syncthreads();
+    const int num_packed = (p.k / 16 + 3) / 4;
+    for (int i = threadIdx.x; i < 8 * 32; i += 256) {
+        const int kq_local = i >> 5, r = i & 31;
+        const int kq = col0 / 64 + kq_local;
+        if (row0 + r < p.rows && kq < num_packed)
+            p.sf_packed[static_cast<long long>(kq) * p.sf_k_stride + static_cast<long long>(row0 + r) * p.sf_row_stride] =
+                *reinterpret_cast<const uint32_t*>(&sf_stage[r][kq_local * 4]);
     }
 }
 

@@ -122,6 +122,30 @@ int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, 
                                              const int32_t* psum_layout, int32_t num_psum_groups,
                                              int32_t psum_alignment, void* stream);
 
+/* ---- NVFP4 variant (packed E2M1, one UE4M3 scale per 16 elements, one FP32 scale per tensor). The reference has no
+ * NVFP4 code; these entry points have no counterpart there. Format and rounding: oracle/nvfp4.py.
+ * Packed scale layout: int32, byte j of int (kq, row) = scale of the 16-element K block 4 kq + j. */
+
+/* out_scale[0] = amax(x) / (6 * 448) (1.0 for an all-zero tensor): the per-tensor scale of the quantiser below. */
+int dgb200_nvfp4_tensor_scale(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, float* out_scale, void* stream);
+
+/* BF16 rows -> packed E2M1 [rows, k/2] + UE4M3 block scales: sf = e4m3_rn(amax16 / 6 / tensor_scale), saturating at 448;
+ * codes of x / (float(sf) * tensor_scale) with the E2M1 thresholds of dgb200_per_token_cast_to_fp4. k % 64 == 0.
+ * sf_packed strides as in dgb200_per_token_cast_to_fp8 ((align(rows, 4), 1) = MN-major for the GEMM). */
+int dgb200_per_token_cast_to_nvfp4(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, const float* tensor_scale,
+                                   void* q, int64_t q_row_stride, void* sf_packed, int64_t sf_k_stride,
+                                   int64_t sf_row_stride, void* stream);
+
+/* D[m, :] = a_scale[0] * b_scales[group(m)] * (A[m, :] . B[group(m)]^T with block scales), FP4 x FP4
+ * (tcgen05 kind::mxf4nvf4, scale_vec::4X). a packed e2m1 [m, k/2]; b packed e2m1 [G, n, k/2]; sfa / sfb packed UE4M3
+ * int32 MN-major ([k/64][align(m,4)] and [G][k/64][align(n,4)]); a_scale, b_scales device floats. k % 256 == 0. */
+int dgb200_m_grouped_nvfp4_gemm_nt_contiguous(
+    const void* a, const void* sfa, int64_t sfa_k_stride, const float* a_scale,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride, const float* b_scales,
+    void* d, int64_t d_row_stride, const int32_t* grouped_layout,
+    int32_t m, int32_t n, int32_t k, int32_t num_groups, int32_t d_is_fp32,
+    int32_t layout_kind, int32_t alignment, void* stream);
+
 /* Router used by the benchmark layer: top-k of the logits (descending, ties to the lower expert index), weights =
  * sigmoid(logit) renormalised to sum to one. No reference counterpart (its tests call torch.topk,
  * tests/test_mega_moe.py:124-125).  logits float [tokens, experts]; topk_idx int64, topk_weights float [tokens, topk]. */
