@@ -24,8 +24,16 @@ from .mega import (  # noqa: F401
     get_block_m_for_mega_moe,
     get_symm_buffer_for_mega_moe,
     get_token_alignment_for_mega_moe,
+    nvfp4_mega_moe,
     route_sigmoid_topk,
     transform_weights_for_mega_moe,
+)
+from .nvfp4 import (  # noqa: F401
+    m_grouped_nvfp4_gemm_nt_contiguous,
+    nvfp4_tensor_scale,
+    pack_nvfp4_sf_mn_major,
+    per_token_cast_to_nvfp4,
+    per_token_cast_to_nvfp4_into,
 )
 from .runtime import (  # noqa: F401
     get_mk_alignment_for_contiguous_layout,

@@ -213,12 +213,27 @@ struct MegaLayout {
     int num_chunks, num_local_experts;
 };
 
-int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, MegaLayout* out) {
+// Quantisation of the layer: the FP8 x MXFP4 path needs nothing beyond the tensors; the NVFP4 path carries the
+// per-tensor FP32 scales (device pointers; x_scale and act_scale hold one value and must be equal on every rank).
+struct LayerQuant {
+    int kind = kKindFp8Fp4;
+    const float* x_scale = nullptr;    // scale of the NVFP4 input rows
+    const float* act_scale = nullptr;  // calibrated scale the post-SwiGLU activations are quantised against
+    const float* l1_scales = nullptr;  // [local experts] scales of the gate/up weights
+    const float* l2_scales = nullptr;  // [local experts] scales of the down weights
+};
+
+// Bytes of one quantised activation row of `width` elements, and packed scale ints (4 scale bytes each) per row.
+inline long long act_row_bytes(int kind, int width) { return kind == kKindNvfp4 ? width / 2 : width; }
+inline int sf_ints_per_row(int kind, int width) { return kind == kKindNvfp4 ? width / 64 : width / 128; }
+
+int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, MegaLayout* out) {
     DGB_REQUIRE(num_ranks >= 1 && num_ranks <= kMaxRanks, "num_ranks must be in [1, %d]", kMaxRanks);
     DGB_REQUIRE(num_experts > 0 && num_experts % num_ranks == 0, "num_experts must be a positive multiple of num_ranks");
     DGB_REQUIRE(max_tokens > 0 && topk > 0 && topk <= 32, "need max tokens > 0 and 0 < topk <= 32");
-    DGB_REQUIRE(hidden % 128 == 0 && inter % 128 == 0 && hidden > 0 && inter > 0,
-                "hidden and intermediate_hidden must be positive multiples of 128");
+    const int k_block = kind == kKindNvfp4 ? 256 : 128;
+    DGB_REQUIRE(hidden % k_block == 0 && inter % k_block == 0 && hidden > 0 && inter > 0,
+                "hidden and intermediate_hidden must be positive multiples of %d", k_block);
     MegaLayout l{};
     l.num_local_experts = num_experts / num_ranks;
     const long long active_topk = std::min(topk, l.num_local_experts);
@@ -231,8 +246,8 @@ int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, i
         off += (bytes + 1023) / 1024 * 1024;
         return at;
     };
-    l.x = take(static_cast<long long>(max_tokens) * hidden);
-    l.x_sf = take(static_cast<long long>(max_tokens) * (hidden / 128) * 4);
+    l.x = take(static_cast<long long>(max_tokens) * act_row_bytes(kind, hidden));
+    l.x_sf = take(static_cast<long long>(max_tokens) * sf_ints_per_row(kind, hidden) * 4);
     l.topk_idx = take(static_cast<long long>(max_tokens) * topk * 8);
     l.topk_weights = take(static_cast<long long>(max_tokens) * topk * 4);
     l.chunk_hist = take(static_cast<long long>(l.num_chunks) * num_experts * 4);
@@ -245,10 +260,10 @@ int make_mega_layout(int num_ranks, int num_experts, int max_tokens, int topk, i
     l.dest_row = take(static_cast<long long>(max_tokens) * topk * 4);
     l.src_of_row = take(l.max_rows * 4);
     l.row_weight = take(l.max_rows * 4);
-    l.l1_acts = take(l.max_rows * hidden);
-    l.l1_sf = take(l.max_rows * (hidden / 128) * 4);
-    l.l2_acts = take(l.max_rows * inter);
-    l.l2_sf = take(l.max_rows * (inter / 128) * 4);
+    l.l1_acts = take(l.max_rows * act_row_bytes(kind, hidden));
+    l.l1_sf = take(l.max_rows * sf_ints_per_row(kind, hidden) * 4);
+    l.l2_acts = take(l.max_rows * act_row_bytes(kind, inter));
+    l.l2_sf = take(l.max_rows * sf_ints_per_row(kind, inter) * 4);
     l.l2_out = take(l.max_rows * hidden * 2);
     l.total = off;
     *out = l;
@@ -290,20 +305,23 @@ int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, i
 
 
 // The two grouped GEMMs of the layer over this rank's expert-sorted rows (shared by the single-rank and the
-// expert-parallel paths): L1 writes FP8 activations + scales, L2 writes BF16 rows into l2_out in the same row order.
-int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
+// expert-parallel paths): L1 writes quantised activations + scales (FP8/UE8M0 or NVFP4/UE4M3), L2 writes BF16 rows
+// into l2_out in the same row order.
+int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
                     const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
                     cudaStream_t stream, int stage_event_base) {
     const int E = l.num_local_experts;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
+    const bool nvfp4 = quant.kind == kKindNvfp4;
     int rc = 0;
     {
         GemmCall c{};
+        c.kind = quant.kind;
         c.a = base + l.l1_acts;
         c.b = l1_w;
         c.a_rows_total = l.max_rows;
         c.b_is_fp4 = 1;
-        c.epilogue = kEpiSwiGLU;
+        c.epilogue = nvfp4 ? kEpiSwiGLUNvfp4 : kEpiSwiGLU;
         c.max_tiles = 0;
         c.sfa = base + l.l1_sf;
         c.sfb = l1_w_sf;
@@ -311,7 +329,7 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
         c.sfa_group_stride = 0;
         c.num_groups_a = 1;
         c.sfb_k_stride = 2 * intermediate_hidden;
-        c.sfb_group_stride = static_cast<long long>(hidden / 128) * 2 * intermediate_hidden;
+        c.sfb_group_stride = static_cast<long long>(sf_ints_per_row(quant.kind, hidden)) * 2 * intermediate_hidden;
         GemmParams& p = c.p;
         p.layout = expert_end;
         p.mode = kModePsum;
@@ -324,8 +342,11 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
         p.gran_b = 32;
         p.act_q = base + l.l2_acts;
         p.act_sf = base + l.l2_sf;
-        p.act_q_row_stride = intermediate_hidden;
+        p.act_q_row_stride = act_row_bytes(quant.kind, intermediate_hidden);
         p.act_sf_k_stride = l.max_rows;
+        p.a_scale = quant.x_scale;
+        p.b_scales = quant.l1_scales;
+        p.out_scale = quant.act_scale;
         p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
         p.fast_math = fast_math;
@@ -334,6 +355,7 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
     if ((rc = record_stage(stage_event_base, stream))) return rc;
     {
         GemmCall c{};
+        c.kind = quant.kind;
         c.a = base + l.l2_acts;
         c.b = l2_w;
         c.a_rows_total = l.max_rows;
@@ -346,7 +368,7 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
         c.sfa_group_stride = 0;
         c.num_groups_a = 1;
         c.sfb_k_stride = hidden;
-        c.sfb_group_stride = static_cast<long long>(intermediate_hidden / 128) * hidden;
+        c.sfb_group_stride = static_cast<long long>(sf_ints_per_row(quant.kind, intermediate_hidden)) * hidden;
         GemmParams& p = c.p;
         p.layout = expert_end;
         p.mode = kModePsum;
@@ -359,6 +381,8 @@ int run_layer_gemms(const MegaLayout& l, uint8_t* base, const void* l1_w, const 
         p.gran_b = 32;
         p.d = base + l.l2_out;
         p.d_row_stride = hidden;
+        p.a_scale = quant.act_scale;
+        p.b_scales = quant.l2_scales;
         if ((rc = run_gemm(c, stream))) return rc;
     }
     return record_stage(stage_event_base + 1, stream);
@@ -374,7 +398,7 @@ uint32_t next_barrier_epoch(const void* buffer) {
 
 constexpr long long kPeerWaitBudgetCycles = 20000000000ll;  // about 10 s: ranks may reach their first call seconds apart
 
-int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
                     int32_t* stats, uint8_t* base, const uint64_t* peer_buffer_ptrs, int rank, int num_ranks, int num_tokens,
                     int num_max_tokens_per_rank, int num_experts, int num_topk, int hidden, int intermediate_hidden,
                     float activation_clamp, int fast_math, cudaStream_t stream) {
@@ -410,7 +434,7 @@ int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* 
         if ((rc = record_stage(1, stream))) return rc;
         dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
             base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
-            hidden, l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row);
+            static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_ints_per_row(quant.kind, hidden), l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row);
     } else if ((rc = record_stage(1, stream))) {
         return rc;
     }
@@ -418,7 +442,7 @@ int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* 
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
     if ((rc = record_stage(2, stream))) return rc;
 
-    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
     if (rc) return rc;
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, static_cast<int>(epoch0 + 3), kPeerWaitBudgetCycles);
     if (num_tokens > 0)
@@ -428,6 +452,91 @@ int run_mega_moe_ep(const MegaLayout& l, void* y, const void* l1_w, const void* 
     return record_stage(5, stream);
 }
 
+
+// The whole layer on this rank (single rank: plan, gather, two GEMMs, combine; several ranks: run_mega_moe_ep).
+int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+                 int32_t* cumulative_local_expert_recv_stats, void* buffer, const uint64_t* peer_buffer_ptrs,
+                 int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
+                 int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                 float activation_clamp, int32_t fast_math, cudaStream_t stream) {
+    MegaLayout l;
+    int rc = make_mega_layout(quant.kind, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
+    if (rc) return rc;
+    DGB_REQUIRE(rank >= 0 && rank < num_ranks && peer_buffer_ptrs != nullptr &&
+                    peer_buffer_ptrs[rank] == reinterpret_cast<uint64_t>(buffer),
+                "rank / peer pointer table do not describe this buffer");
+    DGB_REQUIRE(num_tokens >= 0 && num_tokens <= num_max_tokens_per_rank, "num_tokens (%d) exceeds the buffer capacity (%d)",
+                num_tokens, num_max_tokens_per_rank);
+    DGB_REQUIRE(y != nullptr && l1_w != nullptr && l1_w_sf != nullptr && l2_w != nullptr && l2_w_sf != nullptr && buffer != nullptr,
+                "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 256 == 0, "buffer must be 256-byte aligned");
+    DGB_REQUIRE((2 * intermediate_hidden) % 128 == 0 && intermediate_hidden % 64 == 0, "intermediate_hidden must be a multiple of 64");
+    if (num_tokens == 0 && num_ranks == 1) return 0;
+
+    uint8_t* base = static_cast<uint8_t*>(buffer);
+    const int E = l.num_local_experts;
+    const int entries = num_tokens * num_topk;
+    const int chunks = (entries + kPlanChunk - 1) / kPlanChunk;
+    int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
+    int* expert_start = reinterpret_cast<int*>(base + l.expert_start);
+    int* expert_end = reinterpret_cast<int*>(base + l.expert_end);
+    int* total_rows = reinterpret_cast<int*>(base + l.total_rows);
+    int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
+    int* src_of_row = reinterpret_cast<int*>(base + l.src_of_row);
+    float* row_weight = reinterpret_cast<float*>(base + l.row_weight);
+    const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
+    const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
+
+    struct ClearEvents { ~ClearEvents() { g_num_stage_events = 0; } } clear_events_on_exit;
+    if ((rc = record_stage(0, stream))) return rc;
+    if (num_ranks > 1)
+        return run_mega_moe_ep(quant, l, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, base, peer_buffer_ptrs, rank,
+                               num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden,
+                               intermediate_hidden, activation_clamp, fast_math, stream);
+
+    // 1. dispatch plan: stable counting sort of the (token, k) entries by expert
+    DGB_CUDA(cudaMemsetAsync(src_of_row, 0xff, l.max_rows * 4, stream));
+    dgb200_moe_count_kernel<<<chunks, kPlanChunk, E * sizeof(int), stream>>>(topk_idx, entries, 0, E, chunk_hist);
+    dgb200_moe_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, E, kSegmentAlignment, expert_start, expert_end,
+                                                    total_rows, cumulative_local_expert_recv_stats);
+    dgb200_moe_assign_kernel<<<chunks, kPlanChunk, 32 * E, stream>>>(topk_idx, topk_weights, entries, 0, E, chunk_hist,
+                                                                    expert_start, dest_row, src_of_row, row_weight);
+    DGB_CUDA(cudaGetLastError());
+
+    if ((rc = record_stage(1, stream))) return rc;
+    // 2. gather quantised rows + scales into expert-sorted order
+    const long long upper_rows = std::min<long long>(l.max_rows, static_cast<long long>(entries) + static_cast<long long>(E) * kSegmentAlignment);
+    const int gather_blocks = static_cast<int>((upper_rows + 31) / 32);
+    const int sf_per_row = sf_ints_per_row(quant.kind, hidden);
+    dgb200_moe_gather_kernel<<<gather_blocks, 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
+        base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk,
+        static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, base + l.l1_acts, reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
+    DGB_CUDA(cudaGetLastError());
+
+    if ((rc = record_stage(2, stream))) return rc;
+    // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
+    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    if (rc) return rc;
+    // 5. combine: y[t] = sum over the top-k slots of the rows the L2 GEMM wrote
+    PeerTable self{};
+    self.p[0] = reinterpret_cast<unsigned long long>(base);
+    dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
+        self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden, static_cast<__nv_bfloat16*>(y));
+    DGB_CUDA(cudaGetLastError());
+    return record_stage(5, stream);
+}
+
+// Byte offsets of the buffer regions, in the order the C header documents.
+int export_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, int64_t* out) {
+    DGB_REQUIRE(out != nullptr, "null output");
+    MegaLayout l;
+    const int rc = make_mega_layout(kind, num_ranks, num_experts, max_tokens, topk, hidden, inter, &l);
+    if (rc) return rc;
+    const long long fields[16] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+                                  l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight};
+    for (int i = 0; i < 16; ++i) out[i] = fields[i];
+    return 0;
+}
 
 // --------------------------------------------------------------------------------------------------------------
 // Scratch of the allocation-free dispatch-plan entry point: per-chunk expert histograms (the same role the
@@ -675,99 +784,45 @@ int dgb200_get_token_alignment_for_mega_moe(void) { return 128; }
 int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
                                                int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                                                int64_t* out) {
-    DGB_REQUIRE(out != nullptr, "null output");
-    MegaLayout l;
-    const int rc = make_mega_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
-    if (rc) return rc;
-    out[0] = l.total;
-    out[1] = l.x;
-    out[2] = l.x_sf;
-    out[3] = l.topk_idx;
-    out[4] = l.topk_weights;
-    out[5] = l.l1_acts;
-    out[6] = l.l1_sf;
-    out[7] = l.l2_acts;
-    out[8] = l.l2_sf;
-    out[9] = l.max_rows;
-    out[10] = l.dest_row;
-    out[11] = l.src_of_row;
-    out[12] = l.expert_start;
-    out[13] = l.expert_end;
-    out[14] = l.l2_out;
-    out[15] = l.row_weight;
-    return 0;
+    return export_mega_layout(kKindFp8Fp4, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                              intermediate_hidden, out);
+}
+
+int dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                                     int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                                     int64_t* out) {
+    return export_mega_layout(kKindNvfp4, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                              intermediate_hidden, out);
 }
 
 int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
                             int32_t* cumulative_local_expert_recv_stats, void* buffer, const uint64_t* peer_buffer_ptrs,
                             int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
                             int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
-                            float activation_clamp, int32_t fast_math, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    MegaLayout l;
-    int rc = make_mega_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
-    if (rc) return rc;
-    DGB_REQUIRE(rank >= 0 && rank < num_ranks && peer_buffer_ptrs != nullptr &&
-                    peer_buffer_ptrs[rank] == reinterpret_cast<uint64_t>(buffer),
-                "rank / peer pointer table do not describe this buffer");
-    DGB_REQUIRE(num_tokens >= 0 && num_tokens <= num_max_tokens_per_rank, "num_tokens (%d) exceeds the buffer capacity (%d)",
-                num_tokens, num_max_tokens_per_rank);
-    DGB_REQUIRE(y != nullptr && l1_w != nullptr && l1_w_sf != nullptr && l2_w != nullptr && l2_w_sf != nullptr && buffer != nullptr,
-                "null tensor pointer");
-    DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 256 == 0, "buffer must be 256-byte aligned");
-    DGB_REQUIRE((2 * intermediate_hidden) % 128 == 0 && intermediate_hidden % 64 == 0, "intermediate_hidden must be a multiple of 64");
-    if (num_tokens == 0 && num_ranks == 1) return 0;
+                            float activation_clamp, int32_t fast_math, void* stream) {
+    LayerQuant quant;
+    return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
+                        num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
+                        activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
+}
 
-    uint8_t* base = static_cast<uint8_t*>(buffer);
-    const int E = l.num_local_experts;
-    const int entries = num_tokens * num_topk;
-    const int chunks = (entries + kPlanChunk - 1) / kPlanChunk;
-    int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
-    int* expert_start = reinterpret_cast<int*>(base + l.expert_start);
-    int* expert_end = reinterpret_cast<int*>(base + l.expert_end);
-    int* total_rows = reinterpret_cast<int*>(base + l.total_rows);
-    int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
-    int* src_of_row = reinterpret_cast<int*>(base + l.src_of_row);
-    float* row_weight = reinterpret_cast<float*>(base + l.row_weight);
-    const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
-    const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
-
-    struct ClearEvents { ~ClearEvents() { g_num_stage_events = 0; } } clear_events_on_exit;
-    if ((rc = record_stage(0, stream))) return rc;
-    if (num_ranks > 1)
-        return run_mega_moe_ep(l, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, base, peer_buffer_ptrs, rank,
-                               num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden,
-                               intermediate_hidden, activation_clamp, fast_math, stream);
-
-    // 1. dispatch plan: stable counting sort of the (token, k) entries by expert
-    DGB_CUDA(cudaMemsetAsync(src_of_row, 0xff, l.max_rows * 4, stream));
-    dgb200_moe_count_kernel<<<chunks, kPlanChunk, E * sizeof(int), stream>>>(topk_idx, entries, 0, E, chunk_hist);
-    dgb200_moe_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, E, kSegmentAlignment, expert_start, expert_end,
-                                                    total_rows, cumulative_local_expert_recv_stats);
-    dgb200_moe_assign_kernel<<<chunks, kPlanChunk, 32 * E, stream>>>(topk_idx, topk_weights, entries, 0, E, chunk_hist,
-                                                                    expert_start, dest_row, src_of_row, row_weight);
-    DGB_CUDA(cudaGetLastError());
-
-    if ((rc = record_stage(1, stream))) return rc;
-    // 2. gather FP8 rows + scales into expert-sorted order
-    const long long upper_rows = std::min<long long>(l.max_rows, static_cast<long long>(entries) + static_cast<long long>(E) * kSegmentAlignment);
-    const int gather_blocks = static_cast<int>((upper_rows + 31) / 32);
-    dgb200_moe_gather_kernel<<<gather_blocks, 256, (hidden / 128) * 33 * sizeof(unsigned), stream>>>(
-        base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk, hidden,
-        base + l.l1_acts, reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
-    DGB_CUDA(cudaGetLastError());
-
-    if ((rc = record_stage(2, stream))) return rc;
-    // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
-    rc = run_layer_gemms(l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
-    if (rc) return rc;
-    // 5. combine: y[t] = sum over the top-k slots of the rows the L2 GEMM wrote
-    PeerTable self{};
-    self.p[0] = reinterpret_cast<unsigned long long>(base);
-    dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
-        self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden, static_cast<__nv_bfloat16*>(y));
-    DGB_CUDA(cudaGetLastError());
-    return record_stage(5, stream);
+int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const float* l1_w_scales, const void* l2_w,
+                          const void* l2_w_sf, const float* l2_w_scales, const float* x_scale, const float* act_scale,
+                          int32_t* cumulative_local_expert_recv_stats, void* buffer, const uint64_t* peer_buffer_ptrs,
+                          int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
+                          int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                          float activation_clamp, int32_t fast_math, void* stream) {
+    DGB_REQUIRE(l1_w_scales != nullptr && l2_w_scales != nullptr && x_scale != nullptr && act_scale != nullptr,
+                "null per-tensor scale pointer");
+    LayerQuant quant;
+    quant.kind = kKindNvfp4;
+    quant.x_scale = x_scale;
+    quant.act_scale = act_scale;
+    quant.l1_scales = l1_w_scales;
+    quant.l2_scales = l2_w_scales;
+    return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
+                        num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
+                        activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
 }
 
 int dgb200_set_mega_moe_stage_events(void* const* events, int32_t count) {

@@ -124,27 +124,29 @@ dgb200_moe_assign_kernel(const long long* __restrict__ topk_idx, const float* __
     row_weight[dest] = topk_weights[i];
 }
 
-// Gathers FP8 token rows and their packed scales into expert-sorted order. One CTA per 32 destination rows.
-//   x      e4m3 [tokens, hidden]           x_sf  int32 [tokens, hidden / 128] (token-major, 4 UE8M0 bytes per int)
-//   acts   e4m3 [rows, hidden]             acts_sf int32 MN-major: int (kp, row) at acts_sf[kp * sf_k_stride + row]
+// Gathers quantised token rows and their packed scales into expert-sorted order. One CTA per 32 destination rows.
+//   x      [tokens, row_bytes] bytes (e4m3: hidden; packed e2m1: hidden / 2)
+//   x_sf   int32 [tokens, sf_per_row] token-major, 4 scale bytes per int (UE8M0 per 32: hidden / 128 ints;
+//          UE4M3 per 16: hidden / 64 ints)
+//   acts   [rows, row_bytes]               acts_sf int32 MN-major: int (kp, row) at acts_sf[kp * sf_k_stride + row]
 // Rows whose src_of_row is negative (segment padding) are left untouched.
 __global__ void __launch_bounds__(256)
 dgb200_moe_gather_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
-                         const int* __restrict__ src_of_row, const int* __restrict__ total_rows, int topk, int hidden,
-                         unsigned char* __restrict__ acts, unsigned* __restrict__ acts_sf, long long sf_k_stride) {
-    extern __shared__ unsigned sf_tile[];  // [hidden / 128][33]
+                         const int* __restrict__ src_of_row, const int* __restrict__ total_rows, int topk, int row_bytes,
+                         int sf_per_row, unsigned char* __restrict__ acts, unsigned* __restrict__ acts_sf,
+                         long long sf_k_stride) {
+    extern __shared__ unsigned sf_tile[];  // [sf_per_row][33]
     const int row0 = blockIdx.x * 32;
     if (row0 >= total_rows[0]) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int sf_per_row = hidden / 128;
     for (int rr = 0; rr < 4; ++rr) {
         const int r = warp * 4 + rr;
         const int src = src_of_row[row0 + r];
         if (src < 0) continue;
         const int token = src / topk;
-        const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * hidden);
-        uint4* to = reinterpret_cast<uint4*>(acts + static_cast<long long>(row0 + r) * hidden);
-        for (int c = lane; c < hidden / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
+        const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes);
+        uint4* to = reinterpret_cast<uint4*>(acts + static_cast<long long>(row0 + r) * row_bytes);
+        for (int c = lane; c < row_bytes / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
         for (int c = lane; c < sf_per_row; c += 32) sf_tile[c * 33 + r] = x_sf[static_cast<long long>(token) * sf_per_row + c];
     }
     __syncthreads();
@@ -400,8 +402,8 @@ dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries,
 __global__ void __launch_bounds__(256)
 dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
                       const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights,
-                      const int* __restrict__ dest_row, int num_entries, int topk, int hidden, int experts_per_rank,
-                      int my_rank, int entries_per_rank, const PeerTable peers,
+                      const int* __restrict__ dest_row, int num_entries, int topk, int row_bytes, int sf_per_row,
+                      int experts_per_rank, int my_rank, int entries_per_rank, const PeerTable peers,
                       long long acts_offset, long long sf_offset, long long sf_k_stride, long long weight_offset,
                       long long src_offset) {
     const int lane = threadIdx.x & 31;
@@ -412,11 +414,10 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
     const int owner = static_cast<int>(topk_idx[entry]) / experts_per_rank;
     const int token = entry / topk;
     const unsigned long long base = peers.p[owner];
-    const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * hidden);
-    uint4* to = reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * hidden);
-    for (int c = lane; c < hidden / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
+    const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes);
+    uint4* to = reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * row_bytes);
+    for (int c = lane; c < row_bytes / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
     unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
-    const int sf_per_row = hidden / 128;
     for (int c = lane; c < sf_per_row; c += 32)
         sf[static_cast<long long>(c) * sf_k_stride + dest] = x_sf[static_cast<long long>(token) * sf_per_row + c];
     if (lane == 0) {

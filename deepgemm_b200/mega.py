@@ -27,9 +27,15 @@ def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_pe
     return 128
 
 
-def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden):
+_MMA_TYPES = ('fp8xfp4', 'nvfp4xnvfp4')
+
+
+def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+                   mma_type='fp8xfp4'):
     words = (ctypes.c_int64 * _NUM_LAYOUT_WORDS)()
-    _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe(
+    fn = (_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe if mma_type == 'fp8xfp4' else
+          _lib.lib().dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe)
+    _lib.check(fn(
         num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
         ctypes.cast(words, ctypes.c_void_p)))
     keys = ['total', 'x', 'x_sf', 'topk_idx', 'topk_weights', 'l1_acts', 'l1_sf', 'l2_acts', 'l2_sf', 'max_rows',
@@ -46,8 +52,8 @@ class SymmBuffer:
                  activation: str = 'swiglu'):
         if activation != 'swiglu':
             raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
-        if mma_type != 'fp8xfp4':
-            raise RuntimeError(f'Only the `fp8xfp4` MMA type is built, got `{mma_type}`')
+        if mma_type not in _MMA_TYPES:
+            raise RuntimeError(f'MMA type must be one of {_MMA_TYPES}, got `{mma_type}`')
         if num_shared_experts != 0:
             raise RuntimeError('shared experts are not built')
         self.group = group
@@ -56,8 +62,9 @@ class SymmBuffer:
         self.num_experts, self.num_topk = num_experts, num_topk
         self.num_max_tokens_per_rank = num_max_tokens_per_rank
         self.hidden, self.intermediate_hidden = hidden, intermediate_hidden
+        self.mma_type = mma_type
         self.layout = _buffer_layout(self.num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
-                                     intermediate_hidden)
+                                     intermediate_hidden, mma_type)
         num_bytes = self.layout['total']
         if self.num_ranks == 1:
             self.buffer = torch.empty(num_bytes, dtype=torch.int8, device='cuda')
@@ -74,8 +81,12 @@ class SymmBuffer:
         t, lay = num_max_tokens_per_rank, self.layout
         def view(offset, nbytes, dtype, shape):
             return self.buffer[offset:offset + nbytes].view(dtype).view(shape)
-        self.x = view(lay['x'], t * hidden, torch.float8_e4m3fn, (t, hidden))
-        self.x_sf = view(lay['x_sf'], t * (hidden // 128) * 4, torch.int32, (t, hidden // 128))
+        if mma_type == 'fp8xfp4':
+            self.x = view(lay['x'], t * hidden, torch.float8_e4m3fn, (t, hidden))
+            self.x_sf = view(lay['x_sf'], t * (hidden // 128) * 4, torch.int32, (t, hidden // 128))
+        else:  # packed E2M1 rows, four UE4M3 block scales (64 K elements) per int
+            self.x = view(lay['x'], t * hidden // 2, torch.int8, (t, hidden // 2))
+            self.x_sf = view(lay['x_sf'], t * (hidden // 64) * 4, torch.int32, (t, hidden // 64))
         self.topk_idx = view(lay['topk_idx'], t * num_topk * 8, torch.int64, (t, num_topk))
         self.topk_weights = view(lay['topk_weights'], t * num_topk * 4, torch.float32, (t, num_topk))
 
@@ -121,18 +132,19 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     if activation != 'swiglu':
         raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
     if not isinstance(l1_weights, tuple):
-        raise RuntimeError('BF16 weights are not built; pass (packed FP4 weights, packed UE8M0 scale factors)')
-    return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), _interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE)), \
-        (l2_weights[0], l2_weights[1])
+        raise RuntimeError('BF16 weights are not built; pass (packed FP4 weights, packed scale factors[, tensor scales])')
+    # NVFP4 weights carry a third element, the per-expert FP32 scales, which no reordering touches
+    return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), _interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE)) + \
+        tuple(l1_weights[2:]), tuple(l2_weights)
 
 
-def _check_weight(w, sf, num_groups, n, k, name):
+def _check_weight(w, sf, num_groups, n, k, name, k_per_int=128):
     if not (w.is_cuda and w.dtype == torch.int8 and w.is_contiguous() and tuple(w.shape) == (num_groups, n, k // 2)):
         raise RuntimeError(f'{name} must be a contiguous CUDA int8 tensor of shape {(num_groups, n, k // 2)}')
-    if not (sf.dtype == torch.int32 and tuple(sf.shape) == (num_groups, n, k // 128) and sf.stride(1) == 1 and
+    if not (sf.dtype == torch.int32 and tuple(sf.shape) == (num_groups, n, k // k_per_int) and sf.stride(1) == 1 and
             sf.stride(2) == align(n, 4) and sf.stride(0) == sf.stride(2) * sf.shape[2]):
-        raise RuntimeError(f'{name} scale factors must be packed UE8M0 int32 {(num_groups, n, k // 128)}, MN-major '
-                           '(use transform_sf_into_required_layout)')
+        raise RuntimeError(f'{name} scale factors must be packed int32 {(num_groups, n, k // k_per_int)}, MN-major '
+                           '(use transform_sf_into_required_layout / pack_nvfp4_sf_mn_major)')
 
 
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor],
@@ -150,6 +162,8 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
     if shared_l1_weights is not None or shared_l2_weights is not None:
         raise RuntimeError('shared experts are not built')
     b = sym_buffer
+    if b.mma_type != 'fp8xfp4':
+        raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
     num_local = b.num_experts // b.num_ranks
     _check_weight(l1_weights[0], l1_weights[1], num_local, 2 * b.intermediate_hidden, b.hidden, 'l1_weights')
     _check_weight(l2_weights[0], l2_weights[1], num_local, b.hidden, b.intermediate_hidden, 'l2_weights')
@@ -166,6 +180,44 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
             ctypes.cast(ptrs, ctypes.c_void_p), b.rank, b.num_ranks, y.size(0), b.num_max_tokens_per_rank,
             b.num_experts, b.num_topk, b.hidden, b.intermediate_hidden,
             float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
+            _lib.current_stream_ptr()))
+
+
+def nvfp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor],
+                   l2_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
+                   x_scale: torch.Tensor, act_scale: torch.Tensor,
+                   cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                   activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
+    """The layer of ``fp8_fp4_mega_moe`` with NVFP4 activations and weights (no reference counterpart).
+
+    ``sym_buffer`` must have been created with ``mma_type='nvfp4xnvfp4'``; the caller writes packed E2M1 rows and
+    their UE4M3 scales into ``x`` / ``x_sf`` (``per_token_cast_to_nvfp4_into``). Weights are
+    (int8 [E, N, K / 2], packed MN-major int32 scales [E, N, K / 64], FP32 [E] tensor scales), L1 passed through
+    ``transform_weights_for_mega_moe``. ``x_scale`` is the FP32 scalar x was quantised against and must be the same
+    on every rank; ``act_scale`` is the calibrated FP32 scalar the post-SwiGLU activations are quantised against."""
+    b = sym_buffer
+    if b.mma_type != 'nvfp4xnvfp4':
+        raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
+    num_local = b.num_experts // b.num_ranks
+    _check_weight(l1_weights[0], l1_weights[1], num_local, 2 * b.intermediate_hidden, b.hidden, 'l1_weights', 64)
+    _check_weight(l2_weights[0], l2_weights[1], num_local, b.hidden, b.intermediate_hidden, 'l2_weights', 64)
+    for t, count, name in ((l1_weights[2], num_local, 'l1 tensor scales'), (l2_weights[2], num_local, 'l2 tensor scales'),
+                           (x_scale, 1, 'x_scale'), (act_scale, 1, 'act_scale')):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.numel() == count and t.is_contiguous()):
+            raise RuntimeError(f'{name} must be a contiguous CUDA float32 tensor of {count} element(s)')
+    if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
+        raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
+    stats = cumulative_local_expert_recv_stats
+    if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == num_local and stats.is_contiguous()):
+        raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
+    ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.lib().dgb200_nvfp4_mega_moe(
+            p(y), p(l1_weights[0]), p(l1_weights[1]), p(l1_weights[2]), p(l2_weights[0]), p(l2_weights[1]),
+            p(l2_weights[2]), p(x_scale), p(act_scale), p(stats), p(b.buffer), ctypes.cast(ptrs, ctypes.c_void_p),
+            b.rank, b.num_ranks, y.size(0), b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden,
+            b.intermediate_hidden, float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
             _lib.current_stream_ptr()))
 
 

@@ -180,6 +180,29 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                             int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                             float activation_clamp, int32_t fast_math, void* stream);
 
+/* NVFP4 x NVFP4 form of the layer (no reference counterpart; the reference's layer is FP8 x MXFP4 only).
+ * Buffer layout: same out[16] fields as dgb200_get_symm_buffer_layout_for_mega_moe; the caller writes
+ * x (packed e2m1 [T, hidden / 2]) and x_sf (int32 [T, hidden / 64], four UE4M3 bytes per int, token-major).
+ * hidden and intermediate_hidden must be multiples of 256. */
+int dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                                     int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                                     int64_t* out);
+
+/* Same stages and argument meaning as dgb200_fp8_fp4_mega_moe with NVFP4 tensors:
+ *   l1_w packed e2m1 [E_local, 2 * inter, hidden / 2] (gate/up interleaved by 32), l1_w_sf packed UE4M3 int32
+ *   MN-major [E_local][hidden / 64][2 * inter], l1_w_scales float [E_local]; l2_w [E_local, hidden, inter / 2],
+ *   l2_w_sf [E_local][inter / 64][hidden], l2_w_scales float [E_local].
+ *   x_scale   device float: per-tensor scale the caller quantised x with; must hold the same value on every rank
+ *             (a calibrated input scale), because an expert's rows come from all ranks.
+ *   act_scale device float: calibrated per-tensor scale of the post-SwiGLU activations; the L1 epilogue quantises
+ *             against it (block scales saturate at 448) and the L2 GEMM multiplies by it. */
+int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const float* l1_w_scales, const void* l2_w,
+                          const void* l2_w_sf, const float* l2_w_scales, const float* x_scale, const float* act_scale,
+                          int32_t* cumulative_local_expert_recv_stats, void* buffer, const uint64_t* peer_buffer_ptrs,
+                          int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
+                          int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                          float activation_clamp, int32_t fast_math, void* stream);
+
 /* Dispatch plan for callers that cannot allocate device memory. It has no counterpart in the reference.
  * Some hosts of this library run it from places where cudaMalloc is off limits: inside a region whose memory is
  * owned by another allocator with a fixed pool, in a callback that must not synchronise the device, or in a service

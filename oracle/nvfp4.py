@@ -106,3 +106,22 @@ def moe_layer_nvfp4(x_q, x_sf, x_scale, topk_idx, topk_weights, l1_q, l1_sf, l1_
     for k in range(topk):
         y += torch.where(valid[:, k, None], slot_rows[:, k].float(), torch.zeros(()))
     return y.bfloat16()
+
+
+def calibrate_act_scale(x_q, x_sf, x_scale, topk_idx, topk_weights, l1_q, l1_sf, l1_scales, clamp: Optional[float] = None):
+    """Per-tensor scale of the post-SwiGLU activations over every routed (token, slot): amax / (6 * 448). Stands in
+    for the offline calibration an NVFP4 deployment does; the layer takes the result as an input."""
+    x = dequantize_nvfp4(x_q, x_sf, x_scale)
+    amax = torch.zeros(())
+    for e in range(l1_q.shape[0]):
+        tok, slot = torch.nonzero(topk_idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        acc1 = x[tok] @ dequantize_nvfp4(l1_q[e], l1_sf[e], l1_scales[e]).T
+        half = acc1.shape[1] // 2
+        gate, up = acc1[:, :half].bfloat16().float(), acc1[:, half:].bfloat16().float()
+        if clamp is not None:
+            gate, up = gate.clamp(max=clamp), up.clamp(min=-clamp, max=clamp)
+        act = gate / (1.0 + torch.exp(-gate)) * up * topk_weights[tok, slot].float().unsqueeze(1)
+        amax = torch.maximum(amax, act.abs().amax())
+    return torch.where(amax > 0, amax / (6.0 * 448.0), torch.ones(()))

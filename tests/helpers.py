@@ -59,3 +59,27 @@ def moe_case(tokens, hidden, inter, experts, topk, seed, masked_ratio=0.0, empty
         w = w.masked_fill(mask, 0.0)
     return dict(x=x, x_q=x_q, x_sf=x_sf, l1_q=l1_q, l1_sf=l1_sf, l2_q=l2_q, l2_sf=l2_sf, logits=logits,
                 topk_idx=idx, topk_weights=w)
+
+
+def moe_case_nvfp4(tokens, hidden, inter, experts, topk, seed, masked_ratio=0.0, empty_experts=()):
+    """moe_case with NVFP4 tensors: x and the weights quantised by the NVFP4 oracle (per-16 UE4M3 + tensor scale)."""
+    from oracle import moe as omoe
+    from oracle import nvfp4 as onv
+    torch.manual_seed(seed)
+    x = torch.randn(tokens, hidden).bfloat16()
+    x_q, x_sf, x_scale = onv.quantize_nvfp4(x)
+    w1 = (torch.randn(experts, 2 * inter, hidden) * 0.02).bfloat16()
+    w2 = (torch.randn(experts, hidden, inter) * 0.02).bfloat16()
+    l1 = [onv.quantize_nvfp4(w1[e]) for e in range(experts)]
+    l2 = [onv.quantize_nvfp4(w2[e]) for e in range(experts)]
+    stack = lambda parts, i: torch.stack([p[i] for p in parts])
+    logits = torch.randn(tokens, experts)
+    for e in empty_experts:
+        logits[:, e] = -1e9
+    idx, w = omoe.route_sigmoid_topk(logits, topk)
+    if masked_ratio > 0:
+        mask = torch.rand(idx.shape) < masked_ratio
+        idx = idx.masked_fill(mask, -1)
+        w = w.masked_fill(mask, 0.0)
+    return dict(x=x, x_q=x_q, x_sf=x_sf, x_scale=x_scale, l1_q=stack(l1, 0), l1_sf=stack(l1, 1), l1_scales=stack(l1, 2),
+                l2_q=stack(l2, 0), l2_sf=stack(l2, 1), l2_scales=stack(l2, 2), topk_idx=idx, topk_weights=w)
