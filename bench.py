@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument('--tokens', type=int, default=0, help='override tokens per rank (profiling small cases only)')
     ap.add_argument('--experts', type=int, default=0, help='override the expert count (profiling small cases only)')
     ap.add_argument('--skip-cpu-baseline', action='store_true')
+    ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
+                    help='nvfp4xnvfp4 runs the NVFP4 prefill variant (16384 tokens) instead of the headline workload')
     return ap.parse_args()
 
 
@@ -172,7 +174,7 @@ def run_reference(args, cfg, rank, world):
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': args.gpus,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
-        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8xfp4 (fp32 accumulate)', 'data': 'synthetic',
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': cfg.get('mma', 'fp8xfp4') + ' (fp32 accumulate)', 'data': 'synthetic',
         'config': workload_config(cfg, args.gpus),
         'cpu_baseline': {'value': value, 'unit': 'tokens/s', 'cores': cores, 'kind': 'port',
                          'sample': sample_description(cfg, rows)},
@@ -183,6 +185,13 @@ def run_reference(args, cfg, rank, world):
 
 
 def workload_config(cfg, gpus):
+    if cfg.get('mma') == 'nvfp4xnvfp4':
+        return {'workload': 'NVFP4 prefill variant of the MoE layer (BASELINE config 4)' + ('' if gpus == 1 else f', {gpus}-GPU expert-parallel'),
+                'tokens_per_rank': cfg['tokens'], 'hidden': cfg['hidden'], 'intermediate': cfg['inter'],
+                'experts': cfg['experts'], 'topk': cfg['topk'],
+                'activations': 'nvfp4 e2m1, 1x16 ue4m3 + fp32 tensor scale (calibrated, fixed)',
+                'weights': 'nvfp4 e2m1, 1x16 ue4m3 + fp32 scale per expert matrix',
+                'l2_policy': 'inputs larger than L2 (about 8 GB of expert weights streamed every step)'}
     name = ('single-GPU full MoE layer, MXFP4 weights (BASELINE config 3)' if gpus == 1 else
             f'{gpus}-GPU expert-parallel MoE layer, MXFP4 weights (BASELINE config 5)')
     return {'workload': name, 'tokens_per_rank': cfg['tokens'], 'hidden': cfg['hidden'],
@@ -216,6 +225,29 @@ def build_layer(dg, cfg, keep_cpu_experts):
     return l1, l2, cpu
 
 
+def build_layer_nvfp4(dg, cfg):
+    """Random expert weights ~N(0, 0.02) quantised to NVFP4 on the GPU expert by expert, scales packed MN-major."""
+    import torch
+    e, h, i = cfg['local_experts'], cfg['hidden'], cfg['inter']
+    l1_q = torch.empty((e, 2 * i, h // 2), dtype=torch.int8, device='cuda')
+    l1_sf = torch.empty((e, h // 64, 2 * i), dtype=torch.int32, device='cuda').transpose(1, 2)
+    l2_q = torch.empty((e, h, i // 2), dtype=torch.int8, device='cuda')
+    l2_sf = torch.empty((e, i // 64, h), dtype=torch.int32, device='cuda').transpose(1, 2)
+    l1_s = torch.empty(e, dtype=torch.float32, device='cuda')
+    l2_s = torch.empty(e, dtype=torch.float32, device='cuda')
+    for g in range(e):
+        w = torch.randn(2 * i, h, device='cuda', dtype=torch.bfloat16) * 0.02
+        l1_q[g], sf, l1_s[g] = dg.per_token_cast_to_nvfp4(w, sf_layout='mn')
+        l1_sf[g].copy_(sf)
+        w = torch.randn(h, i, device='cuda', dtype=torch.bfloat16) * 0.02
+        l2_q[g], sf, l2_s[g] = dg.per_token_cast_to_nvfp4(w, sf_layout='mn')
+        l2_sf[g].copy_(sf)
+    l1, l2 = dg.transform_weights_for_mega_moe((l1_q, l1_sf, l1_s), (l2_q, l2_sf, l2_s))
+    del l1_q, l1_sf
+    torch.cuda.empty_cache()
+    return l1, l2
+
+
 def run_ours(args, cfg, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -226,8 +258,16 @@ def run_ours(args, cfg, rank, world, local_rank):
     torch.manual_seed(1234 + rank)
     t, h, i, e, k = cfg['tokens'], cfg['hidden'], cfg['inter'], cfg['experts'], cfg['topk']
     cfg['local_experts'] = e // world
-    l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 and not args.skip_cpu_baseline else 0)
-    buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD if world > 1 else None, e, t, k, h, i)
+    nvfp4 = cfg.get('mma') == 'nvfp4xnvfp4'
+    if nvfp4:
+        args.skip_cpu_baseline = True  # the CPU baseline belongs to the headline workload
+        l1, l2 = build_layer_nvfp4(dg, cfg)
+        # calibrated, fixed scales (equal on every rank): inputs ~N(0, 1) stay below 8; post-SwiGLU values below 64
+        x_scale = torch.tensor(8.0 / (6 * 448), device='cuda')
+        act_scale = torch.tensor(64.0 / (6 * 448), device='cuda')
+    else:
+        l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 and not args.skip_cpu_baseline else 0)
+    buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD if world > 1 else None, e, t, k, h, i, mma_type=cfg.get('mma', 'fp8xfp4'))
     x_host = torch.randn(t, h).bfloat16().pin_memory()
     logits = torch.randn(t, e)
     if world > 1:
@@ -246,11 +286,17 @@ def run_ours(args, cfg, rank, world, local_rank):
 
     def step(events=None):
         dg.route_sigmoid_topk(logits, k, buf.topk_idx, buf.topk_weights)
-        dg.utils.per_token_cast_to_fp8_into(x, buf.x, buf.x_sf, gran_k=32)
+        if nvfp4:
+            dg.per_token_cast_to_nvfp4_into(x, x_scale, buf.x, buf.x_sf)
+        else:
+            dg.utils.per_token_cast_to_fp8_into(x, buf.x, buf.x_sf, gran_k=32)
         if events is not None:
             arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
             _lib.check(lib.dgb200_set_mega_moe_stage_events(ctypes.cast(arr, ctypes.c_void_p), len(events)))
-        dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+        if nvfp4:
+            dg.nvfp4_mega_moe(y, l1, l2, buf, x_scale, act_scale)
+        else:
+            dg.fp8_fp4_mega_moe(y, l1, l2, buf)
 
     def barrier():
         if world > 1:
@@ -312,8 +358,12 @@ def run_ours(args, cfg, rank, world, local_rank):
         dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
     touched = int(((ends - starts) > 0).sum())
     flops = 2.0 * float(rows_all) * h * i * 3
-    l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 32) + rows * (h + h // 32) + rows * (i + i // 32)
-    l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
+    if nvfp4:
+        l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 16) + rows * (h // 2 + h // 16) + rows * (i // 2 + i // 16)
+        l2_bytes = touched * (h * i // 2 + h * i // 16) + rows * (i // 2 + i // 16) + rows * h * 2
+    else:
+        l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 32) + rows * (h + h // 32) + rows * (i + i // 32)
+        l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
     times = torch.tensor([ms_per_step, e2e_ms] + stage_ms, dtype=torch.float64, device='cuda')
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -327,7 +377,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     line = {
         'metric': METRIC, 'value': t * world / (ms_per_step * 1e-3), 'unit': 'tokens/s', 'n_gpus': world,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
-        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8xfp4 (fp32 accumulate)', 'data': 'synthetic',
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': cfg.get('mma', 'fp8xfp4') + ' (fp32 accumulate)', 'data': 'synthetic',
         'config': workload_config(cfg, world),
         'e2e': {'value': t * world / (e2e_ms * 1e-3), 'unit': 'tokens/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': x_host.numel() * 2 + logits_host.numel() * 4, 'd2h_bytes_per_step': y_host.numel() * 2},
@@ -368,6 +418,9 @@ def main():
     world = int(os.environ.get('WORLD_SIZE', '1'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
     cfg = dict(CONFIG3)
+    cfg['mma'] = args.mma
+    if args.mma == 'nvfp4xnvfp4':
+        cfg['tokens'] = 16384
     if args.gpus > 1:
         cfg['tokens'] = 8192
     if args.tokens:
@@ -375,6 +428,8 @@ def main():
     if args.experts:
         cfg['experts'] = args.experts
     if args.impl == 'reference':
+        if args.mma != 'fp8xfp4':
+            raise SystemExit('--impl reference times the headline FP8 x MXFP4 workload only')
         run_reference(args, cfg, rank, world)
         return
     if world != args.gpus:

@@ -22,6 +22,7 @@ from .mega import (  # noqa: F401
     SymmBuffer,
     fp8_fp4_mega_moe,
     get_block_m_for_mega_moe,
+    get_segment_alignment_for_mega_moe,
     get_symm_buffer_for_mega_moe,
     get_token_alignment_for_mega_moe,
     nvfp4_mega_moe,

@@ -39,6 +39,7 @@ _SIGNATURES = {
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_route_sigmoid_topk': [_ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr],
     'dgb200_get_token_alignment_for_mega_moe': [],
+    'dgb200_get_segment_alignment_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_nvfp4_mega_moe': [

@@ -21,7 +21,7 @@ constexpr int kVersion = 100;
 
 template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
 int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_sfa, const CUtensorMap& tm_sfb,
-                const GemmParams& p, int grid, cudaStream_t stream) {
+                const CUtensorMap& tm_out, const GemmParams& p, int grid, cudaStream_t stream) {
     using L = GemmSmem<BLOCK_N, kStages, kKind>;
     auto kernel = dgb200_grouped_gemm_kernel<BLOCK_N, kStages, EPI, kKind>;
     static bool configured = false;  // per instantiation; the attribute is per device function, set on every device once
@@ -33,7 +33,7 @@ int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensor
         configured = true;
         configured_device = dev;
     }
-    kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, p);
+    kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p);
     DGB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -46,6 +46,8 @@ struct GemmCall {
     long long sfa_k_stride, sfa_group_stride, sfb_k_stride, sfb_group_stride;
     int num_groups_a;  // groups of A's scale factors: 1 for the contiguous layouts, num_groups for the masked one
     int kind;          // kKindFp8Fp4 (default) or kKindNvfp4
+    int whole_tile_stores;  // the rows between a group's end and its 128-row tile end are private padding: the
+                            // epilogue may write all 128 rows of every tile
     long long a_rows_total;  // rows of the flattened A
     GemmParams p;
     int b_is_fp4;
@@ -53,10 +55,8 @@ struct GemmCall {
     int max_tiles;  // upper bound on tiles, <= 0 if unknown
 };
 
-// Tuning knobs read once from the environment (defaults are the measured best on B200).
+// Process-wide tuning knobs (defaults are the measured best on B200).
 struct Tuning {
-    int prefetch_distance = 0;
-    int prefetch_mask = 7;
     int block_n = 0;  // 0 = automatic
     int debug_skip = 0;
     long long* trace = nullptr;  // debugging: per-role clock64() samples of CTA 0 (8 roles x trace_cap)
@@ -64,12 +64,7 @@ struct Tuning {
 };
 
 Tuning& tuning() {
-    static Tuning t = [] {
-        Tuning v;
-        if (const char* s = std::getenv("DGB200_PREFETCH_DISTANCE")) v.prefetch_distance = std::max(0, std::atoi(s));
-        if (const char* s = std::getenv("DGB200_PREFETCH_MASK")) v.prefetch_mask = std::atoi(s) & 7;
-        return v;
-    }();
+    static Tuning t;
     return t;
 }
 
@@ -141,18 +136,22 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     }
     if (rc) return rc;
 
-    p.a_ptr = static_cast<const unsigned char*>(c.a);
-    p.b_ptr = static_cast<const unsigned char*>(c.b);
-    p.sfa_ptr = static_cast<const unsigned char*>(c.sfa);
-    p.sfb_ptr = static_cast<const unsigned char*>(c.sfb);
-    p.a_rows = c.a_rows_total;
-    p.a_row_bytes = static_cast<long long>(a_row_bytes);
-    p.b_row_bytes = (nvfp4 || c.b_is_fp4) ? p.k / 2 : p.k;
-    p.b_kb_bytes = (c.b_is_fp4 && !nvfp4) ? 64 : 128;
-    p.sfa_kp_bytes = c.sfa_k_stride * 4;
-    p.sfb_kp_bytes = c.sfb_k_stride * 4;
-    p.prefetch_distance = tuning().prefetch_distance;
-    p.prefetch_mask = tuning().prefetch_mask;
+    // Output tensor map for the staged (shared memory + TMA) epilogue stores of the 256-wide FP8 x FP4 kernels.
+    CUtensorMap tm_out = tm_a;
+    p.tma_store = 0;
+    if (!nvfp4 && block_n == 256 && (c.epilogue == kEpiBF16 || c.epilogue == kEpiSwiGLU)) {
+        if (c.epilogue == kEpiBF16)
+            rc = make_tensor_map_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.d, static_cast<uint64_t>(p.n),
+                                    static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.d_row_stride) * 2, 32, 32,
+                                    CU_TENSOR_MAP_SWIZZLE_64B);
+        else
+            rc = make_tensor_map_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.act_q, static_cast<uint64_t>(p.n / 2),
+                                    static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.act_q_row_stride), 64, 32,
+                                    CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc) return rc;
+        p.tma_store = c.whole_tile_stores ? 2 : 1;
+    }
+
     p.debug_skip = tuning().debug_skip;
     p.trace = tuning().trace;
     p.trace_cap = tuning().trace_cap;
@@ -165,8 +164,8 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 
     if (c.max_tiles > 0 && block_n == 256) grid = std::min(grid, std::max(1, c.max_tiles / 2));
 #define DGB_LAUNCH(EPI, KIND)                                                                                   \
-    return block_n == 256 ? launch_gemm<256, 4, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)            \
-                          : launch_gemm<128, 6, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, p, grid, stream)
+    return block_n == 256 ? launch_gemm<256, 4, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream)            \
+                          : launch_gemm<128, 6, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream)
     if (nvfp4) {
         switch (c.epilogue) {
             case kEpiBF16: DGB_LAUNCH(kEpiBF16, kKindNvfp4);
@@ -190,7 +189,9 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 // layer (the reference's counterpart: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155, and
 // deep_gemm/include/deep_gemm/layout/mega_moe.cuh:46-443). All regions start on 1024-byte boundaries.
 // --------------------------------------------------------------------------------------------------------------
-constexpr int kSegmentAlignment = 16;
+// Rows each expert's segment of the expert-sorted buffers is padded to: one M tile, so that a tile's rows (and the
+// 128-row groups of its scale factors, stored in tcgen05.cp order) never straddle two experts.
+constexpr int kSegmentAlignment = 128;
 
 // Optional CUDA events the next mega-MoE call records at its stage boundaries (set per host thread, used once).
 constexpr int kNumStageEvents = 6;
@@ -322,6 +323,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         c.a_rows_total = l.max_rows;
         c.b_is_fp4 = 1;
         c.epilogue = nvfp4 ? kEpiSwiGLUNvfp4 : kEpiSwiGLU;
+        c.whole_tile_stores = 1;
         c.max_tiles = 0;
         c.sfa = base + l.l1_sf;
         c.sfb = l1_w_sf;
@@ -347,6 +349,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.a_scale = quant.x_scale;
         p.b_scales = quant.l1_scales;
         p.out_scale = quant.act_scale;
+        p.sf_transposed = 1;      // the gather / push kernels and transform_weights_for_mega_moe store tcgen05.cp order
+        p.act_sf_transposed = 1;  // ... and so does this GEMM's epilogue for the next one
         p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
         p.fast_math = fast_math;
@@ -361,6 +365,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         c.a_rows_total = l.max_rows;
         c.b_is_fp4 = 1;
         c.epilogue = kEpiBF16;
+        c.whole_tile_stores = 1;
         c.max_tiles = 0;
         c.sfa = base + l.l2_sf;
         c.sfb = l2_w_sf;
@@ -383,6 +388,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.d_row_stride = hidden;
         p.a_scale = quant.act_scale;
         p.b_scales = quant.l2_scales;
+        p.sf_transposed = 1;
         if ((rc = run_gemm(c, stream))) return rc;
     }
     return record_stage(stage_event_base + 1, stream);
@@ -586,12 +592,7 @@ int dgb200_set_num_sms(int num_sms) {
 
 int dgb200_set_tuning(const char* name, int32_t value) {
     DGB_REQUIRE(name != nullptr, "null name");
-    if (std::strcmp(name, "prefetch_distance") == 0) {
-        DGB_REQUIRE(value >= 0 && value <= 4096, "prefetch_distance must be in [0, 4096]");
-        tuning().prefetch_distance = value;
-    } else if (std::strcmp(name, "prefetch_mask") == 0) {
-        tuning().prefetch_mask = value & 7;
-    } else if (std::strcmp(name, "block_n") == 0) {
+    if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
     } else if (std::strcmp(name, "debug_skip") == 0) {
@@ -780,6 +781,8 @@ int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t exper
 }
 
 int dgb200_get_token_alignment_for_mega_moe(void) { return 128; }
+
+int dgb200_get_segment_alignment_for_mega_moe(void) { return kSegmentAlignment; }
 
 int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
                                                int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,

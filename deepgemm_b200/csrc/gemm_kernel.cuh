@@ -11,12 +11,13 @@
 //   * Tokens sit on the UMMA M side (TMEM lanes), weight channels on the N side (TMEM columns). One epilogue
 //     thread therefore owns one token row: stores are row-contiguous 16-byte vectors straight from registers,
 //     and the SwiGLU / amax / requant epilogue needs no shuffles or shared-memory exchange.
-//   * Scale factors arrive by 1-D bulk copies (no tensor maps), 512 B per 128 rows per packed K group.
+//   * Scale factors arrive through their own tensor maps, 512 B per 128 rows per packed scale int; when the caller
+//     stores them in tcgen05.cp row order (the MoE layer does) they go from shared to tensor memory untouched.
 //   * Stores are clipped to the valid rows of a group, so a masked group never writes into its neighbour.
 //   * Every wait is bounded; a timeout unwinds the CTA and is reported through the status block.
 //
-// Warp roles (384 threads): warp 0 loads A tiles and both scale-factor rows, warp 3 loads the weight tiles and runs the
-// L2 prefetch cursor, warp 1 issues the MMAs, warp 2 allocates TMEM and transposes scale factors for tcgen05.cp,
+// Warp roles (384 threads): warp 0 loads A tiles and both scale-factor rows, warp 3 loads the weight tiles, warp 1
+// issues the MMAs, warp 2 allocates TMEM and (only for scale factors in plain row order) transposes them for tcgen05.cp,
 // warps 4-11 are the epilogue (TMEM lane quarter = warp index % 4, two warps per quarter splitting the columns).
 // The control warpgroup hands registers to the epilogue warpgroups with setmaxnreg.
 #pragma once
@@ -61,23 +62,16 @@ struct GemmParams {
     unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
     unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
     int store_padding;       // psum only: also write the rows between a group's end and its aligned end
-    int prefetch_distance;   // K blocks the loaders' L2 prefetch cursors run ahead of their loads (0 = off)
-    int prefetch_mask;       // bit 0: B tiles, bit 1: A tiles, bit 2: scale factors
-    // raw views of the operands for the prefetch cursors (the loads themselves go through the tensor maps)
-    const unsigned char* a_ptr;
-    const unsigned char* b_ptr;
-    const unsigned char* sfa_ptr;
-    const unsigned char* sfb_ptr;
-    long long a_rows;                      // rows of the flattened A (prefetches stay inside the tensor)
-    long long a_row_bytes, b_row_bytes;    // row pitch of A and B in bytes
-    long long sfa_kp_bytes, sfb_kp_bytes;  // pitch between packed K groups of the scale factors in bytes
-    int b_kb_bytes;                        // bytes of one B row inside one K block: 64 (packed FP4) or 128 (FP8)
     int debug_skip;          // timing experiments only (results become garbage): bit 0 no A loads, 1 no B loads,
                              // 2 no scale-factor loads, 3 no MMA instructions, 4 no scale-factor TMEM copies
     long long* trace;        // optional: CTA 0 records clock64() per role and K block at trace[role * trace_cap + i]
     int trace_cap;
     // SwiGLU epilogue only
     unsigned char* act_q;        // e4m3 [rows, n/2]
+    int tma_store;               // epilogue stores through shared memory + TMA (BLOCK_N = 256, FP8 x FP4 kind): 0 never,
+                                 // 1 for tiles whose 128 rows are all valid, 2 always (rows past a group's end may be overwritten)
+    int sf_transposed;           // scale factors of A and B already lie in the tcgen05.cp row order (sf_row_in_cp_order)
+    int act_sf_transposed;       // the SwiGLU epilogues write act_sf in that order too
     unsigned char* act_sf;       // packed UE8M0 bytes, MN-major ints: ((j/128)*act_sf_k_stride + row)*4 + (j/32)%4
     long long act_q_row_stride;  // bytes
     long long act_sf_k_stride;   // ints
@@ -99,22 +93,34 @@ struct Tile {
     int n_block;
 };
 
-constexpr int kMaxCachedGroups = 1024;  // group extents of up to this many groups are staged in shared memory
+constexpr int kMaxCachedGroups = 512;   // group extents of up to this many groups are staged in shared memory
+
+// Per-group schedule staged in shared memory by the kernel prologue (psum and masked layouts, up to
+// kMaxCachedGroups groups): the layout words, each group's first row and the running tile count. Every warp role
+// walks the tile sequence on its own, and the MMA issuer does so on the critical path between two tiles while the
+// epilogue warps compete for the same issue slots, so finding the next tile must take a handful of instructions.
+struct GroupTable {
+    const int* lay;        // psum ends / masked counts
+    const int* start;      // first row of the group
+    const int* tiles_end;  // tiles of groups 0..g inclusive
+    bool cached;           // false: walk the global layout array with the arithmetic below (more groups than the table holds)
+};
 
 template <int BLOCK_N>
 struct TileScheduler {
     const GemmParams& p;
-    const int* lay;  // per-group extents (psum ends / masked counts): the shared-memory copy when it fits, else global.
-                     // A dependent global load costs several hundred cycles and every role walks the groups per tile.
+    const GroupTable tab;
     int num_n_blocks;
     int tile;  // next global tile index of this CTA
     int g, tiles_before_g;
 
-    __device__ TileScheduler(const GemmParams& params, const int* group_layout)
-        : p(params), lay(group_layout), num_n_blocks(params.n / BLOCK_N), tile(static_cast<int>(blockIdx.x)), g(0),
+    __device__ TileScheduler(const GemmParams& params, const GroupTable& table)
+        : p(params), tab(table), num_n_blocks(params.n / BLOCK_N), tile(static_cast<int>(blockIdx.x)), g(0),
           tiles_before_g(0) {}
 
-    __device__ __forceinline__ void group_extent(int group, int& start, int& rows, int& rows_store) const {
+    // First row, valid rows and rows to store of one group, from the layout words.
+    __device__ __forceinline__ static void group_extent(const GemmParams& p, const int* lay, int group, int& start, int& rows,
+                                                        int& rows_store) {
         if (p.mode == kModeMasked) {
             start = group * p.m;
             rows = min(lay[group], p.m);
@@ -127,6 +133,17 @@ struct TileScheduler {
             const int aligned_end = min((end + p.alignment - 1) / p.alignment * p.alignment, p.m);
             rows_store = p.store_padding ? max(aligned_end - start, 0) : rows;
         }
+    }
+
+    __device__ __forceinline__ void fill(Tile& t, int group, int start, int rows_store, int local) {
+        int mb = 0;
+        while (local >= num_n_blocks) { local -= num_n_blocks; ++mb; }  // groups are a few M blocks tall
+        t.n_block = local;
+        t.row_start = start + mb * 128;
+        t.sf_row_start = p.mode == kModeMasked ? mb * 128 : t.row_start;
+        t.rows_store = min(128, rows_store - mb * 128);
+        t.group = group;
+        tile += static_cast<int>(gridDim.x);
     }
 
     // Returns false when this CTA has no more tiles. A tile with group < 0 must be skipped by every role.
@@ -142,20 +159,27 @@ struct TileScheduler {
             tile += static_cast<int>(gridDim.x);
             return true;
         }
+        if (tab.cached) {
+            while (g < p.num_groups && tile >= tab.tiles_end[g]) ++g;
+            if (g >= p.num_groups) return false;
+            const int start = tab.start[g];
+            int rows_store;
+            if (p.mode == kModeMasked) {
+                rows_store = min(tab.lay[g], p.m);
+            } else if (p.store_padding) {
+                rows_store = max(min((tab.lay[g] + p.alignment - 1) / p.alignment * p.alignment, p.m) - start, 0);
+            } else {
+                rows_store = max(tab.lay[g] - start, 0);
+            }
+            fill(t, g, start, rows_store, tile - (g == 0 ? 0 : tab.tiles_end[g - 1]));
+            return true;
+        }
         while (g < p.num_groups) {
             int start, rows, rows_store;
-            group_extent(g, start, rows, rows_store);
-            const int m_blocks = (max(rows, rows_store) + 127) / 128;
-            const int tiles_g = m_blocks * num_n_blocks;
+            group_extent(p, tab.lay, g, start, rows, rows_store);
+            const int tiles_g = (max(rows, rows_store) + 127) / 128 * num_n_blocks;
             if (tile < tiles_before_g + tiles_g) {
-                const int local = tile - tiles_before_g;
-                const int mb = local / num_n_blocks;
-                t.n_block = local - mb * num_n_blocks;
-                t.row_start = start + mb * 128;
-                t.sf_row_start = p.mode == kModeMasked ? mb * 128 : t.row_start;
-                t.rows_store = min(128, rows_store - mb * 128);
-                t.group = g;
-                tile += static_cast<int>(gridDim.x);
+                fill(t, g, start, rows_store, tile - tiles_before_g);
                 return true;
             }
             tiles_before_g += tiles_g;
@@ -180,7 +204,11 @@ struct GemmSmem {
     static constexpr int kNumBars = 3 * kStages + 4;
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;
     static constexpr int kOffGroups = kOffMisc + 16;
-    static constexpr int kTotal = kOffGroups + kMaxCachedGroups * 4;
+    // Epilogue staging for TMA stores: 32 rows x 64 bytes per epilogue warp, in the 64-byte swizzle (512-byte atoms).
+    // The NVFP4 kind has no room for it next to its larger scale-factor stages and stores from registers.
+    static constexpr int kStageBytesPerWarp = (kKind == kKindFp8Fp4 && BLOCK_N == 256) ? 2048 : 0;
+    static constexpr int kOffStage = (kOffGroups + 3 * kMaxCachedGroups * 4 + 511) / 512 * 512;
+    static constexpr int kTotal = kOffStage + 8 * kStageBytesPerWarp;
     static constexpr int kDynamicBytes = kTotal + 1024;  // slack to align the base to 1024 B
 };
 
@@ -217,7 +245,7 @@ template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-                           const __grid_constant__ GemmParams p) {
+                           const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ GemmParams p) {
     using L = GemmSmem<BLOCK_N, kStages, kKind>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
     constexpr int kSfInts = L::kSfIntsPerRow;          // scale ints per row per K block = tcgen05.cp blocks per 128 rows
@@ -263,12 +291,42 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         prefetch_tensormap(&tm_b);
         prefetch_tensormap(&tm_sfa);
         prefetch_tensormap(&tm_sfb);
+        if (p.tma_store) prefetch_tensormap(&tm_out);
     }
+    // Stage the per-group schedule (see GroupTable): every thread fills its groups, warp 0 turns the per-group tile
+    // counts into running totals.
     int* group_cache = reinterpret_cast<int*>(smem + L::kOffGroups);
+    int* group_start = group_cache + kMaxCachedGroups;
+    int* group_tiles_end = group_start + kMaxCachedGroups;
     const bool cache_groups = p.mode != kModeRowIds && p.num_groups <= kMaxCachedGroups;
-    if (cache_groups)
-        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) group_cache[i] = __ldg(p.layout + i);
-    const int* group_layout = cache_groups ? group_cache : p.layout;
+    if (cache_groups) {
+        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) {
+            int start, rows, rows_store;
+            TileScheduler<BLOCK_N>::group_extent(p, p.layout, i, start, rows, rows_store);
+            group_cache[i] = __ldg(p.layout + i);
+            group_start[i] = start;
+            group_tiles_end[i] = (max(rows, rows_store) + 127) / 128 * (p.n / BLOCK_N);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const int chunk = (p.num_groups + 31) / 32;
+            const int lo = min(static_cast<int>(lane) * chunk, p.num_groups), hi = min(lo + chunk, p.num_groups);
+            int sum = 0;
+            for (int i = lo; i < hi; ++i) sum += group_tiles_end[i];
+            int incl = sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, off);
+                if (static_cast<int>(lane) >= off) incl += v;
+            }
+            int run = incl - sum;
+            for (int i = lo; i < hi; ++i) {
+                run += group_tiles_end[i];
+                group_tiles_end[i] = run;
+            }
+        }
+    }
+    const GroupTable group_layout{cache_groups ? group_cache : p.layout, group_start, group_tiles_end, cache_groups};
     if (warp == 2) tmem_alloc(tmem_ptr_smem, kTmemCols);
     tcgen05_fence_before();
     __syncthreads();
@@ -296,38 +354,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int trace_i = 0;
-            // L2 prefetch cursor for the A rows and their scale factors (see the weight loader below)
-            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
-            Tile pt;
-            int pf_kb = 0;
-            bool pf_valid = false;
-            auto pf_next_tile = [&]() {
-                pf_valid = false;
-                while (pf_sched.next(pt)) {
-                    if (pt.group >= 0) { pf_valid = true; break; }
-                }
-                pf_kb = 0;
-            };
-            auto pf_advance = [&]() {
-                if (!pf_valid) return;
-                if (p.prefetch_mask & 2) {
-                    const unsigned char* base = p.a_ptr + (static_cast<long long>(pt.row_start) + lane) * p.a_row_bytes +
-                                                static_cast<long long>(pf_kb) * 128;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (pt.row_start + static_cast<int>(lane) + j * 32 < p.a_rows) prefetch_l2(base + j * 32 * p.a_row_bytes);
-                }
-                if ((p.prefetch_mask & 4) && pf_kb % a_per == 0 && lane < 4 &&
-                    (pt.sf_row_start + static_cast<int>(lane) * 32) * 4ll < p.sfa_kp_bytes)
-                    prefetch_l2(p.sfa_ptr + (static_cast<long long>(pt.group) * p.sfa_group_rows + pf_kb / a_per) * p.sfa_kp_bytes +
-                                static_cast<long long>(pt.sf_row_start) * 4 + lane * 128);
-                if (++pf_kb == num_kb) pf_next_tile();
-            };
-            if (p.prefetch_distance > 0 && (p.prefetch_mask & 6)) {
-                pf_next_tile();
-                for (int i = 0; i < p.prefetch_distance; ++i) pf_advance();
-            }
-
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int sfa_y = t.group * p.sfa_group_rows, sfb_y = t.group * p.sfb_packed_k;
@@ -352,54 +378,19 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         trace_point(p, 1, trace_i);
                     }
                     __syncwarp();
-                    if (p.prefetch_distance > 0 && (p.prefetch_mask & 6)) pf_advance();
                     ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 3) {
-        // ---------------------------------------------------------------- loader: B (weight) tile + L2 prefetch
+        // ---------------------------------------------------------------- loader: B (weight) tile
         {
             TileScheduler<BLOCK_N> sched(p, group_layout);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int trace_i = 0;
-
-            // L2 prefetch cursor: walks the same (tile, K block) sequence `prefetch_distance` blocks ahead of the
-            // loads. A stage holds only 8 or 16 KB of packed FP4 weights and shared memory bounds the number of
-            // stages, so HBM latency can be covered by prefetches in flight to L2 instead of by more stages.
-            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
-            Tile pt;
-            int pf_kb = 0;
-            bool pf_valid = false;
-            auto pf_next_tile = [&]() {
-                pf_valid = false;
-                while (pf_sched.next(pt)) {
-                    if (pt.group >= 0) { pf_valid = true; break; }
-                }
-                pf_kb = 0;
-            };
-            auto pf_advance = [&]() {
-                if (!pf_valid) return;
-                // every lane prefetches the 128-byte lines of its rows (plain prefetches: the TMA unit stays free)
-                const long long col = static_cast<long long>(pf_kb) * p.b_kb_bytes;
-                if ((p.prefetch_mask & 1) && (col & 127) == 0) {
-                    const unsigned char* base =
-                        p.b_ptr + (static_cast<long long>(pt.group) * p.n + pt.n_block * BLOCK_N + lane) * p.b_row_bytes + col;
-#pragma unroll
-                    for (int j = 0; j < BLOCK_N / 32; ++j) prefetch_l2(base + j * 32 * p.b_row_bytes);
-                }
-                if ((p.prefetch_mask & 4) && pf_kb % b_per == 0 && lane < BLOCK_N / 32)
-                    prefetch_l2(p.sfb_ptr + (static_cast<long long>(pt.group) * p.sfb_packed_k + pf_kb / b_per) * p.sfb_kp_bytes +
-                                static_cast<long long>(pt.n_block) * BLOCK_N * 4 + lane * 128);
-                if (++pf_kb == num_kb) pf_next_tile();
-            };
-            if (p.prefetch_distance > 0) {
-                pf_next_tile();
-                for (int i = 0; i < p.prefetch_distance; ++i) pf_advance();
-            }
 
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
@@ -415,7 +406,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         trace_point(p, 10, trace_i);
                     }
                     __syncwarp();
-                    if (p.prefetch_distance > 0) pf_advance();
                     ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -436,18 +426,25 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
         uint32_t tmem_sfa = 0, tmem_sfb = 0;  // TMEM columns holding the scale factors of the current K block
         bool ok = true;
+        if (lane == 0) trace_point(p, 14, 0);
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
+            if (lane == 0) trace_point(p, 15, static_cast<int>(iter));
             ++iter;
             ok = mbar_wait(tmem_empty_bar + as, aphase ^ 1, abort_flag, kTimeoutTmemEmpty, static_cast<int>(iter));
             if (!ok) break;
+            if (lane == 0) trace_point(p, 14, static_cast<int>(iter));
             tcgen05_fence_after();
             const uint32_t tmem_acc = tmem_base + as * kAccumCols;
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = mbar_wait(sf_ready_bar + stage, phase, abort_flag, kTimeoutSfReady, kb);
+                // scale factors stored in tcgen05.cp order need no transposer pass: the loads' barrier is enough
+                if (lane == 0) trace_point(p, 8, trace_i);
+                ok = mbar_wait((p.sf_transposed ? full_bar : sf_ready_bar) + stage, phase, abort_flag, kTimeoutSfReady, kb);
                 if (!ok) break;
-                tcgen05_fence_after();
+                if (lane == 0) trace_point(p, 11, trace_i);
+                // No tcgen05 fence here: the data this wait covers was written to shared memory through the async proxy
+                // (TMA, or the transposer's stores followed by its proxy fence), not by tcgen05 operations.
                 if (elect_one()) {
                     trace_point(p, 4, trace_i);
                     // One tcgen05.cp moves the scales of 128 rows for one MMA (one packed int per row) into 4 TMEM columns.
@@ -466,6 +463,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     }
                     const uint64_t adesc = make_kmajor_sw128_desc(a_base + stage * L::kABytes);
                     const uint64_t bdesc = make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
+                    trace_point(p, 12, trace_i);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
                         if (DGB_SKIP(p, 8)) continue;
@@ -482,6 +480,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                                  (kb | k4) != 0 ? 1u : 0u);
                         }
                     }
+                    trace_point(p, 13, trace_i);
                     tcgen05_commit(empty_bar + stage);
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
                     trace_point(p, 5, trace_i);
@@ -490,6 +489,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
+            if (lane == 0) trace_point(p, 3, static_cast<int>(iter));
         }
         }
     } else if (warp == 2) {
@@ -499,7 +499,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         Tile t;
         uint32_t stage = 0, phase = 0;
         int trace_i = 0;
-        bool ok = true;
+        bool ok = p.sf_transposed == 0;  // nothing to do when the scale factors arrive in tcgen05.cp order
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -576,9 +576,49 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty_bar + as);
             if (threadIdx.x == 128) trace_point(p, 6, static_cast<int>(iter) - 1);
+            // Row-per-thread stores put 32 different cache lines into every store instruction, and the burst of a whole
+            // tile keeps the load/store pipe busy long enough to stall the control warps' shared-memory accesses.
+            // Staging the warp's 32 x 64-byte slab in shared memory and handing it to TMA costs 4 store wavefronts
+            // per 16-byte column instead of 32.
+            const bool via_tma = L::kStageBytesPerWarp != 0 && (p.tma_store == 2 || (p.tma_store == 1 && t.rows_store == 128));
+            uint8_t* stage_buf = smem + L::kOffStage + (warp - 4) * L::kStageBytesPerWarp;
+            // 16-byte chunk c of this thread's 64-byte row in the 64-byte swizzle pattern of the tensor map
+            auto stage_chunk = [&](int c) { return reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)); };
 
             const bool store = r < t.rows_store && !DGB_SKIP(p, 32);
             const long long row = static_cast<long long>(t.row_start) + r;
+            const long long sf_row = p.act_sf_transposed ? sf_row_in_cp_order(row) : row;  // used by the SwiGLU epilogues
+            if constexpr (L::kStageBytesPerWarp != 0 && EPI == kEpiBF16) {
+                if (via_tma && warp_has_rows) {
+                    // 32 columns (64 bytes of BF16 per row) per TMA store; rows past rows_store hold whatever the MMA
+                    // produced from the tile's padding rows and land in padding rows of D
+                    const int x0 = t.n_block * BLOCK_N + static_cast<int>(half) * kCols;
+#pragma unroll
+                    for (int c = 0; c < kCols / 32; ++c) {
+                        if (lane == 0) bulk_wait_group_read_all();  // the previous slab has left the staging buffer
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *stage_chunk(i) = make_uint4(
+                                pack_bf16x2(__uint_as_float(acc[c * 32 + i * 8 + 0]), __uint_as_float(acc[c * 32 + i * 8 + 1])),
+                                pack_bf16x2(__uint_as_float(acc[c * 32 + i * 8 + 2]), __uint_as_float(acc[c * 32 + i * 8 + 3])),
+                                pack_bf16x2(__uint_as_float(acc[c * 32 + i * 8 + 4]), __uint_as_float(acc[c * 32 + i * 8 + 5])),
+                                pack_bf16x2(__uint_as_float(acc[c * 32 + i * 8 + 6]), __uint_as_float(acc[c * 32 + i * 8 + 7])));
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tm_out, stage_buf, x0 + c * 32, t.row_start + static_cast<int>(q) * 32);
+                            bulk_commit_group();
+                        }
+                    }
+                }
+            }
+            if constexpr (L::kStageBytesPerWarp != 0 && EPI == kEpiSwiGLU) {
+                if (via_tma && warp_has_rows) {
+                    if (lane == 0) bulk_wait_group_read_all();  // the previous tile's slab has left the staging buffer
+                    __syncwarp();
+                }
+            }
             if (store) {
                 if constexpr (kKind == kKindNvfp4) {
                     // fold the two FP32 per-tensor scales into the accumulator
@@ -593,7 +633,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 #pragma unroll
                         for (int i = 0; i < kCols / 4; ++i)
                             st_global_v4(dst + i * 4, acc[i * 4 + 0], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]);
-                    } else {
+                    } else if (!via_tma) {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col0;
 #pragma unroll
                         for (int i = 0; i < kCols / 8; ++i)
@@ -641,7 +681,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             packed[h * 2] = lo;
                             packed[h * 2 + 1] = hi;
                             const int jb = j + h * 16;
-                            p.act_sf[(static_cast<long long>(jb / 64) * p.act_sf_k_stride + row) * 4 + ((jb / 16) & 3)] =
+                            p.act_sf[(static_cast<long long>(jb / 64) * p.act_sf_k_stride + sf_row) * 4 + ((jb / 16) & 3)] =
                                 static_cast<unsigned char>(sf_byte);
                         }
                         st_global_v4(p.act_q + row * p.act_q_row_stride + j / 2, packed[0], packed[1], packed[2], packed[3]);
@@ -678,16 +718,35 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                                                  o[i * 4 + 2] * sf_inv, o[i * 4 + 3] * sf_inv));
                             packed[i] = q4.__x;
                         }
-                        unsigned char* dst = p.act_q + row * p.act_q_row_stride + j;
-                        st_global_v4(dst, packed[0], packed[1], packed[2], packed[3]);
-                        st_global_v4(dst + 16, packed[4], packed[5], packed[6], packed[7]);
-                        p.act_sf[(static_cast<long long>(j / 128) * p.act_sf_k_stride + row) * 4 + ((j / 32) & 3)] =
+                        if (via_tma) {
+                            *stage_chunk(2 * c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            *stage_chunk(2 * c + 1) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            unsigned char* dst = p.act_q + row * p.act_q_row_stride + j;
+                            st_global_v4(dst, packed[0], packed[1], packed[2], packed[3]);
+                            st_global_v4(dst + 16, packed[4], packed[5], packed[6], packed[7]);
+                        }
+                        p.act_sf[(static_cast<long long>(j / 128) * p.act_sf_k_stride + sf_row) * 4 + ((j / 32) & 3)] =
                             static_cast<unsigned char>(sf_byte);
+                    }
+                }
+            }
+            if constexpr (L::kStageBytesPerWarp != 0 && EPI == kEpiSwiGLU) {
+                if (via_tma && warp_has_rows) {
+                    // one 32 x 64-byte slab of FP8 activations per warp and tile (rows past rows_store keep stale bytes
+                    // and land in padding rows)
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_out, stage_buf, t.n_block * (BLOCK_N / 2) + static_cast<int>(half) * (kCols / 2),
+                                     t.row_start + static_cast<int>(q) * 32);
+                        bulk_commit_group();
                     }
                 }
             }
             if (threadIdx.x == 128) trace_point(p, 7, static_cast<int>(iter) - 1);
         }
+        if (L::kStageBytesPerWarp != 0 && lane == 0) bulk_wait_group_all();  // stores still in flight read this CTA's shared memory
     }
 
     // ---------------------------------------------------------------- teardown

@@ -128,7 +128,8 @@ dgb200_moe_assign_kernel(const long long* __restrict__ topk_idx, const float* __
 //   x      [tokens, row_bytes] bytes (e4m3: hidden; packed e2m1: hidden / 2)
 //   x_sf   int32 [tokens, sf_per_row] token-major, 4 scale bytes per int (UE8M0 per 32: hidden / 128 ints;
 //          UE4M3 per 16: hidden / 64 ints)
-//   acts   [rows, row_bytes]               acts_sf int32 MN-major: int (kp, row) at acts_sf[kp * sf_k_stride + row]
+//   acts   [rows, row_bytes]               acts_sf int32 MN-major with every 128 rows in tcgen05.cp order: int (kp, row)
+//                                          at acts_sf[kp * sf_k_stride + sf_row_in_cp_order(row)]
 // Rows whose src_of_row is negative (segment padding) are left untouched.
 __global__ void __launch_bounds__(256)
 dgb200_moe_gather_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
@@ -152,7 +153,8 @@ dgb200_moe_gather_kernel(const unsigned char* __restrict__ x, const unsigned* __
     __syncthreads();
     for (int i = threadIdx.x; i < sf_per_row * 32; i += 256) {
         const int c = i >> 5, r = i & 31;
-        if (src_of_row[row0 + r] >= 0) acts_sf[static_cast<long long>(c) * sf_k_stride + row0 + r] = sf_tile[c * 33 + r];
+        if (src_of_row[row0 + r] >= 0)
+            acts_sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(row0 + r)] = sf_tile[c * 33 + r];
     }
 }
 
@@ -419,7 +421,7 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
     for (int c = lane; c < row_bytes / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
     unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
     for (int c = lane; c < sf_per_row; c += 32)
-        sf[static_cast<long long>(c) * sf_k_stride + dest] = x_sf[static_cast<long long>(token) * sf_per_row + c];
+        sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(dest)] = x_sf[static_cast<long long>(token) * sf_per_row + c];
     if (lane == 0) {
         reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
         reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;

@@ -167,6 +167,18 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// Tiled store shared -> global (bulk async group completion). x * element size must be a multiple of 16 bytes and
+// no coordinate may be negative; rows and columns beyond the tensor's extent are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once the bulk stores of this thread's committed groups have finished reading shared memory.
+__device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Returns once those stores are complete (their writes performed).
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // L2 prefetch of one tile / one span: starts the HBM read early without occupying shared memory.
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
@@ -386,6 +398,13 @@ __device__ __forceinline__ void grid_dependency_wait() {
 }
 __device__ __forceinline__ void grid_dependency_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// tcgen05.cp.32x128b.warpx4 reads, per 128 rows of one packed scale int, 32 rows x 4 words where word j of row r
+// is the scale int of source row r + 32 j. A tensor stored with every aligned group of 128 rows in that order (row
+// r of the group at position 4 (r % 32) + r / 32) can be copied by TMA and handed to tcgen05.cp as it lands.
+__host__ __device__ inline long long sf_row_in_cp_order(long long row) {
+    return (row & ~127ll) + ((row & 31) << 2) + ((row & 127) >> 5);
 }
 
 }  // namespace dgb

@@ -19,6 +19,11 @@ def get_token_alignment_for_mega_moe() -> int:
     return _lib.lib().dgb200_get_token_alignment_for_mega_moe()
 
 
+def get_segment_alignment_for_mega_moe() -> int:
+    """Rows each expert's segment is padded to in the layer's expert-sorted buffers (no reference counterpart)."""
+    return _lib.lib().dgb200_get_segment_alignment_for_mega_moe()
+
+
 def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_tokens: int,
                              num_topk: int, mma_type: str = 'fp8xfp4') -> int:
     """Rows of one M tile. The reference picks 16..192 by expected rows per expert (csrc/apis/mega.hpp:23-32);
@@ -123,19 +128,35 @@ def _interleave_rows(t: torch.Tensor, gran: int) -> torch.Tensor:
     return out
 
 
+def _sf_rows_to_cp_order(sf: torch.Tensor) -> torch.Tensor:
+    """Packed MN-major scale factors [G, N, Kp]: store every aligned group of 128 rows in the order tcgen05.cp reads
+    (row r of a group at position 4 (r % 32) + r / 32), so the kernel copies them from shared to tensor memory as
+    they land. Strides are kept."""
+    n = sf.shape[1]
+    if n % 128 != 0:
+        raise RuntimeError(f'weight rows ({n}) must be a multiple of 128')
+    pos = torch.arange(n, device=sf.device)
+    src = (pos // 128) * 128 + (pos % 4) * 32 + (pos % 128) // 4  # the row that lands at position `pos`
+    out = torch.empty_strided(sf.shape, sf.stride(), dtype=sf.dtype, device=sf.device)
+    out.copy_(sf.index_select(1, src))
+    return out
+
+
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
                                    l2_weights: Tuple[torch.Tensor, torch.Tensor], activation: str = 'swiglu'):
     """Reorders the L1 weights (and their packed scale factors) so that every 64-column slice of an L1 output tile
-    holds 32 gate channels and their 32 up channels. L2 is returned unchanged. The transformed tensors are opaque
-    to the caller, as in the reference (transform_weights_for_mega_moe, deep_gemm/mega/__init__.py:131-149, which
-    interleaves by 8 and pre-transposes scale factors for its own kernel)."""
+    holds 32 gate channels and their 32 up channels, and stores the scale factors of both layers in the row order
+    tcgen05.cp consumes. The transformed tensors are opaque to the caller, as in the reference
+    (transform_weights_for_mega_moe, deep_gemm/mega/__init__.py:131-149, which interleaves by 8 and pre-transposes
+    scale factors for its own kernel)."""
     if activation != 'swiglu':
         raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
     if not isinstance(l1_weights, tuple):
         raise RuntimeError('BF16 weights are not built; pass (packed FP4 weights, packed scale factors[, tensor scales])')
     # NVFP4 weights carry a third element, the per-expert FP32 scales, which no reordering touches
-    return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), _interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE)) + \
-        tuple(l1_weights[2:]), tuple(l2_weights)
+    l1_sf = _sf_rows_to_cp_order(_interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE))
+    return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), l1_sf) + tuple(l1_weights[2:]), \
+        (l2_weights[0], _sf_rows_to_cp_order(l2_weights[1])) + tuple(l2_weights[2:])
 
 
 def _check_weight(w, sf, num_groups, n, k, name, k_per_int=128):

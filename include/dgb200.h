@@ -37,10 +37,8 @@ int dgb200_version(void);
 int dgb200_set_num_sms(int num_sms);
 int dgb200_get_num_sms(void);
 
-/* Process-wide tuning knobs of the GEMM kernels: "prefetch_distance" (K blocks the L2 prefetch cursor runs ahead,
- * 0 = off; also DGB200_PREFETCH_DISTANCE in the environment) and "prefetch_mask" (bit 0 weights, bit 1 activations,
- * bit 2 scale factors; DGB200_PREFETCH_MASK). Plays the role of the reference's heuristics overrides
- * (csrc/apis/runtime.hpp:21-41). */
+/* Process-wide tuning knobs of the GEMM kernels: "block_n" (0 = automatic, 128 or 256: width of an output tile).
+ * Plays the role of the reference's heuristics overrides (csrc/apis/runtime.hpp:21-41). */
 int dgb200_set_tuning(const char* name, int32_t value);
 
 /* Debugging aid: while set, CTA 0 of every GEMM launch records clock64() per warp role and K block into
@@ -155,6 +153,10 @@ int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t exper
 /* Token-count granularity of the mega-MoE buffer. Reference: get_token_alignment_for_mega_moe, csrc/apis/mega.hpp:19-21. */
 int dgb200_get_token_alignment_for_mega_moe(void);
 
+/* Rows every expert's segment is padded to in the expert-sorted buffers (dest_row / expert_start / expert_end follow
+ * it). No reference counterpart: the reference sizes its pools by block_m tiles (csrc/apis/mega.hpp:34-80). */
+int dgb200_get_segment_alignment_for_mega_moe(void);
+
 /* Byte layout of the per-rank mega-MoE buffer. Reference: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155.
  * out[16] = {total bytes, x, x_sf, topk_idx, topk_weights, l1_acts, l1_sf, l2_acts, l2_sf, max_rows (rows, not bytes),
  *            dest_row, src_of_row, expert_start, expert_end, l2_out, row_weight}; all but out[0], out[9] are byte
@@ -169,8 +171,10 @@ int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_ex
  * deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:55-1458 (kernel).
  *   y        bf16 [num_tokens, hidden], written.
  *   l1_w     packed e2m1 [E_local, 2 * inter, hidden / 2], rows gate/up-interleaved by 32;
- *   l1_w_sf  packed UE8M0 int32 (per-32), MN-major [E_local][hidden / 128][2 * inter], same row order.
- *   l2_w     packed e2m1 [E_local, hidden, inter / 2]; l2_w_sf int32 [E_local][inter / 128][hidden].
+ *   l1_w_sf  packed UE8M0 int32 (per-32), MN-major [E_local][hidden / 128][2 * inter], same row order, then every
+ *            aligned group of 128 rows stored in tcgen05.cp order: row r of a group at position 4 (r % 32) + r / 32.
+ *   l2_w     packed e2m1 [E_local, hidden, inter / 2]; l2_w_sf int32 [E_local][inter / 128][hidden], rows in the
+ *            same 128-group order.
  *   cumulative_local_expert_recv_stats  optional int32 [E_local], incremented by the rows each expert received.
  *   buffer / peer_buffer_ptrs  this rank's buffer and the host array of all ranks' buffer addresses.
  *   activation_clamp <= 0 disables the clamp. */
@@ -191,7 +195,7 @@ int dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(int32_t num_ranks, int32_t 
 /* Same stages and argument meaning as dgb200_fp8_fp4_mega_moe with NVFP4 tensors:
  *   l1_w packed e2m1 [E_local, 2 * inter, hidden / 2] (gate/up interleaved by 32), l1_w_sf packed UE4M3 int32
  *   MN-major [E_local][hidden / 64][2 * inter], l1_w_scales float [E_local]; l2_w [E_local, hidden, inter / 2],
- *   l2_w_sf [E_local][inter / 64][hidden], l2_w_scales float [E_local].
+ *   l2_w_sf [E_local][inter / 64][hidden], l2_w_scales float [E_local]; scale rows in the 128-group order above.
  *   x_scale   device float: per-tensor scale the caller quantised x with; must hold the same value on every rank
  *             (a calibrated input scale), because an expert's rows come from all ranks.
  *   act_scale device float: calibrated per-tensor scale of the post-SwiGLU activations; the L1 epilogue quantises

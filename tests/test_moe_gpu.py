@@ -10,6 +10,7 @@ from tests.helpers import moe_case
 
 pytestmark = pytest.mark.gpu
 FP4_TOL = 2e-3
+SEGMENT = 128  # rows each expert's segment is padded to (dgb200_get_segment_alignment_for_mega_moe)
 
 
 @pytest.fixture(scope='module')
@@ -61,7 +62,7 @@ def test_small_layer_matches_oracle(dg, tokens, hidden, inter, experts, topk):
     stats = torch.full((experts,), 5, dtype=torch.int32, device='cuda')
     got, buf = _run_layer(dg, c, tokens, hidden, inter, experts, topk, stats=stats)
     dest, start, end = _plan_views(buf, tokens, topk, experts)
-    want_dest, _, want_start, want_end = omoe.dispatch_plan(c['topk_idx'], experts, 16)
+    want_dest, _, want_start, want_end = omoe.dispatch_plan(c['topk_idx'], experts, SEGMENT)
     assert torch.equal(dest, want_dest), 'dispatch permutation must be bit-exact'
     assert torch.equal(start, want_start) and torch.equal(end, want_end)
     assert torch.equal(stats.cpu(), 5 + (want_end - want_start))
@@ -78,7 +79,7 @@ def test_masked_slots_empty_experts_and_clamp(dg):
                           c['l2_sf'], clamp=0.05)
     got, buf = _run_layer(dg, c, tokens, hidden, inter, experts, topk, clamp=0.05)
     dest, _, end = _plan_views(buf, tokens, topk, experts)
-    want_dest, _, _, want_end = omoe.dispatch_plan(c['topk_idx'], experts, 16)
+    want_dest, _, _, want_end = omoe.dispatch_plan(c['topk_idx'], experts, SEGMENT)
     assert torch.equal(dest, want_dest) and torch.equal(end, want_end)
     assert (dest[c['topk_idx'].reshape(-1) < 0] == -1).all()
     assert quant.calc_diff(got, want) <= FP4_TOL
@@ -134,7 +135,7 @@ def test_full_config_permutation_and_sampled_tokens(dg):
     idx = buf.topk_idx.cpu()
     assert torch.equal(idx, want_idx)
     dest, start, end = _plan_views(buf, tokens, topk, experts)
-    want_dest, _, want_start, want_end = omoe.dispatch_plan(idx, experts, 16)
+    want_dest, _, want_start, want_end = omoe.dispatch_plan(idx, experts, SEGMENT)
     assert torch.equal(dest, want_dest) and torch.equal(end, want_end)
     assert not torch.isnan(y.float()).any()
 

@@ -14,6 +14,7 @@ from tests.helpers import moe_case_nvfp4
 
 pytestmark = pytest.mark.gpu
 FP4_TOL = 2e-3
+SEGMENT = 128  # rows each expert's segment is padded to (dgb200_get_segment_alignment_for_mega_moe)
 
 
 @pytest.fixture(scope='module')
@@ -176,7 +177,7 @@ def test_layer_matches_oracle(dg, tokens, hidden, inter, experts, topk, masked):
     got, buf = _run_layer(dg, c, tokens, hidden, inter, experts, topk, act_scale)
     lay = buf.layout
     dest = buf.buffer[lay['dest_row']:lay['dest_row'] + tokens * topk * 4].view(torch.int32).cpu()
-    want_dest, _, _, _ = omoe.dispatch_plan(c['topk_idx'], experts, 16)
+    want_dest, _, _, _ = omoe.dispatch_plan(c['topk_idx'], experts, SEGMENT)
     assert torch.equal(dest, want_dest), 'dispatch permutation must be bit-exact'
     assert not torch.isnan(got.float()).any()
     assert quant.calc_diff(got, want) <= FP4_TOL

@@ -54,7 +54,7 @@ def test_noalloc_plan_matches_layer_plan_twice_in_a_row():
     for tokens, seed in ((700, 41), (90, 42)):  # 2800 entries = 3 chunks, then a single partial chunk
         case = moe_case(tokens, hidden, inter, experts, topk, seed=seed, masked_ratio=0.2)
         want = _plan_from_layer(dg, case, tokens, hidden, inter, experts, topk)
-        got = _plan_noalloc(case['topk_idx'], experts, 16)
+        got = _plan_noalloc(case['topk_idx'], experts, dg.get_segment_alignment_for_mega_moe())
         for g, w, name in zip(got, want, ('dest_row', 'expert_start', 'expert_end')):
             assert torch.equal(g, w), f'{name} differs from the layer call ({tokens} tokens)'
 
