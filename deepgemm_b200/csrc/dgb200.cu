@@ -57,6 +57,7 @@ struct GemmCall {
 
 // Process-wide tuning knobs (defaults are the measured best on B200).
 struct Tuning {
+    int prefetch_distance = 0;
     int block_n = 0;  // 0 = automatic
     int debug_skip = 0;
     long long* trace = nullptr;  // debugging: per-role clock64() samples of CTA 0 (8 roles x trace_cap)
@@ -152,6 +153,7 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
         p.tma_store = c.whole_tile_stores ? 2 : 1;
     }
 
+    p.prefetch_distance = tuning().prefetch_distance;
     p.debug_skip = tuning().debug_skip;
     p.trace = tuning().trace;
     p.trace_cap = tuning().trace_cap;
@@ -592,7 +594,10 @@ int dgb200_set_num_sms(int num_sms) {
 
 int dgb200_set_tuning(const char* name, int32_t value) {
     DGB_REQUIRE(name != nullptr, "null name");
-    if (std::strcmp(name, "block_n") == 0) {
+    if (std::strcmp(name, "prefetch_distance") == 0) {
+        DGB_REQUIRE(value >= 0 && value <= 4096, "prefetch_distance must be in [0, 4096]");
+        tuning().prefetch_distance = value;
+    } else if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
     } else if (std::strcmp(name, "debug_skip") == 0) {

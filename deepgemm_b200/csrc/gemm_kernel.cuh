@@ -62,6 +62,7 @@ struct GemmParams {
     unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
     unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
     int store_padding;       // psum only: also write the rows between a group's end and its aligned end
+    int prefetch_distance;   // K blocks the weight loader's L2 prefetch cursor runs ahead of its loads (0 = off)
     int debug_skip;          // timing experiments only (results become garbage): bit 0 no A loads, 1 no B loads,
                              // 2 no scale-factor loads, 3 no MMA instructions, 4 no scale-factor TMEM copies
     long long* trace;        // optional: CTA 0 records clock64() per role and K block at trace[role * trace_cap + i]
@@ -392,20 +393,46 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             bool ok = true;
             int trace_i = 0;
 
+            // L2 prefetch cursor: weight tiles are read once from HBM, and the few stages that fit in shared memory do
+            // not cover that latency. The cursor walks the same (tile, K block) sequence p.prefetch_distance blocks
+            // ahead of the loads and asks TMA to bring each weight tile into L2 (no shared memory, no barrier).
+            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
+            Tile pt;
+            int pf_kb = 0, pf_row = 0;
+            bool pf_valid = false;
+            auto pf_next_tile = [&]() {
+                pf_valid = false;
+                while (pf_sched.next(pt)) {
+                    if (pt.group >= 0) { pf_valid = true; break; }
+                }
+                pf_kb = 0;
+                pf_row = pt.group * p.n + pt.n_block * BLOCK_N;
+            };
+            auto pf_advance = [&](bool issue) {
+                if (!pf_valid) return;
+                if (issue) tma_prefetch_2d(&tm_b, pf_kb * 128, pf_row);
+                if (++pf_kb == num_kb) pf_next_tile();
+            };
+            const bool leader = elect_one();
+            if (p.prefetch_distance > 0) {
+                pf_next_tile();
+                for (int i = 0; i < p.prefetch_distance; ++i) pf_advance(leader);
+            }
+
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int b_row = t.group * p.n + t.n_block * BLOCK_N;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    if (elect_one()) {
+                    if (leader) {
                         trace_point(p, 9, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes);
                         if (!DGB_SKIP(p, 2))
                             tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
                         trace_point(p, 10, trace_i);
                     }
-                    __syncwarp();
+                    if (p.prefetch_distance > 0) pf_advance(leader);
                     ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -425,6 +452,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
         uint32_t tmem_sfa = 0, tmem_sfb = 0;  // TMEM columns holding the scale factors of the current K block
+        const bool leader = elect_one();      // the same lane issues every tcgen05 instruction of this CTA
         bool ok = true;
         if (lane == 0) trace_point(p, 14, 0);
         while (ok && sched.next(t)) {
@@ -445,7 +473,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 if (lane == 0) trace_point(p, 11, trace_i);
                 // No tcgen05 fence here: the data this wait covers was written to shared memory through the async proxy
                 // (TMA, or the transposer's stores followed by its proxy fence), not by tcgen05 operations.
-                if (elect_one()) {
+                if (leader) {
                     trace_point(p, 4, trace_i);
                     // One tcgen05.cp moves the scales of 128 rows for one MMA (one packed int per row) into 4 TMEM columns.
                     const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
@@ -485,7 +513,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
                     trace_point(p, 5, trace_i);
                 }
-                __syncwarp();
                 ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
