@@ -43,6 +43,9 @@ def parse_args():
     ap.add_argument('--skip-cpu-baseline', action='store_true')
     ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
                     help='nvfp4xnvfp4 runs the NVFP4 prefill variant (16384 tokens) instead of the headline workload')
+    ap.add_argument('--workload', default='layer', choices=['layer', 'gemm_contiguous', 'gemm_masked'],
+                    help='gemm_contiguous / gemm_masked time the stand-alone grouped GEMMs of BASELINE configs 1 and 2 '
+                         '(one GPU, not the headline line)')
     return ap.parse_args()
 
 
@@ -248,6 +251,84 @@ def build_layer_nvfp4(dg, cfg):
     return l1, l2
 
 
+def run_gemm_workload(args):
+    """BASELINE configs 1 (m-grouped contiguous, 4 experts, N 512, K 1024) and 2 (masked decode GEMM, 32 experts,
+    Poisson(64) rows, N 4096, K 7168), FP8 1x128 activations x MXFP4 1x32 weights, bf16 output. Every timed launch is
+    preceded by a 512 MB write that flushes L2; times are per-launch CUDA events."""
+    import torch
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+    torch.manual_seed(0)
+    masked = args.workload == 'gemm_masked'
+    g, n, k = (32, 4096, 7168) if masked else (4, 512, 1024)
+    w_q = torch.empty((g, n, k // 2), dtype=torch.int8, device='cuda')
+    w_sf = torch.empty((g, n, k // 32), dtype=torch.float32, device='cuda')
+    for e in range(g):
+        w_q[e], w_sf[e] = dg.utils.per_token_cast_to_fp4(torch.randn(n, k, device='cuda', dtype=torch.bfloat16) * 0.02,
+                                                         use_ue8m0=True, gran_k=32)
+    w_sf = dg.transform_sf_into_required_layout(w_sf, n, k, (1, 32), g)  # packed once, as a deployment would
+    if masked:
+        max_m = 256
+        counts = torch.poisson(torch.full((g,), 64.0)).clamp(0, max_m).to(torch.int32)
+        a = torch.randn(g * max_m, k, device='cuda', dtype=torch.bfloat16)
+        a_q, a_sf = dg.utils.per_token_cast_to_fp8(a, use_ue8m0=True, gran_k=128)
+        a_q = a_q.view(g, max_m, k)
+        a_sf = dg.transform_sf_into_required_layout(a_sf.view(g, max_m, k // 128), max_m, k, (1, 128), g)
+        d = torch.empty((g, max_m, n), dtype=torch.bfloat16, device='cuda')
+        layout = counts.cuda()
+        rows = int(counts.sum())
+        call = lambda: dg.m_grouped_fp8_fp4_gemm_nt_masked((a_q, a_sf), (w_q, w_sf), d, layout, 64, recipe_a=(1, 128), recipe_b=(1, 32))
+    else:
+        ms = torch.randint(64, 257, (g,))
+        aligned = (ms + 127) // 128 * 128
+        m = int(aligned.sum())
+        row_ids = torch.full((m,), -1, dtype=torch.int32)
+        start = 0
+        for e in range(g):
+            row_ids[start:start + int(ms[e])] = e
+            start += int(aligned[e])
+        a = torch.randn(m, k, device='cuda', dtype=torch.bfloat16)
+        a_q, a_sf = dg.utils.per_token_cast_to_fp8_mn_major(a, gran_k=128)
+        d = torch.empty((m, n), dtype=torch.bfloat16, device='cuda')
+        layout = row_ids.cuda()
+        rows = int(ms.sum())
+        call = lambda: dg.m_grouped_fp8_fp4_gemm_nt_contiguous((a_q, a_sf), (w_q, w_sf), d, layout, recipe_a=(1, 128), recipe_b=(1, 32))
+    flush = torch.empty(512 << 20, dtype=torch.int8, device='cuda')
+    for _ in range(max(args.warmup, 3)):
+        call()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    total = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        call()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    _lib.device_status()
+    ms_per = total / args.steps
+    peak, peak_kind = measured_peaks()
+    flops = 2.0 * rows * n * k
+    touched = g if not masked else int((counts > 0).sum())
+    nbytes = touched * (n * k // 2 + n * k // 32) + rows * (k + k // 128 + 2 * n)
+    print(json.dumps({
+        'metric': 'grouped_gemm_us', 'value': ms_per * 1e3, 'unit': 'us', 'n_gpus': 1, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': ms_per, 'higher_is_better': False, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'fp8xfp4 (fp32 accumulate)', 'data': 'synthetic',
+        'config': {'workload': ('m-grouped masked FP8xMXFP4 decode GEMM (BASELINE config 2)' if masked else
+                                'm-grouped contiguous FP8xMXFP4 GEMM (BASELINE config 1)'),
+                   'groups': g, 'n': n, 'k': k, 'valid_rows': rows, 'l2_policy': 'L2 flushed by a 512 MB write before every launch'},
+        'gpu_launches': args.steps, 'clocks': clocks, 'tflops': flops / (ms_per * 1e-3) / 1e12,
+        'roofline': {'kernel': 'dgb200_grouped_gemm_kernel', 'bound': 'hbm', 'achieved': nbytes / (ms_per * 1e-3) / 1e9, 'peak': peak,
+                     'unit': 'GB/s', 'frac': nbytes / (ms_per * 1e-3) / 1e9 / peak, 'peak_source': peak_kind, 'traffic': None,
+                     'algorithmic_bytes': nbytes},
+    }), flush=True)
+
+
 def run_ours(args, cfg, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -449,6 +530,11 @@ def main():
         cfg['tokens'] = args.tokens
     if args.experts:
         cfg['experts'] = args.experts
+    if args.workload != 'layer':
+        if args.impl == 'reference' or args.gpus != 1:
+            raise SystemExit('--workload gemm_* is a single-GPU timing of our kernels only')
+        run_gemm_workload(args)
+        return
     if args.impl == 'reference':
         if args.mma != 'fp8xfp4':
             raise SystemExit('--impl reference times the headline FP8 x MXFP4 workload only')
