@@ -363,22 +363,22 @@ def run_ours(args, cfg, rank, world, local_rank):
     logits = logits_host.cuda()
     y = torch.empty((t, h), dtype=torch.bfloat16, device='cuda')
     lib = _lib.lib()
-    kernels_per_step = 9  # router, cast, count, scan, assign, gather, L1, L2, combine (the one memset is not a kernel of ours)
+    # single rank: router, count, scan, assign, quantise + dispatch, L1, L2, combine (the memset is not a kernel of ours);
+    # NVFP4 keeps a separate cast and gather; expert parallel adds the count exchange, the plan and three barriers
+    kernels_per_step = 9 if nvfp4 else (8 if world == 1 else 12)
 
     def step(events=None, x_in=None, logits_in=None, y_out=None):
         x_in, logits_in, y_out = (x if x_in is None else x_in), (logits if logits_in is None else logits_in), (y if y_out is None else y_out)
-        dg.route_sigmoid_topk(logits_in, k, buf.topk_idx, buf.topk_weights)
-        if nvfp4:
-            dg.per_token_cast_to_nvfp4_into(x_in, x_scale, buf.x, buf.x_sf)
-        else:
-            dg.utils.per_token_cast_to_fp8_into(x_in, buf.x, buf.x_sf, gran_k=32)
         if events is not None:
             arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
             _lib.check(lib.dgb200_set_mega_moe_stage_events(ctypes.cast(arr, ctypes.c_void_p), len(events)))
         if nvfp4:
+            dg.route_sigmoid_topk(logits_in, k, buf.topk_idx, buf.topk_weights)
+            dg.per_token_cast_to_nvfp4_into(x_in, x_scale, buf.x, buf.x_sf)
             dg.nvfp4_mega_moe(y_out, l1, l2, buf, x_scale, act_scale)
         else:
-            dg.fp8_fp4_mega_moe(y_out, l1, l2, buf)
+            # router -> dispatch plan -> BF16 rows quantised to FP8 while they are dispatched -> L1 -> L2 -> combine
+            dg.fp8_fp4_mega_moe_bf16_input(y_out, x_in, l1, l2, buf, logits=logits_in)
 
     def barrier():
         if world > 1:
@@ -489,8 +489,8 @@ def run_ours(args, cfg, rank, world, local_rank):
         'roofline': {'kernel': 'dgb200_grouped_gemm_kernel (L1: gate/up GEMM + SwiGLU + FP8 requant)', 'bound': 'hbm',
                      'achieved': l1_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': l1_gbs / peak, 'peak_source': peak_kind,
                      'traffic': int(L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * l1_bytes), 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]},
-        'stages_ms': {'plan': stage_ms[0], 'gather': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
-                      'l2_gemm_scatter': stage_ms[3], 'combine': stage_ms[4]},
+        'stages_ms': {'plan': stage_ms[0], 'dispatch': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
+                      'l2_gemm': stage_ms[3], 'combine': stage_ms[4]},
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9,
         'tflops': tflops,
         'frac_fp4_dense_peak_nominal': tflops / (FP4_DENSE_PEAK_TFLOPS_NOMINAL * world),
@@ -501,7 +501,8 @@ def run_ours(args, cfg, rank, world, local_rank):
     if world == 1 and not args.skip_cpu_baseline:
         idx, w = buf.topk_idx[:t].cpu(), buf.topk_weights[:t].cpu()
         from oracle import quant
-        x_q_c, x_sf_c = buf.x[:t].cpu(), quant.unpack_ue8m0(buf.x_sf[:t].cpu())
+        x_q_g, x_sf_g = dg.utils.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32, use_packed_ue8m0=True)
+        x_q_c, x_sf_c = x_q_g.cpu(), quant.unpack_ue8m0(x_sf_g.cpu())
         sample = dict(cpu_weights)
         sample.update({'x_q': [], 'x_sf': [], 'w': []})
         for g in range(CPU_SAMPLE_EXPERTS):

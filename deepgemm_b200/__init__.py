@@ -6,6 +6,10 @@ path it covers; use ``import deepgemm_b200 as deep_gemm``. Every operator calls 
 """
 from . import _lib, testing, utils  # noqa: F401
 from .gemm import (  # noqa: F401
+    fp8_fp4_gemm_nn,
+    fp8_fp4_gemm_nt,
+    fp8_gemm_nn,
+    fp8_gemm_nt,
     m_grouped_fp8_fp4_gemm_nn_contiguous,
     m_grouped_fp8_fp4_gemm_nt_contiguous,
     m_grouped_fp8_fp4_gemm_nt_masked,
@@ -21,6 +25,7 @@ from .layout import (  # noqa: F401
 from .mega import (  # noqa: F401
     SymmBuffer,
     fp8_fp4_mega_moe,
+    fp8_fp4_mega_moe_bf16_input,
     get_block_m_for_mega_moe,
     get_segment_alignment_for_mega_moe,
     get_symm_buffer_for_mega_moe,

@@ -39,9 +39,13 @@ _SIGNATURES = {
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_route_sigmoid_topk': [_ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr],
     'dgb200_get_token_alignment_for_mega_moe': [],
+    'dgb200_fp8_fp4_gemm_nt': [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_segment_alignment_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_fp8_fp4_mega_moe_bf16_input': [
+        _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+        _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
     'dgb200_nvfp4_mega_moe': [
         _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],

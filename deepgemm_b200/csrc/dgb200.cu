@@ -78,7 +78,8 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     DGB_REQUIRE(p.gran_a == 32 || p.gran_a == 128, "gran_k_a must be 32 or 128, got %d", p.gran_a);
     DGB_REQUIRE(p.gran_b == 32 || p.gran_b == 128, "gran_k_b must be 32 or 128, got %d", p.gran_b);
     DGB_REQUIRE(p.num_groups > 0, "num_groups must be positive");
-    DGB_REQUIRE(c.a != nullptr && c.b != nullptr && c.sfa != nullptr && c.sfb != nullptr && p.layout != nullptr,
+    DGB_REQUIRE(c.a != nullptr && c.b != nullptr && c.sfa != nullptr && c.sfb != nullptr &&
+                    (p.layout != nullptr || p.mode == kModeDense),
                 "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.a) % 16 == 0, "a must be 16-byte aligned");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(c.b) % 32 == 0, "b must be 32-byte aligned");
@@ -166,6 +167,7 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 
     if (c.max_tiles > 0 && block_n == 256) grid = std::min(grid, std::max(1, c.max_tiles / 2));
 #define DGB_LAUNCH(EPI, KIND)                                                                                   \
+    if (block_n == 256 && tuning().debug_skip >= 1000) return launch_gemm<256, 3, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream); \
     return block_n == 256 ? launch_gemm<256, 4, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream)            \
                           : launch_gemm<128, 6, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream)
     if (nvfp4) {
@@ -224,6 +226,10 @@ struct LayerQuant {
     const float* act_scale = nullptr;  // calibrated scale the post-SwiGLU activations are quantised against
     const float* l1_scales = nullptr;  // [local experts] scales of the gate/up weights
     const float* l2_scales = nullptr;  // [local experts] scales of the down weights
+    // FP8 kind only: take the activations as BF16 rows and quantise them while dispatching (the buffer's x / x_sf
+    // views are then neither read nor written)
+    const __nv_bfloat16* x_bf16 = nullptr;
+    long long x_bf16_row_stride = 0;
 };
 
 // Bytes of one quantised activation row of `width` elements, and packed scale ints (4 scale bytes each) per row.
@@ -440,9 +446,15 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         dgb200_ep_assign_kernel<<<chunks, kPlanChunk, 32 * num_experts, stream>>>(topk_idx, entries, num_experts, chunk_hist,
                                                                               reinterpret_cast<const int*>(base + l.my_base), dest_row);
         if ((rc = record_stage(1, stream))) return rc;
-        dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
-            base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
-            static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_ints_per_row(quant.kind, hidden), l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row);
+        if (quant.x_bf16 != nullptr)
+            dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
+                quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden,
+                l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 1);
+        else
+            dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
+                base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
+                static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_ints_per_row(quant.kind, hidden), l.num_local_experts, rank,
+                entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row);
     } else if ((rc = record_stage(1, stream))) {
         return rc;
     }
@@ -516,9 +528,18 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
     const long long upper_rows = std::min<long long>(l.max_rows, static_cast<long long>(entries) + static_cast<long long>(E) * kSegmentAlignment);
     const int gather_blocks = static_cast<int>((upper_rows + 31) / 32);
     const int sf_per_row = sf_ints_per_row(quant.kind, hidden);
-    dgb200_moe_gather_kernel<<<gather_blocks, 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
-        base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk,
-        static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, base + l.l1_acts, reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
+    if (quant.x_bf16 != nullptr) {
+        PeerTable self_table{};
+        for (int r = 0; r < kMaxEpRanks; ++r) self_table.p[r] = reinterpret_cast<unsigned long long>(base);
+        dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
+            quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden, num_experts, 0,
+            entries, self_table, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 0);
+    } else {
+        dgb200_moe_gather_kernel<<<gather_blocks, 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
+            base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk,
+            static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, base + l.l1_acts,
+            reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
+    }
     DGB_CUDA(cudaGetLastError());
 
     if ((rc = record_stage(2, stream))) return rc;
@@ -683,6 +704,41 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
     return run_gemm(c, static_cast<cudaStream_t>(stream));
 }
 
+int dgb200_fp8_fp4_gemm_nt(const void* a, const void* sfa, int64_t sfa_k_stride, const void* b, const void* sfb,
+                           int64_t sfb_k_stride, void* d, int64_t d_row_stride, int32_t m, int32_t n, int32_t k,
+                           int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream) {
+    DGB_REQUIRE(m >= 0, "m must be >= 0");
+    DGB_REQUIRE(d != nullptr || m == 0, "null output");
+    DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
+                "d row stride must cover n and keep rows 16-byte aligned");
+    DGB_REQUIRE(sfa_k_stride >= m, "sfa MN stride (%lld) smaller than m (%d)", static_cast<long long>(sfa_k_stride), m);
+    GemmCall c{};
+    c.a = a;
+    c.b = b;
+    c.a_rows_total = m;
+    c.b_is_fp4 = b_is_fp4;
+    c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
+    c.sfa = sfa;
+    c.sfb = sfb;
+    c.sfa_k_stride = sfa_k_stride;
+    c.num_groups_a = 1;
+    c.sfb_k_stride = sfb_k_stride;
+    GemmParams& p = c.p;
+    p.d = d;
+    p.d_row_stride = d_row_stride;
+    p.mode = kModeDense;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.num_groups = 1;
+    p.alignment = 128;
+    p.gran_a = gran_k_a;
+    p.gran_b = gran_k_b;
+    const long long m_blocks = (static_cast<long long>(m) + 127) / 128;
+    c.max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
+    return run_gemm(c, static_cast<cudaStream_t>(stream));
+}
+
 int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
     const void* a, const void* sfa, int64_t sfa_k_stride, int64_t sfa_group_stride,
     const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
@@ -809,6 +865,32 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                             int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                             float activation_clamp, int32_t fast_math, void* stream) {
     LayerQuant quant;
+    return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
+                        num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
+                        activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_fp8_fp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_stride, const float* logits, const void* l1_w,
+                                       const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+                                       int32_t* cumulative_local_expert_recv_stats, void* buffer,
+                                       const uint64_t* peer_buffer_ptrs, int32_t rank, int32_t num_ranks, int32_t num_tokens,
+                                       int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
+                                       int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream) {
+    DGB_REQUIRE(x != nullptr && reinterpret_cast<uintptr_t>(x) % 16 == 0 && x_row_stride >= hidden && (x_row_stride * 2) % 16 == 0,
+                "x must be 16-byte aligned BF16 rows of at least `hidden` elements");
+    if (logits != nullptr && num_tokens > 0) {
+        MegaLayout l;
+        int rc = make_mega_layout(kKindFp8Fp4, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
+        if (rc) return rc;
+        DGB_REQUIRE(buffer != nullptr && num_tokens <= num_max_tokens_per_rank, "bad buffer or token count");
+        uint8_t* base = static_cast<uint8_t*>(buffer);
+        rc = dgb200_route_sigmoid_topk(logits, num_tokens, num_experts, num_topk, reinterpret_cast<int64_t*>(base + l.topk_idx),
+                                       reinterpret_cast<float*>(base + l.topk_weights), stream);
+        if (rc) return rc;
+    }
+    LayerQuant quant;
+    quant.x_bf16 = static_cast<const __nv_bfloat16*>(x);
+    quant.x_bf16_row_stride = x_row_stride;
     return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
                         num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
                         activation_clamp, fast_math, static_cast<cudaStream_t>(stream));

@@ -16,7 +16,7 @@
 //   * Stores are clipped to the valid rows of a group, so a masked group never writes into its neighbour.
 //   * Every wait is bounded; a timeout unwinds the CTA and is reported through the status block.
 //
-// Warp roles (384 threads): warp 0 loads A tiles and both scale-factor rows, warp 3 loads the weight tiles, warp 1
+// Warp roles (384 threads): warp 0 loads A tiles and their scale factors, warp 3 the weight tiles and theirs, warp 1
 // issues the MMAs, warp 2 allocates TMEM and (only for scale factors in plain row order) transposes them for tcgen05.cp,
 // warps 4-11 are the epilogue (TMEM lane quarter = warp index % 4, two warps per quarter splitting the columns).
 // The control warpgroup hands registers to the epilogue warpgroups with setmaxnreg.
@@ -33,6 +33,7 @@ enum GroupMode : int {
     kModeRowIds = 0,  // layout[m] = group of row m, -1 on padding rows (segments aligned to `alignment`)
     kModePsum = 1,    // layout[g] = end row of group g; group g starts at align(layout[g-1], alignment)
     kModeMasked = 2,  // A/D are [G, max_m, *]; layout[g] = valid rows of group g
+    kModeDense = 3,   // one group covering rows [0, m); no layout array
 };
 
 enum EpilogueKind : int {
@@ -149,14 +150,14 @@ struct TileScheduler {
 
     // Returns false when this CTA has no more tiles. A tile with group < 0 must be skipped by every role.
     __device__ bool next(Tile& t) {
-        if (p.mode == kModeRowIds) {
+        if (p.mode == kModeRowIds || p.mode == kModeDense) {
             const int num_m_blocks = (p.m + 127) / 128;
             if (tile >= num_m_blocks * num_n_blocks) return false;
             const int mb = tile / num_n_blocks;
             t.n_block = tile - mb * num_n_blocks;
             t.row_start = t.sf_row_start = mb * 128;
             t.rows_store = min(128, p.m - t.row_start);
-            t.group = __ldg(p.layout + t.row_start);
+            t.group = p.mode == kModeDense ? 0 : __ldg(p.layout + t.row_start);
             tile += static_cast<int>(gridDim.x);
             return true;
         }
@@ -299,7 +300,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     int* group_cache = reinterpret_cast<int*>(smem + L::kOffGroups);
     int* group_start = group_cache + kMaxCachedGroups;
     int* group_tiles_end = group_start + kMaxCachedGroups;
-    const bool cache_groups = p.mode != kModeRowIds && p.num_groups <= kMaxCachedGroups;
+    const bool cache_groups = (p.mode == kModePsum || p.mode == kModeMasked) && p.num_groups <= kMaxCachedGroups;
     if (cache_groups) {
         for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) {
             int start, rows, rows_store;
@@ -343,7 +344,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     if (warp < 4) {
     setmaxnreg_dec<kRegsControlWarps>();
     if (warp == 0) {
-        // ---------------------------------------------------------------- loader: A tile + both scale-factor rows
+        // ---------------------------------------------------------------- loader: A tile + its scale factors
         // TMA instructions cost on the order of 100 cycles each in the issuing thread, so the loads of one stage are
         // split over two threads (this one and warp 3); both arrive on the stage's full barrier with their own bytes.
         // The whole warp walks the schedule with warp-uniform values and one elected lane issues: TMA and tcgen05
@@ -357,25 +358,20 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             int trace_i = 0;
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
-                const int sfa_y = t.group * p.sfa_group_rows, sfb_y = t.group * p.sfb_packed_k;
+                const int sfa_y = t.group * p.sfa_group_rows;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfa = kb % a_per == 0 && !DGB_SKIP(p, 4), load_sfb = kb % b_per == 0 && !DGB_SKIP(p, 4);
+                    const bool load_sfa = kb % a_per == 0 && !DGB_SKIP(p, 4);
                     if (elect_one()) {
                         trace_point(p, 0, trace_i);
-                        mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) +
-                                                                    (load_sfa ? L::kSfaBytes : 0) +
-                                                                    (load_sfb ? L::kSfbBytes : 0));
+                        mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) + (load_sfa ? L::kSfaBytes : 0));
                         if (!DGB_SKIP(p, 1))
                             tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128,
                                         t.row_start);
                         if (load_sfa)
                             tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage,
                                         t.sf_row_start, sfa_y + kb * kSfInts / a_per);
-                        if (load_sfb)
-                            tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
-                                        t.n_block * BLOCK_N, sfb_y + kb * kSfInts / b_per);
                         trace_point(p, 1, trace_i);
                     }
                     __syncwarp();
@@ -385,7 +381,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             }
         }
     } else if (warp == 3) {
-        // ---------------------------------------------------------------- loader: B (weight) tile
+        // ---------------------------------------------------------------- loader: B (weight) tile + its scale factors
         {
             TileScheduler<BLOCK_N> sched(p, group_layout);
             Tile t;
@@ -422,14 +418,19 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int b_row = t.group * p.n + t.n_block * BLOCK_N;
+                const int sfb_y = t.group * p.sfb_packed_k;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
+                    const bool load_sfb = kb % b_per == 0 && !DGB_SKIP(p, 4);
                     if (leader) {
                         trace_point(p, 9, trace_i);
-                        mbar_arrive_expect_tx(full_bar + stage, DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes);
+                        mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes) + (load_sfb ? L::kSfbBytes : 0));
                         if (!DGB_SKIP(p, 2))
                             tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
+                        if (load_sfb)
+                            tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
+                                        t.n_block * BLOCK_N, sfb_y + kb * kSfInts / b_per);
                         trace_point(p, 10, trace_i);
                     }
                     if (p.prefetch_distance > 0) pf_advance(leader);

@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 
 #include "ptx.cuh"
+#include "quant_kernels.cuh"
 
 namespace dgb {
 
@@ -425,6 +426,84 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
     if (lane == 0) {
         reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
         reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;
+    }
+}
+
+// Fused activation quantisation + dispatch (the step the reference leaves to torch ops before its layer call,
+// README.md:72: per_token_cast_to_fp8 into the buffer, then the in-kernel dispatch pull): one warp per token reads the
+// BF16 row once, quantises it to E4M3 with one UE8M0 scale per 32 elements (the arithmetic of
+// dgb200_cast_rows_kernel<false>, i.e. per_token_cast_to_fp8(use_ue8m0=True, gran_k=32)) and writes row and packed
+// scales straight into each of its top-k destination rows of the expert-sorted buffers, on this rank or a peer.
+// `write_meta` also stores the routing weight and the source entry next to the row (the expert-parallel push does
+// that; on a single rank the plan kernels already have).
+__global__ void __launch_bounds__(256)
+dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long x_row_stride,
+                                 const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights,
+                                 const int* __restrict__ dest_row, int tokens, int topk, int hidden, int experts_per_rank,
+                                 int my_rank, int entries_per_rank, const PeerTable peers, long long acts_offset,
+                                 long long sf_offset, long long sf_k_stride, long long weight_offset, long long src_offset,
+                                 int write_meta) {
+    const int lane = threadIdx.x & 31;
+    const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (token >= tokens) return;
+    int my_dest = -1;
+    unsigned long long my_base = 0;
+    if (lane < topk) {
+        const int entry = token * topk + lane;
+        const int d = dest_row[entry];
+        if (d >= 0) {
+            my_dest = d;
+            my_base = peers.p[static_cast<int>(topk_idx[entry]) / experts_per_rank];
+            if (write_meta) {
+                reinterpret_cast<float*>(my_base + weight_offset)[d] = topk_weights[entry];
+                reinterpret_cast<int*>(my_base + src_offset)[d] = my_rank * entries_per_rank + entry;
+            }
+        }
+    }
+    const __nv_bfloat16* row = x + static_cast<long long>(token) * x_row_stride;
+    for (int col0 = 0; col0 < hidden; col0 += 512) {
+        const int col = col0 + lane * 16;
+        const bool valid = col < hidden;  // hidden is a multiple of 128
+        float v[16];
+        if (valid) {
+            const uint4* src = reinterpret_cast<const uint4*>(row + col);
+            const uint4 r0 = ld_global_nc_v4(src), r1 = ld_global_nc_v4(src + 1);
+            const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // two lanes share a 32-element scale group
+        const uint32_t e = ue8m0_ceil_bits(fmaxf(amax, 1e-4f) / 448.0f);
+        const float inv = 1.0f / __uint_as_float(e << 23);
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_fp8x4_e4m3 q4(make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv));
+            o[i] = q4.__x;
+        }
+        // packed scale int of 128 elements = the scale bytes of lanes L, L + 2, L + 4, L + 6 (L a multiple of 8)
+        const uint32_t e2 = __shfl_down_sync(0xffffffffu, e, 2), e4 = __shfl_down_sync(0xffffffffu, e, 4),
+                       e6 = __shfl_down_sync(0xffffffffu, e, 6);
+        const uint32_t sf_int = e | (e2 << 8) | (e4 << 16) | (e6 << 24);
+        for (int k = 0; k < topk; ++k) {
+            const int d = __shfl_sync(0xffffffffu, my_dest, k);
+            const unsigned long long base = __shfl_sync(0xffffffffu, my_base, k);
+            if (d < 0 || !valid) continue;
+            st_global_v4(reinterpret_cast<unsigned char*>(base + acts_offset) + static_cast<long long>(d) * hidden + col, o[0], o[1],
+                         o[2], o[3]);
+            if ((lane & 7) == 0)
+                reinterpret_cast<unsigned*>(base + sf_offset)[static_cast<long long>(col >> 7) * sf_k_stride + sf_row_in_cp_order(d)] =
+                    sf_int;
+        }
     }
 }
 

@@ -34,6 +34,42 @@ def _check_d(d: torch.Tensor, shape):
         raise RuntimeError('d must be a CUDA bfloat16 tensor with unit stride on N')
 
 
+def fp8_fp4_gemm_nt(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor, torch.Tensor], d: torch.Tensor,
+                    c: Optional[torch.Tensor] = None, recipe: Optional[Tuple[int, int, int]] = None,
+                    recipe_a: Optional[Tuple[int, int]] = None, recipe_b: Optional[Tuple[int, int]] = None,
+                    compiled_dims: str = 'nk', disable_ue8m0_cast: bool = False) -> None:
+    """Dense D = A @ B.T with a [M, K] FP8 and b [N, K] FP8 or packed FP4; d bfloat16 or float32.
+    Reference: fp8_fp4_gemm_nt, csrc/apis/gemm.hpp:73-124. The accumulator input ``c`` is not built."""
+    del compiled_dims
+    if c is not None:
+        raise RuntimeError('accumulation into c is not built')
+    a_q, a_sf = a
+    b_q, b_sf = b
+    if a_q.dtype != torch.float8_e4m3fn:
+        raise RuntimeError('a must be float8_e4m3fn')
+    m, k = _check_ab(a_q, 2, 'a')
+    n, k_ = _check_ab(b_q, 2, 'b')
+    if k != k_:
+        raise RuntimeError(f'K mismatch: a has {k}, b has {k_}')
+    if tuple(d.shape) != (m, n) or d.dtype not in (torch.bfloat16, torch.float32) or not d.is_cuda or d.stride(-1) != 1:
+        raise RuntimeError(f'd must be a CUDA bfloat16 / float32 [{m}, {n}] tensor with unit stride on N')
+    if m == 0:
+        return
+    sfa, sfb, gran_a, gran_b = transform_sf_pair_into_required_layout(
+        a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, None, disable_ue8m0_cast)
+    with torch.cuda.device(d.device):
+        _lib.check(_lib.lib().dgb200_fp8_fp4_gemm_nt(
+            _p(a_q), _p(sfa), sfa.stride(-1), _p(b_q), _p(sfb), sfb.stride(-1), _p(d), d.stride(0), m, n, k, gran_a, gran_b,
+            int(b_q.dtype == kPackedFP4), int(d.dtype == torch.float32), _lib.current_stream_ptr()))
+
+
+def fp8_fp4_gemm_nn(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = 'nk',
+                    disable_ue8m0_cast: bool = False) -> None:
+    """b given as [K, N] over K-major storage (reference: csrc/apis/gemm.hpp:126-137 transposes and calls the NT form)."""
+    fp8_fp4_gemm_nt(a, (b[0].transpose(0, 1), b[1].transpose(0, 1)), d, c, recipe, recipe_a, recipe_b, compiled_dims,
+                    disable_ue8m0_cast)
+
+
 def m_grouped_fp8_fp4_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor, torch.Tensor],
                                          d: torch.Tensor, grouped_layout: torch.Tensor,
                                          recipe: Optional[Tuple[int, int, int]] = None,
@@ -122,6 +158,8 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a: Tuple[torch.Tensor, torch.Tensor], b: Tu
 
 
 # FP8-only names are the same entry points (reference: csrc/apis/gemm.hpp:711-717)
+fp8_gemm_nt = fp8_fp4_gemm_nt
+fp8_gemm_nn = fp8_fp4_gemm_nn
 m_grouped_fp8_gemm_nt_contiguous = m_grouped_fp8_fp4_gemm_nt_contiguous
 m_grouped_fp8_gemm_nn_contiguous = m_grouped_fp8_fp4_gemm_nn_contiguous
 m_grouped_fp8_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked

@@ -204,6 +204,41 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
             _lib.current_stream_ptr()))
 
 
+def fp8_fp4_mega_moe_bf16_input(y: torch.Tensor, x: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                                l2_weights: Tuple[torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
+                                logits: Optional[torch.Tensor] = None,
+                                cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                                activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
+    """``fp8_fp4_mega_moe`` with its prologue fused in (no reference counterpart: the reference's callers quantise x with
+    per_token_cast_to_fp8 into the buffer and route with torch ops, README.md:72, tests/test_mega_moe.py:124-125).
+    ``x`` is BF16 [num_tokens, hidden] and is quantised while it is dispatched; with ``logits`` the router fills the
+    buffer's ``topk_idx`` / ``topk_weights`` first, otherwise the caller has. Same bits as the separate steps."""
+    b = sym_buffer
+    if b.mma_type != 'fp8xfp4':
+        raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
+    num_local = b.num_experts // b.num_ranks
+    _check_weight(l1_weights[0], l1_weights[1], num_local, 2 * b.intermediate_hidden, b.hidden, 'l1_weights')
+    _check_weight(l2_weights[0], l2_weights[1], num_local, b.hidden, b.intermediate_hidden, 'l2_weights')
+    if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
+        raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and tuple(x.shape) == tuple(y.shape) and x.stride(1) == 1):
+        raise RuntimeError('x must be a CUDA bfloat16 [num_tokens, hidden] tensor with unit inner stride')
+    if logits is not None and not (logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous() and
+                                   tuple(logits.shape) == (y.size(0), b.num_experts)):
+        raise RuntimeError('logits must be a contiguous CUDA float32 [num_tokens, num_experts] tensor')
+    stats = cumulative_local_expert_recv_stats
+    if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == num_local and stats.is_contiguous()):
+        raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
+    ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.lib().dgb200_fp8_fp4_mega_moe_bf16_input(
+            p(y), p(x), x.stride(0), p(logits), p(l1_weights[0]), p(l1_weights[1]), p(l2_weights[0]), p(l2_weights[1]),
+            p(stats), p(b.buffer), ctypes.cast(ptrs, ctypes.c_void_p), b.rank, b.num_ranks, y.size(0),
+            b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden, b.intermediate_hidden,
+            float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math), _lib.current_stream_ptr()))
+
+
 def nvfp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor],
                    l2_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
                    x_scale: torch.Tensor, act_scale: torch.Tensor,

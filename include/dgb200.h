@@ -74,6 +74,12 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
     int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
     int32_t layout_kind, int32_t alignment, int32_t store_padding, void* stream);
 
+/* Dense D = A . B^T (one group, no layout array); operands and scales as in the grouped form above.
+ * Reference: fp8_fp4_gemm_nt, csrc/apis/gemm.hpp:73-124 (its optional accumulator input `c` is not built). */
+int dgb200_fp8_fp4_gemm_nt(const void* a, const void* sfa, int64_t sfa_k_stride, const void* b, const void* sfb,
+                           int64_t sfb_k_stride, void* d, int64_t d_row_stride, int32_t m, int32_t n, int32_t k,
+                           int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream);
+
 /* Masked layout: a [G, max_m, k], d [G, max_m, n], only rows < masked_m[g] of each group are computed and
  * written (stores are clipped at masked_m[g]; the reference writes whole tiles, see
  * deep_gemm/include/deep_gemm/scheduler/gemm.cuh:189-216).
@@ -183,6 +189,19 @@ int dgb200_fp8_fp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, cons
                             int32_t rank, int32_t num_ranks, int32_t num_tokens, int32_t num_max_tokens_per_rank,
                             int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                             float activation_clamp, int32_t fast_math, void* stream);
+
+/* The same layer with the two steps the reference leaves to its caller (README.md:72: quantise x with
+ * per_token_cast_to_fp8 into the buffer; tests/test_mega_moe.py:124-125: route with torch.topk) fused into its
+ * prologue: x is BF16 [num_tokens, hidden] (row stride in elements) and is quantised (E4M3, UE8M0 per 32) while it is
+ * dispatched, so the buffer's x / x_sf views are not used; with `logits` (float [num_tokens, num_experts], may be
+ * NULL) the sigmoid / top-k / renormalise router fills topk_idx and topk_weights first. Results are bit-identical to
+ * dgb200_per_token_cast_to_fp8 (gran 32) + dgb200_route_sigmoid_topk + dgb200_fp8_fp4_mega_moe. */
+int dgb200_fp8_fp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_stride, const float* logits, const void* l1_w,
+                                       const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
+                                       int32_t* cumulative_local_expert_recv_stats, void* buffer,
+                                       const uint64_t* peer_buffer_ptrs, int32_t rank, int32_t num_ranks, int32_t num_tokens,
+                                       int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
+                                       int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream);
 
 /* NVFP4 x NVFP4 form of the layer (no reference counterpart; the reference's layer is FP8 x MXFP4 only).
  * Buffer layout: same out[16] fields as dgb200_get_symm_buffer_layout_for_mega_moe; the caller writes

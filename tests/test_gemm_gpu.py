@@ -193,3 +193,28 @@ def test_empty_and_rejected_inputs(dg):
     with pytest.raises(RuntimeError):  # scale-factor extent does not match the recipe
         dg.m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, c['row_ids'].cuda(), recipe_a=(1, 32), recipe_b=(1, 32))
     _finish(dg)
+
+
+@pytest.mark.parametrize('m,n,k,b_fp4,out', [
+    (200, 512, 1024, True, torch.bfloat16),     # ragged M: the last tile is clipped at m
+    (384, 256, 512, False, torch.float32),      # FP8 x FP8, FP32 output, 256-wide tiles with whole-tile TMA... stores
+    (1, 128, 128, True, torch.bfloat16),
+])
+def test_dense_gemm(dg, m, n, k, b_fp4, out):
+    """fp8_fp4_gemm_nt = the grouped kernel with one group and no layout array."""
+    torch.manual_seed(m + n)
+    a = torch.randn(m, k).bfloat16()
+    b = (torch.randn(1, n, k) * 0.02).bfloat16()
+    a_q, a_sf = quant.quantize_fp8_per_token(a, 128)
+    b_q, b_sf = quantize_groups(b, 32 if b_fp4 else 128, b_fp4)
+    want, _ = ogemm.grouped_gemm_contiguous(a_q, a_sf, b_q, b_sf, torch.zeros(m, dtype=torch.int32), 128, 32 if b_fp4 else 128,
+                                            out_dtype=out)
+    d = torch.full((m, n), float('nan'), dtype=out, device='cuda')
+    dg.fp8_fp4_gemm_nt((a_q.cuda(), a_sf.cuda()), (b_q[0].cuda(), b_sf[0].cuda()), d, recipe_a=(1, 128),
+                       recipe_b=(1, 32 if b_fp4 else 128))
+    _finish(dg)
+    assert not torch.isnan(d.float()).any()
+    assert quant.calc_diff(d.cpu().float(), want.float()) <= (FP4_TOL if b_fp4 else FP8_TOL)
+    with pytest.raises(RuntimeError):
+        dg.fp8_fp4_gemm_nt((a_q.cuda(), a_sf.cuda()), (b_q[0].cuda(), b_sf[0].cuda()), d, c=d, recipe_a=(1, 128),
+                           recipe_b=(1, 32 if b_fp4 else 128))

@@ -57,11 +57,16 @@ def _worker(rank, world, port, results):
             status = _lib.device_status()
             assert status[0] == 0, status
             ys.append(y.cpu())
+        # third call: BF16 rows quantised while they are pushed to their owners must give the same bits
+        y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+        dg.fp8_fp4_mega_moe_bf16_input(y, c['x'].cuda(), l1, l2, buf, cumulative_local_expert_recv_stats=None)
+        assert _lib.device_status()[0] == 0
+        ys.append(y.cpu())
         lay = buf.layout
         end = buf.buffer[lay['expert_end']:lay['expert_end'] + per_rank * 4].view(torch.int32).cpu()
         start = buf.buffer[lay['expert_start']:lay['expert_start'] + per_rank * 4].view(torch.int32).cpu()
         dest = buf.buffer[lay['dest_row']:lay['dest_row'] + t * TOPK * 4].view(torch.int32).cpu()
-        results[rank] = dict(y0=ys[0], y1=ys[1], start=start, end=end, dest=dest, stats=stats.cpu())
+        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], start=start, end=end, dest=dest, stats=stats.cpu())
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -82,6 +87,7 @@ def test_two_rank_layer_matches_oracle():
         c, got = cases[rank], results[rank]
         want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
         assert torch.equal(got['y0'], got['y1']), 'two calls on the same buffer must give the same bits'
+        assert torch.equal(got['y0'], got['y_fused']), 'the fused prologue must give the same bits'
         assert not torch.isnan(got['y0'].float()).any()
         assert quant.calc_diff(got['y0'], want) <= 2e-3
         my_base, want_start, want_end = omoe.ep_plan(all_counts, rank, 128)

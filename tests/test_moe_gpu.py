@@ -151,3 +151,37 @@ def test_full_config_permutation_and_sampled_tokens(dg):
             a2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(l2_q[e].cpu(), l2_sf[e].cpu(), 32).T
             acc += a2.bfloat16().float()[0]
         assert quant.calc_diff(y[t].cpu(), acc.bfloat16()) <= FP4_TOL
+
+
+@pytest.mark.parametrize('tokens,hidden,inter,experts,topk,use_logits', [
+    (200, 512, 256, 8, 2, True),
+    (77, 1024, 128, 16, 4, False),
+    (130, 640, 256, 4, 3, True),      # hidden not a multiple of 512: the last column block is partial
+])
+def test_fused_prologue_gives_the_same_bits(dg, tokens, hidden, inter, experts, topk, use_logits):
+    """fp8_fp4_mega_moe_bf16_input (router + quantise-while-dispatching) must equal the separate steps bit for bit,
+    and the separate steps are checked against the oracle."""
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=100 + tokens, masked_ratio=0.0 if use_logits else 0.2)
+    l1, l2 = _device_weights(dg, c)
+    x = c['x'].cuda()
+    # separate steps: quantise into the buffer, route, layer
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    dg.utils.per_token_cast_to_fp8_into(x, buf.x, buf.x_sf, gran_k=32)
+    buf.topk_idx[:tokens].copy_(c['topk_idx'].cuda())
+    buf.topk_weights[:tokens].copy_(c['topk_weights'].cuda())
+    y_ref = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+    dg.fp8_fp4_mega_moe(y_ref, l1, l2, buf, fast_math=False)
+    # fused prologue on a fresh buffer
+    buf2 = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    if not use_logits:
+        buf2.topk_idx[:tokens].copy_(c['topk_idx'].cuda())
+        buf2.topk_weights[:tokens].copy_(c['topk_weights'].cuda())
+    y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+    dg.fp8_fp4_mega_moe_bf16_input(y, x, l1, l2, buf2, logits=c['logits'].cuda() if use_logits else None, fast_math=False)
+    from deepgemm_b200 import _lib
+    assert _lib.device_status()[0] == 0
+    if use_logits:
+        assert torch.equal(buf2.topk_idx[:tokens].cpu(), c['topk_idx'])
+    assert torch.equal(y.cpu(), y_ref.cpu())
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+    assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
