@@ -155,6 +155,9 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     }
 
     p.prefetch_distance = tuning().prefetch_distance;
+    p.b_ptr = static_cast<const unsigned char*>(c.b);
+    p.b_row_bytes = (nvfp4 || c.b_is_fp4) ? p.k / 2 : p.k;
+    p.b_kb_bytes = (c.b_is_fp4 && !nvfp4) ? 64 : 128;
     p.debug_skip = tuning().debug_skip;
     p.trace = tuning().trace;
     p.trace_cap = tuning().trace_cap;

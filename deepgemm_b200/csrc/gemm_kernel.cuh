@@ -63,7 +63,10 @@ struct GemmParams {
     unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
     unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
     int store_padding;       // psum only: also write the rows between a group's end and its aligned end
-    int prefetch_distance;   // K blocks the weight loader's L2 prefetch cursor runs ahead of its loads (0 = off)
+    int prefetch_distance;   // K blocks the weight prefetch cursor runs ahead of the loads (0 = off)
+    const unsigned char* b_ptr;  // raw view of the weights for the prefetch cursor (the loads go through the tensor map)
+    long long b_row_bytes;       // row pitch of B in bytes
+    int b_kb_bytes;              // bytes of one B row inside one K block: 64 (packed FP4 of the FP8 x FP4 kind) or 128
     int debug_skip;          // timing experiments only (results become garbage): bit 0 no A loads, 1 no B loads,
                              // 2 no scale-factor loads, 3 no MMA instructions, 4 no scale-factor TMEM copies
     long long* trace;        // optional: CTA 0 records clock64() per role and K block at trace[role * trace_cap + i]
@@ -273,12 +276,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     uint64_t* tmem_empty_bar = bars + 3 * kStages + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffMisc + 4);
+    volatile int* load_progress = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);  // K blocks the weight loader has issued
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *load_progress = 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(full_bar + i, 2);       // the A-side loader and the B-side loader
             mbar_init(empty_bar + i, 1);      // tcgen05.commit of the MMA issuer
@@ -389,31 +394,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             bool ok = true;
             int trace_i = 0;
 
-            // L2 prefetch cursor: weight tiles are read once from HBM, and the few stages that fit in shared memory do
-            // not cover that latency. The cursor walks the same (tile, K block) sequence p.prefetch_distance blocks
-            // ahead of the loads and asks TMA to bring each weight tile into L2 (no shared memory, no barrier).
-            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
-            Tile pt;
-            int pf_kb = 0, pf_row = 0;
-            bool pf_valid = false;
-            auto pf_next_tile = [&]() {
-                pf_valid = false;
-                while (pf_sched.next(pt)) {
-                    if (pt.group >= 0) { pf_valid = true; break; }
-                }
-                pf_kb = 0;
-                pf_row = pt.group * p.n + pt.n_block * BLOCK_N;
-            };
-            auto pf_advance = [&](bool issue) {
-                if (!pf_valid) return;
-                if (issue) tma_prefetch_2d(&tm_b, pf_kb * 128, pf_row);
-                if (++pf_kb == num_kb) pf_next_tile();
-            };
             const bool leader = elect_one();
-            if (p.prefetch_distance > 0) {
-                pf_next_tile();
-                for (int i = 0; i < p.prefetch_distance; ++i) pf_advance(leader);
-            }
+            int issued = 0;
 
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
@@ -432,12 +414,13 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
                                         t.n_block * BLOCK_N, sfb_y + kb * kSfInts / b_per);
                         trace_point(p, 10, trace_i);
+                        if (p.prefetch_distance > 0) *load_progress = ++issued;
                     }
-                    if (p.prefetch_distance > 0) pf_advance(leader);
                     ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
+            if (leader) *load_progress = 0x3fffffff;  // lets the prefetch cursor run to its end
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -569,6 +552,55 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 if (lane == 0) trace_point(p, 3, trace_i);
                 ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (p.sf_transposed != 0 && p.prefetch_distance > 0) {
+            // With nothing to transpose this warp is free: it walks the tile sequence p.prefetch_distance K blocks ahead
+            // of the loads and prefetches the weight rows into L2 with plain
+            // prefetch instructions. Weight tiles are read once from HBM and the stages that fit in shared memory do
+            // not cover that latency; TMA prefetches would, but they cost the TMA unit a box row per cycle.
+            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
+            Tile pt;
+            int pf_kb = 0;
+            bool pf_valid = false;
+            const unsigned char* pf_base = nullptr;
+            auto pf_next_tile = [&]() {
+                pf_valid = false;
+                while (pf_sched.next(pt)) {
+                    if (pt.group >= 0) { pf_valid = true; break; }
+                }
+                pf_kb = 0;
+                if (pf_valid)
+                    pf_base = p.b_ptr + (static_cast<long long>(pt.group) * p.n + pt.n_block * BLOCK_N + lane) * p.b_row_bytes;
+            };
+            auto pf_advance = [&]() {
+                if (!pf_valid) return;
+                const long long col = static_cast<long long>(pf_kb) * p.b_kb_bytes;
+                if ((col & 127) == 0) {  // one 128-byte line covers two K blocks of packed FP4
+#pragma unroll
+                    for (int j = 0; j < BLOCK_N / 32; ++j) prefetch_l2(pf_base + j * 32 * p.b_row_bytes + col);
+                }
+                if (++pf_kb == num_kb) pf_next_tile();
+            };
+            // Paced by the weight loader's progress counter (K blocks issued so far; a huge value once it is done).
+            pf_next_tile();
+            long long done = 0;
+            long long t0 = 0;
+            uint32_t spins = 0;
+            while (pf_valid) {
+                const long long target = static_cast<long long>(*load_progress) + p.prefetch_distance;
+                if (done < target) {
+                    pf_advance();
+                    ++done;
+                    continue;
+                }
+                __nanosleep(200);
+                if (((++spins) & 0xffu) == 0) {  // bounded like every other wait of this kernel
+                    if (*abort_flag != 0) break;
+                    const long long now = clock64();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > kWaitBudgetCycles) break;  // a prefetcher that gives up costs speed, not correctness
+                }
             }
         }
     }
