@@ -29,7 +29,7 @@ FP4_DENSE_PEAK_TFLOPS_NOMINAL = 9000.0
 FP8_DENSE_PEAK_TFLOPS_NOMINAL = 4500.0
 # DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu capture summarised in
 # profiles/grouped_gemm_small_layer_ncu_full.md (small case, scaled by the units processed).
-L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.03
+L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.06
 
 
 def parse_args():
