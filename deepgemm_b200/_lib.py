@@ -46,6 +46,8 @@ _SIGNATURES = {
     'dgb200_fp8_fp4_mega_moe_bf16_input': [
         _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
+    'dgb200_get_symm_buffer_layout_for_mega_moe_ex': [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_fp8_fp4_mega_moe_ex': [_ptr, _ptr],
     'dgb200_nvfp4_mega_moe': [
         _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
@@ -55,6 +57,18 @@ _SIGNATURES = {
         _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
 }
+
+
+class MegaMoeArgs(ctypes.Structure):
+    """dgb200_mega_moe_args of include/dgb200.h, field for field."""
+    _fields_ = [('struct_size', ctypes.c_size_t)] + \
+        [(n, ctypes.c_void_p) for n in ('y', 'l1_w', 'l1_w_sf', 'l2_w', 'l2_w_sf', 'shared_l1_w', 'shared_l1_w_sf', 'shared_l2_w',
+                                        'shared_l2_w_sf', 'x_bf16', 'logits', 'cumulative_local_expert_recv_stats', 'buffer',
+                                        'peer_buffer_ptrs')] + \
+        [('x_bf16_row_stride', ctypes.c_int64), ('shared_intermediate_hidden', ctypes.c_int32)] + \
+        [(n, ctypes.c_int32) for n in ('rank', 'num_ranks', 'num_tokens', 'num_max_tokens_per_rank', 'num_experts', 'num_topk',
+                                       'hidden', 'intermediate_hidden')] + \
+        [('activation_clamp', ctypes.c_float), ('fast_math', ctypes.c_int32)]
 
 
 def exported_symbols():

@@ -216,6 +216,9 @@ struct MegaLayout {
     long long src_of_row, row_weight;
     long long all_counts, my_base, flags;  // expert-parallel exchange: counts of every rank, this rank's bases, barrier flags
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
+    // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
+    long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
+    long long token_rows;
     long long total;
     long long max_rows;  // capacity of the expert-sorted buffers (rows), a multiple of 128
     int num_chunks, num_local_experts;
@@ -233,13 +236,21 @@ struct LayerQuant {
     // views are then neither read nor written)
     const __nv_bfloat16* x_bf16 = nullptr;
     long long x_bf16_row_stride = 0;
+    // FP8 kind only: shared experts, a dense FP8 x FP8 MLP (per-32 UE8M0 scales) over this rank's own tokens whose
+    // output is one more combine slot (reference: csrc/apis/mega.hpp:211-232). inter = 0: none.
+    const void* shared_l1_w = nullptr;
+    const void* shared_l1_w_sf = nullptr;
+    const void* shared_l2_w = nullptr;
+    const void* shared_l2_w_sf = nullptr;
+    int shared_inter = 0;
 };
 
 // Bytes of one quantised activation row of `width` elements, and packed scale ints (4 scale bytes each) per row.
 inline long long act_row_bytes(int kind, int width) { return kind == kKindNvfp4 ? width / 2 : width; }
 inline int sf_ints_per_row(int kind, int width) { return kind == kKindNvfp4 ? width / 64 : width / 128; }
 
-int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, MegaLayout* out) {
+int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, MegaLayout* out,
+                     int shared_inter = 0) {
     DGB_REQUIRE(num_ranks >= 1 && num_ranks <= kMaxRanks, "num_ranks must be in [1, %d]", kMaxRanks);
     DGB_REQUIRE(num_experts > 0 && num_experts % num_ranks == 0, "num_experts must be a positive multiple of num_ranks");
     DGB_REQUIRE(max_tokens > 0 && topk > 0 && topk <= 32, "need max tokens > 0 and 0 < topk <= 32");
@@ -277,6 +288,15 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l2_acts = take(l.max_rows * act_row_bytes(kind, inter));
     l.l2_sf = take(l.max_rows * sf_ints_per_row(kind, inter) * 4);
     l.l2_out = take(l.max_rows * hidden * 2);
+    l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
+    if (shared_inter > 0) {
+        DGB_REQUIRE(kind == kKindFp8Fp4 && shared_inter % 128 == 0, "shared experts need the FP8 x FP4 layer and a multiple of 128 channels");
+        DGB_REQUIRE(max_tokens % 128 == 0, "with shared experts the token capacity must be a multiple of 128");
+        l.shared_x_sf = take(l.token_rows * (hidden / 128) * 4);
+        l.shared_l2_acts = take(l.token_rows * shared_inter);
+        l.shared_l2_sf = take(l.token_rows * (shared_inter / 128) * 4);
+        l.shared_out = take(l.token_rows * hidden * 2);
+    }
     l.total = off;
     *out = l;
     return 0;
@@ -405,6 +425,85 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     return record_stage(stage_event_base + 1, stream);
 }
 
+// The shared experts' two dense GEMMs over this rank's tokens (token order): x (FP8, scales already in GEMM order)
+// -> SwiGLU (routing weight 1) + FP8 requant -> down GEMM -> bf16 rows in shared_out, the extra combine slot.
+int run_shared_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, int num_tokens, int hidden,
+                     float activation_clamp, int fast_math, cudaStream_t stream) {
+    const int si = quant.shared_inter;
+    int rc = 0;
+    {
+        GemmCall c{};
+        c.a = base + l.x;
+        c.b = quant.shared_l1_w;
+        c.a_rows_total = l.token_rows;
+        c.b_is_fp4 = 0;
+        c.epilogue = kEpiSwiGLU;
+        c.whole_tile_stores = 1;
+        c.sfa = base + l.shared_x_sf;
+        c.sfb = quant.shared_l1_w_sf;
+        c.sfa_k_stride = l.token_rows;
+        c.num_groups_a = 1;
+        c.sfb_k_stride = 2 * si;
+        GemmParams& p = c.p;
+        p.mode = kModeDense;
+        p.m = num_tokens;
+        p.n = 2 * si;
+        p.k = hidden;
+        p.num_groups = 1;
+        p.alignment = 128;
+        p.gran_a = 32;
+        p.gran_b = 32;
+        p.act_q = base + l.shared_l2_acts;
+        p.act_sf = base + l.shared_l2_sf;
+        p.act_q_row_stride = si;
+        p.act_sf_k_stride = l.token_rows;
+        p.row_weight = nullptr;
+        p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
+        p.fast_math = fast_math;
+        p.sf_transposed = 1;
+        p.act_sf_transposed = 1;
+        if ((rc = run_gemm(c, stream))) return rc;
+    }
+    {
+        GemmCall c{};
+        c.a = base + l.shared_l2_acts;
+        c.b = quant.shared_l2_w;
+        c.a_rows_total = l.token_rows;
+        c.b_is_fp4 = 0;
+        c.epilogue = kEpiBF16;
+        c.whole_tile_stores = 1;
+        c.sfa = base + l.shared_l2_sf;
+        c.sfb = quant.shared_l2_w_sf;
+        c.sfa_k_stride = l.token_rows;
+        c.num_groups_a = 1;
+        c.sfb_k_stride = hidden;
+        GemmParams& p = c.p;
+        p.mode = kModeDense;
+        p.m = num_tokens;
+        p.n = hidden;
+        p.k = si;
+        p.num_groups = 1;
+        p.alignment = 128;
+        p.gran_a = 32;
+        p.gran_b = 32;
+        p.d = base + l.shared_out;
+        p.d_row_stride = hidden;
+        p.sf_transposed = 1;
+        if ((rc = run_gemm(c, stream))) return rc;
+    }
+    return 0;
+}
+
+// Scales of x for the shared experts' first GEMM when the caller quantised x into the buffer (token-major ints).
+int run_shared_x_sf(const MegaLayout& l, uint8_t* base, int num_tokens, int hidden, cudaStream_t stream) {
+    const int ints = hidden / 128;
+    dgb200_sf_rows_to_cp_order_kernel<<<(num_tokens + 31) / 32, 256, ints * 33 * sizeof(unsigned), stream>>>(
+        reinterpret_cast<const unsigned*>(base + l.x_sf), num_tokens, ints, reinterpret_cast<unsigned*>(base + l.shared_x_sf),
+        l.token_rows);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 // Epoch counter of the cross-rank barriers, one per buffer (all ranks call in lockstep, so the counters agree).
 uint32_t next_barrier_epoch(const void* buffer) {
     static std::mutex mu;
@@ -427,6 +526,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     const int entries = num_tokens * num_topk;
     const int chunks = std::max(1, (entries + kPlanChunk - 1) / kPlanChunk);
     const int entries_per_rank = num_max_tokens_per_rank * num_topk;
+    const bool with_shared = quant.shared_inter > 0;
     int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
     const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
@@ -452,7 +552,9 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         if (quant.x_bf16 != nullptr)
             dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
                 quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden,
-                l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 1);
+                l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 1,
+                with_shared ? base + l.x : nullptr, with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr,
+                l.token_rows);
         else
             dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
                 base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
@@ -467,10 +569,15 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
 
     rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
     if (rc) return rc;
+    if (with_shared && num_tokens > 0) {
+        if (quant.x_bf16 == nullptr && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
+        if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
+    }
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, static_cast<int>(epoch0 + 3), kPeerWaitBudgetCycles);
     if (num_tokens > 0)
-        dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
-            peers, l.l2_out, topk_idx, dest_row, num_topk, l.num_local_experts, hidden, static_cast<__nv_bfloat16*>(y));
+        dgb200_moe_combine_kernel<<<num_tokens, 128, (num_topk + 1) * sizeof(unsigned long long), stream>>>(
+            peers, l.l2_out, topk_idx, dest_row, num_topk, l.num_local_experts, hidden,
+            with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }
@@ -483,8 +590,13 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
                  int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                  float activation_clamp, int32_t fast_math, cudaStream_t stream) {
     MegaLayout l;
-    int rc = make_mega_layout(quant.kind, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
+    int rc = make_mega_layout(quant.kind, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l,
+                              quant.shared_inter);
     if (rc) return rc;
+    const bool with_shared = quant.shared_inter > 0;
+    DGB_REQUIRE(!with_shared || (quant.shared_l1_w != nullptr && quant.shared_l1_w_sf != nullptr && quant.shared_l2_w != nullptr &&
+                                 quant.shared_l2_w_sf != nullptr),
+                "null shared-expert weight pointer");
     DGB_REQUIRE(rank >= 0 && rank < num_ranks && peer_buffer_ptrs != nullptr &&
                     peer_buffer_ptrs[rank] == reinterpret_cast<uint64_t>(buffer),
                 "rank / peer pointer table do not describe this buffer");
@@ -536,7 +648,8 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
         for (int r = 0; r < kMaxEpRanks; ++r) self_table.p[r] = reinterpret_cast<unsigned long long>(base);
         dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
             quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden, num_experts, 0,
-            entries, self_table, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 0);
+            entries, self_table, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 0,
+            with_shared ? base + l.x : nullptr, with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr, l.token_rows);
     } else {
         dgb200_moe_gather_kernel<<<gather_blocks, 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
             base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk,
@@ -549,11 +662,16 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
     // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
     rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
     if (rc) return rc;
+    if (with_shared) {
+        if (quant.x_bf16 == nullptr && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
+        if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
+    }
     // 5. combine: y[t] = sum over the top-k slots of the rows the L2 GEMM wrote
     PeerTable self{};
     self.p[0] = reinterpret_cast<unsigned long long>(base);
-    dgb200_moe_combine_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
-        self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden, static_cast<__nv_bfloat16*>(y));
+    dgb200_moe_combine_kernel<<<num_tokens, 128, (num_topk + 1) * sizeof(unsigned long long), stream>>>(
+        self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
+        with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }
@@ -897,6 +1015,57 @@ int dgb200_fp8_fp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_str
     return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
                         num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
                         activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                                  int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                                  int32_t shared_intermediate_hidden, int64_t* out) {
+    DGB_REQUIRE(out != nullptr && shared_intermediate_hidden >= 0, "null output or negative shared size");
+    MegaLayout l;
+    const int rc = make_mega_layout(kKindFp8Fp4, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                                    intermediate_hidden, &l, shared_intermediate_hidden);
+    if (rc) return rc;
+    const long long fields[20] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+                                  l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight,
+                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out};
+    for (int i = 0; i < 20; ++i) out[i] = fields[i];
+    return 0;
+}
+
+int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* a, void* stream) {
+    DGB_REQUIRE(a != nullptr && a->struct_size == sizeof(dgb200_mega_moe_args),
+                "dgb200_mega_moe_args: struct_size does not match this library (%zu bytes)", sizeof(dgb200_mega_moe_args));
+    LayerQuant quant;
+    if (a->x_bf16 != nullptr) {
+        DGB_REQUIRE(reinterpret_cast<uintptr_t>(a->x_bf16) % 16 == 0 && a->x_bf16_row_stride >= a->hidden &&
+                        (a->x_bf16_row_stride * 2) % 16 == 0,
+                    "x_bf16 must be 16-byte aligned BF16 rows of at least `hidden` elements");
+        quant.x_bf16 = static_cast<const __nv_bfloat16*>(a->x_bf16);
+        quant.x_bf16_row_stride = a->x_bf16_row_stride;
+    }
+    if (a->shared_intermediate_hidden > 0) {
+        quant.shared_l1_w = a->shared_l1_w;
+        quant.shared_l1_w_sf = a->shared_l1_w_sf;
+        quant.shared_l2_w = a->shared_l2_w;
+        quant.shared_l2_w_sf = a->shared_l2_w_sf;
+        quant.shared_inter = a->shared_intermediate_hidden;
+    }
+    if (a->logits != nullptr && a->num_tokens > 0) {
+        MegaLayout l;
+        int rc = make_mega_layout(kKindFp8Fp4, a->num_ranks, a->num_experts, a->num_max_tokens_per_rank, a->num_topk, a->hidden,
+                                  a->intermediate_hidden, &l, quant.shared_inter);
+        if (rc) return rc;
+        DGB_REQUIRE(a->buffer != nullptr && a->num_tokens <= a->num_max_tokens_per_rank, "bad buffer or token count");
+        uint8_t* base = static_cast<uint8_t*>(a->buffer);
+        rc = dgb200_route_sigmoid_topk(a->logits, a->num_tokens, a->num_experts, a->num_topk,
+                                       reinterpret_cast<int64_t*>(base + l.topk_idx), reinterpret_cast<float*>(base + l.topk_weights),
+                                       stream);
+        if (rc) return rc;
+    }
+    return run_mega_moe(quant, a->y, a->l1_w, a->l1_w_sf, a->l2_w, a->l2_w_sf, a->cumulative_local_expert_recv_stats, a->buffer,
+                        a->peer_buffer_ptrs, a->rank, a->num_ranks, a->num_tokens, a->num_max_tokens_per_rank, a->num_experts,
+                        a->num_topk, a->hidden, a->intermediate_hidden, a->activation_clamp, a->fast_math,
+                        static_cast<cudaStream_t>(stream));
 }
 
 int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const float* l1_w_scales, const void* l2_w,

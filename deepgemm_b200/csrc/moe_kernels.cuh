@@ -213,13 +213,18 @@ struct PeerTable {
 // row for entry (t, k): row dest_row[t * topk + k] of the `rows` buffer of the rank that owns expert topk_idx[t, k]
 // (read in place over NVLink when that is another rank: the combine pulls, nothing is pushed). Slots with
 // dest_row < 0 are skipped. One CTA per token; a thread owns 8 consecutive channels (one 16-byte vector per slot).
+// With shared experts their output row of the token (local, bf16 [tokens, hidden] at `shared_rows`) is one more slot,
+// added after the top-k slots (the reference gives it combine slot index num_topk, ...mega_moe.cuh:1275-1278).
 // Reference: the combine of the fused kernel, deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:1323-1452.
 __global__ void __launch_bounds__(128)
 dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
                           const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
-                          __nv_bfloat16* __restrict__ y) {
+                          const __nv_bfloat16* __restrict__ shared_rows, __nv_bfloat16* __restrict__ y) {
     const int t = blockIdx.x;
-    extern __shared__ unsigned long long slot_rows[];  // address of each slot's row, 0 = skip
+    extern __shared__ unsigned long long slot_rows[];  // address of each slot's row (top-k slots, then the shared one), 0 = skip
+    if (threadIdx.x == topk)
+        slot_rows[topk] = shared_rows != nullptr
+            ? reinterpret_cast<unsigned long long>(shared_rows + static_cast<long long>(t) * hidden) : 0ull;
     if (threadIdx.x < topk) {
         const int d = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
         unsigned long long addr = 0;
@@ -232,7 +237,7 @@ dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const lo
     __syncthreads();
     for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int k = 0; k < topk; ++k) {
+        for (int k = 0; k <= topk; ++k) {
             const unsigned long long addr = slot_rows[k];
             if (addr == 0) continue;
             const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(addr) + c);
@@ -442,7 +447,10 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
                                  const int* __restrict__ dest_row, int tokens, int topk, int hidden, int experts_per_rank,
                                  int my_rank, int entries_per_rank, const PeerTable peers, long long acts_offset,
                                  long long sf_offset, long long sf_k_stride, long long weight_offset, long long src_offset,
-                                 int write_meta) {
+                                 int write_meta, unsigned char* __restrict__ self_q, unsigned* __restrict__ self_sf,
+                                 long long self_sf_k_stride) {
+    // self_q / self_sf (may be null): also keep the quantised row in token order (e4m3 [tokens, hidden]; scales MN-major
+    // in tcgen05.cp row order), which is what the shared experts' GEMM reads.
     const int lane = threadIdx.x & 31;
     const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (token >= tokens) return;
@@ -494,6 +502,10 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
         const uint32_t e2 = __shfl_down_sync(0xffffffffu, e, 2), e4 = __shfl_down_sync(0xffffffffu, e, 4),
                        e6 = __shfl_down_sync(0xffffffffu, e, 6);
         const uint32_t sf_int = e | (e2 << 8) | (e4 << 16) | (e6 << 24);
+        if (self_q != nullptr && valid) {
+            st_global_v4(self_q + static_cast<long long>(token) * hidden + col, o[0], o[1], o[2], o[3]);
+            if ((lane & 7) == 0) self_sf[static_cast<long long>(col >> 7) * self_sf_k_stride + sf_row_in_cp_order(token)] = sf_int;
+        }
         for (int k = 0; k < topk; ++k) {
             const int d = __shfl_sync(0xffffffffu, my_dest, k);
             const unsigned long long base = __shfl_sync(0xffffffffu, my_base, k);
@@ -504,6 +516,25 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
                 reinterpret_cast<unsigned*>(base + sf_offset)[static_cast<long long>(col >> 7) * sf_k_stride + sf_row_in_cp_order(d)] =
                     sf_int;
         }
+    }
+}
+
+// Token-major packed scale factors [tokens][ints_per_row] -> MN-major with every 128 rows in tcgen05.cp order
+// (out[c * k_stride + sf_row_in_cp_order(t)]): the form the GEMM reads when the activations stay in token order
+// (shared experts). 32 tokens per CTA through a padded shared-memory tile.
+__global__ void __launch_bounds__(256)
+dgb200_sf_rows_to_cp_order_kernel(const unsigned* __restrict__ sf, int tokens, int ints_per_row, unsigned* __restrict__ out,
+                                  long long k_stride) {
+    extern __shared__ unsigned sf_tile[];  // [ints_per_row][33]
+    const int t0 = blockIdx.x * 32;
+    for (int i = threadIdx.x; i < 32 * ints_per_row; i += 256) {
+        const int r = i / ints_per_row, c = i - r * ints_per_row;
+        if (t0 + r < tokens) sf_tile[c * 33 + r] = sf[static_cast<long long>(t0 + r) * ints_per_row + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * ints_per_row; i += 256) {
+        const int c = i >> 5, r = i & 31;
+        if (t0 + r < tokens) out[static_cast<long long>(c) * k_stride + sf_row_in_cp_order(t0 + r)] = sf_tile[c * 33 + r];
     }
 }
 

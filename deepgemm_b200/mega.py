@@ -36,15 +36,19 @@ _MMA_TYPES = ('fp8xfp4', 'nvfp4xnvfp4')
 
 
 def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-                   mma_type='fp8xfp4'):
-    words = (ctypes.c_int64 * _NUM_LAYOUT_WORDS)()
-    fn = (_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe if mma_type == 'fp8xfp4' else
-          _lib.lib().dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe)
-    _lib.check(fn(
-        num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-        ctypes.cast(words, ctypes.c_void_p)))
+                   mma_type='fp8xfp4', shared_intermediate_hidden=0):
+    words = (ctypes.c_int64 * 20)()
+    if mma_type == 'fp8xfp4':
+        _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe_ex(
+            num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+            shared_intermediate_hidden, ctypes.cast(words, ctypes.c_void_p)))
+    else:
+        _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(
+            num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+            ctypes.cast(words, ctypes.c_void_p)))
     keys = ['total', 'x', 'x_sf', 'topk_idx', 'topk_weights', 'l1_acts', 'l1_sf', 'l2_acts', 'l2_sf', 'max_rows',
-            'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'l2_out', 'row_weight']
+            'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'l2_out', 'row_weight',
+            'shared_x_sf', 'shared_l2_acts', 'shared_l2_sf', 'shared_out']
     return dict(zip(keys, list(words)))
 
 
@@ -59,8 +63,9 @@ class SymmBuffer:
             raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
         if mma_type not in _MMA_TYPES:
             raise RuntimeError(f'MMA type must be one of {_MMA_TYPES}, got `{mma_type}`')
-        if num_shared_experts != 0:
-            raise RuntimeError('shared experts are not built')
+        if num_shared_experts < 0 or (num_shared_experts > 0 and mma_type != 'fp8xfp4'):
+            raise RuntimeError('shared experts need num_shared_experts >= 0 and the `fp8xfp4` MMA type')
+        self.num_shared_experts = num_shared_experts
         self.group = group
         self.num_ranks = 1 if group is None else group.size()
         self.rank = 0 if group is None else group.rank()
@@ -69,7 +74,7 @@ class SymmBuffer:
         self.hidden, self.intermediate_hidden = hidden, intermediate_hidden
         self.mma_type = mma_type
         self.layout = _buffer_layout(self.num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
-                                     intermediate_hidden, mma_type)
+                                     intermediate_hidden, mma_type, intermediate_hidden * num_shared_experts)
         num_bytes = self.layout['total']
         if self.num_ranks == 1:
             self.buffer = torch.empty(num_bytes, dtype=torch.int8, device='cuda')
@@ -153,6 +158,10 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
         raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
     if not isinstance(l1_weights, tuple):
         raise RuntimeError('BF16 weights are not built; pass (packed FP4 weights, packed scale factors[, tensor scales])')
+    if l1_weights[0].dim() == 2:  # shared experts: one FP8 matrix per layer, same reordering
+        t1, t2 = transform_weights_for_mega_moe(tuple(t.unsqueeze(0) for t in l1_weights),
+                                                tuple(t.unsqueeze(0) for t in l2_weights), activation)
+        return tuple(t[0] for t in t1), tuple(t[0] for t in t2)
     # NVFP4 weights carry a third element, the per-expert FP32 scales, which no reordering touches
     l1_sf = _sf_rows_to_cp_order(_interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE))
     return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), l1_sf) + tuple(l1_weights[2:]), \
@@ -168,75 +177,88 @@ def _check_weight(w, sf, num_groups, n, k, name, k_per_int=128):
                            '(use transform_sf_into_required_layout / pack_nvfp4_sf_mn_major)')
 
 
-def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor],
-                     l2_weights: Tuple[torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
-                     shared_l1_weights=None, shared_l2_weights=None,
-                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
-                     recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
-                     activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
-    """y[t] = sum_k w[t,k] * Expert_{idx[t,k]}(x[t]) over the inputs the caller placed in ``sym_buffer``.
-    Reference: fp8_fp4_mega_moe, deep_gemm/mega/__init__.py:153-176 and csrc/apis/mega.hpp:157-286."""
-    if tuple(recipe) != (1, 1, 32):
-        raise RuntimeError('recipe must be (1, 1, 32)')
-    if activation != 'swiglu':
-        raise RuntimeError('activation must be `swiglu`')
-    if shared_l1_weights is not None or shared_l2_weights is not None:
-        raise RuntimeError('shared experts are not built')
-    b = sym_buffer
+def _check_shared_weight(w, sf, n, k, name):
+    if not (w.is_cuda and w.dtype == torch.float8_e4m3fn and w.is_contiguous() and tuple(w.shape) == (n, k)):
+        raise RuntimeError(f'{name} must be a contiguous CUDA float8_e4m3fn tensor of shape {(n, k)}')
+    if not (sf.dtype == torch.int32 and tuple(sf.shape) == (n, k // 128) and sf.stride(0) == 1 and sf.stride(1) == align(n, 4)):
+        raise RuntimeError(f'{name} scale factors must be packed UE8M0 int32 {(n, k // 128)}, MN-major')
+
+
+def _run_layer(y, l1_weights, l2_weights, b, shared_l1_weights, shared_l2_weights, stats, activation_clamp, fast_math,
+               x=None, logits=None):
+    """Common argument checks and the call into dgb200_fp8_fp4_mega_moe_ex."""
     if b.mma_type != 'fp8xfp4':
         raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
     num_local = b.num_experts // b.num_ranks
     _check_weight(l1_weights[0], l1_weights[1], num_local, 2 * b.intermediate_hidden, b.hidden, 'l1_weights')
     _check_weight(l2_weights[0], l2_weights[1], num_local, b.hidden, b.intermediate_hidden, 'l2_weights')
+    if (shared_l1_weights is None) != (shared_l2_weights is None):
+        raise RuntimeError('shared_l1_weights and shared_l2_weights must be given together')
+    shared_inter = 0
+    if shared_l1_weights is not None:
+        shared_inter = shared_l2_weights[0].size(1)
+        if shared_inter != b.intermediate_hidden * b.num_shared_experts or shared_inter == 0:
+            raise RuntimeError('the buffer was created for a different number of shared experts')
+        _check_shared_weight(shared_l1_weights[0], shared_l1_weights[1], 2 * shared_inter, b.hidden, 'shared_l1_weights')
+        _check_shared_weight(shared_l2_weights[0], shared_l2_weights[1], b.hidden, shared_inter, 'shared_l2_weights')
     if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
         raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
-    stats = cumulative_local_expert_recv_stats
+    if x is not None and not (x.is_cuda and x.dtype == torch.bfloat16 and tuple(x.shape) == tuple(y.shape) and x.stride(1) == 1):
+        raise RuntimeError('x must be a CUDA bfloat16 [num_tokens, hidden] tensor with unit inner stride')
+    if logits is not None and not (logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous() and
+                                   tuple(logits.shape) == (y.size(0), b.num_experts)):
+        raise RuntimeError('logits must be a contiguous CUDA float32 [num_tokens, num_experts] tensor')
     if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == num_local and stats.is_contiguous()):
         raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
     ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
-    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    p = lambda t: t.data_ptr() if t is not None else None
+    args = _lib.MegaMoeArgs(
+        struct_size=ctypes.sizeof(_lib.MegaMoeArgs), y=p(y), l1_w=p(l1_weights[0]), l1_w_sf=p(l1_weights[1]),
+        l2_w=p(l2_weights[0]), l2_w_sf=p(l2_weights[1]),
+        shared_l1_w=p(shared_l1_weights[0]) if shared_inter else None, shared_l1_w_sf=p(shared_l1_weights[1]) if shared_inter else None,
+        shared_l2_w=p(shared_l2_weights[0]) if shared_inter else None, shared_l2_w_sf=p(shared_l2_weights[1]) if shared_inter else None,
+        x_bf16=p(x), logits=p(logits), cumulative_local_expert_recv_stats=p(stats), buffer=p(b.buffer),
+        peer_buffer_ptrs=ctypes.cast(ptrs, ctypes.c_void_p), x_bf16_row_stride=x.stride(0) if x is not None else 0,
+        shared_intermediate_hidden=shared_inter, rank=b.rank, num_ranks=b.num_ranks, num_tokens=y.size(0),
+        num_max_tokens_per_rank=b.num_max_tokens_per_rank, num_experts=b.num_experts, num_topk=b.num_topk, hidden=b.hidden,
+        intermediate_hidden=b.intermediate_hidden,
+        activation_clamp=float(activation_clamp) if activation_clamp is not None else 0.0, fast_math=int(fast_math))
     with torch.cuda.device(y.device):
-        _lib.check(_lib.lib().dgb200_fp8_fp4_mega_moe(
-            p(y), p(l1_weights[0]), p(l1_weights[1]), p(l2_weights[0]), p(l2_weights[1]), p(stats), p(b.buffer),
-            ctypes.cast(ptrs, ctypes.c_void_p), b.rank, b.num_ranks, y.size(0), b.num_max_tokens_per_rank,
-            b.num_experts, b.num_topk, b.hidden, b.intermediate_hidden,
-            float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
-            _lib.current_stream_ptr()))
+        _lib.check(_lib.lib().dgb200_fp8_fp4_mega_moe_ex(ctypes.byref(args), _lib.current_stream_ptr()))
+
+
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                     l2_weights: Tuple[torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
+                     shared_l1_weights: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                     shared_l2_weights: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                     recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
+                     activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
+    """y[t] = sum_k w[t,k] * Expert_{idx[t,k]}(x[t]) (+ SharedExperts(x[t])) over the inputs the caller placed in
+    ``sym_buffer``. Shared experts: (float8_e4m3fn [2 * SI, H], packed UE8M0 int32 scales) and ([H, SI], scales), both
+    passed through ``transform_weights_for_mega_moe``; the buffer must have been created with ``num_shared_experts``.
+    Reference: fp8_fp4_mega_moe, deep_gemm/mega/__init__.py:153-176 and csrc/apis/mega.hpp:157-286."""
+    if tuple(recipe) != (1, 1, 32):
+        raise RuntimeError('recipe must be (1, 1, 32)')
+    if activation != 'swiglu':
+        raise RuntimeError('activation must be `swiglu`')
+    _run_layer(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights,
+               cumulative_local_expert_recv_stats, activation_clamp, fast_math)
 
 
 def fp8_fp4_mega_moe_bf16_input(y: torch.Tensor, x: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor],
                                 l2_weights: Tuple[torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
                                 logits: Optional[torch.Tensor] = None,
+                                shared_l1_weights: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                                shared_l2_weights: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                                 cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                                 activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
     """``fp8_fp4_mega_moe`` with its prologue fused in (no reference counterpart: the reference's callers quantise x with
     per_token_cast_to_fp8 into the buffer and route with torch ops, README.md:72, tests/test_mega_moe.py:124-125).
     ``x`` is BF16 [num_tokens, hidden] and is quantised while it is dispatched; with ``logits`` the router fills the
     buffer's ``topk_idx`` / ``topk_weights`` first, otherwise the caller has. Same bits as the separate steps."""
-    b = sym_buffer
-    if b.mma_type != 'fp8xfp4':
-        raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
-    num_local = b.num_experts // b.num_ranks
-    _check_weight(l1_weights[0], l1_weights[1], num_local, 2 * b.intermediate_hidden, b.hidden, 'l1_weights')
-    _check_weight(l2_weights[0], l2_weights[1], num_local, b.hidden, b.intermediate_hidden, 'l2_weights')
-    if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
-        raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
-    if not (x.is_cuda and x.dtype == torch.bfloat16 and tuple(x.shape) == tuple(y.shape) and x.stride(1) == 1):
-        raise RuntimeError('x must be a CUDA bfloat16 [num_tokens, hidden] tensor with unit inner stride')
-    if logits is not None and not (logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous() and
-                                   tuple(logits.shape) == (y.size(0), b.num_experts)):
-        raise RuntimeError('logits must be a contiguous CUDA float32 [num_tokens, num_experts] tensor')
-    stats = cumulative_local_expert_recv_stats
-    if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == num_local and stats.is_contiguous()):
-        raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
-    ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
-    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
-    with torch.cuda.device(y.device):
-        _lib.check(_lib.lib().dgb200_fp8_fp4_mega_moe_bf16_input(
-            p(y), p(x), x.stride(0), p(logits), p(l1_weights[0]), p(l1_weights[1]), p(l2_weights[0]), p(l2_weights[1]),
-            p(stats), p(b.buffer), ctypes.cast(ptrs, ctypes.c_void_p), b.rank, b.num_ranks, y.size(0),
-            b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden, b.intermediate_hidden,
-            float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math), _lib.current_stream_ptr()))
+    _run_layer(y, l1_weights, l2_weights, sym_buffer, shared_l1_weights, shared_l2_weights,
+               cumulative_local_expert_recv_stats, activation_clamp, fast_math, x=x, logits=logits)
 
 
 def nvfp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor],

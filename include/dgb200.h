@@ -203,6 +203,46 @@ int dgb200_fp8_fp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_str
                                        int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
                                        int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream);
 
+/* Every option of the FP8 x MXFP4 layer in one call: the arguments of dgb200_fp8_fp4_mega_moe, the fused prologue of
+ * dgb200_fp8_fp4_mega_moe_bf16_input (x_bf16 / logits, NULL = not used), and shared experts.
+ * Shared experts (reference: shared_l1_weights / shared_l2_weights of fp8_fp4_mega_moe, csrc/apis/mega.hpp:161-232, and
+ * the SharedLinear1/2 tasks of the fused kernel, ...mega_moe.cuh:769-778,1275-1278): a dense FP8 x FP8 MLP applied to
+ * every token of this rank, its BF16 output row added to the token's combine after the top-k slots.
+ *   shared_l1_w e4m3 [2 * shared_inter, hidden] (rows gate/up-interleaved by 32), shared_l1_w_sf packed UE8M0 int32
+ *   (per-32), MN-major [hidden / 128][2 * shared_inter], 128-row groups in tcgen05.cp order; shared_l2_w e4m3
+ *   [hidden, shared_inter], shared_l2_w_sf [shared_inter / 128][hidden]. shared_intermediate_hidden = 0: none.
+ * The buffer must have been sized with dgb200_get_symm_buffer_layout_for_mega_moe_ex and the same shared size; the
+ * token capacity must then be a multiple of 128. struct_size = sizeof(dgb200_mega_moe_args). */
+typedef struct dgb200_mega_moe_args {
+    size_t struct_size;
+    void* y;
+    const void* l1_w;
+    const void* l1_w_sf;
+    const void* l2_w;
+    const void* l2_w_sf;
+    const void* shared_l1_w;
+    const void* shared_l1_w_sf;
+    const void* shared_l2_w;
+    const void* shared_l2_w_sf;
+    const void* x_bf16;
+    const float* logits;
+    int32_t* cumulative_local_expert_recv_stats;
+    void* buffer;
+    const uint64_t* peer_buffer_ptrs;
+    int64_t x_bf16_row_stride;
+    int32_t shared_intermediate_hidden;
+    int32_t rank, num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden;
+    float activation_clamp;
+    int32_t fast_math;
+} dgb200_mega_moe_args;
+int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* args, void* stream);
+
+/* dgb200_get_symm_buffer_layout_for_mega_moe with room for shared experts: out[20] = the 16 words above, then the byte
+ * offsets of the shared experts' private regions (x scales in GEMM order, activations, their scales, output rows). */
+int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                                  int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                                  int32_t shared_intermediate_hidden, int64_t* out);
+
 /* NVFP4 x NVFP4 form of the layer (no reference counterpart; the reference's layer is FP8 x MXFP4 only).
  * Buffer layout: same out[16] fields as dgb200_get_symm_buffer_layout_for_mega_moe; the caller writes
  * x (packed e2m1 [T, hidden / 2]) and x_sf (int32 [T, hidden / 64], four UE4M3 bytes per int, token-major).

@@ -73,15 +73,30 @@ def swiglu_requant(gate_up: torch.Tensor, weight: torch.Tensor, clamp: Optional[
     return q, sf
 
 
+def shared_expert_rows(x_q: torch.Tensor, x_sf: torch.Tensor, s1_q: torch.Tensor, s1_sf: torch.Tensor, s2_q: torch.Tensor,
+                       s2_sf: torch.Tensor, clamp: Optional[float] = None) -> torch.Tensor:
+    """Shared experts: a dense FP8 x FP8 MLP (per-32 UE8M0 scales on both operands, recipe (1, 1, 32)) over every
+    token, with routing weight 1: x -> [gate | up] GEMM -> swiglu_requant -> down GEMM -> bf16 rows [T, H].
+    Follows the reference's own baseline (tests/test_mega_moe.py:254-279: fp8_gemm_nt, swiglu_apply_weight_to_fp8 with
+    topk_weights=None, fp8_gemm_nt); weights s1_q e4m3 [2 SI, H] with s1_sf fp32 [2 SI, H/32], s2_q [H, SI]."""
+    x = dequantize_fp8(x_q, x_sf, 32)
+    acc1 = x @ dequantize_fp8(s1_q, s1_sf, 32).T
+    a2_q, a2_sf = swiglu_requant(acc1, torch.ones(x.shape[0]), clamp)
+    return (dequantize_fp8(a2_q, a2_sf, 32) @ dequantize_fp8(s2_q, s2_sf, 32).T).bfloat16()
+
+
 def moe_layer(x_q: torch.Tensor, x_sf: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
               l1_q: torch.Tensor, l1_sf: torch.Tensor, l2_q: torch.Tensor, l2_sf: torch.Tensor,
-              clamp: Optional[float] = None, return_intermediates: bool = False):
+              clamp: Optional[float] = None, return_intermediates: bool = False,
+              shared_rows: Optional[torch.Tensor] = None):
     """Whole layer on one rank holding every expert.
 
     x_q e4m3 [T, H] with x_sf fp32 [T, H/32] (per-32 UE8M0, tests/test_mega_moe.py:53-59);
     l1_q int8 [E, 2I, H/2] rows [gate | up] with l1_sf fp32 [E, 2I, H/32]; l2_q int8 [E, H, I/2], l2_sf [E, H, I/32].
     Per expert: acc1 = deq(x) @ deq(W1).T (fp32) -> swiglu_requant -> acc2 = deq(a2) @ deq(W2).T -> bf16 row;
-    y[t] = bf16(sum over valid slots k, ascending, of fp32(row(t, k))) (sm100_fp8_fp4_mega_moe.cuh:1378-1430)."""
+    y[t] = bf16(sum over valid slots k, ascending, of fp32(row(t, k))) (sm100_fp8_fp4_mega_moe.cuh:1378-1430);
+    ``shared_rows`` (bf16 [T, H], see shared_expert_rows) is one more slot after the top-k ones (combine slot index
+    num_topk, sm100_fp8_fp4_mega_moe.cuh:1275-1278)."""
     tokens, hidden = x_q.shape
     num_experts, topk = l1_q.shape[0], topk_idx.shape[1]
     x = dequantize_fp8(x_q, x_sf, 32)
@@ -103,6 +118,8 @@ def moe_layer(x_q: torch.Tensor, x_sf: torch.Tensor, topk_idx: torch.Tensor, top
     y = torch.zeros((tokens, hidden), dtype=torch.float32)
     for k in range(topk):
         y += torch.where(valid[:, k, None], slot_rows[:, k].float(), torch.zeros(()))
+    if shared_rows is not None:
+        y += shared_rows.float()
     y = y.bfloat16()
     return (y, inter) if return_intermediates else y
 

@@ -28,6 +28,14 @@ def _rank_inputs(rank):
     return c
 
 
+def _shared_weights():
+    from oracle import quant
+    torch.manual_seed(4242)
+    s1_q, s1_sf = quant.quantize_fp8_per_token((torch.randn(2 * INTER, HIDDEN) * 0.02).bfloat16(), 32)
+    s2_q, s2_sf = quant.quantize_fp8_per_token((torch.randn(HIDDEN, INTER) * 0.02).bfloat16(), 32)
+    return s1_q, s1_sf, s2_q, s2_sf
+
+
 def _worker(rank, world, port, results):
     import torch.distributed as dist
     import deepgemm_b200 as dg
@@ -40,7 +48,7 @@ def _worker(rank, world, port, results):
         c = _rank_inputs(rank)
         per_rank = EXPERTS // world
         mine = slice(rank * per_rank, (rank + 1) * per_rank)
-        buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, EXPERTS, max(TOKENS), TOPK, HIDDEN, INTER)
+        buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, EXPERTS, max(TOKENS), TOPK, HIDDEN, INTER, num_shared_experts=1)
         l1_sf = dg.transform_sf_into_required_layout(c['l1_sf'][mine].cuda(), 2 * INTER, HIDDEN, (1, 32), per_rank)
         l2_sf = dg.transform_sf_into_required_layout(c['l2_sf'][mine].cuda(), HIDDEN, INTER, (1, 32), per_rank)
         l1, l2 = dg.transform_weights_for_mega_moe((c['l1_q'][mine].cuda(), l1_sf), (c['l2_q'][mine].cuda(), l2_sf))
@@ -62,11 +70,20 @@ def _worker(rank, world, port, results):
         dg.fp8_fp4_mega_moe_bf16_input(y, c['x'].cuda(), l1, l2, buf, cumulative_local_expert_recv_stats=None)
         assert _lib.device_status()[0] == 0
         ys.append(y.cpu())
+        # fourth call: shared experts (rank-local FP8 x FP8 MLP) as an extra combine slot
+        s1_q, s1_sf, s2_q, s2_sf = _shared_weights()
+        sl1, sl2 = dg.transform_weights_for_mega_moe(
+            (s1_q.cuda(), dg.transform_sf_into_required_layout(s1_sf.cuda(), 2 * INTER, HIDDEN, (1, 32))),
+            (s2_q.cuda(), dg.transform_sf_into_required_layout(s2_sf.cuda(), HIDDEN, INTER, (1, 32))))
+        y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2, fast_math=False)
+        assert _lib.device_status()[0] == 0
+        ys.append(y.cpu())
         lay = buf.layout
         end = buf.buffer[lay['expert_end']:lay['expert_end'] + per_rank * 4].view(torch.int32).cpu()
         start = buf.buffer[lay['expert_start']:lay['expert_start'] + per_rank * 4].view(torch.int32).cpu()
         dest = buf.buffer[lay['dest_row']:lay['dest_row'] + t * TOPK * 4].view(torch.int32).cpu()
-        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], start=start, end=end, dest=dest, stats=stats.cpu())
+        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], y_shared=ys[3], start=start, end=end, dest=dest, stats=stats.cpu())
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -94,6 +111,10 @@ def test_two_rank_layer_matches_oracle():
         assert torch.equal(got['start'].long(), want_start) and torch.equal(got['end'].long(), want_end)
         assert torch.equal(got['dest'].long(), omoe.ep_dest_rows(c['topk_idx'], my_base, EXPERTS))
         assert torch.equal(got['stats'].long(), 2 * (want_end - want_start))
+        shared = omoe.shared_expert_rows(c['x_q'], c['x_sf'], *_shared_weights())
+        want_shared = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'],
+                                     c['l2_sf'], shared_rows=shared)
+        assert quant.calc_diff(got['y_shared'], want_shared) <= 2e-3
 
 
 # ---- NVFP4 form of the same layer: rows cross ranks as packed E2M1 + UE4M3 scales, one input scale for all ranks

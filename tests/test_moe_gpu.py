@@ -185,3 +185,48 @@ def test_fused_prologue_gives_the_same_bits(dg, tokens, hidden, inter, experts, 
     assert torch.equal(y.cpu(), y_ref.cpu())
     want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
     assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
+
+
+@pytest.mark.parametrize('tokens,hidden,inter,experts,topk,num_shared,fused', [
+    (200, 512, 256, 8, 2, 1, False),
+    (130, 512, 128, 4, 3, 2, True),
+    (256, 256, 128, 4, 1, 1, True),
+])
+def test_shared_experts(dg, tokens, hidden, inter, experts, topk, num_shared, fused):
+    """Shared experts (FP8 x FP8, recipe (1, 1, 32)) add one combine slot after the top-k ones
+    (reference: shared_l1_weights / shared_l2_weights, csrc/apis/mega.hpp:161-232)."""
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=300 + tokens, masked_ratio=0.1)
+    si = inter * num_shared
+    torch.manual_seed(tokens)
+    s1_q, s1_sf = quant.quantize_fp8_per_token((torch.randn(2 * si, hidden) * 0.02).bfloat16(), 32)
+    s2_q, s2_sf = quant.quantize_fp8_per_token((torch.randn(hidden, si) * 0.02).bfloat16(), 32)
+    shared = omoe.shared_expert_rows(c['x_q'], c['x_sf'], s1_q, s1_sf, s2_q, s2_sf, clamp=10.0)
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'],
+                          clamp=10.0, shared_rows=shared)
+    l1, l2 = _device_weights(dg, c)
+    sl1, sl2 = dg.transform_weights_for_mega_moe(
+        (s1_q.cuda(), dg.transform_sf_into_required_layout(s1_sf.cuda(), 2 * si, hidden, (1, 32))),
+        (s2_q.cuda(), dg.transform_sf_into_required_layout(s2_sf.cuda(), hidden, si, (1, 32))))
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_shared_experts=num_shared)
+    buf.topk_idx[:tokens].copy_(c['topk_idx'].cuda())
+    buf.topk_weights[:tokens].copy_(c['topk_weights'].cuda())
+    y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+    if fused:
+        dg.fp8_fp4_mega_moe_bf16_input(y, c['x'].cuda(), l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2,
+                                       activation_clamp=10.0, fast_math=False)
+    else:
+        buf.x[:tokens].copy_(c['x_q'].cuda())
+        buf.x_sf[:tokens].copy_(quant.pack_ue8m0(c['x_sf']).cuda())
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2, activation_clamp=10.0,
+                            fast_math=False)
+    from deepgemm_b200 import _lib
+    assert _lib.device_status()[0] == 0
+    assert not torch.isnan(y.float()).any()
+    assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
+    # the shared slot alone: y minus the routed part must match the shared rows
+    routed = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'],
+                            clamp=10.0)
+    assert quant.calc_diff(y.cpu().float() - routed.float(), shared.float()) <= 5e-3
+    with pytest.raises(RuntimeError):
+        dg.fp8_fp4_mega_moe(y, l1, l2, dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter),
+                            shared_l1_weights=sl1, shared_l2_weights=sl2)

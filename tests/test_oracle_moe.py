@@ -72,3 +72,25 @@ def test_contiguous_and_psum_oracles_agree():
     d2, m2 = ogemm.grouped_gemm_contiguous(c['a_q'], c['a_sf'], c['b_q'], c['b_sf'], c['psum'], use_psum_layout=True)
     assert torch.equal(m1, m2) and torch.equal(d1[m1], d2[m2])
     assert int(m1.sum()) == sum(c['ms'])
+
+
+def test_shared_expert_rows_add_after_the_topk_slots():
+    c = moe_case(9, 256, 128, 4, 2, seed=8)
+    torch.manual_seed(8)
+    s1_q, s1_sf = quant.quantize_fp8_per_token((torch.randn(2 * 128, 256) * 0.05).bfloat16(), 32)
+    s2_q, s2_sf = quant.quantize_fp8_per_token((torch.randn(256, 128) * 0.05).bfloat16(), 32)
+    shared = omoe.shared_expert_rows(c['x_q'], c['x_sf'], s1_q, s1_sf, s2_q, s2_sf)
+    assert shared.shape == (9, 256) and shared.dtype == torch.bfloat16
+    y0, inter = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'],
+                               c['l2_sf'], return_intermediates=True)
+    y1 = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'],
+                        shared_rows=shared)
+    # rebuild token 0 by hand: fp32 sum of its two slot rows, then the shared row, then one rounding
+    acc = torch.zeros(256)
+    for k in range(2):
+        e = int(c['topk_idx'][0, k])
+        tok, slot, _, _, _, acc2 = inter[e]
+        i = int(torch.nonzero((tok == 0) & (slot == k))[0])
+        acc += acc2[i].bfloat16().float()
+    assert torch.equal(y1[0], (acc + shared[0].float()).bfloat16())
+    assert not torch.equal(y0, y1)
