@@ -732,14 +732,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(o[h * 16 + i]));
                             const uint32_t sf_byte = e4m3_byte(amax / 6.0f / s_out);
                             const float factor = e4m3_to_float(sf_byte) * s_out;
-                            uint32_t lo = 0, hi = 0;
+                            // one reciprocal and the hardware E2M1 conversion instead of 16 divisions and threshold
+                            // ladders: this epilogue otherwise costs more than the tile's MMAs
+                            const float rcp = factor > 0.0f ? 1.0f / factor : 0.0f;
+                            float scaled[16];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                lo |= (factor > 0.0f ? e2m1_code(o[h * 16 + i] / factor) : 0u) << (4 * i);
-                                hi |= (factor > 0.0f ? e2m1_code(o[h * 16 + 8 + i] / factor) : 0u) << (4 * i);
-                            }
-                            packed[h * 2] = lo;
-                            packed[h * 2 + 1] = hi;
+                            for (int i = 0; i < 16; ++i) scaled[i] = o[h * 16 + i] * rcp;
+                            packed[h * 2] = pack_e2m1x8_rn(scaled);
+                            packed[h * 2 + 1] = pack_e2m1x8_rn(scaled + 8);
                             const int jb = j + h * 16;
                             p.act_sf[(static_cast<long long>(jb / 64) * p.act_sf_k_stride + sf_row) * 4 + ((jb / 16) & 3)] =
                                 static_cast<unsigned char>(sf_byte);

@@ -383,6 +383,25 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
     return code;
 }
 
+// Eight floats -> eight packed E2M1 codes (element i in nibble i) with the hardware conversion: round to nearest,
+// ties to even, saturating at 6. Differs from e2m1_code only for values exactly on the thresholds .75, 1.75 and 3.5
+// (which go up here, down there) and in the sign of zero.
+__device__ __forceinline__ uint32_t pack_e2m1x8_rn(const float* v) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+        "}\n"
+        : "=r"(out)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return out;
+}
+
 // E4M3 round-to-nearest-even with saturation at 448, as a byte and back (UE4M3 block scales are non-negative E4M3).
 __device__ __forceinline__ uint32_t e4m3_byte(float x) {
     return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
