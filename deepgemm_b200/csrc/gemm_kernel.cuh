@@ -210,8 +210,8 @@ struct GemmSmem {
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;
     static constexpr int kOffGroups = kOffMisc + 16;
     // Epilogue staging for TMA stores: 32 rows x 64 bytes per epilogue warp, in the 64-byte swizzle (512-byte atoms).
-    // The NVFP4 kind has no room for it next to its larger scale-factor stages and stores from registers.
-    static constexpr int kStageBytesPerWarp = (kKind == kKindFp8Fp4 && BLOCK_N == 256) ? 2048 : 0;
+    // The NVFP4 kind only has room for it next to its larger scale-factor stages with 3 pipeline stages.
+    static constexpr int kStageBytesPerWarp = (BLOCK_N == 256 && (kKind == kKindFp8Fp4 || kStages <= 3)) ? 2048 : 0;
     static constexpr int kOffStage = (kOffGroups + 3 * kMaxCachedGroups * 4 + 511) / 512 * 512;
     static constexpr int kTotal = kOffStage + 8 * kStageBytesPerWarp;
     static constexpr int kDynamicBytes = kTotal + 1024;  // slack to align the base to 1024 B
@@ -648,6 +648,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             const bool store = r < t.rows_store && !DGB_SKIP(p, 32);
             const long long row = static_cast<long long>(t.row_start) + r;
             const long long sf_row = p.act_sf_transposed ? sf_row_in_cp_order(row) : row;  // used by the SwiGLU epilogues
+            if constexpr (kKind == kKindNvfp4) {
+                if (warp_has_rows) {
+                    // fold the two FP32 per-tensor scales into the accumulator
+                    const float alpha = __ldg(p.a_scale) * __ldg(p.b_scales + t.group);
+#pragma unroll
+                    for (int i = 0; i < kCols; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+                }
+            }
             if constexpr (L::kStageBytesPerWarp != 0 && EPI == kEpiBF16) {
                 if (via_tma && warp_has_rows) {
                     // 32 columns (64 bytes of BF16 per row) per TMA store; rows past rows_store hold whatever the MMA
@@ -680,12 +688,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 }
             }
             if (store) {
-                if constexpr (kKind == kKindNvfp4) {
-                    // fold the two FP32 per-tensor scales into the accumulator
-                    const float alpha = __ldg(p.a_scale) * __ldg(p.b_scales + t.group);
-#pragma unroll
-                    for (int i = 0; i < kCols; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
-                }
                 if constexpr (EPI == kEpiBF16 || EPI == kEpiF32) {
                     const long long col0 = static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
                     if constexpr (EPI == kEpiF32) {
