@@ -104,7 +104,10 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
                                 static_cast<uint64_t>(c.sfa_k_stride) * 4, 128, sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     // Wide N tiles give each tcgen05.mma enough work (128 x 256 x 32) to cover the per-K-block issue chain.
-    const int block_n = tuning().block_n != 0 ? tuning().block_n : (p.n % 256 == 0 ? 256 : 128);
+    const bool swiglu = c.epilogue == kEpiSwiGLU || c.epilogue == kEpiSwiGLUNvfp4;
+    // the SwiGLU epilogues pair the two 128-channel halves of a 256-wide tile (gate | up)
+    DGB_REQUIRE(!swiglu || p.n % 256 == 0, "the gate/up GEMM needs n (%d) to be a multiple of 256", p.n);
+    const int block_n = swiglu ? 256 : (tuning().block_n != 0 ? tuning().block_n : (p.n % 256 == 0 ? 256 : 128));
     DGB_REQUIRE((block_n == 128 || block_n == 256) && p.n % block_n == 0, "block_n %d does not divide n %d", block_n, p.n);
     rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
                             static_cast<uint64_t>(packed_k_b) * p.num_groups, static_cast<uint64_t>(c.sfb_k_stride) * 4,

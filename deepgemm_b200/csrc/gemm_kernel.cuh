@@ -627,9 +627,20 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             const bool warp_has_rows = static_cast<int>(q * 32) < t.rows_store;
             uint32_t acc[kCols];
             if (warp_has_rows) {
-                const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16) + half * kCols;
+                if constexpr (EPI == kEpiSwiGLU || EPI == kEpiSwiGLUNvfp4) {
+                    // tile columns are [gate BLOCK_N / 2 | up BLOCK_N / 2]: this thread takes its half of the gate columns
+                    // and the matching up columns
+                    const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16) + half * (kCols / 2);
 #pragma unroll
-                for (int c = 0; c < kCols / 32; ++c) tmem_ld_32x32b_x32(tmem_row + c * 32, acc + c * 32);
+                    for (int c = 0; c < kCols / 64; ++c) {
+                        tmem_ld_32x32b_x32(tmem_row + c * 32, acc + c * 32);
+                        tmem_ld_32x32b_x32(tmem_row + BLOCK_N / 2 + c * 32, acc + kCols / 2 + c * 32);
+                    }
+                } else {
+                    const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16) + half * kCols;
+#pragma unroll
+                    for (int c = 0; c < kCols / 32; ++c) tmem_ld_32x32b_x32(tmem_row + c * 32, acc + c * 32);
+                }
                 tmem_ld_wait();
             }
             tcgen05_fence_before();
@@ -715,8 +726,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         float o[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            float gv = bf16_round(__uint_as_float(acc[c * 64 + i]));
-                            float uv = bf16_round(__uint_as_float(acc[c * 64 + 32 + i]));
+                            float gv = bf16_round(__uint_as_float(acc[c * 32 + i]));
+                            float uv = bf16_round(__uint_as_float(acc[kCols / 2 + c * 32 + i]));
                             if (p.clamp > 0.0f) {
                                 gv = fminf(gv, p.clamp);
                                 uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
@@ -749,8 +760,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         st_global_v4(p.act_q + row * p.act_q_row_stride + j / 2, packed[0], packed[1], packed[2], packed[3]);
                     }
                 } else {
-                    // Columns of a tile: [gate j..j+31 | up j..j+31 | gate j+32.. | up j+32.. | ...]; this thread holds
-                    // kCols / 64 such gate/up pairs. One 32-wide output group = one UE8M0 scale.
+                    // acc[0, kCols / 2) are gate channels, acc[kCols / 2, kCols) the matching up channels (see the drain
+                    // above); one 32-wide output group = one UE8M0 scale.
                     const float w = p.row_weight != nullptr ? __ldg(p.row_weight + row) : 1.0f;
 #pragma unroll
                     for (int c = 0; c < kCols / 64; ++c) {
@@ -758,8 +769,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         float amax = 0.0f;
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            float gv = bf16_round(__uint_as_float(acc[c * 64 + i]));
-                            float uv = bf16_round(__uint_as_float(acc[c * 64 + 32 + i]));
+                            float gv = bf16_round(__uint_as_float(acc[c * 32 + i]));
+                            float uv = bf16_round(__uint_as_float(acc[kCols / 2 + c * 32 + i]));
                             if (p.clamp > 0.0f) {
                                 gv = fminf(gv, p.clamp);
                                 uv = fminf(fmaxf(uv, -p.clamp), p.clamp);

@@ -11,7 +11,7 @@ from . import _lib
 from .utils.math import align
 
 _NUM_LAYOUT_WORDS = 16
-_GATE_UP_INTERLEAVE = 32  # rows: [gate 0..31 | up 0..31 | gate 32..63 | ...], the order the L1 epilogue consumes
+_GATE_UP_INTERLEAVE = 128  # rows: [gate 0..127 | up 0..127 | gate 128..255 | ...]: an L1 output tile is 128 gate + 128 up channels
 
 
 def get_token_alignment_for_mega_moe() -> int:
@@ -149,8 +149,8 @@ def _sf_rows_to_cp_order(sf: torch.Tensor) -> torch.Tensor:
 
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
                                    l2_weights: Tuple[torch.Tensor, torch.Tensor], activation: str = 'swiglu'):
-    """Reorders the L1 weights (and their packed scale factors) so that every 64-column slice of an L1 output tile
-    holds 32 gate channels and their 32 up channels, and stores the scale factors of both layers in the row order
+    """Reorders the L1 weights (and their packed scale factors) so that every 256-row block holds 128 gate channels
+    followed by their 128 up channels (one L1 output tile), and stores the scale factors of both layers in the row order
     tcgen05.cp consumes. The transformed tensors are opaque to the caller, as in the reference
     (transform_weights_for_mega_moe, deep_gemm/mega/__init__.py:131-149, which interleaves by 8 and pre-transposes
     scale factors for its own kernel)."""

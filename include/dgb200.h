@@ -176,7 +176,7 @@ int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_ex
  * Reference: fp8_fp4_mega_moe, csrc/apis/mega.hpp:157-286 (host) and
  * deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:55-1458 (kernel).
  *   y        bf16 [num_tokens, hidden], written.
- *   l1_w     packed e2m1 [E_local, 2 * inter, hidden / 2], rows gate/up-interleaved by 32;
+ *   l1_w     packed e2m1 [E_local, 2 * inter, hidden / 2], rows gate/up-interleaved by 128;
  *   l1_w_sf  packed UE8M0 int32 (per-32), MN-major [E_local][hidden / 128][2 * inter], same row order, then every
  *            aligned group of 128 rows stored in tcgen05.cp order: row r of a group at position 4 (r % 32) + r / 32.
  *   l2_w     packed e2m1 [E_local, hidden, inter / 2]; l2_w_sf int32 [E_local][inter / 128][hidden], rows in the
@@ -208,7 +208,7 @@ int dgb200_fp8_fp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_str
  * Shared experts (reference: shared_l1_weights / shared_l2_weights of fp8_fp4_mega_moe, csrc/apis/mega.hpp:161-232, and
  * the SharedLinear1/2 tasks of the fused kernel, ...mega_moe.cuh:769-778,1275-1278): a dense FP8 x FP8 MLP applied to
  * every token of this rank, its BF16 output row added to the token's combine after the top-k slots.
- *   shared_l1_w e4m3 [2 * shared_inter, hidden] (rows gate/up-interleaved by 32), shared_l1_w_sf packed UE8M0 int32
+ *   shared_l1_w e4m3 [2 * shared_inter, hidden] (rows gate/up-interleaved by 128), shared_l1_w_sf packed UE8M0 int32
  *   (per-32), MN-major [hidden / 128][2 * shared_inter], 128-row groups in tcgen05.cp order; shared_l2_w e4m3
  *   [hidden, shared_inter], shared_l2_w_sf [shared_inter / 128][hidden]. shared_intermediate_hidden = 0: none.
  * The buffer must have been sized with dgb200_get_symm_buffer_layout_for_mega_moe_ex and the same shared size; the
@@ -252,7 +252,7 @@ int dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(int32_t num_ranks, int32_t 
                                                      int64_t* out);
 
 /* Same stages and argument meaning as dgb200_fp8_fp4_mega_moe with NVFP4 tensors:
- *   l1_w packed e2m1 [E_local, 2 * inter, hidden / 2] (gate/up interleaved by 32), l1_w_sf packed UE4M3 int32
+ *   l1_w packed e2m1 [E_local, 2 * inter, hidden / 2] (gate/up interleaved by 128), l1_w_sf packed UE4M3 int32
  *   MN-major [E_local][hidden / 64][2 * inter], l1_w_scales float [E_local]; l2_w [E_local, hidden, inter / 2],
  *   l2_w_sf [E_local][inter / 64][hidden], l2_w_scales float [E_local]; scale rows in the 128-group order above.
  *   x_scale   device float: per-tensor scale the caller quantised x with; must hold the same value on every rank
