@@ -10,6 +10,7 @@
 
 #include "host_common.cuh"
 #include "gemm_kernel.cuh"
+#include "gemm_swap_kernel.cuh"
 #include "quant_kernels.cuh"
 #include "moe_kernels.cuh"
 
@@ -57,6 +58,7 @@ struct GemmCall {
 
 // Process-wide tuning knobs (defaults are the measured best on B200).
 struct Tuning {
+    int swap_ab = -1;  // layer GEMMs: tokens on the UMMA N side (-1 = by expected rows per expert, 0 = never, 1 = always)
     int prefetch_distance = 0;
     int block_n = 0;  // 0 = automatic
     int debug_skip = 0;
@@ -196,6 +198,77 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 #undef DGB_LAUNCH
 }
 
+
+// The layer GEMMs with swapped operands (gemm_swap_kernel.cuh): weights on M, an expert's tokens on N. Takes the same
+// call description as run_gemm; only the FP8 x FP4 / FP8 x FP8 kind, the psum layout with 128-row segments, scale
+// factors in tcgen05.cp order and the SwiGLU / BF16 epilogues.
+template <int EPI>
+int launch_gemm_swap(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_sfx, const CUtensorMap& tm_sfw,
+                     const GemmParams& p, int grid, cudaStream_t stream) {
+    auto kernel = dgb200_swap_gemm_kernel<EPI>;
+    static bool configured = false;
+    static int configured_device = -1;
+    int dev = 0;
+    DGB_CUDA(cudaGetDevice(&dev));
+    if (!configured || configured_device != dev) {
+        DGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SwapSmem::kDynamicBytes));
+        configured = true;
+        configured_device = dev;
+    }
+    kernel<<<grid, kGemmThreads, SwapSmem::kDynamicBytes, stream>>>(tm_x, tm_w, tm_sfx, tm_sfw, p);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int run_gemm_swap(GemmCall& c, cudaStream_t stream) {
+    GemmParams& p = c.p;
+    DGB_REQUIRE(c.kind == kKindFp8Fp4 && p.mode == kModePsum && p.alignment == 128 && p.sf_transposed == 1,
+                "the swapped-operand kernel serves the FP8 layer path only");
+    DGB_REQUIRE(c.epilogue == kEpiSwiGLU || c.epilogue == kEpiBF16, "unknown epilogue %d for the swapped-operand kernel", c.epilogue);
+    DGB_REQUIRE(p.k > 0 && p.k % 128 == 0 && p.n > 0 && p.n % 256 == 0, "k must be a multiple of 128 and n of 256");
+    DGB_REQUIRE(p.num_groups > 0 && p.num_groups <= kMaxCachedGroups, "at most %d groups", kMaxCachedGroups);
+    DGB_REQUIRE(p.gran_a == 32 && p.gran_b == 32, "per-32 scales only");
+    DGB_REQUIRE(c.sfa_k_stride % 4 == 0 && c.sfb_k_stride % 4 == 0 && c.sfb_k_stride >= p.n && c.sfa_k_stride >= c.a_rows_total,
+                "packed scale-factor strides must be multiples of 4 ints that cover MN");
+    const int packed_k = p.k / 128;
+    DGB_REQUIRE(p.num_groups == 1 || c.sfb_group_stride == static_cast<long long>(packed_k) * c.sfb_k_stride,
+                "scale factors of B: group stride must equal packed K x MN stride");
+    p.sfb_packed_k = packed_k;
+    if (c.a_rows_total == 0) return 0;
+    CUtensorMap tm_x, tm_w, tm_sfx, tm_sfw;
+    int rc = make_tensor_map_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, static_cast<uint64_t>(p.k),
+                                static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.k), 128, kSwapMaxTok,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_sfx, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
+                            static_cast<uint64_t>(packed_k), static_cast<uint64_t>(c.sfa_k_stride) * 4, 256, 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_sfw, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
+                            static_cast<uint64_t>(p.num_groups) * packed_k, static_cast<uint64_t>(c.sfb_k_stride) * 4, 256, 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const uint64_t w_rows = static_cast<uint64_t>(p.num_groups) * p.n;
+    if (c.b_is_fp4) {
+        rc = make_tensor_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, c.b, static_cast<uint64_t>(p.k), w_rows,
+                                static_cast<uint64_t>(p.k / 2), 128, 256, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = kFmtE2M1_F8F6F4;
+        p.b_tx_bytes = 256 * 64;  // the mbarrier is credited with the packed bytes
+    } else {
+        rc = make_tensor_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, static_cast<uint64_t>(p.k), w_rows,
+                                static_cast<uint64_t>(p.k), 128, 256, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = kFmtE4M3;
+        p.b_tx_bytes = 256 * 128;
+    }
+    if (rc) return rc;
+    p.trace = tuning().trace;
+    p.trace_cap = tuning().trace_cap;
+    int sms = 0;
+    rc = effective_num_sms(&sms);
+    if (rc) return rc;
+    if (c.epilogue == kEpiSwiGLU) return launch_gemm_swap<kEpiSwiGLU>(tm_x, tm_w, tm_sfx, tm_sfw, p, sms, stream);
+    return launch_gemm_swap<kEpiBF16>(tm_x, tm_w, tm_sfx, tm_sfw, p, sms, stream);
+}
 
 // --------------------------------------------------------------------------------------------------------------
 // Mega-MoE buffer layout. One flat buffer per rank holds the caller-written inputs and every intermediate of the
@@ -347,11 +420,37 @@ int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, i
 // into l2_out in the same row order.
 int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
                     const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
-                    cudaStream_t stream, int stage_event_base) {
+                    cudaStream_t stream, int stage_event_base, long long expected_rows_per_expert) {
     const int E = l.num_local_experts;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
     const bool nvfp4 = quant.kind == kKindNvfp4;
+    // Tokens on the UMMA N side pay off while an expert's rows fit one token tile (no second pass over its weights
+    // for a few rows beyond 128); with many rows per expert both orientations run 128-row tiles.
+    const bool swap = !nvfp4 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0 &&
+                      (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= kSwapMaxTok + 32));
     int rc = 0;
+    // Shared memory bandwidth bounds both kernels (every operand byte is written once by TMA and read by the MMAs):
+    // with tokens on M an expert costs its weights once per 128 rows, with tokens on N once per kSwapMaxTok rows but
+    // the token tile is read twice. So groups of 129..kSwapMaxTok rows go to the swapped kernel, all others to the
+    // tokens-on-M kernel (two launches per GEMM, each skipping the other's groups).
+    // Only the down GEMM is split by default: the swapped SwiGLU epilogue (one thread = one channel, a fully unrolled
+    // walk over up to 80 tokens) is instruction-fetch bound and costs the gate/up GEMM more than the saved passes.
+    auto run_split = [&](GemmCall& c) -> int {
+        if (!swap || (c.epilogue == kEpiSwiGLU && tuning().swap_ab != 1)) return run_gemm(c, stream);
+        GemmCall c2 = c;
+        c.p.rows_lo = 129;
+        c.p.rows_hi = kSwapMaxTok;
+        c.p.rows_skip = 1;
+        c2.p.rows_lo = 129;
+        c2.p.rows_hi = kSwapMaxTok;
+        c2.p.rows_skip = 0;
+        if (tuning().swap_ab == 1) {  // everything through the swapped kernel
+            c2.p.rows_lo = c2.p.rows_hi = 0;
+            return run_gemm_swap(c2, stream);
+        }
+        const int rc1 = run_gemm(c, stream);
+        return rc1 ? rc1 : run_gemm_swap(c2, stream);
+    };
     {
         GemmCall c{};
         c.kind = quant.kind;
@@ -391,7 +490,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
         p.fast_math = fast_math;
-        if ((rc = run_gemm(c, stream))) return rc;
+        if ((rc = run_split(c))) return rc;
     }
     if ((rc = record_stage(stage_event_base, stream))) return rc;
     {
@@ -426,7 +525,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.a_scale = quant.act_scale;
         p.b_scales = quant.l2_scales;
         p.sf_transposed = 1;
-        if ((rc = run_gemm(c, stream))) return rc;
+        if ((rc = run_split(c))) return rc;
     }
     return record_stage(stage_event_base + 1, stream);
 }
@@ -573,7 +672,8 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
     if ((rc = record_stage(2, stream))) return rc;
 
-    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3,
+                         static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts);
     if (rc) return rc;
     if (with_shared && num_tokens > 0) {
         if (quant.x_bf16 == nullptr && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
@@ -666,7 +766,8 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
 
     if ((rc = record_stage(2, stream))) return rc;
     // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
-    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3);
+    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3,
+                         static_cast<long long>(num_tokens) * num_topk / num_experts);
     if (rc) return rc;
     if (with_shared) {
         if (quant.x_bf16 == nullptr && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
@@ -742,7 +843,10 @@ int dgb200_set_num_sms(int num_sms) {
 
 int dgb200_set_tuning(const char* name, int32_t value) {
     DGB_REQUIRE(name != nullptr, "null name");
-    if (std::strcmp(name, "prefetch_distance") == 0) {
+    if (std::strcmp(name, "swap_ab") == 0) {
+        DGB_REQUIRE(value >= -1 && value <= 1, "swap_ab must be -1 (automatic), 0 or 1");
+        tuning().swap_ab = value;
+    } else if (std::strcmp(name, "prefetch_distance") == 0) {
         DGB_REQUIRE(value >= 0 && value <= 4096, "prefetch_distance must be in [0, 4096]");
         tuning().prefetch_distance = value;
     } else if (std::strcmp(name, "block_n") == 0) {

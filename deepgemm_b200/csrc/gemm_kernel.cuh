@@ -63,6 +63,9 @@ struct GemmParams {
     unsigned b_tx_bytes;     // bytes the B tile's TMA reports to the mbarrier
     unsigned b_fmt;          // kFmtE2M1_F8F6F4 or kFmtE4M3
     int store_padding;       // psum only: also write the rows between a group's end and its aligned end
+    int rows_lo, rows_hi;    // psum / masked layouts: only groups whose valid rows lie in [rows_lo, rows_hi] (rows_skip = 0)
+    int rows_skip;           // ... or outside it (rows_skip = 1) are computed; {0, 0, 0} = every group. Lets two kernels
+                             // with different tile orientations split the groups of one GEMM by size.
     int prefetch_distance;   // K blocks the weight prefetch cursor runs ahead of the loads (0 = off)
     const unsigned char* b_ptr;  // raw view of the weights for the prefetch cursor (the loads go through the tensor map)
     long long b_row_bytes;       // row pitch of B in bytes
@@ -110,6 +113,12 @@ struct GroupTable {
     const int* tiles_end;  // tiles of groups 0..g inclusive
     bool cached;           // false: walk the global layout array with the arithmetic below (more groups than the table holds)
 };
+
+__device__ __forceinline__ bool group_selected(const GemmParams& p, int rows) {
+    if (p.rows_lo == 0 && p.rows_hi == 0) return true;
+    const bool inside = rows >= p.rows_lo && rows <= p.rows_hi;
+    return p.rows_skip ? !inside : inside;
+}
 
 template <int BLOCK_N>
 struct TileScheduler {
@@ -182,7 +191,7 @@ struct TileScheduler {
         while (g < p.num_groups) {
             int start, rows, rows_store;
             group_extent(p, tab.lay, g, start, rows, rows_store);
-            const int tiles_g = (max(rows, rows_store) + 127) / 128 * num_n_blocks;
+            const int tiles_g = group_selected(p, rows) ? (max(rows, rows_store) + 127) / 128 * num_n_blocks : 0;
             if (tile < tiles_before_g + tiles_g) {
                 fill(t, g, start, rows_store, tile - tiles_before_g);
                 return true;
@@ -312,7 +321,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             TileScheduler<BLOCK_N>::group_extent(p, p.layout, i, start, rows, rows_store);
             group_cache[i] = __ldg(p.layout + i);
             group_start[i] = start;
-            group_tiles_end[i] = (max(rows, rows_store) + 127) / 128 * (p.n / BLOCK_N);
+            group_tiles_end[i] = group_selected(p, rows) ? (max(rows, rows_store) + 127) / 128 * (p.n / BLOCK_N) : 0;
         }
         __syncthreads();
         if (warp == 0) {
