@@ -230,3 +230,42 @@ def test_shared_experts(dg, tokens, hidden, inter, experts, topk, num_shared, fu
     with pytest.raises(RuntimeError):
         dg.fp8_fp4_mega_moe(y, l1, l2, dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter),
                             shared_l1_weights=sl1, shared_l2_weights=sl2)
+
+
+@pytest.mark.parametrize('tokens,hidden,inter,experts,topk', [
+    (300, 512, 256, 4, 2),     # 150 rows per expert on average: one token tile of up to 160 rows
+    (700, 256, 256, 4, 2),     # 350 rows per expert: cut into 128-row token tiles
+    (40, 512, 128, 8, 3),      # few rows, UMMA N = 16 .. 32; inter 128 -> one 256-row weight block in L1
+])
+def test_swapped_operand_kernel_forced(dg, tokens, hidden, inter, experts, topk):
+    """Both layer GEMMs through the swapped-operand kernel (weights on UMMA M, tokens on N), including its SwiGLU
+    epilogue, which the layer does not select by default."""
+    from deepgemm_b200 import _lib
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=700 + tokens, masked_ratio=0.1)
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'],
+                          clamp=5.0)
+    _lib.check(_lib.lib().dgb200_set_tuning(b'swap_ab', 1))
+    try:
+        got, _ = _run_layer(dg, c, tokens, hidden, inter, experts, topk, clamp=5.0)
+    finally:
+        _lib.check(_lib.lib().dgb200_set_tuning(b'swap_ab', -1))
+    assert not torch.isnan(got.float()).any()
+    assert quant.calc_diff(got, want) <= FP4_TOL
+    _lib.check(_lib.lib().dgb200_set_tuning(b'swap_ab', 0))
+    try:
+        ref, _ = _run_layer(dg, c, tokens, hidden, inter, experts, topk, clamp=5.0)
+    finally:
+        _lib.check(_lib.lib().dgb200_set_tuning(b'swap_ab', -1))
+    assert quant.calc_diff(got, ref) <= 1e-5  # same arithmetic, only the FP32 accumulation order inside the MMA may differ
+
+
+def test_down_gemm_split_by_group_size(dg):
+    """Default dispatch: experts of 129..160 rows take the swapped kernel in the down GEMM, the others the tokens-on-M
+    kernel. Router logits are shaped so that both kinds (and an empty expert) occur."""
+    tokens, hidden, inter, experts, topk = 520, 256, 128, 5, 1
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=77, empty_experts=(4,))
+    counts = torch.bincount(c['topk_idx'].reshape(-1), minlength=experts)
+    assert ((counts >= 129) & (counts <= 160)).any() and (counts[:4] <= 128).any(), 'the seed no longer gives both kinds'
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+    got, _ = _run_layer(dg, c, tokens, hidden, inter, experts, topk)
+    assert quant.calc_diff(got, want) <= FP4_TOL
