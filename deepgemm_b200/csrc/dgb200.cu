@@ -295,6 +295,7 @@ struct MegaLayout {
     long long src_of_row, row_weight;
     long long all_counts, my_base, flags;  // expert-parallel exchange: counts of every rank, this rank's bases, barrier flags
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
+    long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
     long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
     long long token_rows;
@@ -367,6 +368,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l2_acts = take(l.max_rows * act_row_bytes(kind, inter));
     l.l2_sf = take(l.max_rows * sf_ints_per_row(kind, inter) * 4);
     l.l2_out = take(l.max_rows * hidden * 2);
+    l.l1_tmp = kind == kKindFp8Fp4 ? take(l.max_rows * inter * 4) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
         DGB_REQUIRE(kind == kKindFp8Fp4 && shared_inter % 128 == 0, "shared experts need the FP8 x FP4 layer and a multiple of 128 channels");
@@ -435,9 +437,33 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     // tokens-on-M kernel (two launches per GEMM, each skipping the other's groups).
     // Only the down GEMM is split by default: the swapped SwiGLU epilogue (one thread = one channel, a fully unrolled
     // walk over up to 80 tokens) is instruction-fetch bound and costs the gate/up GEMM more than the saved passes.
+    // The gate/up GEMM's swapped half writes BF16 gate/up values into l1_tmp and a small kernel applies SwiGLU + FP8
+    // requant to those rows (same bits as the fused epilogue): the swapped kernel's own SwiGLU epilogue, a fully
+    // unrolled walk over up to 80 tokens per thread, is instruction-fetch bound (swap_ab = 1 forces it for testing).
     auto run_split = [&](GemmCall& c) -> int {
-        if (!swap || (c.epilogue == kEpiSwiGLU && tuning().swap_ab != 1)) return run_gemm(c, stream);
+        if (!swap) return run_gemm(c, stream);
         GemmCall c2 = c;
+        if (c.epilogue == kEpiSwiGLU && tuning().swap_ab != 1) {
+            c.p.rows_lo = 129;
+            c.p.rows_hi = kSwapMaxTok;
+            c.p.rows_skip = 1;
+            c2.p.rows_lo = 129;
+            c2.p.rows_hi = kSwapMaxTok;
+            c2.p.rows_skip = 0;
+            c2.epilogue = kEpiBF16;
+            c2.p.d = base + l.l1_tmp;
+            c2.p.d_row_stride = 2 * intermediate_hidden;
+            int rc1 = run_gemm(c, stream);
+            if (rc1 == 0) rc1 = run_gemm_swap(c2, stream);
+            if (rc1) return rc1;
+            const dim3 grid((kSwapMaxTok + 7) / 8, E);
+            dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, stream>>>(
+                reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
+                129, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
+                reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
+            DGB_CUDA(cudaGetLastError());
+            return 0;
+        }
         c.p.rows_lo = 129;
         c.p.rows_hi = kSwapMaxTok;
         c.p.rows_skip = 1;

@@ -11,6 +11,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "ptx.cuh"
 #include "quant_kernels.cuh"
@@ -535,6 +536,65 @@ dgb200_sf_rows_to_cp_order_kernel(const unsigned* __restrict__ sf, int tokens, i
     for (int i = threadIdx.x; i < 32 * ints_per_row; i += 256) {
         const int c = i >> 5, r = i & 31;
         if (t0 + r < tokens) out[static_cast<long long>(c) * k_stride + sf_row_in_cp_order(t0 + r)] = sf_tile[c * 33 + r];
+    }
+}
+
+// SwiGLU + FP8 requant over rows of BF16 gate/up activations that a GEMM wrote without the fused epilogue (the
+// swapped-operand kernel's SwiGLU epilogue is instruction-fetch bound, so for the experts it serves the gate/up GEMM
+// stores BF16 and this kernel finishes; the arithmetic is the fused epilogue's, bit for bit: the accumulators are
+// rounded to BF16 there too before anything else happens).
+//   tmp  bf16 [rows, 2 * inter], columns in blocks of 256 = [gate 128 | up 128] (the L1 weight row order)
+//   out  e4m3 [rows, inter] + packed UE8M0 scales (one int per row and 128 channels, rows in tcgen05.cp order)
+// grid (ceil(max rows per expert / 8), experts); a warp owns a row, a lane 4 consecutive channels of a 128-block.
+// Only experts whose row count lies in [rows_lo, rows_hi] are processed.
+__global__ void __launch_bounds__(256)
+dgb200_swiglu_requant_rows_kernel(const __nv_bfloat16* __restrict__ tmp, const int* __restrict__ expert_start,
+                                  const int* __restrict__ expert_end, int rows_lo, int rows_hi, int inter,
+                                  const float* __restrict__ row_weight, float clamp, int fast_math,
+                                  unsigned char* __restrict__ act_q, long long act_q_row_stride,
+                                  unsigned* __restrict__ act_sf, long long act_sf_k_stride) {
+    const int e = blockIdx.y;
+    const int start = expert_start[e], rows = expert_end[e] - start;
+    if (rows < rows_lo || rows > rows_hi) return;
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const long long row = static_cast<long long>(start) + r;
+    const float w = row_weight != nullptr ? row_weight[row] : 1.0f;
+    const __nv_bfloat16* src = tmp + row * 2 * inter;
+    for (int blk = 0; blk < inter / 128; ++blk) {
+        const uint2 g2 = *reinterpret_cast<const uint2*>(src + blk * 256 + lane * 4);
+        const uint2 u2 = *reinterpret_cast<const uint2*>(src + blk * 256 + 128 + lane * 4);
+        const unsigned gw[2] = {g2.x, g2.y}, uw[2] = {u2.x, u2.y};
+        float o[4];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float gv = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xffff0000u) : (gw[i >> 1] << 16));
+            float uv = __uint_as_float((i & 1) ? (uw[i >> 1] & 0xffff0000u) : (uw[i >> 1] << 16));
+            if (clamp > 0.0f) {
+                gv = fminf(gv, clamp);
+                uv = fminf(fmaxf(uv, -clamp), clamp);
+            }
+            const float silu = fast_math ? gv * rcp_approx(1.0f + __expf(-gv)) : gv / (1.0f + expf(-gv));
+            o[i] = silu * uv * w;
+            amax = fmaxf(amax, fabsf(o[i]));
+        }
+        // a scale group is 32 channels = 8 lanes
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float s = amax * (1.0f / 448.0f);
+        const unsigned bits = __float_as_uint(s);
+        unsigned ex = (bits >> 23) & 0xffu;
+        if (bits & 0x7fffffu) ++ex;
+        ex = min(max(ex, 1u), 254u);
+        const float sf_inv = __uint_as_float((254u - ex) << 23);
+        const __nv_fp8x4_e4m3 q4(make_float4(o[0] * sf_inv, o[1] * sf_inv, o[2] * sf_inv, o[3] * sf_inv));
+        *reinterpret_cast<unsigned*>(act_q + row * act_q_row_stride + blk * 128 + lane * 4) = q4.__x;
+        // the block's packed scale int = the scale bytes of lanes 0, 8, 16, 24
+        const unsigned e1 = __shfl_sync(0xffffffffu, ex, 8), e2 = __shfl_sync(0xffffffffu, ex, 16), e3 = __shfl_sync(0xffffffffu, ex, 24);
+        if (lane == 0) act_sf[static_cast<long long>(blk) * act_sf_k_stride + sf_row_in_cp_order(row)] = ex | (e1 << 8) | (e2 << 16) | (e3 << 24);
     }
 }
 
