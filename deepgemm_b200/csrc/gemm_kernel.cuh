@@ -509,7 +509,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
-            if (lane == 0) trace_point(p, 3, static_cast<int>(iter));
         }
         }
     } else if (warp == 2) {

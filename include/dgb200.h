@@ -37,13 +37,20 @@ int dgb200_version(void);
 int dgb200_set_num_sms(int num_sms);
 int dgb200_get_num_sms(void);
 
-/* Process-wide tuning knobs of the GEMM kernels: "block_n" (0 = automatic, 128 or 256: width of an output tile).
- * Plays the role of the reference's heuristics overrides (csrc/apis/runtime.hpp:21-41). */
+/* Process-wide tuning knobs of the GEMM kernels. Plays the role of the reference's heuristics overrides
+ * (csrc/apis/runtime.hpp:21-41).
+ *   "block_n"            0 = automatic, 128 or 256: width of an output tile of the tokens-on-M kernel.
+ *   "swap_ab"            layer GEMMs: -1 = split the experts by size between the two tile orientations when the
+ *                        expected rows per expert are small (default), 0 = tokens-on-M kernel only, 1 = everything
+ *                        through the swapped-operand kernel including its fused SwiGLU epilogue (testing).
+ *   "prefetch_distance"  K blocks an L2 prefetch cursor runs ahead of the weight loads (0 = off, the default).
+ *   "debug_skip"         timing experiments, only honoured by builds with -DDGB200_INSTRUMENT. */
 int dgb200_set_tuning(const char* name, int32_t value);
 
-/* Debugging aid: while set, CTA 0 of every GEMM launch records clock64() per warp role and K block into
- * device_buffer (int64 [8][capacity_per_role]; roles: 0/1 producer before/after issue, 2/3 scale-factor transposer,
- * 4/5 MMA issuer, 6/7 epilogue per tile). NULL switches it off. No reference counterpart. */
+/* Debugging aid, only honoured by builds with -DDGB200_INSTRUMENT: while set, CTA 0 of every GEMM launch records
+ * clock64() per trace point and K block (or tile) into device_buffer, int64 [16][capacity_per_role]. Points: 0/1 and
+ * 9/10 loaders before/after issue, 2/3 scale-factor transposer, 4/5 (8, 11..15: finer steps) MMA issuer, 6/7
+ * epilogue per tile. NULL switches it off. No reference counterpart. */
 int dgb200_debug_set_trace(void* device_buffer, int32_t capacity_per_role);
 
 /* Synchronises `stream`, copies the 8-word device status block to `out_words` (may be NULL) and clears it.
