@@ -274,6 +274,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     constexpr uint32_t kSfCol0 = kAccumCols * kNumAccum;
     constexpr uint32_t kTmemCols = 512;
     static_assert(kSfCol0 + kStages * kSfColsPerStage <= kTmemCols, "TMEM budget");
+    // NVFP4 needs 12 tcgen05.cp per K block (4 scale ints per row); issued next to the 4 MMAs they make the MMA warp's
+    // instruction stream, not the tensor pipe, the bound. With scale factors in tcgen05.cp order warp 2 has no
+    // transposing to do and issues the copies instead, one stage ahead of the MMAs.
+    constexpr bool kCpByHelper = kKind == kKindNvfp4;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -461,8 +465,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             for (int kb = 0; kb < num_kb; ++kb) {
                 // scale factors stored in tcgen05.cp order need no transposer pass: the loads' barrier is enough
                 if (lane == 0) trace_point(p, 8, trace_i);
-                ok = mbar_wait((p.sf_transposed ? full_bar : sf_ready_bar) + stage, phase, abort_flag, kTimeoutSfReady, kb);
+                ok = mbar_wait(((p.sf_transposed && !kCpByHelper) ? full_bar : sf_ready_bar) + stage, phase, abort_flag,
+                               kTimeoutSfReady, kb);
                 if (!ok) break;
+                if (kCpByHelper && p.sf_transposed) tcgen05_fence_after();  // the helper warp's tcgen05.cp precede our MMAs
                 if (lane == 0) trace_point(p, 11, trace_i);
                 // No tcgen05 fence here: the data this wait covers was written to shared memory through the async proxy
                 // (TMA, or the transposer's stores followed by its proxy fence), not by tcgen05 operations.
@@ -470,17 +476,22 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     trace_point(p, 4, trace_i);
                     // One tcgen05.cp moves the scales of 128 rows for one MMA (one packed int per row) into 4 TMEM columns.
                     const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
+                    const bool cp_here = !(kCpByHelper && p.sf_transposed);
                     if (kb % a_per == 0) {
                         tmem_sfa = sf_cols;
+                        if (cp_here) {
 #pragma unroll
-                        for (int b = 0; b < kSfBlocksA; ++b)
-                            tcgen05_cp_32x128b_warpx4(tmem_sfa + b * 4, make_sf_desc(sfa_smem + stage * L::kSfaBytes + b * 512));
+                            for (int b = 0; b < kSfBlocksA; ++b)
+                                tcgen05_cp_32x128b_warpx4(tmem_sfa + b * 4, make_sf_desc(sfa_smem + stage * L::kSfaBytes + b * 512));
+                        }
                     }
                     if (kb % b_per == 0) {
                         tmem_sfb = sf_cols + 4 * kSfBlocksA;
+                        if (cp_here) {
 #pragma unroll
-                        for (int b = 0; b < kSfBlocksB; ++b)
-                            tcgen05_cp_32x128b_warpx4(tmem_sfb + b * 4, make_sf_desc(sfb_smem + stage * L::kSfbBytes + b * 512));
+                            for (int b = 0; b < kSfBlocksB; ++b)
+                                tcgen05_cp_32x128b_warpx4(tmem_sfb + b * 4, make_sf_desc(sfb_smem + stage * L::kSfbBytes + b * 512));
+                        }
                     }
                     const uint64_t adesc = make_kmajor_sw128_desc(a_base + stage * L::kABytes);
                     const uint64_t bdesc = make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
@@ -560,6 +571,33 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 if (lane == 0) trace_point(p, 3, trace_i);
                 ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (kCpByHelper && p.sf_transposed != 0) {
+            TileScheduler<BLOCK_N> cp_sched(p, group_layout);
+            const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
+            const bool leader = elect_one();
+            stage = 0;
+            phase = 0;
+            ok = true;
+            while (ok && cp_sched.next(t)) {
+                if (t.group < 0) continue;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
+                    if (!ok) break;
+                    if (leader) {
+                        const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
+#pragma unroll
+                        for (int b = 0; b < kSfBlocksA; ++b)
+                            tcgen05_cp_32x128b_warpx4(sf_cols + b * 4, make_sf_desc(sfa_smem + stage * L::kSfaBytes + b * 512));
+#pragma unroll
+                        for (int b = 0; b < kSfBlocksB; ++b)
+                            tcgen05_cp_32x128b_warpx4(sf_cols + 4 * kSfBlocksA + b * 4,
+                                                      make_sf_desc(sfb_smem + stage * L::kSfbBytes + b * 512));
+                        tcgen05_commit(sf_ready_bar + stage);  // arrives once the copies above have completed
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
             }
         }
         if (p.sf_transposed != 0 && p.prefetch_distance > 0) {
