@@ -187,3 +187,95 @@ def test_two_rank_nvfp4_layer_matches_oracle():
         assert torch.equal(got['y0'], got['y1'])
         assert not torch.isnan(got['y0'].float()).any()
         assert quant.calc_diff(got['y0'], want) <= 2e-3
+
+
+# ---- BASELINE expert-parallel configuration at full size on 2 GPUs: 8192 tokens per rank, hidden 7168, 256 experts
+# sharded over the ranks, top-8, intermediate 2048, Zipf-biased routing. Weights and activations are drawn and quantised
+# on each GPU (the same seed for the weights of an expert on whatever rank owns it).
+def _worker_full(rank, world, port, results):
+    import torch.distributed as dist
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        tokens, hidden, inter, experts, topk = 8192, 7168, 2048, 256, 8
+        per_rank = experts // world
+        l1_q = torch.empty((per_rank, 2 * inter, hidden // 2), dtype=torch.int8, device='cuda')
+        l1_sf = torch.empty((per_rank, 2 * inter, hidden // 32), dtype=torch.float32, device='cuda')
+        l2_q = torch.empty((per_rank, hidden, inter // 2), dtype=torch.int8, device='cuda')
+        l2_sf = torch.empty((per_rank, hidden, inter // 32), dtype=torch.float32, device='cuda')
+        for e in range(per_rank):
+            g = torch.Generator(device='cuda').manual_seed(1000 + rank * per_rank + e)
+            w = torch.randn(2 * inter, hidden, device='cuda', dtype=torch.bfloat16, generator=g) * 0.02
+            l1_q[e], l1_sf[e] = dg.utils.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+            w = torch.randn(hidden, inter, device='cuda', dtype=torch.bfloat16, generator=g) * 0.02
+            l2_q[e], l2_sf[e] = dg.utils.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+        l1, l2 = dg.transform_weights_for_mega_moe(
+            (l1_q, dg.transform_sf_into_required_layout(l1_sf, 2 * inter, hidden, (1, 32), per_rank)),
+            (l2_q, dg.transform_sf_into_required_layout(l2_sf, hidden, inter, (1, 32), per_rank)))
+        gen = torch.Generator().manual_seed(2024)
+        popularity = torch.empty(experts)
+        popularity[torch.randperm(experts, generator=gen)] = 1.0 / torch.arange(1, experts + 1, dtype=torch.float32)
+        torch.manual_seed(50 + rank)
+        x = torch.randn(tokens, hidden).bfloat16().cuda()
+        logits = (torch.randn(tokens, experts) + torch.log(popularity / popularity.sum())).cuda()
+        buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, experts, tokens, topk, hidden, inter)
+        y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
+        dg.fp8_fp4_mega_moe_bf16_input(y, x, l1, l2, buf, logits=logits, fast_math=False)
+        assert _lib.device_status()[0] == 0
+        idx = buf.topk_idx.cpu()
+        # every rank needs every rank's routing for the plan: gather the index tensors over NCCL
+        all_idx = [torch.empty_like(buf.topk_idx) for _ in range(world)]
+        dist.all_gather(all_idx, buf.topk_idx.contiguous())
+        lay = buf.layout
+        dest = buf.buffer[lay['dest_row']:lay['dest_row'] + tokens * topk * 4].view(torch.int32).cpu()
+        end = buf.buffer[lay['expert_end']:lay['expert_end'] + per_rank * 4].view(torch.int32).cpu()
+        # sampled tokens: re-evaluate from the same quantised bits; the weights of remote experts are regenerated here
+        x_q, x_sf = dg.utils.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32)
+        samples = {}
+        for t in (0, 4097, 8191):
+            rows = []
+            for k in range(topk):
+                e = int(idx[t, k])
+                g = torch.Generator(device='cuda').manual_seed(1000 + e)
+                w1 = torch.randn(2 * inter, hidden, device='cuda', dtype=torch.bfloat16, generator=g) * 0.02
+                w2 = torch.randn(hidden, inter, device='cuda', dtype=torch.bfloat16, generator=g) * 0.02
+                q1, s1 = dg.utils.per_token_cast_to_fp4(w1, use_ue8m0=True, gran_k=32)
+                q2, s2 = dg.utils.per_token_cast_to_fp4(w2, use_ue8m0=True, gran_k=32)
+                rows.append((q1.cpu(), s1.cpu(), q2.cpu(), s2.cpu()))
+            samples[t] = dict(x_q=x_q[t:t + 1].cpu(), x_sf=x_sf[t:t + 1].cpu(), rows=rows, w=buf.topk_weights[t].cpu(), y=y[t].cpu())
+        results[rank] = dict(idx=idx, all_idx=[a.cpu() for a in all_idx], dest=dest, end=end, logits=logits.cpu(), samples=samples)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs 2 GPUs')
+def test_two_rank_full_size_plan_and_sampled_tokens():
+    import torch.multiprocessing as mp
+    from oracle import moe as omoe
+    from oracle import quant
+    world, experts, topk, hidden = 2, 256, 8, 7168
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker_full, args=(world, _free_port(), results), nprocs=world, join=True)
+    all_counts = torch.stack([omoe.ep_counts(results[r]['idx'], experts) for r in range(world)])
+    for rank in range(world):
+        got = results[rank]
+        want_idx, _ = omoe.route_sigmoid_topk(got['logits'], topk)
+        assert torch.equal(got['idx'], want_idx), 'routing must be bit-exact'
+        my_base, _, want_end = omoe.ep_plan(all_counts, rank, 128)
+        assert torch.equal(got['end'].long(), want_end)
+        assert torch.equal(got['dest'].long(), omoe.ep_dest_rows(got['idx'], my_base, experts))
+        for t, s in got['samples'].items():
+            acc = torch.zeros(hidden)
+            for k in range(topk):
+                q1, s1, q2, s2 = s['rows'][k]
+                a1 = quant.dequantize_fp8(s['x_q'], s['x_sf'], 32) @ quant.dequantize_fp4(q1, s1, 32).T
+                # transform_weights_for_mega_moe reorders rows only: the untransformed [gate | up] order is what the oracle takes
+                a2_q, a2_sf = omoe.swiglu_requant(a1, s['w'][k:k + 1], None)
+                a2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(q2, s2, 32).T
+                acc += a2.bfloat16().float()[0]
+            assert quant.calc_diff(s['y'], acc.bfloat16()) <= 2e-3

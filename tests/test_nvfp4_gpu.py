@@ -208,3 +208,57 @@ def test_layer_buffer_reuse_is_deterministic(dg):
     assert torch.equal(y_small_reused, y_small_fresh)
     y_big_again, _ = _run_layer(dg, big, 256, hidden, inter, experts, topk, s, buf=buf)
     assert torch.equal(y_big, y_big_again)
+
+
+def test_full_prefill_config_permutation_and_sampled_tokens(dg):
+    """BASELINE NVFP4 prefill layer at full size: 16384 tokens, hidden 7168, 256 experts, top-8, inter 2048. Weights and
+    activations are quantised on the GPU. Checked: routing and the permutation of all 131072 entries bit-exact against
+    the oracle; y of sampled tokens against the oracle evaluated from the same quantised bits."""
+    tokens, hidden, inter, experts, topk = 16384, 7168, 2048, 256, 8
+    torch.manual_seed(0)
+    x = torch.randn(tokens, hidden, device='cuda', dtype=torch.bfloat16)
+    logits = torch.randn(tokens, experts, device='cuda')
+    l1_q = torch.empty((experts, 2 * inter, hidden // 2), dtype=torch.int8, device='cuda')
+    l1_sf = torch.empty((experts, 2 * inter, hidden // 16), dtype=torch.float8_e4m3fn, device='cuda')
+    l2_q = torch.empty((experts, hidden, inter // 2), dtype=torch.int8, device='cuda')
+    l2_sf = torch.empty((experts, hidden, inter // 16), dtype=torch.float8_e4m3fn, device='cuda')
+    l1_s = torch.empty(experts, dtype=torch.float32, device='cuda')
+    l2_s = torch.empty(experts, dtype=torch.float32, device='cuda')
+    for e in range(experts):
+        w = torch.randn(2 * inter, hidden, device='cuda', dtype=torch.bfloat16) * 0.02
+        l1_q[e], l1_sf[e], l1_s[e] = dg.per_token_cast_to_nvfp4(w)
+        w = torch.randn(hidden, inter, device='cuda', dtype=torch.bfloat16) * 0.02
+        l2_q[e], l2_sf[e], l2_s[e] = dg.per_token_cast_to_nvfp4(w)
+    l1, l2 = dg.transform_weights_for_mega_moe((l1_q, dg.pack_nvfp4_sf_mn_major(l1_sf), l1_s),
+                                               (l2_q, dg.pack_nvfp4_sf_mn_major(l2_sf), l2_s))
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, mma_type='nvfp4xnvfp4')
+    x_scale = torch.tensor(8.0 / (6 * 448), device='cuda')
+    act_scale = torch.tensor(64.0 / (6 * 448), device='cuda')
+    dg.per_token_cast_to_nvfp4_into(x, x_scale, buf.x, buf.x_sf)
+    dg.route_sigmoid_topk(logits, topk, buf.topk_idx, buf.topk_weights)
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
+    dg.nvfp4_mega_moe(y, l1, l2, buf, x_scale, act_scale, fast_math=False)
+    _status_ok()
+
+    want_idx, _ = omoe.route_sigmoid_topk(logits.cpu(), topk)
+    idx = buf.topk_idx.cpu()
+    assert torch.equal(idx, want_idx)
+    lay = buf.layout
+    dest = buf.buffer[lay['dest_row']:lay['dest_row'] + tokens * topk * 4].view(torch.int32).cpu()
+    want_dest, _, _, _ = omoe.dispatch_plan(idx, experts, SEGMENT)
+    assert torch.equal(dest, want_dest)
+    assert not torch.isnan(y.float()).any()
+
+    w = buf.topk_weights.cpu()
+    x_q_c = buf.x.cpu()
+    x_sf_c = buf.x_sf.cpu().view(torch.uint8).view(torch.float8_e4m3fn).view(tokens, hidden // 16)
+    xs, acs = x_scale.cpu(), act_scale.cpu()
+    for t in (0, 9001, 16383):
+        acc = torch.zeros(hidden)
+        for k in range(topk):
+            e = int(idx[t, k])
+            a1 = onv.dequantize_nvfp4(x_q_c[t:t + 1], x_sf_c[t:t + 1], xs) @ onv.dequantize_nvfp4(l1_q[e].cpu(), l1_sf[e].cpu(), l1_s[e].cpu()).T
+            a2_q, a2_sf = onv.swiglu_requant_nvfp4(a1, w[t:t + 1, k], None, acs)
+            a2 = onv.dequantize_nvfp4(a2_q, a2_sf, acs) @ onv.dequantize_nvfp4(l2_q[e].cpu(), l2_sf[e].cpu(), l2_s[e].cpu()).T
+            acc += a2.bfloat16().float()[0]
+        assert quant.calc_diff(y[t].cpu(), acc.bfloat16()) <= FP4_TOL
