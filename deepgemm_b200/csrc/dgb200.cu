@@ -426,56 +426,49 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     const int E = l.num_local_experts;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
     const bool nvfp4 = quant.kind == kKindNvfp4;
-    // Tokens on the UMMA N side pay off while an expert's rows fit one token tile (no second pass over its weights
-    // for a few rows beyond 128); with many rows per expert both orientations run 128-row tiles.
-    const bool swap = !nvfp4 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0 &&
-                      (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= kSwapMaxTok + 32));
+    // Which tile orientation serves which experts (measured on B200, hidden 7168, 256 experts):
+    //   few rows per expert (decode): everything through the swapped-operand kernel, whose MMA time follows the token
+    //     count (256 tokens: step 1.23 -> 1.12 ms); its fused SwiGLU epilogue is cheap while a tile holds few tokens;
+    //   around 128 rows per expert: split by group size, experts of 129..kSwapMaxTok rows through the swapped kernel
+    //     (one pass over their weights instead of two), all others through the tokens-on-M kernel. The swapped half of
+    //     the gate/up GEMM stores BF16 gate/up values into l1_tmp and dgb200_swiglu_requant_rows_kernel finishes those
+    //     rows (same bits as the fused epilogue): at this size the swapped kernel's own SwiGLU epilogue, a fully unrolled
+    //     walk over up to 80 tokens per thread, is instruction-fetch bound. The split costs four more launches, which
+    //     only pays where such experts are common;
+    //   otherwise the tokens-on-M kernel alone (with many rows per expert both orientations run 128-row tiles).
+    // dgb200_set_tuning("swap_ab", 0 / 1) forces the tokens-on-M kernel / the swapped kernel with its fused epilogue.
+    enum { kOrientM, kOrientSplit, kOrientSwapAll } orient = kOrientM;
+    if (!nvfp4 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
+        if (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= 40))
+            orient = kOrientSwapAll;
+        else if (tuning().swap_ab == -1 && expected_rows_per_expert >= 100 && expected_rows_per_expert <= kSwapMaxTok + 16)
+            orient = kOrientSplit;
+    }
     int rc = 0;
-    // Shared memory bandwidth bounds both kernels (every operand byte is written once by TMA and read by the MMAs):
-    // with tokens on M an expert costs its weights once per 128 rows, with tokens on N once per kSwapMaxTok rows but
-    // the token tile is read twice. So groups of 129..kSwapMaxTok rows go to the swapped kernel, all others to the
-    // tokens-on-M kernel (two launches per GEMM, each skipping the other's groups).
-    // Only the down GEMM is split by default: the swapped SwiGLU epilogue (one thread = one channel, a fully unrolled
-    // walk over up to 80 tokens) is instruction-fetch bound and costs the gate/up GEMM more than the saved passes.
-    // The gate/up GEMM's swapped half writes BF16 gate/up values into l1_tmp and a small kernel applies SwiGLU + FP8
-    // requant to those rows (same bits as the fused epilogue): the swapped kernel's own SwiGLU epilogue, a fully
-    // unrolled walk over up to 80 tokens per thread, is instruction-fetch bound (swap_ab = 1 forces it for testing).
     auto run_split = [&](GemmCall& c) -> int {
-        if (!swap) return run_gemm(c, stream);
+        if (orient == kOrientM) return run_gemm(c, stream);
+        if (orient == kOrientSwapAll) return run_gemm_swap(c, stream);
         GemmCall c2 = c;
-        if (c.epilogue == kEpiSwiGLU && tuning().swap_ab != 1) {
-            c.p.rows_lo = 129;
-            c.p.rows_hi = kSwapMaxTok;
-            c.p.rows_skip = 1;
-            c2.p.rows_lo = 129;
-            c2.p.rows_hi = kSwapMaxTok;
-            c2.p.rows_skip = 0;
+        c.p.rows_lo = c2.p.rows_lo = 129;
+        c.p.rows_hi = c2.p.rows_hi = kSwapMaxTok;
+        c.p.rows_skip = 1;
+        c2.p.rows_skip = 0;
+        const bool gate_up = c.epilogue == kEpiSwiGLU;
+        if (gate_up) {
             c2.epilogue = kEpiBF16;
             c2.p.d = base + l.l1_tmp;
             c2.p.d_row_stride = 2 * intermediate_hidden;
-            int rc1 = run_gemm(c, stream);
-            if (rc1 == 0) rc1 = run_gemm_swap(c2, stream);
-            if (rc1) return rc1;
-            const dim3 grid((kSwapMaxTok + 7) / 8, E);
-            dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, stream>>>(
-                reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
-                129, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
-                reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
-            DGB_CUDA(cudaGetLastError());
-            return 0;
         }
-        c.p.rows_lo = 129;
-        c.p.rows_hi = kSwapMaxTok;
-        c.p.rows_skip = 1;
-        c2.p.rows_lo = 129;
-        c2.p.rows_hi = kSwapMaxTok;
-        c2.p.rows_skip = 0;
-        if (tuning().swap_ab == 1) {  // everything through the swapped kernel
-            c2.p.rows_lo = c2.p.rows_hi = 0;
-            return run_gemm_swap(c2, stream);
-        }
-        const int rc1 = run_gemm(c, stream);
-        return rc1 ? rc1 : run_gemm_swap(c2, stream);
+        int rc1 = run_gemm(c, stream);
+        if (rc1 == 0) rc1 = run_gemm_swap(c2, stream);
+        if (rc1 || !gate_up) return rc1;
+        const dim3 grid((kSwapMaxTok + 7) / 8, E);
+        dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
+            129, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
+            reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
+        DGB_CUDA(cudaGetLastError());
+        return 0;
     };
     {
         GemmCall c{};
