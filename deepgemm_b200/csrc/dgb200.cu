@@ -441,7 +441,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     if (!nvfp4 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
         if (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= 40))
             orient = kOrientSwapAll;
-        else if (tuning().swap_ab == -1 && expected_rows_per_expert >= 100 && expected_rows_per_expert <= kSwapMaxTok + 16)
+        else if (tuning().swap_ab == 2 ||
+                 (tuning().swap_ab == -1 && expected_rows_per_expert >= 100 && expected_rows_per_expert <= kSwapMaxTok + 16))
             orient = kOrientSplit;
     }
     int rc = 0;
@@ -449,7 +450,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         if (orient == kOrientM) return run_gemm(c, stream);
         if (orient == kOrientSwapAll) return run_gemm_swap(c, stream);
         GemmCall c2 = c;
-        c.p.rows_lo = c2.p.rows_lo = 129;
+        const int split_lo = tuning().swap_ab == 2 ? 1 : 129;  // 2: every expert that fits one token tile (experiments)
+        c.p.rows_lo = c2.p.rows_lo = split_lo;
         c.p.rows_hi = c2.p.rows_hi = kSwapMaxTok;
         c.p.rows_skip = 1;
         c2.p.rows_skip = 0;
@@ -465,7 +467,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         const dim3 grid((kSwapMaxTok + 7) / 8, E);
         dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, stream>>>(
             reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
-            129, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
+            split_lo, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
             reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
         DGB_CUDA(cudaGetLastError());
         return 0;
@@ -863,7 +865,7 @@ int dgb200_set_num_sms(int num_sms) {
 int dgb200_set_tuning(const char* name, int32_t value) {
     DGB_REQUIRE(name != nullptr, "null name");
     if (std::strcmp(name, "swap_ab") == 0) {
-        DGB_REQUIRE(value >= -1 && value <= 1, "swap_ab must be -1 (automatic), 0 or 1");
+        DGB_REQUIRE(value >= -1 && value <= 2, "swap_ab must be -1 (automatic), 0, 1 or 2");
         tuning().swap_ab = value;
     } else if (std::strcmp(name, "prefetch_distance") == 0) {
         DGB_REQUIRE(value >= 0 && value <= 4096, "prefetch_distance must be in [0, 4096]");

@@ -40,9 +40,11 @@ int dgb200_get_num_sms(void);
 /* Process-wide tuning knobs of the GEMM kernels. Plays the role of the reference's heuristics overrides
  * (csrc/apis/runtime.hpp:21-41).
  *   "block_n"            0 = automatic, 128 or 256: width of an output tile of the tokens-on-M kernel.
- *   "swap_ab"            layer GEMMs: -1 = split the experts by size between the two tile orientations when the
- *                        expected rows per expert are small (default), 0 = tokens-on-M kernel only, 1 = everything
- *                        through the swapped-operand kernel including its fused SwiGLU epilogue (testing).
+ *   "swap_ab"            layer GEMMs: -1 = choose the tile orientation from the expected rows per expert (default:
+ *                        swapped-operand kernel alone for decode-sized batches, experts split by size around 128
+ *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
+ *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
+ *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
  *   "prefetch_distance"  K blocks an L2 prefetch cursor runs ahead of the weight loads (0 = off, the default).
  *   "debug_skip"         timing experiments, only honoured by builds with -DDGB200_INSTRUMENT. */
 int dgb200_set_tuning(const char* name, int32_t value);
