@@ -295,6 +295,7 @@ struct MegaLayout {
     long long src_of_row, row_weight;
     long long all_counts, my_base, flags;  // expert-parallel exchange: counts of every rank, this rank's bases, barrier flags
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
+    long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
     long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
@@ -369,6 +370,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l2_sf = take(l.max_rows * sf_ints_per_row(kind, inter) * 4);
     l.l2_out = take(l.max_rows * hidden * 2);
     l.l1_tmp = kind == kKindFp8Fp4 ? take(l.max_rows * inter * 4) : 0;
+    l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
         DGB_REQUIRE(kind == kKindFp8Fp4 && shared_inter % 128 == 0, "shared experts need the FP8 x FP4 layer and a multiple of 128 channels");
@@ -625,7 +627,7 @@ int run_shared_x_sf(const MegaLayout& l, uint8_t* base, int num_tokens, int hidd
     const int ints = hidden / 128;
     dgb200_sf_rows_to_cp_order_kernel<<<(num_tokens + 31) / 32, 256, ints * 33 * sizeof(unsigned), stream>>>(
         reinterpret_cast<const unsigned*>(base + l.x_sf), num_tokens, ints, reinterpret_cast<unsigned*>(base + l.shared_x_sf),
-        l.token_rows);
+        l.token_rows, nullptr);
     DGB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -653,6 +655,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     const int chunks = std::max(1, (entries + kPlanChunk - 1) / kPlanChunk);
     const int entries_per_rank = num_max_tokens_per_rank * num_topk;
     const bool with_shared = quant.shared_inter > 0;
+    const int sf_per_row = sf_ints_per_row(quant.kind, hidden);
     int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
     const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
@@ -678,19 +681,24 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         if (quant.x_bf16 != nullptr)
             dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
                 quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden,
-                l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 1,
-                with_shared ? base + l.x : nullptr, with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr,
-                l.token_rows);
+                l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf_stage, -static_cast<long long>(sf_per_row),
+                l.row_weight, l.src_of_row, 1, with_shared ? base + l.x : nullptr,
+                with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr, l.token_rows);
         else
             dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
                 base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
-                static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_ints_per_row(quant.kind, hidden), l.num_local_experts, rank,
-                entries_per_rank, peers, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row);
+                static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, l.num_local_experts, rank,
+                entries_per_rank, peers, l.l1_acts, l.l1_sf_stage, 0, l.row_weight, l.src_of_row);
     } else if ((rc = record_stage(1, stream))) {
         return rc;
     }
     DGB_CUDA(cudaGetLastError());
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
+    // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
+    dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
+        reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
+        reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows));
+    DGB_CUDA(cudaGetLastError());
     if ((rc = record_stage(2, stream))) return rc;
 
     rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3,

@@ -426,9 +426,18 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
     const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes);
     uint4* to = reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * row_bytes);
     for (int c = lane; c < row_bytes / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
+    // sf_k_stride > 0: straight into the GEMM's layout (one 4-byte store per scale int, each in another cache line);
+    // sf_k_stride <= 0: the row's scale ints contiguously into a row-major staging area of the owner, which brings them
+    // into GEMM order itself after the barrier. Scattered 4-byte stores are what NVLink handles worst: they cost 40 % of
+    // the push at 2 GPUs.
     unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
-    for (int c = lane; c < sf_per_row; c += 32)
-        sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(dest)] = x_sf[static_cast<long long>(token) * sf_per_row + c];
+    for (int c = lane; c < sf_per_row; c += 32) {
+        const unsigned v = x_sf[static_cast<long long>(token) * sf_per_row + c];
+        if (sf_k_stride > 0)
+            sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(dest)] = v;
+        else
+            sf[static_cast<long long>(dest) * sf_per_row + c] = v;
+    }
     if (lane == 0) {
         reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
         reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;
@@ -513,9 +522,13 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
             if (d < 0 || !valid) continue;
             st_global_v4(reinterpret_cast<unsigned char*>(base + acts_offset) + static_cast<long long>(d) * hidden + col, o[0], o[1],
                          o[2], o[3]);
-            if ((lane & 7) == 0)
-                reinterpret_cast<unsigned*>(base + sf_offset)[static_cast<long long>(col >> 7) * sf_k_stride + sf_row_in_cp_order(d)] =
-                    sf_int;
+            if ((lane & 7) == 0) {
+                unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
+                if (sf_k_stride > 0)
+                    sf[static_cast<long long>(col >> 7) * sf_k_stride + sf_row_in_cp_order(d)] = sf_int;
+                else  // row-major staging (see dgb200_ep_push_kernel): -sf_k_stride ints per row
+                    sf[static_cast<long long>(d) * (-sf_k_stride) + (col >> 7)] = sf_int;
+            }
         }
     }
 }
@@ -525,9 +538,11 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
 // (shared experts). 32 tokens per CTA through a padded shared-memory tile.
 __global__ void __launch_bounds__(256)
 dgb200_sf_rows_to_cp_order_kernel(const unsigned* __restrict__ sf, int tokens, int ints_per_row, unsigned* __restrict__ out,
-                                  long long k_stride) {
+                                  long long k_stride, const int* __restrict__ rows_limit) {
     extern __shared__ unsigned sf_tile[];  // [ints_per_row][33]
+    if (rows_limit != nullptr) tokens = min(tokens, rows_limit[0]);  // row count only known on the device
     const int t0 = blockIdx.x * 32;
+    if (t0 >= tokens) return;
     for (int i = threadIdx.x; i < 32 * ints_per_row; i += 256) {
         const int r = i / ints_per_row, c = i - r * ints_per_row;
         if (t0 + r < tokens) sf_tile[c * 33 + r] = sf[static_cast<long long>(t0 + r) * ints_per_row + c];

@@ -70,6 +70,15 @@ def _worker(rank, world, port, results):
         dg.fp8_fp4_mega_moe_bf16_input(y, c['x'].cuda(), l1, l2, buf, cumulative_local_expert_recv_stats=None)
         assert _lib.device_status()[0] == 0
         ys.append(y.cpu())
+        # the same layer with both GEMMs through the swapped-operand kernel (tokens on UMMA N)
+        _lib.check(_lib.lib().dgb200_set_tuning(b'swap_ab', 1))
+        try:
+            y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+            dg.fp8_fp4_mega_moe_bf16_input(y, c['x'].cuda(), l1, l2, buf)
+            assert _lib.device_status()[0] == 0
+        finally:
+            _lib.check(_lib.lib().dgb200_set_tuning(b'swap_ab', -1))
+        y_swapped = y.cpu()
         # fourth call: shared experts (rank-local FP8 x FP8 MLP) as an extra combine slot
         s1_q, s1_sf, s2_q, s2_sf = _shared_weights()
         sl1, sl2 = dg.transform_weights_for_mega_moe(
@@ -83,7 +92,7 @@ def _worker(rank, world, port, results):
         end = buf.buffer[lay['expert_end']:lay['expert_end'] + per_rank * 4].view(torch.int32).cpu()
         start = buf.buffer[lay['expert_start']:lay['expert_start'] + per_rank * 4].view(torch.int32).cpu()
         dest = buf.buffer[lay['dest_row']:lay['dest_row'] + t * TOPK * 4].view(torch.int32).cpu()
-        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], y_shared=ys[3], start=start, end=end, dest=dest, stats=stats.cpu())
+        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], y_shared=ys[3], y_swapped=y_swapped, start=start, end=end, dest=dest, stats=stats.cpu())
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -105,6 +114,7 @@ def test_two_rank_layer_matches_oracle():
         want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
         assert torch.equal(got['y0'], got['y1']), 'two calls on the same buffer must give the same bits'
         assert torch.equal(got['y0'], got['y_fused']), 'the fused prologue must give the same bits'
+        assert quant.calc_diff(got['y_swapped'], got['y0']) <= 1e-5, 'tile orientation must not change the result'
         assert not torch.isnan(got['y0'].float()).any()
         assert quant.calc_diff(got['y0'], want) <= 2e-3
         my_base, want_start, want_end = omoe.ep_plan(all_counts, rank, 128)
