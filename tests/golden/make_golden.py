@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the reference's own torch helpers.
 
-Run once in a container that mounts the reference tree (``python tests/golden/make_golden.py [path-to-reference]``,
-default ``/root/reference``). The reference's ``deep_gemm/utils/math.py`` and ``deep_gemm/testing/numeric.py`` are
+Run once where the reference tree is available: ``python tests/golden/make_golden.py <path-to-the-DeepGEMM-tree>``
+(or set ``DEEPGEMM_REFERENCE_ROOT``). The reference's ``deep_gemm/utils/math.py`` and ``deep_gemm/testing/numeric.py`` are
 pure torch and are imported BY FILE PATH (``import deep_gemm`` itself needs the compiled ``_C`` module); the
 functions run on seeded CPU inputs and their inputs/outputs are stored as small fixtures. The fixtures, not the
 reference tree, travel with this repository: tests only read the ``.npz`` files.
@@ -34,7 +34,9 @@ def u8(t):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get('DEEPGEMM_REFERENCE_ROOT')
+    if not ref_root:
+        raise SystemExit('usage: make_golden.py <path-to-the-DeepGEMM-tree>')
     rmath = load_by_path('ref_math', os.path.join(ref_root, 'deep_gemm/utils/math.py'))
     rnum = load_by_path('ref_numeric', os.path.join(ref_root, 'deep_gemm/testing/numeric.py'))
 
