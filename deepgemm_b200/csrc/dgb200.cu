@@ -199,6 +199,35 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 }
 
 
+// A side stream per device with the two events of a fork / join. The two halves of a GEMM that is split by group size
+// touch disjoint experts: the swapped half is launched on the side stream, so its CTAs take over SMs one by one as
+// the other half's CTAs retire instead of waiting for its last tile (both are persistent kernels of one CTA per SM).
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    std::mutex mu;  // one fork .. join sequence at a time per device (the events are shared)
+};
+
+int side_stream_for_current_device(SideStream** out) {
+    constexpr int kMaxDevices = 64;
+    static SideStream table[kMaxDevices];
+    static std::mutex create_mu;
+    int dev = 0;
+    DGB_CUDA(cudaGetDevice(&dev));
+    DGB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+    SideStream& s = table[dev];
+    {
+        std::lock_guard<std::mutex> lock(create_mu);
+        if (s.stream == nullptr) {
+            DGB_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+            DGB_CUDA(cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming));
+            DGB_CUDA(cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming));
+        }
+    }
+    *out = &s;
+    return 0;
+}
+
 // The layer GEMMs with swapped operands (gemm_swap_kernel.cuh): weights on M, an expert's tokens on N. Takes the same
 // call description as run_gemm; only the FP8 x FP4 / FP8 x FP8 kind, the psum layout with 128-row segments, scale
 // factors in tcgen05.cp order and the SwiGLU / BF16 epilogues.
@@ -463,16 +492,26 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
             c2.p.d = base + l.l1_tmp;
             c2.p.d_row_stride = 2 * intermediate_hidden;
         }
-        int rc1 = run_gemm(c, stream);
-        if (rc1 == 0) rc1 = run_gemm_swap(c2, stream);
-        if (rc1 || !gate_up) return rc1;
-        const dim3 grid((kSwapMaxTok + 7) / 8, E);
-        dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, stream>>>(
-            reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
-            split_lo, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
-            reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
-        DGB_CUDA(cudaGetLastError());
-        return 0;
+        SideStream* side = nullptr;
+        int rc1 = side_stream_for_current_device(&side);
+        if (rc1) return rc1;
+        std::lock_guard<std::mutex> lock(side->mu);
+        DGB_CUDA(cudaEventRecord(side->fork, stream));
+        DGB_CUDA(cudaStreamWaitEvent(side->stream, side->fork, 0));
+        rc1 = run_gemm(c, stream);
+        if (rc1 == 0) rc1 = run_gemm_swap(c2, side->stream);
+        if (rc1 == 0 && gate_up) {
+            const dim3 grid((kSwapMaxTok + 7) / 8, E);
+            dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, side->stream>>>(
+                reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
+                split_lo, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
+                reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
+            if (cudaGetLastError() != cudaSuccess) rc1 = fail(DGB200_ECUDA, "launch of the SwiGLU finisher failed");
+        }
+        // join even after a failed launch, so that the side stream never runs ahead of the caller's stream
+        DGB_CUDA(cudaEventRecord(side->join, side->stream));
+        DGB_CUDA(cudaStreamWaitEvent(stream, side->join, 0));
+        return rc1;
     };
     {
         GemmCall c{};
