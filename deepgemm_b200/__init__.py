@@ -5,6 +5,13 @@ path it covers; use ``import deepgemm_b200 as deep_gemm``. Every operator calls 
 (include/dgb200.h); there is no CPU or PyTorch fallback.
 """
 from . import _lib, testing, utils  # noqa: F401
+from .bf16 import (  # noqa: F401
+    bf16_gemm_nn,
+    bf16_gemm_nt,
+    m_grouped_bf16_gemm_nn_contiguous,
+    m_grouped_bf16_gemm_nt_contiguous,
+    m_grouped_bf16_gemm_nt_masked,
+)
 from .gemm import (  # noqa: F401
     fp8_fp4_gemm_nn,
     fp8_fp4_gemm_nt,
@@ -24,6 +31,7 @@ from .layout import (  # noqa: F401
 )
 from .mega import (  # noqa: F401
     SymmBuffer,
+    bf16_mega_moe,
     fp8_fp4_mega_moe,
     fp8_fp4_mega_moe_bf16_input,
     get_block_m_for_mega_moe,

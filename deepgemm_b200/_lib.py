@@ -39,6 +39,10 @@ _SIGNATURES = {
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_route_sigmoid_topk': [_ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr],
     'dgb200_get_token_alignment_for_mega_moe': [],
+    'dgb200_m_grouped_bf16_gemm_nt_contiguous': [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32, _i32,
+                                                 _i32, _i32, _ptr],
+    'dgb200_m_grouped_bf16_gemm_nt_masked': [_ptr, _ptr, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_bf16_gemm_nt': [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_fp8_fp4_gemm_nt': [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_segment_alignment_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
@@ -51,6 +55,9 @@ _SIGNATURES = {
     'dgb200_nvfp4_mega_moe': [
         _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
+    'dgb200_get_symm_buffer_layout_for_bf16_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_bf16_mega_moe': [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                             ctypes.c_float, _i32, _ptr],
     'dgb200_moe_dispatch_plan_noalloc': [_ptr, _i32, _i32, _i32, _i32, _ptr, _ptr, _ptr, _ptr],
     'dgb200_set_mega_moe_stage_events': [_ptr, _i32],
     'dgb200_fp8_fp4_mega_moe': [

@@ -50,6 +50,7 @@ struct GemmCall {
     int whole_tile_stores;  // the rows between a group's end and its 128-row tile end are private padding: the
                             // epilogue may write all 128 rows of every tile
     long long a_rows_total;  // rows of the flattened A
+    long long a_row_stride_bytes, b_row_stride_bytes;  // BF16 kind only: row pitches of A and B
     GemmParams p;
     int b_is_fp4;
     int epilogue;
@@ -74,8 +75,22 @@ Tuning& tuning() {
 int run_gemm(GemmCall& c, cudaStream_t stream) {
     GemmParams& p = c.p;
     const bool nvfp4 = c.kind == kKindNvfp4;
-    DGB_REQUIRE(p.k > 0 && p.k % (nvfp4 ? 256 : 128) == 0, "k (%d) must be a positive multiple of %d", p.k, nvfp4 ? 256 : 128);
-    if (nvfp4) p.gran_a = p.gran_b = 32;  // unused by this kind; keeps the checks below uniform
+    const bool bf16 = c.kind == kKindBf16;
+    const int k_block = nvfp4 ? 256 : (bf16 ? 64 : 128);
+    DGB_REQUIRE(p.k > 0 && p.k % k_block == 0, "k (%d) must be a positive multiple of %d", p.k, k_block);
+    if (nvfp4 || bf16) p.gran_a = p.gran_b = 32;  // unused by these kinds; keeps the checks below uniform
+    if (bf16) {
+        // no scale factors: the kernel never loads them; the fields below only have to pass the shared checks
+        c.sfa = c.a;
+        c.sfb = c.b;
+        c.sfa_k_stride = (std::max<long long>(c.a_rows_total, 1) + 3) / 4 * 4;
+        c.sfb_k_stride = p.n;
+        c.sfa_group_stride = static_cast<long long>((p.k / 32 + 3) / 4) * c.sfa_k_stride;
+        c.sfb_group_stride = static_cast<long long>((p.k / 32 + 3) / 4) * c.sfb_k_stride;
+        p.sf_transposed = 1;
+        DGB_REQUIRE(c.epilogue == kEpiBF16 || c.epilogue == kEpiF32 || c.epilogue == kEpiSwiGLUBf16,
+                    "unknown epilogue %d for the BF16 kind", c.epilogue);
+    }
     DGB_REQUIRE(p.n > 0 && p.n % 128 == 0, "n (%d) must be a positive multiple of 128", p.n);
     DGB_REQUIRE(p.gran_a == 32 || p.gran_a == 128, "gran_k_a must be 32 or 128, got %d", p.gran_a);
     DGB_REQUIRE(p.gran_b == 32 || p.gran_b == 128, "gran_k_b must be 32 or 128, got %d", p.gran_b);
@@ -101,28 +116,42 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     if (c.a_rows_total == 0) return 0;
 
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
-    int rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
+    int rc = 0;
+    if (!bf16)
+    rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
                                 static_cast<uint64_t>(packed_k_a) * c.num_groups_a,
                                 static_cast<uint64_t>(c.sfa_k_stride) * 4, 128, sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     // Wide N tiles give each tcgen05.mma enough work (128 x 256 x 32) to cover the per-K-block issue chain.
-    const bool swiglu = c.epilogue == kEpiSwiGLU || c.epilogue == kEpiSwiGLUNvfp4;
+    const bool swiglu = c.epilogue == kEpiSwiGLU || c.epilogue == kEpiSwiGLUNvfp4 || c.epilogue == kEpiSwiGLUBf16;
     // the SwiGLU epilogues pair the two 128-channel halves of a 256-wide tile (gate | up)
     DGB_REQUIRE(!swiglu || p.n % 256 == 0, "the gate/up GEMM needs n (%d) to be a multiple of 256", p.n);
     const int block_n = swiglu ? 256 : (tuning().block_n != 0 ? tuning().block_n : (p.n % 256 == 0 ? 256 : 128));
     DGB_REQUIRE((block_n == 128 || block_n == 256) && p.n % block_n == 0, "block_n %d does not divide n %d", block_n, p.n);
+    if (!bf16)
     rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
                             static_cast<uint64_t>(packed_k_b) * p.num_groups, static_cast<uint64_t>(c.sfb_k_stride) * 4,
                             static_cast<uint32_t>(block_n), sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     const uint64_t a_row_bytes = nvfp4 ? p.k / 2 : p.k;  // packed E2M1 or E4M3
+    if (bf16)
+        rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c.a, static_cast<uint64_t>(p.k),
+                                static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(c.a_row_stride_bytes), 64, 128,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    else
     rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, a_row_bytes,
                                 static_cast<uint64_t>(c.a_rows_total), a_row_bytes, 128, 128,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    if (bf16) tm_sfa = tm_sfb = tm_a;  // valid maps for the kernel's descriptor prefetch; never used for a copy
     const uint64_t b_rows = static_cast<uint64_t>(p.num_groups) * p.n;
     const uint32_t BLOCK_N = static_cast<uint32_t>(block_n);
-    if (nvfp4) {
+    if (bf16) {
+        rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c.b, static_cast<uint64_t>(p.k), b_rows,
+                                static_cast<uint64_t>(c.b_row_stride_bytes), 64, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = 0;
+        p.b_tx_bytes = BLOCK_N * 128;
+    } else if (nvfp4) {
         // both operands stay packed in shared memory (two E2M1 per byte): plain byte tensors
         rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, static_cast<uint64_t>(p.k / 2), b_rows,
                                 static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -149,7 +178,8 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     // NVFP4: only the BF16 epilogue (the down GEMM: few K blocks per tile, so its store burst weighs most) trades a
     // pipeline stage for the staging buffers.
     const bool nvfp4_staged = nvfp4 && block_n == 256 && c.epilogue == kEpiBF16;
-    if (block_n == 256 && ((!nvfp4 && (c.epilogue == kEpiBF16 || c.epilogue == kEpiSwiGLU)) || nvfp4_staged)) {
+    if (block_n == 256 && ((!nvfp4 && (c.epilogue == kEpiBF16 || c.epilogue == kEpiSwiGLU)) || nvfp4_staged) &&
+        (static_cast<long long>(p.d_row_stride) * 2) % 16 == 0) {
         if (c.epilogue == kEpiBF16)
             rc = make_tensor_map_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.d, static_cast<uint64_t>(p.n),
                                     static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.d_row_stride) * 2, 32, 32,
@@ -164,7 +194,7 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 
     p.prefetch_distance = tuning().prefetch_distance;
     p.b_ptr = static_cast<const unsigned char*>(c.b);
-    p.b_row_bytes = (nvfp4 || c.b_is_fp4) ? p.k / 2 : p.k;
+    p.b_row_bytes = bf16 ? static_cast<int>(c.b_row_stride_bytes) : (nvfp4 || c.b_is_fp4) ? p.k / 2 : p.k;
     p.b_kb_bytes = (c.b_is_fp4 && !nvfp4) ? 64 : 128;
     p.debug_skip = tuning().debug_skip;
     p.trace = tuning().trace;
@@ -180,6 +210,13 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 #define DGB_LAUNCH(EPI, KIND)                                                                                   \
     return block_n == 256 ? launch_gemm<256, 4, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream)            \
                           : launch_gemm<128, 6, EPI, KIND>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream)
+    if (bf16) {
+        switch (c.epilogue) {
+            case kEpiBF16: DGB_LAUNCH(kEpiBF16, kKindBf16);
+            case kEpiSwiGLUBf16: return launch_gemm<256, 4, kEpiSwiGLUBf16, kKindBf16>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
+            default: DGB_LAUNCH(kEpiF32, kKindBf16);
+        }
+    }
     if (nvfp4) {
         if (nvfp4_staged) return launch_gemm<256, 3, kEpiBF16, kKindNvfp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
         switch (c.epilogue) {
@@ -356,8 +393,8 @@ struct LayerQuant {
 };
 
 // Bytes of one quantised activation row of `width` elements, and packed scale ints (4 scale bytes each) per row.
-inline long long act_row_bytes(int kind, int width) { return kind == kKindNvfp4 ? width / 2 : width; }
-inline int sf_ints_per_row(int kind, int width) { return kind == kKindNvfp4 ? width / 64 : width / 128; }
+inline long long act_row_bytes(int kind, int width) { return kind == kKindNvfp4 ? width / 2 : (kind == kKindBf16 ? width * 2 : width); }
+inline int sf_ints_per_row(int kind, int width) { return kind == kKindNvfp4 ? width / 64 : (kind == kKindBf16 ? 0 : width / 128); }
 
 int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, int topk, int hidden, int inter, MegaLayout* out,
                      int shared_inter = 0) {
@@ -457,6 +494,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     const int E = l.num_local_experts;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
     const bool nvfp4 = quant.kind == kKindNvfp4;
+    const bool bf16 = quant.kind == kKindBf16;
     // Which tile orientation serves which experts (measured on B200, hidden 7168, 256 experts):
     //   few rows per expert (decode): everything through the swapped-operand kernel, whose MMA time follows the token
     //     count (256 tokens: step 1.23 -> 1.12 ms); its fused SwiGLU epilogue is cheap while a tile holds few tokens;
@@ -469,7 +507,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     //   otherwise the tokens-on-M kernel alone (with many rows per expert both orientations run 128-row tiles).
     // dgb200_set_tuning("swap_ab", 0 / 1) forces the tokens-on-M kernel / the swapped kernel with its fused epilogue.
     enum { kOrientM, kOrientSplit, kOrientSwapAll } orient = kOrientM;
-    if (!nvfp4 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
+    if (!nvfp4 && !bf16 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
         if (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= 40))
             orient = kOrientSwapAll;
         else if (tuning().swap_ab == 2 ||
@@ -520,7 +558,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         c.b = l1_w;
         c.a_rows_total = l.max_rows;
         c.b_is_fp4 = 1;
-        c.epilogue = nvfp4 ? kEpiSwiGLUNvfp4 : kEpiSwiGLU;
+        c.epilogue = nvfp4 ? kEpiSwiGLUNvfp4 : (bf16 ? kEpiSwiGLUBf16 : kEpiSwiGLU);
+        c.a_row_stride_bytes = c.b_row_stride_bytes = hidden * 2ll;  // BF16 kind
         c.whole_tile_stores = 1;
         c.max_tiles = 0;
         c.sfa = base + l.l1_sf;
@@ -563,6 +602,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         c.a_rows_total = l.max_rows;
         c.b_is_fp4 = 1;
         c.epilogue = kEpiBF16;
+        c.a_row_stride_bytes = c.b_row_stride_bytes = intermediate_hidden * 2ll;  // BF16 kind
         c.whole_tile_stores = 1;
         c.max_tiles = 0;
         c.sfa = base + l.l2_sf;
@@ -734,6 +774,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     DGB_CUDA(cudaGetLastError());
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
     // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
+    if (sf_per_row > 0)
     dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
         reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
         reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows));
@@ -776,7 +817,8 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
                 "rank / peer pointer table do not describe this buffer");
     DGB_REQUIRE(num_tokens >= 0 && num_tokens <= num_max_tokens_per_rank, "num_tokens (%d) exceeds the buffer capacity (%d)",
                 num_tokens, num_max_tokens_per_rank);
-    DGB_REQUIRE(y != nullptr && l1_w != nullptr && l1_w_sf != nullptr && l2_w != nullptr && l2_w_sf != nullptr && buffer != nullptr,
+    DGB_REQUIRE(y != nullptr && l1_w != nullptr && l2_w != nullptr && buffer != nullptr &&
+                    (quant.kind == kKindBf16 || (l1_w_sf != nullptr && l2_w_sf != nullptr)),
                 "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(buffer) % 256 == 0, "buffer must be 256-byte aligned");
     DGB_REQUIRE((2 * intermediate_hidden) % 128 == 0 && intermediate_hidden % 64 == 0, "intermediate_hidden must be a multiple of 64");
@@ -1080,6 +1122,76 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
     return run_gemm(c, static_cast<cudaStream_t>(stream));
 }
 
+namespace {
+// Shared body of the BF16 GEMM entry points: A [rows, k] and B [num_groups * n, k] BF16 K-major, D BF16 or FP32.
+int run_bf16_gemm(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
+                  int32_t d_is_fp32, const int32_t* layout, int mode, long long a_rows_total, int32_t m, int32_t n, int32_t k,
+                  int32_t num_groups, int32_t alignment, int32_t store_padding, int max_tiles, void* stream) {
+    DGB_REQUIRE(d != nullptr || a_rows_total == 0, "null output");
+    DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
+                "d row stride must cover n and keep rows 16-byte aligned");
+    DGB_REQUIRE(a_row_stride >= k && a_row_stride % 8 == 0 && b_row_stride >= k && b_row_stride % 8 == 0,
+                "a and b row strides must cover k and keep rows 16-byte aligned");
+    GemmCall c{};
+    c.kind = kKindBf16;
+    c.a = a;
+    c.b = b;
+    c.a_rows_total = a_rows_total;
+    c.a_row_stride_bytes = a_row_stride * 2;
+    c.b_row_stride_bytes = b_row_stride * 2;
+    c.num_groups_a = 1;
+    c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
+    GemmParams& p = c.p;
+    p.d = d;
+    p.d_row_stride = d_row_stride;
+    p.layout = layout;
+    p.mode = mode;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.num_groups = num_groups;
+    p.alignment = alignment;
+    p.store_padding = store_padding;
+    c.max_tiles = max_tiles;
+    return run_gemm(c, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d,
+                                             int64_t d_row_stride, const int32_t* grouped_layout, int32_t m, int32_t n,
+                                             int32_t k, int32_t num_groups, int32_t d_is_fp32, int32_t layout_kind,
+                                             int32_t alignment, int32_t store_padding, void* stream) {
+    DGB_REQUIRE(m >= 0, "m must be >= 0");
+    DGB_REQUIRE(layout_kind == DGB200_LAYOUT_ROW_IDS || layout_kind == DGB200_LAYOUT_PSUM, "unknown layout kind %d",
+                layout_kind);
+    DGB_REQUIRE(alignment > 0 && alignment % 4 == 0, "alignment (%d) must be a positive multiple of 4", alignment);
+    DGB_REQUIRE(layout_kind == DGB200_LAYOUT_PSUM || alignment % 128 == 0,
+                "the row-id layout needs an M alignment that is a multiple of 128, got %d", alignment);
+    const int mode = layout_kind == DGB200_LAYOUT_PSUM ? kModePsum : kModeRowIds;
+    const long long m_blocks = (static_cast<long long>(m) + 127) / 128 + (mode == kModePsum ? num_groups : 0);
+    const int max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
+    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, d, d_row_stride, d_is_fp32, grouped_layout, mode, m, m, n, k,
+                         num_groups, alignment, store_padding, max_tiles, stream);
+}
+
+int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, int64_t d_row_stride, const int32_t* masked_m,
+                                         int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
+                                         int32_t d_is_fp32, void* stream) {
+    (void)expected_m;
+    DGB_REQUIRE(max_m > 0 && max_m % 4 == 0, "max_m (%d) must be a positive multiple of 4", max_m);
+    return run_bf16_gemm(a, k, b, k, d, d_row_stride, d_is_fp32, masked_m, kModeMasked,
+                         static_cast<long long>(num_groups) * max_m, max_m, n, k, num_groups, 4, 0, 0, stream);
+}
+
+int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
+                        int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, void* stream) {
+    DGB_REQUIRE(m >= 0, "m must be >= 0");
+    const long long m_blocks = (static_cast<long long>(m) + 127) / 128;
+    const int max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
+    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, d, d_row_stride, d_is_fp32, nullptr, kModeDense, m, m, n, k, 1, 128,
+                         0, max_tiles, stream);
+}
+
 int dgb200_per_token_cast_to_fp8(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, int32_t gran_k, void* q,
                                  int64_t q_row_stride, float* sf_f32, void* sf_packed, int64_t sf_k_stride,
                                  int64_t sf_row_stride, void* stream) {
@@ -1261,6 +1373,23 @@ int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const 
     quant.l1_scales = l1_w_scales;
     quant.l2_scales = l2_w_scales;
     return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
+                        num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
+                        activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                                    int32_t num_topk, int32_t hidden, int32_t intermediate_hidden, int64_t* out) {
+    return export_mega_layout(kKindBf16, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                              intermediate_hidden, out);
+}
+
+int dgb200_bf16_mega_moe(void* y, const void* l1_w, const void* l2_w, int32_t* cumulative_local_expert_recv_stats, void* buffer,
+                         const uint64_t* peer_buffer_ptrs, int32_t rank, int32_t num_ranks, int32_t num_tokens,
+                         int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
+                         int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream) {
+    LayerQuant quant;
+    quant.kind = kKindBf16;
+    return run_mega_moe(quant, y, l1_w, nullptr, l2_w, nullptr, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
                         num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
                         activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
 }

@@ -41,11 +41,14 @@ enum EpilogueKind : int {
     kEpiF32 = 1,     // D fp32 (raw accumulators; bring-up and tests)
     kEpiSwiGLU = 2,  // gate/up -> silu(gate)*up*row_weight -> per-32 UE8M0 FP8 requant
     kEpiSwiGLUNvfp4 = 3,  // gate/up -> silu(gate)*up*row_weight -> NVFP4 (per-16 UE4M3 scales, given per-tensor scale)
+    kEpiSwiGLUBf16 = 4,   // gate/up -> silu(gate)*up*row_weight -> BF16 rows (the BF16 layer)
 };
 
 enum MmaKind : int {
     kKindFp8Fp4 = 0,  // kind::mxf8f6f4: E4M3 activations x E2M1 (unpacked in smem) or E4M3 weights, UE8M0 scales, K block 128
     kKindNvfp4 = 1,   // kind::mxf4nvf4 scale_vec::4X: packed E2M1 x packed E2M1, UE4M3 scale per 16, K block 256
+    kKindBf16 = 2,    // kind::f16: BF16 x BF16, no scale factors, K block 64 (the scale-factor loads, copies and
+                      // TMEM columns of the other kinds stay unused)
 };
 
 constexpr int kMaxRanks = 8;
@@ -220,7 +223,7 @@ struct GemmSmem {
     static constexpr int kOffGroups = kOffMisc + 16;
     // Epilogue staging for TMA stores: 32 rows x 64 bytes per epilogue warp, in the 64-byte swizzle (512-byte atoms).
     // The NVFP4 kind only has room for it next to its larger scale-factor stages with 3 pipeline stages.
-    static constexpr int kStageBytesPerWarp = (BLOCK_N == 256 && (kKind == kKindFp8Fp4 || kStages <= 3)) ? 2048 : 0;
+    static constexpr int kStageBytesPerWarp = (BLOCK_N == 256 && (kKind != kKindNvfp4 || kStages <= 3)) ? 2048 : 0;
     static constexpr int kOffStage = (kOffGroups + 3 * kMaxCachedGroups * 4 + 511) / 512 * 512;
     static constexpr int kTotal = kOffStage + 8 * kStageBytesPerWarp;
     static constexpr int kDynamicBytes = kTotal + 1024;  // slack to align the base to 1024 B
@@ -265,7 +268,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     constexpr int kSfInts = L::kSfIntsPerRow;          // scale ints per row per K block = tcgen05.cp blocks per 128 rows
     constexpr int kSfBlocksA = kSfInts;                // 512-byte blocks of A scales per stage
     constexpr int kSfBlocksB = kSfInts * BLOCK_N / 128;
-    constexpr int kBlockK = kKind == kKindNvfp4 ? 256 : 128;  // K elements per stage (128 bytes per row either way)
+    constexpr int kBlockK = kKind == kKindNvfp4 ? 256 : (kKind == kKindBf16 ? 64 : 128);  // K elements per stage (128 bytes per row either way)
+    constexpr int kTmaXPerKb = kKind == kKindBf16 ? 64 : 128;  // tensor-map elements along K per stage (bytes, 4-bit or 16-bit elements)
+    constexpr bool kScaled = kKind != kKindBf16;
     constexpr uint32_t kAccumCols = BLOCK_N;
     constexpr uint32_t kNumAccum = BLOCK_N == 128 ? 2 : 1;
     // Scale factors get their own TMEM columns per pipeline stage: with a single region every tcgen05.cp would have
@@ -380,12 +385,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfa = kb % a_per == 0 && !DGB_SKIP(p, 4);
+                    const bool load_sfa = kScaled && kb % a_per == 0 && !DGB_SKIP(p, 4);
                     if (elect_one()) {
                         trace_point(p, 0, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) + (load_sfa ? L::kSfaBytes : 0));
                         if (!DGB_SKIP(p, 1))
-                            tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * 128,
+                            tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * kTmaXPerKb,
                                         t.row_start);
                         if (load_sfa)
                             tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage,
@@ -417,12 +422,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfb = kb % b_per == 0 && !DGB_SKIP(p, 4);
+                    const bool load_sfb = kScaled && kb % b_per == 0 && !DGB_SKIP(p, 4);
                     if (leader) {
                         trace_point(p, 9, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes) + (load_sfb ? L::kSfbBytes : 0));
                         if (!DGB_SKIP(p, 2))
-                            tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * 128, b_row);
+                            tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * kTmaXPerKb, b_row);
                         if (load_sfb)
                             tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
                                         t.n_block * BLOCK_N, sfb_y + kb * kSfInts / b_per);
@@ -443,9 +448,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
         int trace_i = 0;
-        const uint32_t idesc = kKind == kKindNvfp4
-            ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
-            : make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
+        const uint32_t idesc = kKind == kKindBf16
+            ? make_idesc_bf16_f32(128, BLOCK_N)
+            : kKind == kKindNvfp4 ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
+                                  : make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
         uint32_t tmem_sfa = 0, tmem_sfb = 0;  // TMEM columns holding the scale factors of the current K block
@@ -465,7 +471,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             for (int kb = 0; kb < num_kb; ++kb) {
                 // scale factors stored in tcgen05.cp order need no transposer pass: the loads' barrier is enough
                 if (lane == 0) trace_point(p, 8, trace_i);
-                ok = mbar_wait(((p.sf_transposed && !kCpByHelper) ? full_bar : sf_ready_bar) + stage, phase, abort_flag,
+                ok = mbar_wait(((!kScaled || (p.sf_transposed && !kCpByHelper)) ? full_bar : sf_ready_bar) + stage, phase, abort_flag,
                                kTimeoutSfReady, kb);
                 if (!ok) break;
                 if (kCpByHelper && p.sf_transposed) tcgen05_fence_after();  // the helper warp's tcgen05.cp precede our MMAs
@@ -476,7 +482,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     trace_point(p, 4, trace_i);
                     // One tcgen05.cp moves the scales of 128 rows for one MMA (one packed int per row) into 4 TMEM columns.
                     const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
-                    const bool cp_here = !(kCpByHelper && p.sf_transposed);
+                    const bool cp_here = kScaled && !(kCpByHelper && p.sf_transposed);
                     if (kb % a_per == 0) {
                         tmem_sfa = sf_cols;
                         if (cp_here) {
@@ -500,7 +506,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
                         if (DGB_SKIP(p, 8)) continue;
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
-                        if constexpr (kKind == kKindNvfp4) {
+                        if constexpr (kKind == kKindBf16) {
+                            // K = 16 BF16 elements (32 bytes) per MMA
+                            tcgen05_mma_f16(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2, idesc, (kb | k4) != 0 ? 1u : 0u);
+                        } else if constexpr (kKind == kKindNvfp4) {
                             // K = 64 per MMA; its 4 scales per row are the 4 bytes of packed int k4 of the stage
                             tcgen05_mma_mxf4nvf4_4x(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2, idesc, tmem_sfa + k4 * 4,
                                                     tmem_sfb + k4 * (BLOCK_N / 32), (kb | k4) != 0 ? 1u : 0u);
@@ -529,7 +538,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         Tile t;
         uint32_t stage = 0, phase = 0;
         int trace_i = 0;
-        bool ok = p.sf_transposed == 0;  // nothing to do when the scale factors arrive in tcgen05.cp order
+        bool ok = kScaled && p.sf_transposed == 0;  // nothing to do when the scale factors arrive in tcgen05.cp order
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -673,7 +682,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             const bool warp_has_rows = static_cast<int>(q * 32) < t.rows_store;
             uint32_t acc[kCols];
             if (warp_has_rows) {
-                if constexpr (EPI == kEpiSwiGLU || EPI == kEpiSwiGLUNvfp4) {
+                if constexpr (EPI == kEpiSwiGLU || EPI == kEpiSwiGLUNvfp4 || EPI == kEpiSwiGLUBf16) {
                     // tile columns are [gate BLOCK_N / 2 | up BLOCK_N / 2]: this thread takes its half of the gate columns
                     // and the matching up columns
                     const uint32_t tmem_row = tmem_base + as * kAccumCols + ((q * 32u) << 16) + half * (kCols / 2);
@@ -804,6 +813,36 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                 static_cast<unsigned char>(sf_byte);
                         }
                         st_global_v4(p.act_q + row * p.act_q_row_stride + j / 2, packed[0], packed[1], packed[2], packed[3]);
+                    }
+                } else if constexpr (EPI == kEpiSwiGLUBf16) {
+                    // Same column order and arithmetic as the FP8 form below, the outputs stay BF16 (reference:
+                    // deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:927-955).
+                    const float w = p.row_weight != nullptr ? __ldg(p.row_weight + row) : 1.0f;
+#pragma unroll
+                    for (int c = 0; c < kCols / 64; ++c) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float o[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                float gv = bf16_round(__uint_as_float(acc[c * 32 + i * 2 + h]));
+                                float uv = bf16_round(__uint_as_float(acc[kCols / 2 + c * 32 + i * 2 + h]));
+                                if (p.clamp > 0.0f) {
+                                    gv = fminf(gv, p.clamp);
+                                    uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                                }
+                                const float silu = p.fast_math ? gv * rcp_approx(1.0f + __expf(-gv))
+                                                               : gv / (1.0f + expf(-gv));
+                                o[h] = silu * uv * w;
+                            }
+                            packed[i] = pack_bf16x2(o[0], o[1]);
+                        }
+                        const int j = t.n_block * (BLOCK_N / 2) + static_cast<int>(half) * (kCols / 2) + c * 32;
+                        unsigned char* dst = p.act_q + row * p.act_q_row_stride + j * 2;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            st_global_v4(dst + i * 16, packed[i * 4], packed[i * 4 + 1], packed[i * 4 + 2], packed[i * 4 + 3]);
                     }
                 } else {
                     // acc[0, kCols / 2) are gate channels, acc[kCols / 2, kCols) the matching up channels (see the drain

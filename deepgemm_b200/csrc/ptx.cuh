@@ -271,6 +271,11 @@ __host__ __device__ constexpr uint32_t make_idesc_block_scaled(uint32_t a_fmt, u
     return (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (scale_type << 23) | ((m >> 4) << 24);
 }
 
+// kind::f16 descriptor: BF16 operands (format 1), both K-major, FP32 accumulator (format 1 at bits [4,6)).
+__host__ __device__ constexpr uint32_t make_idesc_bf16_f32(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
 __device__ __forceinline__ uint32_t idesc_with_sf_ids(uint32_t idesc, uint32_t a_sf_id, uint32_t b_sf_id) {
     return idesc | (a_sf_id << 29) | (b_sf_id << 4);
 }
@@ -293,6 +298,18 @@ __device__ __forceinline__ void tcgen05_mma_mxf8f6f4(uint32_t tmem_d, uint64_t a
         "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
         "}\n"
         :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, BF16 / FP16 operands, K = 16 per instruction, no scales.
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // Packed E2M1 x E2M1, K = 64 per instruction, one UE4M3 scale per 16 K (NVFP4).

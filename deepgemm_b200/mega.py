@@ -32,7 +32,7 @@ def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_pe
     return 128
 
 
-_MMA_TYPES = ('fp8xfp4', 'nvfp4xnvfp4')
+_MMA_TYPES = ('fp8xfp4', 'nvfp4xnvfp4', 'bf16xbf16')
 
 
 def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
@@ -42,6 +42,10 @@ def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hi
         _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe_ex(
             num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
             shared_intermediate_hidden, ctypes.cast(words, ctypes.c_void_p)))
+    elif mma_type == 'bf16xbf16':
+        _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_bf16_mega_moe(
+            num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+            ctypes.cast(words, ctypes.c_void_p)))
     else:
         _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(
             num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
@@ -94,6 +98,9 @@ class SymmBuffer:
         if mma_type == 'fp8xfp4':
             self.x = view(lay['x'], t * hidden, torch.float8_e4m3fn, (t, hidden))
             self.x_sf = view(lay['x_sf'], t * (hidden // 128) * 4, torch.int32, (t, hidden // 128))
+        elif mma_type == 'bf16xbf16':
+            self.x = view(lay['x'], t * hidden * 2, torch.bfloat16, (t, hidden))
+            self.x_sf = None
         else:  # packed E2M1 rows, four UE4M3 block scales (64 K elements) per int
             self.x = view(lay['x'], t * hidden // 2, torch.int8, (t, hidden // 2))
             self.x_sf = view(lay['x_sf'], t * (hidden // 64) * 4, torch.int32, (t, hidden // 64))
@@ -156,8 +163,10 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     scale factors for its own kernel)."""
     if activation != 'swiglu':
         raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
-    if not isinstance(l1_weights, tuple):
-        raise RuntimeError('BF16 weights are not built; pass (packed FP4 weights, packed scale factors[, tensor scales])')
+    if not isinstance(l1_weights, tuple):  # BF16 weights: only the gate/up interleave
+        if l1_weights.dtype != torch.bfloat16 or l2_weights.dtype != torch.bfloat16 or l1_weights.dim() != 3:
+            raise RuntimeError('bare weight tensors must be bfloat16 [E, N, K]')
+        return _interleave_rows(l1_weights, _GATE_UP_INTERLEAVE).contiguous(), l2_weights
     if l1_weights[0].dim() == 2:  # shared experts: one FP8 matrix per layer, same reordering
         t1, t2 = transform_weights_for_mega_moe(tuple(t.unsqueeze(0) for t in l1_weights),
                                                 tuple(t.unsqueeze(0) for t in l2_weights), activation)
@@ -295,6 +304,42 @@ def nvfp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor
             p(y), p(l1_weights[0]), p(l1_weights[1]), p(l1_weights[2]), p(l2_weights[0]), p(l2_weights[1]),
             p(l2_weights[2]), p(x_scale), p(act_scale), p(stats), p(b.buffer), ctypes.cast(ptrs, ctypes.c_void_p),
             b.rank, b.num_ranks, y.size(0), b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden,
+            b.intermediate_hidden, float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
+            _lib.current_stream_ptr()))
+
+
+def bf16_mega_moe(y: torch.Tensor, l1_weights: torch.Tensor, l2_weights: torch.Tensor, sym_buffer: SymmBuffer,
+                  shared_l1_weights: Optional[torch.Tensor] = None, shared_l2_weights: Optional[torch.Tensor] = None,
+                  cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None, activation: str = 'swiglu',
+                  activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
+    """The layer with BF16 activations and weights. Reference: bf16_mega_moe, deep_gemm/mega/__init__.py:178-204.
+
+    ``sym_buffer`` must have been created with ``mma_type='bf16xbf16'``; the caller writes ``x`` (bfloat16), ``topk_idx``
+    and ``topk_weights``. Weights are bfloat16 [E_local, 2 * inter, hidden] / [E_local, hidden, inter] passed through
+    ``transform_weights_for_mega_moe``. Shared experts are not built for this form."""
+    if activation != 'swiglu':
+        raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
+    if shared_l1_weights is not None or shared_l2_weights is not None:
+        raise RuntimeError('shared experts are not built for the BF16 layer')
+    b = sym_buffer
+    if b.mma_type != 'bf16xbf16':
+        raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
+    num_local = b.num_experts // b.num_ranks
+    for w, shape, name in ((l1_weights, (num_local, 2 * b.intermediate_hidden, b.hidden), 'l1_weights'),
+                           (l2_weights, (num_local, b.hidden, b.intermediate_hidden), 'l2_weights')):
+        if not (w.is_cuda and w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == shape):
+            raise RuntimeError(f'{name} must be a contiguous CUDA bfloat16 tensor of shape {shape}')
+    if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
+        raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
+    stats = cumulative_local_expert_recv_stats
+    if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == num_local and stats.is_contiguous()):
+        raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
+    ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.lib().dgb200_bf16_mega_moe(
+            p(y), p(l1_weights), p(l2_weights), p(stats), p(b.buffer), ctypes.cast(ptrs, ctypes.c_void_p), b.rank,
+            b.num_ranks, y.size(0), b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden,
             b.intermediate_hidden, float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
             _lib.current_stream_ptr()))
 

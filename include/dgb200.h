@@ -102,6 +102,21 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
     int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
     int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream);
 
+/* BF16 x BF16 forms of the three GEMMs above (tcgen05 kind::f16, FP32 accumulation, no scale factors): a and b are
+ * BF16 K-major with row strides in elements (multiples of 8), d BF16 or FP32, layouts as above. Requires k % 64 == 0 and
+ * n % 128 == 0.
+ * Reference: m_grouped_bf16_gemm_nt_contiguous csrc/apis/gemm.hpp:464-517, m_grouped_bf16_gemm_nt_masked :528-564,
+ * bf16_gemm_nt :404-438 (its optional accumulator input `c` is not built). */
+int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d,
+                                             int64_t d_row_stride, const int32_t* grouped_layout, int32_t m, int32_t n,
+                                             int32_t k, int32_t num_groups, int32_t d_is_fp32, int32_t layout_kind,
+                                             int32_t alignment, int32_t store_padding, void* stream);
+int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, int64_t d_row_stride, const int32_t* masked_m,
+                                         int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
+                                         int32_t d_is_fp32, void* stream);
+int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
+                        int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, void* stream);
+
 /* BF16 rows -> E4M3 + one UE8M0 scale per gran_k (32 or 128) elements: sf = 2^ceil(log2(max(amax, 1e-4) / 448)),
  * q = e4m3_rn(x / sf). Reference: per_token_cast_to_fp8(use_ue8m0=True), deep_gemm/utils/math.py:26-49 (a torch
  * helper there; one fused kernel here).
@@ -251,6 +266,19 @@ int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* args, void* stream);
 int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
                                                   int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                                                   int32_t shared_intermediate_hidden, int64_t* out);
+
+/* BF16 x BF16 form of the layer. Buffer layout: same out[16] fields as dgb200_get_symm_buffer_layout_for_mega_moe; the
+ * caller writes x (bf16 [T, hidden]); the scale-factor regions are empty. Stages as in dgb200_fp8_fp4_mega_moe with BF16
+ * rows throughout: l1_w bf16 [E_local, 2 * inter, hidden] (gate/up interleaved by 128), l2_w bf16 [E_local, hidden, inter];
+ * the gate/up GEMM's epilogue writes silu(gate) * up * topk_weight as BF16. hidden and inter must be multiples of 128.
+ * Reference: bf16_mega_moe, csrc/apis/mega.hpp:288-400 and deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:52;
+ * shared experts are not built for this form. */
+int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
+                                                    int32_t num_topk, int32_t hidden, int32_t intermediate_hidden, int64_t* out);
+int dgb200_bf16_mega_moe(void* y, const void* l1_w, const void* l2_w, int32_t* cumulative_local_expert_recv_stats, void* buffer,
+                         const uint64_t* peer_buffer_ptrs, int32_t rank, int32_t num_ranks, int32_t num_tokens,
+                         int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
+                         int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream);
 
 /* NVFP4 x NVFP4 form of the layer (no reference counterpart; the reference's layer is FP8 x MXFP4 only).
  * Buffer layout: same out[16] fields as dgb200_get_symm_buffer_layout_for_mega_moe; the caller writes

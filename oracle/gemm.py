@@ -67,3 +67,42 @@ def grouped_gemm_masked(a_q, a_sf, b_q, b_sf, masked_m, gran_k_a=128, gran_k_b=3
             d[g, :rows] = a @ b[g].T
             mask[g, :rows] = True
     return d.to(out_dtype), mask
+
+
+def bf16_grouped_gemm_contiguous(a, b, grouped_layout, use_psum_layout=False, alignment=128, out_dtype=torch.bfloat16):
+    """D[m] = A[m] @ B[group(m)].T on bfloat16 operands with FP32 accumulation: the reference's own check for the
+    BF16 family is the torch product of the same tensors (tests/generators.py:329-410 with use_bf16,
+    tests/test_bf16.py:58-89). Layouts as in grouped_gemm_contiguous. Returns (d, row_mask)."""
+    a32, b32 = a.float(), b.float()
+    m, n = a32.shape[0], b32.shape[1]
+    d = torch.zeros((m, n), dtype=torch.float32)
+    mask = torch.zeros(m, dtype=torch.bool)
+    if use_psum_layout:
+        start = 0
+        for g in range(b32.shape[0]):
+            end = int(grouped_layout[g])
+            if end > start:
+                d[start:end] = a32[start:end] @ b32[g].T
+                mask[start:end] = True
+            start = align(end, alignment)
+    else:
+        for g in range(b32.shape[0]):
+            rows = grouped_layout == g
+            if bool(rows.any()):
+                d[rows] = a32[rows] @ b32[g].T
+                mask |= rows
+    return d.to(out_dtype), mask
+
+
+def bf16_grouped_gemm_masked(a, b, masked_m, out_dtype=torch.bfloat16):
+    """a [G, max_m, K], b [G, N, K] bfloat16; only rows < masked_m[g] are defined (tests/test_bf16.py:118-144).
+    Returns (d [G, max_m, N], row_mask [G, max_m])."""
+    g_count, max_m, _ = a.shape
+    d = torch.zeros((g_count, max_m, b.shape[1]), dtype=torch.float32)
+    mask = torch.zeros((g_count, max_m), dtype=torch.bool)
+    for g in range(g_count):
+        rows = int(masked_m[g])
+        if rows > 0:
+            d[g, :rows] = a[g, :rows].float() @ b[g].float().T
+            mask[g, :rows] = True
+    return d.to(out_dtype), mask

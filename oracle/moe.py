@@ -124,6 +124,39 @@ def moe_layer(x_q: torch.Tensor, x_sf: torch.Tensor, topk_idx: torch.Tensor, top
     return (y, inter) if return_intermediates else y
 
 
+def swiglu_bf16(gate_up: torch.Tensor, weight: torch.Tensor, clamp: Optional[float]) -> torch.Tensor:
+    """L1 epilogue of the BF16 layer on fp32 accumulators [rows, 2I] laid out [gate | up]: round to bf16 -> clamp ->
+    silu(gate) * up * weight in fp32 -> bf16 (sm100_bf16_mega_moe.cuh:927-955). Returns bf16 [rows, I]."""
+    half = gate_up.shape[1] // 2
+    gate = gate_up[:, :half].bfloat16().float()
+    up = gate_up[:, half:].bfloat16().float()
+    if clamp is not None:
+        gate = gate.clamp(max=clamp)
+        up = up.clamp(min=-clamp, max=clamp)
+    return (gate / (1.0 + torch.exp(-gate)) * up * weight.float().unsqueeze(1)).bfloat16()
+
+
+def moe_layer_bf16(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+                   clamp: Optional[float] = None) -> torch.Tensor:
+    """The layer of moe_layer with bfloat16 activations and weights (bf16_mega_moe, csrc/apis/mega.hpp:288-400):
+    x [T, H], w1 [E, 2I, H] rows [gate | up], w2 [E, H, I]; FP32 accumulation, BF16 rows between the stages, the same
+    combine."""
+    tokens, hidden = x.shape
+    num_experts, topk = w1.shape[0], topk_idx.shape[1]
+    slot_rows = torch.zeros((tokens, topk, hidden), dtype=torch.bfloat16)
+    for e in range(num_experts):
+        tok, slot = torch.nonzero(topk_idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        a2 = swiglu_bf16(x[tok].float() @ w1[e].float().T, topk_weights[tok, slot], clamp)
+        slot_rows[tok, slot] = (a2.float() @ w2[e].float().T).bfloat16()
+    valid = (topk_idx >= 0) & (topk_idx < num_experts)
+    y = torch.zeros((tokens, hidden), dtype=torch.float32)
+    for k in range(topk):
+        y += torch.where(valid[:, k, None], slot_rows[:, k].float(), torch.zeros(()))
+    return y.bfloat16()
+
+
 def ep_counts(topk_idx: torch.Tensor, num_experts: int) -> torch.Tensor:
     """Entries of one rank per (global) expert, masked slots (-1) excluded: the vector each rank publishes."""
     flat = topk_idx.reshape(-1)

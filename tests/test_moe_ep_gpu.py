@@ -289,3 +289,66 @@ def test_two_rank_full_size_plan_and_sampled_tokens():
                 a2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(q2, s2, 32).T
                 acc += a2.bfloat16().float()[0]
             assert quant.calc_diff(s['y'], acc.bfloat16()) <= 2e-3
+
+
+# ---- the BF16 layer on 2 ranks: the same push / barrier / pull protocol with BF16 rows and no scale factors
+def _rank_inputs_bf16(rank):
+    from oracle import moe as omoe
+    torch.manual_seed(700 + rank)
+    t = TOKENS[rank]
+    x = torch.randn(t, HIDDEN).bfloat16()
+    idx, w = omoe.route_sigmoid_topk(torch.randn(t, EXPERTS), TOPK)
+    mask = torch.rand(idx.shape) < 0.15
+    idx, w = idx.masked_fill(mask, -1), w.masked_fill(mask, 0.0)
+    torch.manual_seed(79)  # the same weights on every rank
+    w1 = (torch.randn(EXPERTS, 2 * INTER, HIDDEN) * 0.05).bfloat16()
+    w2 = (torch.randn(EXPERTS, HIDDEN, INTER) * 0.05).bfloat16()
+    return dict(x=x, topk_idx=idx, topk_weights=w, w1=w1, w2=w2)
+
+
+def _worker_bf16(rank, world, port, results):
+    import torch.distributed as dist
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        c = _rank_inputs_bf16(rank)
+        per_rank = EXPERTS // world
+        mine = slice(rank * per_rank, (rank + 1) * per_rank)
+        buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, EXPERTS, max(TOKENS), TOPK, HIDDEN, INTER,
+                                              mma_type='bf16xbf16')
+        l1, l2 = dg.transform_weights_for_mega_moe(c['w1'][mine].cuda(), c['w2'][mine].cuda())
+        t = TOKENS[rank]
+        ys = []
+        for _ in range(2):
+            buf.x[:t].copy_(c['x'].cuda())
+            buf.topk_idx[:t].copy_(c['topk_idx'].cuda())
+            buf.topk_weights[:t].copy_(c['topk_weights'].cuda())
+            y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+            dg.bf16_mega_moe(y, l1, l2, buf, fast_math=False)
+            status = _lib.device_status()
+            assert status[0] == 0, status
+            ys.append(y.cpu())
+        results[rank] = dict(y0=ys[0], y1=ys[1])
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs 2 GPUs')
+def test_two_rank_bf16_layer_matches_oracle():
+    import torch.multiprocessing as mp
+    from oracle import moe as omoe
+    from oracle import quant
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker_bf16, args=(world, _free_port(), results), nprocs=world, join=True)
+    for rank in range(world):
+        c, got = _rank_inputs_bf16(rank), results[rank]
+        want = omoe.moe_layer_bf16(c['x'], c['topk_idx'], c['topk_weights'], c['w1'], c['w2'])
+        assert torch.equal(got['y0'], got['y1'])
+        assert not torch.isnan(got['y0'].float()).any()
+        assert quant.calc_diff(got['y0'], want) < 1e-4
