@@ -43,6 +43,8 @@ _SIGNATURES = {
                                                  _i32, _i32, _ptr],
     'dgb200_m_grouped_bf16_gemm_nt_masked': [_ptr, _ptr, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_bf16_gemm_nt': [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_k_grouped_sf_workspace_bytes': [_i32, _i32, _i32, _i32],
+    'dgb200_k_grouped_fp8_gemm_tn_contiguous': [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i32, _i32, _i32, _ptr, _ptr],
     'dgb200_fp8_fp4_gemm_nt': [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_segment_alignment_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
@@ -97,7 +99,7 @@ def lib() -> ctypes.CDLL:
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_int
+            fn.restype = ctypes.c_int64 if name == 'dgb200_k_grouped_sf_workspace_bytes' else ctypes.c_int
         _lib = handle
     return _lib
 

@@ -1235,6 +1235,75 @@ int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, 
     return 0;
 }
 
+int64_t dgb200_k_grouped_sf_workspace_bytes(int32_t num_groups, int32_t m, int32_t n, int32_t sum_k) {
+    if (num_groups <= 0 || m <= 0 || n <= 0 || sum_k < 0) return 0;
+    const long long rows = sum_k / 128 / 4 + num_groups;  // every group rounds its K blocks up to a multiple of 4
+    return rows * ((static_cast<long long>(m) + 3) / 4 * 4 + (static_cast<long long>(n) + 3) / 4 * 4) * 4;
+}
+
+int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, const void* b, const float* sfb, const float* c,
+                                            float* d, const int32_t* ks, int32_t num_groups, int32_t m, int32_t n,
+                                            int32_t sum_k, void* sf_workspace, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DGB_REQUIRE(num_groups > 0 && num_groups <= kMaxCachedGroups, "num_groups must be in [1, %d]", kMaxCachedGroups);
+    DGB_REQUIRE(m > 0 && m % 16 == 0 && n > 0 && n % 128 == 0, "m (%d) must be a positive multiple of 16 and n (%d) of 128", m, n);
+    DGB_REQUIRE(sum_k >= 0 && sum_k % 128 == 0, "the K extents must be multiples of 128 (sum %d)", sum_k);
+    DGB_REQUIRE(c != nullptr && d != nullptr && ks != nullptr, "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0, "c and d must be 16-byte aligned");
+    if (sum_k == 0) {
+        if (c != d) DGB_CUDA(cudaMemcpyAsync(d, c, static_cast<size_t>(num_groups) * m * n * 4, cudaMemcpyDeviceToDevice, stream));
+        return 0;
+    }
+    DGB_REQUIRE(a != nullptr && b != nullptr && sfa != nullptr && sfb != nullptr && sf_workspace != nullptr, "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(sf_workspace) % 16 == 0,
+                "a, b and the workspace must be 16-byte aligned");
+    const long long kp_rows = sum_k / 128 / 4 + num_groups;
+    const long long aligned_m = (static_cast<long long>(m) + 3) / 4 * 4, aligned_n = (static_cast<long long>(n) + 3) / 4 * 4;
+    uint32_t* sfa_packed = static_cast<uint32_t*>(sf_workspace);
+    uint32_t* sfb_packed = sfa_packed + kp_rows * aligned_m;
+    {
+        const dim3 grid_a(static_cast<unsigned>(std::min<long long>((static_cast<long long>(sum_k / 128 / 4 + 1) * m + 255) / 256, 64)), num_groups);
+        dgb200_pack_k_grouped_sf_kernel<<<grid_a, 256, 0, stream>>>(sfa, ks, m, aligned_m, sfa_packed);
+        const dim3 grid_b(static_cast<unsigned>(std::min<long long>((static_cast<long long>(sum_k / 128 / 4 + 1) * n + 255) / 256, 64)), num_groups);
+        dgb200_pack_k_grouped_sf_kernel<<<grid_b, 256, 0, stream>>>(sfb, ks, n, aligned_n, sfb_packed);
+        DGB_CUDA(cudaGetLastError());
+    }
+    GemmParams p{};
+    p.d = d;
+    p.c = c;
+    p.d_row_stride = n;
+    p.layout = ks;
+    p.mode = kModeKGrouped;
+    p.m = m;
+    p.n = n;
+    p.k = sum_k;
+    p.num_groups = num_groups;
+    p.alignment = 128;
+    p.gran_a = p.gran_b = 128;
+    p.b_fmt = kFmtE4M3;
+    p.b_tx_bytes = 128 * 128;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+    int rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a, static_cast<uint64_t>(m), static_cast<uint64_t>(sum_k),
+                                static_cast<uint64_t>(m), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b, static_cast<uint64_t>(n), static_cast<uint64_t>(sum_k),
+                            static_cast<uint64_t>(n), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, sfa_packed, static_cast<uint64_t>(aligned_m),
+                            static_cast<uint64_t>(kp_rows), static_cast<uint64_t>(aligned_m) * 4, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, sfb_packed, static_cast<uint64_t>(aligned_n),
+                            static_cast<uint64_t>(kp_rows), static_cast<uint64_t>(aligned_n) * 4, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    int sms = 0;
+    rc = effective_num_sms(&sms);
+    if (rc) return rc;
+    const long long tiles = static_cast<long long>(num_groups) * ((m + 127) / 128) * (n / 128);
+    const int grid = static_cast<int>(std::min<long long>(sms, tiles));
+    return launch_gemm<128, 6, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_a, p, grid, stream);
+}
+
 int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t experts, int32_t topk, int64_t* topk_idx,
                               float* topk_weights, void* stream) {
     DGB_REQUIRE(logits != nullptr && topk_idx != nullptr && topk_weights != nullptr, "null tensor pointer");

@@ -34,6 +34,7 @@ enum GroupMode : int {
     kModePsum = 1,    // layout[g] = end row of group g; group g starts at align(layout[g-1], alignment)
     kModeMasked = 2,  // A/D are [G, max_m, *]; layout[g] = valid rows of group g
     kModeDense = 3,   // one group covering rows [0, m); no layout array
+    kModeKGrouped = 4,  // groups along K: A [sum_k, m], B [sum_k, n] (MN-major), D [G, m, n]; layout[g] = K rows of group g
 };
 
 enum EpilogueKind : int {
@@ -42,6 +43,7 @@ enum EpilogueKind : int {
     kEpiSwiGLU = 2,  // gate/up -> silu(gate)*up*row_weight -> per-32 UE8M0 FP8 requant
     kEpiSwiGLUNvfp4 = 3,  // gate/up -> silu(gate)*up*row_weight -> NVFP4 (per-16 UE4M3 scales, given per-tensor scale)
     kEpiSwiGLUBf16 = 4,   // gate/up -> silu(gate)*up*row_weight -> BF16 rows (the BF16 layer)
+    kEpiF32Acc = 5,       // D fp32 = C + accumulator; selects the K-grouped form of the kernel (kModeKGrouped)
 };
 
 enum MmaKind : int {
@@ -94,6 +96,7 @@ struct GemmParams {
     const float* a_scale;
     const float* b_scales;
     const float* out_scale;
+    const float* c;  // kEpiF32Acc: accumulator input [G, m, n] (may alias d)
 };
 
 struct Tile {
@@ -102,6 +105,8 @@ struct Tile {
     int rows_store;    // rows of this tile to write
     int group;
     int n_block;
+    // K-grouped form only: first K row of the group in A / B, its K blocks, first packed scale row of the group
+    int k_row_start, num_kb, sf_kp0;
 };
 
 constexpr int kMaxCachedGroups = 512;   // group extents of up to this many groups are staged in shared memory
@@ -165,6 +170,24 @@ struct TileScheduler {
 
     // Returns false when this CTA has no more tiles. A tile with group < 0 must be skipped by every role.
     __device__ bool next(Tile& t) {
+        if (p.mode == kModeKGrouped) {
+            // every group has the same (m blocks x n blocks) output tiles; the table holds (K blocks, first K row,
+            // first packed scale row) per group
+            const int per_group = (p.m + 127) / 128 * num_n_blocks;
+            if (tile >= p.num_groups * per_group) return false;
+            const int group = tile / per_group;
+            const int local = tile - group * per_group;
+            const int mb = local / num_n_blocks;
+            t.n_block = local - mb * num_n_blocks;
+            t.row_start = t.sf_row_start = mb * 128;
+            t.rows_store = min(128, p.m - mb * 128);
+            t.group = group;
+            t.num_kb = tab.lay[group];
+            t.k_row_start = tab.start[group];
+            t.sf_kp0 = tab.tiles_end[group];
+            tile += static_cast<int>(gridDim.x);
+            return true;
+        }
         if (p.mode == kModeRowIds || p.mode == kModeDense) {
             const int num_m_blocks = (p.m + 127) / 128;
             if (tile >= num_m_blocks * num_n_blocks) return false;
@@ -323,8 +346,23 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     int* group_cache = reinterpret_cast<int*>(smem + L::kOffGroups);
     int* group_start = group_cache + kMaxCachedGroups;
     int* group_tiles_end = group_start + kMaxCachedGroups;
-    const bool cache_groups = (p.mode == kModePsum || p.mode == kModeMasked) && p.num_groups <= kMaxCachedGroups;
-    if (cache_groups) {
+    constexpr bool kKG = EPI == kEpiF32Acc;  // K-grouped form: MN-major operands, per-group K extents, D = C + acc
+    const bool cache_groups = ((p.mode == kModePsum || p.mode == kModeMasked) && p.num_groups <= kMaxCachedGroups) || kKG;
+    if constexpr (kKG) {
+        // (K blocks, first K row, first packed scale row) per group: a serial scan by one thread (at most
+        // kMaxCachedGroups groups, checked by the host)
+        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) group_cache[i] = __ldg(p.layout + i) / 128;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int k_row = 0, kp = 0;
+            for (int i = 0; i < p.num_groups; ++i) {
+                group_start[i] = k_row;
+                group_tiles_end[i] = kp;
+                k_row += group_cache[i] * 128;
+                kp += (group_cache[i] + 3) / 4;
+            }
+        }
+    } else if (cache_groups) {
         for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) {
             int start, rows, rows_store;
             TileScheduler<BLOCK_N>::group_extent(p, p.layout, i, start, rows, rows_store);
@@ -381,15 +419,19 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             int trace_i = 0;
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
-                const int sfa_y = t.group * p.sfa_group_rows;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int sfa_y = kKG ? t.sf_kp0 : t.group * p.sfa_group_rows;
+                const int tile_kb = kKG ? t.num_kb : num_kb;
+                for (int kb = 0; kb < tile_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
                     const bool load_sfa = kScaled && kb % a_per == 0 && !DGB_SKIP(p, 4);
                     if (elect_one()) {
                         trace_point(p, 0, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) + (load_sfa ? L::kSfaBytes : 0));
-                        if (!DGB_SKIP(p, 1))
+                        if constexpr (kKG)
+                            tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, t.row_start,
+                                        t.k_row_start + kb * 128);
+                        else if (!DGB_SKIP(p, 1))
                             tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * kTmaXPerKb,
                                         t.row_start);
                         if (load_sfa)
@@ -418,15 +460,19 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int b_row = t.group * p.n + t.n_block * BLOCK_N;
-                const int sfb_y = t.group * p.sfb_packed_k;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int sfb_y = kKG ? t.sf_kp0 : t.group * p.sfb_packed_k;
+                const int tile_kb = kKG ? t.num_kb : num_kb;
+                for (int kb = 0; kb < tile_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
                     const bool load_sfb = kScaled && kb % b_per == 0 && !DGB_SKIP(p, 4);
                     if (leader) {
                         trace_point(p, 9, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes) + (load_sfb ? L::kSfbBytes : 0));
-                        if (!DGB_SKIP(p, 2))
+                        if constexpr (kKG)
+                            tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, t.n_block * BLOCK_N,
+                                        t.k_row_start + kb * 128);
+                        else if (!DGB_SKIP(p, 2))
                             tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * kTmaXPerKb, b_row);
                         if (load_sfb)
                             tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
@@ -448,7 +494,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
         int trace_i = 0;
-        const uint32_t idesc = kKind == kKindBf16
+        const uint32_t idesc = kKG
+            ? (make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, 128, BLOCK_N, kScaleUE8M0) | (1u << 15) | (1u << 16))  // both MN-major
+            : kKind == kKindBf16
             ? make_idesc_bf16_f32(128, BLOCK_N)
             : kKind == kKindNvfp4 ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
                                   : make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
@@ -468,7 +516,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             if (lane == 0) trace_point(p, 14, static_cast<int>(iter));
             tcgen05_fence_after();
             const uint32_t tmem_acc = tmem_base + as * kAccumCols;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            const int tile_kb = kKG ? t.num_kb : num_kb;
+            if (kKG && tile_kb == 0 && leader) tcgen05_commit(tmem_full_bar + as);  // empty group: D = C, nothing to wait for
+            for (int kb = 0; kb < tile_kb; ++kb) {
                 // scale factors stored in tcgen05.cp order need no transposer pass: the loads' barrier is enough
                 if (lane == 0) trace_point(p, 8, trace_i);
                 ok = mbar_wait(((!kScaled || (p.sf_transposed && !kCpByHelper)) ? full_bar : sf_ready_bar) + stage, phase, abort_flag,
@@ -499,8 +549,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                 tcgen05_cp_32x128b_warpx4(tmem_sfb + b * 4, make_sf_desc(sfb_smem + stage * L::kSfbBytes + b * 512));
                         }
                     }
-                    const uint64_t adesc = make_kmajor_sw128_desc(a_base + stage * L::kABytes);
-                    const uint64_t bdesc = make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
+                    const uint64_t adesc = kKG ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, L::kABytes)
+                                               : make_kmajor_sw128_desc(a_base + stage * L::kABytes);
+                    const uint64_t bdesc = kKG ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, L::kBBytes)
+                                               : make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
+                    // K-major: +32 bytes along K inside the swizzle span per MMA; MN-major: 32 K rows = 4 groups of 1024 B
+                    constexpr uint32_t kDescStep = kKG ? 256 : 2;
                     trace_point(p, 12, trace_i);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
@@ -516,14 +570,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         } else {
                             const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                             const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
-                            tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2,
+                            tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * kDescStep, bdesc + k4 * kDescStep,
                                                  idesc_with_sf_ids(idesc, sfa_id, sfb_id), tmem_sfa, tmem_sfb,
                                                  (kb | k4) != 0 ? 1u : 0u);
                         }
                     }
                     trace_point(p, 13, trace_i);
                     tcgen05_commit(empty_bar + stage);
-                    if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar + as);
+                    if (kb == tile_kb - 1) tcgen05_commit(tmem_full_bar + as);
                     trace_point(p, 5, trace_i);
                 }
                 ++trace_i;
@@ -541,7 +595,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         bool ok = kScaled && p.sf_transposed == 0;  // nothing to do when the scale factors arrive in tcgen05.cp order
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            const int tile_kb = kKG ? t.num_kb : num_kb;
+            for (int kb = 0; kb < tile_kb; ++kb) {
                 ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
                 if (lane == 0) trace_point(p, 2, trace_i);
@@ -770,6 +825,23 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 2]), __uint_as_float(acc[i * 8 + 3])),
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 4]), __uint_as_float(acc[i * 8 + 5])),
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 6]), __uint_as_float(acc[i * 8 + 7])));
+                    }
+                } else if constexpr (EPI == kEpiF32Acc) {
+                    // D[g] = C[g] + accumulator (an empty group contributes nothing: its accumulator was never written)
+                    const long long off = (static_cast<long long>(t.group) * p.m + row) * p.d_row_stride +
+                                          static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
+                    const float4* src = reinterpret_cast<const float4*>(p.c + off);
+                    float* dst = reinterpret_cast<float*>(p.d) + off;
+                    const bool empty = t.num_kb == 0;
+#pragma unroll
+                    for (int i = 0; i < kCols / 4; ++i) {
+                        const float4 cv = src[i];
+                        const float a0 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 0]);
+                        const float a1 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 1]);
+                        const float a2 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 2]);
+                        const float a3 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 3]);
+                        st_global_v4(dst + i * 4, __float_as_uint(cv.x + a0), __float_as_uint(cv.y + a1),
+                                     __float_as_uint(cv.z + a2), __float_as_uint(cv.w + a3));
                     }
                 } else if constexpr (EPI == kEpiSwiGLUNvfp4) {
                     // Same column order as below; the 32 outputs of a gate/up pair are requantised to NVFP4: two

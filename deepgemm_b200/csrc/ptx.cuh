@@ -253,6 +253,13 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     return make_smem_desc(smem_addr, 1024, kSwizzle128B);
 }
 
+// MN-major operand tile (rows = K, each row 128 contiguous bytes of M or N, 128-byte swizzle, as a TMA box of a
+// [K, MN] tensor lands): 8-row K groups are 1024 B apart (stride offset); the leading offset is the distance between
+// 128-byte chunks along MN, which a 128-wide 8-bit tile has only one of.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return make_smem_desc(smem_addr, 1024, kSwizzle128B) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16);
+}
+
 // Scale-factor block for tcgen05.cp 32x128b: 32 rows of 16 bytes, contiguous; 8-row groups 128 B apart.
 __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
     return make_smem_desc(smem_addr, 128, kSwizzleNone);

@@ -252,4 +252,35 @@ __global__ void __launch_bounds__(256) dgb200_cast_rows_nvfp4_kernel(const CastN
     }
 }
 
+// Scale factors of a K-grouped operand: FP32 powers of two [sum of ceil(k_g / 128) rows, mn], the groups' rows
+// concatenated (the reference's tests build them per group, tests/generators.py:413-435) -> packed UE8M0 ints
+// [sum of ceil(K blocks_g / 4) rows, aligned mn]: int (j, col) of group g holds the exponent bytes of the group's K
+// blocks 4j .. 4j+3 (zero past the group's end), so every group starts on an int boundary. One block row per group
+// (blockIdx.y); each block finds its group's first rows with a serial scan over ks (at most a few hundred groups).
+// Reference: transform_k_grouped_sf_into_required_layout, csrc/apis/layout.hpp (called from csrc/apis/gemm.hpp:335-336).
+__global__ void __launch_bounds__(256)
+dgb200_pack_k_grouped_sf_kernel(const float* __restrict__ sf, const int* __restrict__ ks, int mn, long long aligned_mn,
+                                uint32_t* __restrict__ out) {
+    const int g = blockIdx.y;
+    int kb0 = 0, kp0 = 0;
+    for (int i = 0; i < g; ++i) {
+        const int kb = ks[i] / 128;
+        kb0 += kb;
+        kp0 += (kb + 3) / 4;
+    }
+    const int num_kb = ks[g] / 128;
+    const int num_kp = (num_kb + 3) / 4;
+    for (long long i = blockIdx.x * 256ll + threadIdx.x; i < static_cast<long long>(num_kp) * mn; i += gridDim.x * 256ll) {
+        const int j = static_cast<int>(i / mn), col = static_cast<int>(i - static_cast<long long>(j) * mn);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int kb = j * 4 + b;
+            if (kb < num_kb)
+                packed |= ((__float_as_uint(sf[static_cast<long long>(kb0 + kb) * mn + col]) >> 23) & 0xffu) << (8 * b);
+        }
+        out[static_cast<long long>(kp0 + j) * aligned_mn + col] = packed;
+    }
+}
+
 }  // namespace dgb

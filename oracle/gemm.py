@@ -106,3 +106,19 @@ def bf16_grouped_gemm_masked(a, b, masked_m, out_dtype=torch.bfloat16):
             d[g, :rows] = a[g, :rows].float() @ b[g].float().T
             mask[g, :rows] = True
     return d.to(out_dtype), mask
+
+
+def k_grouped_gemm(a_q, a_sf, b_q, b_sf, c, ks, gran_k=128):
+    """d[g] = c[g] + deq(A_g).T @ deq(B_g) for the K-grouped layout: a_q e4m3 [sum_k, m] with a_sf fp32
+    [sum_k / gran_k, m] (one scale per gran_k K rows and channel, groups concatenated), likewise b; ks = K rows per group.
+    The reference checks its kernel against the unquantised product (tests/generators.py:449-453,
+    tests/test_fp8_fp4.py:186-230); here the dequantised operands are multiplied, as in the other GEMM oracles."""
+    a = a_q.float() * a_sf.repeat_interleave(gran_k, dim=0)
+    b = b_q.float() * b_sf.repeat_interleave(gran_k, dim=0)
+    d = c.clone().float()
+    start = 0
+    for g, k in enumerate(ks):
+        if k > 0:
+            d[g] += a[start:start + k].T @ b[start:start + k]
+        start += k
+    return d
