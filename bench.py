@@ -43,7 +43,8 @@ def parse_args():
     ap.add_argument('--skip-cpu-baseline', action='store_true')
     ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
                     help='nvfp4xnvfp4 runs the NVFP4 prefill variant (16384 tokens) instead of the headline workload')
-    ap.add_argument('--workload', default='layer', choices=['layer', 'gemm_contiguous', 'gemm_masked'],
+    ap.add_argument('--workload', default='layer', choices=['layer', 'gemm_contiguous', 'gemm_masked', 'bf16_gemm_contiguous', 'bf16_gemm_masked',
+                                                            'bf16_gemm_dense', 'bf16_layer', 'k_grouped_gemm'],
                     help='gemm_contiguous / gemm_masked time the stand-alone grouped GEMMs of BASELINE configs 1 and 2 '
                          '(one GPU, not the headline line)')
     return ap.parse_args()
@@ -329,6 +330,108 @@ def run_gemm_workload(args):
     }), flush=True)
 
 
+def measured_bf16_tflops():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)['bf16_tflops']), 'measured'
+    return 1590.0, 'fallback'
+
+
+def run_family_workload(args):
+    """Stand-alone timings of the operators next to the headline path: the BF16 family and the K-grouped FP8 GEMM.
+    Shapes: bf16_gemm_contiguous 8 groups x 4096 rows, N 4096, K 7168; bf16_gemm_masked 32 groups x 64 of 256 rows, N 4096,
+    K 7168; bf16_gemm_dense 8192^3; bf16_layer 4096 tokens, 64 experts, top-8, hidden 7168, intermediate 2048;
+    k_grouped_gemm 8 groups, m 4096, n 7168, 4096 K rows per group (FP32 accumulation into d). Inputs are larger than L2
+    except where a 512 MB flush is stated; times are CUDA events over all timed launches."""
+    import torch
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+    torch.manual_seed(0)
+    w = args.workload
+    hbm_peak, hbm_kind = measured_peaks()
+    tf_peak, tf_kind = measured_bf16_tflops()
+    bound, flops, nbytes, dtype, extra = 'tensor', 0.0, 0.0, 'bf16 (fp32 accumulate)', {}
+    rb = lambda *shape: torch.randn(*shape, device='cuda').bfloat16()
+    if w == 'bf16_gemm_contiguous':
+        g, mg, n, k = 8, 4096, 4096, 7168
+        a, b, d = rb(g * mg, k), rb(g, n, k), torch.empty(g * mg, n, device='cuda', dtype=torch.bfloat16)
+        layout = torch.arange(g, device='cuda', dtype=torch.int32).repeat_interleave(mg)
+        call = lambda: dg.m_grouped_bf16_gemm_nt_contiguous(a, b, d, layout)
+        flops, nbytes = 2.0 * g * mg * n * k, 2.0 * (a.numel() + b.numel() + d.numel())
+        extra = {'groups': g, 'rows_per_group': mg, 'n': n, 'k': k}
+    elif w == 'bf16_gemm_masked':
+        g, mm, n, k, rows = 32, 256, 4096, 7168, 64
+        a, b, d = rb(g, mm, k), rb(g, n, k), torch.empty(g, mm, n, device='cuda', dtype=torch.bfloat16)
+        masked = torch.full((g,), rows, device='cuda', dtype=torch.int32)
+        call = lambda: dg.m_grouped_bf16_gemm_nt_masked(a, b, d, masked, rows)
+        bound, flops = 'hbm', 2.0 * g * rows * n * k
+        nbytes = 2.0 * (b.numel() + g * rows * (k + n))
+        extra = {'groups': g, 'valid_rows_per_group': rows, 'n': n, 'k': k}
+    elif w == 'bf16_gemm_dense':
+        m = n = k = 8192
+        a, b, d = rb(m, k), rb(n, k), torch.empty(m, n, device='cuda', dtype=torch.bfloat16)
+        call = lambda: dg.bf16_gemm_nt(a, b, d)
+        flops, nbytes = 2.0 * m * n * k, 2.0 * (a.numel() + b.numel() + d.numel())
+        extra = {'m': m, 'n': n, 'k': k}
+    elif w == 'bf16_layer':
+        t, h, i, e, topk = 4096, 7168, 2048, 64, 8
+        buf = dg.get_symm_buffer_for_mega_moe(None, e, t, topk, h, i, mma_type='bf16xbf16')
+        buf.x.copy_(rb(t, h))
+        dg.route_sigmoid_topk(torch.randn(t, e, device='cuda'), topk, buf.topk_idx, buf.topk_weights)
+        w1 = (torch.randn(e, 2 * i, h, device='cuda') * 0.02).bfloat16()
+        l1, l2 = dg.transform_weights_for_mega_moe(w1, (torch.randn(e, h, i, device='cuda') * 0.02).bfloat16())
+        del w1
+        y = torch.empty(t, h, device='cuda', dtype=torch.bfloat16)
+        call = lambda: dg.bf16_mega_moe(y, l1, l2, buf)
+        flops = 2.0 * t * topk * h * i * 3
+        nbytes = 2.0 * (l1.numel() + l2.numel()) + t * topk * (2 * h * 2 + 2 * i * 2) + t * h * 2 * (2 + topk)
+        extra = {'tokens': t, 'hidden': h, 'intermediate': i, 'experts': e, 'topk': topk, 'tokens_per_s': None}
+    else:  # k_grouped_gemm
+        g, m, n, kg = 8, 4096, 7168, 4096
+        ks = [kg] * g
+        a = torch.randn(g * kg, m, device='cuda').to(torch.float8_e4m3fn)
+        b = torch.randn(g * kg, n, device='cuda').to(torch.float8_e4m3fn)
+        sfa, sfb = torch.ones(g * kg // 128, m, device='cuda'), torch.ones(g * kg // 128, n, device='cuda')
+        d = torch.zeros(g, m, n, device='cuda')
+        layout = torch.tensor(ks, dtype=torch.int32, device='cuda')
+        call = lambda: dg.k_grouped_fp8_gemm_tn_contiguous((a, sfa), (b, sfb), d, ks, layout, c=d)
+        flops, nbytes = 2.0 * g * kg * m * n, float(a.numel() + b.numel() + 2 * d.numel() * 4)
+        dtype, tf_peak, tf_kind = 'fp8 e4m3 (fp32 accumulate)', 4500.0, 'nominal dense FP8'
+        extra = {'groups': g, 'm': m, 'n': n, 'k_per_group': kg}
+    for _ in range(max(args.warmup, 3)):
+        call()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    status = _lib.device_status()
+    assert status[0] == 0, status
+    ms_per = e0.elapsed_time(e1) / args.steps
+    tflops = flops / (ms_per * 1e-3) / 1e12
+    gbs = nbytes / (ms_per * 1e-3) / 1e9
+    if 'tokens_per_s' in extra:
+        extra['tokens_per_s'] = extra['tokens'] / (ms_per * 1e-3)
+    extra['workload'] = w
+    extra['l2_policy'] = 'inputs larger than L2'
+    roofline = ({'bound': 'hbm', 'achieved': gbs, 'peak': hbm_peak, 'unit': 'GB/s', 'frac': gbs / hbm_peak, 'peak_source': hbm_kind}
+                if bound == 'hbm' else
+                {'bound': 'tensor', 'achieved': tflops, 'peak': tf_peak, 'unit': 'TFLOP/s', 'frac': tflops / tf_peak, 'peak_source': tf_kind})
+    roofline.update({'kernel': 'dgb200_grouped_gemm_kernel', 'traffic': None, 'algorithmic_bytes': nbytes})
+    print(json.dumps({
+        'metric': 'kernel_us', 'value': ms_per * 1e3, 'unit': 'us', 'n_gpus': 1, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': ms_per, 'higher_is_better': False, 'scaling': 'weak', 'vs_baseline': None, 'dtype': dtype,
+        'data': 'synthetic', 'config': extra, 'gpu_launches': args.steps, 'clocks': clocks, 'tflops': tflops, 'gbs': gbs,
+        'roofline': roofline,
+    }), flush=True)
+
+
 def run_ours(args, cfg, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -540,7 +643,10 @@ def main():
     if args.workload != 'layer':
         if args.impl == 'reference' or args.gpus != 1:
             raise SystemExit('--workload gemm_* is a single-GPU timing of our kernels only')
-        run_gemm_workload(args)
+        if args.workload in ('gemm_contiguous', 'gemm_masked'):
+            run_gemm_workload(args)
+        else:
+            run_family_workload(args)
         return
     if args.impl == 'reference':
         if args.mma != 'fp8xfp4':

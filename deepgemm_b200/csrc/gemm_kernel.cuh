@@ -128,7 +128,7 @@ __device__ __forceinline__ bool group_selected(const GemmParams& p, int rows) {
     return p.rows_skip ? !inside : inside;
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, bool kKGrouped = false>
 struct TileScheduler {
     const GemmParams& p;
     const GroupTable tab;
@@ -170,7 +170,7 @@ struct TileScheduler {
 
     // Returns false when this CTA has no more tiles. A tile with group < 0 must be skipped by every role.
     __device__ bool next(Tile& t) {
-        if (p.mode == kModeKGrouped) {
+        if constexpr (kKGrouped) {
             // every group has the same (m blocks x n blocks) output tiles; the table holds (K blocks, first K row,
             // first packed scale row) per group
             const int per_group = (p.m + 127) / 128 * num_n_blocks;
@@ -365,7 +365,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     } else if (cache_groups) {
         for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) {
             int start, rows, rows_store;
-            TileScheduler<BLOCK_N>::group_extent(p, p.layout, i, start, rows, rows_store);
+            TileScheduler<BLOCK_N, EPI == kEpiF32Acc>::group_extent(p, p.layout, i, start, rows, rows_store);
             group_cache[i] = __ldg(p.layout + i);
             group_start[i] = start;
             group_tiles_end[i] = group_selected(p, rows) ? (max(rows, rows_store) + 127) / 128 * (p.n / BLOCK_N) : 0;
@@ -412,7 +412,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // instructions take their descriptors from uniform registers, which a single-lane (divergent) loop would
         // have to refill through slow register-to-uniform moves for every instruction.
         {
-            TileScheduler<BLOCK_N> sched(p, group_layout);
+            TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -448,7 +448,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     } else if (warp == 3) {
         // ---------------------------------------------------------------- loader: B (weight) tile + its scale factors
         {
-            TileScheduler<BLOCK_N> sched(p, group_layout);
+            TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -490,7 +490,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // ---------------------------------------------------------------- MMA issuer
         // Warp-uniform loop, one elected lane issues (see the loader above).
         {
-        TileScheduler<BLOCK_N> sched(p, group_layout);
+        TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
         int trace_i = 0;
@@ -588,7 +588,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     } else if (warp == 2) {
         // ---------------------------------------------------------------- scale-factor transposer
         // tcgen05.cp 32x128b wants, per 128 rows, 32 rows x 4 words with word j of row r = source row r + 32 j.
-        TileScheduler<BLOCK_N> sched(p, group_layout);
+        TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
         Tile t;
         uint32_t stage = 0, phase = 0;
         int trace_i = 0;
@@ -638,7 +638,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             }
         }
         if (kCpByHelper && p.sf_transposed != 0) {
-            TileScheduler<BLOCK_N> cp_sched(p, group_layout);
+            TileScheduler<BLOCK_N, EPI == kEpiF32Acc> cp_sched(p, group_layout);
             const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
             const bool leader = elect_one();
             stage = 0;
@@ -669,7 +669,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             // of the loads and prefetches the weight rows into L2 with plain
             // prefetch instructions. Weight tiles are read once from HBM and the stages that fit in shared memory do
             // not cover that latency; TMA prefetches would, but they cost the TMA unit a box row per cycle.
-            TileScheduler<BLOCK_N> pf_sched(p, group_layout);
+            TileScheduler<BLOCK_N, EPI == kEpiF32Acc> pf_sched(p, group_layout);
             Tile pt;
             int pf_kb = 0;
             bool pf_valid = false;
@@ -721,7 +721,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // Each thread first drains its half row of the accumulator into registers and releases the accumulator, so
         // the MMA issuer can start the next tile while the arithmetic and the stores below run.
         constexpr int kCols = BLOCK_N / 2;  // accumulator columns per thread
-        TileScheduler<BLOCK_N> sched(p, group_layout);
+        TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
         Tile t;
         uint32_t iter = 0;
         const uint32_t q = warp & 3, half = (warp - 4) >> 2;
