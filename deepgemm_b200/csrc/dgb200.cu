@@ -1282,7 +1282,13 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
     p.alignment = 128;
     p.gran_a = p.gran_b = 128;
     p.b_fmt = kFmtE4M3;
-    p.b_tx_bytes = 128 * 128;
+    // Wide tiles halve the shared-memory fill per MMA cycle, which bounds the 128-wide tile (measured 1.29 -> 1.40 PFLOP/s
+    // at 32 K blocks per group); with short K extents the FP32 epilogue dominates and the 128-wide tile's two
+    // accumulators, which let it overlap the next tile's MMAs, win instead.
+    const int block_n = tuning().block_n != 0 ? tuning().block_n
+                                              : ((n % 256 == 0 && sum_k / 128 / num_groups >= 16) ? 256 : 128);
+    DGB_REQUIRE(n % block_n == 0, "block_n %d does not divide n %d", block_n, n);
+    p.b_tx_bytes = block_n * 128;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a, static_cast<uint64_t>(m), static_cast<uint64_t>(sum_k),
                                 static_cast<uint64_t>(m), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1294,13 +1300,16 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
                             static_cast<uint64_t>(kp_rows), static_cast<uint64_t>(aligned_m) * 4, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, sfb_packed, static_cast<uint64_t>(aligned_n),
-                            static_cast<uint64_t>(kp_rows), static_cast<uint64_t>(aligned_n) * 4, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+                            static_cast<uint64_t>(kp_rows), static_cast<uint64_t>(aligned_n) * 4, static_cast<uint32_t>(block_n), 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     int sms = 0;
     rc = effective_num_sms(&sms);
     if (rc) return rc;
-    const long long tiles = static_cast<long long>(num_groups) * ((m + 127) / 128) * (n / 128);
+    const long long tiles = static_cast<long long>(num_groups) * ((m + 127) / 128) * (n / block_n);
     const int grid = static_cast<int>(std::min<long long>(sms, tiles));
+    // the wide tile halves the shared-memory fill per MMA cycle (the 128-wide one is bound by it)
+    if (block_n == 256) return launch_gemm<256, 4, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_a, p, grid, stream);
     return launch_gemm<128, 6, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_a, p, grid, stream);
 }
 

@@ -469,10 +469,13 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     if (leader) {
                         trace_point(p, 9, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes) + (load_sfb ? L::kSfbBytes : 0));
-                        if constexpr (kKG)
-                            tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, t.n_block * BLOCK_N,
-                                        t.k_row_start + kb * 128);
-                        else if (!DGB_SKIP(p, 2))
+                        if constexpr (kKG) {
+                            // one box per 128 channels of N (a 128-byte swizzle span), 16 KB apart in the stage
+#pragma unroll
+                            for (int h = 0; h < BLOCK_N / 128; ++h)
+                                tma_load_2d(smem + L::kOffB + stage * L::kBBytes + h * 16384, &tm_b, full_bar + stage,
+                                            t.n_block * BLOCK_N + h * 128, t.k_row_start + kb * 128);
+                        } else if (!DGB_SKIP(p, 2))
                             tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * kTmaXPerKb, b_row);
                         if (load_sfb)
                             tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
@@ -551,7 +554,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     }
                     const uint64_t adesc = kKG ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, L::kABytes)
                                                : make_kmajor_sw128_desc(a_base + stage * L::kABytes);
-                    const uint64_t bdesc = kKG ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, L::kBBytes)
+                    const uint64_t bdesc = kKG ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, 16384)
                                                : make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
                     // K-major: +32 bytes along K inside the swizzle span per MMA; MN-major: 32 K rows = 4 groups of 1024 B
                     constexpr uint32_t kDescStep = kKG ? 256 : 2;
