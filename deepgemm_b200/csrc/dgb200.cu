@@ -117,29 +117,31 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
 
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     int rc = 0;
-    if (!bf16)
-    rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
+    if (!bf16) {
+        rc = make_tensor_map_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfa, static_cast<uint64_t>(c.sfa_k_stride),
                                 static_cast<uint64_t>(packed_k_a) * c.num_groups_a,
                                 static_cast<uint64_t>(c.sfa_k_stride) * 4, 128, sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc) return rc;
+        if (rc) return rc;
+    }
     // Wide N tiles give each tcgen05.mma enough work (128 x 256 x 32) to cover the per-K-block issue chain.
     const bool swiglu = c.epilogue == kEpiSwiGLU || c.epilogue == kEpiSwiGLUNvfp4 || c.epilogue == kEpiSwiGLUBf16;
     // the SwiGLU epilogues pair the two 128-channel halves of a 256-wide tile (gate | up)
     DGB_REQUIRE(!swiglu || p.n % 256 == 0, "the gate/up GEMM needs n (%d) to be a multiple of 256", p.n);
     const int block_n = swiglu ? 256 : (tuning().block_n != 0 ? tuning().block_n : (p.n % 256 == 0 ? 256 : 128));
     DGB_REQUIRE((block_n == 128 || block_n == 256) && p.n % block_n == 0, "block_n %d does not divide n %d", block_n, p.n);
-    if (!bf16)
-    rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
-                            static_cast<uint64_t>(packed_k_b) * p.num_groups, static_cast<uint64_t>(c.sfb_k_stride) * 4,
-                            static_cast<uint32_t>(block_n), sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc) return rc;
+    if (!bf16) {
+        rc = make_tensor_map_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, c.sfb, static_cast<uint64_t>(c.sfb_k_stride),
+                                static_cast<uint64_t>(packed_k_b) * p.num_groups, static_cast<uint64_t>(c.sfb_k_stride) * 4,
+                                static_cast<uint32_t>(block_n), sf_box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+    }
     const uint64_t a_row_bytes = nvfp4 ? p.k / 2 : p.k;  // packed E2M1 or E4M3
     if (bf16)
         rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c.a, static_cast<uint64_t>(p.k),
                                 static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(c.a_row_stride_bytes), 64, 128,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     else
-    rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, a_row_bytes,
+        rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.a, a_row_bytes,
                                 static_cast<uint64_t>(c.a_rows_total), a_row_bytes, 128, 128,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
@@ -178,7 +180,13 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     // NVFP4: only the BF16 epilogue (the down GEMM: few K blocks per tile, so its store burst weighs most) trades a
     // pipeline stage for the staging buffers.
     const bool nvfp4_staged = nvfp4 && block_n == 256 && c.epilogue == kEpiBF16;
-    if (block_n == 256 && ((!nvfp4 && (c.epilogue == kEpiBF16 || c.epilogue == kEpiSwiGLU)) || nvfp4_staged) &&
+    if (block_n == 256 && c.epilogue == kEpiSwiGLUBf16) {
+        rc = make_tensor_map_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.act_q, static_cast<uint64_t>(p.n / 2),
+                                static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(p.act_q_row_stride), 32, 32,
+                                CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc) return rc;
+        p.tma_store = c.whole_tile_stores ? 2 : 1;
+    } else if (block_n == 256 && ((!nvfp4 && (c.epilogue == kEpiBF16 || c.epilogue == kEpiSwiGLU)) || nvfp4_staged) &&
         (static_cast<long long>(p.d_row_stride) * 2) % 16 == 0) {
         if (c.epilogue == kEpiBF16)
             rc = make_tensor_map_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.d, static_cast<uint64_t>(p.n),
@@ -775,9 +783,9 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
     // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
     if (sf_per_row > 0)
-    dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
-        reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
-        reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows));
+        dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
+            reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
+            reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows));
     DGB_CUDA(cudaGetLastError());
     if ((rc = record_stage(2, stream))) return rc;
 

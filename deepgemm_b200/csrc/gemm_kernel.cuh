@@ -811,6 +811,55 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     __syncwarp();
                 }
             }
+            if constexpr (EPI == kEpiSwiGLUBf16) {
+                // Same column order and arithmetic as the FP8 form below, the outputs stay BF16 (reference:
+                // deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:927-955). One 32-output group is one
+                // 32 x 64-byte slab of the warp: staged in shared memory and stored by TMA like the BF16 epilogue's, or
+                // written row by row where the tile's tail rows must stay untouched.
+                if (warp_has_rows) {
+                    const float w = (p.row_weight != nullptr && (store || via_tma)) ? __ldg(p.row_weight + row) : 1.0f;
+#pragma unroll
+                    for (int c = 0; c < kCols / 64; ++c) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float o[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                float gv = bf16_round(__uint_as_float(acc[c * 32 + i * 2 + h]));
+                                float uv = bf16_round(__uint_as_float(acc[kCols / 2 + c * 32 + i * 2 + h]));
+                                if (p.clamp > 0.0f) {
+                                    gv = fminf(gv, p.clamp);
+                                    uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                                }
+                                const float silu = p.fast_math ? gv * rcp_approx(1.0f + __expf(-gv))
+                                                               : gv / (1.0f + expf(-gv));
+                                o[h] = silu * uv * w;
+                            }
+                            packed[i] = pack_bf16x2(o[0], o[1]);
+                        }
+                        const int j = t.n_block * (BLOCK_N / 2) + static_cast<int>(half) * (kCols / 2) + c * 32;
+                        if (via_tma) {
+                            if (lane == 0) bulk_wait_group_read_all();  // the previous slab has left the staging buffer
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                *stage_chunk(i) = make_uint4(packed[i * 4], packed[i * 4 + 1], packed[i * 4 + 2], packed[i * 4 + 3]);
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_2d(&tm_out, stage_buf, j, t.row_start + static_cast<int>(q) * 32);
+                                bulk_commit_group();
+                            }
+                        } else if (store) {
+                            unsigned char* dst = p.act_q + row * p.act_q_row_stride + j * 2;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                st_global_v4(dst + i * 16, packed[i * 4], packed[i * 4 + 1], packed[i * 4 + 2], packed[i * 4 + 3]);
+                        }
+                    }
+                }
+            }
             if (store) {
                 if constexpr (EPI == kEpiBF16 || EPI == kEpiF32) {
                     const long long col0 = static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
@@ -890,35 +939,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         st_global_v4(p.act_q + row * p.act_q_row_stride + j / 2, packed[0], packed[1], packed[2], packed[3]);
                     }
                 } else if constexpr (EPI == kEpiSwiGLUBf16) {
-                    // Same column order and arithmetic as the FP8 form below, the outputs stay BF16 (reference:
-                    // deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:927-955).
-                    const float w = p.row_weight != nullptr ? __ldg(p.row_weight + row) : 1.0f;
-#pragma unroll
-                    for (int c = 0; c < kCols / 64; ++c) {
-                        uint32_t packed[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float o[2];
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                float gv = bf16_round(__uint_as_float(acc[c * 32 + i * 2 + h]));
-                                float uv = bf16_round(__uint_as_float(acc[kCols / 2 + c * 32 + i * 2 + h]));
-                                if (p.clamp > 0.0f) {
-                                    gv = fminf(gv, p.clamp);
-                                    uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
-                                }
-                                const float silu = p.fast_math ? gv * rcp_approx(1.0f + __expf(-gv))
-                                                               : gv / (1.0f + expf(-gv));
-                                o[h] = silu * uv * w;
-                            }
-                            packed[i] = pack_bf16x2(o[0], o[1]);
-                        }
-                        const int j = t.n_block * (BLOCK_N / 2) + static_cast<int>(half) * (kCols / 2) + c * 32;
-                        unsigned char* dst = p.act_q + row * p.act_q_row_stride + j * 2;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            st_global_v4(dst + i * 16, packed[i * 4], packed[i * 4 + 1], packed[i * 4 + 2], packed[i * 4 + 3]);
-                    }
+                    // handled above, warp-uniformly (its staged stores need the whole warp)
                 } else {
                     // acc[0, kCols / 2) are gate channels, acc[kCols / 2, kCols) the matching up channels (see the drain
                     // above); one 32-wide output group = one UE8M0 scale.
