@@ -24,7 +24,7 @@ from .gemm import (  # noqa: F401
     m_grouped_fp8_gemm_nt_contiguous,
     m_grouped_fp8_gemm_nt_masked,
 )
-from .kgrouped import k_grouped_fp8_gemm_tn_contiguous  # noqa: F401
+from .kgrouped import k_grouped_bf16_gemm_tn_contiguous, k_grouped_fp8_gemm_tn_contiguous  # noqa: F401
 from .layout import (  # noqa: F401
     get_mn_major_tma_aligned_packed_ue8m0_tensor,
     get_tma_aligned_size,

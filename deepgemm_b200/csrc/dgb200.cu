@@ -1321,6 +1321,52 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
     return launch_gemm<128, 6, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_a, p, grid, stream);
 }
 
+int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const float* c, float* d, const int32_t* ks,
+                                             int32_t num_groups, int32_t m, int32_t n, int32_t sum_k, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DGB_REQUIRE(num_groups > 0 && num_groups <= kMaxCachedGroups, "num_groups must be in [1, %d]", kMaxCachedGroups);
+    DGB_REQUIRE(m > 0 && m % 8 == 0 && n > 0 && n % 128 == 0, "m (%d) must be a positive multiple of 8 and n (%d) of 128", m, n);
+    DGB_REQUIRE(sum_k >= 0 && sum_k % 64 == 0, "the K extents must be multiples of 64 (sum %d)", sum_k);
+    DGB_REQUIRE(c != nullptr && d != nullptr && ks != nullptr, "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0, "c and d must be 16-byte aligned");
+    if (sum_k == 0) {
+        if (c != d) DGB_CUDA(cudaMemcpyAsync(d, c, static_cast<size_t>(num_groups) * m * n * 4, cudaMemcpyDeviceToDevice, stream));
+        return 0;
+    }
+    DGB_REQUIRE(a != nullptr && b != nullptr, "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0, "a and b must be 16-byte aligned");
+    GemmParams p{};
+    p.d = d;
+    p.c = c;
+    p.d_row_stride = n;
+    p.layout = ks;
+    p.mode = kModeKGrouped;
+    p.m = m;
+    p.n = n;
+    p.k = sum_k;
+    p.num_groups = num_groups;
+    p.alignment = 128;
+    p.gran_a = p.gran_b = 32;
+    p.sf_transposed = 1;
+    const int block_n = tuning().block_n != 0 ? tuning().block_n : ((n % 256 == 0 && sum_k / 64 / num_groups >= 16) ? 256 : 128);
+    DGB_REQUIRE(n % block_n == 0, "block_n %d does not divide n %d", block_n, n);
+    p.b_tx_bytes = block_n * 128;
+    CUtensorMap tm_a, tm_b;
+    int rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, static_cast<uint64_t>(m), static_cast<uint64_t>(sum_k),
+                                static_cast<uint64_t>(m) * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, static_cast<uint64_t>(n), static_cast<uint64_t>(sum_k),
+                            static_cast<uint64_t>(n) * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    int sms = 0;
+    rc = effective_num_sms(&sms);
+    if (rc) return rc;
+    const long long tiles = static_cast<long long>(num_groups) * ((m + 127) / 128) * (n / block_n);
+    const int grid = static_cast<int>(std::min<long long>(sms, tiles));
+    if (block_n == 256) return launch_gemm<256, 4, kEpiF32Acc, kKindBf16>(tm_a, tm_b, tm_a, tm_a, tm_a, p, grid, stream);
+    return launch_gemm<128, 6, kEpiF32Acc, kKindBf16>(tm_a, tm_b, tm_a, tm_a, tm_a, p, grid, stream);
+}
+
 int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t experts, int32_t topk, int64_t* topk_idx,
                               float* topk_weights, void* stream) {
     DGB_REQUIRE(logits != nullptr && topk_idx != nullptr && topk_weights != nullptr, "null tensor pointer");

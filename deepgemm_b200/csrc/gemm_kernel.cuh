@@ -351,14 +351,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     if constexpr (kKG) {
         // (K blocks, first K row, first packed scale row) per group: a serial scan by one thread (at most
         // kMaxCachedGroups groups, checked by the host)
-        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) group_cache[i] = __ldg(p.layout + i) / 128;
+        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) group_cache[i] = __ldg(p.layout + i) / kBlockK;
         __syncthreads();
         if (threadIdx.x == 0) {
             int k_row = 0, kp = 0;
             for (int i = 0; i < p.num_groups; ++i) {
                 group_start[i] = k_row;
                 group_tiles_end[i] = kp;
-                k_row += group_cache[i] * 128;
+                k_row += group_cache[i] * kBlockK;
                 kp += (group_cache[i] + 3) / 4;
             }
         }
@@ -428,10 +428,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     if (elect_one()) {
                         trace_point(p, 0, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) + (load_sfa ? L::kSfaBytes : 0));
-                        if constexpr (kKG)
-                            tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, t.row_start,
-                                        t.k_row_start + kb * 128);
-                        else if (!DGB_SKIP(p, 1))
+                        if constexpr (kKG) {
+                            // MN-major A: one box per 128 bytes of M (128 E4M3 or 64 BF16 channels) x kBlockK K rows
+                            constexpr int kBoxes = kKind == kKindBf16 ? 2 : 1;
+#pragma unroll
+                            for (int h = 0; h < kBoxes; ++h)
+                                tma_load_2d(smem + L::kOffA + stage * L::kABytes + h * (L::kABytes / kBoxes), &tm_a,
+                                            full_bar + stage, t.row_start + h * (128 / kBoxes), t.k_row_start + kb * kBlockK);
+                        } else if (!DGB_SKIP(p, 1))
                             tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * kTmaXPerKb,
                                         t.row_start);
                         if (load_sfa)
@@ -470,11 +474,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         trace_point(p, 9, trace_i);
                         mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes) + (load_sfb ? L::kSfbBytes : 0));
                         if constexpr (kKG) {
-                            // one box per 128 channels of N (a 128-byte swizzle span), 16 KB apart in the stage
+                            // one box per 128 bytes of N (a swizzle span: 128 E4M3 or 64 BF16 channels) x kBlockK K rows
+                            constexpr int kChan = kKind == kKindBf16 ? 64 : 128;
 #pragma unroll
-                            for (int h = 0; h < BLOCK_N / 128; ++h)
-                                tma_load_2d(smem + L::kOffB + stage * L::kBBytes + h * 16384, &tm_b, full_bar + stage,
-                                            t.n_block * BLOCK_N + h * 128, t.k_row_start + kb * 128);
+                            for (int h = 0; h < BLOCK_N / kChan; ++h)
+                                tma_load_2d(smem + L::kOffB + stage * L::kBBytes + h * (128 * kBlockK), &tm_b, full_bar + stage,
+                                            t.n_block * BLOCK_N + h * kChan, t.k_row_start + kb * kBlockK);
                         } else if (!DGB_SKIP(p, 2))
                             tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * kTmaXPerKb, b_row);
                         if (load_sfb)
@@ -498,7 +503,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         uint32_t stage = 0, phase = 0, iter = 0;
         int trace_i = 0;
         const uint32_t idesc = kKG
-            ? (make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, 128, BLOCK_N, kScaleUE8M0) | (1u << 15) | (1u << 16))  // both MN-major
+            ? ((kKind == kKindBf16 ? make_idesc_bf16_f32(128, BLOCK_N)
+                                   : make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, 128, BLOCK_N, kScaleUE8M0)) |
+               (1u << 15) | (1u << 16))  // both operands MN-major
             : kKind == kKindBf16
             ? make_idesc_bf16_f32(128, BLOCK_N)
             : kKind == kKindNvfp4 ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
@@ -552,12 +559,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                 tcgen05_cp_32x128b_warpx4(tmem_sfb + b * 4, make_sf_desc(sfb_smem + stage * L::kSfbBytes + b * 512));
                         }
                     }
-                    const uint64_t adesc = kKG ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, L::kABytes)
+                    // MN-major tiles: consecutive 128-byte chunks along M / N are one TMA box (128 bytes x kBlockK rows) apart
+                    const uint64_t adesc = kKG ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, 128 * kBlockK)
                                                : make_kmajor_sw128_desc(a_base + stage * L::kABytes);
-                    const uint64_t bdesc = kKG ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, 16384)
+                    const uint64_t bdesc = kKG ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, 128 * kBlockK)
                                                : make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
-                    // K-major: +32 bytes along K inside the swizzle span per MMA; MN-major: 32 K rows = 4 groups of 1024 B
-                    constexpr uint32_t kDescStep = kKG ? 256 : 2;
+                    // K-major: +32 bytes along K inside the swizzle span per MMA; MN-major: the K rows of one MMA (32 E4M3 or
+                    // 16 BF16) are 4 or 2 groups of 8 rows = 1024 B each
+                    constexpr uint32_t kDescStep = kKG ? (kKind == kKindBf16 ? 128 : 256) : 2;
                     trace_point(p, 12, trace_i);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
@@ -565,7 +574,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
                         if constexpr (kKind == kKindBf16) {
                             // K = 16 BF16 elements (32 bytes) per MMA
-                            tcgen05_mma_f16(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2, idesc, (kb | k4) != 0 ? 1u : 0u);
+                            tcgen05_mma_f16(tmem_acc, adesc + k4 * kDescStep, bdesc + k4 * kDescStep, idesc, (kb | k4) != 0 ? 1u : 0u);
                         } else if constexpr (kKind == kKindNvfp4) {
                             // K = 64 per MMA; its 4 scales per row are the 4 bytes of packed int k4 of the stage
                             tcgen05_mma_mxf4nvf4_4x(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2, idesc, tmem_sfa + k4 * 4,

@@ -131,6 +131,12 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
                                             float* d, const int32_t* ks, int32_t num_groups, int32_t m, int32_t n,
                                             int32_t sum_k, void* sf_workspace, void* stream);
 
+/* BF16 form of the K-grouped GEMM: a bf16 [sum_k, m], b bf16 [sum_k, n] (MN-major), every ks[g] a multiple of 64,
+ * m % 8 == 0, n % 128 == 0; c, d, ks as above; no scale factors, no workspace.
+ * Reference: k_grouped_bf16_gemm_tn_contiguous, csrc/apis/gemm.hpp:566-608 (plain ks layout). */
+int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const float* c, float* d, const int32_t* ks,
+                                             int32_t num_groups, int32_t m, int32_t n, int32_t sum_k, void* stream);
+
 /* BF16 rows -> E4M3 + one UE8M0 scale per gran_k (32 or 128) elements: sf = 2^ceil(log2(max(amax, 1e-4) / 448)),
  * q = e4m3_rn(x / sf). Reference: per_token_cast_to_fp8(use_ue8m0=True), deep_gemm/utils/math.py:26-49 (a torch
  * helper there; one fused kernel here).

@@ -74,3 +74,32 @@ def test_rejected_inputs(dg):
         dg.k_grouped_fp8_gemm_tn_contiguous(*args, [64], layout, c=d)
     with pytest.raises(RuntimeError):
         dg.k_grouped_fp8_gemm_tn_contiguous(*args, [128], layout, c=d, use_psum_layout=True)
+
+
+@pytest.mark.parametrize('ks,m,n', [
+    ([64], 128, 128),
+    ([192, 64, 640], 128, 256),
+    ([512, 0, 1088, 320], 256, 128),
+    ([64 * 5, 64 * 9], 200, 384),
+    ([4096, 2048], 512, 512),
+])
+def test_k_grouped_bf16_matches_oracle(dg, ks, m, n):
+    """BF16 form: the reference checks it against the torch product of the same tensors with calc_diff < 1e-5 ... here
+    the FP32 product of the BF16 operands."""
+    from deepgemm_b200 import _lib
+    torch.manual_seed(sum(ks) + n)
+    k = sum(ks)
+    a, b = torch.randn(k, m).bfloat16(), torch.randn(k, n).bfloat16()
+    c = torch.randn(len(ks), m, n) * 32
+    d = c.cuda()
+    layout = torch.tensor(ks, dtype=torch.int32, device='cuda')
+    dg.k_grouped_bf16_gemm_tn_contiguous(a.cuda(), b.cuda(), d, ks, layout, c=d)
+    assert _lib.device_status()[0] == 0
+    got, start = d.cpu(), 0
+    for g, kg in enumerate(ks):
+        if kg == 0:
+            assert torch.equal(got[g], c[g])
+        else:
+            want = a[start:start + kg].float().T @ b[start:start + kg].float()
+            assert quant.calc_diff(got[g] - c[g], want) < 1e-5
+        start += kg
