@@ -1245,17 +1245,21 @@ int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, 
 
 int64_t dgb200_k_grouped_sf_workspace_bytes(int32_t num_groups, int32_t m, int32_t n, int32_t sum_k) {
     if (num_groups <= 0 || m <= 0 || n <= 0 || sum_k < 0) return 0;
-    const long long rows = sum_k / 128 / 4 + num_groups;  // every group rounds its K blocks up to a multiple of 4
+    const long long rows = sum_k / 128 / 4 + 2ll * num_groups;  // every group rounds its K blocks up to a multiple of 4
     return rows * ((static_cast<long long>(m) + 3) / 4 * 4 + (static_cast<long long>(n) + 3) / 4 * 4) * 4;
 }
 
-int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, const void* b, const float* sfb, const float* c,
-                                            float* d, const int32_t* ks, int32_t num_groups, int32_t m, int32_t n,
-                                            int32_t sum_k, void* sf_workspace, void* stream_) {
+int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int32_t sf_rows, const void* b, const float* sfb,
+                                            const float* c, float* d, const int32_t* ks, int32_t use_psum_layout,
+                                            int32_t k_alignment, int32_t num_groups, int32_t m, int32_t n, int32_t sum_k,
+                                            void* sf_workspace, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     DGB_REQUIRE(num_groups > 0 && num_groups <= kMaxCachedGroups, "num_groups must be in [1, %d]", kMaxCachedGroups);
     DGB_REQUIRE(m > 0 && m % 16 == 0 && n > 0 && n % 128 == 0, "m (%d) must be a positive multiple of 16 and n (%d) of 128", m, n);
-    DGB_REQUIRE(sum_k >= 0 && sum_k % 128 == 0, "the K extents must be multiples of 128 (sum %d)", sum_k);
+    DGB_REQUIRE(sum_k >= 0 && sum_k % 128 == 0, "the K rows of a and b (%d) must be a multiple of 128", sum_k);
+    DGB_REQUIRE(!use_psum_layout || (k_alignment > 0 && k_alignment % 128 == 0),
+                "the psum layout needs a K alignment that is a multiple of 128, got %d", k_alignment);
+    DGB_REQUIRE(sf_rows >= 0, "sf_rows must be >= 0");
     DGB_REQUIRE(c != nullptr && d != nullptr && ks != nullptr, "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0, "c and d must be 16-byte aligned");
     if (sum_k == 0) {
@@ -1266,15 +1270,15 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0 &&
                     reinterpret_cast<uintptr_t>(sf_workspace) % 16 == 0,
                 "a, b and the workspace must be 16-byte aligned");
-    const long long kp_rows = sum_k / 128 / 4 + num_groups;
+    const long long kp_rows = sum_k / 128 / 4 + 2ll * num_groups;
     const long long aligned_m = (static_cast<long long>(m) + 3) / 4 * 4, aligned_n = (static_cast<long long>(n) + 3) / 4 * 4;
     uint32_t* sfa_packed = static_cast<uint32_t*>(sf_workspace);
     uint32_t* sfb_packed = sfa_packed + kp_rows * aligned_m;
     {
         const dim3 grid_a(static_cast<unsigned>(std::min<long long>((static_cast<long long>(sum_k / 128 / 4 + 1) * m + 255) / 256, 64)), num_groups);
-        dgb200_pack_k_grouped_sf_kernel<<<grid_a, 256, 0, stream>>>(sfa, ks, m, aligned_m, sfa_packed);
+        dgb200_pack_k_grouped_sf_kernel<<<grid_a, 256, 0, stream>>>(sfa, sf_rows, ks, use_psum_layout, k_alignment, m, aligned_m, sfa_packed);
         const dim3 grid_b(static_cast<unsigned>(std::min<long long>((static_cast<long long>(sum_k / 128 / 4 + 1) * n + 255) / 256, 64)), num_groups);
-        dgb200_pack_k_grouped_sf_kernel<<<grid_b, 256, 0, stream>>>(sfb, ks, n, aligned_n, sfb_packed);
+        dgb200_pack_k_grouped_sf_kernel<<<grid_b, 256, 0, stream>>>(sfb, sf_rows, ks, use_psum_layout, k_alignment, n, aligned_n, sfb_packed);
         DGB_CUDA(cudaGetLastError());
     }
     GemmParams p{};
@@ -1287,7 +1291,8 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
     p.n = n;
     p.k = sum_k;
     p.num_groups = num_groups;
-    p.alignment = 128;
+    p.alignment = use_psum_layout ? k_alignment : 128;
+    p.kg_psum = use_psum_layout ? 1 : 0;
     p.gran_a = p.gran_b = 128;
     p.b_fmt = kFmtE4M3;
     // Wide tiles halve the shared-memory fill per MMA cycle, which bounds the 128-wide tile (measured 1.29 -> 1.40 PFLOP/s
@@ -1322,11 +1327,14 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, con
 }
 
 int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const float* c, float* d, const int32_t* ks,
-                                             int32_t num_groups, int32_t m, int32_t n, int32_t sum_k, void* stream_) {
+                                             int32_t use_psum_layout, int32_t k_alignment, int32_t num_groups, int32_t m,
+                                             int32_t n, int32_t sum_k, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     DGB_REQUIRE(num_groups > 0 && num_groups <= kMaxCachedGroups, "num_groups must be in [1, %d]", kMaxCachedGroups);
     DGB_REQUIRE(m > 0 && m % 8 == 0 && n > 0 && n % 128 == 0, "m (%d) must be a positive multiple of 8 and n (%d) of 128", m, n);
-    DGB_REQUIRE(sum_k >= 0 && sum_k % 64 == 0, "the K extents must be multiples of 64 (sum %d)", sum_k);
+    DGB_REQUIRE(sum_k >= 0 && sum_k % 64 == 0, "the K rows of a and b (%d) must be a multiple of 64", sum_k);
+    DGB_REQUIRE(!use_psum_layout || (k_alignment > 0 && k_alignment % 64 == 0),
+                "the psum layout needs a K alignment that is a multiple of 64, got %d", k_alignment);
     DGB_REQUIRE(c != nullptr && d != nullptr && ks != nullptr, "null tensor pointer");
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0, "c and d must be 16-byte aligned");
     if (sum_k == 0) {
@@ -1345,7 +1353,8 @@ int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const
     p.n = n;
     p.k = sum_k;
     p.num_groups = num_groups;
-    p.alignment = 128;
+    p.alignment = use_psum_layout ? k_alignment : 128;
+    p.kg_psum = use_psum_layout ? 1 : 0;
     p.gran_a = p.gran_b = 32;
     p.sf_transposed = 1;
     const int block_n = tuning().block_n != 0 ? tuning().block_n : ((n % 256 == 0 && sum_k / 64 / num_groups >= 16) ? 256 : 128);

@@ -97,7 +97,25 @@ struct GemmParams {
     const float* b_scales;
     const float* out_scale;
     const float* c;  // kEpiF32Acc: accumulator input [G, m, n] (may alias d)
+    int kg_psum;     // kModeKGrouped: layout[g] is the end K row of group g (groups start at multiples of `alignment`,
+                     // the gap rows are zero) instead of its K extent
 };
+
+// K rows [start, start + len) of group `g` of a K-grouped operand; `prev_end` carries the running end between calls
+// made for g = 0, 1, ... in order.
+__device__ __forceinline__ void k_group_extent(const int* layout, int g, int psum, int alignment, int& prev_end, int& start,
+                                               int& len) {
+    const int v = layout[g];
+    if (psum) {
+        start = (prev_end + alignment - 1) / alignment * alignment;
+        len = max(v - start, 0);
+        prev_end = v;
+    } else {
+        start = prev_end;
+        len = v;
+        prev_end += v;
+    }
+}
 
 struct Tile {
     int row_start;     // first row in the flattened A / D
@@ -351,15 +369,16 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     if constexpr (kKG) {
         // (K blocks, first K row, first packed scale row) per group: a serial scan by one thread (at most
         // kMaxCachedGroups groups, checked by the host)
-        for (int i = threadIdx.x; i < p.num_groups; i += kGemmThreads) group_cache[i] = __ldg(p.layout + i) / kBlockK;
-        __syncthreads();
         if (threadIdx.x == 0) {
-            int k_row = 0, kp = 0;
+            int prev_end = 0, kp = 0;
             for (int i = 0; i < p.num_groups; ++i) {
-                group_start[i] = k_row;
+                int start, len;
+                k_group_extent(p.layout, i, p.kg_psum, p.alignment, prev_end, start, len);
+                const int blocks = (len + kBlockK - 1) / kBlockK;  // a partial last block reads the zero rows of the gap
+                group_cache[i] = blocks;
+                group_start[i] = start;
                 group_tiles_end[i] = kp;
-                k_row += group_cache[i] * kBlockK;
-                kp += (group_cache[i] + 3) / 4;
+                kp += (blocks + 3) / 4;
             }
         }
     } else if (cache_groups) {

@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include "gemm_kernel.cuh"  // k_group_extent
 #include "ptx.cuh"
 
 namespace dgb {
@@ -259,16 +260,19 @@ __global__ void __launch_bounds__(256) dgb200_cast_rows_nvfp4_kernel(const CastN
 // (blockIdx.y); each block finds its group's first rows with a serial scan over ks (at most a few hundred groups).
 // Reference: transform_k_grouped_sf_into_required_layout, csrc/apis/layout.hpp (called from csrc/apis/gemm.hpp:335-336).
 __global__ void __launch_bounds__(256)
-dgb200_pack_k_grouped_sf_kernel(const float* __restrict__ sf, const int* __restrict__ ks, int mn, long long aligned_mn,
-                                uint32_t* __restrict__ out) {
+dgb200_pack_k_grouped_sf_kernel(const float* __restrict__ sf, int sf_rows, const int* __restrict__ ks, int psum, int alignment,
+                                int mn, long long aligned_mn, uint32_t* __restrict__ out) {
     const int g = blockIdx.y;
-    int kb0 = 0, kp0 = 0;
-    for (int i = 0; i < g; ++i) {
-        const int kb = ks[i] / 128;
-        kb0 += kb;
-        kp0 += (kb + 3) / 4;
+    int kb0 = 0, kp0 = 0, prev_end = 0, start = 0, len = 0;
+    for (int i = 0; i <= g; ++i) {
+        if (i > 0) {
+            const int kb = (len + 127) / 128;
+            kb0 += kb;
+            kp0 += (kb + 3) / 4;
+        }
+        k_group_extent(ks, i, psum, alignment, prev_end, start, len);
     }
-    const int num_kb = ks[g] / 128;
+    const int num_kb = (len + 127) / 128;
     const int num_kp = (num_kb + 3) / 4;
     for (long long i = blockIdx.x * 256ll + threadIdx.x; i < static_cast<long long>(num_kp) * mn; i += gridDim.x * 256ll) {
         const int j = static_cast<int>(i / mn), col = static_cast<int>(i - static_cast<long long>(j) * mn);
@@ -276,7 +280,7 @@ dgb200_pack_k_grouped_sf_kernel(const float* __restrict__ sf, const int* __restr
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const int kb = j * 4 + b;
-            if (kb < num_kb)
+            if (kb < num_kb && kb0 + kb < sf_rows)
                 packed |= ((__float_as_uint(sf[static_cast<long long>(kb0 + kb) * mn + col]) >> 23) & 0xffu) << (8 * b);
         }
         out[static_cast<long long>(kp0 + j) * aligned_mn + col] = packed;

@@ -118,24 +118,29 @@ int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int6
                         int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, void* stream);
 
 /* K-grouped FP8 GEMM (the MoE weight gradient): for every group g, d[g] = c[g] + a[rows of g]^T . b[rows of g] with
- * a e4m3 [sum_k, m] and b e4m3 [sum_k, n] (both MN-major: the K rows of the groups concatenated, ks[g] rows each, every
- * ks[g] a multiple of 128), sfa float [sum_k / 128, m] and sfb float [sum_k / 128, n] (one power-of-two scale per
- * 128 K rows and channel, groups concatenated), c and d float [num_groups, m, n] (may alias), ks int32 [num_groups]
- * on the device. sf_workspace: dgb200_k_grouped_sf_workspace_bytes(...) bytes of device scratch for the packed scales.
- * m % 16 == 0, n % 128 == 0, num_groups <= 512. Same kernel as the m-grouped GEMMs with MN-major shared-memory
- * descriptors, per-group K extents and an accumulating FP32 epilogue.
- * Reference: k_grouped_fp8_gemm_tn_contiguous, csrc/apis/gemm.hpp:299-346 (recipe (1, 1, 128), plain ks layout; its
- * psum layout and recipe (1, 1, 32) are not built). */
+ * a e4m3 [sum_k, m] and b e4m3 [sum_k, n] (both MN-major: the K rows of the groups one after the other), sfa float
+ * [sf_rows, m] and sfb float [sf_rows, n] (one power-of-two scale per 128 K rows of a group and channel, ceil(k_g / 128)
+ * rows per group, groups concatenated), c and d float [num_groups, m, n] (may alias), ks int32 [num_groups] on the device:
+ *   use_psum_layout = 0: ks[g] = K rows of group g, each a multiple of 128, groups packed back to back;
+ *   use_psum_layout = 1: ks[g] = end K row of group g; group g starts at align(ks[g-1], k_alignment) (k_alignment a
+ *                        multiple of 128) and the rows between a group's end and the next start are zero.
+ * sum_k = rows of a and b (a multiple of 128). sf_workspace: dgb200_k_grouped_sf_workspace_bytes(...) bytes of device
+ * scratch for the packed scales. m % 16 == 0, n % 128 == 0, num_groups <= 512. Same kernel as the m-grouped GEMMs with
+ * MN-major shared-memory descriptors, per-group K extents and an accumulating FP32 epilogue.
+ * Reference: k_grouped_fp8_gemm_tn_contiguous, csrc/apis/gemm.hpp:299-346 (recipe (1, 1, 128); recipe (1, 1, 32) and
+ * K alignments below 128 are not built). */
 int64_t dgb200_k_grouped_sf_workspace_bytes(int32_t num_groups, int32_t m, int32_t n, int32_t sum_k);
-int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, const void* b, const float* sfb, const float* c,
-                                            float* d, const int32_t* ks, int32_t num_groups, int32_t m, int32_t n,
-                                            int32_t sum_k, void* sf_workspace, void* stream);
+int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int32_t sf_rows, const void* b, const float* sfb,
+                                            const float* c, float* d, const int32_t* ks, int32_t use_psum_layout,
+                                            int32_t k_alignment, int32_t num_groups, int32_t m, int32_t n, int32_t sum_k,
+                                            void* sf_workspace, void* stream);
 
-/* BF16 form of the K-grouped GEMM: a bf16 [sum_k, m], b bf16 [sum_k, n] (MN-major), every ks[g] a multiple of 64,
- * m % 8 == 0, n % 128 == 0; c, d, ks as above; no scale factors, no workspace.
- * Reference: k_grouped_bf16_gemm_tn_contiguous, csrc/apis/gemm.hpp:566-608 (plain ks layout). */
+/* BF16 form of the K-grouped GEMM: a bf16 [sum_k, m], b bf16 [sum_k, n] (MN-major), K extents / alignment multiples of
+ * 64, m % 8 == 0, n % 128 == 0; c, d, ks and the two layouts as above; no scale factors, no workspace.
+ * Reference: k_grouped_bf16_gemm_tn_contiguous, csrc/apis/gemm.hpp:566-608. */
 int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const float* c, float* d, const int32_t* ks,
-                                             int32_t num_groups, int32_t m, int32_t n, int32_t sum_k, void* stream);
+                                             int32_t use_psum_layout, int32_t k_alignment, int32_t num_groups, int32_t m,
+                                             int32_t n, int32_t sum_k, void* stream);
 
 /* BF16 rows -> E4M3 + one UE8M0 scale per gran_k (32 or 128) elements: sf = 2^ceil(log2(max(amax, 1e-4) / 448)),
  * q = e4m3_rn(x / sf). Reference: per_token_cast_to_fp8(use_ue8m0=True), deep_gemm/utils/math.py:26-49 (a torch

@@ -122,3 +122,25 @@ def k_grouped_gemm(a_q, a_sf, b_q, b_sf, c, ks, gran_k=128):
             d[g] += a[start:start + k].T @ b[start:start + k]
         start += k
     return d
+
+
+def k_grouped_gemm_psum(a_q, a_sf, b_q, b_sf, c, ends, alignment, gran_k=128):
+    """K-grouped GEMM with the psum layout (tests/generators.py:482-533): ends[g] = end K row of group g, group g starts
+    at align(ends[g - 1], alignment); the scale factors hold ceil(k_g / gran_k) rows per group, groups concatenated.
+    Operands may be quantised (a_sf / b_sf given) or plain (a_sf = b_sf = None)."""
+    d = c.clone().float()
+    prev_end, sf_row = 0, 0
+    for g, end in enumerate(ends):
+        start = align(prev_end, alignment)
+        k = max(int(end) - start, 0)
+        prev_end = int(end)
+        if k == 0:
+            continue
+        a, b = a_q[start:start + k].float(), b_q[start:start + k].float()
+        if a_sf is not None:
+            blocks = (k + gran_k - 1) // gran_k
+            a = a * a_sf[sf_row:sf_row + blocks].repeat_interleave(gran_k, dim=0)[:k]
+            b = b * b_sf[sf_row:sf_row + blocks].repeat_interleave(gran_k, dim=0)[:k]
+            sf_row += blocks
+        d[g] += a.T @ b
+    return d

@@ -72,8 +72,6 @@ def test_rejected_inputs(dg):
         dg.k_grouped_fp8_gemm_tn_contiguous(*args, [128], layout, c=d, recipe=(1, 1, 32))
     with pytest.raises(RuntimeError):
         dg.k_grouped_fp8_gemm_tn_contiguous(*args, [64], layout, c=d)
-    with pytest.raises(RuntimeError):
-        dg.k_grouped_fp8_gemm_tn_contiguous(*args, [128], layout, c=d, use_psum_layout=True)
 
 
 @pytest.mark.parametrize('ks,m,n', [
@@ -103,3 +101,60 @@ def test_k_grouped_bf16_matches_oracle(dg, ks, m, n):
             want = a[start:start + kg].float().T @ b[start:start + kg].float()
             assert quant.calc_diff(got[g] - c[g], want) < 1e-5
         start += kg
+
+
+def _psum_case(real_ks, m, n, alignment, seed):
+    """Inputs as the reference's generate_k_grouped_contiguous_psum builds them (tests/generators.py:492-533): every group
+    starts at a multiple of the alignment, the gap rows are zero."""
+    torch.manual_seed(seed)
+    ends, prev = [], 0
+    for k in real_ks:
+        prev = -(-prev // alignment) * alignment + k
+        ends.append(prev)
+    total = -(-ends[-1] // alignment) * alignment
+    a, b = torch.zeros(total, m).bfloat16(), torch.zeros(total, n).bfloat16()
+    for k, end in zip(real_ks, ends):
+        a[end - k:end] = torch.randn(k, m).bfloat16()
+        b[end - k:end] = torch.randn(k, n).bfloat16()
+    return a, b, ends, total
+
+
+@pytest.mark.parametrize('real_ks,m,n', [([300, 0, 129, 1000], 128, 256), ([128, 5, 2049], 256, 128), ([4000, 1111], 384, 512)])
+@pytest.mark.parametrize('fp8', [True, False])
+def test_k_grouped_psum_layout(dg, real_ks, m, n, fp8):
+    from deepgemm_b200 import _lib
+    alignment = dg.get_mk_alignment_for_contiguous_layout()
+    assert alignment == 128
+    a, b, ends, total = _psum_case(real_ks, m, n, alignment, seed=sum(real_ks))
+    c = torch.randn(len(real_ks), m, n) * 32
+    d = c.cuda()
+    layout = torch.tensor(ends, dtype=torch.int32, device='cuda')
+    if fp8:
+        a_q, b_q = torch.zeros(total, m, dtype=torch.float8_e4m3fn), torch.zeros(total, n, dtype=torch.float8_e4m3fn)
+        a_sfs, b_sfs = [], []
+        for k, end in zip(real_ks, ends):  # per group, padded to a multiple of 128 rows (tests/generators.py:425-433)
+            if k == 0:
+                continue
+            pad = -(-k // 128) * 128
+            for src, q_out, sfs, mn in ((a, a_q, a_sfs, m), (b, b_q, b_sfs, n)):
+                block = torch.zeros(pad, mn).bfloat16()
+                block[:k] = src[end - k:end]
+                q, sf = _per_channel_fp8(block)
+                q_out[end - k:end] = q[:k]
+                sfs.append(sf)
+        a_sf, b_sf = torch.cat(a_sfs), torch.cat(b_sfs)
+        want = ogemm.k_grouped_gemm_psum(a_q, a_sf, b_q, b_sf, c, ends, alignment)
+        dg.k_grouped_fp8_gemm_tn_contiguous((a_q.cuda(), a_sf.cuda()), (b_q.cuda(), b_sf.cuda()), d, None, layout, c=d,
+                                            use_psum_layout=True)
+        tol = FP8_TOL
+    else:
+        want = ogemm.k_grouped_gemm_psum(a, None, b, None, c, ends, alignment)
+        dg.k_grouped_bf16_gemm_tn_contiguous(a.cuda(), b.cuda(), d, None, layout, c=d, use_psum_layout=True)
+        tol = 1e-5
+    assert _lib.device_status()[0] == 0
+    got = d.cpu()
+    for g, k in enumerate(real_ks):
+        if k == 0:
+            assert torch.equal(got[g], c[g])
+        else:
+            assert quant.calc_diff(got[g] - c[g], want[g] - c[g]) <= tol
