@@ -84,6 +84,18 @@ def quantize_fp8_per_token(x: torch.Tensor, gran_k: int = 128, packed: bool = Fa
     return q, sf
 
 
+def quantize_fp8_per_channel(x: torch.Tensor, gran_k: int = 128):
+    """Operand quantiser of the K-grouped GEMM: x [k, mn] with k a multiple of ``gran_k``; one UE8M0 scale per ``gran_k``
+    K rows and channel. Follows ``per_channel_cast_to_fp8(use_ue8m0=True)`` (deep_gemm/utils/math.py:52-59):
+    ``sf = ue8m0_ceil(max(amax, 1e-4) / 448)``, ``q = e4m3(x * (1 / sf))``. Returns (q e4m3 [k, mn], sf fp32 [k / gran_k, mn])."""
+    assert x.dim() == 2 and x.shape[0] % gran_k == 0
+    k, mn = x.shape
+    view = x.float().view(-1, gran_k, mn)
+    sf = ue8m0_ceil(view.abs().amax(dim=1).clamp(min=1e-4) / 448.0)
+    q = (view * (1.0 / sf.unsqueeze(1))).to(torch.float8_e4m3fn).view(k, mn)
+    return q, sf
+
+
 def e2m1_codes(x: torch.Tensor) -> torch.Tensor:
     """fp32 -> 4-bit E2M1 codes (uint8): magnitude index 0..7 by strict-greater thresholds, sign in bit 3,
     negative zero canonicalised to +0. Follows ``_quantize_to_fp4_e2m1`` (deep_gemm/utils/math.py:84-93)."""

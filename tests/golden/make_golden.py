@@ -11,6 +11,10 @@ What is pinned:
                cast_back_from_fp8 / cast_back_from_fp4, ceil_to_ue8m0, pack/unpack, calc_diff
   layout.npz   the packed MN-major scale-factor layout as restated by the reference's own layout test
                (tests/test_layout.py:20-42) and the mega-MoE weight interleave (deep_gemm/mega/__init__.py:97-111)
+  kgrouped.npz per_channel_cast_to_fp8 (the K-grouped GEMM's operand quantiser, one scale per 128 K rows and channel) and
+               the K-grouped product d[g] = c[g] + a_g^T b_g over the dequantised operands, as the reference's generator
+               forms it (tests/generators.py:413-453); written by ``make_golden.py <tree> --only kgrouped`` without
+               touching the other two files
 """
 import importlib.util
 import os
@@ -39,6 +43,9 @@ def main():
         raise SystemExit('usage: make_golden.py <path-to-the-DeepGEMM-tree>')
     rmath = load_by_path('ref_math', os.path.join(ref_root, 'deep_gemm/utils/math.py'))
     rnum = load_by_path('ref_numeric', os.path.join(ref_root, 'deep_gemm/testing/numeric.py'))
+    if '--only' in sys.argv and sys.argv[sys.argv.index('--only') + 1] == 'kgrouped':
+        make_kgrouped(rmath)
+        return
 
     out = {}
     torch.manual_seed(1234)
@@ -104,6 +111,32 @@ def main():
     lay['interleave_g8'] = t[:, src].contiguous().numpy()
     np.savez_compressed(os.path.join(HERE, 'layout.npz'), **lay)
     print('wrote quant.npz, layout.npz')
+    make_kgrouped(rmath)
+
+
+def make_kgrouped(rmath):
+    torch.manual_seed(4321)
+    ks = [256, 128, 384]
+    m, n = 48, 40
+    a = torch.randn(sum(ks), m).bfloat16()
+    b = torch.randn(sum(ks), n).bfloat16()
+    a[0:128, 0] = 0.0                       # an all-zero (K block, channel): amax clamp at 1e-4
+    a[128:256, 1] = 448.0 * 2.0 ** -2       # amax / 448 exactly a power of two
+    b[256:384] = b[256:384] * 1e-5
+    out = {'ks': np.array(ks, dtype=np.int64), 'a_bf16': u8(a), 'b_bf16': u8(b)}
+    (a_q, a_sf), (b_q, b_sf) = (rmath.per_channel_cast_to_fp8(t, use_ue8m0=True, gran_k=128) for t in (a, b))
+    out.update({'a_q': u8(a_q), 'a_sf': a_sf.numpy(), 'b_q': u8(b_q), 'b_sf': b_sf.numpy()})
+    c = torch.randn(len(ks), m, n) * 32
+    d = c.clone()
+    a_deq = a_q.float() * a_sf.repeat_interleave(128, dim=0)
+    b_deq = b_q.float() * b_sf.repeat_interleave(128, dim=0)
+    start = 0
+    for g, k in enumerate(ks):
+        d[g] = c[g] + a_deq[start:start + k].T @ b_deq[start:start + k]
+        start += k
+    out.update({'c': c.numpy(), 'd': d.numpy()})
+    np.savez_compressed(os.path.join(HERE, 'kgrouped.npz'), **out)
+    print('wrote kgrouped.npz')
 
 
 if __name__ == '__main__':

@@ -80,3 +80,22 @@ def test_gate_up_interleave_matches_reference(gl):
     u = torch.arange(128 * 2).view(128, 2)
     v = olay.interleave_gate_up(u, 32)
     assert torch.equal(v[:32], u[:32]) and torch.equal(v[32:64], u[64:96]) and torch.equal(v[64:96], u[32:64])
+
+
+def test_k_grouped_quantiser_and_product_match_reference(golden_dir):
+    """per_channel_cast_to_fp8 bit for bit; the K-grouped product over the dequantised operands to FP32 rounding."""
+    from oracle import gemm as ogemm
+    g = np.load(os.path.join(golden_dir, 'kgrouped.npz'))
+    ks = [int(k) for k in g['ks']]
+    qs = {}
+    for name in ('a', 'b'):
+        x = _bf16(g[f'{name}_bf16'])
+        q, sf = quant.quantize_fp8_per_channel(x, 128)
+        assert np.array_equal(q.view(torch.uint8).numpy(), g[f'{name}_q'])
+        assert np.array_equal(sf.numpy(), g[f'{name}_sf'])
+        qs[name] = (q, sf)
+    d = ogemm.k_grouped_gemm(qs['a'][0], qs['a'][1], qs['b'][0], qs['b'][1], torch.from_numpy(g['c'].copy()), ks)
+    assert np.allclose(d.numpy(), g['d'], rtol=0, atol=1e-4)
+    ends = np.cumsum(ks).tolist()  # K extents that are multiples of the alignment: the psum layout is the same split
+    d2 = ogemm.k_grouped_gemm_psum(qs['a'][0], qs['a'][1], qs['b'][0], qs['b'][1], torch.from_numpy(g['c'].copy()), ends, 128)
+    assert torch.equal(d2, d)
