@@ -1243,16 +1243,33 @@ int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, 
     return 0;
 }
 
+int dgb200_per_channel_cast_to_fp8(const void* x, int32_t k, int32_t mn, int32_t gran_k, void* q, float* sf, void* stream) {
+    DGB_REQUIRE(k >= 0 && mn > 0 && mn % 2 == 0, "mn (%d) must be a positive even number", mn);
+    DGB_REQUIRE(gran_k == 32 || gran_k == 128, "gran_k must be 32 or 128, got %d", gran_k);
+    DGB_REQUIRE(k % gran_k == 0, "k (%d) must be a multiple of gran_k (%d)", k, gran_k);
+    if (k == 0) return 0;
+    DGB_REQUIRE(x != nullptr && q != nullptr && sf != nullptr, "null tensor pointer");
+    DGB_REQUIRE(reinterpret_cast<uintptr_t>(x) % 4 == 0 && reinterpret_cast<uintptr_t>(q) % 2 == 0 &&
+                    reinterpret_cast<uintptr_t>(sf) % 8 == 0,
+                "x, q and sf must be 4-, 2- and 8-byte aligned");
+    const dim3 grid((mn / 2 + 255) / 256, k / gran_k);
+    dgb200_cast_channels_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), k, mn, gran_k, static_cast<unsigned char*>(q), sf);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int64_t dgb200_k_grouped_sf_workspace_bytes(int32_t num_groups, int32_t m, int32_t n, int32_t sum_k) {
     if (num_groups <= 0 || m <= 0 || n <= 0 || sum_k < 0) return 0;
-    const long long rows = sum_k / 128 / 4 + 2ll * num_groups;  // every group rounds its K blocks up to a multiple of 4
+    const long long rows = sum_k / 128 + 2ll * num_groups;  // one packed row per K block at most (scales per 32 K rows)
     return rows * ((static_cast<long long>(m) + 3) / 4 * 4 + (static_cast<long long>(n) + 3) / 4 * 4) * 4;
 }
 
 int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int32_t sf_rows, const void* b, const float* sfb,
                                             const float* c, float* d, const int32_t* ks, int32_t use_psum_layout,
-                                            int32_t k_alignment, int32_t num_groups, int32_t m, int32_t n, int32_t sum_k,
-                                            void* sf_workspace, void* stream_) {
+                                            int32_t k_alignment, int32_t gran_k, int32_t num_groups, int32_t m, int32_t n,
+                                            int32_t sum_k, void* sf_workspace, void* stream_) {
+    DGB_REQUIRE(gran_k == 32 || gran_k == 128, "gran_k must be 32 or 128, got %d", gran_k);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     DGB_REQUIRE(num_groups > 0 && num_groups <= kMaxCachedGroups, "num_groups must be in [1, %d]", kMaxCachedGroups);
     DGB_REQUIRE(m > 0 && m % 16 == 0 && n > 0 && n % 128 == 0, "m (%d) must be a positive multiple of 16 and n (%d) of 128", m, n);
@@ -1270,15 +1287,15 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int
     DGB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0 &&
                     reinterpret_cast<uintptr_t>(sf_workspace) % 16 == 0,
                 "a, b and the workspace must be 16-byte aligned");
-    const long long kp_rows = sum_k / 128 / 4 + 2ll * num_groups;
+    const long long kp_rows = sum_k / 128 + 2ll * num_groups;
     const long long aligned_m = (static_cast<long long>(m) + 3) / 4 * 4, aligned_n = (static_cast<long long>(n) + 3) / 4 * 4;
     uint32_t* sfa_packed = static_cast<uint32_t*>(sf_workspace);
     uint32_t* sfb_packed = sfa_packed + kp_rows * aligned_m;
     {
         const dim3 grid_a(static_cast<unsigned>(std::min<long long>((static_cast<long long>(sum_k / 128 / 4 + 1) * m + 255) / 256, 64)), num_groups);
-        dgb200_pack_k_grouped_sf_kernel<<<grid_a, 256, 0, stream>>>(sfa, sf_rows, ks, use_psum_layout, k_alignment, m, aligned_m, sfa_packed);
+        dgb200_pack_k_grouped_sf_kernel<<<grid_a, 256, 0, stream>>>(sfa, sf_rows, ks, use_psum_layout, k_alignment, gran_k, m, aligned_m, sfa_packed);
         const dim3 grid_b(static_cast<unsigned>(std::min<long long>((static_cast<long long>(sum_k / 128 / 4 + 1) * n + 255) / 256, 64)), num_groups);
-        dgb200_pack_k_grouped_sf_kernel<<<grid_b, 256, 0, stream>>>(sfb, sf_rows, ks, use_psum_layout, k_alignment, n, aligned_n, sfb_packed);
+        dgb200_pack_k_grouped_sf_kernel<<<grid_b, 256, 0, stream>>>(sfb, sf_rows, ks, use_psum_layout, k_alignment, gran_k, n, aligned_n, sfb_packed);
         DGB_CUDA(cudaGetLastError());
     }
     GemmParams p{};
@@ -1293,7 +1310,7 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int
     p.num_groups = num_groups;
     p.alignment = use_psum_layout ? k_alignment : 128;
     p.kg_psum = use_psum_layout ? 1 : 0;
-    p.gran_a = p.gran_b = 128;
+    p.gran_a = p.gran_b = gran_k;
     p.b_fmt = kFmtE4M3;
     // Wide tiles halve the shared-memory fill per MMA cycle, which bounds the 128-wide tile (measured 1.29 -> 1.40 PFLOP/s
     // at 32 K blocks per group); with short K extents the FP32 epilogue dominates and the 128-wide tile's two

@@ -378,7 +378,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 group_cache[i] = blocks;
                 group_start[i] = start;
                 group_tiles_end[i] = kp;
-                kp += (blocks + 3) / 4;
+                kp += p.gran_a == 32 ? blocks : (blocks + 3) / 4;  // packed scale rows: one per K block, or per 4 K blocks
             }
         }
     } else if (cache_groups) {

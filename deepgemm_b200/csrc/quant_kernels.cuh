@@ -253,35 +253,64 @@ __global__ void __launch_bounds__(256) dgb200_cast_rows_nvfp4_kernel(const CastN
     }
 }
 
-// Scale factors of a K-grouped operand: FP32 powers of two [sum of ceil(k_g / 128) rows, mn], the groups' rows
-// concatenated (the reference's tests build them per group, tests/generators.py:413-435) -> packed UE8M0 ints
-// [sum of ceil(K blocks_g / 4) rows, aligned mn]: int (j, col) of group g holds the exponent bytes of the group's K
-// blocks 4j .. 4j+3 (zero past the group's end), so every group starts on an int boundary. One block row per group
-// (blockIdx.y); each block finds its group's first rows with a serial scan over ks (at most a few hundred groups).
-// Reference: transform_k_grouped_sf_into_required_layout, csrc/apis/layout.hpp (called from csrc/apis/gemm.hpp:335-336).
+// Operand quantiser of the K-grouped GEMM: x bf16 [k, mn] -> e4m3 [k, mn] + one FP32 power-of-two scale per gran_k K rows
+// and channel [k / gran_k, mn]: sf = 2^ceil(log2(max(amax, 1e-4) / 448)), q = e4m3_rn(x / sf). One thread owns two
+// neighbouring channels of one K block (warps read 128 contiguous bytes per row); the second pass over the block's rows
+// comes from L2. Reference: per_channel_cast_to_fp8(use_ue8m0=True), deep_gemm/utils/math.py:52-59 (torch ops there).
+__global__ void __launch_bounds__(256)
+dgb200_cast_channels_kernel(const __nv_bfloat16* __restrict__ x, int k, int mn, int gran_k, unsigned char* __restrict__ q,
+                            float* __restrict__ sf) {
+    const int col = (blockIdx.x * 256 + threadIdx.x) * 2;
+    const int row0 = blockIdx.y * gran_k;
+    if (col >= mn) return;
+    const int rows = min(gran_k, k - row0);
+    float amax0 = 0.0f, amax1 = 0.0f;
+    for (int r = 0; r < rows; ++r) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(x + static_cast<long long>(row0 + r) * mn + col);
+        amax0 = fmaxf(amax0, fabsf(__uint_as_float(w << 16)));
+        amax1 = fmaxf(amax1, fabsf(__uint_as_float(w & 0xffff0000u)));
+    }
+    const uint32_t e0 = ue8m0_ceil_bits(fmaxf(amax0, 1e-4f) / 448.0f), e1 = ue8m0_ceil_bits(fmaxf(amax1, 1e-4f) / 448.0f);
+    const float sf0 = __uint_as_float(e0 << 23), sf1 = __uint_as_float(e1 << 23);
+    const float inv0 = 1.0f / sf0, inv1 = 1.0f / sf1;
+    *reinterpret_cast<float2*>(sf + static_cast<long long>(blockIdx.y) * mn + col) = make_float2(sf0, sf1);
+    for (int r = 0; r < rows; ++r) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(x + static_cast<long long>(row0 + r) * mn + col);
+        const __nv_fp8x2_e4m3 q2(make_float2(__uint_as_float(w << 16) * inv0, __uint_as_float(w & 0xffff0000u) * inv1));
+        *reinterpret_cast<unsigned short*>(q + static_cast<long long>(row0 + r) * mn + col) = q2.__x;
+    }
+}
+
+// Scale factors of a K-grouped operand: FP32 powers of two [sum of ceil(k_g / gran_k) rows, mn], the groups' rows
+// concatenated (the reference's tests build them per group, tests/generators.py:413-435) -> packed UE8M0 ints, every
+// group starting on an int boundary: with gran_k = 128 int (j, col) of a group holds the exponent bytes of its K blocks
+// 4j .. 4j+3, with gran_k = 32 those of the four 32-row scales of K block j (zero past the group's end). One block row
+// per group (blockIdx.y); each block finds its group's first rows with a serial scan over the layout (at most a few
+// hundred groups). Reference: transform_k_grouped_sf_into_required_layout, csrc/apis/layout.hpp (called from
+// csrc/apis/gemm.hpp:335-336).
 __global__ void __launch_bounds__(256)
 dgb200_pack_k_grouped_sf_kernel(const float* __restrict__ sf, int sf_rows, const int* __restrict__ ks, int psum, int alignment,
-                                int mn, long long aligned_mn, uint32_t* __restrict__ out) {
+                                int gran_k, int mn, long long aligned_mn, uint32_t* __restrict__ out) {
     const int g = blockIdx.y;
-    int kb0 = 0, kp0 = 0, prev_end = 0, start = 0, len = 0;
+    int row0 = 0, kp0 = 0, prev_end = 0, start = 0, len = 0;
     for (int i = 0; i <= g; ++i) {
         if (i > 0) {
-            const int kb = (len + 127) / 128;
-            kb0 += kb;
-            kp0 += (kb + 3) / 4;
+            const int rows = (len + gran_k - 1) / gran_k;
+            row0 += rows;
+            kp0 += (rows + 3) / 4;
         }
         k_group_extent(ks, i, psum, alignment, prev_end, start, len);
     }
-    const int num_kb = (len + 127) / 128;
-    const int num_kp = (num_kb + 3) / 4;
+    const int num_rows = (len + gran_k - 1) / gran_k;
+    const int num_kp = (num_rows + 3) / 4;
     for (long long i = blockIdx.x * 256ll + threadIdx.x; i < static_cast<long long>(num_kp) * mn; i += gridDim.x * 256ll) {
         const int j = static_cast<int>(i / mn), col = static_cast<int>(i - static_cast<long long>(j) * mn);
         uint32_t packed = 0;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const int kb = j * 4 + b;
-            if (kb < num_kb && kb0 + kb < sf_rows)
-                packed |= ((__float_as_uint(sf[static_cast<long long>(kb0 + kb) * mn + col]) >> 23) & 0xffu) << (8 * b);
+            const int r = j * 4 + b;
+            if (r < num_rows && row0 + r < sf_rows)
+                packed |= ((__float_as_uint(sf[static_cast<long long>(row0 + r) * mn + col]) >> 23) & 0xffu) << (8 * b);
         }
         out[static_cast<long long>(kp0 + j) * aligned_mn + col] = packed;
     }

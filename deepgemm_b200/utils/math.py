@@ -83,6 +83,23 @@ def per_token_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128,
     return q, (packed if use_packed_ue8m0 else sf)
 
 
+def per_channel_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x bfloat16 [K, MN] -> (e4m3 [K, MN], fp32 [K / gran_k, MN]): one scale per ``gran_k`` K rows and channel, the
+    operand format of the K-grouped GEMM. Reference: per_channel_cast_to_fp8, deep_gemm/utils/math.py:52-59."""
+    if not use_ue8m0:
+        raise RuntimeError('only UE8M0 (power-of-two) scales are supported on sm_100a')
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
+        raise RuntimeError('x must be a contiguous CUDA bfloat16 [K, MN] tensor')
+    k, mn = x.shape
+    if k % gran_k != 0:
+        raise RuntimeError(f'K ({k}) must be a multiple of gran_k ({gran_k})')
+    q = torch.empty((k, mn), dtype=torch.float8_e4m3fn, device=x.device)
+    sf = torch.empty((k // gran_k, mn), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().dgb200_per_channel_cast_to_fp8(_ptr(x), k, mn, gran_k, _ptr(q), _ptr(sf), _lib.current_stream_ptr()))
+    return q, sf
+
+
 def per_token_cast_to_fp4(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128,
                           use_packed_ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """(int8 [M, K / 2] packed E2M1, scales). Reference: per_token_cast_to_fp4, deep_gemm/utils/math.py:96-122."""

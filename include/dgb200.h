@@ -117,23 +117,28 @@ int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, 
 int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
                         int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, void* stream);
 
+/* Operand quantiser of the K-grouped GEMM: x bf16 [k, mn] contiguous -> q e4m3 [k, mn] and sf float [k / gran_k, mn], one
+ * power-of-two scale per gran_k (32 or 128) K rows and channel; k % gran_k == 0, mn even.
+ * Reference: per_channel_cast_to_fp8(use_ue8m0=True), deep_gemm/utils/math.py:52-59 (a torch helper there). */
+int dgb200_per_channel_cast_to_fp8(const void* x, int32_t k, int32_t mn, int32_t gran_k, void* q, float* sf, void* stream);
+
 /* K-grouped FP8 GEMM (the MoE weight gradient): for every group g, d[g] = c[g] + a[rows of g]^T . b[rows of g] with
  * a e4m3 [sum_k, m] and b e4m3 [sum_k, n] (both MN-major: the K rows of the groups one after the other), sfa float
- * [sf_rows, m] and sfb float [sf_rows, n] (one power-of-two scale per 128 K rows of a group and channel, ceil(k_g / 128)
- * rows per group, groups concatenated), c and d float [num_groups, m, n] (may alias), ks int32 [num_groups] on the device:
+ * [sf_rows, m] and sfb float [sf_rows, n] (one power-of-two scale per gran_k = 32 or 128 K rows of a group and channel,
+ * ceil(k_g / gran_k) rows per group, groups concatenated), c and d float [num_groups, m, n] (may alias), ks int32 [num_groups] on the device:
  *   use_psum_layout = 0: ks[g] = K rows of group g, each a multiple of 128, groups packed back to back;
  *   use_psum_layout = 1: ks[g] = end K row of group g; group g starts at align(ks[g-1], k_alignment) (k_alignment a
  *                        multiple of 128) and the rows between a group's end and the next start are zero.
  * sum_k = rows of a and b (a multiple of 128). sf_workspace: dgb200_k_grouped_sf_workspace_bytes(...) bytes of device
  * scratch for the packed scales. m % 16 == 0, n % 128 == 0, num_groups <= 512. Same kernel as the m-grouped GEMMs with
  * MN-major shared-memory descriptors, per-group K extents and an accumulating FP32 epilogue.
- * Reference: k_grouped_fp8_gemm_tn_contiguous, csrc/apis/gemm.hpp:299-346 (recipe (1, 1, 128); recipe (1, 1, 32) and
+ * Reference: k_grouped_fp8_gemm_tn_contiguous, csrc/apis/gemm.hpp:299-346 (recipes (1, 1, 128) and (1, 1, 32);
  * K alignments below 128 are not built). */
 int64_t dgb200_k_grouped_sf_workspace_bytes(int32_t num_groups, int32_t m, int32_t n, int32_t sum_k);
 int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int32_t sf_rows, const void* b, const float* sfb,
                                             const float* c, float* d, const int32_t* ks, int32_t use_psum_layout,
-                                            int32_t k_alignment, int32_t num_groups, int32_t m, int32_t n, int32_t sum_k,
-                                            void* sf_workspace, void* stream);
+                                            int32_t k_alignment, int32_t gran_k, int32_t num_groups, int32_t m, int32_t n,
+                                            int32_t sum_k, void* sf_workspace, void* stream);
 
 /* BF16 form of the K-grouped GEMM: a bf16 [sum_k, m], b bf16 [sum_k, n] (MN-major), K extents / alignment multiples of
  * 64, m % 8 == 0, n % 128 == 0; c, d, ks and the two layouts as above; no scale factors, no workspace.

@@ -68,7 +68,7 @@ def test_rejected_inputs(dg):
     with pytest.raises(RuntimeError):
         dg.k_grouped_fp8_gemm_tn_contiguous(*args, [128], layout, c=None)
     with pytest.raises(RuntimeError):
-        dg.k_grouped_fp8_gemm_tn_contiguous(*args, [128], layout, c=d, recipe=(1, 1, 32))
+        dg.k_grouped_fp8_gemm_tn_contiguous(*args, [128], layout, c=d, recipe=(1, 1, 64))
     with pytest.raises(RuntimeError):
         dg.k_grouped_fp8_gemm_tn_contiguous(*args, [64], layout, c=d)
 
@@ -157,3 +157,26 @@ def test_k_grouped_psum_layout(dg, real_ks, m, n, fp8):
             assert torch.equal(got[g], c[g])
         else:
             assert quant.calc_diff(got[g] - c[g], want[g] - c[g]) <= tol
+
+
+@pytest.mark.parametrize('ks,m,n', [([256, 128, 640], 128, 256), ([4096, 0, 2048], 256, 512)])
+def test_k_grouped_recipe_32(dg, ks, m, n):
+    """One scale per 32 K rows and channel (recipe (1, 1, 32))."""
+    from deepgemm_b200 import _lib
+    torch.manual_seed(sum(ks))
+    k = sum(ks)
+    a_q, a_sf = quant.quantize_fp8_per_channel(torch.randn(k, m).bfloat16() * torch.logspace(-2, 2, k).unsqueeze(1), 32)
+    b_q, b_sf = quant.quantize_fp8_per_channel(torch.randn(k, n).bfloat16(), 32)
+    c = torch.randn(len(ks), m, n)
+    want = ogemm.k_grouped_gemm(a_q, a_sf, b_q, b_sf, c, ks, gran_k=32)
+    d = c.cuda()
+    layout = torch.tensor(ks, dtype=torch.int32, device='cuda')
+    dg.k_grouped_fp8_gemm_tn_contiguous((a_q.cuda(), a_sf.cuda()), (b_q.cuda(), b_sf.cuda()), d, ks, layout, c=d,
+                                        recipe=(1, 1, 32))
+    assert _lib.device_status()[0] == 0
+    got = d.cpu()
+    for g, kg in enumerate(ks):
+        if kg == 0:
+            assert torch.equal(got[g], c[g])
+        else:
+            assert quant.calc_diff(got[g] - c[g], want[g] - c[g]) <= FP8_TOL

@@ -109,3 +109,17 @@ def test_router_matches_oracle(dg):
     want_idx, want_w = omoe.route_sigmoid_topk(logits, 8)
     assert torch.equal(idx.cpu(), want_idx)
     assert torch.allclose(w.cpu(), want_w, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize('k,mn', [(128, 2), (384, 48), (1024, 7168), (256, 4098)])
+@pytest.mark.parametrize('gran', [32, 128])
+def test_per_channel_fp8_cast_bit_exact(dg, k, mn, gran):
+    """Operand quantiser of the K-grouped GEMM: one scale per `gran` K rows and channel."""
+    x = _inputs(k, mn, seed=k + mn)
+    x[:gran, 0] = 0  # an all-zero (K block, channel)
+    want_q, want_sf = quant.quantize_fp8_per_channel(x, gran)
+    q, sf = dg.utils.per_channel_cast_to_fp8(x.cuda(), use_ue8m0=True, gran_k=gran)
+    assert torch.equal(q.cpu().view(torch.uint8), want_q.view(torch.uint8))
+    assert torch.equal(sf.cpu(), want_sf)
+    with pytest.raises(RuntimeError):
+        dg.utils.per_channel_cast_to_fp8(x[:gran - 1].cuda(), use_ue8m0=True, gran_k=gran)
