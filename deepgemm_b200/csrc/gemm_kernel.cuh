@@ -16,6 +16,13 @@
 //   * Stores are clipped to the valid rows of a group, so a masked group never writes into its neighbour.
 //   * Every wait is bounded; a timeout unwinds the CTA and is reported through the status block.
 //
+// Other forms of the same kernel (template parameters):
+//   * kKindNvfp4: packed E2M1 x packed E2M1 with UE4M3 scales per 16 and FP32 tensor scales (kind::mxf4nvf4).
+//   * kKindBf16: BF16 x BF16 without scales (kind::f16), the reference's BF16 GEMM family
+//     (deep_gemm/include/deep_gemm/impls/sm100_bf16_gemm.cuh) and the BF16 layer's GEMMs.
+//   * kEpiF32Acc: the K-grouped GEMM d[g] = c[g] + A_g^T B_g with MN-major operands (FP8 with per-channel scales, or
+//     BF16); replaces the reference's K-grouped use of its 1d1d kernels (scheduler/gemm.cuh:238-261).
+//
 // Warp roles (384 threads): warp 0 loads A tiles and their scale factors, warp 3 the weight tiles and theirs, warp 1
 // issues the MMAs, warp 2 allocates TMEM and (only for scale factors in plain row order) transposes them for tcgen05.cp,
 // warps 4-11 are the epilogue (TMEM lane quarter = warp index % 4, two warps per quarter splitting the columns).
