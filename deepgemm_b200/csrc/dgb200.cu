@@ -23,7 +23,7 @@ constexpr int kVersion = 100;
 template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
 int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_sfa, const CUtensorMap& tm_sfb,
                 const CUtensorMap& tm_out, const GemmParams& p, int grid, cudaStream_t stream) {
-    using L = GemmSmem<BLOCK_N, kStages, kKind>;
+    using L = GemmSmem<BLOCK_N, kStages, kKind, EPI == kEpiF32Acc>;
     auto kernel = dgb200_grouped_gemm_kernel<BLOCK_N, kStages, EPI, kKind>;
     static bool configured = false;  // per instantiation; the attribute is per device function, set on every device once
     static int configured_device = -1;
@@ -1243,6 +1243,20 @@ int dgb200_transform_sf_into_required_layout(const float* sf, int64_t stride_g, 
     return 0;
 }
 
+namespace {
+// The K-grouped epilogue adds its accumulators into d (TMA reductions for whole tiles, row by row for the tail of m), so d
+// must hold c before the kernel starts; the kernel then reads and writes d only.
+int prepare_k_grouped_output(CUtensorMap* tm_out, GemmParams& p, const float* c, float* d, int num_groups, int m, int n,
+                             cudaStream_t stream) {
+    if (c != d)
+        DGB_CUDA(cudaMemcpyAsync(d, c, static_cast<size_t>(num_groups) * m * n * 4, cudaMemcpyDeviceToDevice, stream));
+    p.c = d;
+    p.tma_store = 1;  // whole 128-row tiles only: a slab must not reach into the next group's rows
+    return make_tensor_map_2d(tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, d, static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(num_groups) * m, static_cast<uint64_t>(n) * 4, 16, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+}  // namespace
+
 int dgb200_per_channel_cast_to_fp8(const void* x, int32_t k, int32_t mn, int32_t gran_k, void* q, float* sf, void* stream) {
     DGB_REQUIRE(k >= 0 && mn > 0 && mn % 2 == 0, "mn (%d) must be a positive even number", mn);
     DGB_REQUIRE(gran_k == 32 || gran_k == 128, "gran_k must be 32 or 128, got %d", gran_k);
@@ -1339,8 +1353,10 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int
     const long long tiles = static_cast<long long>(num_groups) * ((m + 127) / 128) * (n / block_n);
     const int grid = static_cast<int>(std::min<long long>(sms, tiles));
     // the wide tile halves the shared-memory fill per MMA cycle (the 128-wide one is bound by it)
-    if (block_n == 256) return launch_gemm<256, 4, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_a, p, grid, stream);
-    return launch_gemm<128, 6, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_a, p, grid, stream);
+    CUtensorMap tm_out;
+    if ((rc = prepare_k_grouped_output(&tm_out, p, c, d, num_groups, m, n, stream))) return rc;
+    if (block_n == 256) return launch_gemm<256, 4, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
+    return launch_gemm<128, 6, kEpiF32Acc, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
 }
 
 int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const float* c, float* d, const int32_t* ks,
@@ -1389,8 +1405,10 @@ int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const
     if (rc) return rc;
     const long long tiles = static_cast<long long>(num_groups) * ((m + 127) / 128) * (n / block_n);
     const int grid = static_cast<int>(std::min<long long>(sms, tiles));
-    if (block_n == 256) return launch_gemm<256, 4, kEpiF32Acc, kKindBf16>(tm_a, tm_b, tm_a, tm_a, tm_a, p, grid, stream);
-    return launch_gemm<128, 6, kEpiF32Acc, kKindBf16>(tm_a, tm_b, tm_a, tm_a, tm_a, p, grid, stream);
+    CUtensorMap tm_out;
+    if ((rc = prepare_k_grouped_output(&tm_out, p, c, d, num_groups, m, n, stream))) return rc;
+    if (block_n == 256) return launch_gemm<256, 4, kEpiF32Acc, kKindBf16>(tm_a, tm_b, tm_a, tm_a, tm_out, p, grid, stream);
+    return launch_gemm<128, 6, kEpiF32Acc, kKindBf16>(tm_a, tm_b, tm_a, tm_a, tm_out, p, grid, stream);
 }
 
 int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t experts, int32_t topk, int64_t* topk_idx,

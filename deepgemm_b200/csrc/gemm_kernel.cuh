@@ -254,7 +254,7 @@ struct TileScheduler {
     }
 };
 
-template <int BLOCK_N, int kStages, int kKind = kKindFp8Fp4>
+template <int BLOCK_N, int kStages, int kKind = kKindFp8Fp4, bool kAlwaysStaged = false>
 struct GemmSmem {
     static constexpr int kSfIntsPerRow = kKind == kKindNvfp4 ? 4 : 1;  // packed scale ints per row per K block
     static constexpr int kABytes = 128 * 128;
@@ -271,7 +271,8 @@ struct GemmSmem {
     static constexpr int kOffGroups = kOffMisc + 16;
     // Epilogue staging for TMA stores: 32 rows x 64 bytes per epilogue warp, in the 64-byte swizzle (512-byte atoms).
     // The NVFP4 kind only has room for it next to its larger scale-factor stages with 3 pipeline stages.
-    static constexpr int kStageBytesPerWarp = (BLOCK_N == 256 && (kKind != kKindNvfp4 || kStages <= 3)) ? 2048 : 0;
+    static constexpr int kStageBytesPerWarp =
+        (kAlwaysStaged || (BLOCK_N == 256 && (kKind != kKindNvfp4 || kStages <= 3))) ? 2048 : 0;
     static constexpr int kOffStage = (kOffGroups + 3 * kMaxCachedGroups * 4 + 511) / 512 * 512;
     static constexpr int kTotal = kOffStage + 8 * kStageBytesPerWarp;
     static constexpr int kDynamicBytes = kTotal + 1024;  // slack to align the base to 1024 B
@@ -311,8 +312,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                            const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ GemmParams p) {
-    using L = GemmSmem<BLOCK_N, kStages, kKind>;
+    using L = GemmSmem<BLOCK_N, kStages, kKind, EPI == kEpiF32Acc>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
+    static_assert(L::kDynamicBytes <= 232448, "shared memory budget");
     constexpr int kSfInts = L::kSfIntsPerRow;          // scale ints per row per K block = tcgen05.cp blocks per 128 rows
     constexpr int kSfBlocksA = kSfInts;                // 512-byte blocks of A scales per stage
     constexpr int kSfBlocksB = kSfInts * BLOCK_N / 128;
@@ -846,6 +848,30 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     __syncwarp();
                 }
             }
+            if constexpr (EPI == kEpiF32Acc) {
+                // D += accumulator through TMA reductions (FP32 add in the memory system; d already holds c): the warp's
+                // 32 rows x 16 columns per slab, coalesced, and no read of c through the load/store pipe. Row-per-thread
+                // loads and stores of FP32 tiles cost more than the MMAs of a tile with a short K extent.
+                if (via_tma && warp_has_rows && t.num_kb != 0) {
+                    const int x0 = t.n_block * BLOCK_N + static_cast<int>(half) * kCols;
+                    const int y0 = t.group * p.m + t.row_start + static_cast<int>(q) * 32;
+#pragma unroll
+                    for (int c = 0; c < kCols / 16; ++c) {
+                        if (lane == 0) bulk_wait_group_read_all();  // the previous slab has left the staging buffer
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *stage_chunk(i) = make_uint4(acc[c * 16 + i * 4 + 0], acc[c * 16 + i * 4 + 1], acc[c * 16 + i * 4 + 2],
+                                                         acc[c * 16 + i * 4 + 3]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_reduce_add_2d(&tm_out, stage_buf, x0 + c * 16, y0);
+                            bulk_commit_group();
+                        }
+                    }
+                }
+            }
             if constexpr (EPI == kEpiSwiGLUBf16) {
                 // Same column order and arithmetic as the FP8 form below, the outputs stay BF16 (reference:
                 // deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:927-955). One 32-output group is one
@@ -914,7 +940,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 6]), __uint_as_float(acc[i * 8 + 7])));
                     }
                 } else if constexpr (EPI == kEpiF32Acc) {
-                    // D[g] = C[g] + accumulator (an empty group contributes nothing: its accumulator was never written)
+                    // tiles with fewer than 128 rows (the tail of m): D[g] = C[g] + accumulator row by row (an empty group
+                    // contributes nothing: its accumulator was never written)
+                    if (!via_tma) {
                     const long long off = (static_cast<long long>(t.group) * p.m + row) * p.d_row_stride +
                                           static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
                     const float4* src = reinterpret_cast<const float4*>(p.c + off);
@@ -929,6 +957,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         const float a3 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 3]);
                         st_global_v4(dst + i * 4, __float_as_uint(cv.x + a0), __float_as_uint(cv.y + a1),
                                      __float_as_uint(cv.z + a2), __float_as_uint(cv.w + a3));
+                    }
                     }
                 } else if constexpr (EPI == kEpiSwiGLUNvfp4) {
                     // Same column order as below; the 32 outputs of a gate/up pair are requantised to NVFP4: two

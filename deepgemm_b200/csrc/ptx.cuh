@@ -173,6 +173,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  :: "l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
 }
+// Tiled reduction shared -> global: every element of the box is added to the tensor's element (the tensor map's data
+// type, FP32 here) by the memory system; same coordinate rules and completion mechanism as the store above.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once the bulk stores of this thread's committed groups have finished reading shared memory.
 __device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
