@@ -447,11 +447,12 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
-        DGB_REQUIRE(kind == kKindFp8Fp4 && shared_inter % 128 == 0, "shared experts need the FP8 x FP4 layer and a multiple of 128 channels");
+        DGB_REQUIRE((kind == kKindFp8Fp4 || kind == kKindBf16) && shared_inter % 128 == 0,
+                    "shared experts need the FP8 x FP4 or the BF16 layer and a multiple of 128 channels");
         DGB_REQUIRE(max_tokens % 128 == 0, "with shared experts the token capacity must be a multiple of 128");
-        l.shared_x_sf = take(l.token_rows * (hidden / 128) * 4);
-        l.shared_l2_acts = take(l.token_rows * shared_inter);
-        l.shared_l2_sf = take(l.token_rows * (shared_inter / 128) * 4);
+        l.shared_x_sf = take(l.token_rows * sf_ints_per_row(kind, hidden) * 4);
+        l.shared_l2_acts = take(l.token_rows * act_row_bytes(kind, shared_inter));
+        l.shared_l2_sf = take(l.token_rows * sf_ints_per_row(kind, shared_inter) * 4);
         l.shared_out = take(l.token_rows * hidden * 2);
     }
     l.total = off;
@@ -645,14 +646,17 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
 int run_shared_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, int num_tokens, int hidden,
                      float activation_clamp, int fast_math, cudaStream_t stream) {
     const int si = quant.shared_inter;
+    const bool bf16 = quant.kind == kKindBf16;
     int rc = 0;
     {
         GemmCall c{};
+        c.kind = quant.kind;
         c.a = base + l.x;
         c.b = quant.shared_l1_w;
         c.a_rows_total = l.token_rows;
+        c.a_row_stride_bytes = c.b_row_stride_bytes = hidden * 2ll;  // BF16 kind
         c.b_is_fp4 = 0;
-        c.epilogue = kEpiSwiGLU;
+        c.epilogue = bf16 ? kEpiSwiGLUBf16 : kEpiSwiGLU;
         c.whole_tile_stores = 1;
         c.sfa = base + l.shared_x_sf;
         c.sfb = quant.shared_l1_w_sf;
@@ -670,7 +674,7 @@ int run_shared_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base
         p.gran_b = 32;
         p.act_q = base + l.shared_l2_acts;
         p.act_sf = base + l.shared_l2_sf;
-        p.act_q_row_stride = si;
+        p.act_q_row_stride = act_row_bytes(quant.kind, si);
         p.act_sf_k_stride = l.token_rows;
         p.row_weight = nullptr;
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
@@ -681,9 +685,11 @@ int run_shared_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base
     }
     {
         GemmCall c{};
+        c.kind = quant.kind;
         c.a = base + l.shared_l2_acts;
         c.b = quant.shared_l2_w;
         c.a_rows_total = l.token_rows;
+        c.a_row_stride_bytes = c.b_row_stride_bytes = si * 2ll;  // BF16 kind
         c.b_is_fp4 = 0;
         c.epilogue = kEpiBF16;
         c.whole_tile_stores = 1;
@@ -793,7 +799,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                          static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts);
     if (rc) return rc;
     if (with_shared && num_tokens > 0) {
-        if (quant.x_bf16 == nullptr && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
+        if (quant.x_bf16 == nullptr && quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
         if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
     }
     dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, static_cast<int>(epoch0 + 3), kPeerWaitBudgetCycles);
@@ -817,8 +823,8 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
                               quant.shared_inter);
     if (rc) return rc;
     const bool with_shared = quant.shared_inter > 0;
-    DGB_REQUIRE(!with_shared || (quant.shared_l1_w != nullptr && quant.shared_l1_w_sf != nullptr && quant.shared_l2_w != nullptr &&
-                                 quant.shared_l2_w_sf != nullptr),
+    DGB_REQUIRE(!with_shared || (quant.shared_l1_w != nullptr && quant.shared_l2_w != nullptr &&
+                                 (quant.kind == kKindBf16 || (quant.shared_l1_w_sf != nullptr && quant.shared_l2_w_sf != nullptr))),
                 "null shared-expert weight pointer");
     DGB_REQUIRE(rank >= 0 && rank < num_ranks && peer_buffer_ptrs != nullptr &&
                     peer_buffer_ptrs[rank] == reinterpret_cast<uint64_t>(buffer),
@@ -888,7 +894,7 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
                          static_cast<long long>(num_tokens) * num_topk / num_experts);
     if (rc) return rc;
     if (with_shared) {
-        if (quant.x_bf16 == nullptr && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
+        if (quant.x_bf16 == nullptr && quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
         if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
     }
     // 5. combine: y[t] = sum over the top-k slots of the rows the L2 GEMM wrote
@@ -1554,17 +1560,33 @@ int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const 
 }
 
 int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
-                                                    int32_t num_topk, int32_t hidden, int32_t intermediate_hidden, int64_t* out) {
-    return export_mega_layout(kKindBf16, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
-                              intermediate_hidden, out);
+                                                    int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                                    int32_t shared_intermediate_hidden, int64_t* out) {
+    DGB_REQUIRE(out != nullptr && shared_intermediate_hidden >= 0, "null output or negative shared size");
+    MegaLayout l;
+    const int rc = make_mega_layout(kKindBf16, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                                    intermediate_hidden, &l, shared_intermediate_hidden);
+    if (rc) return rc;
+    const long long fields[20] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+                                  l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight,
+                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out};
+    for (int i = 0; i < 20; ++i) out[i] = fields[i];
+    return 0;
 }
 
-int dgb200_bf16_mega_moe(void* y, const void* l1_w, const void* l2_w, int32_t* cumulative_local_expert_recv_stats, void* buffer,
+int dgb200_bf16_mega_moe(void* y, const void* l1_w, const void* l2_w, const void* shared_l1_w, const void* shared_l2_w,
+                         int32_t shared_intermediate_hidden, int32_t* cumulative_local_expert_recv_stats, void* buffer,
                          const uint64_t* peer_buffer_ptrs, int32_t rank, int32_t num_ranks, int32_t num_tokens,
                          int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
                          int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream) {
     LayerQuant quant;
     quant.kind = kKindBf16;
+    DGB_REQUIRE(shared_intermediate_hidden >= 0, "negative shared size");
+    if (shared_intermediate_hidden > 0) {
+        quant.shared_l1_w = shared_l1_w;
+        quant.shared_l2_w = shared_l2_w;
+        quant.shared_inter = shared_intermediate_hidden;
+    }
     return run_mega_moe(quant, y, l1_w, nullptr, l2_w, nullptr, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
                         num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
                         activation_clamp, fast_math, static_cast<cudaStream_t>(stream));

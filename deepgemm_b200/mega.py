@@ -45,7 +45,7 @@ def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hi
     elif mma_type == 'bf16xbf16':
         _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_bf16_mega_moe(
             num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-            ctypes.cast(words, ctypes.c_void_p)))
+            shared_intermediate_hidden, ctypes.cast(words, ctypes.c_void_p)))
     else:
         _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe(
             num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
@@ -67,8 +67,8 @@ class SymmBuffer:
             raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
         if mma_type not in _MMA_TYPES:
             raise RuntimeError(f'MMA type must be one of {_MMA_TYPES}, got `{mma_type}`')
-        if num_shared_experts < 0 or (num_shared_experts > 0 and mma_type != 'fp8xfp4'):
-            raise RuntimeError('shared experts need num_shared_experts >= 0 and the `fp8xfp4` MMA type')
+        if num_shared_experts < 0 or (num_shared_experts > 0 and mma_type not in ('fp8xfp4', 'bf16xbf16')):
+            raise RuntimeError('shared experts need num_shared_experts >= 0 and the `fp8xfp4` or `bf16xbf16` MMA type')
         self.num_shared_experts = num_shared_experts
         self.group = group
         self.num_ranks = 1 if group is None else group.size()
@@ -164,8 +164,10 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     if activation != 'swiglu':
         raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
     if not isinstance(l1_weights, tuple):  # BF16 weights: only the gate/up interleave
-        if l1_weights.dtype != torch.bfloat16 or l2_weights.dtype != torch.bfloat16 or l1_weights.dim() != 3:
-            raise RuntimeError('bare weight tensors must be bfloat16 [E, N, K]')
+        if l1_weights.dtype != torch.bfloat16 or l2_weights.dtype != torch.bfloat16 or l1_weights.dim() not in (2, 3):
+            raise RuntimeError('bare weight tensors must be bfloat16 [E, N, K] (or [N, K] for shared experts)')
+        if l1_weights.dim() == 2:
+            return _interleave_rows(l1_weights.unsqueeze(0), _GATE_UP_INTERLEAVE)[0].contiguous(), l2_weights
         return _interleave_rows(l1_weights, _GATE_UP_INTERLEAVE).contiguous(), l2_weights
     if l1_weights[0].dim() == 2:  # shared experts: one FP8 matrix per layer, same reordering
         t1, t2 = transform_weights_for_mega_moe(tuple(t.unsqueeze(0) for t in l1_weights),
@@ -316,12 +318,21 @@ def bf16_mega_moe(y: torch.Tensor, l1_weights: torch.Tensor, l2_weights: torch.T
 
     ``sym_buffer`` must have been created with ``mma_type='bf16xbf16'``; the caller writes ``x`` (bfloat16), ``topk_idx``
     and ``topk_weights``. Weights are bfloat16 [E_local, 2 * inter, hidden] / [E_local, hidden, inter] passed through
-    ``transform_weights_for_mega_moe``. Shared experts are not built for this form."""
+    ``transform_weights_for_mega_moe``; shared experts likewise as 2-D tensors [2 * SI, hidden] / [hidden, SI] with
+    SI = intermediate_hidden * num_shared_experts of the buffer."""
     if activation != 'swiglu':
         raise RuntimeError(f'Only `swiglu` activation is supported, got `{activation}`')
-    if shared_l1_weights is not None or shared_l2_weights is not None:
-        raise RuntimeError('shared experts are not built for the BF16 layer')
+    if (shared_l1_weights is None) != (shared_l2_weights is None):
+        raise RuntimeError('shared_l1_weights and shared_l2_weights must be given together')
     b = sym_buffer
+    shared_inter = 0
+    if shared_l1_weights is not None:
+        shared_inter = b.intermediate_hidden * b.num_shared_experts
+        for w, shape, name in ((shared_l1_weights, (2 * shared_inter, b.hidden), 'shared_l1_weights'),
+                               (shared_l2_weights, (b.hidden, shared_inter), 'shared_l2_weights')):
+            if shared_inter == 0 or not (w.is_cuda and w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == shape):
+                raise RuntimeError(f'{name} must be a contiguous CUDA bfloat16 tensor of shape {shape} '
+                                   '(the buffer must have been created with num_shared_experts > 0)')
     if b.mma_type != 'bf16xbf16':
         raise RuntimeError(f'the buffer was created for `{b.mma_type}`')
     num_local = b.num_experts // b.num_ranks
@@ -338,7 +349,8 @@ def bf16_mega_moe(y: torch.Tensor, l1_weights: torch.Tensor, l2_weights: torch.T
     p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
     with torch.cuda.device(y.device):
         _lib.check(_lib.lib().dgb200_bf16_mega_moe(
-            p(y), p(l1_weights), p(l2_weights), p(stats), p(b.buffer), ctypes.cast(ptrs, ctypes.c_void_p), b.rank,
+            p(y), p(l1_weights), p(l2_weights), p(shared_l1_weights), p(shared_l2_weights), shared_inter, p(stats), p(b.buffer),
+            ctypes.cast(ptrs, ctypes.c_void_p), b.rank,
             b.num_ranks, y.size(0), b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden,
             b.intermediate_hidden, float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math),
             _lib.current_stream_ptr()))

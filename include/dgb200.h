@@ -301,11 +301,16 @@ int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num
  * caller writes x (bf16 [T, hidden]); the scale-factor regions are empty. Stages as in dgb200_fp8_fp4_mega_moe with BF16
  * rows throughout: l1_w bf16 [E_local, 2 * inter, hidden] (gate/up interleaved by 128), l2_w bf16 [E_local, hidden, inter];
  * the gate/up GEMM's epilogue writes silu(gate) * up * topk_weight as BF16. hidden and inter must be multiples of 128.
- * Reference: bf16_mega_moe, csrc/apis/mega.hpp:288-400 and deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:52;
- * shared experts are not built for this form. */
+ * Shared experts (shared_intermediate_hidden > 0): shared_l1_w bf16 [2 * shared_inter, hidden] (interleaved likewise),
+ * shared_l2_w bf16 [hidden, shared_inter], a dense MLP over this rank's tokens with routing weight 1 whose rows are one
+ * more combine slot; the token capacity must then be a multiple of 128. out[20] as in
+ * dgb200_get_symm_buffer_layout_for_mega_moe_ex.
+ * Reference: bf16_mega_moe, csrc/apis/mega.hpp:288-400 and deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:52. */
 int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
-                                                    int32_t num_topk, int32_t hidden, int32_t intermediate_hidden, int64_t* out);
-int dgb200_bf16_mega_moe(void* y, const void* l1_w, const void* l2_w, int32_t* cumulative_local_expert_recv_stats, void* buffer,
+                                                    int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
+                                                    int32_t shared_intermediate_hidden, int64_t* out);
+int dgb200_bf16_mega_moe(void* y, const void* l1_w, const void* l2_w, const void* shared_l1_w, const void* shared_l2_w,
+                         int32_t shared_intermediate_hidden, int32_t* cumulative_local_expert_recv_stats, void* buffer,
                          const uint64_t* peer_buffer_ptrs, int32_t rank, int32_t num_ranks, int32_t num_tokens,
                          int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
                          int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream);

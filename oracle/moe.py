@@ -136,8 +136,15 @@ def swiglu_bf16(gate_up: torch.Tensor, weight: torch.Tensor, clamp: Optional[flo
     return (gate / (1.0 + torch.exp(-gate)) * up * weight.float().unsqueeze(1)).bfloat16()
 
 
+def shared_expert_rows_bf16(x: torch.Tensor, s1: torch.Tensor, s2: torch.Tensor, clamp: Optional[float] = None) -> torch.Tensor:
+    """Shared experts of the BF16 layer: dense MLP over every token with routing weight 1, s1 [2 SI, H] rows [gate | up],
+    s2 [H, SI] (shared_l1_weights / shared_l2_weights of bf16_mega_moe, csrc/apis/mega.hpp:288-400). Returns bf16 [T, H]."""
+    a2 = swiglu_bf16(x.float() @ s1.float().T, torch.ones(x.shape[0]), clamp)
+    return (a2.float() @ s2.float().T).bfloat16()
+
+
 def moe_layer_bf16(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
-                   clamp: Optional[float] = None) -> torch.Tensor:
+                   clamp: Optional[float] = None, shared_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The layer of moe_layer with bfloat16 activations and weights (bf16_mega_moe, csrc/apis/mega.hpp:288-400):
     x [T, H], w1 [E, 2I, H] rows [gate | up], w2 [E, H, I]; FP32 accumulation, BF16 rows between the stages, the same
     combine."""
@@ -154,6 +161,8 @@ def moe_layer_bf16(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.
     y = torch.zeros((tokens, hidden), dtype=torch.float32)
     for k in range(topk):
         y += torch.where(valid[:, k, None], slot_rows[:, k].float(), torch.zeros(()))
+    if shared_rows is not None:
+        y += shared_rows.float()
     return y.bfloat16()
 
 

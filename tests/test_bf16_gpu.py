@@ -164,3 +164,32 @@ def test_bf16_layer_matches_oracle(dg, tokens, hidden, inter, experts, topk, cla
     assert quant.calc_diff(got, want) < 1e-4
     counts = torch.bincount(idx[idx >= 0].reshape(-1), minlength=experts).int()
     assert torch.equal(stats.cpu(), 2 * counts)
+
+
+@pytest.mark.parametrize('tokens,num_shared', [(256, 1), (100, 2)])
+def test_bf16_layer_with_shared_experts(dg, tokens, num_shared):
+    from oracle import moe as omoe
+    hidden, inter, experts, topk = 512, 128, 8, 2
+    x, w1, w2, idx, w = _layer_case(tokens, hidden, inter, experts, topk, seed=tokens + 7, masked_ratio=0.1)
+    si = inter * num_shared
+    s1 = (torch.randn(2 * si, hidden) * 0.05).bfloat16()
+    s2 = (torch.randn(hidden, si) * 0.05).bfloat16()
+    want = omoe.moe_layer_bf16(x, idx, w, w1, w2, shared_rows=omoe.shared_expert_rows_bf16(x, s1, s2))
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_shared_experts=num_shared,
+                                          mma_type='bf16xbf16')
+    buf.x[:tokens].copy_(x.cuda())
+    buf.topk_idx[:tokens].copy_(idx.cuda())
+    buf.topk_weights[:tokens].copy_(w.cuda())
+    l1, l2 = dg.transform_weights_for_mega_moe(w1.cuda(), w2.cuda())
+    sl1, sl2 = dg.transform_weights_for_mega_moe(s1.cuda(), s2.cuda())
+    y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+    dg.bf16_mega_moe(y, l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2)
+    _finish()
+    got = y.cpu()
+    assert not torch.isnan(got.float()).any()
+    assert quant.calc_diff(got, want) < 1e-4
+    # the same buffer without the shared experts
+    y2 = torch.full_like(y, float('nan'))
+    dg.bf16_mega_moe(y2, l1, l2, buf)
+    _finish()
+    assert quant.calc_diff(y2.cpu(), omoe.moe_layer_bf16(x, idx, w, w1, w2)) < 1e-4
