@@ -42,3 +42,20 @@ def test_transform_keeps_shapes_and_handles_shared_2d_weights():
     s2 = (torch.zeros((hidden, inter), dtype=torch.float8_e4m3fn), torch.zeros((inter // 128, hidden), dtype=torch.int32).t())
     u1, u2 = mega.transform_weights_for_mega_moe(s1, s2)
     assert u1[0].shape == s1[0].shape and u1[1].shape == s1[1].shape and u2[0].dtype == torch.float8_e4m3fn
+
+
+def test_bf16_weights_only_get_the_gate_up_interleave():
+    """bfloat16 layer weights (bare tensors, 3-D per expert or 2-D for shared experts): L1 rows interleaved by 128,
+    L2 untouched (reference: transform_weights_for_mega_moe on bare tensors, deep_gemm/mega/__init__.py:131-149)."""
+    import pytest
+    e, inter, hidden = 3, 256, 64
+    w1 = torch.arange(e * 2 * inter, dtype=torch.float32).view(e, 2 * inter, 1).repeat(1, 1, hidden).bfloat16()
+    w2 = torch.randn(e, hidden, inter).bfloat16()
+    t1, t2 = mega.transform_weights_for_mega_moe(w1, w2)
+    assert t1.is_contiguous() and t1.shape == w1.shape and t2 is w2
+    assert torch.equal(t1, mega._interleave_rows(w1, 128))
+    assert torch.equal(t1[:, 128:256], w1[:, inter:inter + 128]) and torch.equal(t1[:, 256:384], w1[:, 128:256])
+    s1, s2 = mega.transform_weights_for_mega_moe(w1[0], w2[0])
+    assert torch.equal(s1, t1[0]) and s2.shape == w2[0].shape
+    with pytest.raises(RuntimeError):
+        mega.transform_weights_for_mega_moe(w1.float(), w2)
