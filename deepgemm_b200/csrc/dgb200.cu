@@ -1332,11 +1332,9 @@ int dgb200_k_grouped_fp8_gemm_tn_contiguous(const void* a, const float* sfa, int
     p.kg_psum = use_psum_layout ? 1 : 0;
     p.gran_a = p.gran_b = gran_k;
     p.b_fmt = kFmtE4M3;
-    // Wide tiles halve the shared-memory fill per MMA cycle, which bounds the 128-wide tile (measured 1.29 -> 1.40 PFLOP/s
-    // at 32 K blocks per group); with short K extents the FP32 epilogue dominates and the 128-wide tile's two
-    // accumulators, which let it overlap the next tile's MMAs, win instead.
-    const int block_n = tuning().block_n != 0 ? tuning().block_n
-                                              : ((n % 256 == 0 && sum_k / 128 / num_groups >= 16) ? 256 : 128);
+    // Wide tiles halve the shared-memory fill per MMA cycle, which bounds the 128-wide tile (measured 1.1 - 1.8 vs
+    // 1.7 - 2.0 PFLOP/s over 1024 .. 8192 K rows per group).
+    const int block_n = tuning().block_n != 0 ? tuning().block_n : (n % 256 == 0 ? 256 : 128);
     DGB_REQUIRE(n % block_n == 0, "block_n %d does not divide n %d", block_n, n);
     p.b_tx_bytes = block_n * 128;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
@@ -1396,7 +1394,7 @@ int dgb200_k_grouped_bf16_gemm_tn_contiguous(const void* a, const void* b, const
     p.kg_psum = use_psum_layout ? 1 : 0;
     p.gran_a = p.gran_b = 32;
     p.sf_transposed = 1;
-    const int block_n = tuning().block_n != 0 ? tuning().block_n : ((n % 256 == 0 && sum_k / 64 / num_groups >= 16) ? 256 : 128);
+    const int block_n = tuning().block_n != 0 ? tuning().block_n : (n % 256 == 0 ? 256 : 128);
     DGB_REQUIRE(n % block_n == 0, "block_n %d does not divide n %d", block_n, n);
     p.b_tx_bytes = block_n * 128;
     CUtensorMap tm_a, tm_b;
