@@ -42,13 +42,13 @@ _SIGNATURES = {
     'dgb200_m_grouped_bf16_gemm_nt_contiguous': [_ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32, _i32,
                                                  _i32, _i32, _ptr],
     'dgb200_m_grouped_bf16_gemm_nt_masked': [_ptr, _ptr, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
-    'dgb200_bf16_gemm_nt': [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_bf16_gemm_nt': [_ptr, _i64, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_k_grouped_bf16_gemm_tn_contiguous': [_ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_per_channel_cast_to_fp8': [_ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr],
     'dgb200_k_grouped_sf_workspace_bytes': [_i32, _i32, _i32, _i32],
     'dgb200_k_grouped_fp8_gemm_tn_contiguous': [_ptr, _ptr, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i32, _i32, _i32, _i32, _i32,
                                                 _i32, _ptr, _ptr],
-    'dgb200_fp8_fp4_gemm_nt': [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_fp8_fp4_gemm_nt': [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_segment_alignment_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],

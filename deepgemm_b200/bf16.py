@@ -7,6 +7,7 @@ from typing import Optional
 import torch
 
 from . import _lib
+from .gemm import _prepare_accumulator
 from .runtime import get_mk_alignment_for_contiguous_layout
 
 
@@ -32,10 +33,8 @@ def _check_out(d: torch.Tensor, shape, allow_fp32: bool):
 def bf16_gemm_nt(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[torch.Tensor] = None,
                  compiled_dims: str = 'nk') -> None:
     """Dense D = A @ B.T, a [M, K], b [N, K] bfloat16, d bfloat16 or float32.
-    Reference: bf16_gemm_nt, csrc/apis/gemm.hpp:404-438. The accumulator input ``c`` is not built."""
+    With ``c`` (float32, float32 d): d = c + a @ b.T. Reference: bf16_gemm_nt, csrc/apis/gemm.hpp:404-438."""
     del compiled_dims
-    if c is not None:
-        raise RuntimeError('accumulation into c is not built')
     m, k = _check_bf16(a, 2, 'a')
     n, k_ = _check_bf16(b, 2, 'b')
     if k != k_:
@@ -43,9 +42,10 @@ def bf16_gemm_nt(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[
     _check_out(d, (m, n), True)
     if m == 0:
         return
+    accumulate = _prepare_accumulator(c, d)
     with torch.cuda.device(d.device):
         _lib.check(_lib.lib().dgb200_bf16_gemm_nt(_p(a), a.stride(0), _p(b), b.stride(0), _p(d), d.stride(0), m, n, k,
-                                                  int(d.dtype == torch.float32), _lib.current_stream_ptr()))
+                                                  int(d.dtype == torch.float32), accumulate, _lib.current_stream_ptr()))
 
 
 def bf16_gemm_nn(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[torch.Tensor] = None,

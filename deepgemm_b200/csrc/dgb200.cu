@@ -1061,8 +1061,10 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
 
 int dgb200_fp8_fp4_gemm_nt(const void* a, const void* sfa, int64_t sfa_k_stride, const void* b, const void* sfb,
                            int64_t sfb_k_stride, void* d, int64_t d_row_stride, int32_t m, int32_t n, int32_t k,
-                           int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream) {
+                           int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, int32_t accumulate,
+                           void* stream) {
     DGB_REQUIRE(m >= 0, "m must be >= 0");
+    DGB_REQUIRE(!accumulate || d_is_fp32, "accumulation needs a float32 d");
     DGB_REQUIRE(d != nullptr || m == 0, "null output");
     DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
                 "d row stride must cover n and keep rows 16-byte aligned");
@@ -1089,6 +1091,7 @@ int dgb200_fp8_fp4_gemm_nt(const void* a, const void* sfa, int64_t sfa_k_stride,
     p.alignment = 128;
     p.gran_a = gran_k_a;
     p.gran_b = gran_k_b;
+    p.accumulate = accumulate ? 1 : 0;
     const long long m_blocks = (static_cast<long long>(m) + 127) / 128;
     c.max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
     return run_gemm(c, static_cast<cudaStream_t>(stream));
@@ -1139,7 +1142,7 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
 namespace {
 // Shared body of the BF16 GEMM entry points: A [rows, k] and B [num_groups * n, k] BF16 K-major, D BF16 or FP32.
 int run_bf16_gemm(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
-                  int32_t d_is_fp32, const int32_t* layout, int mode, long long a_rows_total, int32_t m, int32_t n, int32_t k,
+                  int32_t d_is_fp32, int32_t accumulate, const int32_t* layout, int mode, long long a_rows_total, int32_t m, int32_t n, int32_t k,
                   int32_t num_groups, int32_t alignment, int32_t store_padding, int max_tiles, void* stream) {
     DGB_REQUIRE(d != nullptr || a_rows_total == 0, "null output");
     DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
@@ -1166,6 +1169,8 @@ int run_bf16_gemm(const void* a, int64_t a_row_stride, const void* b, int64_t b_
     p.num_groups = num_groups;
     p.alignment = alignment;
     p.store_padding = store_padding;
+    p.accumulate = accumulate ? 1 : 0;
+    DGB_REQUIRE(!accumulate || d_is_fp32, "accumulation needs a float32 d");
     c.max_tiles = max_tiles;
     return run_gemm(c, static_cast<cudaStream_t>(stream));
 }
@@ -1184,7 +1189,7 @@ int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride
     const int mode = layout_kind == DGB200_LAYOUT_PSUM ? kModePsum : kModeRowIds;
     const long long m_blocks = (static_cast<long long>(m) + 127) / 128 + (mode == kModePsum ? num_groups : 0);
     const int max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
-    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, d, d_row_stride, d_is_fp32, grouped_layout, mode, m, m, n, k,
+    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, d, d_row_stride, d_is_fp32, 0, grouped_layout, mode, m, m, n, k,
                          num_groups, alignment, store_padding, max_tiles, stream);
 }
 
@@ -1193,16 +1198,16 @@ int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, 
                                          int32_t d_is_fp32, void* stream) {
     (void)expected_m;
     DGB_REQUIRE(max_m > 0 && max_m % 4 == 0, "max_m (%d) must be a positive multiple of 4", max_m);
-    return run_bf16_gemm(a, k, b, k, d, d_row_stride, d_is_fp32, masked_m, kModeMasked,
+    return run_bf16_gemm(a, k, b, k, d, d_row_stride, d_is_fp32, 0, masked_m, kModeMasked,
                          static_cast<long long>(num_groups) * max_m, max_m, n, k, num_groups, 4, 0, 0, stream);
 }
 
 int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
-                        int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, void* stream) {
+                        int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, int32_t accumulate, void* stream) {
     DGB_REQUIRE(m >= 0, "m must be >= 0");
     const long long m_blocks = (static_cast<long long>(m) + 127) / 128;
     const int max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
-    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, d, d_row_stride, d_is_fp32, nullptr, kModeDense, m, m, n, k, 1, 128,
+    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, d, d_row_stride, d_is_fp32, accumulate, nullptr, kModeDense, m, m, n, k, 1, 128,
                          0, max_tiles, stream);
 }
 

@@ -104,6 +104,7 @@ struct GemmParams {
     const float* b_scales;
     const float* out_scale;
     const float* c;  // kEpiF32Acc: accumulator input [G, m, n] (may alias d)
+    int accumulate;  // kEpiF32 only: d += accumulator instead of d = accumulator (the dense GEMMs' input c, already in d)
     int kg_psum;     // kModeKGrouped: layout[g] is the end K row of group g (groups start at multiples of `alignment`,
                      // the gap rows are zero) instead of its K extent
 };
@@ -926,9 +927,20 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     const long long col0 = static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
                     if constexpr (EPI == kEpiF32) {
                         float* dst = reinterpret_cast<float*>(p.d) + row * p.d_row_stride + col0;
+                        if (p.accumulate) {
 #pragma unroll
-                        for (int i = 0; i < kCols / 4; ++i)
-                            st_global_v4(dst + i * 4, acc[i * 4 + 0], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]);
+                            for (int i = 0; i < kCols / 4; ++i) {
+                                const float4 old = *reinterpret_cast<const float4*>(dst + i * 4);
+                                st_global_v4(dst + i * 4, __float_as_uint(old.x + __uint_as_float(acc[i * 4 + 0])),
+                                             __float_as_uint(old.y + __uint_as_float(acc[i * 4 + 1])),
+                                             __float_as_uint(old.z + __uint_as_float(acc[i * 4 + 2])),
+                                             __float_as_uint(old.w + __uint_as_float(acc[i * 4 + 3])));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < kCols / 4; ++i)
+                                st_global_v4(dst + i * 4, acc[i * 4 + 0], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]);
+                        }
                     } else if (!via_tma) {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col0;
 #pragma unroll

@@ -27,6 +27,18 @@ def _check_ab(t: torch.Tensor, rank: int, name: str):
     return tuple(t.shape[:-1]) + (k,)
 
 
+def _prepare_accumulator(c, d):
+    """The reference's accumulator input (csrc/apis/gemm.hpp:73-124, :404-438; its tests pass c with a float32 d):
+    d = c + a @ b.T. The kernel adds into d, so c is first copied there unless it is d itself. Returns the flag."""
+    if c is None:
+        return 0
+    if d.dtype != torch.float32 or c.dtype != torch.float32 or tuple(c.shape) != tuple(d.shape) or not c.is_cuda:
+        raise RuntimeError('c must be a CUDA float32 tensor of the shape of a float32 d')
+    if c.data_ptr() != d.data_ptr():
+        d.copy_(c)
+    return 1
+
+
 def _check_d(d: torch.Tensor, shape):
     if tuple(d.shape) != tuple(shape):
         raise RuntimeError(f'd has shape {tuple(d.shape)}, expected {tuple(shape)}')
@@ -39,10 +51,8 @@ def fp8_fp4_gemm_nt(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor,
                     recipe_a: Optional[Tuple[int, int]] = None, recipe_b: Optional[Tuple[int, int]] = None,
                     compiled_dims: str = 'nk', disable_ue8m0_cast: bool = False) -> None:
     """Dense D = A @ B.T with a [M, K] FP8 and b [N, K] FP8 or packed FP4; d bfloat16 or float32.
-    Reference: fp8_fp4_gemm_nt, csrc/apis/gemm.hpp:73-124. The accumulator input ``c`` is not built."""
+    With ``c`` (float32, float32 d): d = c + a @ b.T. Reference: fp8_fp4_gemm_nt, csrc/apis/gemm.hpp:73-124."""
     del compiled_dims
-    if c is not None:
-        raise RuntimeError('accumulation into c is not built')
     a_q, a_sf = a
     b_q, b_sf = b
     if a_q.dtype != torch.float8_e4m3fn:
@@ -55,12 +65,13 @@ def fp8_fp4_gemm_nt(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor,
         raise RuntimeError(f'd must be a CUDA bfloat16 / float32 [{m}, {n}] tensor with unit stride on N')
     if m == 0:
         return
+    accumulate = _prepare_accumulator(c, d)
     sfa, sfb, gran_a, gran_b = transform_sf_pair_into_required_layout(
         a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, None, disable_ue8m0_cast)
     with torch.cuda.device(d.device):
         _lib.check(_lib.lib().dgb200_fp8_fp4_gemm_nt(
             _p(a_q), _p(sfa), sfa.stride(-1), _p(b_q), _p(sfb), sfb.stride(-1), _p(d), d.stride(0), m, n, k, gran_a, gran_b,
-            int(b_q.dtype == kPackedFP4), int(d.dtype == torch.float32), _lib.current_stream_ptr()))
+            int(b_q.dtype == kPackedFP4), int(d.dtype == torch.float32), accumulate, _lib.current_stream_ptr()))
 
 
 def fp8_fp4_gemm_nn(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = 'nk',

@@ -83,11 +83,13 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
     int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
     int32_t layout_kind, int32_t alignment, int32_t store_padding, void* stream);
 
-/* Dense D = A . B^T (one group, no layout array); operands and scales as in the grouped form above.
- * Reference: fp8_fp4_gemm_nt, csrc/apis/gemm.hpp:73-124 (its optional accumulator input `c` is not built). */
+/* Dense D = A . B^T (one group, no layout array); operands and scales as in the grouped form above. accumulate != 0
+ * (float32 d only): D += A . B^T, the reference's accumulator input `c` after the caller has put c into d.
+ * Reference: fp8_fp4_gemm_nt, csrc/apis/gemm.hpp:73-124. */
 int dgb200_fp8_fp4_gemm_nt(const void* a, const void* sfa, int64_t sfa_k_stride, const void* b, const void* sfb,
                            int64_t sfb_k_stride, void* d, int64_t d_row_stride, int32_t m, int32_t n, int32_t k,
-                           int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, void* stream);
+                           int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32, int32_t accumulate,
+                           void* stream);
 
 /* Masked layout: a [G, max_m, k], d [G, max_m, n], only rows < masked_m[g] of each group are computed and
  * written (stores are clipped at masked_m[g]; the reference writes whole tiles, see
@@ -106,7 +108,7 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
  * BF16 K-major with row strides in elements (multiples of 8), d BF16 or FP32, layouts as above. Requires k % 64 == 0 and
  * n % 128 == 0.
  * Reference: m_grouped_bf16_gemm_nt_contiguous csrc/apis/gemm.hpp:464-517, m_grouped_bf16_gemm_nt_masked :528-564,
- * bf16_gemm_nt :404-438 (its optional accumulator input `c` is not built). */
+ * bf16_gemm_nt :404-438 (accumulate as in dgb200_fp8_fp4_gemm_nt). */
 int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d,
                                              int64_t d_row_stride, const int32_t* grouped_layout, int32_t m, int32_t n,
                                              int32_t k, int32_t num_groups, int32_t d_is_fp32, int32_t layout_kind,
@@ -115,7 +117,7 @@ int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, 
                                          int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
                                          int32_t d_is_fp32, void* stream);
 int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, void* d, int64_t d_row_stride,
-                        int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, void* stream);
+                        int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, int32_t accumulate, void* stream);
 
 /* Operand quantiser of the K-grouped GEMM: x bf16 [k, mn] contiguous -> q e4m3 [k, mn] and sf float [k / gran_k, mn], one
  * power-of-two scale per gran_k (32 or 128) K rows and channel; k % gran_k == 0, mn even.

@@ -106,6 +106,12 @@ def test_dense(dg, m, n, k, out):
     dg.bf16_gemm_nn(a, b.transpose(0, 1), d2)
     _finish()
     assert torch.equal(d2, d)
+    if out == torch.float32:  # the accumulator input: d = c + a @ b.T
+        c = torch.randn(m, n, device='cuda') * 3
+        d3 = torch.full_like(d, float('nan'))
+        dg.bf16_gemm_nt(a, b, d3, c=c)
+        _finish()
+        assert torch.equal(d3, c + d)
 
 
 def test_rejected_inputs(dg):
@@ -117,7 +123,7 @@ def test_rejected_inputs(dg):
     with pytest.raises(RuntimeError):
         dg.bf16_gemm_nt(a.float(), b, d)
     with pytest.raises(RuntimeError):
-        dg.bf16_gemm_nt(a, b, d, c=d)
+        dg.bf16_gemm_nt(a, b, d, c=d)  # accumulation needs a float32 d
 
 
 # ----------------------------------------------------------------------------------------------------------------

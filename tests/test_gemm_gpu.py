@@ -215,6 +215,17 @@ def test_dense_gemm(dg, m, n, k, b_fp4, out):
     _finish(dg)
     assert not torch.isnan(d.float()).any()
     assert quant.calc_diff(d.cpu().float(), want.float()) <= (FP4_TOL if b_fp4 else FP8_TOL)
-    with pytest.raises(RuntimeError):
-        dg.fp8_fp4_gemm_nt((a_q.cuda(), a_sf.cuda()), (b_q[0].cuda(), b_sf[0].cuda()), d, c=d, recipe_a=(1, 128),
-                           recipe_b=(1, 32 if b_fp4 else 128))
+    args = ((a_q.cuda(), a_sf.cuda()), (b_q[0].cuda(), b_sf[0].cuda()))
+    recipes = dict(recipe_a=(1, 128), recipe_b=(1, 32 if b_fp4 else 128))
+    if out == torch.float32:
+        # the accumulator input: d = c + a @ b.T, c given separately or as d itself
+        c = torch.randn(m, n, device='cuda') * 3
+        d2 = torch.full_like(d, float('nan'))
+        dg.fp8_fp4_gemm_nt(*args, d2, c=c, **recipes)
+        d3 = c.clone()
+        dg.fp8_fp4_gemm_nt(*args, d3, c=d3, **recipes)
+        _finish(dg)
+        assert torch.equal(d2, c + d) and torch.equal(d3, d2)
+    else:
+        with pytest.raises(RuntimeError):
+            dg.fp8_fp4_gemm_nt(*args, d, c=d, **recipes)  # accumulation needs float32
