@@ -94,3 +94,47 @@ def test_shared_expert_rows_add_after_the_topk_slots():
         acc += acc2[i].bfloat16().float()
     assert torch.equal(y1[0], (acc + shared[0].float()).bfloat16())
     assert not torch.equal(y0, y1)
+
+
+def test_bf16_layer_oracle_against_a_dense_evaluation():
+    """moe_layer_bf16 (per-expert gather form) against evaluating every expert on every token and selecting."""
+    import torch
+    from oracle import moe as omoe
+    torch.manual_seed(11)
+    tokens, hidden, inter, experts, topk = 37, 64, 32, 5, 2
+    x = torch.randn(tokens, hidden).bfloat16()
+    w1 = (torch.randn(experts, 2 * inter, hidden) * 0.1).bfloat16()
+    w2 = (torch.randn(experts, hidden, inter) * 0.1).bfloat16()
+    idx, w = omoe.route_sigmoid_topk(torch.randn(tokens, experts), topk)
+    idx[3, 1] = -1  # a masked slot
+    s1 = (torch.randn(2 * inter, hidden) * 0.1).bfloat16()
+    s2 = (torch.randn(hidden, inter) * 0.1).bfloat16()
+    shared = omoe.shared_expert_rows_bf16(x, s1, s2)
+    got = omoe.moe_layer_bf16(x, idx, w, w1, w2, clamp=1.0, shared_rows=shared)
+    y = torch.zeros(tokens, hidden)
+    for k in range(topk):
+        for t in range(tokens):
+            e = int(idx[t, k])
+            if e < 0:
+                continue
+            a2 = omoe.swiglu_bf16(x[t:t + 1].float() @ w1[e].float().T, w[t:t + 1, k], 1.0)
+            y[t] += (a2.float() @ w2[e].float().T).bfloat16().float()[0]
+    y += shared.float()
+    assert torch.equal(got, y.bfloat16())
+
+
+def test_k_grouped_oracle_layouts_agree():
+    """Plain K extents and the psum layout describe the same split when every extent is a multiple of the alignment."""
+    import torch
+    from oracle import gemm as ogemm
+    from oracle import quant
+    torch.manual_seed(5)
+    ks, m, n = [256, 0, 128], 24, 16
+    a, b = torch.randn(sum(ks), m).bfloat16(), torch.randn(sum(ks), n).bfloat16()
+    a_q, a_sf = quant.quantize_fp8_per_channel(a, 128)
+    b_q, b_sf = quant.quantize_fp8_per_channel(b, 128)
+    c = torch.randn(len(ks), m, n)
+    d1 = ogemm.k_grouped_gemm(a_q, a_sf, b_q, b_sf, c, ks)
+    d2 = ogemm.k_grouped_gemm_psum(a_q, a_sf, b_q, b_sf, c, [256, 256, 384], 128)
+    assert torch.equal(d1, d2) and torch.equal(d1[1], c[1])
+    assert not torch.equal(d1[0], c[0])
