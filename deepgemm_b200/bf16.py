@@ -15,12 +15,22 @@ def _p(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def _check_bf16(t: torch.Tensor, rank: int, name: str):
+def _check_bf16(t: torch.Tensor, rank: int, name: str, allow_mn_major: bool = False):
     if not t.is_cuda or t.dim() != rank or t.dtype != torch.bfloat16:
         raise RuntimeError(f'{name} must be a {rank}-D CUDA bfloat16 tensor')
-    if t.stride(-1) != 1:
+    if t.stride(-1) != 1 and not (allow_mn_major and t.stride(-2) == 1):
         raise RuntimeError(f'{name} must be K-major')
     return tuple(t.shape)
+
+
+def _b_major(b: torch.Tensor, name: str):
+    """(mn_major flag, row stride in elements) of a weight operand [.., N, K]: K contiguous, or N contiguous (a transposed
+    view of [.., K, N] storage, the operand of the reference's "nn" forms)."""
+    if b.stride(-1) == 1:
+        return 0, b.stride(-2)
+    if b.stride(-2) == 1:
+        return 1, b.stride(-1)
+    raise RuntimeError(f'{name} must be contiguous along K or along N')
 
 
 def _check_out(d: torch.Tensor, shape, allow_fp32: bool):
@@ -36,21 +46,23 @@ def bf16_gemm_nt(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[
     With ``c`` (float32, float32 d): d = c + a @ b.T. Reference: bf16_gemm_nt, csrc/apis/gemm.hpp:404-438."""
     del compiled_dims
     m, k = _check_bf16(a, 2, 'a')
-    n, k_ = _check_bf16(b, 2, 'b')
+    n, k_ = _check_bf16(b, 2, 'b', allow_mn_major=True)
     if k != k_:
         raise RuntimeError(f'K mismatch: a has {k}, b has {k_}')
     _check_out(d, (m, n), True)
     if m == 0:
         return
     accumulate = _prepare_accumulator(c, d)
+    b_mn, b_stride = _b_major(b, 'b')
     with torch.cuda.device(d.device):
-        _lib.check(_lib.lib().dgb200_bf16_gemm_nt(_p(a), a.stride(0), _p(b), b.stride(0), _p(d), d.stride(0), m, n, k,
+        _lib.check(_lib.lib().dgb200_bf16_gemm_nt(_p(a), a.stride(0), _p(b), b_stride, b_mn, _p(d), d.stride(0), m, n, k,
                                                   int(d.dtype == torch.float32), accumulate, _lib.current_stream_ptr()))
 
 
 def bf16_gemm_nn(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[torch.Tensor] = None,
                  compiled_dims: str = 'nk') -> None:
-    """b given as [K, N] over K-major storage (reference: csrc/apis/gemm.hpp:440-446 transposes and calls the NT form)."""
+    """b given as [K, N] (reference: csrc/apis/gemm.hpp:440-446 transposes the view and calls the NT form): a row-major
+    [K, N] tensor is an MN-major operand and is read as such."""
     bf16_gemm_nt(a, b.transpose(0, 1), d, c, compiled_dims)
 
 
@@ -61,11 +73,12 @@ def m_grouped_bf16_gemm_nt_contiguous(a: torch.Tensor, b: torch.Tensor, d: torch
     """D[m] = A[m] @ B[group(m)].T; reference: m_grouped_bf16_gemm_nt_contiguous, csrc/apis/gemm.hpp:464-517."""
     del compiled_dims
     m, k = _check_bf16(a, 2, 'a')
-    num_groups, n, k_ = _check_bf16(b, 3, 'b')
+    num_groups, n, k_ = _check_bf16(b, 3, 'b', allow_mn_major=True)
     if k != k_:
         raise RuntimeError(f'K mismatch: a has {k}, b has {k_}')
-    if not b.is_contiguous():
-        raise RuntimeError('b must be contiguous')
+    b_mn, b_stride = _b_major(b, 'b')
+    if not (b.is_contiguous() or (b_mn and b.transpose(1, 2).is_contiguous())):
+        raise RuntimeError('b must be contiguous ([G, N, K], or [G, K, N] storage viewed as [G, N, K])')
     _check_out(d, (m, n), False)
     if grouped_layout.dtype != torch.int32 or not grouped_layout.is_contiguous() or not grouped_layout.is_cuda:
         raise RuntimeError('grouped_layout must be a contiguous CUDA int32 tensor')
@@ -81,7 +94,7 @@ def m_grouped_bf16_gemm_nt_contiguous(a: torch.Tensor, b: torch.Tensor, d: torch
         return
     with torch.cuda.device(d.device):
         _lib.check(_lib.lib().dgb200_m_grouped_bf16_gemm_nt_contiguous(
-            _p(a), a.stride(0), _p(b), b.stride(1), _p(d), d.stride(0), _p(grouped_layout), m, n, k, num_groups, 0,
+            _p(a), a.stride(0), _p(b), b_stride, b_mn, _p(d), d.stride(0), _p(grouped_layout), m, n, k, num_groups, 0,
             1 if use_psum_layout else 0, get_mk_alignment_for_contiguous_layout(),
             int(bool(ensure_zero_padding and use_psum_layout)), _lib.current_stream_ptr()))
 
@@ -89,7 +102,8 @@ def m_grouped_bf16_gemm_nt_contiguous(a: torch.Tensor, b: torch.Tensor, d: torch
 def m_grouped_bf16_gemm_nn_contiguous(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, grouped_layout: torch.Tensor,
                                       compiled_dims: str = 'nk', use_psum_layout: bool = False,
                                       ensure_zero_padding: bool = True) -> None:
-    """B given as [G, K, N] over K-major storage; reference: csrc/apis/gemm.hpp:519-526."""
+    """B given as [G, K, N] (contiguous: an MN-major operand; or a view of [G, N, K] storage); reference:
+    csrc/apis/gemm.hpp:519-526."""
     m_grouped_bf16_gemm_nt_contiguous(a, b.transpose(1, 2), d, grouped_layout, compiled_dims, use_psum_layout,
                                       ensure_zero_padding, None)
 

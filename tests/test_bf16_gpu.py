@@ -62,6 +62,13 @@ def test_m_grouped_contiguous(dg, use_psum, n, k):
     dg.m_grouped_bf16_gemm_nn_contiguous(a.cuda(), b.cuda().transpose(1, 2), d2, layout.cuda(), use_psum_layout=use_psum)
     _finish()
     assert torch.equal(d2.cpu()[mask], got[mask])
+    # ... and genuinely [G, K, N] storage (an MN-major operand) gives the same bits
+    d3 = torch.zeros_like(d)
+    b_kn = b.cuda().transpose(1, 2).contiguous()
+    dg.m_grouped_bf16_gemm_nn_contiguous(a.cuda(), b_kn, d3, layout.cuda(), use_psum_layout=use_psum)
+    dg.m_grouped_bf16_gemm_nt_contiguous(a.cuda(), b_kn.transpose(1, 2), d2, layout.cuda(), use_psum_layout=use_psum)
+    _finish()
+    assert torch.equal(d3.cpu()[mask], got[mask]) and torch.equal(d2.cpu()[mask], got[mask])
 
 
 def test_psum_zero_padding(dg):
@@ -104,6 +111,10 @@ def test_dense(dg, m, n, k, out):
     assert quant.calc_diff(d.cpu(), want.cpu()) < BF16_TOL
     d2 = torch.zeros_like(d)
     dg.bf16_gemm_nn(a, b.transpose(0, 1), d2)
+    _finish()
+    assert torch.equal(d2, d)
+    d2.zero_()
+    dg.bf16_gemm_nn(a, b.transpose(0, 1).contiguous(), d2)  # row-major [K, N] storage: an MN-major operand
     _finish()
     assert torch.equal(d2, d)
     if out == torch.float32:  # the accumulator input: d = c + a @ b.T
