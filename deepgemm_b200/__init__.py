@@ -8,6 +8,8 @@ from . import _lib, testing, utils  # noqa: F401
 from .bf16 import (  # noqa: F401
     bf16_gemm_nn,
     bf16_gemm_nt,
+    bf16_gemm_tn,
+    bf16_gemm_tt,
     m_grouped_bf16_gemm_nn_contiguous,
     m_grouped_bf16_gemm_nt_contiguous,
     m_grouped_bf16_gemm_nt_masked,

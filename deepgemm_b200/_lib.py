@@ -42,7 +42,7 @@ _SIGNATURES = {
     'dgb200_m_grouped_bf16_gemm_nt_contiguous': [_ptr, _i64, _ptr, _i64, _i32, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32,
                                                  _i32, _i32, _i32, _ptr],
     'dgb200_m_grouped_bf16_gemm_nt_masked': [_ptr, _ptr, _ptr, _i64, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
-    'dgb200_bf16_gemm_nt': [_ptr, _i64, _ptr, _i64, _i32, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_bf16_gemm_nt': [_ptr, _i64, _i32, _ptr, _i64, _i32, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_k_grouped_bf16_gemm_tn_contiguous': [_ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_per_channel_cast_to_fp8': [_ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr],
     'dgb200_k_grouped_sf_workspace_bytes': [_i32, _i32, _i32, _i32],

@@ -45,7 +45,7 @@ def bf16_gemm_nt(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[
     """Dense D = A @ B.T, a [M, K], b [N, K] bfloat16, d bfloat16 or float32.
     With ``c`` (float32, float32 d): d = c + a @ b.T. Reference: bf16_gemm_nt, csrc/apis/gemm.hpp:404-438."""
     del compiled_dims
-    m, k = _check_bf16(a, 2, 'a')
+    m, k = _check_bf16(a, 2, 'a', allow_mn_major=True)
     n, k_ = _check_bf16(b, 2, 'b', allow_mn_major=True)
     if k != k_:
         raise RuntimeError(f'K mismatch: a has {k}, b has {k_}')
@@ -53,9 +53,10 @@ def bf16_gemm_nt(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[
     if m == 0:
         return
     accumulate = _prepare_accumulator(c, d)
+    a_mn, a_stride = _b_major(a, 'a')
     b_mn, b_stride = _b_major(b, 'b')
     with torch.cuda.device(d.device):
-        _lib.check(_lib.lib().dgb200_bf16_gemm_nt(_p(a), a.stride(0), _p(b), b_stride, b_mn, _p(d), d.stride(0), m, n, k,
+        _lib.check(_lib.lib().dgb200_bf16_gemm_nt(_p(a), a_stride, a_mn, _p(b), b_stride, b_mn, _p(d), d.stride(0), m, n, k,
                                                   int(d.dtype == torch.float32), accumulate, _lib.current_stream_ptr()))
 
 
@@ -64,6 +65,18 @@ def bf16_gemm_nn(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[
     """b given as [K, N] (reference: csrc/apis/gemm.hpp:440-446 transposes the view and calls the NT form): a row-major
     [K, N] tensor is an MN-major operand and is read as such."""
     bf16_gemm_nt(a, b.transpose(0, 1), d, c, compiled_dims)
+
+
+def bf16_gemm_tn(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[torch.Tensor] = None,
+                 compiled_dims: str = 'nk') -> None:
+    """a given as [K, M], b as [K, N] (reference: csrc/apis/gemm.hpp:448-454)."""
+    bf16_gemm_nt(a.transpose(0, 1), b.transpose(0, 1), d, c, compiled_dims)
+
+
+def bf16_gemm_tt(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, c: Optional[torch.Tensor] = None,
+                 compiled_dims: str = 'nk') -> None:
+    """a given as [K, M], b as [N, K] (reference: csrc/apis/gemm.hpp:456-462)."""
+    bf16_gemm_nt(a.transpose(0, 1), b, d, c, compiled_dims)
 
 
 def m_grouped_bf16_gemm_nt_contiguous(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, grouped_layout: torch.Tensor,

@@ -52,6 +52,7 @@ struct GemmCall {
     long long a_rows_total;  // rows of the flattened A
     long long a_row_stride_bytes, b_row_stride_bytes;  // BF16 kind only: row pitches of A and B
     int b_mn_major;  // BF16 kind only: B is [groups * k, n] with n contiguous (b_row_stride_bytes = pitch of a K row)
+    int a_mn_major;  // BF16 kind, dense mode only: A is [k, m] with m contiguous (a_row_stride_bytes = pitch of a K row)
     GemmParams p;
     int b_is_fp4;
     int epilogue;
@@ -137,7 +138,13 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
         if (rc) return rc;
     }
     const uint64_t a_row_bytes = nvfp4 ? p.k / 2 : p.k;  // packed E2M1 or E4M3
-    if (bf16)
+    if (bf16 && c.a_mn_major) {
+        DGB_REQUIRE(p.mode == kModeDense, "an MN-major A is built for the dense GEMM only");
+        rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c.a, static_cast<uint64_t>(c.a_rows_total),
+                                static_cast<uint64_t>(p.k), static_cast<uint64_t>(c.a_row_stride_bytes), 64, 64,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+        p.a_mn_major = 1;
+    } else if (bf16)
         rc = make_tensor_map_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c.a, static_cast<uint64_t>(p.k),
                                 static_cast<uint64_t>(c.a_rows_total), static_cast<uint64_t>(c.a_row_stride_bytes), 64, 128,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1148,13 +1155,13 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
 
 namespace {
 // Shared body of the BF16 GEMM entry points: A [rows, k] and B [num_groups * n, k] BF16 K-major, D BF16 or FP32.
-int run_bf16_gemm(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, int32_t b_mn_major, void* d,
+int run_bf16_gemm(const void* a, int64_t a_row_stride, int32_t a_mn_major, const void* b, int64_t b_row_stride, int32_t b_mn_major, void* d,
                   int64_t d_row_stride, int32_t d_is_fp32, int32_t accumulate, const int32_t* layout, int mode, long long a_rows_total, int32_t m, int32_t n, int32_t k,
                   int32_t num_groups, int32_t alignment, int32_t store_padding, int max_tiles, void* stream) {
     DGB_REQUIRE(d != nullptr || a_rows_total == 0, "null output");
     DGB_REQUIRE(d_row_stride >= n && (d_row_stride * (d_is_fp32 ? 4 : 2)) % 16 == 0,
                 "d row stride must cover n and keep rows 16-byte aligned");
-    DGB_REQUIRE(a_row_stride >= k && a_row_stride % 8 == 0 && b_row_stride >= (b_mn_major ? n : k) && b_row_stride % 8 == 0,
+    DGB_REQUIRE(a_row_stride >= (a_mn_major ? m : k) && a_row_stride % 8 == 0 && b_row_stride >= (b_mn_major ? n : k) && b_row_stride % 8 == 0,
                 "a and b row strides must cover their rows and keep them 16-byte aligned");
     GemmCall c{};
     c.kind = kKindBf16;
@@ -1164,6 +1171,7 @@ int run_bf16_gemm(const void* a, int64_t a_row_stride, const void* b, int64_t b_
     c.a_row_stride_bytes = a_row_stride * 2;
     c.b_row_stride_bytes = b_row_stride * 2;
     c.b_mn_major = b_mn_major ? 1 : 0;
+    c.a_mn_major = a_mn_major ? 1 : 0;
     c.num_groups_a = 1;
     c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
     GemmParams& p = c.p;
@@ -1197,7 +1205,7 @@ int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride
     const int mode = layout_kind == DGB200_LAYOUT_PSUM ? kModePsum : kModeRowIds;
     const long long m_blocks = (static_cast<long long>(m) + 127) / 128 + (mode == kModePsum ? num_groups : 0);
     const int max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
-    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, b_mn_major, d, d_row_stride, d_is_fp32, 0, grouped_layout, mode, m, m, n, k,
+    return run_bf16_gemm(a, a_row_stride, 0, b, b_row_stride, b_mn_major, d, d_row_stride, d_is_fp32, 0, grouped_layout, mode, m, m, n, k,
                          num_groups, alignment, store_padding, max_tiles, stream);
 }
 
@@ -1206,18 +1214,19 @@ int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, 
                                          int32_t d_is_fp32, void* stream) {
     (void)expected_m;
     DGB_REQUIRE(max_m > 0 && max_m % 4 == 0, "max_m (%d) must be a positive multiple of 4", max_m);
-    return run_bf16_gemm(a, k, b, k, 0, d, d_row_stride, d_is_fp32, 0, masked_m, kModeMasked,
+    return run_bf16_gemm(a, k, 0, b, k, 0, d, d_row_stride, d_is_fp32, 0, masked_m, kModeMasked,
                          static_cast<long long>(num_groups) * max_m, max_m, n, k, num_groups, 4, 0, 0, stream);
 }
 
-int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, int32_t b_mn_major, void* d,
-                        int64_t d_row_stride, int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, int32_t accumulate,
-                        void* stream) {
+int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, int32_t a_mn_major, const void* b, int64_t b_row_stride,
+                        int32_t b_mn_major, void* d, int64_t d_row_stride, int32_t m, int32_t n, int32_t k, int32_t d_is_fp32,
+                        int32_t accumulate, void* stream) {
     DGB_REQUIRE(m >= 0, "m must be >= 0");
     const long long m_blocks = (static_cast<long long>(m) + 127) / 128;
     const int max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
-    return run_bf16_gemm(a, a_row_stride, b, b_row_stride, b_mn_major, d, d_row_stride, d_is_fp32, accumulate, nullptr, kModeDense, m, m,
-                         n, k, 1, 128,
+    DGB_REQUIRE(!a_mn_major || m % 8 == 0, "an MN-major a needs m (%d) to be a multiple of 8", m);
+    return run_bf16_gemm(a, a_row_stride, a_mn_major, b, b_row_stride, b_mn_major, d, d_row_stride, d_is_fp32, accumulate, nullptr,
+                         kModeDense, m, m, n, k, 1, 128,
                          0, max_tiles, stream);
 }
 

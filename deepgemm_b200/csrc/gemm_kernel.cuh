@@ -104,6 +104,7 @@ struct GemmParams {
     const float* b_scales;
     const float* out_scale;
     const float* c;  // kEpiF32Acc: accumulator input [G, m, n] (may alias d)
+    int a_mn_major;  // BF16 kind, dense mode only: A is [k, m] with m contiguous (the reference's "tn" / "tt" forms)
     int b_mn_major;  // BF16 kind only: B is [groups * k, n] with n contiguous (the reference's "nn" forms) instead of [groups * n, k]
     int accumulate;  // kEpiF32 only: d += accumulator instead of d = accumulator (the dense GEMMs' input c, already in d)
     int kg_psum;     // kModeKGrouped: layout[g] is the end K row of group g (groups start at multiples of `alignment`,
@@ -465,6 +466,11 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             for (int h = 0; h < kBoxes; ++h)
                                 tma_load_2d(smem + L::kOffA + stage * L::kABytes + h * (L::kABytes / kBoxes), &tm_a,
                                             full_bar + stage, t.row_start + h * (128 / kBoxes), t.k_row_start + kb * kBlockK);
+                        } else if (kKind == kKindBf16 && p.a_mn_major) {
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)
+                                tma_load_2d(smem + L::kOffA + stage * L::kABytes + h * 8192, &tm_a, full_bar + stage,
+                                            t.row_start + h * 64, kb * 64);
                         } else if (!DGB_SKIP(p, 1))
                             tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * kTmaXPerKb,
                                         t.row_start);
@@ -543,7 +549,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                    : make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, 128, BLOCK_N, kScaleUE8M0)) |
                (1u << 15) | (1u << 16))  // both operands MN-major
             : kKind == kKindBf16
-            ? (make_idesc_bf16_f32(128, BLOCK_N) | (p.b_mn_major ? (1u << 16) : 0u))
+            ? (make_idesc_bf16_f32(128, BLOCK_N) | (p.a_mn_major ? (1u << 15) : 0u) | (p.b_mn_major ? (1u << 16) : 0u))
             : kKind == kKindNvfp4 ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
                                   : make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
@@ -596,14 +602,16 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         }
                     }
                     // MN-major tiles: consecutive 128-byte chunks along M / N are one TMA box (128 bytes x kBlockK rows) apart
-                    const uint64_t adesc = kKG ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, 128 * kBlockK)
-                                               : make_kmajor_sw128_desc(a_base + stage * L::kABytes);
+                    const bool a_mn = kKG || (kKind == kKindBf16 && p.a_mn_major);
+                    const uint64_t adesc = a_mn ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, 128 * kBlockK)
+                                                : make_kmajor_sw128_desc(a_base + stage * L::kABytes);
                     const bool b_mn = kKG || (kKind == kKindBf16 && p.b_mn_major);
                     const uint64_t bdesc = b_mn ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, 128 * kBlockK)
                                                 : make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
                     // K-major: +32 bytes along K inside the swizzle span per MMA; MN-major: the K rows of one MMA (32 E4M3 or
                     // 16 BF16) are 4 or 2 groups of 8 rows = 1024 B each
                     constexpr uint32_t kDescStep = kKG ? (kKind == kKindBf16 ? 128 : 256) : 2;
+                    const uint32_t a_step = (kKind == kKindBf16 && a_mn) ? 128u : kDescStep;
                     const uint32_t b_step = (kKind == kKindBf16 && b_mn) ? 128u : kDescStep;
                     trace_point(p, 12, trace_i);
 #pragma unroll
@@ -612,7 +620,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
                         if constexpr (kKind == kKindBf16) {
                             // K = 16 BF16 elements (32 bytes) per MMA
-                            tcgen05_mma_f16(tmem_acc, adesc + k4 * kDescStep, bdesc + k4 * b_step, idesc, (kb | k4) != 0 ? 1u : 0u);
+                            tcgen05_mma_f16(tmem_acc, adesc + k4 * a_step, bdesc + k4 * b_step, idesc, (kb | k4) != 0 ? 1u : 0u);
                         } else if constexpr (kKind == kKindNvfp4) {
                             // K = 64 per MMA; its 4 scales per row are the 4 bytes of packed int k4 of the stage
                             tcgen05_mma_mxf4nvf4_4x(tmem_acc, adesc + k4 * 2, bdesc + k4 * 2, idesc, tmem_sfa + k4 * 4,

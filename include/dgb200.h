@@ -108,7 +108,8 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_masked(
  * BF16 K-major with row strides in elements (multiples of 8), d BF16 or FP32, layouts as above. Requires k % 64 == 0 and
  * n % 128 == 0. b_mn_major != 0 (contiguous and dense forms): b is [num_groups * k, n] with n contiguous, the operand
  * of the reference's "nn" forms (csrc/apis/gemm.hpp:440-446, :519-526), read through MN-major shared-memory descriptors;
- * b_row_stride is then the pitch of one K row.
+ * b_row_stride is then the pitch of one K row. a_mn_major != 0 (dense form only): likewise a is [k, m] with m contiguous
+ * (the "tn" / "tt" forms, csrc/apis/gemm.hpp:448-462), m % 8 == 0.
  * Reference: m_grouped_bf16_gemm_nt_contiguous csrc/apis/gemm.hpp:464-517, m_grouped_bf16_gemm_nt_masked :528-564,
  * bf16_gemm_nt :404-438 (accumulate as in dgb200_fp8_fp4_gemm_nt). */
 int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride,
@@ -118,9 +119,9 @@ int dgb200_m_grouped_bf16_gemm_nt_contiguous(const void* a, int64_t a_row_stride
 int dgb200_m_grouped_bf16_gemm_nt_masked(const void* a, const void* b, void* d, int64_t d_row_stride, const int32_t* masked_m,
                                          int32_t num_groups, int32_t max_m, int32_t n, int32_t k, int32_t expected_m,
                                          int32_t d_is_fp32, void* stream);
-int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, const void* b, int64_t b_row_stride, int32_t b_mn_major, void* d,
-                        int64_t d_row_stride, int32_t m, int32_t n, int32_t k, int32_t d_is_fp32, int32_t accumulate,
-                        void* stream);
+int dgb200_bf16_gemm_nt(const void* a, int64_t a_row_stride, int32_t a_mn_major, const void* b, int64_t b_row_stride,
+                        int32_t b_mn_major, void* d, int64_t d_row_stride, int32_t m, int32_t n, int32_t k, int32_t d_is_fp32,
+                        int32_t accumulate, void* stream);
 
 /* Operand quantiser of the K-grouped GEMM: x bf16 [k, mn] contiguous -> q e4m3 [k, mn] and sf float [k / gran_k, mn], one
  * power-of-two scale per gran_k (32 or 128) K rows and channel; k % gran_k == 0, mn even.

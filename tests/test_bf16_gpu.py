@@ -99,6 +99,7 @@ def test_masked(dg, max_m):
 
 
 @pytest.mark.parametrize('m,n,k,out', [(1, 128, 64, torch.bfloat16), (300, 768, 1024, torch.bfloat16),
+                                       (200, 384, 320, torch.bfloat16), (72, 256, 128, torch.float32),
                                        (4096, 4096, 4096, torch.bfloat16), (130, 256, 512, torch.float32)])
 def test_dense(dg, m, n, k, out):
     torch.manual_seed(m + n + k)
@@ -117,6 +118,16 @@ def test_dense(dg, m, n, k, out):
     dg.bf16_gemm_nn(a, b.transpose(0, 1).contiguous(), d2)  # row-major [K, N] storage: an MN-major operand
     _finish()
     assert torch.equal(d2, d)
+    if m % 8 == 0:  # a given as [K, M] storage: MN-major A
+        a_km = a.transpose(0, 1).contiguous()
+        d2.zero_()
+        dg.bf16_gemm_tt(a_km, b, d2)
+        _finish()
+        assert torch.equal(d2, d)
+        d2.zero_()
+        dg.bf16_gemm_tn(a_km, b.transpose(0, 1).contiguous(), d2)
+        _finish()
+        assert torch.equal(d2, d)
     if out == torch.float32:  # the accumulator input: d = c + a @ b.T
         c = torch.randn(m, n, device='cuda') * 3
         d3 = torch.full_like(d, float('nan'))
