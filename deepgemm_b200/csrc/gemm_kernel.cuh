@@ -103,7 +103,7 @@ struct GemmParams {
     const float* a_scale;
     const float* b_scales;
     const float* out_scale;
-    const float* c;  // kEpiF32Acc: accumulator input [G, m, n] (may alias d)
+    const float* c;  // kEpiF32Acc: unused by the kernel (the host puts c into d before the launch)
     int a_mn_major;  // BF16 kind, dense mode only: A is [k, m] with m contiguous (the reference's "tn" / "tt" forms)
     int b_mn_major;  // BF16 kind only: B is [groups * k, n] with n contiguous (the reference's "nn" forms) instead of [groups * n, k]
     int accumulate;  // kEpiF32 only: d += accumulator instead of d = accumulator (the dense GEMMs' input c, already in d)
@@ -969,24 +969,20 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                                          pack_bf16x2(__uint_as_float(acc[i * 8 + 6]), __uint_as_float(acc[i * 8 + 7])));
                     }
                 } else if constexpr (EPI == kEpiF32Acc) {
-                    // tiles with fewer than 128 rows (the tail of m): D[g] = C[g] + accumulator row by row (an empty group
-                    // contributes nothing: its accumulator was never written)
-                    if (!via_tma) {
-                    const long long off = (static_cast<long long>(t.group) * p.m + row) * p.d_row_stride +
-                                          static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
-                    const float4* src = reinterpret_cast<const float4*>(p.c + off);
-                    float* dst = reinterpret_cast<float*>(p.d) + off;
-                    const bool empty = t.num_kb == 0;
+                    // tiles with fewer than 128 rows (the tail of m): d += accumulator row by row (d already holds c; an
+                    // empty group adds nothing: its accumulator was never written)
+                    if (!via_tma && t.num_kb != 0) {
+                        const long long off = (static_cast<long long>(t.group) * p.m + row) * p.d_row_stride +
+                                              static_cast<long long>(t.n_block) * BLOCK_N + half * kCols;
+                        float* dst = reinterpret_cast<float*>(p.d) + off;
 #pragma unroll
-                    for (int i = 0; i < kCols / 4; ++i) {
-                        const float4 cv = src[i];
-                        const float a0 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 0]);
-                        const float a1 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 1]);
-                        const float a2 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 2]);
-                        const float a3 = empty ? 0.0f : __uint_as_float(acc[i * 4 + 3]);
-                        st_global_v4(dst + i * 4, __float_as_uint(cv.x + a0), __float_as_uint(cv.y + a1),
-                                     __float_as_uint(cv.z + a2), __float_as_uint(cv.w + a3));
-                    }
+                        for (int i = 0; i < kCols / 4; ++i) {
+                            const float4 cv = *reinterpret_cast<const float4*>(dst + i * 4);
+                            st_global_v4(dst + i * 4, __float_as_uint(cv.x + __uint_as_float(acc[i * 4 + 0])),
+                                         __float_as_uint(cv.y + __uint_as_float(acc[i * 4 + 1])),
+                                         __float_as_uint(cv.z + __uint_as_float(acc[i * 4 + 2])),
+                                         __float_as_uint(cv.w + __uint_as_float(acc[i * 4 + 3])));
+                        }
                     }
                 } else if constexpr (EPI == kEpiSwiGLUNvfp4) {
                     // Same column order as below; the 32 outputs of a gate/up pair are requantised to NVFP4: two
