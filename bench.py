@@ -24,12 +24,16 @@ if ROOT not in sys.path:
 
 CONFIG3 = dict(tokens=4096, hidden=7168, inter=2048, experts=256, topk=8)
 METRIC = 'mega_moe_layer_tokens_per_s'
-CPU_SAMPLE_EXPERTS = 4  # experts whose routed rows the CPU legs evaluate per pass
+CPU_SAMPLE_EXPERTS = 16  # experts whose routed rows the CPU legs evaluate per pass (both legs time the same rows)
+INPUT_SEED = 1234        # CPU generator seed of rank 0's tokens and router logits (rank r uses INPUT_SEED + r)
 FP4_DENSE_PEAK_TFLOPS_NOMINAL = 9000.0
 FP8_DENSE_PEAK_TFLOPS_NOMINAL = 4500.0
-# DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the ncu capture summarised in
-# profiles/grouped_gemm_small_layer_ncu_full.md (small case, scaled by the units processed).
+# DRAM bytes (read + write) per algorithmic byte of the gate/up GEMM: dram__bytes_read.sum + dram__bytes_write.sum of
+# an ncu capture of the same kernels on a 32-expert, 512-token layer (same rows per expert as the headline workload),
+# divided by that case's algorithmic bytes. Traffic grows in proportion to experts and rows, so a full launch is
+# this ratio times its own algorithmic bytes.
 L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.06
+L1_TRAFFIC_SOURCE = 'ncu capture of a 32-expert, 512-token layer (about 128 rows per expert), scaled by algorithmic bytes'
 
 
 def parse_args():
@@ -41,6 +45,8 @@ def parse_args():
     ap.add_argument('--tokens', type=int, default=0, help='override tokens per rank (profiling small cases only)')
     ap.add_argument('--experts', type=int, default=0, help='override the expert count (profiling small cases only)')
     ap.add_argument('--skip-cpu-baseline', action='store_true')
+    ap.add_argument('--skip-other-configs', action='store_true',
+                    help='N = 1 only: leave out the extra timings (8192-token base, BASELINE configs 1, 2 and 4) after the headline line')
     ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
                     help='nvfp4xnvfp4 runs the NVFP4 prefill variant (16384 tokens) instead of the headline workload')
     ap.add_argument('--workload', default='layer', choices=['layer', 'gemm_contiguous', 'gemm_masked', 'bf16_gemm_contiguous', 'bf16_gemm_masked',
@@ -138,18 +144,19 @@ def time_cpu_sample(sample, steps, warmup):
     return rows, dt, torch.get_num_threads()
 
 
-def make_cpu_sample_on_cpu(cfg, seed=0):
-    """Seeded CPU-only inputs for the reference arm: all tokens routed over all experts, rows of the first
-    CPU_SAMPLE_EXPERTS experts kept; their weights drawn ~N(0, 0.02) and quantised to MXFP4 by the oracle."""
+def make_cpu_sample_on_cpu(cfg):
+    """Seeded CPU-only inputs for the reference arm: rank 0's tokens and router logits of the GPU arm (same generator,
+    same order of draws, so the same routed rows), rows of the first CPU_SAMPLE_EXPERTS experts kept; their weights drawn
+    ~N(0, 0.02) and quantised to MXFP4 by the oracle (weight values do not change the time)."""
     import torch
     from oracle import moe as omoe
     from oracle import quant
-    torch.manual_seed(seed)
+    torch.manual_seed(INPUT_SEED)
     x = torch.randn(cfg['tokens'], cfg['hidden']).bfloat16()
     idx, w = omoe.route_sigmoid_topk(torch.randn(cfg['tokens'], cfg['experts']), cfg['topk'])
     x_q, x_sf = quant.quantize_fp8_per_token(x, 32)
     sample = {k: [] for k in ('x_q', 'x_sf', 'w', 'l1_q', 'l1_sf', 'l2_q', 'l2_sf')}
-    for e in range(CPU_SAMPLE_EXPERTS):
+    for e in range(min(CPU_SAMPLE_EXPERTS, cfg['experts'])):
         tok, slot = torch.nonzero(idx == e, as_tuple=True)
         sample['x_q'].append(x_q[tok])
         sample['x_sf'].append(x_sf[tok])
@@ -164,8 +171,16 @@ def make_cpu_sample_on_cpu(cfg, seed=0):
 
 
 def sample_description(cfg, rows):
-    return (f'routed rows of experts 0..{CPU_SAMPLE_EXPERTS - 1} of the same workload ({rows} of '
-            f'{cfg["tokens"] * cfg["topk"]} rows), weights dequantised on the fly, torch fp32 matmul')
+    return (f'routed rows of experts 0..{min(CPU_SAMPLE_EXPERTS, cfg["experts"]) - 1} of the same workload ({rows} of '
+            f'{cfg["tokens"] * cfg["topk"]} rows), weights dequantised on the fly, torch fp32 matmul; the rate is '
+            'extrapolated from this sample to the whole batch')
+
+
+def cpu_baseline_entry(cfg, rows, dt, cores):
+    """tokens/s of the CPU leg: the sampled rows are rows / topk tokens' worth of work."""
+    value = rows / cfg['topk'] / dt
+    return {'value': value, 'unit': 'tokens/s', 'cores': cores, 'kind': 'port', 'sample': sample_description(cfg, rows),
+            'extrapolated': True, 'sample_fraction': rows / float(cfg['tokens'] * cfg['topk'])}
 
 
 def run_reference(args, cfg, rank, world):
@@ -174,14 +189,14 @@ def run_reference(args, cfg, rank, world):
         return
     sample = make_cpu_sample_on_cpu(cfg)
     rows, dt, cores = time_cpu_sample(sample, args.steps, args.warmup)
-    value = rows / cfg['topk'] / dt
+    entry = cpu_baseline_entry(cfg, rows, dt, cores)
+    value = entry['value']
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': args.gpus,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
         'scaling': 'weak', 'vs_baseline': None, 'dtype': cfg.get('mma', 'fp8xfp4') + ' (fp32 accumulate)', 'data': 'synthetic',
         'config': workload_config(cfg, args.gpus),
-        'cpu_baseline': {'value': value, 'unit': 'tokens/s', 'cores': cores, 'kind': 'port',
-                         'sample': sample_description(cfg, rows)},
+        'cpu_baseline': entry,
         'e2e': {'value': value, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
@@ -253,6 +268,10 @@ def build_layer_nvfp4(dg, cfg):
 
 
 def run_gemm_workload(args):
+    print(json.dumps(measure_gemm_workload(args.workload == 'gemm_masked', args.steps, args.warmup)), flush=True)
+
+
+def measure_gemm_workload(masked, steps, warmup):
     """BASELINE configs 1 (m-grouped contiguous, 4 experts, N 512, K 1024) and 2 (masked decode GEMM, 32 experts,
     Poisson(64) rows, N 4096, K 7168), FP8 1x128 activations x MXFP4 1x32 weights, bf16 output. Every timed launch is
     preceded by a 512 MB write that flushes L2; times are per-launch CUDA events."""
@@ -260,7 +279,6 @@ def run_gemm_workload(args):
     import deepgemm_b200 as dg
     from deepgemm_b200 import _lib
     torch.manual_seed(0)
-    masked = args.workload == 'gemm_masked'
     g, n, k = (32, 4096, 7168) if masked else (4, 512, 1024)
     w_q = torch.empty((g, n, k // 2), dtype=torch.int8, device='cuda')
     w_sf = torch.empty((g, n, k // 32), dtype=torch.float32, device='cuda')
@@ -295,13 +313,13 @@ def run_gemm_workload(args):
         rows = int(ms.sum())
         call = lambda: dg.m_grouped_fp8_fp4_gemm_nt_contiguous((a_q, a_sf), (w_q, w_sf), d, layout, recipe_a=(1, 128), recipe_b=(1, 32))
     flush = torch.empty(512 << 20, dtype=torch.int8, device='cuda')
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         call()
     torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     total = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -311,23 +329,23 @@ def run_gemm_workload(args):
         total += e0.elapsed_time(e1)
     clocks = sampler.stop()
     _lib.device_status()
-    ms_per = total / args.steps
+    ms_per = total / steps
     peak, peak_kind = measured_peaks()
     flops = 2.0 * rows * n * k
     touched = g if not masked else int((counts > 0).sum())
     nbytes = touched * (n * k // 2 + n * k // 32) + rows * (k + k // 128 + 2 * n)
-    print(json.dumps({
-        'metric': 'grouped_gemm_us', 'value': ms_per * 1e3, 'unit': 'us', 'n_gpus': 1, 'steps': args.steps, 'warmup': args.warmup,
+    return {
+        'metric': 'grouped_gemm_us', 'value': ms_per * 1e3, 'unit': 'us', 'n_gpus': 1, 'steps': steps, 'warmup': warmup,
         'ms_per_step': ms_per, 'higher_is_better': False, 'scaling': 'weak', 'vs_baseline': None,
         'dtype': 'fp8xfp4 (fp32 accumulate)', 'data': 'synthetic',
         'config': {'workload': ('m-grouped masked FP8xMXFP4 decode GEMM (BASELINE config 2)' if masked else
                                 'm-grouped contiguous FP8xMXFP4 GEMM (BASELINE config 1)'),
                    'groups': g, 'n': n, 'k': k, 'valid_rows': rows, 'l2_policy': 'L2 flushed by a 512 MB write before every launch'},
-        'gpu_launches': args.steps, 'clocks': clocks, 'tflops': flops / (ms_per * 1e-3) / 1e12,
+        'gpu_launches': steps, 'clocks': clocks, 'tflops': flops / (ms_per * 1e-3) / 1e12,
         'roofline': {'kernel': 'dgb200_grouped_gemm_kernel', 'bound': 'hbm', 'achieved': nbytes / (ms_per * 1e-3) / 1e9, 'peak': peak,
                      'unit': 'GB/s', 'frac': nbytes / (ms_per * 1e-3) / 1e9 / peak, 'peak_source': peak_kind, 'traffic': None,
                      'algorithmic_bytes': nbytes},
-    }), flush=True)
+    }
 
 
 def measured_bf16_tflops():
@@ -432,28 +450,120 @@ def run_family_workload(args):
     }), flush=True)
 
 
-def run_ours(args, cfg, rank, world, local_rank):
+def ep_parity_check(dg, _lib, rank, world):
+    """Correctness of the expert-parallel path at this world size, run after the timed regions: one small layer on every
+    rank (256 tokens per rank, hidden 512, intermediate 256, 8 experts per rank, top-4, 15 % masked slots, one shared
+    expert), all ranks' outputs and dispatch plans gathered to rank 0 and compared with the CPU oracle (checker only).
+    The check mirrors the reference's fused-against-baseline comparison (tests/test_mega_moe.py:316-329).
+    Returns {'calc_diff_max', 'plan_bit_exact', 'ranks', 'ok'} on rank 0, None elsewhere."""
+    import torch
+    import torch.distributed as dist
+    tokens, hidden, inter, topk, per_rank = 256, 512, 256, 4, 8
+    experts = per_rank * world
+
+    def inputs_of(r):
+        # the same weights on every rank, tokens and routing seeded by the rank
+        from oracle import moe as omoe
+        from oracle import quant
+        g = torch.Generator().manual_seed(9100 + r)
+        x = torch.randn(tokens, hidden, generator=g).bfloat16()
+        idx, w = omoe.route_sigmoid_topk(torch.randn(tokens, experts, generator=g), topk)
+        mask = torch.rand(idx.shape, generator=g) < 0.15
+        idx, w = idx.masked_fill(mask, -1), w.masked_fill(mask, 0.0)
+        x_q, x_sf = quant.quantize_fp8_per_token(x, 32)
+        return dict(x_q=x_q, x_sf=x_sf, topk_idx=idx, topk_weights=w)
+
+    def weights():
+        from oracle import quant
+        g = torch.Generator().manual_seed(9001)
+        out = {}
+        for name, shape in (('l1', (experts, 2 * inter, hidden)), ('l2', (experts, hidden, inter))):
+            qs, sfs = zip(*[quant.quantize_fp4_per_token((torch.randn(*shape[1:], generator=g) * 0.02).bfloat16(), 32)
+                            for _ in range(experts)])
+            out[name + '_q'], out[name + '_sf'] = torch.stack(qs), torch.stack(sfs)
+        out['s1_q'], out['s1_sf'] = quant.quantize_fp8_per_token((torch.randn(2 * inter, hidden, generator=g) * 0.02).bfloat16(), 32)
+        out['s2_q'], out['s2_sf'] = quant.quantize_fp8_per_token((torch.randn(hidden, inter, generator=g) * 0.02).bfloat16(), 32)
+        return out
+
+    from oracle import quant
+    c, wt = inputs_of(rank), weights()
+    mine = slice(rank * per_rank, (rank + 1) * per_rank)
+    buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, experts, tokens, topk, hidden, inter, num_shared_experts=1)
+    l1_sf = dg.transform_sf_into_required_layout(wt['l1_sf'][mine].cuda(), 2 * inter, hidden, (1, 32), per_rank)
+    l2_sf = dg.transform_sf_into_required_layout(wt['l2_sf'][mine].cuda(), hidden, inter, (1, 32), per_rank)
+    l1, l2 = dg.transform_weights_for_mega_moe((wt['l1_q'][mine].cuda(), l1_sf), (wt['l2_q'][mine].cuda(), l2_sf))
+    sl1, sl2 = dg.transform_weights_for_mega_moe(
+        (wt['s1_q'].cuda(), dg.transform_sf_into_required_layout(wt['s1_sf'].cuda(), 2 * inter, hidden, (1, 32))),
+        (wt['s2_q'].cuda(), dg.transform_sf_into_required_layout(wt['s2_sf'].cuda(), hidden, inter, (1, 32))))
+    buf.x[:tokens].copy_(c['x_q'].cuda())
+    buf.x_sf[:tokens].copy_(quant.pack_ue8m0(c['x_sf']).cuda())
+    buf.topk_idx[:tokens].copy_(c['topk_idx'].cuda())
+    buf.topk_weights[:tokens].copy_(c['topk_weights'].cuda())
+    y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+    dg.fp8_fp4_mega_moe(y, l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2)
+    status = _lib.device_status(raise_on_error=False)
+    lay = buf.layout
+    plan = torch.cat([buf.buffer[lay[k]:lay[k] + n * 4].view(torch.int32) for k, n in
+                      (('expert_start', per_rank), ('expert_end', per_rank), ('dest_row', tokens * topk))])
+    ys = [torch.empty_like(y) for _ in range(world)]
+    plans = [torch.empty_like(plan) for _ in range(world)]
+    codes = [torch.zeros(1, dtype=torch.int32, device='cuda') for _ in range(world)]
+    dist.all_gather(ys, y)
+    dist.all_gather(plans, plan)
+    dist.all_gather(codes, torch.tensor([status[0]], dtype=torch.int32, device='cuda'))
+    if rank != 0:
+        return None
+    from oracle import moe as omoe
+    cases = [inputs_of(r) for r in range(world)]
+    all_counts = torch.stack([omoe.ep_counts(cs['topk_idx'], experts) for cs in cases])
+    diff_max, plan_ok = 0.0, True
+    for r in range(world):
+        cs = cases[r]
+        shared = omoe.shared_expert_rows(cs['x_q'], cs['x_sf'], wt['s1_q'], wt['s1_sf'], wt['s2_q'], wt['s2_sf'])
+        want = omoe.moe_layer(cs['x_q'], cs['x_sf'], cs['topk_idx'], cs['topk_weights'], wt['l1_q'], wt['l1_sf'], wt['l2_q'],
+                              wt['l2_sf'], shared_rows=shared)
+        got = ys[r].cpu()
+        d = float(quant.calc_diff(got, want)) if not torch.isnan(got.float()).any() else float('inf')
+        diff_max = max(diff_max, d)
+        my_base, want_start, want_end = omoe.ep_plan(all_counts, r, 128)
+        p = plans[r].cpu().long()
+        plan_ok = plan_ok and torch.equal(p[:per_rank], want_start) and torch.equal(p[per_rank:2 * per_rank], want_end) and \
+            torch.equal(p[2 * per_rank:], omoe.ep_dest_rows(cs['topk_idx'], my_base, experts).long())
+    status_ok = all(int(cd) == 0 for cd in codes)
+    return {'calc_diff_max': diff_max, 'plan_bit_exact': bool(plan_ok), 'device_status_ok': status_ok, 'ranks': world,
+            'tolerance': 2e-3, 'ok': bool(plan_ok and status_ok and diff_max <= 2e-3),
+            'case': f'{tokens} tokens/rank, hidden {hidden}, inter {inter}, {experts} experts, top-{topk}, 15% masked, 1 shared expert'}
+
+
+def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True, with_cpu=True, weights=None):
+    """Builds (or reuses) the layer's weights, times `steps` passes after `warmup` untimed ones and returns, on rank 0,
+    the JSON line as a dict plus the weights (None and the weights on the other ranks)."""
     import torch
     import torch.distributed as dist
     import deepgemm_b200 as dg
     from deepgemm_b200 import _lib
 
     torch.cuda.set_device(local_rank)
-    torch.manual_seed(1234 + rank)
+    torch.manual_seed(INPUT_SEED + rank)
     t, h, i, e, k = cfg['tokens'], cfg['hidden'], cfg['inter'], cfg['experts'], cfg['topk']
     cfg['local_experts'] = e // world
     nvfp4 = cfg.get('mma') == 'nvfp4xnvfp4'
-    if nvfp4:
-        args.skip_cpu_baseline = True  # the CPU baseline belongs to the headline workload
+    with_cpu = with_cpu and rank == 0 and world == 1 and not nvfp4 and not args.skip_cpu_baseline
+    # the first CPU draws of this function are the tokens and the logits, in this order: the reference arm repeats them
+    x_host = torch.randn(t, h).bfloat16().pin_memory()
+    logits = torch.randn(t, e)
+    cpu_weights = None
+    if weights is not None:
+        l1, l2 = weights
+    elif nvfp4:
         l1, l2 = build_layer_nvfp4(dg, cfg)
+    else:
+        l1, l2, cpu_weights = build_layer(dg, cfg, min(CPU_SAMPLE_EXPERTS, e) if with_cpu else 0)
+    if nvfp4:
         # calibrated, fixed scales (equal on every rank): inputs ~N(0, 1) stay below 8; post-SwiGLU values below 64
         x_scale = torch.tensor(8.0 / (6 * 448), device='cuda')
         act_scale = torch.tensor(64.0 / (6 * 448), device='cuda')
-    else:
-        l1, l2, cpu_weights = build_layer(dg, cfg, CPU_SAMPLE_EXPERTS if rank == 0 and world == 1 and not args.skip_cpu_baseline else 0)
     buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD if world > 1 else None, e, t, k, h, i, mma_type=cfg.get('mma', 'fp8xfp4'))
-    x_host = torch.randn(t, h).bfloat16().pin_memory()
-    logits = torch.randn(t, e)
     if world > 1:
         # expert popularity ~ Zipf(s = 1): rank r of a seeded random permutation of the experts has weight 1 / (r + 1)
         g = torch.Generator().manual_seed(2024)
@@ -466,11 +576,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     logits = logits_host.cuda()
     y = torch.empty((t, h), dtype=torch.bfloat16, device='cuda')
     lib = _lib.lib()
-    # single rank: router, count, scan, assign, quantise + dispatch, L1, L2, combine (the memset is not a kernel of ours);
-    # NVFP4 keeps a separate cast and gather; expert parallel adds the count exchange, the plan and three barriers
-    # single-rank FP8 layer: both GEMMs are split over the two tile orientations (the library decides from the expected
-    # rows per expert), so 2 + 2 GEMM launches and the SwiGLU finisher instead of 2 launches
-    kernels_per_step = 9 if nvfp4 else (11 if world == 1 else 12)
+    kernels_per_step = kernels_of_one_step(nvfp4, world)
 
     def step(events=None, x_in=None, logits_in=None, y_out=None):
         x_in, logits_in, y_out = (x if x_in is None else x_in), (logits if logits_in is None else logits_in), (y if y_out is None else y_out)
@@ -492,11 +598,11 @@ def run_ours(args, cfg, rank, world, local_rank):
 
     # ---- device-resident timing
     barrier()
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     barrier()
-    status = _lib.device_status()
-    stage_events = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(args.steps)]
+    _lib.device_status()
+    stage_events = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(steps)]
     for evs in stage_events:  # create the underlying handles before they are handed to the library
         for ev in evs:
             ev.record()
@@ -506,123 +612,192 @@ def run_ours(args, cfg, rank, world, local_rank):
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0.record()
-    for s in range(args.steps):
+    for s in range(steps):
         step(stage_events[s])
     t1.record()
     barrier()
     clocks = sampler.stop()
-    ms_per_step = t0.elapsed_time(t1) / args.steps
-    status = _lib.device_status()
-    stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_events) / args.steps for j in range(5)]
+    ms_per_step = t0.elapsed_time(t1) / steps
+    _lib.device_status()
+    stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_events) / steps for j in range(5)]
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region.
     # Every step copies its own inputs from pinned host memory and its result back; the three legs run on three
     # streams over double-buffered device staging, so step s + 1's upload and step s - 1's download overlap step s.
-    compute = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    xs, lgs, ys = [x, torch.empty_like(x)], [logits, torch.empty_like(logits)], [y, torch.empty_like(y)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_done = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+    e2e_ms = float('nan')
+    if with_e2e:
+        compute = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        xs, lgs, ys = [x, torch.empty_like(x)], [logits, torch.empty_like(logits)], [y, torch.empty_like(y)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_done = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_steps(n):
-        for s in range(n):
-            slot = s & 1
-            with torch.cuda.stream(s_in):
-                s_in.wait_event(ev_done[slot])   # the step that last read this slot's inputs has finished
-                xs[slot].copy_(x_host, non_blocking=True)
-                lgs[slot].copy_(logits_host, non_blocking=True)
-                ev_in[slot].record(s_in)
-            compute.wait_event(ev_in[slot])
-            compute.wait_event(ev_out[slot])     # this slot's previous result has left the device
-            step(None, xs[slot], lgs[slot], ys[slot])
-            ev_done[slot].record(compute)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_done[slot])
-                y_host.copy_(ys[slot], non_blocking=True)
-                ev_out[slot].record(s_out)
-        compute.wait_event(ev_out[0])
-        compute.wait_event(ev_out[1])
+        def e2e_steps(n):
+            for s in range(n):
+                slot = s & 1
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_done[slot])   # the step that last read this slot's inputs has finished
+                    xs[slot].copy_(x_host, non_blocking=True)
+                    lgs[slot].copy_(logits_host, non_blocking=True)
+                    ev_in[slot].record(s_in)
+                compute.wait_event(ev_in[slot])
+                compute.wait_event(ev_out[slot])     # this slot's previous result has left the device
+                step(None, xs[slot], lgs[slot], ys[slot])
+                ev_done[slot].record(compute)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[slot])
+                    y_host.copy_(ys[slot], non_blocking=True)
+                    ev_out[slot].record(s_out)
+            compute.wait_event(ev_out[0])
+            compute.wait_event(ev_out[1])
 
-    e2e_steps(max(args.warmup, 3))
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    e2e_steps(args.steps)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / args.steps
-    _lib.device_status()
+        e2e_steps(max(warmup, 3))
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_steps(steps)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / steps
+        _lib.device_status()
 
-    # ---- algorithmic work of this batch
+    # ---- algorithmic work of this batch, per rank
     lay = buf.layout
     ends = buf.buffer[lay['expert_end']:lay['expert_end'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
     starts = buf.buffer[lay['expert_start']:lay['expert_start'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
     rows = int((ends - starts).sum())
-    rows_all = torch.tensor([float(rows)], device='cuda')
-    rows_max = rows_all.clone()
-    if world > 1:
-        dist.all_reduce(rows_all)
-        dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
     touched = int(((ends - starts) > 0).sum())
-    flops = 2.0 * float(rows_all) * h * i * 3
     if nvfp4:
         l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 16) + rows * (h // 2 + h // 16) + rows * (i // 2 + i // 16)
         l2_bytes = touched * (h * i // 2 + h * i // 16) + rows * (i // 2 + i // 16) + rows * h * 2
     else:
         l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 32) + rows * (h + h // 32) + rows * (i + i // 32)
         l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
-    times = torch.tensor([ms_per_step, e2e_ms] + stage_ms, dtype=torch.float64, device='cuda')
+    # every rank's own numbers travel to rank 0: the step time is the maximum over ranks, everything that explains it
+    # (stage times, bytes, flops) is taken from ONE rank, the one with the most routed rows
+    mine = torch.tensor([ms_per_step, e2e_ms] + stage_ms + [rows, touched, l1_bytes, l2_bytes], dtype=torch.float64, device='cuda')
+    per_rank = [torch.empty_like(mine) for _ in range(world)]
     if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_per_step, e2e_ms = float(times[0]), float(times[1])
-    stage_ms = [float(v) for v in times[2:]]
+        dist.all_gather(per_rank, mine)
+    else:
+        per_rank = [mine]
     if rank != 0:
-        return
-    peak, peak_kind = measured_peaks()
-    l1_gbs = l1_bytes / (stage_ms[2] * 1e-3) / 1e9
+        return None, (l1, l2)
+    table = torch.stack(per_rank).cpu()
+    ms_per_step, e2e_ms = float(table[:, 0].max()), float(table[:, 1].max())
+    hot = int(table[:, 7].argmax())
+    stage_ms = [float(v) for v in table[hot, 2:7]]
+    rows_hot, l1_bytes, l2_bytes = int(table[hot, 7]), int(table[hot, 9]), int(table[hot, 10])
+    rows_all = float(table[:, 7].sum())
+    flops = 2.0 * rows_all * h * i * 3
+    hbm_peak, peak_kind = measured_peaks()
     tflops = flops / (ms_per_step * 1e-3) / 1e12
+    # dominant kernel = the gate/up GEMM of the most loaded rank; which roofline binds it follows from its arithmetic
+    # intensity against the ridge of the FP8 tensor rate (nominal; this pool has no measured FP8 figure) over HBM
+    l1_flops = 2.0 * rows_hot * h * 2 * i
+    l1_s = stage_ms[2] * 1e-3
+    mma_peak_nominal = FP4_DENSE_PEAK_TFLOPS_NOMINAL if nvfp4 else FP8_DENSE_PEAK_TFLOPS_NOMINAL
+    tensor_bound = l1_bytes > 0 and l1_flops / l1_bytes > mma_peak_nominal * 1e12 / (hbm_peak * 1e9)
+    l1_kernel_name = ('dgb200_grouped_gemm_kernel (gate/up GEMM + SwiGLU + requant)' if nvfp4 or world > 1 else L1_STAGE_KERNELS)
+    if tensor_bound:
+        roofline = {'kernel': l1_kernel_name, 'bound': 'tensor', 'achieved': l1_flops / l1_s / 1e12, 'peak': mma_peak_nominal,
+                    'unit': 'TFLOP/s', 'frac': l1_flops / l1_s / 1e12 / mma_peak_nominal,
+                    'peak_source': 'nominal dense ' + ('FP4' if nvfp4 else 'FP8') + ' rate (no measured figure for this type on this pool)',
+                    'traffic': None, 'algorithmic_flops': l1_flops, 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]}
+    else:
+        l1_gbs = l1_bytes / l1_s / 1e9
+        roofline = {'kernel': l1_kernel_name, 'bound': 'hbm', 'achieved': l1_gbs, 'peak': hbm_peak, 'unit': 'GB/s',
+                    'frac': l1_gbs / hbm_peak, 'peak_source': peak_kind,
+                    'traffic': int(L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * l1_bytes) if not nvfp4 else None,
+                    'traffic_source': L1_TRAFFIC_SOURCE if not nvfp4 else None,
+                    'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]}
+    if world > 1:
+        roofline['rank'] = hot
     line = {
         'metric': METRIC, 'value': t * world / (ms_per_step * 1e-3), 'unit': 'tokens/s', 'n_gpus': world,
-        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
+        'steps': steps, 'warmup': warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True,
         'scaling': 'weak', 'vs_baseline': None, 'dtype': cfg.get('mma', 'fp8xfp4') + ' (fp32 accumulate)', 'data': 'synthetic',
         'config': workload_config(cfg, world),
-        'e2e': {'value': t * world / (e2e_ms * 1e-3), 'unit': 'tokens/s', 'ms_per_step': e2e_ms,
-                'h2d_bytes_per_step': x_host.numel() * 2 + logits_host.numel() * 4, 'd2h_bytes_per_step': y_host.numel() * 2},
-        'gpu_launches': kernels_per_step * args.steps,
+        'gpu_launches': kernels_per_step * steps,
         'clocks': clocks,
-        # the gate/up GEMM is split by expert size over the two tile orientations: the timed stage holds both launches
-        # and, for the swapped half, the small SwiGLU + requant kernel (single rank, FP8 kind; otherwise one launch)
-        'roofline': {'kernel': 'gate/up GEMM + SwiGLU + FP8 requant (dgb200_grouped_gemm_kernel + dgb200_swap_gemm_kernel + '
-                               'dgb200_swiglu_requant_rows_kernel)' if (world == 1 and not nvfp4) else
-                               'dgb200_grouped_gemm_kernel (L1: gate/up GEMM + SwiGLU + requant)', 'bound': 'hbm',
-                     'achieved': l1_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': l1_gbs / peak, 'peak_source': peak_kind,
-                     'traffic': int(L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * l1_bytes), 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]},
+        'roofline': roofline,
+        # stage times of the most loaded rank (rank `stages_rank`); with several ranks the cross-rank waits are inside
         'stages_ms': {'plan': stage_ms[0], 'dispatch': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
                       'l2_gemm': stage_ms[3], 'combine': stage_ms[4]},
+        'stages_rank': hot,
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9,
         'tflops': tflops,
         'frac_fp4_dense_peak_nominal': tflops / (FP4_DENSE_PEAK_TFLOPS_NOMINAL * world),
         'frac_fp8_rate_peak_nominal': tflops / (FP8_DENSE_PEAK_TFLOPS_NOMINAL * world),
-        'routed_rows': rows,
-        'load_imbalance_max_over_mean': float(rows_max) / (float(rows_all) / world) if float(rows_all) > 0 else None,
+        'routed_rows': rows_hot,
+        'load_imbalance_max_over_mean': rows_hot / (rows_all / world) if rows_all > 0 else None,
     }
-    if world == 1 and not args.skip_cpu_baseline:
+    if with_e2e:
+        line['e2e'] = {'value': t * world / (e2e_ms * 1e-3), 'unit': 'tokens/s', 'ms_per_step': e2e_ms,
+                       'h2d_bytes_per_step': x_host.numel() * 2 + logits_host.numel() * 4, 'd2h_bytes_per_step': y_host.numel() * 2}
+    if with_cpu and cpu_weights is not None:
         idx, w = buf.topk_idx[:t].cpu(), buf.topk_weights[:t].cpu()
         from oracle import quant
         x_q_g, x_sf_g = dg.utils.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32, use_packed_ue8m0=True)
         x_q_c, x_sf_c = x_q_g.cpu(), quant.unpack_ue8m0(x_sf_g.cpu())
         sample = dict(cpu_weights)
         sample.update({'x_q': [], 'x_sf': [], 'w': []})
-        for g in range(CPU_SAMPLE_EXPERTS):
+        for g in range(len(cpu_weights['l1_q'])):
             tok, slot = torch.nonzero(idx == g, as_tuple=True)
             sample['x_q'].append(x_q_c[tok])
             sample['x_sf'].append(x_sf_c[tok])
             sample['w'].append(w[tok, slot])
         srows, dt, cores = time_cpu_sample(sample, 3, 1)
-        line['cpu_baseline'] = {'value': srows / k / dt, 'unit': 'tokens/s', 'cores': cores, 'kind': 'port',
-                                'sample': sample_description(cfg, srows)}
-    print(json.dumps(line), flush=True)
+        line['cpu_baseline'] = cpu_baseline_entry(cfg, srows, dt, cores)
+    buf.destroy()
+    return line, (l1, l2)
+
+
+def kernels_of_one_step(nvfp4, world):
+    """Launches of this library's kernels in one pass of the layer (the memset of the single-rank plan is not a kernel of
+    ours). FP8 layer on one rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the
+    two tile orientations (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather;
+    expert parallel adds the count exchange, the plan, the scale reorder and three barriers."""
+    return 9 if nvfp4 else (11 if world == 1 else 12)
+
+
+L1_STAGE_KERNELS = ('gate/up GEMM + SwiGLU + FP8 requant (dgb200_grouped_gemm_kernel + dgb200_swap_gemm_kernel + '
+                    'dgb200_swiglu_requant_rows_kernel)')
+
+
+def run_ours(args, cfg, rank, world, local_rank):
+    import torch
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+    line, weights = layer_line(args, cfg, rank, world, local_rank, args.steps, args.warmup)
+    headline = world == 1 and cfg.get('mma') != 'nvfp4xnvfp4' and not args.tokens and not args.experts
+    failed = False
+    if world > 1:
+        parity = ep_parity_check(dg, _lib, rank, world)
+        if rank == 0:
+            line['ep_parity'] = parity
+            failed = not parity['ok']
+    elif headline and not args.skip_other_configs:
+        # the same layer at 8192 tokens (the per-rank batch of the expert-parallel runs): the like-for-like base of the
+        # weak-scaling curve; the headline value above stays BASELINE config 3
+        cfg8 = dict(cfg, tokens=8192)
+        base, _ = layer_line(args, cfg8, rank, world, local_rank, max(args.steps // 2, 3), 3, with_e2e=False, with_cpu=False, weights=weights)
+        line['base_8192_tokens_per_rank'] = {k: base[k] for k in ('value', 'unit', 'ms_per_step', 'stages_ms', 'clocks')}
+        del weights
+        torch.cuda.empty_cache()
+        other = {}
+        for name, masked in (('config1_m_grouped_contiguous', False), ('config2_m_grouped_masked', True)):
+            other[name] = measure_gemm_workload(masked, max(args.steps, 10), 3)
+        cfg4 = dict(cfg, mma='nvfp4xnvfp4', tokens=16384)
+        c4, w4 = layer_line(args, cfg4, rank, world, local_rank, max(args.steps // 2, 3), 3, with_e2e=False, with_cpu=False)
+        del w4
+        other['config4_nvfp4_prefill_layer'] = {k: c4[k] for k in ('value', 'unit', 'ms_per_step', 'tflops', 'frac_fp4_dense_peak_nominal',
+                                                                  'stages_ms', 'clocks', 'roofline', 'config')}
+        line['other_configs'] = other
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    return 1 if failed else 0
 
 
 def main():
@@ -661,11 +836,16 @@ def main():
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         torch.cuda.set_device(local_rank)
         dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
-    run_ours(args, cfg, rank, world, local_rank)
+    rc = run_ours(args, cfg, rank, world, local_rank)
     if world > 1:
         import torch.distributed as dist
+        code = torch.tensor([rc], device='cuda')
+        dist.broadcast(code, 0)  # every rank leaves with rank 0's verdict on the parity check
+        rc = int(code)
         dist.barrier()
         dist.destroy_process_group()
+    if rc:
+        raise SystemExit(rc)
 
 
 if __name__ == '__main__':

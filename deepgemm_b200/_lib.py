@@ -19,10 +19,12 @@ _SIGNATURES = {
     'dgb200_version': [],
     'dgb200_set_num_sms': [ctypes.c_int],
     'dgb200_get_num_sms': [],
-    'dgb200_debug_set_trace': [_ptr, _i32],
     'dgb200_set_tuning': [ctypes.c_char_p, _i32],
     'dgb200_device_status': [_ptr, _ptr],
     'dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous': [
+        _ptr, _ptr, _i64, _ptr, _ptr, _i64, _i64, _ptr, _i64, _ptr,
+        _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
+    'dgb200_m_grouped_fp8_fp4_gemm_nn_contiguous': [
         _ptr, _ptr, _i64, _ptr, _ptr, _i64, _i64, _ptr, _i64, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_m_grouped_fp8_fp4_gemm_nt_masked': [

@@ -48,8 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the library if any source is newer than it; returns the path of the shared object."""
     if not force and not is_stale():
         return LIB_PATH
-    extra = ['-DDGB200_INSTRUMENT'] if os.environ.get('DGB200_INSTRUMENT') == '1' else []
-    extra += os.environ.get('DGB200_EXTRA_NVCC_FLAGS', '').split()
+    extra = os.environ.get('DGB200_EXTRA_NVCC_FLAGS', '').split()
     cmd = [_nvcc()] + NVCC_FLAGS + extra + (['-Xptxas', '-v'] if verbose else []) + \
           ['-o', LIB_PATH, os.path.join(CSRC, 'dgb200.cu')]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -6,7 +6,6 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
-#include <unordered_map>
 
 #include "host_common.cuh"
 #include "gemm_kernel.cuh"
@@ -51,7 +50,8 @@ struct GemmCall {
                             // epilogue may write all 128 rows of every tile
     long long a_rows_total;  // rows of the flattened A
     long long a_row_stride_bytes, b_row_stride_bytes;  // BF16 kind only: row pitches of A and B
-    int b_mn_major;  // BF16 kind only: B is [groups * k, n] with n contiguous (b_row_stride_bytes = pitch of a K row)
+    int b_mn_major;  // BF16 kind: B is [groups * k, n] with n contiguous (b_row_stride_bytes = pitch of a K row); FP8 x FP4
+                     // kind: likewise, dense rows of n bytes (E4M3) or n / 2 bytes (packed E2M1, two N elements per byte)
     int a_mn_major;  // BF16 kind, dense mode only: A is [k, m] with m contiguous (a_row_stride_bytes = pitch of a K row)
     GemmParams p;
     int b_is_fp4;
@@ -62,11 +62,9 @@ struct GemmCall {
 // Process-wide tuning knobs (defaults are the measured best on B200).
 struct Tuning {
     int swap_ab = -1;  // layer GEMMs: tokens on the UMMA N side (-1 = by expected rows per expert, 0 = never, 1 = always)
-    int prefetch_distance = 0;
     int block_n = 0;  // 0 = automatic
-    int debug_skip = 0;
-    long long* trace = nullptr;  // debugging: per-role clock64() samples of CTA 0 (8 roles x trace_cap)
-    int trace_cap = 0;
+    long long peer_wait_cycles = 20000000000ll;  // budget of a wait for another rank, SM clock cycles (about 10 s: ranks
+                                                 // may reach their first call seconds apart)
 };
 
 Tuning& tuning() {
@@ -173,6 +171,18 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
                                 static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
         p.b_fmt = kFmtE2M1_MXF4;
         p.b_tx_bytes = BLOCK_N * 128;
+    } else if (c.b_mn_major) {
+        // [groups * k, n] with n contiguous: boxes of 128 channels x 128 K rows, read through MN-major descriptors
+        const uint64_t k_rows = static_cast<uint64_t>(p.num_groups) * p.k;
+        if (c.b_is_fp4)
+            rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, c.b, static_cast<uint64_t>(p.n), k_rows,
+                                    static_cast<uint64_t>(p.n / 2), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        else
+            rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, c.b, static_cast<uint64_t>(p.n), k_rows,
+                                    static_cast<uint64_t>(p.n), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        p.b_fmt = c.b_is_fp4 ? kFmtE2M1_F8F6F4 : kFmtE4M3;
+        p.b_tx_bytes = BLOCK_N * (c.b_is_fp4 ? 64 : 128);
+        p.b_mn_major = 1;
     } else if (c.b_is_fp4) {
         rc = make_tensor_map_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, c.b, static_cast<uint64_t>(p.k), b_rows,
                                 static_cast<uint64_t>(p.k / 2), 128, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -213,14 +223,6 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
         if (rc) return rc;
         p.tma_store = c.whole_tile_stores ? 2 : 1;
     }
-
-    p.prefetch_distance = tuning().prefetch_distance;
-    p.b_ptr = static_cast<const unsigned char*>(c.b);
-    p.b_row_bytes = bf16 ? static_cast<int>(c.b_row_stride_bytes) : (nvfp4 || c.b_is_fp4) ? p.k / 2 : p.k;
-    p.b_kb_bytes = (c.b_is_fp4 && !nvfp4) ? 64 : 128;
-    p.debug_skip = tuning().debug_skip;
-    p.trace = tuning().trace;
-    p.trace_cap = tuning().trace_cap;
 
     int sms = 0;
     rc = effective_num_sms(&sms);
@@ -349,8 +351,6 @@ int run_gemm_swap(GemmCall& c, cudaStream_t stream) {
         p.b_tx_bytes = 256 * 128;
     }
     if (rc) return rc;
-    p.trace = tuning().trace;
-    p.trace_cap = tuning().trace_cap;
     int sms = 0;
     rc = effective_num_sms(&sms);
     if (rc) return rc;
@@ -739,16 +739,6 @@ int run_shared_x_sf(const MegaLayout& l, uint8_t* base, int num_tokens, int hidd
     return 0;
 }
 
-// Epoch counter of the cross-rank barriers, one per buffer (all ranks call in lockstep, so the counters agree).
-uint32_t next_barrier_epoch(const void* buffer) {
-    static std::mutex mu;
-    static std::unordered_map<const void*, uint32_t> epochs;
-    std::lock_guard<std::mutex> lock(mu);
-    return ++epochs[buffer];
-}
-
-constexpr long long kPeerWaitBudgetCycles = 20000000000ll;  // about 10 s: ranks may reach their first call seconds apart
-
 int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const void* l1_w, const void* l1_w_sf, const void* l2_w, const void* l2_w_sf,
                     int32_t* stats, uint8_t* base, const uint64_t* peer_buffer_ptrs, int rank, int num_ranks, int num_tokens,
                     int num_max_tokens_per_rank, int num_experts, int num_topk, int hidden, int intermediate_hidden,
@@ -767,14 +757,14 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
     const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
     const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
-    const uint32_t epoch0 = next_barrier_epoch(base) * 4;
+    const long long peer_budget = tuning().peer_wait_cycles;
     int rc = 0;
     if ((rc = record_stage(0, stream))) return rc;
 
     // count this rank's entries per (global) expert and publish the totals to every rank
     dgb200_moe_count_kernel<<<chunks, kPlanChunk, num_experts * sizeof(int), stream>>>(topk_idx, entries, 0, num_experts, chunk_hist);
     dgb200_ep_share_counts_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, num_experts, rank, num_ranks, peers, l.all_counts);
-    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 0, rank, num_ranks, static_cast<int>(epoch0 + 1), kPeerWaitBudgetCycles);
+    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 0, rank, num_ranks, peer_budget);
     // the same global plan on every rank, then push rows to their owners
     dgb200_ep_plan_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
                                                    kSegmentAlignment, reinterpret_cast<int*>(base + l.my_base),
@@ -800,7 +790,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         return rc;
     }
     DGB_CUDA(cudaGetLastError());
-    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, static_cast<int>(epoch0 + 2), kPeerWaitBudgetCycles);
+    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, peer_budget);
     // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
     if (sf_per_row > 0)
         dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
@@ -816,7 +806,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         if (quant.x_bf16 == nullptr && quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
         if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
     }
-    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, static_cast<int>(epoch0 + 3), kPeerWaitBudgetCycles);
+    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, peer_budget);
     if (num_tokens > 0)
         dgb200_moe_combine_kernel<<<num_tokens, 128, (num_topk + 1) * sizeof(unsigned long long), stream>>>(
             peers, l.l2_out, topk_idx, dest_row, num_topk, l.num_local_experts, hidden,
@@ -984,23 +974,15 @@ int dgb200_set_tuning(const char* name, int32_t value) {
     if (std::strcmp(name, "swap_ab") == 0) {
         DGB_REQUIRE(value >= -1 && value <= 2, "swap_ab must be -1 (automatic), 0, 1 or 2");
         tuning().swap_ab = value;
-    } else if (std::strcmp(name, "prefetch_distance") == 0) {
-        DGB_REQUIRE(value >= 0 && value <= 4096, "prefetch_distance must be in [0, 4096]");
-        tuning().prefetch_distance = value;
     } else if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
-    } else if (std::strcmp(name, "debug_skip") == 0) {
-        tuning().debug_skip = value;
+    } else if (std::strcmp(name, "peer_wait_us") == 0) {
+        DGB_REQUIRE(value >= 1, "peer_wait_us must be at least 1 microsecond");
+        tuning().peer_wait_cycles = static_cast<long long>(value) * 2000;  // SM clock below 2 GHz: at least `value` us
     } else {
         return fail(DGB200_EINVAL, "unknown tuning knob '%s'", name);
     }
-    return 0;
-}
-
-int dgb200_debug_set_trace(void* device_buffer, int32_t capacity_per_role) {
-    tuning().trace = static_cast<long long*>(device_buffer);
-    tuning().trace_cap = device_buffer != nullptr ? capacity_per_role : 0;
     return 0;
 }
 
@@ -1025,9 +1007,10 @@ int dgb200_device_status(int32_t* out_words, void* stream) {
     return 0;
 }
 
-int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
+namespace {
+int run_m_grouped_contiguous(
     const void* a, const void* sfa, int64_t sfa_k_stride,
-    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
+    const void* b, int b_mn_major, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
     void* d, int64_t d_row_stride, const int32_t* grouped_layout,
     int32_t m, int32_t n, int32_t k, int32_t num_groups,
     int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
@@ -1045,6 +1028,7 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
     GemmCall c{};
     c.a = a;
     c.b = b;
+    c.b_mn_major = b_mn_major;
     c.a_rows_total = m;
     c.b_is_fp4 = b_is_fp4;
     c.epilogue = d_is_fp32 ? kEpiF32 : kEpiBF16;
@@ -1071,6 +1055,32 @@ int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
     const long long m_blocks = (static_cast<long long>(m) + 127) / 128 + (p.mode == kModePsum ? num_groups : 0);
     c.max_tiles = static_cast<int>(std::min<long long>(m_blocks * (n / 128 > 0 ? n / 128 : 1), 1 << 30));
     return run_gemm(c, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
+    const void* a, const void* sfa, int64_t sfa_k_stride,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
+    void* d, int64_t d_row_stride, const int32_t* grouped_layout,
+    int32_t m, int32_t n, int32_t k, int32_t num_groups,
+    int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
+    int32_t layout_kind, int32_t alignment, int32_t store_padding, void* stream) {
+    return run_m_grouped_contiguous(a, sfa, sfa_k_stride, b, 0, sfb, sfb_k_stride, sfb_group_stride, d, d_row_stride, grouped_layout,
+                                    m, n, k, num_groups, gran_k_a, gran_k_b, b_is_fp4, d_is_fp32, layout_kind, alignment,
+                                    store_padding, stream);
+}
+
+int dgb200_m_grouped_fp8_fp4_gemm_nn_contiguous(
+    const void* a, const void* sfa, int64_t sfa_k_stride,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
+    void* d, int64_t d_row_stride, const int32_t* grouped_layout,
+    int32_t m, int32_t n, int32_t k, int32_t num_groups,
+    int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
+    int32_t layout_kind, int32_t alignment, int32_t store_padding, void* stream) {
+    DGB_REQUIRE(n % 32 == 0, "an MN-major b needs n (%d) to be a multiple of 32", n);
+    return run_m_grouped_contiguous(a, sfa, sfa_k_stride, b, 1, sfb, sfb_k_stride, sfb_group_stride, d, d_row_stride, grouped_layout,
+                                    m, n, k, num_groups, gran_k_a, gran_k_b, b_is_fp4, d_is_fp32, layout_kind, alignment,
+                                    store_padding, stream);
 }
 
 int dgb200_fp8_fp4_gemm_nt(const void* a, const void* sfa, int64_t sfa_k_stride, const void* b, const void* sfb,
@@ -1519,10 +1529,10 @@ int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num
     const int rc = make_mega_layout(kKindFp8Fp4, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
                                     intermediate_hidden, &l, shared_intermediate_hidden);
     if (rc) return rc;
-    const long long fields[20] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+    const long long fields[21] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
                                   l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight,
-                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out};
-    for (int i = 0; i < 20; ++i) out[i] = fields[i];
+                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out, l.flags};
+    for (int i = 0; i < 21; ++i) out[i] = fields[i];
     return 0;
 }
 
@@ -1589,10 +1599,10 @@ int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t n
     const int rc = make_mega_layout(kKindBf16, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
                                     intermediate_hidden, &l, shared_intermediate_hidden);
     if (rc) return rc;
-    const long long fields[20] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+    const long long fields[21] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
                                   l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight,
-                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out};
-    for (int i = 0; i < 20; ++i) out[i] = fields[i];
+                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out, l.flags};
+    for (int i = 0; i < 21; ++i) out[i] = fields[i];
     return 0;
 }
 

@@ -78,14 +78,6 @@ struct GemmParams {
     int rows_lo, rows_hi;    // psum / masked layouts: only groups whose valid rows lie in [rows_lo, rows_hi] (rows_skip = 0)
     int rows_skip;           // ... or outside it (rows_skip = 1) are computed; {0, 0, 0} = every group. Lets two kernels
                              // with different tile orientations split the groups of one GEMM by size.
-    int prefetch_distance;   // K blocks the weight prefetch cursor runs ahead of the loads (0 = off)
-    const unsigned char* b_ptr;  // raw view of the weights for the prefetch cursor (the loads go through the tensor map)
-    long long b_row_bytes;       // row pitch of B in bytes
-    int b_kb_bytes;              // bytes of one B row inside one K block: 64 (packed FP4 of the FP8 x FP4 kind) or 128
-    int debug_skip;          // timing experiments only (results become garbage): bit 0 no A loads, 1 no B loads,
-                             // 2 no scale-factor loads, 3 no MMA instructions, 4 no scale-factor TMEM copies
-    long long* trace;        // optional: CTA 0 records clock64() per role and K block at trace[role * trace_cap + i]
-    int trace_cap;
     // SwiGLU epilogue only
     unsigned char* act_q;        // e4m3 [rows, n/2]
     int tma_store;               // epilogue stores through shared memory + TMA (BLOCK_N = 256, FP8 x FP4 kind): 0 never,
@@ -105,7 +97,8 @@ struct GemmParams {
     const float* out_scale;
     const float* c;  // kEpiF32Acc: unused by the kernel (the host puts c into d before the launch)
     int a_mn_major;  // BF16 kind, dense mode only: A is [k, m] with m contiguous (the reference's "tn" / "tt" forms)
-    int b_mn_major;  // BF16 kind only: B is [groups * k, n] with n contiguous (the reference's "nn" forms) instead of [groups * n, k]
+    int b_mn_major;  // BF16 and FP8 x FP4 kinds: B is [groups * k, n] with n contiguous (the reference's "nn" forms; packed FP4
+                     // then holds two consecutive N elements per byte) instead of [groups * n, k]
     int accumulate;  // kEpiF32 only: d += accumulator instead of d = accumulator (the dense GEMMs' input c, already in d)
     int kg_psum;     // kModeKGrouped: layout[g] is the end K row of group g (groups start at multiples of `alignment`,
                      // the gap rows are zero) instead of its K extent
@@ -294,18 +287,6 @@ __device__ __forceinline__ void ue8m0_scale_for_amax(float amax, float& sf_inv, 
     sf_inv = __uint_as_float((254u - e) << 23);  // 2^(127-e)
 }
 
-// Instrumentation (per-role clock samples, load / MMA skipping for timing experiments) is compiled in only with
-// -DDGB200_INSTRUMENT: even a never-taken branch is measurable in the single-thread issue loops below.
-#ifdef DGB200_INSTRUMENT
-__device__ __forceinline__ void trace_point(const GemmParams& p, int role, int index) {
-    if (p.trace != nullptr && blockIdx.x == 0 && index < p.trace_cap) p.trace[role * p.trace_cap + index] = clock64();
-}
-#define DGB_SKIP(p, bit) (((p).debug_skip & (bit)) != 0)
-#else
-__device__ __forceinline__ void trace_point(const GemmParams&, int, int) {}
-#define DGB_SKIP(p, bit) false
-#endif
-
 constexpr int kGemmThreads = 384;       // warps 0-3: loaders / MMA / transposer; warps 4-11: epilogue
 constexpr int kRegsControlWarps = 96;   // after setmaxnreg: the control warpgroup gives registers away ...
 constexpr int kRegsEpilogueWarps = 200; // ... to the two epilogue warpgroups, which hold a drained accumulator
@@ -347,14 +328,12 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     uint64_t* tmem_empty_bar = bars + 3 * kStages + 2;
     uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffMisc + 4);
-    volatile int* load_progress = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);  // K blocks the weight loader has issued
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        *load_progress = 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(full_bar + i, 2);       // the A-side loader and the B-side loader
             mbar_init(empty_bar + i, 1);      // tcgen05.commit of the MMA issuer
@@ -386,7 +365,15 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             for (int i = 0; i < p.num_groups; ++i) {
                 int start, len;
                 k_group_extent(p.layout, i, p.kg_psum, p.alignment, prev_end, start, len);
-                const int blocks = (len + kBlockK - 1) / kBlockK;  // a partial last block reads the zero rows of the gap
+                // Plain layout: the groups abut, so an extent that is not a whole number of K blocks would make the
+                // last block read the next group's rows, and extents that overrun the operands would read past them.
+                // Such a group is reported and left out (d keeps c). In the psum layout a partial last block reads
+                // the zero rows of the gap, which is what that layout is for.
+                if (len < 0 || start + len > p.k || (!p.kg_psum && len % kBlockK != 0)) {
+                    report_error(kBadArgument, i, len);
+                    len = 0;
+                }
+                const int blocks = (len + kBlockK - 1) / kBlockK;
                 group_cache[i] = blocks;
                 group_start[i] = start;
                 group_tiles_end[i] = kp;
@@ -447,7 +434,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            int trace_i = 0;
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
                 const int sfa_y = kKG ? t.sf_kp0 : t.group * p.sfa_group_rows;
@@ -455,10 +441,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 for (int kb = 0; kb < tile_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfa = kScaled && kb % a_per == 0 && !DGB_SKIP(p, 4);
+                    const bool load_sfa = kScaled && kb % a_per == 0;
                     if (elect_one()) {
-                        trace_point(p, 0, trace_i);
-                        mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 1) ? 0 : L::kABytes) + (load_sfa ? L::kSfaBytes : 0));
+                        mbar_arrive_expect_tx(full_bar + stage, L::kABytes + (load_sfa ? L::kSfaBytes : 0));
                         if constexpr (kKG) {
                             // MN-major A: one box per 128 bytes of M (128 E4M3 or 64 BF16 channels) x kBlockK K rows
                             constexpr int kBoxes = kKind == kKindBf16 ? 2 : 1;
@@ -471,16 +456,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             for (int h = 0; h < 2; ++h)
                                 tma_load_2d(smem + L::kOffA + stage * L::kABytes + h * 8192, &tm_a, full_bar + stage,
                                             t.row_start + h * 64, kb * 64);
-                        } else if (!DGB_SKIP(p, 1))
+                        } else
                             tma_load_2d(smem + L::kOffA + stage * L::kABytes, &tm_a, full_bar + stage, kb * kTmaXPerKb,
                                         t.row_start);
                         if (load_sfa)
                             tma_load_2d(smem + L::kOffSfa + stage * L::kSfaBytes, &tm_sfa, full_bar + stage,
                                         t.sf_row_start, sfa_y + kb * kSfInts / a_per);
-                        trace_point(p, 1, trace_i);
                     }
                     __syncwarp();
-                    ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -492,10 +475,8 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            int trace_i = 0;
 
             const bool leader = elect_one();
-            int issued = 0;
 
             while (ok && sched.next(t)) {
                 if (t.group < 0) continue;
@@ -505,10 +486,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 for (int kb = 0; kb < tile_kb; ++kb) {
                     ok = mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, kTimeoutEmpty, kb);
                     if (!ok) break;
-                    const bool load_sfb = kScaled && kb % b_per == 0 && !DGB_SKIP(p, 4);
+                    const bool load_sfb = kScaled && kb % b_per == 0;
                     if (leader) {
-                        trace_point(p, 9, trace_i);
-                        mbar_arrive_expect_tx(full_bar + stage, (DGB_SKIP(p, 2) ? 0 : p.b_tx_bytes) + (load_sfb ? L::kSfbBytes : 0));
+                        mbar_arrive_expect_tx(full_bar + stage, p.b_tx_bytes + (load_sfb ? L::kSfbBytes : 0));
                         if constexpr (kKG) {
                             // one box per 128 bytes of N (a swizzle span: 128 E4M3 or 64 BF16 channels) x kBlockK K rows
                             constexpr int kChan = kKind == kKindBf16 ? 64 : 128;
@@ -522,19 +502,21 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             for (int h = 0; h < BLOCK_N / 64; ++h)
                                 tma_load_2d(smem + L::kOffB + stage * L::kBBytes + h * 8192, &tm_b, full_bar + stage,
                                             t.n_block * BLOCK_N + h * 64, t.group * p.k + kb * 64);
-                        } else if (!DGB_SKIP(p, 2))
+                        } else if (kKind == kKindFp8Fp4 && p.b_mn_major) {
+                            // MN-major 8-bit (or 4-bit in byte containers) weights: boxes of 128 channels x 128 K rows
+#pragma unroll
+                            for (int h = 0; h < BLOCK_N / 128; ++h)
+                                tma_load_2d(smem + L::kOffB + stage * L::kBBytes + h * 16384, &tm_b, full_bar + stage,
+                                            t.n_block * BLOCK_N + h * 128, t.group * p.k + kb * 128);
+                        } else
                             tma_load_2d(smem + L::kOffB + stage * L::kBBytes, &tm_b, full_bar + stage, kb * kTmaXPerKb, b_row);
                         if (load_sfb)
                             tma_load_2d(smem + L::kOffSfb + stage * L::kSfbBytes, &tm_sfb, full_bar + stage,
                                         t.n_block * BLOCK_N, sfb_y + kb * kSfInts / b_per);
-                        trace_point(p, 10, trace_i);
-                        if (p.prefetch_distance > 0) *load_progress = ++issued;
                     }
-                    ++trace_i;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
-            if (leader) *load_progress = 0x3fffffff;  // lets the prefetch cursor run to its end
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -543,7 +525,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
         Tile t;
         uint32_t stage = 0, phase = 0, iter = 0;
-        int trace_i = 0;
         const uint32_t idesc = kKG
             ? ((kKind == kKindBf16 ? make_idesc_bf16_f32(128, BLOCK_N)
                                    : make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, 128, BLOCK_N, kScaleUE8M0)) |
@@ -551,37 +532,32 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             : kKind == kKindBf16
             ? (make_idesc_bf16_f32(128, BLOCK_N) | (p.a_mn_major ? (1u << 15) : 0u) | (p.b_mn_major ? (1u << 16) : 0u))
             : kKind == kKindNvfp4 ? make_idesc_block_scaled(kFmtE2M1_MXF4, kFmtE2M1_MXF4, 128, BLOCK_N, kScaleUE4M3)
-                                  : make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0);
+                                  : (make_idesc_block_scaled(kFmtE4M3, p.b_fmt, 128, BLOCK_N, kScaleUE8M0) |
+                                     (p.b_mn_major ? (1u << 16) : 0u));
         const uint32_t a_base = smem_u32(smem + L::kOffA), b_base = smem_u32(smem + L::kOffB);
         const uint32_t sfa_smem = smem_u32(smem + L::kOffSfa), sfb_smem = smem_u32(smem + L::kOffSfb);
         uint32_t tmem_sfa = 0, tmem_sfb = 0;  // TMEM columns holding the scale factors of the current K block
         const bool leader = elect_one();      // the same lane issues every tcgen05 instruction of this CTA
         bool ok = true;
-        if (lane == 0) trace_point(p, 14, 0);
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
-            if (lane == 0) trace_point(p, 15, static_cast<int>(iter));
             ++iter;
             ok = mbar_wait(tmem_empty_bar + as, aphase ^ 1, abort_flag, kTimeoutTmemEmpty, static_cast<int>(iter));
             if (!ok) break;
-            if (lane == 0) trace_point(p, 14, static_cast<int>(iter));
             tcgen05_fence_after();
             const uint32_t tmem_acc = tmem_base + as * kAccumCols;
             const int tile_kb = kKG ? t.num_kb : num_kb;
             if (kKG && tile_kb == 0 && leader) tcgen05_commit(tmem_full_bar + as);  // empty group: D = C, nothing to wait for
             for (int kb = 0; kb < tile_kb; ++kb) {
                 // scale factors stored in tcgen05.cp order need no transposer pass: the loads' barrier is enough
-                if (lane == 0) trace_point(p, 8, trace_i);
                 ok = mbar_wait(((!kScaled || (p.sf_transposed && !kCpByHelper)) ? full_bar : sf_ready_bar) + stage, phase, abort_flag,
                                kTimeoutSfReady, kb);
                 if (!ok) break;
                 if (kCpByHelper && p.sf_transposed) tcgen05_fence_after();  // the helper warp's tcgen05.cp precede our MMAs
-                if (lane == 0) trace_point(p, 11, trace_i);
                 // No tcgen05 fence here: the data this wait covers was written to shared memory through the async proxy
                 // (TMA, or the transposer's stores followed by its proxy fence), not by tcgen05 operations.
                 if (leader) {
-                    trace_point(p, 4, trace_i);
                     // One tcgen05.cp moves the scales of 128 rows for one MMA (one packed int per row) into 4 TMEM columns.
                     const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
                     const bool cp_here = kScaled && !(kCpByHelper && p.sf_transposed);
@@ -605,18 +581,16 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     const bool a_mn = kKG || (kKind == kKindBf16 && p.a_mn_major);
                     const uint64_t adesc = a_mn ? make_mnmajor_sw128_desc(a_base + stage * L::kABytes, 128 * kBlockK)
                                                 : make_kmajor_sw128_desc(a_base + stage * L::kABytes);
-                    const bool b_mn = kKG || (kKind == kKindBf16 && p.b_mn_major);
+                    const bool b_mn = kKG || ((kKind == kKindBf16 || kKind == kKindFp8Fp4) && p.b_mn_major);
                     const uint64_t bdesc = b_mn ? make_mnmajor_sw128_desc(b_base + stage * L::kBBytes, 128 * kBlockK)
                                                 : make_kmajor_sw128_desc(b_base + stage * L::kBBytes);
                     // K-major: +32 bytes along K inside the swizzle span per MMA; MN-major: the K rows of one MMA (32 E4M3 or
                     // 16 BF16) are 4 or 2 groups of 8 rows = 1024 B each
                     constexpr uint32_t kDescStep = kKG ? (kKind == kKindBf16 ? 128 : 256) : 2;
                     const uint32_t a_step = (kKind == kKindBf16 && a_mn) ? 128u : kDescStep;
-                    const uint32_t b_step = (kKind == kKindBf16 && b_mn) ? 128u : kDescStep;
-                    trace_point(p, 12, trace_i);
+                    const uint32_t b_step = (kKind == kKindBf16 && b_mn) ? 128u : ((kKind == kKindFp8Fp4 && b_mn) ? 256u : kDescStep);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
-                        if (DGB_SKIP(p, 8)) continue;
                         // +32 bytes along K inside the 128-byte swizzle span = +2 in the (addr >> 4) field
                         if constexpr (kKind == kKindBf16) {
                             // K = 16 BF16 elements (32 bytes) per MMA
@@ -628,17 +602,14 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         } else {
                             const uint32_t sfa_id = p.gran_a == 32 ? k4 : static_cast<uint32_t>(kb % 4);
                             const uint32_t sfb_id = p.gran_b == 32 ? k4 : static_cast<uint32_t>(kb % 4);
-                            tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * kDescStep, bdesc + k4 * kDescStep,
+                            tcgen05_mma_mxf8f6f4(tmem_acc, adesc + k4 * a_step, bdesc + k4 * b_step,
                                                  idesc_with_sf_ids(idesc, sfa_id, sfb_id), tmem_sfa, tmem_sfb,
                                                  (kb | k4) != 0 ? 1u : 0u);
                         }
                     }
-                    trace_point(p, 13, trace_i);
                     tcgen05_commit(empty_bar + stage);
                     if (kb == tile_kb - 1) tcgen05_commit(tmem_full_bar + as);
-                    trace_point(p, 5, trace_i);
                 }
-                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -649,7 +620,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         TileScheduler<BLOCK_N, EPI == kEpiF32Acc> sched(p, group_layout);
         Tile t;
         uint32_t stage = 0, phase = 0;
-        int trace_i = 0;
         bool ok = kScaled && p.sf_transposed == 0;  // nothing to do when the scale factors arrive in tcgen05.cp order
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
@@ -657,7 +627,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             for (int kb = 0; kb < tile_kb; ++kb) {
                 ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
-                if (lane == 0) trace_point(p, 2, trace_i);
                 // All reads first, one warp barrier, then all writes: this warp serves every K block in turn, so its
                 // service time bounds the whole pipeline.
                 const bool do_a = kb % a_per == 0, do_b = kb % b_per == 0;
@@ -690,8 +659,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sf_ready_bar + stage);
-                if (lane == 0) trace_point(p, 3, trace_i);
-                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -719,55 +686,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         tcgen05_commit(sf_ready_bar + stage);  // arrives once the copies above have completed
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
-                }
-            }
-        }
-        if (p.sf_transposed != 0 && p.prefetch_distance > 0) {
-            // With nothing to transpose this warp is free: it walks the tile sequence p.prefetch_distance K blocks ahead
-            // of the loads and prefetches the weight rows into L2 with plain
-            // prefetch instructions. Weight tiles are read once from HBM and the stages that fit in shared memory do
-            // not cover that latency; TMA prefetches would, but they cost the TMA unit a box row per cycle.
-            TileScheduler<BLOCK_N, EPI == kEpiF32Acc> pf_sched(p, group_layout);
-            Tile pt;
-            int pf_kb = 0;
-            bool pf_valid = false;
-            const unsigned char* pf_base = nullptr;
-            auto pf_next_tile = [&]() {
-                pf_valid = false;
-                while (pf_sched.next(pt)) {
-                    if (pt.group >= 0) { pf_valid = true; break; }
-                }
-                pf_kb = 0;
-                if (pf_valid)
-                    pf_base = p.b_ptr + (static_cast<long long>(pt.group) * p.n + pt.n_block * BLOCK_N + lane) * p.b_row_bytes;
-            };
-            auto pf_advance = [&]() {
-                if (!pf_valid) return;
-                const long long col = static_cast<long long>(pf_kb) * p.b_kb_bytes;
-                if ((col & 127) == 0) {  // one 128-byte line covers two K blocks of packed FP4
-#pragma unroll
-                    for (int j = 0; j < BLOCK_N / 32; ++j) prefetch_l2(pf_base + j * 32 * p.b_row_bytes + col);
-                }
-                if (++pf_kb == num_kb) pf_next_tile();
-            };
-            // Paced by the weight loader's progress counter (K blocks issued so far; a huge value once it is done).
-            pf_next_tile();
-            long long done = 0;
-            long long t0 = 0;
-            uint32_t spins = 0;
-            while (pf_valid) {
-                const long long target = static_cast<long long>(*load_progress) + p.prefetch_distance;
-                if (done < target) {
-                    pf_advance();
-                    ++done;
-                    continue;
-                }
-                __nanosleep(200);
-                if (((++spins) & 0xffu) == 0) {  // bounded like every other wait of this kernel
-                    if (*abort_flag != 0) break;
-                    const long long now = clock64();
-                    if (t0 == 0) t0 = now;
-                    else if (now - t0 > kWaitBudgetCycles) break;  // a prefetcher that gives up costs speed, not correctness
                 }
             }
         }
@@ -814,7 +732,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty_bar + as);
-            if (threadIdx.x == 128) trace_point(p, 6, static_cast<int>(iter) - 1);
             // Row-per-thread stores put 32 different cache lines into every store instruction, and the burst of a whole
             // tile keeps the load/store pipe busy long enough to stall the control warps' shared-memory accesses.
             // Staging the warp's 32 x 64-byte slab in shared memory and handing it to TMA costs 4 store wavefronts
@@ -824,7 +741,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             // 16-byte chunk c of this thread's 64-byte row in the 64-byte swizzle pattern of the tensor map
             auto stage_chunk = [&](int c) { return reinterpret_cast<uint4*>(stage_buf + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)); };
 
-            const bool store = r < t.rows_store && !DGB_SKIP(p, 32);
+            const bool store = r < t.rows_store;
             const long long row = static_cast<long long>(t.row_start) + r;
             const long long sf_row = p.act_sf_transposed ? sf_row_in_cp_order(row) : row;  // used by the SwiGLU epilogues
             if constexpr (kKind == kKindNvfp4) {
@@ -1087,7 +1004,6 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     }
                 }
             }
-            if (threadIdx.x == 128) trace_point(p, 7, static_cast<int>(iter) - 1);
         }
         if (L::kStageBytesPerWarp != 0 && lane == 0) bulk_wait_group_all();  // stores still in flight read this CTA's shared memory
     }

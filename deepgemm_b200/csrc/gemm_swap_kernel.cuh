@@ -225,7 +225,6 @@ dgb200_swap_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
         const uint32_t w_base = smem_u32(smem + L::kOffW), x_base = smem_u32(smem + L::kOffX);
         const uint32_t sfw_smem = smem_u32(smem + L::kOffSfw), sfx_smem = smem_u32(smem + L::kOffSfx);
         const bool leader = elect_one();
-        int trace_i = 0;
         bool ok = true;
         while (ok && sched.next(t)) {
             ok = mbar_wait(tmem_empty_bar, (iter & 1) ^ 1, abort_flag, kTimeoutTmemEmpty, static_cast<int>(iter));
@@ -239,7 +238,6 @@ dgb200_swap_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
                 ok = mbar_wait(full_bar + stage, phase, abort_flag, kTimeoutFull, kb);
                 if (!ok) break;
                 if (leader) {
-                    trace_point(p, 4, trace_i);
                     const uint32_t sf_cols = tmem_base + kSfCol0 + stage * kSfColsPerStage;
                     const uint32_t tmem_sfw = sf_cols, tmem_sfx = sf_cols + 8;
                     tcgen05_cp_32x128b_warpx4(tmem_sfw, make_sf_desc(sfw_smem + stage * L::kSfwBytes));
@@ -260,7 +258,6 @@ dgb200_swap_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
                     tcgen05_commit(empty_bar + stage);
                     if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar);
                 }
-                ++trace_i;
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -298,7 +295,6 @@ dgb200_swap_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty_bar);
-            if (threadIdx.x == 128) trace_point(p, 6, static_cast<int>(iter) - 1);
 
             if constexpr (EPI == kEpiSwiGLU) {
                 // accumulator 0 = gate channels, accumulator 1 = up channels of output channels j .. j + 127
@@ -347,7 +343,6 @@ dgb200_swap_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
                     }
                 }
             }
-            if (threadIdx.x == 128) trace_point(p, 7, static_cast<int>(iter) - 1);
         }
     }
 

@@ -292,17 +292,29 @@ dgb200_ep_share_counts_kernel(int* __restrict__ chunk_hist, int num_chunks, int 
     }
 }
 
-// Cross-rank barrier: one warp; lane r signals rank r and waits for rank r's signal. Flags only grow (epoch), so they
-// never need a reset. Bounded: a peer that does not show up within the budget is reported, not waited for forever.
+// Cross-rank barrier: one warp; lane r signals rank r and waits for rank r's signal. The flags region of the buffer is
+// int [4][kMaxEpRanks]: row `which` (0..2) holds, in slot r, the epoch rank r last signalled for that barrier; row 3
+// holds this rank's own epoch counters (word `which`), advanced by this kernel. The epoch therefore lives and dies
+// with the buffer (zeroed once when the buffer is created, on every rank, before the first call): a replayed launch
+// advances it like a fresh one, and a new buffer at a recycled address starts from zero on every rank alike. Flags
+// only grow, so they never need a reset. Bounded: a peer that does not show up within the budget is reported through
+// the status block, not waited for forever.
 __global__ void __launch_bounds__(32)
 dgb200_ep_barrier_kernel(const PeerTable peers, long long flags_offset, int which, int my_rank,
-                         int num_ranks, int epoch, long long budget_cycles) {
+                         int num_ranks, long long budget_cycles) {
     const int lane = threadIdx.x;
+    int* local = reinterpret_cast<int*>(peers.p[my_rank] + flags_offset);
+    int epoch = 0;
+    if (lane == 0) {
+        epoch = local[3 * kMaxEpRanks + which] + 1;
+        local[3 * kMaxEpRanks + which] = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
     __threadfence_system();
     if (lane < num_ranks) {
         int* remote = reinterpret_cast<int*>(peers.p[lane] + flags_offset) + which * kMaxEpRanks + my_rank;
         asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(remote), "r"(epoch) : "memory");
-        const int* mine = reinterpret_cast<const int*>(peers.p[my_rank] + flags_offset) + which * kMaxEpRanks + lane;
+        const int* mine = local + which * kMaxEpRanks + lane;
         const long long t0 = clock64();
         while (true) {
             int seen;

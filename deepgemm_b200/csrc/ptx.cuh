@@ -185,28 +185,6 @@ __device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.as
 // Returns once those stores are complete (their writes performed).
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// L2 prefetch of one tile / one span: starts the HBM read early without occupying shared memory.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                 :: "l"(map), "r"(x), "r"(y) : "memory");
-}
-
-__device__ __forceinline__ void bulk_prefetch_1d(const void* gmem_src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gmem_src), "r"(bytes) : "memory");
-}
-
-// Plain L2 prefetch of the cache line holding `p` (issued from ordinary lanes, so it does not occupy the TMA unit).
-__device__ __forceinline__ void prefetch_l2(const void* p) {
-    asm volatile("prefetch.global.L2 [%0];" :: "l"(p));
-}
-
-// `bytes` must be a multiple of 16; both addresses 16-byte aligned.
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        :: "r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
 // ----------------------------------------------------------------------------------------------
 // tcgen05: tensor memory management
 // ----------------------------------------------------------------------------------------------
@@ -333,18 +311,6 @@ __device__ __forceinline__ void tcgen05_mma_mxf4nvf4_4x(uint32_t tmem_d, uint64_
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
-        "}\n"
-        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
-}
-
-// Packed E2M1 x E2M1, K = 64 per instruction, one UE8M0 scale per 32 K (MXFP4 on both sides).
-__device__ __forceinline__ void tcgen05_mma_mxf4_2x(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                                    uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
         "}\n"
         :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
 }

@@ -27,6 +27,23 @@ def _check_ab(t: torch.Tensor, rank: int, name: str):
     return tuple(t.shape[:-1]) + (k,)
 
 
+def _check_grouped_b(t: torch.Tensor):
+    """b of the m-grouped contiguous GEMM, logically [G, N, K]: K-major and contiguous, or MN-major, i.e. a transposed
+    view of contiguous [G, K, N] storage (FP8) or [G, K, N / 2] storage (packed FP4, two N elements per byte, logical
+    shape [G, N / 2, K]), as the reference accepts on SM100 (csrc/apis/gemm.hpp:181-183, tests/generators.py:282-292).
+    Returns (num_groups, n, k, mn_major)."""
+    if not t.is_cuda or t.dim() != 3:
+        raise RuntimeError('b must be a 3-D CUDA tensor')
+    if t.dtype not in (torch.float8_e4m3fn, kPackedFP4):
+        raise RuntimeError('b must be float8_e4m3fn or packed FP4 (int8)')
+    fp4 = t.dtype == kPackedFP4
+    if t.is_contiguous():
+        return t.size(0), t.size(1), t.size(2) * (2 if fp4 else 1), False
+    if t.transpose(1, 2).is_contiguous():
+        return t.size(0), t.size(1) * (2 if fp4 else 1), t.size(2), True
+    raise RuntimeError('b must be K-major and contiguous, or the transposed view of a contiguous [G, K, N] tensor')
+
+
 def _prepare_accumulator(c, d):
     """The reference's accumulator input (csrc/apis/gemm.hpp:73-124, :404-438; its tests pass c with a float32 d):
     d = c + a @ b.T. The kernel adds into d, so c is first copied there unless it is d itself. Returns the flag."""
@@ -96,9 +113,11 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b
     if a_q.dtype != torch.float8_e4m3fn:
         raise RuntimeError('a must be float8_e4m3fn')
     m, k = _check_ab(a_q, 2, 'a')
-    num_groups, n, k_ = _check_ab(b_q, 3, 'b')
+    num_groups, n, k_, b_mn_major = _check_grouped_b(b_q)
     if k != k_:
         raise RuntimeError(f'K mismatch: a has {k}, b has {k_}')
+    if b_mn_major and n % 32 != 0:
+        raise RuntimeError('an MN-major b needs N to be a multiple of 32')
     _check_d(d, (m, n))
     if d.stride(0) * 2 % 16 != 0:
         raise RuntimeError('d rows must be 16-byte aligned')
@@ -117,8 +136,10 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b
     sfa, sfb, gran_a, gran_b = transform_sf_pair_into_required_layout(
         a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, num_groups, disable_ue8m0_cast,
         grouped_layout if use_psum_layout else None)
+    entry = _lib.lib().dgb200_m_grouped_fp8_fp4_gemm_nn_contiguous if b_mn_major else \
+        _lib.lib().dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous
     with torch.cuda.device(d.device):
-        _lib.check(_lib.lib().dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
+        _lib.check(entry(
             _p(a_q), _p(sfa), sfa.stride(-1), _p(b_q), _p(sfb), sfb.stride(-1), sfb.stride(0),
             _p(d), d.stride(0), _p(grouped_layout), m, n, k, num_groups, gran_a, gran_b,
             int(b_q.dtype == kPackedFP4), 0, 1 if use_psum_layout else 0,
@@ -129,8 +150,8 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b
 def m_grouped_fp8_fp4_gemm_nn_contiguous(a, b, d, grouped_layout, recipe=None, recipe_a=None, recipe_b=None,
                                          compiled_dims: str = 'nk', disable_ue8m0_cast: bool = False,
                                          use_psum_layout: bool = False, ensure_zero_padding: bool = True) -> None:
-    """B given as [G, K, N]; reference: csrc/apis/gemm.hpp:234-248 (transposes the views and calls the NT form).
-    Weights must therefore already be stored K-major underneath, as this kernel only reads K-major B."""
+    """B given as [G, K, N] (packed FP4: [G, K, N / 2]); reference: csrc/apis/gemm.hpp:234-248 (transposes the views and
+    calls the NT form, which reads a contiguous [G, K, N] tensor as an MN-major operand)."""
     m_grouped_fp8_fp4_gemm_nt_contiguous(a, (b[0].transpose(1, 2), b[1].transpose(1, 2)), d, grouped_layout, recipe,
                                          recipe_a, recipe_b, compiled_dims, disable_ue8m0_cast, use_psum_layout,
                                          ensure_zero_padding, None)

@@ -37,7 +37,7 @@ _MMA_TYPES = ('fp8xfp4', 'nvfp4xnvfp4', 'bf16xbf16')
 
 def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
                    mma_type='fp8xfp4', shared_intermediate_hidden=0):
-    words = (ctypes.c_int64 * 20)()
+    words = (ctypes.c_int64 * 21)()
     if mma_type == 'fp8xfp4':
         _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe_ex(
             num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
@@ -52,7 +52,7 @@ def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hi
             ctypes.cast(words, ctypes.c_void_p)))
     keys = ['total', 'x', 'x_sf', 'topk_idx', 'topk_weights', 'l1_acts', 'l1_sf', 'l2_acts', 'l2_sf', 'max_rows',
             'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'l2_out', 'row_weight',
-            'shared_x_sf', 'shared_l2_acts', 'shared_l2_sf', 'shared_out']
+            'shared_x_sf', 'shared_l2_acts', 'shared_l2_sf', 'shared_out', 'flags']
     return dict(zip(keys, list(words)))
 
 

@@ -1,7 +1,8 @@
 """Process-global knobs with the reference's names (csrc/apis/runtime.hpp:12-48, csrc/apis/layout.hpp:142-150).
 
 Kernels here are compiled ahead of time, so knobs that only steer the reference's JIT (compiled dims, block-size
-multiples) are accepted and ignored."""
+multiples) are accepted and ignored; knobs that would change how a kernel runs and are not built (PDL, tensor-core
+throttling) raise when set to anything but their default."""
 from . import _lib
 
 _state = {'tc_util': 100, 'pdl': False, 'mk_alignment': 128}
@@ -16,8 +17,12 @@ def get_num_sms() -> int:
 
 
 def set_tc_util(tc_util: int) -> None:
+    """The reference throttles its MMA issue loop to ``tc_util`` percent (csrc/apis/runtime.hpp:21-27). The kernels
+    here always issue at full rate: 100 is accepted, any other value is refused rather than silently ignored."""
     if not 0 <= tc_util <= 100:
         raise RuntimeError('tc_util must be in [0, 100]')
+    if tc_util != 100:
+        raise RuntimeError('tensor-core throttling is not built into these kernels: tc_util must stay 100')
     _state['tc_util'] = int(tc_util)
 
 
@@ -26,7 +31,11 @@ def get_tc_util() -> int:
 
 
 def set_pdl(enabled: bool) -> None:
-    _state['pdl'] = bool(enabled)
+    """Programmatic dependent launch (csrc/apis/runtime.hpp:24-28) is not built into these kernels: switching it on is
+    refused rather than silently ignored; ``set_pdl(False)`` is accepted."""
+    if enabled:
+        raise RuntimeError('programmatic dependent launch is not built into these kernels: set_pdl(True) is refused')
+    _state['pdl'] = False
 
 
 def get_pdl() -> bool:

@@ -45,15 +45,9 @@ int dgb200_get_num_sms(void);
  *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
  *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
  *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
- *   "prefetch_distance"  K blocks an L2 prefetch cursor runs ahead of the weight loads (0 = off, the default).
- *   "debug_skip"         timing experiments, only honoured by builds with -DDGB200_INSTRUMENT. */
+ *   "peer_wait_us"       expert-parallel layer: how long a rank waits for a flag another rank writes before it gives
+ *                        up, records DGB200 status code 7 (peer timeout) and carries on (default 10 s; at least 1). */
 int dgb200_set_tuning(const char* name, int32_t value);
-
-/* Debugging aid, only honoured by builds with -DDGB200_INSTRUMENT: while set, CTA 0 of every GEMM launch records
- * clock64() per trace point and K block (or tile) into device_buffer, int64 [16][capacity_per_role]. Points: 0/1 and
- * 9/10 loaders before/after issue, 2/3 scale-factor transposer, 4/5 (8, 11..15: finer steps) MMA issuer, 6/7
- * epilogue per tile. NULL switches it off. No reference counterpart. */
-int dgb200_debug_set_trace(void* device_buffer, int32_t capacity_per_role);
 
 /* Synchronises `stream`, copies the 8-word device status block to `out_words` (may be NULL) and clears it.
  * Returns DGB200_EDEVICE when word 0 is non-zero. Words: {code, block, detail a, detail b, 0, 0, 0, 0}.
@@ -76,6 +70,19 @@ int dgb200_device_status(int32_t* out_words, void* stream);
  *                  (ensure_zero_padding=True, csrc/apis/gemm.hpp:166).
  * Requires k % 128 == 0, n % 128 == 0. */
 int dgb200_m_grouped_fp8_fp4_gemm_nt_contiguous(
+    const void* a, const void* sfa, int64_t sfa_k_stride,
+    const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
+    void* d, int64_t d_row_stride, const int32_t* grouped_layout,
+    int32_t m, int32_t n, int32_t k, int32_t num_groups,
+    int32_t gran_k_a, int32_t gran_k_b, int32_t b_is_fp4, int32_t d_is_fp32,
+    int32_t layout_kind, int32_t alignment, int32_t store_padding, void* stream);
+
+/* The same GEMM with an MN-major b, the operand of the reference's m_grouped_fp8_fp4_gemm_nn_contiguous
+ * (csrc/apis/gemm.hpp:234-248; on SM100 the NT form accepts an MN-major b as well, :181-183):
+ *   b  b_is_fp4 ? packed e2m1 [num_groups, k, n / 2] (even n index in the low nibble) : e4m3 [num_groups, k, n],
+ *      rows dense. Read through MN-major shared-memory descriptors; n must be a multiple of 32.
+ * Every other argument as above (sfb stays int (g, kp, ch) at sfb[g*sfb_group_stride + kp*sfb_k_stride + ch]). */
+int dgb200_m_grouped_fp8_fp4_gemm_nn_contiguous(
     const void* a, const void* sfa, int64_t sfa_k_stride,
     const void* b, const void* sfb, int64_t sfb_k_stride, int64_t sfb_group_stride,
     void* d, int64_t d_row_stride, const int32_t* grouped_layout,
@@ -297,8 +304,12 @@ typedef struct dgb200_mega_moe_args {
 } dgb200_mega_moe_args;
 int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* args, void* stream);
 
-/* dgb200_get_symm_buffer_layout_for_mega_moe with room for shared experts: out[20] = the 16 words above, then the byte
- * offsets of the shared experts' private regions (x scales in GEMM order, activations, their scales, output rows). */
+/* dgb200_get_symm_buffer_layout_for_mega_moe with room for shared experts: out[21] = the 16 words above, then the byte
+ * offsets of the shared experts' private regions (x scales in GEMM order, activations, their scales, output rows) and,
+ * last, of the cross-rank barrier words (int32 [4][8]: rows 0..2 = per barrier, the epoch each rank last signalled;
+ * row 3 = this rank's own epoch counters). The whole buffer must be zeroed once after it is allocated, on every rank
+ * and before any rank's first call (the barrier words are never reset afterwards; everything else is rewritten by
+ * each call before it is read). */
 int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
                                                   int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                                                   int32_t shared_intermediate_hidden, int64_t* out);
@@ -309,7 +320,7 @@ int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num
  * the gate/up GEMM's epilogue writes silu(gate) * up * topk_weight as BF16. hidden and inter must be multiples of 128.
  * Shared experts (shared_intermediate_hidden > 0): shared_l1_w bf16 [2 * shared_inter, hidden] (interleaved likewise),
  * shared_l2_w bf16 [hidden, shared_inter], a dense MLP over this rank's tokens with routing weight 1 whose rows are one
- * more combine slot; the token capacity must then be a multiple of 128. out[20] as in
+ * more combine slot; the token capacity must then be a multiple of 128. out[21] as in
  * dgb200_get_symm_buffer_layout_for_mega_moe_ex.
  * Reference: bf16_mega_moe, csrc/apis/mega.hpp:288-400 and deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:52. */
 int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,

@@ -37,6 +37,18 @@ def u8(t):
     return t.contiguous().view(torch.uint8).numpy()
 
 
+def load_functions(path, names):
+    """Executes only the named top-level functions of a Python source file (with torch in scope) and returns them."""
+    import ast
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    picked = [node for node in tree.body if isinstance(node, ast.FunctionDef) and node.name in names]
+    assert len(picked) == len(names), f'{path} no longer defines {names}'
+    scope = {'torch': torch}
+    exec(compile(ast.Module(body=picked, type_ignores=[]), path, 'exec'), scope)
+    return {name: scope[name] for name in names}
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get('DEEPGEMM_REFERENCE_ROOT')
     if not ref_root:
@@ -101,14 +113,19 @@ def main():
         lay[f'{tag}_sf'] = sf.view(g, mn, sf_k).numpy()
         lay[f'{tag}_packed'] = ints.numpy()                      # logical [g, mn, packed_k]
         lay[f'{tag}_strides'] = np.array([ints.shape[2] * rmath.align(mn, 4), 1, rmath.align(mn, 4)], dtype=np.int64)
-    # gate/up interleave of the reference's weight transform (granularity 8: deep_gemm/mega/__init__.py:97-111),
-    # written out as an explicit row map: output row r takes gate row 8*(r//16) + r%16 when r%16 < 8,
-    # else up row half + 8*(r//16) + r%16 - 8
-    t = torch.arange(2 * 64 * 3, dtype=torch.int32).view(2, 64, 3)
-    rows = torch.arange(64)
-    src = torch.where(rows % 16 < 8, 8 * (rows // 16) + rows % 16, 32 + 8 * (rows // 16) + rows % 16 - 8)
+    # gate/up interleave and tcgen05.cp ("UTCCP") row order of the reference's weight transform: the two function
+    # bodies are lifted out of deep_gemm/mega/__init__.py (:97-128) with ast and executed here, because importing that
+    # module needs the compiled _C extension; what is stored is therefore the reference's own output
+    mega_fns = load_functions(os.path.join(ref_root, 'deep_gemm', 'mega', '__init__.py'),
+                              ('_interleave_weights', '_transpose_sf_for_utccp'))
+    t = torch.arange(2 * 512 * 3, dtype=torch.int32).view(2, 512, 3)
     lay['interleave_in'] = t.numpy()
-    lay['interleave_g8'] = t[:, src].contiguous().numpy()
+    for gran in (8, 16, 128):
+        lay[f'interleave_g{gran}'] = mega_fns['_interleave_weights'](t, gran).numpy()
+    lay['interleave_2d_g8'] = mega_fns['_interleave_weights'](t[0], 8).numpy()
+    sf_in = torch.arange(2 * 384 * 5, dtype=torch.int32).view(2, 384, 5)
+    lay['utccp_in'] = sf_in.numpy()
+    lay['utccp_out'] = mega_fns['_transpose_sf_for_utccp'](sf_in).numpy()
     np.savez_compressed(os.path.join(HERE, 'layout.npz'), **lay)
     print('wrote quant.npz, layout.npz')
     make_kgrouped(rmath)

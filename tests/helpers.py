@@ -83,3 +83,50 @@ def moe_case_nvfp4(tokens, hidden, inter, experts, topk, seed, masked_ratio=0.0,
         w = w.masked_fill(mask, 0.0)
     return dict(x=x, x_q=x_q, x_sf=x_sf, x_scale=x_scale, l1_q=stack(l1, 0), l1_sf=stack(l1, 1), l1_scales=stack(l1, 2),
                 l2_q=stack(l2, 0), l2_sf=stack(l2, 1), l2_scales=stack(l2, 2), topk_idx=idx, topk_weights=w)
+
+
+def pick_sampled_tokens(topk_idx: torch.Tensor, num: int, seed: int):
+    """Tokens for the value checks of the full-size layers: a quarter each routed to some expert that received at most
+    128 rows, 129..160 rows and more than 160 rows (the sizes at which the layer's GEMMs change their tiling), where such
+    experts exist, the rest drawn uniformly. Returns a sorted list of distinct token indices."""
+    g = torch.Generator().manual_seed(seed)
+    flat = topk_idx.reshape(-1)
+    counts = torch.bincount(flat[flat >= 0])
+    rows_of = torch.where(topk_idx >= 0, counts[topk_idx.clamp(min=0)], torch.zeros((), dtype=counts.dtype))
+    chosen = set()
+    for lo, hi in ((1, 128), (129, 160), (161, 1 << 30)):
+        hits = torch.nonzero(((rows_of >= lo) & (rows_of <= hi)).any(dim=1)).reshape(-1)
+        if hits.numel():
+            chosen.update(hits[torch.randperm(hits.numel(), generator=g)[:num // 4]].tolist())
+    while len(chosen) < num:
+        chosen.add(int(torch.randint(0, topk_idx.shape[0], (1,), generator=g)))
+    return sorted(chosen)
+
+
+def oracle_rows_of_sampled_tokens(tokens, topk_idx, topk_weights, x_rows, l1_weight, l2_weight, requant, hidden):
+    """y of the sampled tokens from the oracle's arithmetic, each expert's weights dequantised once:
+    x_rows(token list) -> fp32 [n, H]; l1_weight(e) / l2_weight(e) -> fp32 [2I, H] / [H, I];
+    requant(acc1, weights) -> fp32 [n, I] (the dequantised post-SwiGLU activations). The slots of a token are summed
+    in ascending order in fp32 from their bf16 rows, as the layer's combine does. Returns {token: bf16 [H]}."""
+    by_expert = {}
+    for t in tokens:
+        for k in range(topk_idx.shape[1]):
+            e = int(topk_idx[t, k])
+            if e >= 0:
+                by_expert.setdefault(e, []).append((t, k))
+    rows = {}
+    for e, pairs in by_expert.items():
+        toks = [t for t, _ in pairs]
+        w = torch.stack([topk_weights[t, k] for t, k in pairs])
+        acc1 = x_rows(toks) @ l1_weight(e).T
+        acc2 = requant(acc1, w) @ l2_weight(e).T
+        for i, pair in enumerate(pairs):
+            rows[pair] = acc2[i].bfloat16().float()
+    out = {}
+    for t in tokens:
+        acc = torch.zeros(hidden)
+        for k in range(topk_idx.shape[1]):
+            if (t, k) in rows:
+                acc += rows[(t, k)]
+        out[t] = acc.bfloat16()
+    return out

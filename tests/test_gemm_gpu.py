@@ -229,3 +229,40 @@ def test_dense_gemm(dg, m, n, k, b_fp4, out):
     else:
         with pytest.raises(RuntimeError):
             dg.fp8_fp4_gemm_nt(*args, d, c=d, **recipes)  # accumulation needs float32
+
+
+def _transpose_packed_fp4(q):
+    """[N, K / 2] packed along K -> [K, N / 2] packed along N (even N index in the low nibble), the storage of an
+    MN-major FP4 operand (the reference's test helper of the same purpose: deep_gemm/utils/math.py:125-138)."""
+    n = q.shape[0]
+    codes = torch.stack([q & 0x0F, (q >> 4) & 0x0F], dim=2).reshape(n, -1)  # [N, K] one code per element
+    t = codes.t().contiguous().view(-1, n // 2, 2)
+    return ((t[:, :, 0] & 0x0F) | ((t[:, :, 1] & 0x0F) << 4)).to(torch.int8).contiguous()
+
+
+@pytest.mark.parametrize('b_fp4', [False, True])
+@pytest.mark.parametrize('via_nn', [False, True])
+def test_mn_major_b(dg, b_fp4, via_nn):
+    """b stored [G, K, N] (N contiguous; packed FP4: [G, K, N / 2]): the operand of m_grouped_fp8_fp4_gemm_nn_contiguous,
+    which the NT form also accepts as a transposed view (reference: csrc/apis/gemm.hpp:181-183, :234-248). Same numbers
+    as the K-major storage of the same weights."""
+    gran_b = 32 if b_fp4 else 128
+    c = contiguous_case(3, 384, 512, 50, 260, seed=17, gran_b=gran_b, b_fp4=b_fp4)
+    want, mask = ogemm.grouped_gemm_contiguous(c['a_q'], c['a_sf'], c['b_q'], c['b_sf'], c['row_ids'], 128, gran_b)
+    if b_fp4:
+        storage = torch.stack([_transpose_packed_fp4(c['b_q'][g]) for g in range(3)]).cuda()  # [G, K, N / 2]
+    else:
+        storage = c['b_q'].transpose(1, 2).contiguous().cuda()                                 # [G, K, N]
+    sf = _cuda_packed(c['b_sf'])
+    d = torch.full((c['m'], 384), float('nan'), dtype=torch.bfloat16, device='cuda')
+    a = (c['a_q'].cuda(), _cuda_packed(c['a_sf']))
+    if via_nn:
+        dg.m_grouped_fp8_fp4_gemm_nn_contiguous(a, (storage, sf.transpose(1, 2)), d, c['row_ids'].cuda(),
+                                                recipe_a=(1, 128), recipe_b=(1, gran_b))
+    else:
+        dg.m_grouped_fp8_fp4_gemm_nt_contiguous(a, (storage.transpose(1, 2), sf), d, c['row_ids'].cuda(),
+                                                recipe_a=(1, 128), recipe_b=(1, gran_b))
+    _finish(dg)
+    got = d.cpu()
+    assert not torch.isnan(got[mask].float()).any()
+    assert quant.calc_diff(got[mask], want[mask]) <= (FP4_TOL if b_fp4 else FP8_TOL)

@@ -180,3 +180,29 @@ def test_k_grouped_recipe_32(dg, ks, m, n):
             assert torch.equal(got[g], c[g])
         else:
             assert quant.calc_diff(got[g] - c[g], want[g] - c[g]) <= FP8_TOL
+
+
+def test_k_grouped_rejects_extents_that_disagree_with_the_host_list(dg):
+    """Plain layout: the kernel only sees the device-side extents. Extents that are not whole K blocks (or that overrun
+    the operands) are reported through the status block and their groups left untouched (d keeps c); nothing reads the
+    neighbouring group's rows."""
+    from deepgemm_b200 import _lib
+    torch.manual_seed(5)
+    ks_host = [128, 128]
+    m, n = 128, 128
+    a, b = torch.randn(sum(ks_host), m).bfloat16().cuda(), torch.randn(sum(ks_host), n).bfloat16().cuda()
+    c = torch.randn(2, m, n)
+    d = c.cuda()
+    lying = torch.tensor([96, 160], dtype=torch.int32, device='cuda')  # same sum, neither a multiple of 64
+    dg.k_grouped_bf16_gemm_tn_contiguous(a, b, d, ks_host, lying, c=d)
+    status = _lib.device_status(raise_on_error=False)
+    assert status[0] == 6, status  # bad argument
+    assert _lib.device_status()[0] == 0  # reading the status block clears it
+    assert torch.equal(d.cpu(), c)
+    overrun = torch.tensor([128, 256], dtype=torch.int32, device='cuda')  # the second group runs past the operands
+    dg.k_grouped_bf16_gemm_tn_contiguous(a, b, d, ks_host, overrun, c=d)
+    status = _lib.device_status(raise_on_error=False)
+    assert status[0] == 6 and status[2] == 1, status
+    got = d.cpu()
+    assert torch.equal(got[1], c[1])
+    assert quant.calc_diff(got[0] - c[0], a[:128].float().T.cpu() @ b[:128].float().cpu()) < 1e-5

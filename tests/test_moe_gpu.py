@@ -6,7 +6,7 @@ import torch
 from oracle import layout as olay
 from oracle import moe as omoe
 from oracle import quant
-from tests.helpers import moe_case
+from tests.helpers import moe_case, oracle_rows_of_sampled_tokens, pick_sampled_tokens
 
 pytestmark = pytest.mark.gpu
 FP4_TOL = 2e-3
@@ -139,18 +139,25 @@ def test_full_config_permutation_and_sampled_tokens(dg):
     assert torch.equal(dest, want_dest) and torch.equal(end, want_end)
     assert not torch.isnan(y.float()).any()
 
-    sample = [0, 1777, 4095]
+    # values: 64 tokens, among them tokens of experts with at most 128, 129..160 and more than 160 rows
     w = buf.topk_weights.cpu()
     x_q_c, x_sf_c = x_q.cpu(), quant.unpack_ue8m0(x_sf.cpu())
+    sample = sorted(set(pick_sampled_tokens(idx, 64, seed=3) + [0, 4095]))
+    sizes = (want_end - want_start)
+    hit = sizes[idx[sample].reshape(-1)]
+    assert (hit <= 128).any() and (hit > 128).any()
+
+    def requant(acc1, weights):
+        a2_q, a2_sf = omoe.swiglu_requant(acc1, weights, None)
+        return quant.dequantize_fp8(a2_q, a2_sf, 32)
+
+    want_rows = oracle_rows_of_sampled_tokens(
+        sample, idx, w, lambda toks: quant.dequantize_fp8(x_q_c[toks], x_sf_c[toks], 32),
+        lambda e: quant.dequantize_fp4(l1_q[e].cpu(), l1_sf[e].cpu(), 32),
+        lambda e: quant.dequantize_fp4(l2_q[e].cpu(), l2_sf[e].cpu(), 32), requant, hidden)
+    y_c = y.cpu()
     for t in sample:
-        acc = torch.zeros(hidden)
-        for k in range(topk):
-            e = int(idx[t, k])
-            a1 = quant.dequantize_fp8(x_q_c[t:t + 1], x_sf_c[t:t + 1], 32) @ quant.dequantize_fp4(l1_q[e].cpu(), l1_sf[e].cpu(), 32).T
-            a2_q, a2_sf = omoe.swiglu_requant(a1, w[t:t + 1, k], None)
-            a2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(l2_q[e].cpu(), l2_sf[e].cpu(), 32).T
-            acc += a2.bfloat16().float()[0]
-        assert quant.calc_diff(y[t].cpu(), acc.bfloat16()) <= FP4_TOL
+        assert quant.calc_diff(y_c[t], want_rows[t]) <= FP4_TOL, t
 
 
 @pytest.mark.parametrize('tokens,hidden,inter,experts,topk,use_logits', [
@@ -269,3 +276,53 @@ def test_down_gemm_split_by_group_size(dg):
     want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
     got, _ = _run_layer(dg, c, tokens, hidden, inter, experts, topk)
     assert quant.calc_diff(got, want) <= FP4_TOL
+
+
+def test_peer_wait_runs_out_and_the_library_stays_usable(dg):
+    """Failure detection of the expert-parallel barrier, on one GPU and without faulting it: the layer is called as rank 0
+    of 2 with both entries of the peer table pointing at this process's own buffer, so the flag "rank 1" should write
+    never changes. With a 2 ms budget every barrier gives up, records the peer-timeout status (code 7, detail = the rank
+    that did not answer) and the call returns; reading the status clears it. All tokens are routed to experts of rank 0,
+    so the output is still the oracle's. After the test writes the missing flags itself the same call passes cleanly."""
+    import ctypes
+    from deepgemm_b200 import _lib, mega
+    tokens, hidden, inter, experts, topk = 96, 512, 256, 8, 2
+    local = experts // 2
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=31, empty_experts=tuple(range(local, experts)))
+    assert int(c['topk_idx'].max()) < local
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+    lay = mega._buffer_layout(2, experts, 128, topk, hidden, inter)
+    raw = torch.zeros(lay['total'], dtype=torch.int8, device='cuda')
+    view = lambda key, nbytes, dtype: raw[lay[key]:lay[key] + nbytes].view(dtype)
+    view('x', tokens * hidden, torch.float8_e4m3fn).view(tokens, hidden).copy_(c['x_q'].cuda())
+    view('x_sf', tokens * (hidden // 128) * 4, torch.int32).view(tokens, hidden // 128).copy_(quant.pack_ue8m0(c['x_sf']).cuda())
+    view('topk_idx', tokens * topk * 8, torch.int64).view(tokens, topk).copy_(c['topk_idx'].cuda())
+    view('topk_weights', tokens * topk * 4, torch.float32).view(tokens, topk).copy_(c['topk_weights'].cuda())
+    mine = {k: c[k][:local] for k in ('l1_q', 'l1_sf', 'l2_q', 'l2_sf')}
+    l1, l2 = _device_weights(dg, mine)
+    ptrs = (ctypes.c_uint64 * 2)(raw.data_ptr(), raw.data_ptr())
+    lib = _lib.lib()
+
+    def call():
+        y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+        _lib.check(lib.dgb200_fp8_fp4_mega_moe(
+            y.data_ptr(), l1[0].data_ptr(), l1[1].data_ptr(), l2[0].data_ptr(), l2[1].data_ptr(), None, raw.data_ptr(),
+            ctypes.cast(ptrs, ctypes.c_void_p), 0, 2, tokens, 128, experts, topk, hidden, inter, 0.0, 1, _lib.current_stream_ptr()))
+        return y
+
+    _lib.check(lib.dgb200_set_tuning(b'peer_wait_us', 2000))
+    try:
+        y = call()
+        status = _lib.device_status(raise_on_error=False)
+        assert status[0] == 7 and status[2] == 1, status  # peer timeout, waiting for rank 1
+        assert _lib.device_status()[0] == 0, 'reading the status block clears it'
+        assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
+        # play the missing rank: its flags, far ahead of any epoch this test reaches
+        flags = view('flags', 4 * 8 * 4, torch.int32).view(4, 8)
+        flags[:3, 1] = 1 << 20
+        torch.cuda.synchronize()
+        y = call()
+        assert _lib.device_status()[0] == 0
+        assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
+    finally:
+        _lib.check(lib.dgb200_set_tuning(b'peer_wait_us', 10_000_000))

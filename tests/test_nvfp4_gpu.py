@@ -10,7 +10,7 @@ import torch
 from oracle import moe as omoe
 from oracle import nvfp4 as onv
 from oracle import quant
-from tests.helpers import moe_case_nvfp4
+from tests.helpers import moe_case_nvfp4, oracle_rows_of_sampled_tokens, pick_sampled_tokens
 
 pytestmark = pytest.mark.gpu
 FP4_TOL = 2e-3
@@ -253,12 +253,16 @@ def test_full_prefill_config_permutation_and_sampled_tokens(dg):
     x_q_c = buf.x.cpu()
     x_sf_c = buf.x_sf.cpu().view(torch.uint8).view(torch.float8_e4m3fn).view(tokens, hidden // 16)
     xs, acs = x_scale.cpu(), act_scale.cpu()
-    for t in (0, 9001, 16383):
-        acc = torch.zeros(hidden)
-        for k in range(topk):
-            e = int(idx[t, k])
-            a1 = onv.dequantize_nvfp4(x_q_c[t:t + 1], x_sf_c[t:t + 1], xs) @ onv.dequantize_nvfp4(l1_q[e].cpu(), l1_sf[e].cpu(), l1_s[e].cpu()).T
-            a2_q, a2_sf = onv.swiglu_requant_nvfp4(a1, w[t:t + 1, k], None, acs)
-            a2 = onv.dequantize_nvfp4(a2_q, a2_sf, acs) @ onv.dequantize_nvfp4(l2_q[e].cpu(), l2_sf[e].cpu(), l2_s[e].cpu()).T
-            acc += a2.bfloat16().float()[0]
-        assert quant.calc_diff(y[t].cpu(), acc.bfloat16()) <= FP4_TOL
+    sample = sorted(set(pick_sampled_tokens(idx, 64, seed=4) + [0, 16383]))
+
+    def requant(acc1, weights):
+        a2_q, a2_sf = onv.swiglu_requant_nvfp4(acc1, weights, None, acs)
+        return onv.dequantize_nvfp4(a2_q, a2_sf, acs)
+
+    want_rows = oracle_rows_of_sampled_tokens(
+        sample, idx, w, lambda toks: onv.dequantize_nvfp4(x_q_c[toks], x_sf_c[toks], xs),
+        lambda e: onv.dequantize_nvfp4(l1_q[e].cpu(), l1_sf[e].cpu(), l1_s[e].cpu()),
+        lambda e: onv.dequantize_nvfp4(l2_q[e].cpu(), l2_sf[e].cpu(), l2_s[e].cpu()), requant, hidden)
+    y_c = y.cpu()
+    for t in sample:
+        assert quant.calc_diff(y_c[t], want_rows[t]) <= FP4_TOL, t

@@ -74,12 +74,17 @@ def test_packed_sf_layout_matches_reference(gl, tag):
 
 
 def test_gate_up_interleave_matches_reference(gl):
+    """The fixtures are outputs of the reference's own _interleave_weights / _transpose_sf_for_utccp
+    (deep_gemm/mega/__init__.py:97-128): the oracle's and the package's row maps must reproduce them bit for bit."""
+    from deepgemm_b200 import mega
     t = torch.from_numpy(gl['interleave_in'].copy())
-    assert np.array_equal(olay.interleave_gate_up(t, 8).numpy(), gl['interleave_g8'])
-    # granularity 32 (the one the CUDA L1 epilogue consumes) obeys the same row map
-    u = torch.arange(128 * 2).view(128, 2)
-    v = olay.interleave_gate_up(u, 32)
-    assert torch.equal(v[:32], u[:32]) and torch.equal(v[32:64], u[64:96]) and torch.equal(v[64:96], u[32:64])
+    for gran in (8, 16, 128):
+        want = gl[f'interleave_g{gran}']
+        assert np.array_equal(olay.interleave_gate_up(t, gran).numpy(), want)
+        assert np.array_equal(mega._interleave_rows(t, gran).numpy(), want)
+    assert np.array_equal(olay.interleave_gate_up(t[0], 8).numpy(), gl['interleave_2d_g8'])
+    sf = torch.from_numpy(gl['utccp_in'].copy())
+    assert np.array_equal(mega._sf_rows_to_cp_order(sf).numpy(), gl['utccp_out'])
 
 
 def test_k_grouped_quantiser_and_product_match_reference(golden_dir):

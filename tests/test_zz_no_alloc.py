@@ -32,12 +32,13 @@ def _plan_from_layer(dg, case, tokens, hidden, inter, experts, topk):
     return take('dest_row', tokens * topk), take('expert_start', experts), take('expert_end', experts)
 
 
-def _plan_noalloc(topk_idx, experts, alignment):
+def _plan_noalloc(topk_idx, experts, alignment, tokens=None):
     from deepgemm_b200 import _lib
     lib = _lib.lib()
-    tokens, topk = topk_idx.shape
+    topk = topk_idx.shape[1]
+    tokens = topk_idx.shape[0] if tokens is None else tokens  # fewer than the tensor holds: only the first rows are read
     idx = topk_idx.cuda().contiguous()
-    dest = torch.full((tokens * topk,), -7, dtype=torch.int32, device='cuda')
+    dest = torch.full((max(tokens * topk, 1),), -7, dtype=torch.int32, device='cuda')
     start = torch.full((experts,), -7, dtype=torch.int32, device='cuda')
     end = torch.full((experts,), -7, dtype=torch.int32, device='cuda')
     p = lambda t: ctypes.c_void_p(t.data_ptr())
@@ -67,3 +68,19 @@ def test_noalloc_plan_rejects_oversized_problems():
     assert 'exceeds the built-in scratch' in lib.dgb200_last_error().decode()
     assert lib.dgb200_moe_dispatch_plan_noalloc(one, 16, 2, 513, 16, one, one, one, None) == 1
     assert 'exceeds the built-in scratch' in lib.dgb200_last_error().decode()
+
+
+def test_noalloc_plan_at_the_documented_limit_and_with_no_tokens():
+    """Exactly 65536 entries over 512 experts fill the built-in scratch to its last word (64 chunks x 512 counters) and
+    need the assign kernel's largest shared-memory footprint; checked against a stable argsort on the host. A call with
+    no tokens must leave every expert's segment empty."""
+    from oracle import moe as omoe
+    tokens, topk, experts, alignment = 8192, 8, 512, 16
+    g = torch.Generator().manual_seed(77)
+    idx = torch.stack([torch.randperm(experts, generator=g)[:topk] for _ in range(tokens)])
+    idx = idx.masked_fill(torch.rand(idx.shape, generator=g) < 0.1, -1)
+    dest, start, end = _plan_noalloc(idx, experts, alignment)
+    want_dest, _, want_start, want_end = omoe.dispatch_plan(idx, experts, alignment)
+    assert torch.equal(dest.cpu(), want_dest) and torch.equal(start.cpu(), want_start) and torch.equal(end.cpu(), want_end)
+    _, start, end = _plan_noalloc(idx[:1], experts, alignment, tokens=0)
+    assert torch.equal(start, end) and int(end.max()) == 0
