@@ -52,6 +52,8 @@ _SIGNATURES = {
                                                 _i32, _ptr, _ptr],
     'dgb200_fp8_fp4_gemm_nt': [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_segment_alignment_for_mega_moe': [],
+    'dgb200_get_gate_up_interleave_for_mega_moe': [],
+    'dgb200_get_weight_tile_rows_for_mega_moe': [],
     'dgb200_get_symm_buffer_layout_for_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_fp8_fp4_mega_moe_bf16_input': [

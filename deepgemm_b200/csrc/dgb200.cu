@@ -10,6 +10,7 @@
 #include "host_common.cuh"
 #include "gemm_kernel.cuh"
 #include "gemm_swap_kernel.cuh"
+#include "expert_mlp_kernel.cuh"
 #include "quant_kernels.cuh"
 #include "moe_kernels.cuh"
 
@@ -63,6 +64,9 @@ struct GemmCall {
 struct Tuning {
     int swap_ab = -1;  // layer GEMMs: tokens on the UMMA N side (-1 = by expected rows per expert, 0 = never, 1 = always)
     int block_n = 0;  // 0 = automatic
+    int mlp_kernel = -1;  // FP8 x FP4 layer GEMMs: 0 = separate gate/up and down kernels (tokens-on-M / swapped split),
+                          // 1 = the fused expert-MLP kernel on single CTAs, 2 = on CTA pairs; -1 = not yet read from
+                          // the environment (DGB200_MLP_KERNEL, default below)
     long long peer_wait_cycles = 20000000000ll;  // budget of a wait for another rank, SM clock cycles (about 10 s: ranks
                                                  // may reach their first call seconds apart)
 };
@@ -70,6 +74,20 @@ struct Tuning {
 Tuning& tuning() {
     static Tuning t;
     return t;
+}
+
+constexpr int kDefaultMlpKernel = 0;
+
+// Which kernels run the FP8 x FP4 layer's GEMMs. Fixed at first use for the life of the process, because the weights'
+// gate/up interleave (transform_weights_for_mega_moe) depends on it: 16 rows for the fused kernel, 128 otherwise.
+int mlp_kernel_choice() {
+    Tuning& t = tuning();
+    if (t.mlp_kernel < 0) {
+        const char* env = std::getenv("DGB200_MLP_KERNEL");
+        t.mlp_kernel = env != nullptr ? std::atoi(env) : kDefaultMlpKernel;
+        if (t.mlp_kernel < 0 || t.mlp_kernel > 2) t.mlp_kernel = kDefaultMlpKernel;
+    }
+    return t.mlp_kernel;
 }
 
 int run_gemm(GemmCall& c, cudaStream_t stream) {
@@ -385,6 +403,7 @@ struct MegaLayout {
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
     long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
+    long long tile_done;  // FP8 kind: one counter per token tile of the fused expert-MLP kernel (max_rows / 128 + local experts)
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
     long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
     long long token_rows;
@@ -458,6 +477,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l2_sf = take(l.max_rows * sf_ints_per_row(kind, inter) * 4);
     l.l2_out = take(l.max_rows * hidden * 2);
     l.l1_tmp = kind == kKindFp8Fp4 ? take(l.max_rows * inter * 4) : 0;
+    l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_local_experts) * 4) : 0;
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
@@ -508,6 +528,81 @@ int run_cast(bool fp4, const void* x, long long x_row_stride, int rows, int k, i
 }
 
 
+// Both GEMMs of the FP8 x MXFP4 layer in one launch of the fused expert-MLP kernel (expert_mlp_kernel.cuh).
+int run_expert_mlp(bool pair, const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
+                   const void* l2_w_sf, int hidden, int inter, float activation_clamp, int fast_math, cudaStream_t stream) {
+    const int E = l.num_local_experts;
+    const int ctas = pair ? 2 : 1;
+    DGB_REQUIRE(E <= kMlpMaxExperts, "the fused expert-MLP kernel holds the tables of at most %d experts per rank", kMlpMaxExperts);
+    DGB_REQUIRE((2 * inter) % (128 * ctas) == 0 && hidden % (128 * ctas) == 0 && hidden % 128 == 0 && inter % 128 == 0,
+                "hidden and 2 x intermediate_hidden must be multiples of %d", 128 * ctas);
+    MlpMaps maps;
+    MlpParams p{};
+    p.expert_end = reinterpret_cast<const int*>(base + l.expert_end);
+    p.num_experts = E;
+    p.phase_mask = 3;
+    p.ph[0] = MlpPhase{2 * inter, hidden, 8192u, kFmtE2M1_F8F6F4};
+    p.ph[1] = MlpPhase{hidden, inter, 8192u, kFmtE2M1_F8F6F4};
+    p.act_q = base + l.l2_acts;
+    p.act_q_row_stride = inter;
+    p.out = reinterpret_cast<__nv_bfloat16*>(base + l.l2_out);
+    p.out_row_stride = hidden;
+    p.act_sf = base + l.l2_sf;
+    p.act_sf_k_stride = l.max_rows;
+    p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
+    p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
+    p.fast_math = fast_math;
+    p.tile_done = reinterpret_cast<unsigned*>(base + l.tile_done);
+    int sms = 0;
+    int rc = effective_num_sms(&sms);
+    if (rc) return rc;
+    const int num_clusters = std::max(1, sms / ctas);
+    p.tiles_per_group = std::max(1, (2 * num_clusters + p.ph[0].n / (128 * ctas) - 1) / (p.ph[0].n / (128 * ctas)));
+    const uint64_t rows = static_cast<uint64_t>(l.max_rows);
+    const void* x[2] = {base + l.l1_acts, base + l.l2_acts};
+    const void* sfx[2] = {base + l.l1_sf, base + l.l2_sf};
+    const void* w[2] = {l1_w, l2_w};
+    const void* sfw[2] = {l1_w_sf, l2_w_sf};
+    for (int ph = 0; ph < 2; ++ph) {
+        const uint64_t k = static_cast<uint64_t>(p.ph[ph].k), n = static_cast<uint64_t>(p.ph[ph].n);
+        for (int i = 0; i < kMlpXMaps; ++i)
+            if ((rc = make_tensor_map_2d(&maps.x[ph][i], CU_TENSOR_MAP_DATA_TYPE_UINT8, x[ph], k, rows, k, 128, 16 * (i + 1), CU_TENSOR_MAP_SWIZZLE_128B)))
+                return rc;
+        if ((rc = make_tensor_map_2d(&maps.w[ph], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, w[ph], 128, static_cast<uint64_t>(E) * n * (k / 128), 64,
+                                     128, 256, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+        if ((rc = make_tensor_map_2d(&maps.sfx[ph], CU_TENSOR_MAP_DATA_TYPE_INT32, sfx[ph], rows, k / 128, rows * 4, 128, 2, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+        if ((rc = make_tensor_map_2d(&maps.sfw[ph], CU_TENSOR_MAP_DATA_TYPE_INT32, sfw[ph], n, static_cast<uint64_t>(E) * (k / 128), n * 4, 128, 2,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    }
+    DGB_CUDA(cudaMemsetAsync(p.tile_done, 0, static_cast<size_t>(l.max_rows / 128 + E) * 4, stream));
+
+    const int smem_bytes = pair ? MlpSmem<true>::kTotal : MlpSmem<false>::kTotal;
+    const void* kernel = pair ? reinterpret_cast<const void*>(&dgb200_expert_mlp_kernel<true>)
+                              : reinterpret_cast<const void*>(&dgb200_expert_mlp_kernel<false>);
+    static int configured_device[2] = {-1, -1};
+    int dev = 0;
+    DGB_CUDA(cudaGetDevice(&dev));
+    if (configured_device[pair ? 1 : 0] != dev) {
+        DGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        configured_device[pair ? 1 : 0] = dev;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_clusters * ctas));
+    cfg.blockDim = dim3(kMlpThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    void* args[2] = {&maps, &p};
+    DGB_CUDA(cudaLaunchKernelExC(&cfg, kernel, args));
+    return 0;
+}
+
 // The two grouped GEMMs of the layer over this rank's expert-sorted rows (shared by the single-rank and the
 // expert-parallel paths): L1 writes quantised activations + scales (FP8/UE8M0 or NVFP4/UE4M3), L2 writes BF16 rows
 // into l2_out in the same row order.
@@ -529,6 +624,14 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     //     only pays where such experts are common;
     //   otherwise the tokens-on-M kernel alone (with many rows per expert both orientations run 128-row tiles).
     // dgb200_set_tuning("swap_ab", 0 / 1) forces the tokens-on-M kernel / the swapped kernel with its fused epilogue.
+    if (!nvfp4 && !bf16 && mlp_kernel_choice() != 0) {
+        const bool pair = mlp_kernel_choice() == 2 && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0;
+        const int rc_mlp = run_expert_mlp(pair, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden,
+                                          activation_clamp, fast_math, stream);
+        if (rc_mlp) return rc_mlp;
+        const int rc_ev = record_stage(stage_event_base, stream);  // one launch: the down stage's share is inside the first interval
+        return rc_ev ? rc_ev : record_stage(stage_event_base + 1, stream);
+    }
     enum { kOrientM, kOrientSplit, kOrientSwapAll } orient = kOrientM;
     if (!nvfp4 && !bf16 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
         if (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= 40))
@@ -985,6 +1088,7 @@ int dgb200_set_tuning(const char* name, int32_t value) {
     }
     return 0;
 }
+
 
 int dgb200_get_num_sms(void) {
     int sms = 0;
@@ -1469,6 +1573,10 @@ int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t exper
 int dgb200_get_token_alignment_for_mega_moe(void) { return 128; }
 
 int dgb200_get_segment_alignment_for_mega_moe(void) { return kSegmentAlignment; }
+
+int dgb200_get_weight_tile_rows_for_mega_moe(void) { return mlp_kernel_choice() != 0 ? 128 : 0; }
+
+int dgb200_get_gate_up_interleave_for_mega_moe(void) { return mlp_kernel_choice() != 0 ? kMlpGateUpInterleave : 128; }
 
 int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
                                                int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,

@@ -84,16 +84,6 @@ struct SwapScheduler {
     }
 };
 
-// 16 consecutive TMEM columns of this thread's lane.
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t tmem_addr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(tmem_addr) : "memory");
-}
-
 // tm_x: tokens [rows, K] bytes, box 128 x kSwapMaxTok; tm_w: weights (16U4_ALIGN16B) box 128 x 256;
 // tm_sfx / tm_sfw: packed scale ints, box 256 x 1. p: the GemmParams of the layer call (psum layout, alignment 128).
 template <int EPI>

@@ -185,6 +185,17 @@ __device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.as
 // Returns once those stores are complete (their writes performed).
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// L2 prefetch of one contiguous span (16-byte aligned address, size a multiple of 16 bytes): starts the HBM read
+// early without occupying shared memory; handled by the bulk-copy unit, no completion to wait for.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+// L2 prefetch of one box of a tiled tensor map (same coordinate rules as the load).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" :: "l"(map), "r"(x), "r"(y) : "memory");
+}
+
 // ----------------------------------------------------------------------------------------------
 // tcgen05: tensor memory management
 // ----------------------------------------------------------------------------------------------
@@ -313,6 +324,111 @@ __device__ __forceinline__ void tcgen05_mma_mxf4nvf4_4x(uint32_t tmem_d, uint64_
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
         "}\n"
         :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// ----------------------------------------------------------------------------------------------
+// CTA pairs (thread-block cluster of two, tcgen05 cta_group::2). One thread of the even CTA (the leader) issues copies,
+// MMAs and commits for both; every address below is CTA-relative and applies to both CTAs of the pair alike.
+// Reference counterparts: deep_gemm/include/deep_gemm/ptx/tcgen05.cuh:61-98, deep_gemm/include/deep_gemm/common/tma_copy.cuh:37-45
+// (per-CTA loads that complete on the leader's barrier; no cluster multicast of loaded data anywhere).
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+
+// Shared-memory address of `local` (an address of this CTA) as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+
+// Arrives (count 1, no transaction bytes) on an mbarrier given by its cluster-wide shared address.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+
+// Tiled load into THIS CTA's shared memory whose completion bytes are credited to an mbarrier of either CTA of the pair
+// (`bar_cluster_addr` from map_to_cta). Plain per-CTA load: the data is not multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t x,
+                                                 int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+
+// Warp-collective, executed by the same warp of BOTH CTAs of the pair.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t num_cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(smem_dst)), "r"(num_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t tmem_addr, uint32_t num_cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_addr), "r"(num_cols) : "memory");
+}
+
+// All previously issued tcgen05 operations of this thread arrive, when they retire, on the mbarrier at this shared
+// offset in every CTA named by `cta_mask` (bit r = CTA r of the cluster).
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4_pair(uint32_t tmem_addr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" :: "r"(tmem_addr), "l"(sdesc) : "memory");
+}
+
+// D[tmem, 128 lanes per CTA] (+)= A[256 rows: 128 from each CTA's shared memory] * B[N rows: N / 2 from each CTA]^T.
+__device__ __forceinline__ void tcgen05_mma_mxf8f6f4_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t tmem_addr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(tmem_addr) : "memory");
+}
+
+// Named barrier among `count` threads (a multiple of 32) of this CTA; id 0 is __syncthreads.
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(count) : "memory");
+}
+
+// Generic-proxy accesses before, async-proxy (TMA) accesses after: every state space.
+__device__ __forceinline__ void fence_proxy_async_all() {
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+__device__ __forceinline__ void red_release_gpu_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Waits until at most `kPending` of this thread's committed bulk stores have not finished READING shared memory.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(kPending) : "memory");
 }
 
 // Each lane reads 32 consecutive 32-bit columns of its own TMEM lane (lane quarter = warp index % 4).

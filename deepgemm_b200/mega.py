@@ -154,6 +154,18 @@ def _sf_rows_to_cp_order(sf: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def _to_weight_tiles(w: torch.Tensor, tile_rows: int) -> torch.Tensor:
+    """Packed FP4 weights [E, N, K / 2] -> the same bytes as contiguous tiles of ``tile_rows`` rows x 128 K elements, in the
+    order (expert, row block, K block): the storage dgb200_get_weight_tile_rows_for_mega_moe asks for. The tensor keeps
+    its shape; only libdgb200.so interprets the bytes."""
+    e, n, kb2 = w.shape
+    if tile_rows <= 0:
+        return w
+    if n % tile_rows != 0 or kb2 % 64 != 0:
+        raise RuntimeError(f'weight rows ({n}) must be a multiple of {tile_rows} and K a multiple of 128')
+    return w.view(e, n // tile_rows, tile_rows, kb2 // 64, 64).permute(0, 1, 3, 2, 4).contiguous().view(e, n, kb2)
+
+
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
                                    l2_weights: Tuple[torch.Tensor, torch.Tensor], activation: str = 'swiglu'):
     """Reorders the L1 weights (and their packed scale factors) so that every 256-row block holds 128 gate channels
@@ -174,9 +186,15 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
                                                 tuple(t.unsqueeze(0) for t in l2_weights), activation)
         return tuple(t[0] for t in t1), tuple(t[0] for t in t2)
     # NVFP4 weights carry a third element, the per-expert FP32 scales, which no reordering touches
-    l1_sf = _sf_rows_to_cp_order(_interleave_rows(l1_weights[1], _GATE_UP_INTERLEAVE))
-    return (_interleave_rows(l1_weights[0], _GATE_UP_INTERLEAVE), l1_sf) + tuple(l1_weights[2:]), \
-        (l2_weights[0], _sf_rows_to_cp_order(l2_weights[1])) + tuple(l2_weights[2:])
+    gran = _GATE_UP_INTERLEAVE
+    if len(l1_weights) == 2 and l1_weights[0].dtype == torch.int8:  # the FP8 x MXFP4 layer's routed experts
+        gran = _lib.lib().dgb200_get_gate_up_interleave_for_mega_moe()
+    l1_sf = _sf_rows_to_cp_order(_interleave_rows(l1_weights[1], gran))
+    l1_w, l2_w = _interleave_rows(l1_weights[0], gran), l2_weights[0]
+    if len(l1_weights) == 2 and l1_w.dtype == torch.int8:
+        tile_rows = _lib.lib().dgb200_get_weight_tile_rows_for_mega_moe()
+        l1_w, l2_w = _to_weight_tiles(l1_w, tile_rows), _to_weight_tiles(l2_w, tile_rows)
+    return (l1_w, l1_sf) + tuple(l1_weights[2:]), (l2_w, _sf_rows_to_cp_order(l2_weights[1])) + tuple(l2_weights[2:])
 
 
 def _check_weight(w, sf, num_groups, n, k, name, k_per_int=128):

@@ -230,6 +230,19 @@ int dgb200_get_token_alignment_for_mega_moe(void);
  * it). No reference counterpart: the reference sizes its pools by block_m tiles (csrc/apis/mega.hpp:34-80). */
 int dgb200_get_segment_alignment_for_mega_moe(void);
 
+/* Rows of one gate/up interleave block of the FP8 x MXFP4 layer's L1 weights: the rows of l1_w (and of its scale
+ * factors) must be ordered [gate 0..g-1 | up 0..g-1 | gate g..2g-1 | ...] with g = this value (16 for the fused
+ * expert-MLP kernel, 128 for the separate gate/up and down kernels; fixed for the life of the process).
+ * Reference: _interleave_weights (granularity 8), deep_gemm/mega/__init__.py:97-111. */
+int dgb200_get_gate_up_interleave_for_mega_moe(void);
+
+/* Rows of one weight tile of the FP8 x MXFP4 layer, or 0 for plain row-major weights. With r > 0 the packed E2M1 bytes
+ * of l1_w and l2_w must be stored as contiguous tiles of r rows x 128 K elements (r x 64 bytes), in the order (expert,
+ * r-row block, K block): byte (e, n, kb, c) of the row-major [E_local, N, K / 2] tensor (kb = K block of 64 bytes,
+ * c < 64) moves to offset (((e * N / r + n / r) * (K / 128) + kb) * r + n % r) * 64 + c. The fused expert-MLP kernel
+ * reads a tile as one TMA box and asks for it ahead of time with one bulk L2 prefetch. No reference counterpart. */
+int dgb200_get_weight_tile_rows_for_mega_moe(void);
+
 /* Byte layout of the per-rank mega-MoE buffer. Reference: get_symm_buffer_size_for_mega_moe, csrc/apis/mega.hpp:34-155.
  * out[16] = {total bytes, x, x_sf, topk_idx, topk_weights, l1_acts, l1_sf, l2_acts, l2_sf, max_rows (rows, not bytes),
  *            dest_row, src_of_row, expert_start, expert_end, l2_out, row_weight}; all but out[0], out[9] are byte
