@@ -576,7 +576,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     logits = logits_host.cuda()
     y = torch.empty((t, h), dtype=torch.bfloat16, device='cuda')
     lib = _lib.lib()
-    kernels_per_step = kernels_of_one_step(nvfp4, world)
+    kernels_per_step = kernels_of_one_step(nvfp4, world, cfg['local_experts'])
 
     def step(events=None, x_in=None, logits_in=None, y_out=None):
         x_in, logits_in, y_out = (x if x_in is None else x_in), (logits if logits_in is None else logits_in), (y if y_out is None else y_out)
@@ -697,9 +697,15 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     # intensity against the ridge of the FP8 tensor rate (nominal; this pool has no measured FP8 figure) over HBM
     l1_flops = 2.0 * rows_hot * h * 2 * i
     l1_s = stage_ms[2] * 1e-3
+    gemms_in_one_interval = world > 1  # expert parallel: gate/up and down GEMMs alternate phase by phase
+    if gemms_in_one_interval:
+        l1_flops = 2.0 * rows_hot * h * 3 * i
+        l1_bytes = l1_bytes + l2_bytes
     mma_peak_nominal = FP4_DENSE_PEAK_TFLOPS_NOMINAL if nvfp4 else FP8_DENSE_PEAK_TFLOPS_NOMINAL
     tensor_bound = l1_bytes > 0 and l1_flops / l1_bytes > mma_peak_nominal * 1e12 / (hbm_peak * 1e9)
-    l1_kernel_name = ('dgb200_grouped_gemm_kernel (gate/up GEMM + SwiGLU + requant)' if nvfp4 or world > 1 else L1_STAGE_KERNELS)
+    l1_kernel_name = ('dgb200_grouped_gemm_kernel (gate/up + SwiGLU + requant and down GEMMs of all expert phases, with the waits for '
+                      'the other ranks\' rows between them)' if world > 1 else
+                      'dgb200_grouped_gemm_kernel (gate/up GEMM + SwiGLU + requant)' if nvfp4 else L1_STAGE_KERNELS)
     if tensor_bound:
         roofline = {'kernel': l1_kernel_name, 'bound': 'tensor', 'achieved': l1_flops / l1_s / 1e12, 'peak': mma_peak_nominal,
                     'unit': 'TFLOP/s', 'frac': l1_flops / l1_s / 1e12 / mma_peak_nominal,
@@ -723,10 +729,12 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         'clocks': clocks,
         'roofline': roofline,
         # stage times of the most loaded rank (rank `stages_rank`); with several ranks the cross-rank waits are inside
-        'stages_ms': {'plan': stage_ms[0], 'dispatch': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
-                      'l2_gemm': stage_ms[3], 'combine': stage_ms[4]},
+        'stages_ms': ({'plan': stage_ms[0], 'dispatch': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
+                       'l2_gemm': stage_ms[3], 'combine': stage_ms[4]} if not gemms_in_one_interval else
+                      {'plan': stage_ms[0], 'dispatch_push': stage_ms[1], 'gemms_all_phases': stage_ms[2] + stage_ms[3],
+                       'combine_all_phases': stage_ms[4]}),
         'stages_rank': hot,
-        'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9,
+        'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9 if not gemms_in_one_interval else None,
         'tflops': tflops,
         'frac_fp4_dense_peak_nominal': tflops / (FP4_DENSE_PEAK_TFLOPS_NOMINAL * world),
         'frac_fp8_rate_peak_nominal': tflops / (FP8_DENSE_PEAK_TFLOPS_NOMINAL * world),
@@ -754,12 +762,16 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     return line, (l1, l2)
 
 
-def kernels_of_one_step(nvfp4, world):
-    """Launches of this library's kernels in one pass of the layer (the memset of the single-rank plan is not a kernel of
-    ours). FP8 layer on one rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the
-    two tile orientations (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather;
-    expert parallel adds the count exchange, the plan, the scale reorder and three barriers."""
-    return 9 if nvfp4 else (11 if world == 1 else 12)
+def kernels_of_one_step(nvfp4, world, local_experts):
+    """Launches of this library's kernels in one pass of the layer (memsets are not kernels of ours). FP8 layer on one
+    rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the two tile orientations
+    (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather. Expert parallel, P =
+    min(4, local experts) phases: router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
+    per phase flag + scale reorder + L1 + L2 + flag, per phase flag + combine."""
+    if world == 1:
+        return 9 if nvfp4 else 11
+    phases = min(4, local_experts)
+    return 7 + 2 * phases + 5 * phases + 2 * phases
 
 
 L1_STAGE_KERNELS = ('gate/up GEMM + SwiGLU + FP8 requant (dgb200_grouped_gemm_kernel + dgb200_swap_gemm_kernel + '
@@ -800,8 +812,18 @@ def run_ours(args, cfg, rank, world, local_rank):
     return 1 if failed else 0
 
 
+def keep_stdout_for_the_json_line():
+    """Native libraries (NCCL's version banner, for one) write to file descriptor 1 behind Python's back. Point that
+    descriptor at stderr and keep the original for sys.stdout, so the one JSON line is all that reaches stdout."""
+    sys.stdout.flush()
+    kept = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(kept, 'w')
+
+
 def main():
     args = parse_args()
+    keep_stdout_for_the_json_line()
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))

@@ -403,6 +403,7 @@ struct MegaLayout {
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
     long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
+    long long combine_partial;  // expert parallel: fp32 [max tokens, hidden], the running sums of the phased combine
     long long tile_done;  // FP8 kind: one counter per token tile of the fused expert-MLP kernel (max_rows / 128 + local experts)
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
     long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
@@ -464,7 +465,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.chunk_hist = take(static_cast<long long>(l.num_chunks) * num_experts * 4);
     l.all_counts = take(static_cast<long long>(num_ranks) * num_experts * 4);
     l.my_base = take(num_experts * 4ll);
-    l.flags = take(4 * kMaxEpRanks * 4);
+    l.flags = take(kEpFlagRows * kMaxEpRanks * 4);
     l.expert_start = take(l.num_local_experts * 4ll);
     l.expert_end = take(l.num_local_experts * 4ll);
     l.total_rows = take(16);
@@ -479,6 +480,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l1_tmp = kind == kKindFp8Fp4 ? take(l.max_rows * inter * 4) : 0;
     l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_local_experts) * 4) : 0;
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
+    l.combine_partial = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * hidden * 4) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
         DGB_REQUIRE((kind == kKindFp8Fp4 || kind == kKindBf16) && shared_inter % 128 == 0,
@@ -608,8 +610,12 @@ int run_expert_mlp(bool pair, const MegaLayout& l, uint8_t* base, const void* l1
 // into l2_out in the same row order.
 int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
                     const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
-                    cudaStream_t stream, int stage_event_base, long long expected_rows_per_expert) {
+                    cudaStream_t stream, int stage_event_base, long long expected_rows_per_expert, int group_begin = 0,
+                    int group_end = 0) {
     const int E = l.num_local_experts;
+    // [group_begin, group_end): the local experts this call computes ({0, 0} = all of them)
+    const int first_expert = (group_begin == 0 && group_end == 0) ? 0 : group_begin;
+    const int num_call_experts = (group_begin == 0 && group_end == 0) ? E : group_end - group_begin;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
     const bool nvfp4 = quant.kind == kKindNvfp4;
     const bool bf16 = quant.kind == kKindBf16;
@@ -625,6 +631,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
     //   otherwise the tokens-on-M kernel alone (with many rows per expert both orientations run 128-row tiles).
     // dgb200_set_tuning("swap_ab", 0 / 1) forces the tokens-on-M kernel / the swapped kernel with its fused epilogue.
     if (!nvfp4 && !bf16 && mlp_kernel_choice() != 0) {
+        DGB_REQUIRE(group_begin == 0 && group_end == 0, "the fused expert-MLP kernel computes all experts of a rank in one launch");
         const bool pair = mlp_kernel_choice() == 2 && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0;
         const int rc_mlp = run_expert_mlp(pair, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden,
                                           activation_clamp, fast_math, stream);
@@ -665,11 +672,11 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         rc1 = run_gemm(c, stream);
         if (rc1 == 0) rc1 = run_gemm_swap(c2, side->stream);
         if (rc1 == 0 && gate_up) {
-            const dim3 grid((kSwapMaxTok + 7) / 8, E);
+            const dim3 grid((kSwapMaxTok + 7) / 8, num_call_experts);
             dgb200_swiglu_requant_rows_kernel<<<grid, 256, 0, side->stream>>>(
                 reinterpret_cast<const __nv_bfloat16*>(base + l.l1_tmp), reinterpret_cast<const int*>(base + l.expert_start), expert_end,
                 split_lo, kSwapMaxTok, intermediate_hidden, c.p.row_weight, c.p.clamp, c.p.fast_math, c.p.act_q, c.p.act_q_row_stride,
-                reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride);
+                reinterpret_cast<unsigned*>(c.p.act_sf), c.p.act_sf_k_stride, first_expert);
             if (cudaGetLastError() != cudaSuccess) rc1 = fail(DGB200_ECUDA, "launch of the SwiGLU finisher failed");
         }
         // join even after a failed launch, so that the side stream never runs ahead of the caller's stream
@@ -702,6 +709,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.n = 2 * intermediate_hidden;
         p.k = hidden;
         p.num_groups = E;
+        p.group_begin = group_begin;
+        p.group_end = group_end;
         p.alignment = kSegmentAlignment;
         p.gran_a = 32;
         p.gran_b = 32;
@@ -745,6 +754,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.n = hidden;
         p.k = intermediate_hidden;
         p.num_groups = E;
+        p.group_begin = group_begin;
+        p.group_end = group_end;
         p.alignment = kSegmentAlignment;
         p.gran_a = 32;
         p.gran_b = 32;
@@ -837,7 +848,7 @@ int run_shared_x_sf(const MegaLayout& l, uint8_t* base, int num_tokens, int hidd
     const int ints = hidden / 128;
     dgb200_sf_rows_to_cp_order_kernel<<<(num_tokens + 31) / 32, 256, ints * 33 * sizeof(unsigned), stream>>>(
         reinterpret_cast<const unsigned*>(base + l.x_sf), num_tokens, ints, reinterpret_cast<unsigned*>(base + l.shared_x_sf),
-        l.token_rows, nullptr);
+        l.token_rows, nullptr, nullptr, nullptr);
     DGB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -846,74 +857,112 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                     int32_t* stats, uint8_t* base, const uint64_t* peer_buffer_ptrs, int rank, int num_ranks, int num_tokens,
                     int num_max_tokens_per_rank, int num_experts, int num_topk, int hidden, int intermediate_hidden,
                     float activation_clamp, int fast_math, cudaStream_t stream) {
+    // Expert-parallel layer, every step a kernel on the caller's stream. The local experts of every rank are cut into
+    // up to kMaxEpPhases phases; dispatch, GEMMs and combine run phase by phase behind per-phase flags, so that the
+    // NVLink traffic of one phase overlaps the GEMMs of the others (on the rank that receives the most rows: rows of later
+    // phases arrive while it computes earlier ones, and its peers pull finished phases while it computes the rest):
+    //   count -> publish counts -> flag row 0 (signal + wait) -> plan -> assign
+    //   for each phase q: push the entries of phase-q experts to their owners -> signal "dispatch q"
+    //   for each phase q: wait "dispatch q" of all ranks -> scale reorder -> L1(q) -> L2(q) -> signal "outputs q"
+    //   for each phase q: wait "outputs q" of all ranks -> combine phase q (pull rows, FP32 running sums; last phase writes y)
+    // Reference: the fused kernel overlaps the same traffic tile by tile (sm100_fp8_fp4_mega_moe.cuh:533-556, :1274-1300)
+    // behind three barriers (comm/barrier.cuh:47-89).
     PeerTable peers{};
     for (int r = 0; r < num_ranks; ++r) {
         DGB_REQUIRE(peer_buffer_ptrs[r] != 0, "peer buffer %d is not mapped", r);
         peers.p[r] = peer_buffer_ptrs[r];
     }
+    const int E = l.num_local_experts;
     const int entries = num_tokens * num_topk;
     const int chunks = std::max(1, (entries + kPlanChunk - 1) / kPlanChunk);
     const int entries_per_rank = num_max_tokens_per_rank * num_topk;
     const bool with_shared = quant.shared_inter > 0;
     const int sf_per_row = sf_ints_per_row(quant.kind, hidden);
+    const bool fused_mlp = quant.kind == kKindFp8Fp4 && mlp_kernel_choice() != 0;
+    const int phases = fused_mlp ? 1 : std::min(kMaxEpPhases, E);
     int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
+    const int* expert_start = reinterpret_cast<const int*>(base + l.expert_start);
+    const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
     const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
     const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
     const long long peer_budget = tuning().peer_wait_cycles;
+    auto flag = [&](int row, int do_signal, int do_wait) {
+        dgb200_ep_flag_kernel<<<1, 32, 0, stream>>>(peers, l.flags, row, rank, num_ranks, do_signal, do_wait, peer_budget);
+    };
+    auto phase_begin = [&](int q) { return static_cast<int>(static_cast<long long>(q) * E / phases); };
     int rc = 0;
     if ((rc = record_stage(0, stream))) return rc;
 
     // count this rank's entries per (global) expert and publish the totals to every rank
     dgb200_moe_count_kernel<<<chunks, kPlanChunk, num_experts * sizeof(int), stream>>>(topk_idx, entries, 0, num_experts, chunk_hist);
     dgb200_ep_share_counts_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, num_experts, rank, num_ranks, peers, l.all_counts);
-    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 0, rank, num_ranks, peer_budget);
-    // the same global plan on every rank, then push rows to their owners
+    flag(0, 1, 1);
+    // the same global plan on every rank
     dgb200_ep_plan_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
                                                    kSegmentAlignment, reinterpret_cast<int*>(base + l.my_base),
                                                    reinterpret_cast<int*>(base + l.expert_start),
                                                    reinterpret_cast<int*>(base + l.expert_end),
                                                    reinterpret_cast<int*>(base + l.total_rows), stats);
-    if (entries > 0) {
+    if (entries > 0)
         dgb200_ep_assign_kernel<<<chunks, kPlanChunk, 32 * num_experts, stream>>>(topk_idx, entries, num_experts, chunk_hist,
                                                                               reinterpret_cast<const int*>(base + l.my_base), dest_row);
-        if ((rc = record_stage(1, stream))) return rc;
-        if (quant.x_bf16 != nullptr)
-            dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
-                quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden,
-                l.num_local_experts, rank, entries_per_rank, peers, l.l1_acts, l.l1_sf_stage, -static_cast<long long>(sf_per_row),
-                l.row_weight, l.src_of_row, 1, with_shared ? base + l.x : nullptr,
-                with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr, l.token_rows);
-        else
+    DGB_CUDA(cudaGetLastError());
+    if ((rc = record_stage(1, stream))) return rc;
+
+    // dispatch, phase by phase: rows + scales + weight + source id stored straight into the owners' expert-sorted buffers
+    if (quant.x_bf16 != nullptr && num_tokens > 0) {
+        // BF16 input: quantise once into the buffer's x / x_sf views (the bits of per_token_cast_to_fp8, gran 32), push from there
+        rc = run_cast(false, quant.x_bf16, quant.x_bf16_row_stride, num_tokens, hidden, 32, base + l.x, hidden, nullptr, base + l.x_sf, 1,
+                      sf_per_row, stream);
+        if (rc) return rc;
+    }
+    for (int q = 0; q < phases; ++q) {
+        if (entries > 0)
             dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
                 base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
-                static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, l.num_local_experts, rank,
-                entries_per_rank, peers, l.l1_acts, l.l1_sf_stage, 0, l.row_weight, l.src_of_row);
-    } else if ((rc = record_stage(1, stream))) {
-        return rc;
+                static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, E, rank, entries_per_rank, peers, l.l1_acts,
+                l.l1_sf_stage, 0, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1));
+        flag(1 + q, 1, 0);
     }
-    DGB_CUDA(cudaGetLastError());
-    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 1, rank, num_ranks, peer_budget);
-    // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
-    if (sf_per_row > 0)
-        dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
-            reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
-            reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows));
     DGB_CUDA(cudaGetLastError());
     if ((rc = record_stage(2, stream))) return rc;
 
-    rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream, 3,
-                         static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts);
-    if (rc) return rc;
+    // GEMMs, phase by phase, each as soon as every rank's rows for the phase have landed
+    for (int q = 0; q < phases; ++q) {
+        const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
+        flag(1 + q, 0, 1);
+        if (g1 == g0) { flag(1 + kMaxEpPhases + q, 1, 0); continue; }
+        // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
+        if (sf_per_row > 0)
+            dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
+                reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
+                reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows),
+                expert_start + g0, expert_end + g1 - 1);
+        DGB_CUDA(cudaGetLastError());
+        rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream,
+                             kNumStageEvents /* no stage events inside the loop */,
+                             static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts,
+                             phases == 1 ? 0 : g0, phases == 1 ? 0 : g1);
+        if (rc) return rc;
+        flag(1 + kMaxEpPhases + q, 1, 0);
+    }
+    if ((rc = record_stage(3, stream))) return rc;  // both GEMMs of all phases lie before this point
+    if ((rc = record_stage(4, stream))) return rc;
     if (with_shared && num_tokens > 0) {
-        if (quant.x_bf16 == nullptr && quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
+        if (quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
         if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
     }
-    dgb200_ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, l.flags, 2, rank, num_ranks, peer_budget);
-    if (num_tokens > 0)
-        dgb200_moe_combine_kernel<<<num_tokens, 128, (num_topk + 1) * sizeof(unsigned long long), stream>>>(
-            peers, l.l2_out, topk_idx, dest_row, num_topk, l.num_local_experts, hidden,
-            with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
+    // combine, phase by phase, each as soon as every rank has finished the phase's experts
+    for (int q = 0; q < phases; ++q) {
+        flag(1 + kMaxEpPhases + q, 0, 1);
+        if (num_tokens > 0)
+            dgb200_moe_combine_phase_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
+                peers, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
+                with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
+                reinterpret_cast<float*>(base + l.combine_partial), static_cast<__nv_bfloat16*>(y), phase_begin(q), phase_begin(q + 1),
+                q == 0 ? 1 : 0, q == phases - 1 ? 1 : 0);
+    }
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }

@@ -78,6 +78,8 @@ struct GemmParams {
     int rows_lo, rows_hi;    // psum / masked layouts: only groups whose valid rows lie in [rows_lo, rows_hi] (rows_skip = 0)
     int rows_skip;           // ... or outside it (rows_skip = 1) are computed; {0, 0, 0} = every group. Lets two kernels
                              // with different tile orientations split the groups of one GEMM by size.
+    int group_begin, group_end;  // psum / masked layouts: only groups in [group_begin, group_end) are computed; {0, 0} = all.
+                                 // The expert-parallel layer runs its experts phase by phase.
     // SwiGLU epilogue only
     unsigned char* act_q;        // e4m3 [rows, n/2]
     int tma_store;               // epilogue stores through shared memory + TMA (BLOCK_N = 256, FP8 x FP4 kind): 0 never,
@@ -142,6 +144,10 @@ struct GroupTable {
     const int* tiles_end;  // tiles of groups 0..g inclusive
     bool cached;           // false: walk the global layout array with the arithmetic below (more groups than the table holds)
 };
+
+__device__ __forceinline__ bool group_in_range(const GemmParams& p, int group) {
+    return (p.group_begin == 0 && p.group_end == 0) || (group >= p.group_begin && group < p.group_end);
+}
 
 __device__ __forceinline__ bool group_selected(const GemmParams& p, int rows) {
     if (p.rows_lo == 0 && p.rows_hi == 0) return true;
@@ -238,7 +244,7 @@ struct TileScheduler {
         while (g < p.num_groups) {
             int start, rows, rows_store;
             group_extent(p, tab.lay, g, start, rows, rows_store);
-            const int tiles_g = group_selected(p, rows) ? (max(rows, rows_store) + 127) / 128 * num_n_blocks : 0;
+            const int tiles_g = (group_selected(p, rows) && group_in_range(p, g)) ? (max(rows, rows_store) + 127) / 128 * num_n_blocks : 0;
             if (tile < tiles_before_g + tiles_g) {
                 fill(t, g, start, rows_store, tile - tiles_before_g);
                 return true;
@@ -386,7 +392,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             TileScheduler<BLOCK_N, EPI == kEpiF32Acc>::group_extent(p, p.layout, i, start, rows, rows_store);
             group_cache[i] = __ldg(p.layout + i);
             group_start[i] = start;
-            group_tiles_end[i] = group_selected(p, rows) ? (max(rows, rows_store) + 127) / 128 * (p.n / BLOCK_N) : 0;
+            group_tiles_end[i] = (group_selected(p, rows) && group_in_range(p, i)) ? (max(rows, rows_store) + 127) / 128 * (p.n / BLOCK_N) : 0;
         }
         __syncthreads();
         if (warp == 0) {

@@ -138,7 +138,7 @@ dgb200_swap_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
         const int end = __ldg(p.layout + i);
         group_lay[i] = end;
         group_start[i] = start;
-        group_tiles_end[i] = group_selected(p, end - start) ? swap_token_tiles(end - start) * num_w_blocks : 0;
+        group_tiles_end[i] = (group_selected(p, end - start) && group_in_range(p, i)) ? swap_token_tiles(end - start) * num_w_blocks : 0;
     }
     __syncthreads();
     if (warp == 0) {

@@ -258,6 +258,78 @@ dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const lo
     }
 }
 
+// The combine of the expert-parallel layer, one phase of the local experts at a time: phase q adds, for every token, the
+// rows of the slots whose expert (numbered within its owner) lies in [local_expert_begin, local_expert_end), read in
+// place from the owners over NVLink. The running sum of a token is kept in FP32 in `partial` ([tokens, hidden]) between
+// phases: the first phase starts from zero (or from the shared experts' row), the last one writes bf16 y. The rows of a
+// phase can be pulled as soon as every rank has finished that phase's experts, while later phases are still being
+// computed; within a phase the slots are added in ascending order. Tokens without a slot in a middle phase are skipped.
+__global__ void __launch_bounds__(128)
+dgb200_moe_combine_phase_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
+                                const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
+                                const __nv_bfloat16* __restrict__ shared_rows, float* __restrict__ partial,
+                                __nv_bfloat16* __restrict__ y, int local_expert_begin, int local_expert_end, int first, int last) {
+    const int t = blockIdx.x;
+    extern __shared__ unsigned long long slot_rows[];  // address of each slot's row of this phase, 0 = skip
+    __shared__ int any;
+    if (threadIdx.x == 0) any = 0;
+    __syncthreads();
+    if (threadIdx.x < topk) {
+        const int d = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
+        unsigned long long addr = 0;
+        if (d >= 0) {
+            const int e = static_cast<int>(topk_idx[static_cast<long long>(t) * topk + threadIdx.x]);
+            const int owner = e / experts_per_rank, local_expert = e - owner * experts_per_rank;
+            if (local_expert >= local_expert_begin && local_expert < local_expert_end) {
+                addr = peers.p[owner] + rows_offset + static_cast<unsigned long long>(d) * hidden * 2;
+                any = 1;
+            }
+        }
+        slot_rows[threadIdx.x] = addr;
+    }
+    __syncthreads();
+    if (!any && !first && !last) return;
+    float* part = partial + static_cast<long long>(t) * hidden;
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (!first) {
+            const float4 a = reinterpret_cast<const float4*>(part)[2 * c], b = reinterpret_cast<const float4*>(part)[2 * c + 1];
+            acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+        }
+        for (int k = 0; k < topk; ++k) {
+            const unsigned long long addr = slot_rows[k];
+            if (addr == 0) continue;
+            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(addr) + c);
+            const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += __uint_as_float(w[i] << 16);
+                acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+        if (last) {
+            if (shared_rows != nullptr) {  // the shared experts' row is the slot after the top-k ones
+                const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(shared_rows + static_cast<long long>(t) * hidden) + c);
+                const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] += __uint_as_float(w[i] << 16);
+                    acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+                }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]);
+            o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]);
+            o.w = pack_bf16x2(acc[6], acc[7]);
+            reinterpret_cast<uint4*>(y + static_cast<long long>(t) * hidden)[c] = o;
+        } else {
+            reinterpret_cast<float4*>(part)[2 * c] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            reinterpret_cast<float4*>(part)[2 * c + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+    }
+}
+
 // ==================================================================================================================
 // Expert-parallel dispatch: ranks own contiguous blocks of experts (expert e lives on rank e / experts_per_rank, as
 // in the reference: deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:372,389). Every rank holds one
@@ -292,42 +364,63 @@ dgb200_ep_share_counts_kernel(int* __restrict__ chunk_hist, int num_chunks, int 
     }
 }
 
-// Cross-rank barrier: one warp; lane r signals rank r and waits for rank r's signal. The flags region of the buffer is
-// int [4][kMaxEpRanks]: row `which` (0..2) holds, in slot r, the epoch rank r last signalled for that barrier; row 3
-// holds this rank's own epoch counters (word `which`), advanced by this kernel. The epoch therefore lives and dies
-// with the buffer (zeroed once when the buffer is created, on every rank, before the first call): a replayed launch
-// advances it like a fresh one, and a new buffer at a recycled address starts from zero on every rank alike. Flags
-// only grow, so they never need a reset. Bounded: a peer that does not show up within the budget is reported through
-// the status block, not waited for forever.
+// Cross-rank flags of the expert-parallel layer. The flags region of the buffer is int [kEpFlagRows][kMaxEpRanks]:
+//   rows 0 .. kEpFlagRows - 5:  flag rows; slot s holds the epoch rank s last signalled on that row
+//   rows kEpFlagRows - 4, - 3:  this rank's own count of signals sent per flag row (word = row)
+//   rows kEpFlagRows - 2, - 1:  this rank's own count of waits completed per flag row
+// Rows: 0 = "my per-expert counts are published"; 1 + q = "my rows for expert phase q are pushed" (dispatch);
+// 1 + kMaxEpPhases + q = "my experts of phase q have their outputs ready" (combine). All ranks make the same sequence of
+// calls, so the n-th wait on a row pairs with every rank's n-th signal on it: the epochs live and die with the buffer
+// (zeroed once when the buffer is created, on every rank, before the first call), a replayed launch advances them like
+// a fresh one, and flags only grow, so nothing ever needs a reset. One warp; lane s signals rank s and / or waits for
+// rank s. Bounded: a peer that does not show up within the budget is reported through the status block (peer timeout,
+// detail = the rank), not waited for forever.
+constexpr int kMaxEpPhases = 4;
+constexpr int kEpFlagRows = 1 + 2 * kMaxEpPhases + 4;  // 9 flag rows, then 2 + 2 rows of this rank's own counters
+
 __global__ void __launch_bounds__(32)
-dgb200_ep_barrier_kernel(const PeerTable peers, long long flags_offset, int which, int my_rank,
-                         int num_ranks, long long budget_cycles) {
+dgb200_ep_flag_kernel(const PeerTable peers, long long flags_offset, int row, int my_rank, int num_ranks, int do_signal,
+                      int do_wait, long long budget_cycles) {
     const int lane = threadIdx.x;
     int* local = reinterpret_cast<int*>(peers.p[my_rank] + flags_offset);
-    int epoch = 0;
-    if (lane == 0) {
-        epoch = local[3 * kMaxEpRanks + which] + 1;
-        local[3 * kMaxEpRanks + which] = epoch;
-    }
-    epoch = __shfl_sync(0xffffffffu, epoch, 0);
-    __threadfence_system();
-    if (lane < num_ranks) {
-        int* remote = reinterpret_cast<int*>(peers.p[lane] + flags_offset) + which * kMaxEpRanks + my_rank;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(remote), "r"(epoch) : "memory");
-        const int* mine = local + which * kMaxEpRanks + lane;
-        const long long t0 = clock64();
-        while (true) {
-            int seen;
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if (seen - epoch >= 0) break;
-            if (clock64() - t0 > budget_cycles) {
-                report_error(kTimeoutPeer, lane, seen);
-                break;
-            }
-            __nanosleep(100);
+    int* sent = local + (kEpFlagRows - 4) * kMaxEpRanks + row;
+    int* waited = local + (kEpFlagRows - 2) * kMaxEpRanks + row;
+    if (do_signal) {
+        int epoch = 0;
+        if (lane == 0) {
+            epoch = *sent + 1;
+            *sent = epoch;
+        }
+        epoch = __shfl_sync(0xffffffffu, epoch, 0);
+        __threadfence_system();  // everything this rank stored before (to any rank) is visible before the flag
+        if (lane < num_ranks) {
+            int* remote = reinterpret_cast<int*>(peers.p[lane] + flags_offset) + row * kMaxEpRanks + my_rank;
+            asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(remote), "r"(epoch) : "memory");
         }
     }
-    __threadfence_system();
+    if (do_wait) {
+        int epoch = 0;
+        if (lane == 0) {
+            epoch = *waited + 1;
+            *waited = epoch;
+        }
+        epoch = __shfl_sync(0xffffffffu, epoch, 0);
+        if (lane < num_ranks) {
+            const int* mine = local + row * kMaxEpRanks + lane;
+            const long long t0 = clock64();
+            while (true) {
+                int seen;
+                asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                if (seen - epoch >= 0) break;
+                if (clock64() - t0 > budget_cycles) {
+                    report_error(kTimeoutPeer, lane, seen);
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        __threadfence_system();
+    }
 }
 
 // One CTA. From all_counts[source rank][expert] derives, identically on every rank:
@@ -418,21 +511,24 @@ dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries,
     dest_row[i] = my_base[e] + chunk_hist[static_cast<long long>(blockIdx.x) * num_experts + e] + before + rank_in_warp;
 }
 
-// One warp per entry: stores the token's FP8 row, its packed scales (into the owner's MN-major scale buffer), the routing
-// weight and the source id into the owner rank's buffers.
+// One warp per entry: stores the token's quantised row, its packed scales (into the owner's MN-major scale buffer), the
+// routing weight and the source id into the owner rank's buffers.
 __global__ void __launch_bounds__(256)
 dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
                       const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights,
                       const int* __restrict__ dest_row, int num_entries, int topk, int row_bytes, int sf_per_row,
                       int experts_per_rank, int my_rank, int entries_per_rank, const PeerTable peers,
                       long long acts_offset, long long sf_offset, long long sf_k_stride, long long weight_offset,
-                      long long src_offset) {
+                      long long src_offset, int local_expert_begin, int local_expert_end) {
     const int lane = threadIdx.x & 31;
     const int entry = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (entry >= num_entries) return;
     const int dest = dest_row[entry];
     if (dest < 0) return;
     const int owner = static_cast<int>(topk_idx[entry]) / experts_per_rank;
+    // only the entries whose expert (numbered within its owner) lies in [begin, end): the layer pushes phase by phase
+    const int local_expert = static_cast<int>(topk_idx[entry]) - owner * experts_per_rank;
+    if (local_expert < local_expert_begin || local_expert >= local_expert_end) return;
     const int token = entry / topk;
     const unsigned long long base = peers.p[owner];
     const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes);
@@ -550,10 +646,16 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
 // (shared experts). 32 tokens per CTA through a padded shared-memory tile.
 __global__ void __launch_bounds__(256)
 dgb200_sf_rows_to_cp_order_kernel(const unsigned* __restrict__ sf, int tokens, int ints_per_row, unsigned* __restrict__ out,
-                                  long long k_stride, const int* __restrict__ rows_limit) {
+                                  long long k_stride, const int* __restrict__ rows_limit, const int* __restrict__ first_row,
+                                  const int* __restrict__ last_row_end) {
     extern __shared__ unsigned sf_tile[];  // [ints_per_row][33]
     if (rows_limit != nullptr) tokens = min(tokens, rows_limit[0]);  // row count only known on the device
-    const int t0 = blockIdx.x * 32;
+    int begin = 0;
+    if (first_row != nullptr) {  // only the rows [first_row[0], last_row_end[0]) (a range of expert segments; both multiples of 32 or the end)
+        begin = first_row[0];
+        tokens = min(tokens, last_row_end[0]);
+    }
+    const int t0 = begin + blockIdx.x * 32;
     if (t0 >= tokens) return;
     for (int i = threadIdx.x; i < 32 * ints_per_row; i += 256) {
         const int r = i / ints_per_row, c = i - r * ints_per_row;
@@ -579,8 +681,8 @@ dgb200_swiglu_requant_rows_kernel(const __nv_bfloat16* __restrict__ tmp, const i
                                   const int* __restrict__ expert_end, int rows_lo, int rows_hi, int inter,
                                   const float* __restrict__ row_weight, float clamp, int fast_math,
                                   unsigned char* __restrict__ act_q, long long act_q_row_stride,
-                                  unsigned* __restrict__ act_sf, long long act_sf_k_stride) {
-    const int e = blockIdx.y;
+                                  unsigned* __restrict__ act_sf, long long act_sf_k_stride, int first_expert) {
+    const int e = first_expert + blockIdx.y;
     const int start = expert_start[e], rows = expert_end[e] - start;
     if (rows < rows_lo || rows > rows_hi) return;
     const int lane = threadIdx.x & 31;

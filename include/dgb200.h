@@ -256,7 +256,8 @@ int dgb200_get_symm_buffer_layout_for_mega_moe(int32_t num_ranks, int32_t num_ex
  * Reference: fp8_fp4_mega_moe, csrc/apis/mega.hpp:157-286 (host) and
  * deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:55-1458 (kernel).
  *   y        bf16 [num_tokens, hidden], written.
- *   l1_w     packed e2m1 [E_local, 2 * inter, hidden / 2], rows gate/up-interleaved by 128;
+ *   l1_w     packed e2m1 [E_local, 2 * inter, hidden / 2], rows gate/up-interleaved in blocks of
+ *            dgb200_get_gate_up_interleave_for_mega_moe() rows, bytes tiled as dgb200_get_weight_tile_rows_for_mega_moe() says;
  *   l1_w_sf  packed UE8M0 int32 (per-32), MN-major [E_local][hidden / 128][2 * inter], same row order, then every
  *            aligned group of 128 rows stored in tcgen05.cp order: row r of a group at position 4 (r % 32) + r / 32.
  *   l2_w     packed e2m1 [E_local, hidden, inter / 2]; l2_w_sf int32 [E_local][inter / 128][hidden], rows in the
@@ -319,9 +320,10 @@ int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* args, void* stream);
 
 /* dgb200_get_symm_buffer_layout_for_mega_moe with room for shared experts: out[21] = the 16 words above, then the byte
  * offsets of the shared experts' private regions (x scales in GEMM order, activations, their scales, output rows) and,
- * last, of the cross-rank barrier words (int32 [4][8]: rows 0..2 = per barrier, the epoch each rank last signalled;
- * row 3 = this rank's own epoch counters). The whole buffer must be zeroed once after it is allocated, on every rank
- * and before any rank's first call (the barrier words are never reset afterwards; everything else is rewritten by
+ * last, of the cross-rank flag words (int32 [13][8]: rows 0..8 = flag rows, slot s = the epoch rank s last signalled:
+ * row 0 counts published, rows 1..4 dispatch phases, rows 5..8 output phases; rows 9..12 = this rank's own counts of
+ * signals sent and waits completed per flag row). The whole buffer must be zeroed once after it is allocated, on every
+ * rank and before any rank's first call (the flag words are never reset afterwards; everything else is rewritten by
  * each call before it is read). */
 int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
                                                   int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,

@@ -88,11 +88,29 @@ def _worker(rank, world, port, results):
         dg.fp8_fp4_mega_moe(y, l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2, fast_math=False)
         assert _lib.device_status()[0] == 0
         ys.append(y.cpu())
-        lay = buf.layout
+        # a second buffer whose allocation history differs between the ranks (rank 0 allocates something else first, rank
+        # 1 frees its first buffer before): the flag epochs live in the buffer, so a new buffer starts from zero on every
+        # rank no matter where the allocator placed it
+        if rank == 0:
+            filler = torch.empty(37 << 20, dtype=torch.int8, device='cuda')
+        else:
+            buf.destroy()
+        buf2 = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, EXPERTS, max(TOKENS), TOPK, HIDDEN, INTER, num_shared_experts=1)
+        buf2.x[:t].copy_(c['x_q'].cuda())
+        buf2.x_sf[:t].copy_(quant.pack_ue8m0(c['x_sf']).cuda())
+        buf2.topk_idx[:t].copy_(c['topk_idx'].cuda())
+        buf2.topk_weights[:t].copy_(c['topk_weights'].cuda())
+        y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf2)
+        assert _lib.device_status()[0] == 0
+        y_second_buffer = y.cpu()
+        lay = buf2.layout
+        buf = buf2
         end = buf.buffer[lay['expert_end']:lay['expert_end'] + per_rank * 4].view(torch.int32).cpu()
         start = buf.buffer[lay['expert_start']:lay['expert_start'] + per_rank * 4].view(torch.int32).cpu()
         dest = buf.buffer[lay['dest_row']:lay['dest_row'] + t * TOPK * 4].view(torch.int32).cpu()
-        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], y_shared=ys[3], y_swapped=y_swapped, start=start, end=end, dest=dest, stats=stats.cpu())
+        results[rank] = dict(y0=ys[0], y1=ys[1], y_fused=ys[2], y_shared=ys[3], y_swapped=y_swapped, y_second_buffer=y_second_buffer, start=start, end=end, dest=dest,
+                             stats=stats.cpu())
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -114,6 +132,7 @@ def test_two_rank_layer_matches_oracle():
         want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
         assert torch.equal(got['y0'], got['y1']), 'two calls on the same buffer must give the same bits'
         assert torch.equal(got['y0'], got['y_fused']), 'the fused prologue must give the same bits'
+        assert torch.equal(got['y0'], got['y_second_buffer']), 'a second buffer (new flag epochs) must give the same bits'
         assert quant.calc_diff(got['y_swapped'], got['y0']) <= 1e-5, 'tile orientation must not change the result'
         assert not torch.isnan(got['y0'].float()).any()
         assert quant.calc_diff(got['y0'], want) <= 2e-3

@@ -281,7 +281,7 @@ def test_down_gemm_split_by_group_size(dg):
 def test_peer_wait_runs_out_and_the_library_stays_usable(dg):
     """Failure detection of the expert-parallel barrier, on one GPU and without faulting it: the layer is called as rank 0
     of 2 with both entries of the peer table pointing at this process's own buffer, so the flag "rank 1" should write
-    never changes. With a 2 ms budget every barrier gives up, records the peer-timeout status (code 7, detail = the rank
+    never changes. With a 2 ms budget every wait on such a flag gives up, records the peer-timeout status (code 7, detail = the rank
     that did not answer) and the call returns; reading the status clears it. All tokens are routed to experts of rank 0,
     so the output is still the oracle's. After the test writes the missing flags itself the same call passes cleanly."""
     import ctypes
@@ -318,8 +318,8 @@ def test_peer_wait_runs_out_and_the_library_stays_usable(dg):
         assert _lib.device_status()[0] == 0, 'reading the status block clears it'
         assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
         # play the missing rank: its flags, far ahead of any epoch this test reaches
-        flags = view('flags', 4 * 8 * 4, torch.int32).view(4, 8)
-        flags[:3, 1] = 1 << 20
+        flags = view('flags', 13 * 8 * 4, torch.int32).view(13, 8)
+        flags[:9, 1] = 1 << 20
         torch.cuda.synchronize()
         y = call()
         assert _lib.device_status()[0] == 0
