@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument('--tokens', type=int, default=0, help='override tokens per rank (profiling small cases only)')
     ap.add_argument('--experts', type=int, default=0, help='override the expert count (profiling small cases only)')
     ap.add_argument('--skip-cpu-baseline', action='store_true')
+    ap.add_argument('--guest-experts', type=int, default=4,
+                    help='expert-parallel runs: guest expert slots per rank for the hot-expert row spill (0 = every expert\'s '
+                         'rows stay on its owner)')
     ap.add_argument('--skip-other-configs', action='store_true',
                     help='N = 1 only: leave out the extra timings (8192-token base, BASELINE configs 1, 2 and 4) after the headline line')
     ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
@@ -450,10 +453,12 @@ def run_family_workload(args):
     }), flush=True)
 
 
-def ep_parity_check(dg, _lib, rank, world):
+def ep_parity_check(dg, _lib, rank, world, guests):
     """Correctness of the expert-parallel path at this world size, run after the timed regions: one small layer on every
     rank (256 tokens per rank, hidden 512, intermediate 256, 8 experts per rank, top-4, 15 % masked slots, one shared
-    expert), all ranks' outputs and dispatch plans gathered to rank 0 and compared with the CPU oracle (checker only).
+    expert, routing biased towards two experts of rank 0 so that, with `guests` guest slots per rank, rows of hot experts
+    spill to other ranks), all ranks' outputs and dispatch plans gathered to rank 0 and compared with the CPU oracle
+    (checker only).
     The check mirrors the reference's fused-against-baseline comparison (tests/test_mega_moe.py:316-329).
     Returns {'calc_diff_max', 'plan_bit_exact', 'ranks', 'ok'} on rank 0, None elsewhere."""
     import torch
@@ -467,7 +472,9 @@ def ep_parity_check(dg, _lib, rank, world):
         from oracle import quant
         g = torch.Generator().manual_seed(9100 + r)
         x = torch.randn(tokens, hidden, generator=g).bfloat16()
-        idx, w = omoe.route_sigmoid_topk(torch.randn(tokens, experts, generator=g), topk)
+        logits = torch.randn(tokens, experts, generator=g)
+        logits[:, :2] += 2.0
+        idx, w = omoe.route_sigmoid_topk(logits, topk)
         mask = torch.rand(idx.shape, generator=g) < 0.15
         idx, w = idx.masked_fill(mask, -1), w.masked_fill(mask, 0.0)
         x_q, x_sf = quant.quantize_fp8_per_token(x, 32)
@@ -492,6 +499,8 @@ def ep_parity_check(dg, _lib, rank, world):
     l1_sf = dg.transform_sf_into_required_layout(wt['l1_sf'][mine].cuda(), 2 * inter, hidden, (1, 32), per_rank)
     l2_sf = dg.transform_sf_into_required_layout(wt['l2_sf'][mine].cuda(), hidden, inter, (1, 32), per_rank)
     l1, l2 = dg.transform_weights_for_mega_moe((wt['l1_q'][mine].cuda(), l1_sf), (wt['l2_q'][mine].cuda(), l2_sf))
+    if guests > 0:
+        l1, l2 = dg.share_weights_for_mega_moe(dist.group.WORLD, l1, l2, num_guest_experts=guests)
     sl1, sl2 = dg.transform_weights_for_mega_moe(
         (wt['s1_q'].cuda(), dg.transform_sf_into_required_layout(wt['s1_sf'].cuda(), 2 * inter, hidden, (1, 32))),
         (wt['s2_q'].cuda(), dg.transform_sf_into_required_layout(wt['s2_sf'].cuda(), hidden, inter, (1, 32))))
@@ -503,8 +512,10 @@ def ep_parity_check(dg, _lib, rank, world):
     dg.fp8_fp4_mega_moe(y, l1, l2, buf, shared_l1_weights=sl1, shared_l2_weights=sl2)
     status = _lib.device_status(raise_on_error=False)
     lay = buf.layout
+    slots = per_rank + guests
     plan = torch.cat([buf.buffer[lay[k]:lay[k] + n * 4].view(torch.int32) for k, n in
-                      (('expert_start', per_rank), ('expert_end', per_rank), ('dest_row', tokens * topk))])
+                      (('expert_start', slots), ('expert_end', slots), ('dest_row', tokens * topk), ('my_dest', experts),
+                       ('my_slot', experts), ('guest_expert', guests))])
     ys = [torch.empty_like(y) for _ in range(world)]
     plans = [torch.empty_like(plan) for _ in range(world)]
     codes = [torch.zeros(1, dtype=torch.int32, device='cuda') for _ in range(world)]
@@ -516,7 +527,7 @@ def ep_parity_check(dg, _lib, rank, world):
     from oracle import moe as omoe
     cases = [inputs_of(r) for r in range(world)]
     all_counts = torch.stack([omoe.ep_counts(cs['topk_idx'], experts) for cs in cases])
-    diff_max, plan_ok = 0.0, True
+    diff_max, plan_ok, spilled = 0.0, True, 0
     for r in range(world):
         cs = cases[r]
         shared = omoe.shared_expert_rows(cs['x_q'], cs['x_sf'], wt['s1_q'], wt['s1_sf'], wt['s2_q'], wt['s2_sf'])
@@ -525,13 +536,19 @@ def ep_parity_check(dg, _lib, rank, world):
         got = ys[r].cpu()
         d = float(quant.calc_diff(got, want)) if not torch.isnan(got.float()).any() else float('inf')
         diff_max = max(diff_max, d)
-        my_base, want_start, want_end = omoe.ep_plan(all_counts, r, 128)
         p = plans[r].cpu().long()
-        plan_ok = plan_ok and torch.equal(p[:per_rank], want_start) and torch.equal(p[per_rank:2 * per_rank], want_end) and \
-            torch.equal(p[2 * per_rank:], omoe.ep_dest_rows(cs['topk_idx'], my_base, experts).long())
+        if guests > 0:
+            my_base, my_dest, my_slot, want_start, want_end, guest = omoe.ep_plan_with_spill(all_counts, r, 128, guests)
+            spilled += int((guest >= 0).sum())
+            want_plan = torch.cat([want_start, want_end, omoe.ep_dest_rows(cs['topk_idx'], my_base, experts).long(), my_dest, my_slot, guest])
+        else:
+            my_base, want_start, want_end = omoe.ep_plan(all_counts, r, 128)
+            want_plan = torch.cat([want_start, want_end, omoe.ep_dest_rows(cs['topk_idx'], my_base, experts).long(), p[2 * slots + tokens * topk:]])
+        plan_ok = plan_ok and torch.equal(p, want_plan)
     status_ok = all(int(cd) == 0 for cd in codes)
     return {'calc_diff_max': diff_max, 'plan_bit_exact': bool(plan_ok), 'device_status_ok': status_ok, 'ranks': world,
-            'tolerance': 2e-3, 'ok': bool(plan_ok and status_ok and diff_max <= 2e-3),
+            'tolerance': 2e-3, 'ok': bool(plan_ok and status_ok and diff_max <= 2e-3), 'guest_slots_per_rank': guests,
+            'experts_spilled': spilled,
             'case': f'{tokens} tokens/rank, hidden {hidden}, inter {inter}, {experts} experts, top-{topk}, 15% masked, 1 shared expert'}
 
 
@@ -563,6 +580,10 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         # calibrated, fixed scales (equal on every rank): inputs ~N(0, 1) stay below 8; post-SwiGLU values below 64
         x_scale = torch.tensor(8.0 / (6 * 448), device='cuda')
         act_scale = torch.tensor(64.0 / (6 * 448), device='cuda')
+    guests = args.guest_experts if world > 1 and not nvfp4 else 0
+    if guests > 0:
+        # hot experts may spill rows to other ranks: the weights move into symmetric memory with room for guest experts
+        l1, l2 = dg.share_weights_for_mega_moe(dist.group.WORLD, l1, l2, num_guest_experts=guests)
     buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD if world > 1 else None, e, t, k, h, i, mma_type=cfg.get('mma', 'fp8xfp4'))
     if world > 1:
         # expert popularity ~ Zipf(s = 1): rank r of a seeded random permutation of the experts has weight 1 / (r + 1)
@@ -576,7 +597,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     logits = logits_host.cuda()
     y = torch.empty((t, h), dtype=torch.bfloat16, device='cuda')
     lib = _lib.lib()
-    kernels_per_step = kernels_of_one_step(nvfp4, world, cfg['local_experts'])
+    kernels_per_step = kernels_of_one_step(nvfp4, world, cfg['local_experts'], guests)
 
     def step(events=None, x_in=None, logits_in=None, y_out=None):
         x_in, logits_in, y_out = (x if x_in is None else x_in), (logits if logits_in is None else logits_in), (y if y_out is None else y_out)
@@ -664,10 +685,16 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
 
     # ---- algorithmic work of this batch, per rank
     lay = buf.layout
-    ends = buf.buffer[lay['expert_end']:lay['expert_end'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
-    starts = buf.buffer[lay['expert_start']:lay['expert_start'] + cfg['local_experts'] * 4].view(torch.int32).cpu()
+    slots = cfg['local_experts'] + guests  # guest slots follow the rank's own experts
+    ends = buf.buffer[lay['expert_end']:lay['expert_end'] + slots * 4].view(torch.int32).cpu()
+    starts = buf.buffer[lay['expert_start']:lay['expert_start'] + slots * 4].view(torch.int32).cpu()
     rows = int((ends - starts).sum())
     touched = int(((ends - starts) > 0).sum())
+    rows_before_spill = spilled_experts = None
+    if guests > 0:
+        rows_before_spill = buf.buffer[lay['rank_rows']:lay['rank_rows'] + world * 4].view(torch.int32).cpu().tolist()
+        hosted = buf.buffer[lay['guest_expert']:lay['guest_expert'] + guests * 4].view(torch.int32).cpu()
+        spilled_experts = int((hosted >= 0).sum())
     if nvfp4:
         l1_bytes = touched * (2 * i * h // 2 + 2 * i * h // 16) + rows * (h // 2 + h // 16) + rows * (i // 2 + i // 16)
         l2_bytes = touched * (h * i // 2 + h * i // 16) + rows * (i // 2 + i // 16) + rows * h * 2
@@ -676,7 +703,8 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
     # every rank's own numbers travel to rank 0: the step time is the maximum over ranks, everything that explains it
     # (stage times, bytes, flops) is taken from ONE rank, the one with the most routed rows
-    mine = torch.tensor([ms_per_step, e2e_ms] + stage_ms + [rows, touched, l1_bytes, l2_bytes], dtype=torch.float64, device='cuda')
+    mine = torch.tensor([ms_per_step, e2e_ms] + stage_ms + [rows, touched, l1_bytes, l2_bytes, spilled_experts or 0],
+                        dtype=torch.float64, device='cuda')
     per_rank = [torch.empty_like(mine) for _ in range(world)]
     if world > 1:
         dist.all_gather(per_rank, mine)
@@ -741,6 +769,14 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         'routed_rows': rows_hot,
         'load_imbalance_max_over_mean': rows_hot / (rows_all / world) if rows_all > 0 else None,
     }
+    if world > 1:
+        # hot-expert row spill: rows per rank as routed (every expert on its owner) and as computed (above)
+        line['hot_expert_spill'] = {
+            'guest_slots_per_rank': guests,
+            'guest_slots_used': int(table[:, 11].sum()),
+            'load_imbalance_as_routed': (max(rows_before_spill) / (sum(rows_before_spill) / world)) if rows_before_spill else
+            line['load_imbalance_max_over_mean'],
+        }
     if with_e2e:
         line['e2e'] = {'value': t * world / (e2e_ms * 1e-3), 'unit': 'tokens/s', 'ms_per_step': e2e_ms,
                        'h2d_bytes_per_step': x_host.numel() * 2 + logits_host.numel() * 4, 'd2h_bytes_per_step': y_host.numel() * 2}
@@ -762,16 +798,17 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     return line, (l1, l2)
 
 
-def kernels_of_one_step(nvfp4, world, local_experts):
+def kernels_of_one_step(nvfp4, world, local_experts, guests=0):
     """Launches of this library's kernels in one pass of the layer (memsets are not kernels of ours). FP8 layer on one
     rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the two tile orientations
     (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather. Expert parallel, P =
     min(4, local experts) phases: router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
-    per phase flag + scale reorder + L1 + L2 + flag, per phase flag + combine."""
+    per phase flag + scale reorder + L1 + L2 + flag, per phase flag + combine; with guest experts one more launch fetches
+    their weights and the guest slots count as experts."""
     if world == 1:
         return 9 if nvfp4 else 11
-    phases = min(4, local_experts)
-    return 7 + 2 * phases + 5 * phases + 2 * phases
+    phases = min(4, local_experts + guests)
+    return 7 + 2 * phases + 5 * phases + 2 * phases + (1 if guests else 0)
 
 
 L1_STAGE_KERNELS = ('gate/up GEMM + SwiGLU + FP8 requant (dgb200_grouped_gemm_kernel + dgb200_swap_gemm_kernel + '
@@ -786,7 +823,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     headline = world == 1 and cfg.get('mma') != 'nvfp4xnvfp4' and not args.tokens and not args.experts
     failed = False
     if world > 1:
-        parity = ep_parity_check(dg, _lib, rank, world)
+        parity = ep_parity_check(dg, _lib, rank, world, args.guest_experts if cfg.get('mma') != 'nvfp4xnvfp4' else 0)
         if rank == 0:
             line['ep_parity'] = parity
             failed = not parity['ok']

@@ -43,6 +43,7 @@ from .mega import (  # noqa: F401
     get_token_alignment_for_mega_moe,
     nvfp4_mega_moe,
     route_sigmoid_topk,
+    share_weights_for_mega_moe,
     transform_weights_for_mega_moe,
 )
 from .nvfp4 import (  # noqa: F401

@@ -84,7 +84,8 @@ class MegaMoeArgs(ctypes.Structure):
         [('x_bf16_row_stride', ctypes.c_int64), ('shared_intermediate_hidden', ctypes.c_int32)] + \
         [(n, ctypes.c_int32) for n in ('rank', 'num_ranks', 'num_tokens', 'num_max_tokens_per_rank', 'num_experts', 'num_topk',
                                        'hidden', 'intermediate_hidden')] + \
-        [('activation_clamp', ctypes.c_float), ('fast_math', ctypes.c_int32)]
+        [('activation_clamp', ctypes.c_float), ('fast_math', ctypes.c_int32), ('num_guest_experts', ctypes.c_int32)] + \
+        [(n, ctypes.c_void_p) for n in ('peer_l1_w', 'peer_l1_w_sf', 'peer_l2_w', 'peer_l2_w_sf')]
 
 
 def exported_symbols():

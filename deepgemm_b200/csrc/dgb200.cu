@@ -400,6 +400,9 @@ struct MegaLayout {
     long long chunk_hist, expert_start, expert_end, total_rows, dest_row;  // dispatch plan
     long long src_of_row, row_weight;
     long long all_counts, my_base, flags;  // expert-parallel exchange: counts of every rank, this rank's bases, barrier flags
+    // hot-expert row spill (expert parallel): computing rank and expert slot of this rank's entries per expert, the
+    // experts this rank hosts in its guest slots, every rank's rows before / after the spill
+    long long my_dest, my_slot, guest_expert, rank_rows;
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
     long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
@@ -411,6 +414,7 @@ struct MegaLayout {
     long long total;
     long long max_rows;  // capacity of the expert-sorted buffers (rows), a multiple of 128
     int num_chunks, num_local_experts;
+    int num_slots;  // expert segments the plan arrays hold: the local experts plus, expert parallel, kMaxGuestExperts guest slots
 };
 
 // Quantisation of the layer: the FP8 x MXFP4 path needs nothing beyond the tensors; the NVFP4 path carries the
@@ -432,6 +436,11 @@ struct LayerQuant {
     const void* shared_l2_w = nullptr;
     const void* shared_l2_w_sf = nullptr;
     int shared_inter = 0;
+    // expert parallel, FP8 kind only: hot-expert row spill. guest_slots > 0: the four weight tensors of every rank have
+    // room for that many guest experts after the rank's own and peer_w[i][r] is the address of tensor i (gate/up weights,
+    // their scales, down weights, their scales) on rank r as mapped into this process.
+    int guest_slots = 0;
+    const uint64_t* peer_w[4] = {nullptr, nullptr, nullptr, nullptr};
 };
 
 // Bytes of one quantised activation row of `width` elements, and packed scale ints (4 scale bytes each) per row.
@@ -450,7 +459,8 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.num_local_experts = num_experts / num_ranks;
     const long long active_topk = std::min(topk, l.num_local_experts);
     const long long routed = static_cast<long long>(max_tokens) * num_ranks * active_topk;
-    l.max_rows = (routed + static_cast<long long>(l.num_local_experts) * kSegmentAlignment + 127) / 128 * 128;
+    l.num_slots = l.num_local_experts + (num_ranks > 1 ? kMaxGuestExperts : 0);
+    l.max_rows = (routed + static_cast<long long>(l.num_slots) * kSegmentAlignment + 127) / 128 * 128;
     l.num_chunks = static_cast<int>((static_cast<long long>(max_tokens) * topk + kPlanChunk - 1) / kPlanChunk);
     long long off = 0;
     auto take = [&off](long long bytes) {
@@ -466,8 +476,12 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.all_counts = take(static_cast<long long>(num_ranks) * num_experts * 4);
     l.my_base = take(num_experts * 4ll);
     l.flags = take(kEpFlagRows * kMaxEpRanks * 4);
-    l.expert_start = take(l.num_local_experts * 4ll);
-    l.expert_end = take(l.num_local_experts * 4ll);
+    l.expert_start = take(l.num_slots * 4ll);
+    l.expert_end = take(l.num_slots * 4ll);
+    l.my_dest = take(num_experts * 4ll);
+    l.my_slot = take(num_experts * 4ll);
+    l.guest_expert = take(kMaxGuestExperts * 4);
+    l.rank_rows = take(2 * kMaxEpRanks * 4);
     l.total_rows = take(16);
     l.dest_row = take(static_cast<long long>(max_tokens) * topk * 4);
     l.src_of_row = take(l.max_rows * 4);
@@ -478,7 +492,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.l2_sf = take(l.max_rows * sf_ints_per_row(kind, inter) * 4);
     l.l2_out = take(l.max_rows * hidden * 2);
     l.l1_tmp = kind == kKindFp8Fp4 ? take(l.max_rows * inter * 4) : 0;
-    l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_local_experts) * 4) : 0;
+    l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_slots) * 4) : 0;
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.combine_partial = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * hidden * 4) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
@@ -612,8 +626,8 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
                     const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
                     cudaStream_t stream, int stage_event_base, long long expected_rows_per_expert, int group_begin = 0,
                     int group_end = 0) {
-    const int E = l.num_local_experts;
-    // [group_begin, group_end): the local experts this call computes ({0, 0} = all of them)
+    const int E = l.num_local_experts + quant.guest_slots;  // guest slots follow the rank's own experts, in the plan and in the weights
+    // [group_begin, group_end): the expert slots this call computes ({0, 0} = all of them)
     const int first_expert = (group_begin == 0 && group_end == 0) ? 0 : group_begin;
     const int num_call_experts = (group_begin == 0 && group_end == 0) ? E : group_end - group_begin;
     const int* expert_end = reinterpret_cast<const int*>(base + l.expert_end);
@@ -879,7 +893,35 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     const bool with_shared = quant.shared_inter > 0;
     const int sf_per_row = sf_ints_per_row(quant.kind, hidden);
     const bool fused_mlp = quant.kind == kKindFp8Fp4 && mlp_kernel_choice() != 0;
-    const int phases = fused_mlp ? 1 : std::min(kMaxEpPhases, E);
+    // hot-expert row spill: V = own experts + guest slots; the plan decides which rows of which experts move
+    const int G = quant.guest_slots;
+    const int V = E + G;
+    const bool spill = G > 0;
+    GuestWeightTables guest_tables{};
+    if (spill) {
+        DGB_REQUIRE(quant.kind == kKindFp8Fp4 && !fused_mlp, "guest experts need the FP8 x MXFP4 layer with its separate GEMM kernels");
+        DGB_REQUIRE(G <= kMaxGuestExperts && V <= kMaxSpillSlots - 1, "at most %d guest experts and %d expert slots per rank",
+                    kMaxGuestExperts, kMaxSpillSlots - 1);
+        DGB_REQUIRE(static_cast<long long>(num_ranks) * num_experts * 6 <= 30 * 1024, "too many experts x ranks for the spill plan's tables");
+        const void* local_w[4] = {l1_w, l1_w_sf, l2_w, l2_w_sf};
+        const long long bytes[4] = {2ll * intermediate_hidden * hidden / 2, 2ll * intermediate_hidden * (hidden / 128) * 4,
+                                    static_cast<long long>(hidden) * intermediate_hidden / 2,
+                                    static_cast<long long>(hidden) * (intermediate_hidden / 128) * 4};
+        for (int i = 0; i < 4; ++i) {
+            DGB_REQUIRE(quant.peer_w[i] != nullptr, "guest experts need the peer addresses of all four weight tensors");
+            for (int r = 0; r < num_ranks; ++r) {
+                DGB_REQUIRE(quant.peer_w[i][r] != 0 && quant.peer_w[i][r] % 16 == 0, "weight tensor %d of rank %d is not mapped", i, r);
+                guest_tables.peer[i][r] = quant.peer_w[i][r];
+            }
+            DGB_REQUIRE(quant.peer_w[i][rank] == reinterpret_cast<uintptr_t>(local_w[i]),
+                        "the peer address table does not name this rank's weight tensor %d", i);
+            guest_tables.local[i] = reinterpret_cast<uintptr_t>(local_w[i]);
+            guest_tables.bytes[i] = bytes[i];
+        }
+    }
+    const int* my_dest = spill ? reinterpret_cast<const int*>(base + l.my_dest) : nullptr;
+    const int* my_slot = spill ? reinterpret_cast<const int*>(base + l.my_slot) : nullptr;
+    const int phases = fused_mlp ? 1 : std::min(kMaxEpPhases, V);
     int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
     const int* expert_start = reinterpret_cast<const int*>(base + l.expert_start);
@@ -890,7 +932,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     auto flag = [&](int row, int do_signal, int do_wait) {
         dgb200_ep_flag_kernel<<<1, 32, 0, stream>>>(peers, l.flags, row, rank, num_ranks, do_signal, do_wait, peer_budget);
     };
-    auto phase_begin = [&](int q) { return static_cast<int>(static_cast<long long>(q) * E / phases); };
+    auto phase_begin = [&](int q) { return static_cast<int>(static_cast<long long>(q) * V / phases); };
     int rc = 0;
     if ((rc = record_stage(0, stream))) return rc;
 
@@ -899,11 +941,19 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     dgb200_ep_share_counts_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, num_experts, rank, num_ranks, peers, l.all_counts);
     flag(0, 1, 1);
     // the same global plan on every rank
-    dgb200_ep_plan_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
-                                                   kSegmentAlignment, reinterpret_cast<int*>(base + l.my_base),
-                                                   reinterpret_cast<int*>(base + l.expert_start),
-                                                   reinterpret_cast<int*>(base + l.expert_end),
-                                                   reinterpret_cast<int*>(base + l.total_rows), stats);
+    if (spill)
+        dgb200_ep_spill_plan_kernel<<<1, 1024, static_cast<size_t>(num_ranks) * num_experts * 6, stream>>>(
+            reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank, kSegmentAlignment, G,
+            reinterpret_cast<int*>(base + l.my_base), reinterpret_cast<int*>(base + l.my_dest), reinterpret_cast<int*>(base + l.my_slot),
+            reinterpret_cast<int*>(base + l.expert_start), reinterpret_cast<int*>(base + l.expert_end),
+            reinterpret_cast<int*>(base + l.total_rows), reinterpret_cast<int*>(base + l.guest_expert),
+            reinterpret_cast<int*>(base + l.rank_rows), stats);
+    else
+        dgb200_ep_plan_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
+                                                       kSegmentAlignment, reinterpret_cast<int*>(base + l.my_base),
+                                                       reinterpret_cast<int*>(base + l.expert_start),
+                                                       reinterpret_cast<int*>(base + l.expert_end),
+                                                       reinterpret_cast<int*>(base + l.total_rows), stats);
     if (entries > 0)
         dgb200_ep_assign_kernel<<<chunks, kPlanChunk, 32 * num_experts, stream>>>(topk_idx, entries, num_experts, chunk_hist,
                                                                               reinterpret_cast<const int*>(base + l.my_base), dest_row);
@@ -922,10 +972,15 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
             dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
                 base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
                 static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, E, rank, entries_per_rank, peers, l.l1_acts,
-                l.l1_sf_stage, 0, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1));
+                l.l1_sf_stage, 0, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1), my_dest, my_slot);
         flag(1 + q, 1, 0);
     }
     DGB_CUDA(cudaGetLastError());
+    if (spill) {
+        // the weights of the experts this rank hosts as a guest, from their owners (while the other ranks' rows arrive)
+        dgb200_ep_fetch_guest_weights_kernel<<<dim3(74, G), 256, 0, stream>>>(reinterpret_cast<const int*>(base + l.guest_expert), E, guest_tables);
+        DGB_CUDA(cudaGetLastError());
+    }
     if ((rc = record_stage(2, stream))) return rc;
 
     // GEMMs, phase by phase, each as soon as every rank's rows for the phase have landed
@@ -961,7 +1016,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                 peers, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
                 with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
                 reinterpret_cast<float*>(base + l.combine_partial), static_cast<__nv_bfloat16*>(y), phase_begin(q), phase_begin(q + 1),
-                q == 0 ? 1 : 0, q == phases - 1 ? 1 : 0);
+                q == 0 ? 1 : 0, q == phases - 1 ? 1 : 0, my_dest, my_slot);
     }
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
@@ -1686,10 +1741,11 @@ int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num
     const int rc = make_mega_layout(kKindFp8Fp4, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
                                     intermediate_hidden, &l, shared_intermediate_hidden);
     if (rc) return rc;
-    const long long fields[21] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+    const long long fields[26] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
                                   l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight,
-                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out, l.flags};
-    for (int i = 0; i < 21; ++i) out[i] = fields[i];
+                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out, l.flags,
+                                  l.my_base, l.my_dest, l.my_slot, l.guest_expert, l.rank_rows};
+    for (int i = 0; i < 26; ++i) out[i] = fields[i];
     return 0;
 }
 
@@ -1710,6 +1766,13 @@ int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* a, void* stream) {
         quant.shared_l2_w = a->shared_l2_w;
         quant.shared_l2_w_sf = a->shared_l2_w_sf;
         quant.shared_inter = a->shared_intermediate_hidden;
+    }
+    if (a->num_guest_experts > 0 && a->num_ranks > 1) {
+        quant.guest_slots = a->num_guest_experts;
+        quant.peer_w[0] = a->peer_l1_w;
+        quant.peer_w[1] = a->peer_l1_w_sf;
+        quant.peer_w[2] = a->peer_l2_w;
+        quant.peer_w[3] = a->peer_l2_w_sf;
     }
     if (a->logits != nullptr && a->num_tokens > 0) {
         MegaLayout l;
@@ -1756,10 +1819,11 @@ int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t n
     const int rc = make_mega_layout(kKindBf16, num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
                                     intermediate_hidden, &l, shared_intermediate_hidden);
     if (rc) return rc;
-    const long long fields[21] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
+    const long long fields[26] = {l.total, l.x, l.x_sf, l.topk_idx, l.topk_weights, l.l1_acts, l.l1_sf, l.l2_acts, l.l2_sf,
                                   l.max_rows, l.dest_row, l.src_of_row, l.expert_start, l.expert_end, l.l2_out, l.row_weight,
-                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out, l.flags};
-    for (int i = 0; i < 21; ++i) out[i] = fields[i];
+                                  l.shared_x_sf, l.shared_l2_acts, l.shared_l2_sf, l.shared_out, l.flags,
+                                  l.my_base, l.my_dest, l.my_slot, l.guest_expert, l.rank_rows};
+    for (int i = 0; i < 26; ++i) out[i] = fields[i];
     return 0;
 }
 

@@ -268,7 +268,8 @@ __global__ void __launch_bounds__(128)
 dgb200_moe_combine_phase_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
                                 const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
                                 const __nv_bfloat16* __restrict__ shared_rows, float* __restrict__ partial,
-                                __nv_bfloat16* __restrict__ y, int local_expert_begin, int local_expert_end, int first, int last) {
+                                __nv_bfloat16* __restrict__ y, int local_expert_begin, int local_expert_end, int first, int last,
+                                const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
     const int t = blockIdx.x;
     extern __shared__ unsigned long long slot_rows[];  // address of each slot's row of this phase, 0 = skip
     __shared__ int any;
@@ -279,7 +280,9 @@ dgb200_moe_combine_phase_kernel(const PeerTable peers, long long rows_offset, co
         unsigned long long addr = 0;
         if (d >= 0) {
             const int e = static_cast<int>(topk_idx[static_cast<long long>(t) * topk + threadIdx.x]);
-            const int owner = e / experts_per_rank, local_expert = e - owner * experts_per_rank;
+            // computing rank and expert slot: the owner and the expert's index there, or what the spill plan says
+            const int owner = my_dest != nullptr ? my_dest[e] : e / experts_per_rank;
+            const int local_expert = my_slot != nullptr ? my_slot[e] : e - owner * experts_per_rank;
             if (local_expert >= local_expert_begin && local_expert < local_expert_end) {
                 addr = peers.p[owner] + rows_offset + static_cast<unsigned long long>(d) * hidden * 2;
                 any = 1;
@@ -483,6 +486,199 @@ dgb200_ep_plan_kernel(const int* __restrict__ all_counts, int num_experts, int n
     }
 }
 
+// ---- hot-expert row spill -------------------------------------------------------------------------------------------------
+// With skewed routing the rank that owns the popular experts receives several times the mean number of rows and every
+// other rank waits for it. Each rank therefore keeps kMaxGuestExperts spare expert slots after its own experts, and the
+// plan may move the rows that some source ranks route to a hot expert onto a less loaded rank, which computes them in a
+// guest slot with a copy of the expert's weights fetched from the owner (dgb200_ep_fetch_guest_weights_kernel). A row's
+// arithmetic does not depend on the rank that computes it, so the layer's output is the same bits as without the spill.
+// No reference counterpart: the reference keeps every expert's rows on its owner (sm100_fp8_fp4_mega_moe.cuh:372,389).
+constexpr int kMaxGuestExperts = 8;
+constexpr int kMaxSpillSlots = 256;  // expert slots per rank (own + guest) the plan's tables index with one byte
+
+// One CTA. The spill table and this rank's plan under it, derived identically on every rank from
+// all_counts[source rank][expert] with integer arithmetic only:
+//   load[r] = rows of the experts r owns; repeat at most ranks * guest_slots times:
+//     hi = the most loaded rank, lo = the least loaded rank other than hi with a free guest slot (ties: lower rank);
+//     gap = load[hi] - load[lo]; stop when gap < max(256, total rows / (32 * ranks));
+//     e = the expert owned by hi with the most rows still on hi (ties: lower e); stop when it has none;
+//     walk the source ranks from the last to the first: the rows (s, e) still on hi move to lo while
+//     2 * moved + count[s][e] < gap; stop when nothing moved; lo hosts e in the guest slot it already has for e, else in
+//     its next free one.
+// Outputs: my_base / my_dest / my_slot [experts]: first row, computing rank and expert slot there of THIS rank's entries
+// for e; slot_start / slot_end [per_rank + guest_slots]: this rank's own segments (the psum layout its GEMMs walk), each
+// padded to `alignment`, rows inside a slot ordered by (source rank, entry); total_rows; guest_expert [guest_slots]:
+// the experts this rank hosts (-1 = unused); rank_rows [2][ranks]: every rank's rows before and after the spill.
+// Dynamic shared memory: the counts (ranks * experts ints) and the two byte tables (2 * ranks * experts bytes).
+__global__ void __launch_bounds__(1024)
+dgb200_ep_spill_plan_kernel(const int* __restrict__ all_counts, int num_experts, int num_ranks, int my_rank, int alignment,
+                            int guest_slots, int* __restrict__ my_base, int* __restrict__ my_dest, int* __restrict__ my_slot,
+                            int* __restrict__ slot_start, int* __restrict__ slot_end, int* __restrict__ total_rows,
+                            int* __restrict__ guest_expert, int* __restrict__ rank_rows, int* __restrict__ cumulative_stats) {
+    extern __shared__ int spill_smem[];
+    int* counts = spill_smem;                                                              // [ranks][experts]
+    unsigned char* dest = reinterpret_cast<unsigned char*>(counts + num_ranks * num_experts);  // [experts][ranks]
+    unsigned char* slot = dest + num_ranks * num_experts;                                  // [experts][ranks]
+    __shared__ int rows_of[kMaxEpRanks * kMaxSpillSlots];   // rows per (rank, slot), then the slot's first row
+    __shared__ int rows_cnt[kMaxEpRanks * kMaxSpillSlots];
+    __shared__ int load[kMaxEpRanks], used[kMaxEpRanks], guest[kMaxEpRanks][kMaxGuestExperts];
+    __shared__ int total_all;
+    const int per_rank = num_experts / num_ranks;
+    const int slots = per_rank + guest_slots;
+    const int tid = static_cast<int>(threadIdx.x), lane = tid & 31;
+
+    for (int i = tid; i < num_ranks * num_experts; i += blockDim.x) {
+        counts[i] = all_counts[i];
+        const int e = i / num_ranks, s = i - e * num_ranks;
+        dest[e * num_ranks + s] = static_cast<unsigned char>(e / per_rank);
+        slot[e * num_ranks + s] = static_cast<unsigned char>(e % per_rank);
+    }
+    if (tid < kMaxEpRanks) {
+        used[tid] = 0;
+        for (int g = 0; g < kMaxGuestExperts; ++g) guest[tid][g] = -1;
+    }
+    __syncthreads();
+    if (tid < num_ranks) {
+        int sum = 0;
+        for (int e = tid * per_rank; e < (tid + 1) * per_rank; ++e)
+            for (int s = 0; s < num_ranks; ++s) sum += counts[s * num_experts + e];
+        load[tid] = sum;
+        rank_rows[tid] = sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int sum = 0;
+        for (int r = 0; r < num_ranks; ++r) sum += load[r];
+        total_all = sum;
+    }
+    __syncthreads();
+
+    if (tid < 32 && guest_slots > 0) {  // the greedy moves, one warp
+        const int min_gap = max(256, total_all / (32 * num_ranks));
+        for (int iter = 0; iter < num_ranks * guest_slots; ++iter) {
+            int hi = 0, lo = -1;
+            for (int r = 1; r < num_ranks; ++r)
+                if (load[r] > load[hi]) hi = r;
+            for (int r = 0; r < num_ranks; ++r)
+                if (r != hi && used[r] < guest_slots && (lo < 0 || load[r] < load[lo])) lo = r;
+            if (lo < 0) break;
+            const int gap = load[hi] - load[lo];
+            if (gap < min_gap) break;
+            // the expert of hi with the most rows still on hi, ties to the lower expert
+            int best_rows = -1, best_e = 0x7fffffff;
+            for (int local = lane; local < per_rank; local += 32) {
+                const int e = hi * per_rank + local;
+                int v = 0;
+                for (int s = 0; s < num_ranks; ++s)
+                    if (dest[e * num_ranks + s] == hi) v += counts[s * num_experts + e];
+                if (v > best_rows) { best_rows = v; best_e = e; }
+            }
+            for (int off = 16; off > 0; off >>= 1) {
+                const int r2 = __shfl_xor_sync(0xffffffffu, best_rows, off), e2 = __shfl_xor_sync(0xffffffffu, best_e, off);
+                if (r2 > best_rows || (r2 == best_rows && e2 < best_e)) { best_rows = r2; best_e = e2; }
+            }
+            if (best_rows <= 0) break;
+            int moved = 0;
+            if (lane == 0) {
+                const int e = best_e;
+                int g = -1;
+                for (int i = 0; i < used[lo]; ++i)
+                    if (guest[lo][i] == e) g = i;
+                const bool hosted = g >= 0;
+                if (!hosted) g = used[lo];
+                for (int s = num_ranks - 1; s >= 0; --s) {
+                    const int c = counts[s * num_experts + e];
+                    if (c > 0 && dest[e * num_ranks + s] == hi && 2 * moved + c < gap) {
+                        dest[e * num_ranks + s] = static_cast<unsigned char>(lo);
+                        slot[e * num_ranks + s] = static_cast<unsigned char>(per_rank + g);
+                        moved += c;
+                    }
+                }
+                if (moved > 0) {
+                    if (!hosted) { guest[lo][g] = e; used[lo] += 1; }
+                    load[hi] -= moved;
+                    load[lo] += moved;
+                }
+            }
+            moved = __shfl_sync(0xffffffffu, moved, 0);
+            __syncwarp();
+            if (moved == 0) break;
+        }
+    }
+    __syncthreads();
+
+    // rows per (rank, slot), then each rank's segment starts
+    for (int i = tid; i < num_ranks * kMaxSpillSlots; i += blockDim.x) rows_cnt[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < num_ranks * num_experts; i += blockDim.x) {
+        const int e = i / num_ranks, s = i - e * num_ranks;
+        const int c = counts[s * num_experts + e];
+        if (c > 0) atomicAdd(&rows_cnt[dest[i] * kMaxSpillSlots + slot[i]], c);
+    }
+    __syncthreads();
+    if (tid < num_ranks) {
+        int cursor = 0;
+        for (int v = 0; v < slots; ++v) {
+            rows_of[tid * kMaxSpillSlots + v] = cursor;
+            cursor = (cursor + rows_cnt[tid * kMaxSpillSlots + v] + alignment - 1) / alignment * alignment;
+        }
+        rank_rows[num_ranks + tid] = load[tid];
+        if (tid == my_rank) total_rows[0] = cursor;
+    }
+    __syncthreads();
+    for (int e = tid; e < num_experts; e += blockDim.x) {
+        const int d = dest[e * num_ranks + my_rank], v = slot[e * num_ranks + my_rank];
+        int before = 0, total = 0;
+        for (int s = 0; s < num_ranks; ++s) {
+            const int c = counts[s * num_experts + e];
+            if (s < my_rank && dest[e * num_ranks + s] == d) before += c;
+            total += c;
+        }
+        my_base[e] = rows_of[d * kMaxSpillSlots + v] + before;
+        my_dest[e] = d;
+        my_slot[e] = v;
+        if (cumulative_stats != nullptr && e / per_rank == my_rank) cumulative_stats[e - my_rank * per_rank] += total;
+    }
+    for (int v = tid; v < slots; v += blockDim.x) {
+        slot_start[v] = rows_of[my_rank * kMaxSpillSlots + v];
+        slot_end[v] = rows_of[my_rank * kMaxSpillSlots + v] + rows_cnt[my_rank * kMaxSpillSlots + v];
+    }
+    if (tid < guest_slots) guest_expert[tid] = guest[my_rank][tid];
+}
+
+// Copies the weights of the experts this rank hosts in its guest slots from their owners: four tensors per expert
+// (gate/up weights, their scales, down weights, their scales), `bytes[i]` each, expert-major on every rank with the
+// guest slots after the rank's own experts. gridDim.y = guest slots; the CTAs of a row share the expert's bytes.
+struct GuestWeightTables {
+    unsigned long long peer[4][kMaxEpRanks];  // base address of tensor i on every rank, as mapped into this process
+    unsigned long long local[4];              // the same tensors of this rank
+    long long bytes[4];                       // bytes of one expert in tensor i (multiples of 16)
+};
+__global__ void __launch_bounds__(256)
+dgb200_ep_fetch_guest_weights_kernel(const int* __restrict__ guest_expert, int experts_per_rank, const GuestWeightTables t) {
+    const int e = guest_expert[blockIdx.y];
+    if (e < 0) return;
+    const int owner = e / experts_per_rank, local_expert = e - owner * experts_per_rank;
+    const long long slot_index = experts_per_rank + static_cast<long long>(blockIdx.y);
+#pragma unroll 1
+    for (int i = 0; i < 4; ++i) {
+        const uint4* from = reinterpret_cast<const uint4*>(t.peer[i][owner] + static_cast<unsigned long long>(local_expert * t.bytes[i]));
+        uint4* to = reinterpret_cast<uint4*>(t.local[i] + static_cast<unsigned long long>(slot_index * t.bytes[i]));
+        const long long vecs = t.bytes[i] / 16;
+        const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+        long long c = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+        for (; c + 3 * stride < vecs; c += 4 * stride) {  // four independent loads in flight per thread
+            const uint4 v0 = ld_global_nc_v4(from + c), v1 = ld_global_nc_v4(from + c + stride);
+            const uint4 v2 = ld_global_nc_v4(from + c + 2 * stride), v3 = ld_global_nc_v4(from + c + 3 * stride);
+            to[c] = v0;
+            to[c + stride] = v1;
+            to[c + 2 * stride] = v2;
+            to[c + 3 * stride] = v3;
+        }
+        for (; c < vecs; c += stride) to[c] = ld_global_nc_v4(from + c);
+    }
+}
+
 // dest_row[entry] = row on the owner rank (my_base[e] + stable rank of the entry among this rank's entries for e).
 __global__ void __launch_bounds__(kPlanChunk)
 dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries, int num_experts,
@@ -519,15 +715,19 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
                       const int* __restrict__ dest_row, int num_entries, int topk, int row_bytes, int sf_per_row,
                       int experts_per_rank, int my_rank, int entries_per_rank, const PeerTable peers,
                       long long acts_offset, long long sf_offset, long long sf_k_stride, long long weight_offset,
-                      long long src_offset, int local_expert_begin, int local_expert_end) {
+                      long long src_offset, int local_expert_begin, int local_expert_end,
+                      const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
     const int lane = threadIdx.x & 31;
     const int entry = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (entry >= num_entries) return;
     const int dest = dest_row[entry];
     if (dest < 0) return;
-    const int owner = static_cast<int>(topk_idx[entry]) / experts_per_rank;
-    // only the entries whose expert (numbered within its owner) lies in [begin, end): the layer pushes phase by phase
-    const int local_expert = static_cast<int>(topk_idx[entry]) - owner * experts_per_rank;
+    // the rank that computes this entry and the expert slot there: the expert's owner and its index among the owner's
+    // experts, unless the plan spilled the rows this rank routes to the expert (my_dest / my_slot, may be null)
+    const int expert = static_cast<int>(topk_idx[entry]);
+    const int owner = my_dest != nullptr ? my_dest[expert] : expert / experts_per_rank;
+    // only the entries whose slot lies in [begin, end): the layer pushes phase by phase
+    const int local_expert = my_slot != nullptr ? my_slot[expert] : expert - owner * experts_per_rank;
     if (local_expert < local_expert_begin || local_expert >= local_expert_end) return;
     const int token = entry / topk;
     const unsigned long long base = peers.p[owner];

@@ -37,7 +37,7 @@ _MMA_TYPES = ('fp8xfp4', 'nvfp4xnvfp4', 'bf16xbf16')
 
 def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
                    mma_type='fp8xfp4', shared_intermediate_hidden=0):
-    words = (ctypes.c_int64 * 21)()
+    words = (ctypes.c_int64 * 26)()
     if mma_type == 'fp8xfp4':
         _lib.check(_lib.lib().dgb200_get_symm_buffer_layout_for_mega_moe_ex(
             num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
@@ -52,7 +52,8 @@ def _buffer_layout(num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hi
             ctypes.cast(words, ctypes.c_void_p)))
     keys = ['total', 'x', 'x_sf', 'topk_idx', 'topk_weights', 'l1_acts', 'l1_sf', 'l2_acts', 'l2_sf', 'max_rows',
             'dest_row', 'src_of_row', 'expert_start', 'expert_end', 'l2_out', 'row_weight',
-            'shared_x_sf', 'shared_l2_acts', 'shared_l2_sf', 'shared_out', 'flags']
+            'shared_x_sf', 'shared_l2_acts', 'shared_l2_sf', 'shared_out', 'flags',
+            'my_base', 'my_dest', 'my_slot', 'guest_expert', 'rank_rows']
     return dict(zip(keys, list(words)))
 
 
@@ -197,6 +198,59 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     return (l1_w, l1_sf) + tuple(l1_weights[2:]), (l2_w, _sf_rows_to_cp_order(l2_weights[1])) + tuple(l2_weights[2:])
 
 
+MAX_GUEST_EXPERTS = 8
+
+
+class _SpillInfo:
+    """What the layer call needs to let hot experts spill rows to other ranks: the number of guest slots and, for each
+    of the four weight tensors, its address on every rank. Keeps the symmetric allocations alive."""
+
+    def __init__(self, num_guest_experts, peer_ptrs, keep):
+        self.num_guest_experts = num_guest_experts
+        self.peer_ptrs = peer_ptrs  # four lists of num_ranks addresses: l1_w, l1_w_sf, l2_w, l2_w_sf
+        self.keep = keep
+
+
+def share_weights_for_mega_moe(group, l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                               l2_weights: Tuple[torch.Tensor, torch.Tensor], num_guest_experts: int = 4):
+    """Expert-parallel runs with skewed routing: lets ranks compute rows of other ranks' hot experts (no reference
+    counterpart; the reference keeps every expert's rows on its owner, so its step time follows the most loaded rank).
+
+    Takes the FP8 x MXFP4 layer's routed weights as ``transform_weights_for_mega_moe`` returned them, moves them into
+    symmetric memory with room for ``num_guest_experts`` more experts behind the rank's own, and returns the same
+    ``(weights, scales)`` pairs (views of the first ``E_local`` experts). ``fp8_fp4_mega_moe`` recognises them: every call
+    then derives, from the exchanged per-expert counts, which rows of which hot experts move to less loaded ranks, and
+    those ranks fetch the experts' weights from the owners into their guest slots during the call. Outputs are the same
+    bits as without it. Collective: every rank of ``group`` must call it with the same ``num_guest_experts``."""
+    if group is None or group.size() == 1 or num_guest_experts <= 0:
+        return l1_weights, l2_weights
+    if num_guest_experts > MAX_GUEST_EXPERTS:
+        raise RuntimeError(f'at most {MAX_GUEST_EXPERTS} guest experts')
+    if len(l1_weights) != 2 or l1_weights[0].dtype != torch.int8:
+        raise RuntimeError('only the FP8 x MXFP4 layer (packed int8 weights + packed UE8M0 scales) can share its weights')
+    import torch.distributed._symmetric_memory as symm_mem
+    shared, ptrs, keep = [], [], []
+    for t in (l1_weights[0], l1_weights[1], l2_weights[0], l2_weights[1]):
+        experts = t.shape[0]
+        per_expert = t.stride(0) * t.element_size()  # bytes: both weights and MN-major packed scales are expert-major
+        if per_expert % 16 != 0 or t.storage_offset() != 0:
+            raise RuntimeError('weight tensors must start their storage and hold a multiple of 16 bytes per expert')
+        flat = symm_mem.empty((experts + num_guest_experts) * per_expert, dtype=torch.int8, device=t.device)
+        handle = symm_mem.rendezvous(flat, group=group)
+        flat.zero_()
+        view = flat[:experts * per_expert].view(t.dtype).as_strided(t.shape, t.stride())
+        view.copy_(t)
+        shared.append(view)
+        ptrs.append([int(p) for p in handle.buffer_ptrs])
+        keep.append((flat, handle))
+    info = _SpillInfo(num_guest_experts, ptrs, keep)
+    for view in shared:
+        view._dgb200_spill = info
+    torch.cuda.synchronize()
+    group.barrier()
+    return (shared[0], shared[1]), (shared[2], shared[3])
+
+
 def _check_weight(w, sf, num_groups, n, k, name, k_per_int=128):
     if not (w.is_cuda and w.dtype == torch.int8 and w.is_contiguous() and tuple(w.shape) == (num_groups, n, k // 2)):
         raise RuntimeError(f'{name} must be a contiguous CUDA int8 tensor of shape {(num_groups, n, k // 2)}')
@@ -241,6 +295,10 @@ def _run_layer(y, l1_weights, l2_weights, b, shared_l1_weights, shared_l2_weight
         raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_local_experts] tensor')
     ptrs = (ctypes.c_uint64 * len(b.handle.buffer_ptrs))(*[int(p) for p in b.handle.buffer_ptrs])
     p = lambda t: t.data_ptr() if t is not None else None
+    spill = getattr(l1_weights[0], '_dgb200_spill', None) if b.num_ranks > 1 else None
+    if spill is not None and any(getattr(t, '_dgb200_spill', None) is not spill for t in (l1_weights[1], l2_weights[0], l2_weights[1])):
+        raise RuntimeError('l1_weights and l2_weights must come from the same share_weights_for_mega_moe call')
+    peer_w = [(ctypes.c_uint64 * b.num_ranks)(*spill.peer_ptrs[i]) for i in range(4)] if spill is not None else [None] * 4
     args = _lib.MegaMoeArgs(
         struct_size=ctypes.sizeof(_lib.MegaMoeArgs), y=p(y), l1_w=p(l1_weights[0]), l1_w_sf=p(l1_weights[1]),
         l2_w=p(l2_weights[0]), l2_w_sf=p(l2_weights[1]),
@@ -251,7 +309,12 @@ def _run_layer(y, l1_weights, l2_weights, b, shared_l1_weights, shared_l2_weight
         shared_intermediate_hidden=shared_inter, rank=b.rank, num_ranks=b.num_ranks, num_tokens=y.size(0),
         num_max_tokens_per_rank=b.num_max_tokens_per_rank, num_experts=b.num_experts, num_topk=b.num_topk, hidden=b.hidden,
         intermediate_hidden=b.intermediate_hidden,
-        activation_clamp=float(activation_clamp) if activation_clamp is not None else 0.0, fast_math=int(fast_math))
+        activation_clamp=float(activation_clamp) if activation_clamp is not None else 0.0, fast_math=int(fast_math),
+        num_guest_experts=spill.num_guest_experts if spill is not None else 0,
+        peer_l1_w=ctypes.cast(peer_w[0], ctypes.c_void_p) if spill is not None else None,
+        peer_l1_w_sf=ctypes.cast(peer_w[1], ctypes.c_void_p) if spill is not None else None,
+        peer_l2_w=ctypes.cast(peer_w[2], ctypes.c_void_p) if spill is not None else None,
+        peer_l2_w_sf=ctypes.cast(peer_w[3], ctypes.c_void_p) if spill is not None else None)
     with torch.cuda.device(y.device):
         _lib.check(_lib.lib().dgb200_fp8_fp4_mega_moe_ex(ctypes.byref(args), _lib.current_stream_ptr()))
 

@@ -315,14 +315,33 @@ typedef struct dgb200_mega_moe_args {
     int32_t rank, num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden;
     float activation_clamp;
     int32_t fast_math;
+    /* Hot-expert row spill, expert-parallel runs only (num_guest_experts = 0: every expert's rows stay on its owner).
+     * With skewed routing the rank that owns the popular experts receives several times the mean number of rows and
+     * all ranks wait for it. With num_guest_experts = G > 0 (at most 8) every rank derives, from the exchanged
+     * per-expert counts, the same plan that moves the rows some source ranks route to a hot expert onto a less loaded
+     * rank; that rank computes them in one of its G guest slots with a copy of the expert's weights, which it fetches
+     * from the owner during the call. Outputs are the same bits as without the spill. Requirements: l1_w, l1_w_sf,
+     * l2_w, l2_w_sf of EVERY rank hold E_local + G experts (the guest slots, after the rank's own experts, are scratch
+     * of the library) and are mapped into every process; peer_l1_w[r] ... peer_l2_w_sf[r] are the addresses of rank
+     * r's four tensors in this process (host arrays of num_ranks entries; entry `rank` must equal l1_w ... l2_w_sf).
+     * Every rank must pass the same G. No reference counterpart (the reference keeps an expert's rows on its owner). */
+    int32_t num_guest_experts;
+    const uint64_t* peer_l1_w;
+    const uint64_t* peer_l1_w_sf;
+    const uint64_t* peer_l2_w;
+    const uint64_t* peer_l2_w_sf;
 } dgb200_mega_moe_args;
 int dgb200_fp8_fp4_mega_moe_ex(const dgb200_mega_moe_args* args, void* stream);
 
-/* dgb200_get_symm_buffer_layout_for_mega_moe with room for shared experts: out[21] = the 16 words above, then the byte
+/* dgb200_get_symm_buffer_layout_for_mega_moe with room for shared experts: out[26] = the 16 words above, then the byte
  * offsets of the shared experts' private regions (x scales in GEMM order, activations, their scales, output rows) and,
  * last, of the cross-rank flag words (int32 [13][8]: rows 0..8 = flag rows, slot s = the epoch rank s last signalled:
  * row 0 counts published, rows 1..4 dispatch phases, rows 5..8 output phases; rows 9..12 = this rank's own counts of
- * signals sent and waits completed per flag row). The whole buffer must be zeroed once after it is allocated, on every
+ * signals sent and waits completed per flag row), then five more private regions of the expert-parallel plan:
+ * my_base, my_dest, my_slot (int32 [num_experts] each: first row, computing rank and expert slot there of this
+ * rank's entries per expert; my_dest / my_slot are written only with guest experts), guest_expert (int32 [8]: the
+ * experts this rank hosts, -1 = unused) and rank_rows (int32 [2][num_ranks]: every rank's rows before and after the
+ * spill). expert_start / expert_end hold E_local entries, plus 8 guest slots when num_ranks > 1. The whole buffer must be zeroed once after it is allocated, on every
  * rank and before any rank's first call (the flag words are never reset afterwards; everything else is rewritten by
  * each call before it is read). */
 int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,
@@ -335,7 +354,7 @@ int dgb200_get_symm_buffer_layout_for_mega_moe_ex(int32_t num_ranks, int32_t num
  * the gate/up GEMM's epilogue writes silu(gate) * up * topk_weight as BF16. hidden and inter must be multiples of 128.
  * Shared experts (shared_intermediate_hidden > 0): shared_l1_w bf16 [2 * shared_inter, hidden] (interleaved likewise),
  * shared_l2_w bf16 [hidden, shared_inter], a dense MLP over this rank's tokens with routing weight 1 whose rows are one
- * more combine slot; the token capacity must then be a multiple of 128. out[21] as in
+ * more combine slot; the token capacity must then be a multiple of 128. out[26] as in
  * dgb200_get_symm_buffer_layout_for_mega_moe_ex.
  * Reference: bf16_mega_moe, csrc/apis/mega.hpp:288-400 and deep_gemm/include/deep_gemm/impls/sm100_bf16_mega_moe.cuh:52. */
 int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,

@@ -204,3 +204,94 @@ def ep_dest_rows(topk_idx: torch.Tensor, my_base: torch.Tensor, num_experts: int
             dest[i] = int(my_base[e]) + int(seen[e])
             seen[e] += 1
     return dest
+
+
+def ep_spill_table(all_counts: torch.Tensor, guest_slots: int):
+    """Which rank computes the rows that source rank s routes to expert e, when hot experts may spill rows to other ranks.
+
+    No reference counterpart (the reference keeps every expert's rows on its owner, sm100_fp8_fp4_mega_moe.cuh:372,389).
+    Every rank has ``guest_slots`` spare expert slots after its own experts. From the same all_counts [ranks, experts]
+    every rank derives the same table with integer arithmetic only:
+
+      load[r] = rows of the experts r owns; repeat at most ranks * guest_slots times:
+        hi = the most loaded rank, lo = the least loaded rank other than hi that still has a free guest slot (ties: lower rank);
+        gap = load[hi] - load[lo]; stop when gap < max(256, total rows / (32 * ranks));
+        e  = the expert owned by hi with the most rows still on hi (ties: lower e); stop when it has none;
+        walk the source ranks from the last to the first: the rows (s, e) still on hi move to lo while
+        2 * moved + count[s][e] < gap (each move must shrink the gap); stop when nothing moved;
+        lo hosts e in a guest slot (the one it already has for e, else its next free one).
+
+    Returns (dest int64 [experts, ranks]: the computing rank of (e, s); slot int64 [experts, ranks]: the expert slot on
+    that rank (own experts 0..per_rank-1, guests per_rank..per_rank+guest_slots-1); guest int64 [ranks, guest_slots]:
+    the expert each guest slot hosts, -1 = unused)."""
+    ranks, experts = all_counts.shape
+    per_rank = experts // ranks
+    counts = all_counts.to(torch.int64)
+    dest = (torch.arange(experts) // per_rank).unsqueeze(1).repeat(1, ranks)
+    slot = (torch.arange(experts) % per_rank).unsqueeze(1).repeat(1, ranks)
+    guest = torch.full((ranks, max(guest_slots, 1)), -1, dtype=torch.int64)[:, :guest_slots]
+    used = [0] * ranks
+    load = [int(counts[:, r * per_rank:(r + 1) * per_rank].sum()) for r in range(ranks)]
+    min_gap = max(256, int(counts.sum()) // (32 * ranks))
+    for _ in range(ranks * guest_slots):
+        hi = max(range(ranks), key=lambda r: (load[r], -r))
+        free = [r for r in range(ranks) if r != hi and used[r] < guest_slots]
+        if not free:
+            break
+        lo = min(free, key=lambda r: (load[r], r))
+        gap = load[hi] - load[lo]
+        if gap < min_gap:
+            break
+        on_hi = lambda e: sum(int(counts[s, e]) for s in range(ranks) if int(dest[e, s]) == hi)
+        e = max(range(hi * per_rank, (hi + 1) * per_rank), key=lambda e: (on_hi(e), -e))
+        if on_hi(e) == 0:
+            break
+        hosted = [g for g in range(used[lo]) if int(guest[lo, g]) == e]
+        g = hosted[0] if hosted else used[lo]
+        moved = 0
+        for s in reversed(range(ranks)):
+            c = int(counts[s, e])
+            if c > 0 and int(dest[e, s]) == hi and 2 * moved + c < gap:
+                dest[e, s] = lo
+                slot[e, s] = per_rank + g
+                moved += c
+        if moved == 0:
+            break
+        if not hosted:
+            guest[lo, g] = e
+            used[lo] += 1
+        load[hi] -= moved
+        load[lo] += moved
+    return dest, slot, guest
+
+
+def ep_plan_with_spill(all_counts: torch.Tensor, rank: int, alignment: int, guest_slots: int):
+    """The expert-parallel dispatch plan of one rank under ep_spill_table. On every rank the expert slots (own experts,
+    then guest slots) are laid out one after the other, each padded to ``alignment``; inside a slot the rows are ordered
+    by (source rank, entry).
+
+    Returns (my_base int64 [experts]: first row, on the computing rank, of this rank's entries for e;
+             my_dest, my_slot int64 [experts]: that rank and the expert slot there;
+             slot_start, slot_end int64 [per_rank + guest_slots] of this rank's own slots;
+             guest int64 [guest_slots]: the experts this rank hosts as a guest, -1 = unused)."""
+    ranks, experts = all_counts.shape
+    per_rank = experts // ranks
+    slots = per_rank + guest_slots
+    dest, slot, guest = ep_spill_table(all_counts, guest_slots)
+    rows = torch.zeros(ranks, slots, dtype=torch.int64)
+    before_me = torch.zeros(experts, dtype=torch.int64)
+    for e in range(experts):
+        for s in range(ranks):
+            d, v = int(dest[e, s]), int(slot[e, s])
+            if s < rank and d == int(dest[e, rank]):
+                before_me[e] += int(all_counts[s, e])
+            rows[d, v] += int(all_counts[s, e])
+    start = torch.zeros(ranks, slots, dtype=torch.int64)
+    for d in range(ranks):
+        cursor = 0
+        for v in range(slots):
+            start[d, v] = cursor
+            cursor = align(cursor + int(rows[d, v]), alignment)
+    my_dest, my_slot = dest[:, rank].clone(), slot[:, rank].clone()
+    my_base = start[my_dest, my_slot] + before_me
+    return my_base, my_dest, my_slot, start[rank].clone(), (start[rank] + rows[rank]).clone(), guest[rank].clone()

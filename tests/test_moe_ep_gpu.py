@@ -146,6 +146,107 @@ def test_two_rank_layer_matches_oracle():
         assert quant.calc_diff(got['y_shared'], want_shared) <= 2e-3
 
 
+# ---- hot-expert row spill: skewed routing, rows of hot experts computed by the other rank in a guest slot
+SP_EXPERTS, SP_TOPK, SP_TOKENS, SP_GUESTS = 16, 4, (600, 420), 2
+
+
+def _rank_inputs_spill(rank):
+    from oracle import moe as omoe
+    from tests.helpers import moe_case
+    c = moe_case(SP_TOKENS[rank], HIDDEN, INTER, SP_EXPERTS, SP_TOPK, seed=700 + rank)
+    # experts 0..2 (all owned by rank 0) are chosen by almost every token
+    logits = c['logits'].clone()
+    logits[:, :3] += 4.0
+    c['topk_idx'], c['topk_weights'] = omoe.route_sigmoid_topk(logits, SP_TOPK)
+    w = moe_case(4, HIDDEN, INTER, SP_EXPERTS, SP_TOPK, seed=79)  # the same weights on every rank
+    for k in ('l1_q', 'l1_sf', 'l2_q', 'l2_sf'):
+        c[k] = w[k]
+    return c
+
+
+def _worker_spill(rank, world, port, results):
+    import torch.distributed as dist
+    import deepgemm_b200 as dg
+    from deepgemm_b200 import _lib
+    from oracle import quant
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        c = _rank_inputs_spill(rank)
+        per_rank = SP_EXPERTS // world
+        mine = slice(rank * per_rank, (rank + 1) * per_rank)
+        buf = dg.get_symm_buffer_for_mega_moe(dist.group.WORLD, SP_EXPERTS, max(SP_TOKENS), SP_TOPK, HIDDEN, INTER)
+        l1_sf = dg.transform_sf_into_required_layout(c['l1_sf'][mine].cuda(), 2 * INTER, HIDDEN, (1, 32), per_rank)
+        l2_sf = dg.transform_sf_into_required_layout(c['l2_sf'][mine].cuda(), HIDDEN, INTER, (1, 32), per_rank)
+        l1, l2 = dg.transform_weights_for_mega_moe((c['l1_q'][mine].cuda(), l1_sf), (c['l2_q'][mine].cuda(), l2_sf))
+        l1s, l2s = dg.share_weights_for_mega_moe(dist.group.WORLD, l1, l2, num_guest_experts=SP_GUESTS)
+        t = SP_TOKENS[rank]
+        out = {}
+        for name, (w1, w2) in (('plain', (l1, l2)), ('spill', (l1s, l2s)), ('spill_again', (l1s, l2s))):
+            buf.x[:t].copy_(c['x_q'].cuda())
+            buf.x_sf[:t].copy_(quant.pack_ue8m0(c['x_sf']).cuda())
+            buf.topk_idx[:t].copy_(c['topk_idx'].cuda())
+            buf.topk_weights[:t].copy_(c['topk_weights'].cuda())
+            stats = torch.zeros(per_rank, dtype=torch.int32, device='cuda')
+            y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+            dg.fp8_fp4_mega_moe(y, w1, w2, buf, cumulative_local_expert_recv_stats=stats)
+            status = _lib.device_status()
+            assert status[0] == 0, status
+            out['y_' + name] = y.cpu()
+            out['stats_' + name] = stats.cpu()
+        lay, raw = buf.layout, buf.buffer
+        take = lambda key, n: raw[lay[key]:lay[key] + n * 4].view(torch.int32).cpu().clone()
+        slots = per_rank + SP_GUESTS
+        out.update(start=take('expert_start', slots), end=take('expert_end', slots), dest=take('dest_row', t * SP_TOPK),
+                   my_base=take('my_base', SP_EXPERTS), my_dest=take('my_dest', SP_EXPERTS), my_slot=take('my_slot', SP_EXPERTS),
+                   guest=take('guest_expert', SP_GUESTS), rank_rows=take('rank_rows', 2 * world))
+        results[rank] = out
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs 2 GPUs')
+def test_two_rank_hot_expert_spill_matches_oracle():
+    """Routing that sends most rows to rank 0's experts: with guest slots the plan moves rows of hot experts to rank 1,
+    which computes them with weights fetched from rank 0. Every plan array must equal the oracle's (ep_plan_with_spill),
+    the output must match the layer oracle, and must not depend on whether rows were spilled beyond the order of the
+    combine's FP32 additions."""
+    import torch.multiprocessing as mp
+    from oracle import moe as omoe
+    from oracle import quant
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker_spill, args=(world, _free_port(), results), nprocs=world, join=True)
+    cases = [_rank_inputs_spill(r) for r in range(world)]
+    all_counts = torch.stack([omoe.ep_counts(c['topk_idx'], SP_EXPERTS) for c in cases])
+    per_rank = SP_EXPERTS // world
+    rows_before = [int(all_counts[:, r * per_rank:(r + 1) * per_rank].sum()) for r in range(world)]
+    hosted = 0
+    for rank in range(world):
+        c, got = cases[rank], results[rank]
+        want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+        assert not torch.isnan(got['y_spill'].float()).any()
+        assert quant.calc_diff(got['y_spill'], want) <= 2e-3
+        assert quant.calc_diff(got['y_spill'], got['y_plain']) <= 1e-6
+        assert torch.equal(got['y_spill'], got['y_spill_again']), 'two calls must give the same bits'
+        my_base, my_dest, my_slot, start, end, guest = omoe.ep_plan_with_spill(all_counts, rank, 128, SP_GUESTS)
+        assert torch.equal(got['my_base'].long(), my_base) and torch.equal(got['my_dest'].long(), my_dest)
+        assert torch.equal(got['my_slot'].long(), my_slot) and torch.equal(got['guest'].long(), guest)
+        assert torch.equal(got['start'].long(), start) and torch.equal(got['end'].long(), end)
+        assert torch.equal(got['dest'].long(), omoe.ep_dest_rows(c['topk_idx'], my_base, SP_EXPERTS))
+        owned = all_counts[:, rank * per_rank:(rank + 1) * per_rank].sum(dim=0)
+        assert torch.equal(got['stats_spill'].long(), owned) and torch.equal(got['stats_plain'].long(), owned)
+        assert got['rank_rows'][:world].tolist() == rows_before
+        assert int(got['rank_rows'][world + rank]) == int((end - start).sum())
+        hosted += int((guest >= 0).sum())
+    assert hosted > 0, 'the case must make at least one expert spill'
+    after = results[0]['rank_rows'][world:].tolist()
+    assert max(after) - min(after) < max(rows_before) - min(rows_before)
+
+
 # ---- NVFP4 form of the same layer: rows cross ranks as packed E2M1 + UE4M3 scales, one input scale for all ranks
 NV_HIDDEN, NV_INTER = 512, 256
 NV_X_SCALE = 6.0 / (6.0 * 448.0)

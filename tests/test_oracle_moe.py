@@ -138,3 +138,41 @@ def test_k_grouped_oracle_layouts_agree():
     d2 = ogemm.k_grouped_gemm_psum(a_q, a_sf, b_q, b_sf, c, [256, 256, 384], 128)
     assert torch.equal(d1, d2) and torch.equal(d1[1], c[1])
     assert not torch.equal(d1[0], c[0])
+
+
+def test_spill_plan_conserves_rows_and_balances():
+    """ep_plan_with_spill over Zipf-skewed counts of 8 ranks: every (expert, source) pair lands in exactly one slot of
+    one rank, the ranks agree on every segment, guests only host other ranks' experts, and the loads end up closer."""
+    from oracle import moe as omoe
+    ranks, experts, guests = 8, 64, 4
+    per_rank = experts // ranks
+    g = torch.Generator().manual_seed(5)
+    popularity = 1.0 / torch.arange(1, experts + 1, dtype=torch.float32)[torch.randperm(experts, generator=g)]
+    counts = torch.stack([torch.poisson(4000 * popularity / popularity.sum() * torch.ones(experts), generator=g).long()
+                          for _ in range(ranks)])
+    dest, slot, guest = omoe.ep_spill_table(counts, guests)
+    plans = [omoe.ep_plan_with_spill(counts, r, 128, guests) for r in range(ranks)]
+    rows_seen = torch.zeros(ranks, per_rank + guests, dtype=torch.long)
+    for e in range(experts):
+        for s in range(ranks):
+            d, v = int(dest[e, s]), int(slot[e, s])
+            assert int(plans[s][1][e]) == d and int(plans[s][2][e]) == v
+            assert (v < per_rank and d == e // per_rank and v == e % per_rank) or \
+                (v >= per_rank and d != e // per_rank and int(guest[d, v - per_rank]) == e)
+            # this source's rows lie inside the segment the computing rank holds for the slot, after the earlier sources'
+            start, end = int(plans[d][3][v]), int(plans[d][4][v])
+            base = int(plans[s][0][e])
+            assert start <= base and base + int(counts[s, e]) <= end
+            rows_seen[d, v] += int(counts[s, e])
+    for r in range(ranks):
+        assert torch.equal(rows_seen[r], plans[r][4] - plans[r][3])
+        assert all(int(plans[r][3][v]) % 128 == 0 for v in range(per_rank + guests))
+        assert all(int(plans[r][3][v + 1]) >= int(plans[r][4][v]) for v in range(per_rank + guests - 1))
+    before = torch.stack([counts[:, r * per_rank:(r + 1) * per_rank].sum() for r in range(ranks)])
+    after = rows_seen.sum(dim=1)
+    assert int(after.sum()) == int(counts.sum())
+    assert int(after.max()) < int(before.max()) and int(after.max() - after.min()) < int(before.max() - before.min()) // 4
+    # no guest slots: the plain plan
+    my_base, my_dest, my_slot, start, end, none = omoe.ep_plan_with_spill(counts, 3, 128, 0)
+    plain_base, plain_start, plain_end = omoe.ep_plan(counts, 3, 128)
+    assert torch.equal(my_base, plain_base) and torch.equal(start, plain_start) and torch.equal(end, plain_end) and none.numel() == 0
