@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument('--guest-experts', type=int, default=4,
                     help='expert-parallel runs: guest expert slots per rank for the hot-expert row spill (0 = every expert\'s '
                          'rows stay on its owner)')
+    ap.add_argument('--comm-sms', type=int, default=-1,
+                    help='expert-parallel runs: SMs kept for the kernels that move rows while the GEMMs run (the library\'s '
+                         '"ep_comm_sms" knob; -1 = its default, 0 = one stream without overlap)')
     ap.add_argument('--skip-other-configs', action='store_true',
                     help='N = 1 only: leave out the extra timings (8192-token base, BASELINE configs 1, 2 and 4) after the headline line')
     ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
@@ -759,8 +762,8 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         # stage times of the most loaded rank (rank `stages_rank`); with several ranks the cross-rank waits are inside
         'stages_ms': ({'plan': stage_ms[0], 'dispatch': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
                        'l2_gemm': stage_ms[3], 'combine': stage_ms[4]} if not gemms_in_one_interval else
-                      {'plan': stage_ms[0], 'dispatch_push': stage_ms[1], 'gemms_all_phases': stage_ms[2] + stage_ms[3],
-                       'combine_all_phases': stage_ms[4]}),
+                      {'plan': stage_ms[0], 'dispatch_until_first_phase_landed': stage_ms[1],
+                       'gemms_all_phases': stage_ms[2] + stage_ms[3], 'return_tail_and_combine': stage_ms[4]}),
         'stages_rank': hot,
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9 if not gemms_in_one_interval else None,
         'tflops': tflops,
@@ -802,13 +805,13 @@ def kernels_of_one_step(nvfp4, world, local_experts, guests=0):
     """Launches of this library's kernels in one pass of the layer (memsets are not kernels of ours). FP8 layer on one
     rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the two tile orientations
     (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather. Expert parallel, P =
-    min(4, local experts) phases: router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
-    per phase flag + scale reorder + L1 + L2 + flag, per phase flag + combine; with guest experts one more launch fetches
-    their weights and the guest slots count as experts."""
+    min(4, expert slots) phases: router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
+    flag + scale reorder + L1 + L2, return push + flag, and at the end a flag wait per phase and the combine; with guest
+    experts one more launch fetches their weights and the guest slots count as experts."""
     if world == 1:
         return 9 if nvfp4 else 11
     phases = min(4, local_experts + guests)
-    return 7 + 2 * phases + 5 * phases + 2 * phases + (1 if guests else 0)
+    return 7 + 9 * phases + 1 + (1 if guests else 0)
 
 
 L1_STAGE_KERNELS = ('gate/up GEMM + SwiGLU + FP8 requant (dgb200_grouped_gemm_kernel + dgb200_swap_gemm_kernel + '
@@ -895,6 +898,9 @@ def main():
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         torch.cuda.set_device(local_rank)
         dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
+    if args.comm_sms >= 0:
+        from deepgemm_b200 import _lib
+        _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', args.comm_sms))
     rc = run_ours(args, cfg, rank, world, local_rank)
     if world > 1:
         import torch.distributed as dist

@@ -67,6 +67,8 @@ struct Tuning {
     int mlp_kernel = -1;  // FP8 x FP4 layer GEMMs: 0 = separate gate/up and down kernels (tokens-on-M / swapped split),
                           // 1 = the fused expert-MLP kernel on single CTAs, 2 = on CTA pairs; -1 = not yet read from
                           // the environment (DGB200_MLP_KERNEL, default below)
+    int ep_comm_sms = 24;  // expert-parallel layer: SMs kept free of GEMM CTAs for the kernels that move rows over NVLink
+                           // while the GEMMs run (0 = no overlap: one stream, pull combine)
     long long peer_wait_cycles = 20000000000ll;  // budget of a wait for another rank, SM clock cycles (about 10 s: ranks
                                                  // may reach their first call seconds apart)
 };
@@ -307,6 +309,53 @@ int side_stream_for_current_device(SideStream** out) {
     return 0;
 }
 
+// The second stream of the expert-parallel layer with the events that order it against the caller's stream: the
+// kernels that move rows between ranks run there, on the SMs the GEMMs leave free, while the GEMMs of other expert
+// phases run on the caller's stream.
+struct EpStreams {
+    cudaStream_t comm = nullptr;
+    cudaEvent_t planned = nullptr, fetched = nullptr, returned = nullptr;
+    cudaEvent_t pushed[kMaxEpPhases] = {}, computed[kMaxEpPhases] = {};
+    std::mutex mu;  // one layer call at a time per device enqueues on these (the events are shared)
+};
+
+int ep_streams_for_current_device(EpStreams** out) {
+    constexpr int kMaxDevices = 64;
+    static EpStreams table[kMaxDevices];
+    static std::mutex create_mu;
+    int dev = 0;
+    DGB_CUDA(cudaGetDevice(&dev));
+    DGB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+    EpStreams& s = table[dev];
+    {
+        std::lock_guard<std::mutex> lock(create_mu);
+        if (s.comm == nullptr) {
+            DGB_CUDA(cudaStreamCreateWithFlags(&s.comm, cudaStreamNonBlocking));
+            cudaEvent_t* all[3] = {&s.planned, &s.fetched, &s.returned};
+            for (cudaEvent_t* e : all) DGB_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+            for (int q = 0; q < kMaxEpPhases; ++q) {
+                DGB_CUDA(cudaEventCreateWithFlags(&s.pushed[q], cudaEventDisableTiming));
+                DGB_CUDA(cudaEventCreateWithFlags(&s.computed[q], cudaEventDisableTiming));
+            }
+        }
+    }
+    *out = &s;
+    return 0;
+}
+
+// Launch shape of a row-moving kernel that shares the GPU with GEMMs: `sms` CTAs of 1024 threads that each ask for so
+// much dynamic shared memory that no second one (and no GEMM CTA) fits on their SM, so together they occupy exactly
+// `sms` SMs instead of a few warps on every SM (the block scheduler spreads small CTAs over all SMs, and a GEMM CTA
+// needs a whole SM's registers).
+constexpr int kCommCtaThreads = 1024;
+constexpr int kCommCtaSmemBytes = 120 * 1024;
+
+template <typename Kernel>
+int allow_comm_smem(Kernel kernel) {
+    DGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommCtaSmemBytes));
+    return 0;
+}
+
 // The layer GEMMs with swapped operands (gemm_swap_kernel.cuh): weights on M, an expert's tokens on N. Takes the same
 // call description as run_gemm; only the FP8 x FP4 / FP8 x FP8 kind, the psum layout with 128-row segments, scale
 // factors in tcgen05.cp order and the SwiGLU / BF16 epilogues.
@@ -407,6 +456,7 @@ struct MegaLayout {
     long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
     long long combine_partial;  // expert parallel: fp32 [max tokens, hidden], the running sums of the phased combine
+    long long returned;  // expert parallel: bf16 [max tokens * topk, hidden], the output rows the computing ranks sent back
     long long tile_done;  // FP8 kind: one counter per token tile of the fused expert-MLP kernel (max_rows / 128 + local experts)
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
     long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
@@ -495,6 +545,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_slots) * 4) : 0;
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.combine_partial = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * hidden * 4) : 0;
+    l.returned = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * topk * hidden * 2) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
         DGB_REQUIRE((kind == kKindFp8Fp4 || kind == kKindBf16) && shared_inter % 128 == 0,
@@ -960,34 +1011,35 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     DGB_CUDA(cudaGetLastError());
     if ((rc = record_stage(1, stream))) return rc;
 
-    // dispatch, phase by phase: rows + scales + weight + source id stored straight into the owners' expert-sorted buffers
+    // dispatch, phase by phase: rows + scales + weight + source id stored straight into the computing ranks' expert-sorted buffers
     if (quant.x_bf16 != nullptr && num_tokens > 0) {
         // BF16 input: quantise once into the buffer's x / x_sf views (the bits of per_token_cast_to_fp8, gran 32), push from there
         rc = run_cast(false, quant.x_bf16, quant.x_bf16_row_stride, num_tokens, hidden, 32, base + l.x, hidden, nullptr, base + l.x_sf, 1,
                       sf_per_row, stream);
         if (rc) return rc;
     }
-    for (int q = 0; q < phases; ++q) {
-        if (entries > 0)
-            dgb200_ep_push_kernel<<<(entries + 7) / 8, 256, 0, stream>>>(
-                base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
-                static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, E, rank, entries_per_rank, peers, l.l1_acts,
-                l.l1_sf_stage, 0, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1), my_dest, my_slot);
-        flag(1 + q, 1, 0);
-    }
-    DGB_CUDA(cudaGetLastError());
-    if (spill) {
-        // the weights of the experts this rank hosts as a guest, from their owners (while the other ranks' rows arrive)
-        dgb200_ep_fetch_guest_weights_kernel<<<dim3(74, G), 256, 0, stream>>>(reinterpret_cast<const int*>(base + l.guest_expert), E, guest_tables);
-        DGB_CUDA(cudaGetLastError());
-    }
-    if ((rc = record_stage(2, stream))) return rc;
-
-    // GEMMs, phase by phase, each as soon as every rank's rows for the phase have landed
-    for (int q = 0; q < phases; ++q) {
+    // Overlap: with several phases and ep_comm_sms > 0 the kernels that move rows run on a second stream, on SMs the
+    // GEMMs leave free: the pushes of later phases under the GEMMs of earlier ones, and the output rows of a finished
+    // phase go back to their source ranks (return push) under the GEMMs of the next; the combine is then a local sum.
+    // Otherwise everything runs on the caller's stream and the combine pulls the rows phase by phase.
+    const int comm_sms = tuning().ep_comm_sms;
+    const bool overlap = phases > 1 && comm_sms > 0;
+    const int push_grid = std::max(1, (entries + 7) / 8);
+    auto push = [&](int q, cudaStream_t on, bool few_sms) {
+        if (entries <= 0) return;
+        dgb200_ep_push_kernel<<<few_sms ? comm_sms : push_grid, few_sms ? kCommCtaThreads : 256, few_sms ? kCommCtaSmemBytes : 0, on>>>(
+            base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
+            static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, E, rank, entries_per_rank, peers, l.l1_acts,
+            l.l1_sf_stage, 0, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1), my_dest, my_slot);
+    };
+    auto fetch_guests = [&](cudaStream_t on) {
+        // the weights of the experts this rank hosts as a guest, from their owners
+        dgb200_ep_fetch_guest_weights_kernel<<<dim3(overlap ? std::max(1, comm_sms / std::max(1, G)) : 74, G), 256, 0, on>>>(
+            reinterpret_cast<const int*>(base + l.guest_expert), E, guest_tables);
+    };
+    auto gemms = [&](int q) -> int {
         const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
-        flag(1 + q, 0, 1);
-        if (g1 == g0) { flag(1 + kMaxEpPhases + q, 1, 0); continue; }
+        if (g1 == g0) return 0;
         // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
         if (sf_per_row > 0)
             dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
@@ -995,29 +1047,106 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                 reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows),
                 expert_start + g0, expert_end + g1 - 1);
         DGB_CUDA(cudaGetLastError());
-        rc = run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream,
-                             kNumStageEvents /* no stage events inside the loop */,
-                             static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts,
-                             phases == 1 ? 0 : g0, phases == 1 ? 0 : g1);
-        if (rc) return rc;
-        flag(1 + kMaxEpPhases + q, 1, 0);
+        return run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream,
+                               kNumStageEvents /* no stage events inside the loop */,
+                               static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts,
+                               phases == 1 ? 0 : g0, phases == 1 ? 0 : g1);
+    };
+
+    if (!overlap) {
+        for (int q = 0; q < phases; ++q) {
+            push(q, stream, false);
+            flag(1 + q, 1, 0);
+        }
+        DGB_CUDA(cudaGetLastError());
+        if (spill) fetch_guests(stream);
+        DGB_CUDA(cudaGetLastError());
+        if ((rc = record_stage(2, stream))) return rc;
+        // GEMMs, phase by phase, each as soon as every rank's rows for the phase have landed
+        for (int q = 0; q < phases; ++q) {
+            flag(1 + q, 0, 1);
+            if ((rc = gemms(q))) return rc;
+            flag(1 + kMaxEpPhases + q, 1, 0);
+        }
+        if ((rc = record_stage(3, stream))) return rc;  // both GEMMs of all phases lie before this point
+        if ((rc = record_stage(4, stream))) return rc;
+        if (with_shared && num_tokens > 0) {
+            if (quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
+            if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
+        }
+        // combine, phase by phase, each as soon as every rank has finished the phase's experts
+        for (int q = 0; q < phases; ++q) {
+            flag(1 + kMaxEpPhases + q, 0, 1);
+            if (num_tokens > 0)
+                dgb200_moe_combine_phase_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
+                    peers, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
+                    with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
+                    reinterpret_cast<float*>(base + l.combine_partial), static_cast<__nv_bfloat16*>(y), phase_begin(q), phase_begin(q + 1),
+                    q == 0 ? 1 : 0, q == phases - 1 ? 1 : 0, my_dest, my_slot);
+        }
+        DGB_CUDA(cudaGetLastError());
+        return record_stage(5, stream);
     }
+
+    EpStreams* ep = nullptr;
+    if ((rc = ep_streams_for_current_device(&ep))) return rc;
+    if ((rc = allow_comm_smem(dgb200_ep_push_kernel))) return rc;
+    if ((rc = allow_comm_smem(dgb200_ep_return_rows_kernel))) return rc;
+    std::lock_guard<std::mutex> ep_lock(ep->mu);
+    cudaStream_t comm = ep->comm;
+    auto flag_on = [&](cudaStream_t on, int row, int do_signal, int do_wait) {
+        dgb200_ep_flag_kernel<<<1, 32, 0, on>>>(peers, l.flags, row, rank, num_ranks, do_signal, do_wait, peer_budget);
+    };
+    // second stream: every push (the first on all SMs: nothing else runs yet), the guest weights, then the return pushes
+    DGB_CUDA(cudaEventRecord(ep->planned, stream));
+    DGB_CUDA(cudaStreamWaitEvent(comm, ep->planned, 0));
+    for (int q = 0; q < phases; ++q) {
+        push(q, comm, q > 0);
+        flag_on(comm, 1 + q, 1, 0);
+        DGB_CUDA(cudaEventRecord(ep->pushed[q], comm));
+    }
+    if (spill) fetch_guests(comm);
+    DGB_CUDA(cudaGetLastError());
+    DGB_CUDA(cudaEventRecord(ep->fetched, comm));
+    // caller's stream: the GEMMs of phase q as soon as every rank's rows for it have landed, on all SMs but comm_sms
+    int rc_gemm = 0;
+    for (int q = 0; q < phases && rc_gemm == 0; ++q) {
+        DGB_CUDA(cudaStreamWaitEvent(stream, ep->pushed[q], 0));
+        flag_on(stream, 1 + q, 0, 1);
+        if (q == 0 && (rc = record_stage(2, stream))) rc_gemm = rc;  // the rows of the first phase are here
+        if (phase_begin(q + 1) > E) DGB_CUDA(cudaStreamWaitEvent(stream, ep->fetched, 0));  // guest slots: their weights are here
+        reserved_sms() = comm_sms;
+        if (rc_gemm == 0) rc_gemm = gemms(q);
+        reserved_sms() = 0;
+        DGB_CUDA(cudaEventRecord(ep->computed[q], stream));
+        // second stream: this phase's output rows back to their source ranks, then "outputs q" to every rank
+        DGB_CUDA(cudaStreamWaitEvent(comm, ep->computed[q], 0));
+        const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
+        if (g1 > g0) {
+            const bool last = q == phases - 1;  // nothing runs next to the last one: all SMs
+            dgb200_ep_return_rows_kernel<<<last ? 592 : comm_sms, last ? 256 : kCommCtaThreads, last ? 0 : kCommCtaSmemBytes, comm>>>(
+                reinterpret_cast<const __nv_bfloat16*>(base + l.l2_out), reinterpret_cast<const int*>(base + l.src_of_row), expert_start,
+                expert_end, g0, g1, hidden, entries_per_rank, peers, l.returned);
+        }
+        flag_on(comm, 1 + kMaxEpPhases + q, 1, 0);
+    }
+    DGB_CUDA(cudaGetLastError());
+    // join: the second stream never runs ahead of the caller's stream, whatever happened above
+    DGB_CUDA(cudaEventRecord(ep->returned, comm));
     if ((rc = record_stage(3, stream))) return rc;  // both GEMMs of all phases lie before this point
     if ((rc = record_stage(4, stream))) return rc;
-    if (with_shared && num_tokens > 0) {
-        if (quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
-        if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
+    if (rc_gemm == 0 && with_shared && num_tokens > 0) {
+        if (quant.kind != kKindBf16) rc_gemm = run_shared_x_sf(l, base, num_tokens, hidden, stream);
+        if (rc_gemm == 0) rc_gemm = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream);
     }
-    // combine, phase by phase, each as soon as every rank has finished the phase's experts
-    for (int q = 0; q < phases; ++q) {
-        flag(1 + kMaxEpPhases + q, 0, 1);
-        if (num_tokens > 0)
-            dgb200_moe_combine_phase_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
-                peers, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
-                with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
-                reinterpret_cast<float*>(base + l.combine_partial), static_cast<__nv_bfloat16*>(y), phase_begin(q), phase_begin(q + 1),
-                q == 0 ? 1 : 0, q == phases - 1 ? 1 : 0, my_dest, my_slot);
-    }
+    DGB_CUDA(cudaStreamWaitEvent(stream, ep->returned, 0));
+    if (rc_gemm) return rc_gemm;
+    // combine: once every rank's rows of every phase have arrived, a local sum in slot order
+    for (int q = 0; q < phases; ++q) flag_on(stream, 1 + kMaxEpPhases + q, 0, 1);
+    if (num_tokens > 0)
+        dgb200_moe_combine_returned_kernel<<<num_tokens, 128, 0, stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(base + l.returned), dest_row, num_topk, hidden,
+            with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }
@@ -1184,6 +1313,9 @@ int dgb200_set_tuning(const char* name, int32_t value) {
     } else if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
+    } else if (std::strcmp(name, "ep_comm_sms") == 0) {
+        DGB_REQUIRE(value >= 0 && value <= 64, "ep_comm_sms must be in [0, 64]");
+        tuning().ep_comm_sms = value;
     } else if (std::strcmp(name, "peer_wait_us") == 0) {
         DGB_REQUIRE(value >= 1, "peer_wait_us must be at least 1 microsecond");
         tuning().peer_wait_cycles = static_cast<long long>(value) * 2000;  // SM clock below 2 GHz: at least `value` us

@@ -2,6 +2,7 @@
 // Counterparts in the reference: csrc/utils/exception.hpp:12-107 (DG_HOST_ASSERT / CUDA check macros),
 // csrc/jit/handle.hpp:174-219 (launch config), csrc/jit_kernels/impls/runtime_utils.hpp:113-150 (tensor maps).
 #pragma once
+#include <algorithm>
 
 #include <cstdarg>
 #include <cstdio>
@@ -47,12 +48,20 @@ inline int& num_sms_setting() {
 }
 
 // SM count of the current device, narrowed by dgb200_set_num_sms.
+// SMs the persistent GEMM kernels of the calling host thread leave free (the expert-parallel layer keeps a few for
+// the kernels that move rows over NVLink while its GEMMs run).
+inline int& reserved_sms() {
+    thread_local int reserved = 0;
+    return reserved;
+}
+
 inline int effective_num_sms(int* out) {
     int dev = 0, sms = 0;
     DGB_CUDA(cudaGetDevice(&dev));
     DGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int want = num_sms_setting();
-    *out = (want > 0 && want < sms) ? want : sms;
+    const int usable = (want > 0 && want < sms) ? want : sms;
+    *out = std::max(1, usable - std::max(0, reserved_sms()));
     return 0;
 }
 

@@ -707,9 +707,29 @@ dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries,
     dest_row[i] = my_base[e] + chunk_hist[static_cast<long long>(blockIdx.x) * num_experts + e] + before + rank_in_warp;
 }
 
-// One warp per entry: stores the token's quantised row, its packed scales (into the owner's MN-major scale buffer), the
-// routing weight and the source id into the owner rank's buffers.
-__global__ void __launch_bounds__(256)
+// Copies `bytes` (a multiple of 16) from `from` to `to` with the whole warp, up to seven 16-byte loads per lane in flight
+// before the first store: the copies of the expert-parallel layer read local memory and write a peer's, and may run on
+// a handful of SMs next to the GEMMs, so the memory-level parallelism has to come from each thread.
+__device__ __forceinline__ void warp_copy_row(const uint4* __restrict__ from, uint4* __restrict__ to, int bytes, int lane) {
+    const int vecs = bytes / 16;
+    for (int c0 = lane; c0 < vecs; c0 += 32 * 7) {
+        uint4 v[7];
+#pragma unroll
+        for (int j = 0; j < 7; ++j)
+            if (c0 + 32 * j < vecs) v[j] = ld_global_nc_v4(from + c0 + 32 * j);
+#pragma unroll
+        for (int j = 0; j < 7; ++j)
+            if (c0 + 32 * j < vecs) to[c0 + 32 * j] = v[j];
+    }
+}
+
+// Dispatch push of the expert-parallel layer: every entry (token, k) of this rank whose expert slot lies in
+// [local_expert_begin, local_expert_end) is stored into the buffers of the rank that computes it: the token's quantised
+// row, its packed scales, the routing weight and the source id. A warp examines 32 entries at a time (one per lane) and
+// then copies the rows of those that belong to the phase one after the other, so a launch that pushes one phase of the
+// experts skips the other entries cheaply. Any grid and block size: while GEMMs hold most SMs the layer launches this
+// kernel on the few SMs it kept free.
+__global__ void __launch_bounds__(1024)
 dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
                       const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights,
                       const int* __restrict__ dest_row, int num_entries, int topk, int row_bytes, int sf_per_row,
@@ -718,37 +738,114 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
                       long long src_offset, int local_expert_begin, int local_expert_end,
                       const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
     const int lane = threadIdx.x & 31;
-    const int entry = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (entry >= num_entries) return;
-    const int dest = dest_row[entry];
-    if (dest < 0) return;
-    // the rank that computes this entry and the expert slot there: the expert's owner and its index among the owner's
-    // experts, unless the plan spilled the rows this rank routes to the expert (my_dest / my_slot, may be null)
-    const int expert = static_cast<int>(topk_idx[entry]);
-    const int owner = my_dest != nullptr ? my_dest[expert] : expert / experts_per_rank;
-    // only the entries whose slot lies in [begin, end): the layer pushes phase by phase
-    const int local_expert = my_slot != nullptr ? my_slot[expert] : expert - owner * experts_per_rank;
-    if (local_expert < local_expert_begin || local_expert >= local_expert_end) return;
-    const int token = entry / topk;
-    const unsigned long long base = peers.p[owner];
-    const uint4* from = reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes);
-    uint4* to = reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * row_bytes);
-    for (int c = lane; c < row_bytes / 16; c += 32) to[c] = ld_global_nc_v4(from + c);
-    // sf_k_stride > 0: straight into the GEMM's layout (one 4-byte store per scale int, each in another cache line);
-    // sf_k_stride <= 0: the row's scale ints contiguously into a row-major staging area of the owner, which brings them
-    // into GEMM order itself after the barrier. Scattered 4-byte stores are what NVLink handles worst: they cost 40 % of
-    // the push at 2 GPUs.
-    unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
-    for (int c = lane; c < sf_per_row; c += 32) {
-        const unsigned v = x_sf[static_cast<long long>(token) * sf_per_row + c];
-        if (sf_k_stride > 0)
-            sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(dest)] = v;
-        else
-            sf[static_cast<long long>(dest) * sf_per_row + c] = v;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int num_warps = gridDim.x * warps_per_cta;
+    for (int first = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * 32; first < num_entries; first += num_warps * 32) {
+        int my_row = -1, my_owner = 0;
+        if (first + lane < num_entries) {
+            my_row = dest_row[first + lane];
+            if (my_row >= 0) {
+                // the rank that computes this entry and the expert slot there: the expert's owner and its index among the
+                // owner's experts, unless the plan spilled the rows this rank routes to the expert (my_dest / my_slot)
+                const int expert = static_cast<int>(topk_idx[first + lane]);
+                my_owner = my_dest != nullptr ? my_dest[expert] : expert / experts_per_rank;
+                const int local_expert = my_slot != nullptr ? my_slot[expert] : expert - my_owner * experts_per_rank;
+                if (local_expert < local_expert_begin || local_expert >= local_expert_end) my_row = -1;
+            }
+        }
+        unsigned todo = __ballot_sync(0xffffffffu, my_row >= 0);
+        while (todo != 0) {
+            const int src_lane = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const int entry = first + src_lane;
+            const int dest = __shfl_sync(0xffffffffu, my_row, src_lane);
+            const int owner = __shfl_sync(0xffffffffu, my_owner, src_lane);
+            const int token = entry / topk;
+            const unsigned long long base = peers.p[owner];
+            warp_copy_row(reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes),
+                          reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * row_bytes), row_bytes, lane);
+            // sf_k_stride > 0: straight into the GEMM's layout (one 4-byte store per scale int, each in another cache line);
+            // sf_k_stride <= 0: the row's scale ints contiguously into a row-major staging area of the owner, which brings
+            // them into GEMM order itself after the barrier. Scattered 4-byte stores are what NVLink handles worst: they
+            // cost 40 % of the push at 2 GPUs.
+            unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
+            for (int c = lane; c < sf_per_row; c += 32) {
+                const unsigned v = x_sf[static_cast<long long>(token) * sf_per_row + c];
+                if (sf_k_stride > 0)
+                    sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(dest)] = v;
+                else
+                    sf[static_cast<long long>(dest) * sf_per_row + c] = v;
+            }
+            if (lane == 0) {
+                reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
+                reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;
+            }
+        }
     }
-    if (lane == 0) {
-        reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
-        reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;
+}
+
+// Return push of the expert-parallel layer: the BF16 output rows of the expert slots [slot_begin, slot_end) of this rank
+// go back to the ranks their tokens came from, row `entry` of the receiver's `returned` buffer ([entries per rank, hidden]
+// bf16; src_of_row[r] = source rank * entries_per_rank + entry, written by the dispatch push). A warp per row, rows of
+// the slots dealt round-robin to the grid's warps; local reads, remote writes, any grid and block size. The receiver
+// sums a token's rows itself once all of them have arrived (dgb200_moe_combine_returned_kernel).
+__global__ void __launch_bounds__(1024)
+dgb200_ep_return_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ src_of_row,
+                             const int* __restrict__ slot_start, const int* __restrict__ slot_end_rows, int slot_begin,
+                             int slot_end, int hidden, int entries_per_rank, const PeerTable peers, long long returned_offset) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int num_warps = gridDim.x * warps_per_cta;
+    const int warp = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int row_bytes = hidden * 2;
+    for (int v = slot_begin; v < slot_end; ++v) {
+        const int end = slot_end_rows[v];
+        for (int r = slot_start[v] + warp; r < end; r += num_warps) {
+            const int src = src_of_row[r];
+            const int rank = src / entries_per_rank, entry = src - rank * entries_per_rank;
+            warp_copy_row(reinterpret_cast<const uint4*>(rows + static_cast<long long>(r) * hidden),
+                          reinterpret_cast<uint4*>(peers.p[rank] + returned_offset + static_cast<long long>(entry) * row_bytes),
+                          row_bytes, lane);
+        }
+    }
+}
+
+// y[t, :] = bf16( sum over valid k, in ascending k, of float(returned[t * topk + k, :]) ) (+ the shared experts' row of the
+// token as one more slot): the combine over rows that dgb200_ep_return_rows_kernel of every computing rank stored into
+// this rank's `returned` buffer. Slots with dest_row < 0 (masked) are skipped. One CTA per token, a thread owns 8
+// consecutive channels; the same order of additions as the single-rank combine.
+__global__ void __launch_bounds__(128)
+dgb200_moe_combine_returned_kernel(const __nv_bfloat16* __restrict__ returned, const int* __restrict__ dest_row, int topk,
+                                   int hidden, const __nv_bfloat16* __restrict__ shared_rows, __nv_bfloat16* __restrict__ y) {
+    const int t = blockIdx.x;
+    __shared__ int valid[32];
+    if (threadIdx.x < 32) valid[threadIdx.x] = static_cast<int>(threadIdx.x) < topk && dest_row[static_cast<long long>(t) * topk + threadIdx.x] >= 0;
+    __syncthreads();
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int k = 0; k <= topk; ++k) {
+            const __nv_bfloat16* row;
+            if (k < topk) {
+                if (!valid[k]) continue;
+                row = returned + (static_cast<long long>(t) * topk + k) * hidden;
+            } else {
+                if (shared_rows == nullptr) continue;
+                row = shared_rows + static_cast<long long>(t) * hidden;
+            }
+            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(row) + c);
+            const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += __uint_as_float(w[i] << 16);
+                acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        reinterpret_cast<uint4*>(y + static_cast<long long>(t) * hidden)[c] = o;
     }
 }
 

@@ -45,6 +45,9 @@ int dgb200_get_num_sms(void);
  *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
  *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
  *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
+ *   "ep_comm_sms"        expert-parallel layer: SMs kept free of GEMM CTAs for the kernels that move rows between
+ *                        ranks while the GEMMs of other expert phases run (default 24, at most 64). 0 = no overlap: one
+ *                        stream, rows pulled by the combine. Every rank must use the same value.
  *   "peer_wait_us"       expert-parallel layer: how long a rank waits for a flag another rank writes before it gives
  *                        up, records DGB200 status code 7 (peer timeout) and carries on (default 10 s; at least 1). */
 int dgb200_set_tuning(const char* name, int32_t value);
@@ -320,7 +323,9 @@ typedef struct dgb200_mega_moe_args {
      * all ranks wait for it. With num_guest_experts = G > 0 (at most 8) every rank derives, from the exchanged
      * per-expert counts, the same plan that moves the rows some source ranks route to a hot expert onto a less loaded
      * rank; that rank computes them in one of its G guest slots with a copy of the expert's weights, which it fetches
-     * from the owner during the call. Outputs are the same bits as without the spill. Requirements: l1_w, l1_w_sf,
+     * from the owner during the call. A row's arithmetic does not depend on the rank that computes it; outputs can
+     * differ from a run without the spill only where the layer picks another tile orientation for an expert whose row
+     * count changed, or (with "ep_comm_sms" = 0) in the order of the combine's FP32 additions: last bits of FP32 sums. Requirements: l1_w, l1_w_sf,
      * l2_w, l2_w_sf of EVERY rank hold E_local + G experts (the guest slots, after the rank's own experts, are scratch
      * of the library) and are mapped into every process; peer_l1_w[r] ... peer_l2_w_sf[r] are the addresses of rank
      * r's four tensors in this process (host arrays of num_ranks entries; entry `rank` must equal l1_w ... l2_w_sf).
