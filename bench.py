@@ -72,15 +72,18 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    FIELDS = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
-              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
-              'clocks_event_reasons.sw_power_cap')
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs. nvidia-smi needs up to a
+    second to start on a box with eight GPUs, so it is started before the warm-up and the samples are cut to the timed
+    region afterwards by their timestamps (begin() / end() mark it)."""
+    FIELDS = ('timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+              'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+              'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.file = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
         self.proc = None
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
@@ -90,32 +93,55 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def begin(self):
+        import datetime
+        self.t_begin = datetime.datetime.now()
+
+    def end(self):
+        import datetime
+        self.t_end = datetime.datetime.now()
+
     def stop(self):
+        import datetime
         if self.proc is None:
             return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        if self.t_end is None:
+            self.end()
         time.sleep(0.15)
         self.proc.terminate()
         self.proc.wait()
         self.file.flush()
         self.file.seek(0)
-        clocks, max_clock, reasons = [], None, set()
+        rows = []  # (time, sm clock, max sm clock, reasons)
         for line in self.file.read().splitlines():
             parts = [p.strip() for p in line.split(',')]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                clocks.append(float(parts[1]))
-                max_clock = float(parts[2])
+                try:
+                    when = datetime.datetime.strptime(parts[0], '%Y/%m/%d %H:%M:%S.%f')
+                except ValueError:
+                    when = None  # unknown timestamp format: keep the sample, it cannot be cut to the window
+                rows.append((when, float(parts[2]), float(parts[3]),
+                             [name for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'),
+                                                        parts[6:10]) if val.lower().startswith('active')]))
             except ValueError:
                 continue
-            for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), parts[5:9]):
-                if val.lower().startswith('active'):
-                    reasons.add(name)
         self.file.close()
         os.unlink(self.file.name)
-        clocks.sort()
-        return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None, 'sm_max_mhz': max_clock,
-                'samples': len(clocks), 'reasons': sorted(reasons)}
+        window = 'timed region'
+        if self.t_begin is not None and rows and all(r[0] is not None for r in rows):
+            pad = datetime.timedelta(milliseconds=10)
+            inside = [r for r in rows if self.t_begin - pad <= r[0] <= self.t_end + pad]
+            if not inside and rows:  # a timed region shorter than the sampling period: the samples next to it
+                middle = self.t_begin + (self.t_end - self.t_begin) / 2
+                inside = sorted(rows, key=lambda r: abs((r[0] - middle).total_seconds()))[:3]
+                window = 'nearest samples (timed region shorter than the sampling period)'
+            rows = inside
+        clocks = sorted(r[1] for r in rows)
+        reasons = sorted({name for r in rows for name in r[3]})
+        return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None, 'sm_max_mhz': rows[-1][2] if rows else None,
+                'samples': len(clocks), 'reasons': reasons, 'window': window}
 
 
 def cpu_sample_pass(sample):
@@ -600,7 +626,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     logits = logits_host.cuda()
     y = torch.empty((t, h), dtype=torch.bfloat16, device='cuda')
     lib = _lib.lib()
-    kernels_per_step = kernels_of_one_step(nvfp4, world, cfg['local_experts'], guests)
+    kernels_per_step = kernels_of_one_step(nvfp4, world, cfg['local_experts'], guests, args.comm_sms)
 
     def step(events=None, x_in=None, logits_in=None, y_out=None):
         x_in, logits_in, y_out = (x if x_in is None else x_in), (logits if logits_in is None else logits_in), (y if y_out is None else y_out)
@@ -621,6 +647,8 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         torch.cuda.synchronize()
 
     # ---- device-resident timing
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     barrier()
     for _ in range(warmup):
         step()
@@ -631,15 +659,15 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         for ev in evs:
             ev.record()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.begin()
     t0.record()
     for s in range(steps):
         step(stage_events[s])
     t1.record()
     barrier()
+    sampler.end()
     clocks = sampler.stop()
     ms_per_step = t0.elapsed_time(t1) / steps
     _lib.device_status()
@@ -762,8 +790,8 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         # stage times of the most loaded rank (rank `stages_rank`); with several ranks the cross-rank waits are inside
         'stages_ms': ({'plan': stage_ms[0], 'dispatch': stage_ms[1], 'l1_gemm_swiglu': stage_ms[2],
                        'l2_gemm': stage_ms[3], 'combine': stage_ms[4]} if not gemms_in_one_interval else
-                      {'plan': stage_ms[0], 'dispatch_until_first_phase_landed': stage_ms[1],
-                       'gemms_all_phases': stage_ms[2] + stage_ms[3], 'return_tail_and_combine': stage_ms[4]}),
+                      {'plan': stage_ms[0], 'dispatch_push': stage_ms[1],
+                       'gemms_and_return_push': stage_ms[2] + stage_ms[3], 'waits_and_combine': stage_ms[4]}),
         'stages_rank': hot,
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9 if not gemms_in_one_interval else None,
         'tflops': tflops,
@@ -801,16 +829,16 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     return line, (l1, l2)
 
 
-def kernels_of_one_step(nvfp4, world, local_experts, guests=0):
+def kernels_of_one_step(nvfp4, world, local_experts, guests=0, comm_sms=0):
     """Launches of this library's kernels in one pass of the layer (memsets are not kernels of ours). FP8 layer on one
     rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the two tile orientations
     (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather. Expert parallel, P =
-    min(4, expert slots) phases: router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
+    phases (one with guest experts on one stream, else min(4, expert slots)): router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
     flag + scale reorder + L1 + L2, return push + flag, and at the end a flag wait per phase and the combine; with guest
     experts one more launch fetches their weights and the guest slots count as experts."""
     if world == 1:
         return 9 if nvfp4 else 11
-    phases = min(4, local_experts + guests)
+    phases = 1 if (guests and comm_sms <= 0) else min(4, local_experts + guests)
     return 7 + 9 * phases + 1 + (1 if guests else 0)
 
 

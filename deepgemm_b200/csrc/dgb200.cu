@@ -67,8 +67,8 @@ struct Tuning {
     int mlp_kernel = -1;  // FP8 x FP4 layer GEMMs: 0 = separate gate/up and down kernels (tokens-on-M / swapped split),
                           // 1 = the fused expert-MLP kernel on single CTAs, 2 = on CTA pairs; -1 = not yet read from
                           // the environment (DGB200_MLP_KERNEL, default below)
-    int ep_comm_sms = 24;  // expert-parallel layer: SMs kept free of GEMM CTAs for the kernels that move rows over NVLink
-                           // while the GEMMs run (0 = no overlap: one stream, pull combine)
+    int ep_comm_sms = 0;  // expert-parallel layer: SMs kept free of GEMM CTAs for kernels that move rows over NVLink on a
+                          // second stream while the GEMMs run (0 = one stream: every kernel on all SMs)
     long long peer_wait_cycles = 20000000000ll;  // budget of a wait for another rank, SM clock cycles (about 10 s: ranks
                                                  // may reach their first call seconds apart)
 };
@@ -343,16 +343,29 @@ int ep_streams_for_current_device(EpStreams** out) {
     return 0;
 }
 
-// Launch shape of a row-moving kernel that shares the GPU with GEMMs: `sms` CTAs of 1024 threads that each ask for so
-// much dynamic shared memory that no second one (and no GEMM CTA) fits on their SM, so together they occupy exactly
-// `sms` SMs instead of a few warps on every SM (the block scheduler spreads small CTAs over all SMs, and a GEMM CTA
-// needs a whole SM's registers).
-constexpr int kCommCtaThreads = 1024;
+// Launch shape of a row-moving kernel (dispatch push, return push): as many warps per CTA as row-sized slots fit into
+// an SM's shared memory (one row in flight per warp), one CTA per SM. Beside GEMMs it runs as `comm_sms` such CTAs, each
+// asking for at least kCommCtaSmemBytes of dynamic shared memory so that no second one and no GEMM CTA fits on its SM:
+// together they occupy exactly `comm_sms` SMs instead of a few warps on every SM (the block scheduler spreads small
+// CTAs over all SMs, and a GEMM CTA needs a whole SM's registers). Alone on the GPU it runs on every SM.
 constexpr int kCommCtaSmemBytes = 120 * 1024;
 
+struct RowMoverLaunch {
+    int warps;
+    int smem_bytes;
+};
+
+inline RowMoverLaunch row_mover_launch(long long slot_bytes, bool beside_gemms) {
+    RowMoverLaunch r;
+    r.warps = static_cast<int>(std::max(1ll, std::min<long long>(kRowMoverMaxWarps, (kRowMoverSmemBudget - 512) / slot_bytes)));
+    const long long need = (r.warps * 8 + 15) / 16 * 16 + r.warps * slot_bytes;
+    r.smem_bytes = static_cast<int>(beside_gemms ? std::max<long long>(need, kCommCtaSmemBytes) : need);
+    return r;
+}
+
 template <typename Kernel>
-int allow_comm_smem(Kernel kernel) {
-    DGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommCtaSmemBytes));
+int allow_row_mover_smem(Kernel kernel) {
+    DGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowMoverSmemBudget));
     return 0;
 }
 
@@ -455,8 +468,8 @@ struct MegaLayout {
     long long l1_acts, l1_sf, l2_acts, l2_sf, l2_out;  // l2_out: bf16 [max_rows, hidden], the rows the combine gathers
     long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
-    long long combine_partial;  // expert parallel: fp32 [max tokens, hidden], the running sums of the phased combine
-    long long returned;  // expert parallel: bf16 [max tokens * topk, hidden], the output rows the computing ranks sent back
+    long long combine_partial;  // expert parallel, pull combine: fp32 [max tokens, hidden], the running sums between phases
+    long long returned;  // expert parallel, return push: bf16 [max tokens * topk, hidden], the output rows the computing ranks sent back
     long long tile_done;  // FP8 kind: one counter per token tile of the fused expert-MLP kernel (max_rows / 128 + local experts)
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
     long long shared_x_sf, shared_l2_acts, shared_l2_sf, shared_out;
@@ -972,7 +985,11 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     }
     const int* my_dest = spill ? reinterpret_cast<const int*>(base + l.my_dest) : nullptr;
     const int* my_slot = spill ? reinterpret_cast<const int*>(base + l.my_slot) : nullptr;
-    const int phases = fused_mlp ? 1 : std::min(kMaxEpPhases, V);
+    // Expert phases: several when their transfers can hide something, i.e. under other phases' GEMMs on the second stream
+    // (ep_comm_sms > 0) or behind the most loaded rank's GEMMs when rows stay on their owners; with balanced loads on one
+    // stream a single phase (fewer launches, larger GEMMs).
+    const int comm_sms = tuning().ep_comm_sms;
+    const int phases = fused_mlp ? 1 : std::min((spill && comm_sms == 0) ? 1 : kMaxEpPhases, V);
     int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
     const int* expert_start = reinterpret_cast<const int*>(base + l.expert_start);
@@ -1022,15 +1039,21 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     // GEMMs leave free: the pushes of later phases under the GEMMs of earlier ones, and the output rows of a finished
     // phase go back to their source ranks (return push) under the GEMMs of the next; the combine is then a local sum.
     // Otherwise everything runs on the caller's stream and the combine pulls the rows phase by phase.
-    const int comm_sms = tuning().ep_comm_sms;
     const bool overlap = phases > 1 && comm_sms > 0;
-    const int push_grid = std::max(1, (entries + 7) / 8);
+    int all_sms = 0;
+    if ((rc = effective_num_sms(&all_sms))) return rc;
+    const long long push_slot_bytes = act_row_bytes(quant.kind, hidden) + ((4 * sf_per_row) % 16 == 0 ? 4ll * sf_per_row : 0);
+    DGB_REQUIRE(push_slot_bytes % 16 == 0 && push_slot_bytes <= kRowMoverSmemBudget - 1024 && hidden * 2ll <= kRowMoverSmemBudget - 1024,
+                "rows of %lld bytes do not fit the row movers' shared-memory slots", push_slot_bytes);
+    if ((rc = allow_row_mover_smem(dgb200_ep_push_kernel))) return rc;
+    if ((rc = allow_row_mover_smem(dgb200_ep_return_rows_kernel))) return rc;
     auto push = [&](int q, cudaStream_t on, bool few_sms) {
         if (entries <= 0) return;
-        dgb200_ep_push_kernel<<<few_sms ? comm_sms : push_grid, few_sms ? kCommCtaThreads : 256, few_sms ? kCommCtaSmemBytes : 0, on>>>(
+        const RowMoverLaunch shape = row_mover_launch(push_slot_bytes, few_sms);
+        dgb200_ep_push_kernel<<<few_sms ? comm_sms : all_sms, shape.warps * 32, shape.smem_bytes, on>>>(
             base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
             static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, E, rank, entries_per_rank, peers, l.l1_acts,
-            l.l1_sf_stage, 0, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1), my_dest, my_slot);
+            l.l1_sf_stage, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1), my_dest, my_slot);
     };
     auto fetch_guests = [&](cudaStream_t on) {
         // the weights of the experts this rank hosts as a guest, from their owners
@@ -1053,6 +1076,23 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                                phases == 1 ? 0 : g0, phases == 1 ? 0 : g1);
     };
 
+    // the BF16 output rows of phase q's expert slots back to the ranks their tokens came from
+    auto return_rows = [&](int q, cudaStream_t on, bool few_sms) {
+        const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
+        if (g1 == g0) return;
+        const RowMoverLaunch shape = row_mover_launch(hidden * 2ll, few_sms);
+        dgb200_ep_return_rows_kernel<<<few_sms ? comm_sms : all_sms, shape.warps * 32, shape.smem_bytes, on>>>(
+            reinterpret_cast<const __nv_bfloat16*>(base + l.l2_out), reinterpret_cast<const int*>(base + l.src_of_row), expert_start,
+            expert_end, g0, g1, hidden, entries_per_rank, peers, l.returned);
+    };
+    // once every rank's rows of every phase have arrived: a local sum per token, in slot order
+    auto combine = [&]() {
+        if (num_tokens > 0)
+            dgb200_moe_combine_returned_kernel<<<num_tokens, 128, 0, stream>>>(
+                reinterpret_cast<const __nv_bfloat16*>(base + l.returned), dest_row, num_topk, hidden,
+                with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
+    };
+
     if (!overlap) {
         for (int q = 0; q < phases; ++q) {
             push(q, stream, false);
@@ -1062,10 +1102,14 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         if (spill) fetch_guests(stream);
         DGB_CUDA(cudaGetLastError());
         if ((rc = record_stage(2, stream))) return rc;
-        // GEMMs, phase by phase, each as soon as every rank's rows for the phase have landed
+        // GEMMs, phase by phase, each as soon as every rank's rows for the phase have landed. How the output rows get back
+        // to the tokens' ranks depends on who has time: with balanced loads (spill) the computing rank pushes them right
+        // away and the combine is a local sum; when rows stay on their owners the most loaded rank is the critical path
+        // and the others idle, so those pull the rows of each finished phase themselves (phased combine).
         for (int q = 0; q < phases; ++q) {
             flag(1 + q, 0, 1);
             if ((rc = gemms(q))) return rc;
+            if (spill) return_rows(q, stream, false);
             flag(1 + kMaxEpPhases + q, 1, 0);
         }
         if ((rc = record_stage(3, stream))) return rc;  // both GEMMs of all phases lie before this point
@@ -1074,24 +1118,22 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
             if (quant.kind != kKindBf16 && (rc = run_shared_x_sf(l, base, num_tokens, hidden, stream))) return rc;
             if ((rc = run_shared_gemms(quant, l, base, num_tokens, hidden, activation_clamp, fast_math, stream))) return rc;
         }
-        // combine, phase by phase, each as soon as every rank has finished the phase's experts
         for (int q = 0; q < phases; ++q) {
             flag(1 + kMaxEpPhases + q, 0, 1);
-            if (num_tokens > 0)
+            if (!spill && num_tokens > 0)
                 dgb200_moe_combine_phase_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
                     peers, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
                     with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
                     reinterpret_cast<float*>(base + l.combine_partial), static_cast<__nv_bfloat16*>(y), phase_begin(q), phase_begin(q + 1),
                     q == 0 ? 1 : 0, q == phases - 1 ? 1 : 0, my_dest, my_slot);
         }
+        if (spill) combine();
         DGB_CUDA(cudaGetLastError());
         return record_stage(5, stream);
     }
 
     EpStreams* ep = nullptr;
     if ((rc = ep_streams_for_current_device(&ep))) return rc;
-    if ((rc = allow_comm_smem(dgb200_ep_push_kernel))) return rc;
-    if ((rc = allow_comm_smem(dgb200_ep_return_rows_kernel))) return rc;
     std::lock_guard<std::mutex> ep_lock(ep->mu);
     cudaStream_t comm = ep->comm;
     auto flag_on = [&](cudaStream_t on, int row, int do_signal, int do_wait) {
@@ -1121,13 +1163,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         DGB_CUDA(cudaEventRecord(ep->computed[q], stream));
         // second stream: this phase's output rows back to their source ranks, then "outputs q" to every rank
         DGB_CUDA(cudaStreamWaitEvent(comm, ep->computed[q], 0));
-        const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
-        if (g1 > g0) {
-            const bool last = q == phases - 1;  // nothing runs next to the last one: all SMs
-            dgb200_ep_return_rows_kernel<<<last ? 592 : comm_sms, last ? 256 : kCommCtaThreads, last ? 0 : kCommCtaSmemBytes, comm>>>(
-                reinterpret_cast<const __nv_bfloat16*>(base + l.l2_out), reinterpret_cast<const int*>(base + l.src_of_row), expert_start,
-                expert_end, g0, g1, hidden, entries_per_rank, peers, l.returned);
-        }
+        return_rows(q, comm, q < phases - 1);  // nothing runs next to the last one: all SMs
         flag_on(comm, 1 + kMaxEpPhases + q, 1, 0);
     }
     DGB_CUDA(cudaGetLastError());
@@ -1141,12 +1177,8 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     }
     DGB_CUDA(cudaStreamWaitEvent(stream, ep->returned, 0));
     if (rc_gemm) return rc_gemm;
-    // combine: once every rank's rows of every phase have arrived, a local sum in slot order
     for (int q = 0; q < phases; ++q) flag_on(stream, 1 + kMaxEpPhases + q, 0, 1);
-    if (num_tokens > 0)
-        dgb200_moe_combine_returned_kernel<<<num_tokens, 128, 0, stream>>>(
-            reinterpret_cast<const __nv_bfloat16*>(base + l.returned), dest_row, num_topk, hidden,
-            with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
+    combine();
     DGB_CUDA(cudaGetLastError());
     return record_stage(5, stream);
 }

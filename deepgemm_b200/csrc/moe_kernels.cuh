@@ -258,81 +258,6 @@ dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const lo
     }
 }
 
-// The combine of the expert-parallel layer, one phase of the local experts at a time: phase q adds, for every token, the
-// rows of the slots whose expert (numbered within its owner) lies in [local_expert_begin, local_expert_end), read in
-// place from the owners over NVLink. The running sum of a token is kept in FP32 in `partial` ([tokens, hidden]) between
-// phases: the first phase starts from zero (or from the shared experts' row), the last one writes bf16 y. The rows of a
-// phase can be pulled as soon as every rank has finished that phase's experts, while later phases are still being
-// computed; within a phase the slots are added in ascending order. Tokens without a slot in a middle phase are skipped.
-__global__ void __launch_bounds__(128)
-dgb200_moe_combine_phase_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
-                                const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
-                                const __nv_bfloat16* __restrict__ shared_rows, float* __restrict__ partial,
-                                __nv_bfloat16* __restrict__ y, int local_expert_begin, int local_expert_end, int first, int last,
-                                const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
-    const int t = blockIdx.x;
-    extern __shared__ unsigned long long slot_rows[];  // address of each slot's row of this phase, 0 = skip
-    __shared__ int any;
-    if (threadIdx.x == 0) any = 0;
-    __syncthreads();
-    if (threadIdx.x < topk) {
-        const int d = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
-        unsigned long long addr = 0;
-        if (d >= 0) {
-            const int e = static_cast<int>(topk_idx[static_cast<long long>(t) * topk + threadIdx.x]);
-            // computing rank and expert slot: the owner and the expert's index there, or what the spill plan says
-            const int owner = my_dest != nullptr ? my_dest[e] : e / experts_per_rank;
-            const int local_expert = my_slot != nullptr ? my_slot[e] : e - owner * experts_per_rank;
-            if (local_expert >= local_expert_begin && local_expert < local_expert_end) {
-                addr = peers.p[owner] + rows_offset + static_cast<unsigned long long>(d) * hidden * 2;
-                any = 1;
-            }
-        }
-        slot_rows[threadIdx.x] = addr;
-    }
-    __syncthreads();
-    if (!any && !first && !last) return;
-    float* part = partial + static_cast<long long>(t) * hidden;
-    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (!first) {
-            const float4 a = reinterpret_cast<const float4*>(part)[2 * c], b = reinterpret_cast<const float4*>(part)[2 * c + 1];
-            acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
-        }
-        for (int k = 0; k < topk; ++k) {
-            const unsigned long long addr = slot_rows[k];
-            if (addr == 0) continue;
-            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(addr) + c);
-            const unsigned w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[2 * i] += __uint_as_float(w[i] << 16);
-                acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
-            }
-        }
-        if (last) {
-            if (shared_rows != nullptr) {  // the shared experts' row is the slot after the top-k ones
-                const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(shared_rows + static_cast<long long>(t) * hidden) + c);
-                const unsigned w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    acc[2 * i] += __uint_as_float(w[i] << 16);
-                    acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
-                }
-            }
-            uint4 o;
-            o.x = pack_bf16x2(acc[0], acc[1]);
-            o.y = pack_bf16x2(acc[2], acc[3]);
-            o.z = pack_bf16x2(acc[4], acc[5]);
-            o.w = pack_bf16x2(acc[6], acc[7]);
-            reinterpret_cast<uint4*>(y + static_cast<long long>(t) * hidden)[c] = o;
-        } else {
-            reinterpret_cast<float4*>(part)[2 * c] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            reinterpret_cast<float4*>(part)[2 * c + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        }
-    }
-}
-
 // ==================================================================================================================
 // Expert-parallel dispatch: ranks own contiguous blocks of experts (expert e lives on rank e / experts_per_rank, as
 // in the reference: deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:372,389). Every rank holds one
@@ -483,6 +408,81 @@ dgb200_ep_plan_kernel(const int* __restrict__ all_counts, int num_experts, int n
         }
         if (owner == my_rank && threadIdx.x == 0) total_rows[0] = carry;
         __syncthreads();
+    }
+}
+
+// The combine of the expert-parallel layer, one phase of the local experts at a time: phase q adds, for every token, the
+// rows of the slots whose expert (numbered within its owner) lies in [local_expert_begin, local_expert_end), read in
+// place from the owners over NVLink. The running sum of a token is kept in FP32 in `partial` ([tokens, hidden]) between
+// phases: the first phase starts from zero (or from the shared experts' row), the last one writes bf16 y. The rows of a
+// phase can be pulled as soon as every rank has finished that phase's experts, while later phases are still being
+// computed; within a phase the slots are added in ascending order. Tokens without a slot in a middle phase are skipped.
+__global__ void __launch_bounds__(128)
+dgb200_moe_combine_phase_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
+                                const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
+                                const __nv_bfloat16* __restrict__ shared_rows, float* __restrict__ partial,
+                                __nv_bfloat16* __restrict__ y, int local_expert_begin, int local_expert_end, int first, int last,
+                                const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
+    const int t = blockIdx.x;
+    extern __shared__ unsigned long long slot_rows[];  // address of each slot's row of this phase, 0 = skip
+    __shared__ int any;
+    if (threadIdx.x == 0) any = 0;
+    __syncthreads();
+    if (threadIdx.x < topk) {
+        const int d = dest_row[static_cast<long long>(t) * topk + threadIdx.x];
+        unsigned long long addr = 0;
+        if (d >= 0) {
+            const int e = static_cast<int>(topk_idx[static_cast<long long>(t) * topk + threadIdx.x]);
+            // computing rank and expert slot: the owner and the expert's index there, or what the spill plan says
+            const int owner = my_dest != nullptr ? my_dest[e] : e / experts_per_rank;
+            const int local_expert = my_slot != nullptr ? my_slot[e] : e - owner * experts_per_rank;
+            if (local_expert >= local_expert_begin && local_expert < local_expert_end) {
+                addr = peers.p[owner] + rows_offset + static_cast<unsigned long long>(d) * hidden * 2;
+                any = 1;
+            }
+        }
+        slot_rows[threadIdx.x] = addr;
+    }
+    __syncthreads();
+    if (!any && !first && !last) return;
+    float* part = partial + static_cast<long long>(t) * hidden;
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (!first) {
+            const float4 a = reinterpret_cast<const float4*>(part)[2 * c], b = reinterpret_cast<const float4*>(part)[2 * c + 1];
+            acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+        }
+        for (int k = 0; k < topk; ++k) {
+            const unsigned long long addr = slot_rows[k];
+            if (addr == 0) continue;
+            const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(addr) + c);
+            const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += __uint_as_float(w[i] << 16);
+                acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+        if (last) {
+            if (shared_rows != nullptr) {  // the shared experts' row is the slot after the top-k ones
+                const uint4 v = ld_global_nc_v4(reinterpret_cast<const uint4*>(shared_rows + static_cast<long long>(t) * hidden) + c);
+                const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] += __uint_as_float(w[i] << 16);
+                    acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+                }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]);
+            o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]);
+            o.w = pack_bf16x2(acc[6], acc[7]);
+            reinterpret_cast<uint4*>(y + static_cast<long long>(t) * hidden)[c] = o;
+        } else {
+            reinterpret_cast<float4*>(part)[2 * c] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            reinterpret_cast<float4*>(part)[2 * c + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
     }
 }
 
@@ -707,40 +707,79 @@ dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries,
     dest_row[i] = my_base[e] + chunk_hist[static_cast<long long>(blockIdx.x) * num_experts + e] + before + rank_in_warp;
 }
 
-// Copies `bytes` (a multiple of 16) from `from` to `to` with the whole warp, up to seven 16-byte loads per lane in flight
-// before the first store: the copies of the expert-parallel layer read local memory and write a peer's, and may run on
-// a handful of SMs next to the GEMMs, so the memory-level parallelism has to come from each thread.
-__device__ __forceinline__ void warp_copy_row(const uint4* __restrict__ from, uint4* __restrict__ to, int bytes, int lane) {
-    const int vecs = bytes / 16;
-    for (int c0 = lane; c0 < vecs; c0 += 32 * 7) {
-        uint4 v[7];
-#pragma unroll
-        for (int j = 0; j < 7; ++j)
-            if (c0 + 32 * j < vecs) v[j] = ld_global_nc_v4(from + c0 + 32 * j);
-#pragma unroll
-        for (int j = 0; j < 7; ++j)
-            if (c0 + 32 * j < vecs) to[c0 + 32 * j] = v[j];
-    }
+// ---- rows between ranks through the bulk-copy unit --------------------------------------------------------------------------
+// The kernels that move rows between ranks (dispatch push, return push) read local memory and write a peer's. While GEMMs
+// hold most SMs they run on a handful of SMs, so what they move is bounded by the bytes each SM keeps in flight: every
+// warp owns one row-sized slot of shared memory and one mbarrier, and its first lane copies a row as
+//   cp.async.bulk global -> slot (completes on the mbarrier) ; cp.async.bulk slot -> peer global (bulk group),
+// so a CTA has one row per warp in flight (some 200 KB per SM) without holding it in registers. Every wait is bounded.
+constexpr int kRowMoverMaxWarps = 32;
+constexpr int kRowMoverSmemBudget = 216 * 1024;
+
+struct RowMover {
+    uint32_t slot;        // shared-memory address of this warp's slot
+    uint64_t* bar;        // its mbarrier
+    uint32_t parity;      // phase the next load completes
+    volatile uint32_t* abort_flag;
+};
+
+// Shared-memory carve-up of a row-moving CTA: [warps] mbarriers, then [warps] slots of slot_bytes (16-byte multiples).
+__device__ __forceinline__ RowMover row_mover_init(unsigned char* smem, int slot_bytes, volatile uint32_t* abort_flag) {
+    const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if ((threadIdx.x & 31) == 0) mbar_init(&bars[warp], 1);
+    fence_mbar_init();
+    __syncthreads();
+    RowMover m;
+    m.bar = &bars[warp];
+    m.slot = smem_u32(smem + ((warps * 8 + 15) / 16 * 16) + static_cast<long long>(warp) * slot_bytes);
+    m.parity = 0;
+    m.abort_flag = abort_flag;
+    return m;
+}
+
+// Called by lane 0 of a warp: copies bytes0 from src0 to dst0 and (bytes1 > 0) bytes1 from src1 to dst1 through the warp's
+// slot. Returns false when a wait ran out (recorded in the status block).
+__device__ __forceinline__ bool row_mover_copy(RowMover& m, const void* src0, void* dst0, uint32_t bytes0, const void* src1, void* dst1,
+                                               uint32_t bytes1) {
+    bulk_wait_group_read_all();  // the store that last used the slot has read it
+    mbar_arrive_expect_tx(m.bar, bytes0 + bytes1);
+    bulk_load_1d(m.slot, src0, bytes0, m.bar);
+    if (bytes1 > 0) bulk_load_1d(m.slot + bytes0, src1, bytes1, m.bar);
+    if (!mbar_wait(m.bar, m.parity, m.abort_flag, kTimeoutRowMover, static_cast<int>(blockIdx.x))) return false;
+    m.parity ^= 1u;
+    bulk_store_1d(dst0, m.slot, bytes0);
+    if (bytes1 > 0) bulk_store_1d(dst1, m.slot + bytes0, bytes1);
+    bulk_commit_group();
+    return true;
 }
 
 // Dispatch push of the expert-parallel layer: every entry (token, k) of this rank whose expert slot lies in
 // [local_expert_begin, local_expert_end) is stored into the buffers of the rank that computes it: the token's quantised
-// row, its packed scales, the routing weight and the source id. A warp examines 32 entries at a time (one per lane) and
-// then copies the rows of those that belong to the phase one after the other, so a launch that pushes one phase of the
-// experts skips the other entries cheaply. Any grid and block size: while GEMMs hold most SMs the layer launches this
-// kernel on the few SMs it kept free.
+// row and its packed scale ints (row-major staging area of the receiver, which brings them into GEMM order itself: one
+// 4-byte remote store per scale int, each in another cache line, cost 40 % of the push), the routing weight and the
+// source id. A warp examines 32 entries at a time (one per lane), then its first lane moves the rows of those that
+// belong to the phase one after the other, so a launch that pushes one phase of the experts skips the other entries
+// cheaply. Any grid; dynamic shared memory: row_mover_smem_bytes(warps, row_bytes + 4 * sf_per_row) or more.
 __global__ void __launch_bounds__(1024)
 dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __restrict__ x_sf,
                       const long long* __restrict__ topk_idx, const float* __restrict__ topk_weights,
                       const int* __restrict__ dest_row, int num_entries, int topk, int row_bytes, int sf_per_row,
                       int experts_per_rank, int my_rank, int entries_per_rank, const PeerTable peers,
-                      long long acts_offset, long long sf_offset, long long sf_k_stride, long long weight_offset,
+                      long long acts_offset, long long sf_offset, long long weight_offset,
                       long long src_offset, int local_expert_begin, int local_expert_end,
                       const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
+    extern __shared__ __align__(16) unsigned char mover_smem[];
+    __shared__ uint32_t abort_flag;
+    const int sf_bytes = sf_per_row * 4;
+    const int bulk_sf_bytes = sf_bytes % 16 == 0 ? sf_bytes : 0;  // a bulk copy moves multiples of 16 bytes; else plain stores
+    RowMover mover = row_mover_init(mover_smem, row_bytes + bulk_sf_bytes, &abort_flag);
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int num_warps = gridDim.x * warps_per_cta;
-    for (int first = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * 32; first < num_entries; first += num_warps * 32) {
+    bool ok = true;
+    for (int first = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * 32; first < num_entries && ok; first += num_warps * 32) {
         int my_row = -1, my_owner = 0;
         if (first + lane < num_entries) {
             my_row = dest_row[first + lane];
@@ -754,60 +793,62 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
             }
         }
         unsigned todo = __ballot_sync(0xffffffffu, my_row >= 0);
-        while (todo != 0) {
+        while (todo != 0 && ok) {
             const int src_lane = __ffs(todo) - 1;
             todo &= todo - 1;
             const int entry = first + src_lane;
             const int dest = __shfl_sync(0xffffffffu, my_row, src_lane);
             const int owner = __shfl_sync(0xffffffffu, my_owner, src_lane);
-            const int token = entry / topk;
-            const unsigned long long base = peers.p[owner];
-            warp_copy_row(reinterpret_cast<const uint4*>(x + static_cast<long long>(token) * row_bytes),
-                          reinterpret_cast<uint4*>(base + acts_offset + static_cast<long long>(dest) * row_bytes), row_bytes, lane);
-            // sf_k_stride > 0: straight into the GEMM's layout (one 4-byte store per scale int, each in another cache line);
-            // sf_k_stride <= 0: the row's scale ints contiguously into a row-major staging area of the owner, which brings
-            // them into GEMM order itself after the barrier. Scattered 4-byte stores are what NVLink handles worst: they
-            // cost 40 % of the push at 2 GPUs.
-            unsigned* sf = reinterpret_cast<unsigned*>(base + sf_offset);
-            for (int c = lane; c < sf_per_row; c += 32) {
-                const unsigned v = x_sf[static_cast<long long>(token) * sf_per_row + c];
-                if (sf_k_stride > 0)
-                    sf[static_cast<long long>(c) * sf_k_stride + sf_row_in_cp_order(dest)] = v;
-                else
-                    sf[static_cast<long long>(dest) * sf_per_row + c] = v;
-            }
             if (lane == 0) {
+                const int token = entry / topk;
+                const unsigned long long base = peers.p[owner];
+                ok = row_mover_copy(mover, x + static_cast<long long>(token) * row_bytes,
+                                    reinterpret_cast<void*>(base + acts_offset + static_cast<long long>(dest) * row_bytes),
+                                    static_cast<uint32_t>(row_bytes), x_sf + static_cast<long long>(token) * sf_per_row,
+                                    reinterpret_cast<void*>(base + sf_offset + static_cast<long long>(dest) * sf_bytes),
+                                    static_cast<uint32_t>(bulk_sf_bytes));
+                if (bulk_sf_bytes == 0)
+                    for (int c = 0; c < sf_per_row; ++c)
+                        reinterpret_cast<unsigned*>(base + sf_offset)[static_cast<long long>(dest) * sf_per_row + c] =
+                            x_sf[static_cast<long long>(token) * sf_per_row + c];
                 reinterpret_cast<float*>(base + weight_offset)[dest] = topk_weights[entry];
                 reinterpret_cast<int*>(base + src_offset)[dest] = my_rank * entries_per_rank + entry;
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
     }
+    if (lane == 0) bulk_wait_group_all();  // this warp's stores are complete before the kernel ends
 }
 
 // Return push of the expert-parallel layer: the BF16 output rows of the expert slots [slot_begin, slot_end) of this rank
 // go back to the ranks their tokens came from, row `entry` of the receiver's `returned` buffer ([entries per rank, hidden]
 // bf16; src_of_row[r] = source rank * entries_per_rank + entry, written by the dispatch push). A warp per row, rows of
-// the slots dealt round-robin to the grid's warps; local reads, remote writes, any grid and block size. The receiver
-// sums a token's rows itself once all of them have arrived (dgb200_moe_combine_returned_kernel).
+// the slots dealt round-robin to the grid's warps. The receiver sums a token's rows itself once all of them have arrived
+// (dgb200_moe_combine_returned_kernel). Dynamic shared memory as for the dispatch push, slot = one row.
 __global__ void __launch_bounds__(1024)
 dgb200_ep_return_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ src_of_row,
                              const int* __restrict__ slot_start, const int* __restrict__ slot_end_rows, int slot_begin,
                              int slot_end, int hidden, int entries_per_rank, const PeerTable peers, long long returned_offset) {
-    const int lane = threadIdx.x & 31;
+    extern __shared__ __align__(16) unsigned char mover_smem[];
+    __shared__ uint32_t abort_flag;
+    const int row_bytes = hidden * 2;
+    RowMover mover = row_mover_init(mover_smem, row_bytes, &abort_flag);
+    if ((threadIdx.x & 31) != 0) return;  // one lane per warp drives the copies
     const int warps_per_cta = blockDim.x >> 5;
     const int num_warps = gridDim.x * warps_per_cta;
     const int warp = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
-    const int row_bytes = hidden * 2;
-    for (int v = slot_begin; v < slot_end; ++v) {
+    bool ok = true;
+    for (int v = slot_begin; v < slot_end && ok; ++v) {
         const int end = slot_end_rows[v];
-        for (int r = slot_start[v] + warp; r < end; r += num_warps) {
+        for (int r = slot_start[v] + warp; r < end && ok; r += num_warps) {
             const int src = src_of_row[r];
             const int rank = src / entries_per_rank, entry = src - rank * entries_per_rank;
-            warp_copy_row(reinterpret_cast<const uint4*>(rows + static_cast<long long>(r) * hidden),
-                          reinterpret_cast<uint4*>(peers.p[rank] + returned_offset + static_cast<long long>(entry) * row_bytes),
-                          row_bytes, lane);
+            ok = row_mover_copy(mover, rows + static_cast<long long>(r) * hidden,
+                                reinterpret_cast<void*>(peers.p[rank] + returned_offset + static_cast<long long>(entry) * row_bytes),
+                                static_cast<uint32_t>(row_bytes), nullptr, nullptr, 0u);
         }
     }
+    bulk_wait_group_all();
 }
 
 // y[t, :] = bf16( sum over valid k, in ascending k, of float(returned[t * topk + k, :]) ) (+ the shared experts' row of the

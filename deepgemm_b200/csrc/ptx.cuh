@@ -36,6 +36,7 @@ enum StatusCode : int {
     kBadArgument = 6,
     kTimeoutPeer = 7,       // waited for a flag another rank writes
     kTimeoutGrid = 8,       // waited for a flag another CTA of this grid writes
+    kTimeoutRowMover = 9,   // a row-moving warp waited for its bulk load
 };
 
 __device__ __forceinline__ void report_error(int code, int a, int b) {
@@ -184,6 +185,16 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 __device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // Returns once those stores are complete (their writes performed).
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes): global -> shared completing on an
+// mbarrier of this CTA, and shared -> global as part of the thread's bulk async-group.
+__device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* gmem_dst, uint32_t smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(gmem_dst), "r"(smem_src), "r"(bytes) : "memory");
+}
 
 // L2 prefetch of one contiguous span (16-byte aligned address, size a multiple of 16 bytes): starts the HBM read
 // early without occupying shared memory; handled by the bulk-copy unit, no completion to wait for.

@@ -45,9 +45,11 @@ int dgb200_get_num_sms(void);
  *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
  *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
  *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
- *   "ep_comm_sms"        expert-parallel layer: SMs kept free of GEMM CTAs for the kernels that move rows between
- *                        ranks while the GEMMs of other expert phases run (default 24, at most 64). 0 = no overlap: one
- *                        stream, rows pulled by the combine. Every rank must use the same value.
+ *   "ep_comm_sms"        expert-parallel layer: 0 (default) = every kernel on the caller's stream and on all SMs.
+ *                        n > 0 (at most 64) = the kernels that move rows between ranks run on a second, library-owned
+ *                        stream on n SMs that the GEMMs leave free, beside the GEMMs of other expert phases (measured
+ *                        on B200: an SM moves about 5 GB/s over NVLink, so hiding the transfers costs more SMs than it
+ *                        saves time at 4 and 8 ranks). Every rank must use the same value.
  *   "peer_wait_us"       expert-parallel layer: how long a rank waits for a flag another rank writes before it gives
  *                        up, records DGB200 status code 7 (peer timeout) and carries on (default 10 s; at least 1). */
 int dgb200_set_tuning(const char* name, int32_t value);
@@ -325,7 +327,7 @@ typedef struct dgb200_mega_moe_args {
      * rank; that rank computes them in one of its G guest slots with a copy of the expert's weights, which it fetches
      * from the owner during the call. A row's arithmetic does not depend on the rank that computes it; outputs can
      * differ from a run without the spill only where the layer picks another tile orientation for an expert whose row
-     * count changed, or (with "ep_comm_sms" = 0) in the order of the combine's FP32 additions: last bits of FP32 sums. Requirements: l1_w, l1_w_sf,
+     * count changed, i.e. in the last bits of FP32 sums. Requirements: l1_w, l1_w_sf,
      * l2_w, l2_w_sf of EVERY rank hold E_local + G experts (the guest slots, after the rank's own experts, are scratch
      * of the library) and are mapped into every process; peer_l1_w[r] ... peer_l2_w_sf[r] are the addresses of rank
      * r's four tensors in this process (host arrays of num_ranks entries; entry `rank` must equal l1_w ... l2_w_sf).

@@ -195,20 +195,16 @@ def _worker_spill(rank, world, port, results):
             assert status[0] == 0, status
             out['y_' + name] = y.cpu()
             out['stats_' + name] = stats.cpu()
-        # the same call without the second stream (rows pulled by a phased combine): only the order of the combine's FP32
-        # additions differs
-        _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', 0))
+        # the same calls with the row-moving kernels on the library's second stream, beside the GEMMs of four expert phases
+        _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', 16))
         try:
-            y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
-            dg.fp8_fp4_mega_moe(y, l1s, l2s, buf)
-            assert _lib.device_status()[0] == 0
-            out['y_one_stream'] = y.cpu()
-            y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
-            dg.fp8_fp4_mega_moe(y, l1, l2, buf)
-            assert _lib.device_status()[0] == 0
-            out['y_one_stream_plain'] = y.cpu()
+            for name, (w1, w2) in (('two_streams', (l1s, l2s)), ('two_streams_plain', (l1, l2)), ('two_streams_again', (l1s, l2s))):
+                y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+                dg.fp8_fp4_mega_moe(y, w1, w2, buf)
+                assert _lib.device_status()[0] == 0
+                out['y_' + name] = y.cpu()
         finally:
-            _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', 24))
+            _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', 0))
         buf.x[:t].copy_(c['x_q'].cuda())
         y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
         dg.fp8_fp4_mega_moe(y, l1s, l2s, buf)  # leaves the plan of a spilled, overlapped call in the buffer
@@ -252,8 +248,9 @@ def test_two_rank_hot_expert_spill_matches_oracle():
         # a row's arithmetic does not depend on the rank that computes it; the tile orientation the layer picks for an
         # expert by its row count may, in the last bits of the FP32 sums
         assert quant.calc_diff(got['y_spill'], got['y_plain']) <= 1e-6
-        assert quant.calc_diff(got['y_one_stream'], got['y_spill']) <= 1e-6
-        assert quant.calc_diff(got['y_one_stream_plain'], got['y_spill']) <= 1e-6
+        assert quant.calc_diff(got['y_two_streams'], got['y_spill']) <= 1e-6
+        assert quant.calc_diff(got['y_two_streams_plain'], got['y_spill']) <= 1e-6
+        assert torch.equal(got['y_two_streams'], got['y_two_streams_again'])
         assert torch.equal(got['y_spill'], got['y_spill_again']), 'two calls must give the same bits'
         my_base, my_dest, my_slot, start, end, guest = omoe.ep_plan_with_spill(all_counts, rank, 128, SP_GUESTS)
         assert torch.equal(got['my_base'].long(), my_base) and torch.equal(got['my_dest'].long(), my_dest)
