@@ -71,8 +71,74 @@ def measured_peaks():
     return 6650.0, 'fallback'
 
 
+class NvmlClockSampler:
+    """SM clock and throttle reasons of one GPU read through NVML (read-only queries) every few milliseconds by a thread
+    of this process, between begin() and end(). Preferred over a nvidia-smi child process, which needs up to a second to
+    start and then answers slowly while eight ranks query it at once."""
+    REASONS = ((0x8, 'hw_slowdown'), (0x40, 'hw_thermal_slowdown'), (0x20, 'sw_thermal_slowdown'), (0x4, 'sw_power_cap'))
+
+    def __init__(self, gpu_index: int):
+        import threading
+        import pynvml
+        import torch
+        self.nvml = pynvml
+        pynvml.nvmlInit()
+        try:
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(f'GPU-{torch.cuda.get_device_properties(gpu_index).uuid}')
+        except Exception:
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        self.query()  # fails here, not in the thread, if a query is unsupported
+        self.samples, self.active, self.done = [], False, False
+        self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def query(self):
+        reasons = getattr(self.nvml, 'nvmlDeviceGetCurrentClocksEventReasons',
+                          getattr(self.nvml, 'nvmlDeviceGetCurrentClocksThrottleReasons', None))(self.handle)
+        return float(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)), int(reasons)
+
+    def run(self):
+        while not self.done:
+            if self.active:
+                try:
+                    self.samples.append(self.query())
+                except Exception:
+                    pass
+            time.sleep(0.004)
+
+    def start(self):
+        self.thread.start()
+
+    def begin(self):
+        self.active = True
+
+    def end(self):
+        self.active = False
+
+    def stop(self):
+        self.active = False
+        if not self.samples:
+            self.samples.append(self.query())
+        self.done = True
+        self.thread.join()
+        clocks = sorted(c for c, _ in self.samples)
+        mask = 0
+        for _, r in self.samples:
+            mask |= r
+        return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None, 'sm_max_mhz': self.max_clock, 'samples': len(clocks),
+                'reasons': sorted(name for bit, name in self.REASONS if mask & bit), 'window': 'timed region', 'source': 'nvml'}
+
+
+def make_clock_sampler(gpu_index: int):
+    try:
+        return NvmlClockSampler(gpu_index)
+    except Exception:
+        return ClockSampler(gpu_index)
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs. nvidia-smi needs up to a
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (used when NVML cannot be
+    loaded in-process). nvidia-smi needs up to a
     second to start on a box with eight GPUs, so it is started before the warm-up and the samples are cut to the timed
     region afterwards by their timestamps (begin() / end() mark it)."""
     FIELDS = ('timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
@@ -348,8 +414,9 @@ def measure_gemm_workload(masked, steps, warmup):
     for _ in range(max(warmup, 3)):
         call()
     torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device())
+    sampler = make_clock_sampler(torch.cuda.current_device())
     sampler.start()
+    sampler.begin()
     total = 0.0
     for _ in range(steps):
         flush.zero_()
@@ -452,8 +519,9 @@ def run_family_workload(args):
     for _ in range(max(args.warmup, 3)):
         call()
     torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    sampler = make_clock_sampler(0)
     sampler.start()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -647,7 +715,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         torch.cuda.synchronize()
 
     # ---- device-resident timing
-    sampler = ClockSampler(local_rank)
+    sampler = make_clock_sampler(local_rank)
     sampler.start()
     barrier()
     for _ in range(warmup):
