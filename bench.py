@@ -51,6 +51,10 @@ def parse_args():
     ap.add_argument('--comm-sms', type=int, default=-1,
                     help='expert-parallel runs: SMs kept for the kernels that move rows while the GEMMs run (the library\'s '
                          '"ep_comm_sms" knob; -1 = its default, 0 = one stream without overlap)')
+    ap.add_argument('--pdl', type=int, default=-1, help='programmatic dependent launch: 0 / 1 (-1 = the library\'s default)')
+    ap.add_argument('--no-stage-events', action='store_true',
+                    help='profiling aid: the timed steps record no CUDA events at the stage boundaries (stages_ms and the '
+                         'roofline then come out empty)')
     ap.add_argument('--skip-other-configs', action='store_true',
                     help='N = 1 only: leave out the extra timings (8192-token base, BASELINE configs 1, 2 and 4) after the headline line')
     ap.add_argument('--mma', default='fp8xfp4', choices=['fp8xfp4', 'nvfp4xnvfp4'],
@@ -699,7 +703,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     def step(events=None, x_in=None, logits_in=None, y_out=None):
         x_in, logits_in, y_out = (x if x_in is None else x_in), (logits if logits_in is None else logits_in), (y if y_out is None else y_out)
         if events is not None:
-            arr = (ctypes.c_void_p * len(events))(*[ev.cuda_event for ev in events])
+            arr = (ctypes.c_void_p * len(events))(*[None if ev is None else ev.cuda_event for ev in events])
             _lib.check(lib.dgb200_set_mega_moe_stage_events(ctypes.cast(arr, ctypes.c_void_p), len(events)))
         if nvfp4:
             dg.route_sigmoid_topk(logits_in, k, buf.topk_idx, buf.topk_weights)
@@ -727,19 +731,31 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         for ev in evs:
             ev.record()
     barrier()
+    # The timed steps carry only the two events around the roofline kernel (the gate/up GEMM stage; expert parallel: all
+    # GEMMs): an event between two kernels serialises their launches, so the full stage breakdown comes from a second pass
+    # of the same steps that is not part of the timed region.
+    roof_a, roof_b = 2, 3
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.begin()
     t0.record()
     for s in range(steps):
-        step(stage_events[s])
+        step(None if args.no_stage_events else [ev if j in (roof_a, roof_b) else None for j, ev in enumerate(stage_events[s])])
     t1.record()
     barrier()
     sampler.end()
     clocks = sampler.stop()
     ms_per_step = t0.elapsed_time(t1) / steps
     _lib.device_status()
-    stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_events) / steps for j in range(5)]
+    if args.no_stage_events:
+        stage_ms, roof_ms = [float('nan')] * 5, float('nan')
+    else:
+        roof_ms = sum(evs[roof_a].elapsed_time(evs[roof_b]) for evs in stage_events) / steps
+        for s in range(steps):
+            step(stage_events[s])
+        barrier()
+        _lib.device_status()
+        stage_ms = [sum(evs[j].elapsed_time(evs[j + 1]) for evs in stage_events) / steps for j in range(5)]
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region.
     # Every step copies its own inputs from pinned host memory and its result back; the three legs run on three
@@ -802,7 +818,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         l2_bytes = touched * (h * i // 2 + h * i // 32) + rows * (i + i // 32) + rows * h * 2
     # every rank's own numbers travel to rank 0: the step time is the maximum over ranks, everything that explains it
     # (stage times, bytes, flops) is taken from ONE rank, the one with the most routed rows
-    mine = torch.tensor([ms_per_step, e2e_ms] + stage_ms + [rows, touched, l1_bytes, l2_bytes, spilled_experts or 0],
+    mine = torch.tensor([ms_per_step, e2e_ms] + stage_ms + [rows, touched, l1_bytes, l2_bytes, spilled_experts or 0, roof_ms],
                         dtype=torch.float64, device='cuda')
     per_rank = [torch.empty_like(mine) for _ in range(world)]
     if world > 1:
@@ -815,6 +831,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     ms_per_step, e2e_ms = float(table[:, 0].max()), float(table[:, 1].max())
     hot = int(table[:, 7].argmax())
     stage_ms = [float(v) for v in table[hot, 2:7]]
+    roof_ms = float(table[hot, 12])  # the roofline kernel's interval inside the timed steps, same rank
     rows_hot, l1_bytes, l2_bytes = int(table[hot, 7]), int(table[hot, 9]), int(table[hot, 10])
     rows_all = float(table[:, 7].sum())
     flops = 2.0 * rows_all * h * i * 3
@@ -823,7 +840,7 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
     # dominant kernel = the gate/up GEMM of the most loaded rank; which roofline binds it follows from its arithmetic
     # intensity against the ridge of the FP8 tensor rate (nominal; this pool has no measured FP8 figure) over HBM
     l1_flops = 2.0 * rows_hot * h * 2 * i
-    l1_s = stage_ms[2] * 1e-3
+    l1_s = roof_ms * 1e-3
     gemms_in_one_interval = world > 1  # expert parallel: gate/up and down GEMMs alternate phase by phase
     if gemms_in_one_interval:
         l1_flops = 2.0 * rows_hot * h * 3 * i
@@ -837,14 +854,14 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         roofline = {'kernel': l1_kernel_name, 'bound': 'tensor', 'achieved': l1_flops / l1_s / 1e12, 'peak': mma_peak_nominal,
                     'unit': 'TFLOP/s', 'frac': l1_flops / l1_s / 1e12 / mma_peak_nominal,
                     'peak_source': 'nominal dense ' + ('FP4' if nvfp4 else 'FP8') + ' rate (no measured figure for this type on this pool)',
-                    'traffic': None, 'algorithmic_flops': l1_flops, 'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]}
+                    'traffic': None, 'algorithmic_flops': l1_flops, 'algorithmic_bytes': l1_bytes, 'kernel_ms': roof_ms}
     else:
         l1_gbs = l1_bytes / l1_s / 1e9
         roofline = {'kernel': l1_kernel_name, 'bound': 'hbm', 'achieved': l1_gbs, 'peak': hbm_peak, 'unit': 'GB/s',
                     'frac': l1_gbs / hbm_peak, 'peak_source': peak_kind,
                     'traffic': int(L1_KERNEL_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * l1_bytes) if not nvfp4 else None,
                     'traffic_source': L1_TRAFFIC_SOURCE if not nvfp4 else None,
-                    'algorithmic_bytes': l1_bytes, 'kernel_ms': stage_ms[2]}
+                    'algorithmic_bytes': l1_bytes, 'kernel_ms': roof_ms}
     if world > 1:
         roofline['rank'] = hot
     line = {
@@ -861,6 +878,9 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
                       {'plan': stage_ms[0], 'dispatch_push': stage_ms[1],
                        'gemms_and_return_push': stage_ms[2] + stage_ms[3], 'waits_and_combine': stage_ms[4]}),
         'stages_rank': hot,
+        'stages_source': ('a second pass of the same steps with CUDA events at every stage boundary; the timed steps carry only the '
+                          'two events around the roofline kernel (roofline.kernel_ms), because an event between two kernels '
+                          'serialises their launches'),
         'l2_gemm_hbm_gbs': l2_bytes / (stage_ms[3] * 1e-3) / 1e9 if not gemms_in_one_interval else None,
         'tflops': tflops,
         'frac_fp4_dense_peak_nominal': tflops / (FP4_DENSE_PEAK_TFLOPS_NOMINAL * world),
@@ -997,6 +1017,9 @@ def main():
     if args.comm_sms >= 0:
         from deepgemm_b200 import _lib
         _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', args.comm_sms))
+    if args.pdl >= 0:
+        from deepgemm_b200 import _lib
+        _lib.check(_lib.lib().dgb200_set_tuning(b'pdl', args.pdl))
     rc = run_ours(args, cfg, rank, world, local_rank)
     if world > 1:
         import torch.distributed as dist

@@ -20,6 +20,28 @@ namespace {
 
 constexpr int kVersion = 100;
 
+bool use_pdl();  // the "pdl" tuning knob (set_pdl)
+
+// Kernel launch with, when `pdl` is set, the programmatic-stream-serialization attribute: the kernel may be launched
+// while the preceding kernel of the stream still runs and parks in its pdl_prologue() until that one has completed
+// (reference: the launch attribute in csrc/jit/handle.hpp:77, switched by set_pdl, csrc/apis/runtime.hpp:24-28). Only
+// kernels whose first statement is pdl_prologue() may be launched this way.
+template <typename... Params, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream, bool pdl,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
 int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_sfa, const CUtensorMap& tm_sfb,
                 const CUtensorMap& tm_out, const GemmParams& p, int grid, cudaStream_t stream) {
@@ -34,8 +56,7 @@ int launch_gemm(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensor
         configured = true;
         configured_device = dev;
     }
-    kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p);
-    DGB_CUDA(cudaGetLastError());
+    DGB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), L::kDynamicBytes, stream, use_pdl(), tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p));
     return 0;
 }
 
@@ -67,6 +88,7 @@ struct Tuning {
     int mlp_kernel = -1;  // FP8 x FP4 layer GEMMs: 0 = separate gate/up and down kernels (tokens-on-M / swapped split),
                           // 1 = the fused expert-MLP kernel on single CTAs, 2 = on CTA pairs; -1 = not yet read from
                           // the environment (DGB200_MLP_KERNEL, default below)
+    int pdl = 1;  // programmatic dependent launch between the kernels of the single-rank layer (set_pdl)
     int ep_comm_sms = 0;  // expert-parallel layer: SMs kept free of GEMM CTAs for kernels that move rows over NVLink on a
                           // second stream while the GEMMs run (0 = one stream: every kernel on all SMs)
     long long peer_wait_cycles = 20000000000ll;  // budget of a wait for another rank, SM clock cycles (about 10 s: ranks
@@ -77,6 +99,8 @@ Tuning& tuning() {
     static Tuning t;
     return t;
 }
+
+bool use_pdl() { return tuning().pdl != 0; }
 
 constexpr int kDefaultMlpKernel = 0;
 
@@ -385,8 +409,7 @@ int launch_gemm_swap(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         configured = true;
         configured_device = dev;
     }
-    kernel<<<grid, kGemmThreads, SwapSmem::kDynamicBytes, stream>>>(tm_x, tm_w, tm_sfx, tm_sfw, p);
-    DGB_CUDA(cudaGetLastError());
+    DGB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), SwapSmem::kDynamicBytes, stream, use_pdl(), tm_x, tm_w, tm_sfx, tm_sfw, p));
     return 0;
 }
 
@@ -453,7 +476,7 @@ thread_local cudaEvent_t g_stage_events[kNumStageEvents];
 thread_local int g_num_stage_events = 0;
 
 int record_stage(int index, cudaStream_t stream) {
-    if (index < g_num_stage_events) DGB_CUDA(cudaEventRecord(g_stage_events[index], stream));
+    if (index < g_num_stage_events && g_stage_events[index] != nullptr) DGB_CUDA(cudaEventRecord(g_stage_events[index], stream));
     return 0;
 }  // rows each expert segment is padded to in the expert-sorted buffers
 
@@ -1233,12 +1256,13 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
 
     // 1. dispatch plan: stable counting sort of the (token, k) entries by expert
     DGB_CUDA(cudaMemsetAsync(src_of_row, 0xff, l.max_rows * 4, stream));
-    dgb200_moe_count_kernel<<<chunks, kPlanChunk, E * sizeof(int), stream>>>(topk_idx, entries, 0, E, chunk_hist);
-    dgb200_moe_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, E, kSegmentAlignment, expert_start, expert_end,
-                                                    total_rows, cumulative_local_expert_recv_stats);
-    dgb200_moe_assign_kernel<<<chunks, kPlanChunk, 32 * E, stream>>>(topk_idx, topk_weights, entries, 0, E, chunk_hist,
-                                                                    expert_start, dest_row, src_of_row, row_weight);
-    DGB_CUDA(cudaGetLastError());
+    const bool pdl = use_pdl();
+    DGB_CUDA(launch_kernel(dgb200_moe_count_kernel, dim3(chunks), dim3(kPlanChunk), E * sizeof(int), stream, pdl, topk_idx, entries, 0, E,
+                           chunk_hist));
+    DGB_CUDA(launch_kernel(dgb200_moe_scan_kernel, dim3(1), dim3(1024), 0, stream, pdl, chunk_hist, chunks, E, kSegmentAlignment,
+                           expert_start, expert_end, total_rows, cumulative_local_expert_recv_stats));
+    DGB_CUDA(launch_kernel(dgb200_moe_assign_kernel, dim3(chunks), dim3(kPlanChunk), 32 * E, stream, pdl, topk_idx, topk_weights, entries, 0,
+                           E, chunk_hist, expert_start, dest_row, src_of_row, row_weight));
 
     if ((rc = record_stage(1, stream))) return rc;
     // 2. gather quantised rows + scales into expert-sorted order
@@ -1248,17 +1272,17 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
     if (quant.x_bf16 != nullptr) {
         PeerTable self_table{};
         for (int r = 0; r < kMaxEpRanks; ++r) self_table.p[r] = reinterpret_cast<unsigned long long>(base);
-        dgb200_moe_quant_dispatch_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(
-            quant.x_bf16, quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden, num_experts, 0,
-            entries, self_table, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 0,
-            with_shared ? base + l.x : nullptr, with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr, l.token_rows);
+        DGB_CUDA(launch_kernel(dgb200_moe_quant_dispatch_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0, stream, pdl, quant.x_bf16,
+                               quant.x_bf16_row_stride, topk_idx, topk_weights, dest_row, num_tokens, num_topk, hidden, num_experts, 0, entries,
+                               self_table, l.l1_acts, l.l1_sf, l.max_rows, l.row_weight, l.src_of_row, 0,
+                               with_shared ? base + l.x : nullptr, with_shared ? reinterpret_cast<unsigned*>(base + l.shared_x_sf) : nullptr,
+                               l.token_rows));
     } else {
-        dgb200_moe_gather_kernel<<<gather_blocks, 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
-            base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk,
-            static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, base + l.l1_acts,
-            reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows);
+        DGB_CUDA(launch_kernel(dgb200_moe_gather_kernel, dim3(gather_blocks), dim3(256), sf_per_row * 33 * sizeof(unsigned), stream, pdl,
+                               base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), src_of_row, total_rows, num_topk,
+                               static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, base + l.l1_acts,
+                               reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows));
     }
-    DGB_CUDA(cudaGetLastError());
 
     if ((rc = record_stage(2, stream))) return rc;
     // 3 + 4. L1 (gate/up GEMM, fused SwiGLU + FP8 requant) and L2 (down GEMM, rows scattered to their combine slots)
@@ -1272,10 +1296,10 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
     // 5. combine: y[t] = sum over the top-k slots of the rows the L2 GEMM wrote
     PeerTable self{};
     self.p[0] = reinterpret_cast<unsigned long long>(base);
-    dgb200_moe_combine_kernel<<<num_tokens, 128, (num_topk + 1) * sizeof(unsigned long long), stream>>>(
-        self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
-        with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
-    DGB_CUDA(cudaGetLastError());
+    DGB_CUDA(launch_kernel(dgb200_moe_combine_kernel, dim3(num_tokens), dim3(128), (num_topk + 1) * sizeof(unsigned long long), stream, pdl,
+                           self, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
+                           with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
+                           static_cast<__nv_bfloat16*>(y)));
     return record_stage(5, stream);
 }
 
@@ -1345,6 +1369,9 @@ int dgb200_set_tuning(const char* name, int32_t value) {
     } else if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
+    } else if (std::strcmp(name, "pdl") == 0) {
+        DGB_REQUIRE(value == 0 || value == 1, "pdl must be 0 or 1");
+        tuning().pdl = value;
     } else if (std::strcmp(name, "ep_comm_sms") == 0) {
         DGB_REQUIRE(value >= 0 && value <= 64, "ep_comm_sms must be in [0, 64]");
         tuning().ep_comm_sms = value;
@@ -1831,10 +1858,11 @@ int dgb200_route_sigmoid_topk(const float* logits, int32_t tokens, int32_t exper
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     long long* idx = reinterpret_cast<long long*>(topk_idx);
     if (experts <= 256)
-        dgb200_route_sigmoid_topk_kernel<8><<<grid, 256, 0, s>>>(logits, tokens, experts, topk, idx, topk_weights);
+        DGB_CUDA(launch_kernel(dgb200_route_sigmoid_topk_kernel<8>, dim3(grid), dim3(256), 0, s, use_pdl(), logits, tokens, experts, topk, idx,
+                               topk_weights));
     else
-        dgb200_route_sigmoid_topk_kernel<32><<<grid, 256, 0, s>>>(logits, tokens, experts, topk, idx, topk_weights);
-    DGB_CUDA(cudaGetLastError());
+        DGB_CUDA(launch_kernel(dgb200_route_sigmoid_topk_kernel<32>, dim3(grid), dim3(256), 0, s, use_pdl(), logits, tokens, experts, topk, idx,
+                               topk_weights));
     return 0;
 }
 

@@ -356,6 +356,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         prefetch_tensormap(&tm_sfb);
         if (p.tma_store) prefetch_tensormap(&tm_out);
     }
+    pdl_prologue();  // everything above touches only this CTA's shared memory and the kernel's own parameters
     // Stage the per-group schedule (see GroupTable): every thread fills its groups, warp 0 turns the per-group tile
     // counts into running totals.
     int* group_cache = reinterpret_cast<int*>(smem + L::kOffGroups);

@@ -25,6 +25,7 @@ constexpr int kPlanChunk = 1024;  // (token, k) entries per CTA in the count / a
 __global__ void __launch_bounds__(kPlanChunk)
 dgb200_moe_count_kernel(const long long* __restrict__ topk_idx, int num_entries, int expert_lo, int num_local_experts,
                         int* __restrict__ chunk_hist) {
+    pdl_prologue();
     extern __shared__ int hist[];
     for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) hist[e] = 0;
     __syncthreads();
@@ -44,6 +45,7 @@ __global__ void __launch_bounds__(1024)
 dgb200_moe_scan_kernel(int* __restrict__ chunk_hist, int num_chunks, int num_local_experts, int alignment,
                        int* __restrict__ expert_start, int* __restrict__ expert_end, int* __restrict__ total_rows,
                        int* __restrict__ cumulative_stats) {
+    pdl_prologue();
     __shared__ int warp_sums[32];
     __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
@@ -98,6 +100,7 @@ dgb200_moe_assign_kernel(const long long* __restrict__ topk_idx, const float* __
                          int expert_lo, int num_local_experts, const int* __restrict__ chunk_hist,
                          const int* __restrict__ expert_start, int* __restrict__ dest_row, int* __restrict__ src_of_row,
                          float* __restrict__ row_weight) {
+    pdl_prologue();
     extern __shared__ unsigned char warp_hist[];  // [32 warps][num_local_experts], counts <= 32
     for (int i = threadIdx.x; i < 32 * num_local_experts; i += blockDim.x) warp_hist[i] = 0;
     __syncthreads();
@@ -138,6 +141,7 @@ dgb200_moe_gather_kernel(const unsigned char* __restrict__ x, const unsigned* __
                          const int* __restrict__ src_of_row, const int* __restrict__ total_rows, int topk, int row_bytes,
                          int sf_per_row, unsigned char* __restrict__ acts, unsigned* __restrict__ acts_sf,
                          long long sf_k_stride) {
+    pdl_prologue();
     extern __shared__ unsigned sf_tile[];  // [sf_per_row][33]
     const int row0 = blockIdx.x * 32;
     if (row0 >= total_rows[0]) return;
@@ -167,6 +171,7 @@ template <int kMaxPerLane>
 __global__ void __launch_bounds__(256)
 dgb200_route_sigmoid_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int topk,
                                  long long* __restrict__ topk_idx, float* __restrict__ topk_weights) {
+    pdl_prologue();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (t >= tokens) return;
@@ -221,6 +226,7 @@ __global__ void __launch_bounds__(128)
 dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const long long* __restrict__ topk_idx,
                           const int* __restrict__ dest_row, int topk, int experts_per_rank, int hidden,
                           const __nv_bfloat16* __restrict__ shared_rows, __nv_bfloat16* __restrict__ y) {
+    pdl_prologue();
     const int t = blockIdx.x;
     extern __shared__ unsigned long long slot_rows[];  // address of each slot's row (top-k slots, then the shared one), 0 = skip
     if (threadIdx.x == topk)
@@ -905,6 +911,7 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
                                  long long sf_offset, long long sf_k_stride, long long weight_offset, long long src_offset,
                                  int write_meta, unsigned char* __restrict__ self_q, unsigned* __restrict__ self_sf,
                                  long long self_sf_k_stride) {
+    pdl_prologue();
     // self_q / self_sf (may be null): also keep the quantised row in token order (e4m3 [tokens, hidden]; scales MN-major
     // in tcgen05.cp row order), which is what the shared experts' GEMM reads.
     const int lane = threadIdx.x & 31;
@@ -986,6 +993,7 @@ __global__ void __launch_bounds__(256)
 dgb200_sf_rows_to_cp_order_kernel(const unsigned* __restrict__ sf, int tokens, int ints_per_row, unsigned* __restrict__ out,
                                   long long k_stride, const int* __restrict__ rows_limit, const int* __restrict__ first_row,
                                   const int* __restrict__ last_row_end) {
+    pdl_prologue();
     extern __shared__ unsigned sf_tile[];  // [ints_per_row][33]
     if (rows_limit != nullptr) tokens = min(tokens, rows_limit[0]);  // row count only known on the device
     int begin = 0;
@@ -1020,6 +1028,7 @@ dgb200_swiglu_requant_rows_kernel(const __nv_bfloat16* __restrict__ tmp, const i
                                   const float* __restrict__ row_weight, float clamp, int fast_math,
                                   unsigned char* __restrict__ act_q, long long act_q_row_stride,
                                   unsigned* __restrict__ act_sf, long long act_sf_k_stride, int first_expert) {
+    pdl_prologue();
     const int e = first_expert + blockIdx.y;
     const int start = expert_start[e], rows = expert_end[e] - start;
     if (rows < rows_lo || rows > rows_hi) return;

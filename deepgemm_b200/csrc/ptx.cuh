@@ -541,6 +541,14 @@ __device__ __forceinline__ void grid_dependency_wait() {
 __device__ __forceinline__ void grid_dependency_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+// First statement of every kernel that may be launched with programmatic stream serialization: nothing the preceding
+// kernel of the stream wrote is read, and nothing it may still read is written, before the wait returns (it returns
+// at once when the launch carries no such dependency); the next kernel of the stream may then be launched early and
+// parks in its own wait.
+__device__ __forceinline__ void pdl_prologue() {
+    grid_dependency_wait();
+    grid_dependency_launch_dependents();
+}
 
 // tcgen05.cp.32x128b.warpx4 reads, per 128 rows of one packed scale int, 32 rows x 4 words where word j of row r
 // is the scale int of source row r + 32 j. A tensor stored with every aligned group of 128 rows in that order (row

@@ -1,11 +1,11 @@
 """Process-global knobs with the reference's names (csrc/apis/runtime.hpp:12-48, csrc/apis/layout.hpp:142-150).
 
 Kernels here are compiled ahead of time, so knobs that only steer the reference's JIT (compiled dims, block-size
-multiples) are accepted and ignored; knobs that would change how a kernel runs and are not built (PDL, tensor-core
-throttling) raise when set to anything but their default."""
+multiples) are accepted and ignored; a knob that would change how a kernel runs and is not built (tensor-core
+throttling) raises when set to anything but its default."""
 from . import _lib
 
-_state = {'tc_util': 100, 'pdl': False, 'mk_alignment': 128}
+_state = {'tc_util': 100, 'pdl': True, 'mk_alignment': 128}
 
 
 def set_num_sms(num_sms: int) -> None:
@@ -31,11 +31,10 @@ def get_tc_util() -> int:
 
 
 def set_pdl(enabled: bool) -> None:
-    """Programmatic dependent launch (csrc/apis/runtime.hpp:24-28) is not built into these kernels: switching it on is
-    refused rather than silently ignored; ``set_pdl(False)`` is accepted."""
-    if enabled:
-        raise RuntimeError('programmatic dependent launch is not built into these kernels: set_pdl(True) is refused')
-    _state['pdl'] = False
+    """Programmatic dependent launch between the kernels of the single-rank layer and of the GEMM entry points
+    (reference: set_pdl, csrc/apis/runtime.hpp:24-28). On by default; the reference's default is off."""
+    _lib.check(_lib.lib().dgb200_set_tuning(b'pdl', 1 if enabled else 0))
+    _state['pdl'] = bool(enabled)
 
 
 def get_pdl() -> bool:

@@ -45,6 +45,10 @@ int dgb200_get_num_sms(void);
  *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
  *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
  *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
+ *   "pdl"                1 (default) = the kernels of the single-rank layer and of the GEMM entry points are launched
+ *                        with programmatic stream serialization: a kernel may start while its predecessor in the
+ *                        stream still runs and waits (griddepcontrol.wait) before it touches memory. 0 = plain
+ *                        launches. Reference: set_pdl, csrc/apis/runtime.hpp:24-28.
  *   "ep_comm_sms"        expert-parallel layer: 0 (default) = every kernel on the caller's stream and on all SMs.
  *                        n > 0 (at most 64) = the kernels that move rows between ranks run on a second, library-owned
  *                        stream on n SMs that the GEMMs leave free, beside the GEMMs of other expert phases (measured

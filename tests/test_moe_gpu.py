@@ -278,6 +278,30 @@ def test_down_gemm_split_by_group_size(dg):
     assert quant.calc_diff(got, want) <= FP4_TOL
 
 
+def test_programmatic_dependent_launch_on_and_off(dg):
+    """set_pdl (reference: csrc/apis/runtime.hpp:24-28): the layer's kernels launched with programmatic stream
+    serialization (the default) and with plain launches must give the same plan and the same bits, call after call."""
+    tokens, hidden, inter, experts, topk = 333, 512, 256, 16, 4
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=61, masked_ratio=0.1)
+    assert dg.get_pdl() is True
+    outs, plans = [], []
+    try:
+        for enabled in (True, False, True):
+            dg.set_pdl(enabled)
+            assert dg.get_pdl() is enabled
+            for _ in range(3):  # back-to-back calls: a kernel may start before its predecessor has finished
+                y, buf = _run_layer(dg, c, tokens, hidden, inter, experts, topk)
+            outs.append(y)
+            plans.append(_plan_views(buf, tokens, topk, experts))
+    finally:
+        dg.set_pdl(True)
+    want = omoe.moe_layer(c['x_q'], c['x_sf'], c['topk_idx'], c['topk_weights'], c['l1_q'], c['l1_sf'], c['l2_q'], c['l2_sf'])
+    assert quant.calc_diff(outs[0], want) <= FP4_TOL
+    for y, plan in zip(outs[1:], plans[1:]):
+        assert torch.equal(y, outs[0])
+        assert all(torch.equal(a, b) for a, b in zip(plan, plans[0]))
+
+
 def test_peer_wait_runs_out_and_the_library_stays_usable(dg):
     """Failure detection of the expert-parallel barrier, on one GPU and without faulting it: the layer is called as rank 0
     of 2 with both entries of the peer table pointing at this process's own buffer, so the flag "rank 1" should write
