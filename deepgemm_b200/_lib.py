@@ -69,6 +69,7 @@ _SIGNATURES = {
                              _i32, ctypes.c_float, _i32, _ptr],
     'dgb200_moe_dispatch_plan_noalloc': [_ptr, _i32, _i32, _i32, _i32, _ptr, _ptr, _ptr, _ptr],
     'dgb200_set_mega_moe_stage_events': [_ptr, _i32],
+    'dgb200_ep_plan_with_guest_experts': [_ptr, _i32, _i32, _i32, _i32, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     'dgb200_fp8_fp4_mega_moe': [
         _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],

@@ -2076,6 +2076,29 @@ int dgb200_moe_dispatch_plan_noalloc(const int64_t* topk_idx, int32_t num_tokens
     return 0;
 }
 
+int dgb200_ep_plan_with_guest_experts(const int32_t* all_counts, int32_t num_ranks, int32_t num_experts, int32_t rank,
+                                      int32_t alignment, int32_t num_guest_experts, int32_t* my_base, int32_t* my_dest,
+                                      int32_t* my_slot, int32_t* slot_start, int32_t* slot_end, int32_t* guest_expert,
+                                      int32_t* rank_rows, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DGB_REQUIRE(all_counts != nullptr && my_base != nullptr && my_dest != nullptr && my_slot != nullptr && slot_start != nullptr &&
+                    slot_end != nullptr && guest_expert != nullptr && rank_rows != nullptr,
+                "null tensor pointer");
+    DGB_REQUIRE(num_ranks >= 1 && num_ranks <= kMaxEpRanks && num_experts > 0 && num_experts % num_ranks == 0 && rank >= 0 &&
+                    rank < num_ranks && alignment > 0,
+                "need 1 <= num_ranks <= %d, num_experts a positive multiple of it, 0 <= rank < num_ranks, alignment > 0", kMaxEpRanks);
+    DGB_REQUIRE(num_guest_experts >= 0 && num_guest_experts <= kMaxGuestExperts &&
+                    num_experts / num_ranks + num_guest_experts <= kMaxSpillSlots - 1,
+                "at most %d guest experts and %d expert slots per rank", kMaxGuestExperts, kMaxSpillSlots - 1);
+    DGB_REQUIRE(static_cast<long long>(num_ranks) * num_experts * 6 <= 30 * 1024, "too many experts x ranks for the plan's tables");
+    // the row total is internal to the layer call; here it lands behind the rank_rows output ([2][num_ranks] + 1 word)
+    dgb200_ep_spill_plan_kernel<<<1, 1024, static_cast<size_t>(num_ranks) * num_experts * 6, stream>>>(
+        all_counts, num_experts, num_ranks, rank, alignment, num_guest_experts, my_base, my_dest, my_slot, slot_start, slot_end,
+        rank_rows + 2 * num_ranks, guest_expert, rank_rows, nullptr);
+    DGB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int dgb200_nvfp4_tensor_scale(const void* x, int64_t x_row_stride, int32_t rows, int32_t k, float* out_scale, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     DGB_REQUIRE(x != nullptr && out_scale != nullptr, "null tensor pointer");

@@ -400,6 +400,23 @@ int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const 
                           int32_t num_experts, int32_t num_topk, int32_t hidden, int32_t intermediate_hidden,
                           float activation_clamp, int32_t fast_math, void* stream);
 
+/* The expert-parallel dispatch plan with guest experts (hot-expert row spill, see dgb200_mega_moe_args) as rank `rank`
+ * derives it inside the layer call, as a call of its own: for schedulers that want to know where rows will be computed
+ * before they launch the layer, and for tests. No reference counterpart. All pointers are device memory.
+ *   all_counts    int32 [num_ranks, num_experts]: entries that source rank s routes to expert e
+ *   my_base, my_dest, my_slot  int32 [num_experts]: first row, computing rank and expert slot there of rank `rank`'s
+ *                 entries for each expert (slots 0 .. E_local - 1 = the computing rank's own experts, then guest slots)
+ *   slot_start, slot_end  int32 [E_local + num_guest_experts]: the row segments of rank `rank`'s own slots, each
+ *                 starting at a multiple of `alignment`; inside a slot rows are ordered by (source rank, entry)
+ *   guest_expert  int32 [num_guest_experts]: the experts rank `rank` hosts, -1 = unused
+ *   rank_rows     int32 [2 * num_ranks + 1]: every rank's rows as routed, every rank's rows as computed, and rank
+ *                 `rank`'s padded row total
+ * num_ranks <= 8, num_guest_experts <= 8, E_local + num_guest_experts <= 255, num_ranks * num_experts <= 5120. */
+int dgb200_ep_plan_with_guest_experts(const int32_t* all_counts, int32_t num_ranks, int32_t num_experts, int32_t rank,
+                                      int32_t alignment, int32_t num_guest_experts, int32_t* my_base, int32_t* my_dest,
+                                      int32_t* my_slot, int32_t* slot_start, int32_t* slot_end, int32_t* guest_expert,
+                                      int32_t* rank_rows, void* stream);
+
 /* Dispatch plan for callers that cannot allocate device memory. It has no counterpart in the reference.
  * Some hosts of this library run it from places where cudaMalloc is off limits: inside a region whose memory is
  * owned by another allocator with a fixed pool, in a callback that must not synchronise the device, or in a service
