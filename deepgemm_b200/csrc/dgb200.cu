@@ -88,6 +88,7 @@ struct Tuning {
     int mlp_kernel = -1;  // FP8 x FP4 layer GEMMs: 0 = separate gate/up and down kernels (tokens-on-M / swapped split),
                           // 1 = the fused expert-MLP kernel on single CTAs, 2 = on CTA pairs; -1 = not yet read from
                           // the environment (DGB200_MLP_KERNEL, default below)
+    int fused_return = 1;  // expert-parallel layer with guest experts: the down GEMM's epilogue sends the output rows back
     int pdl = 1;  // programmatic dependent launch between the kernels of the single-rank layer (set_pdl)
     int ep_comm_sms = 0;  // expert-parallel layer: SMs kept free of GEMM CTAs for kernels that move rows over NVLink on a
                           // second stream while the GEMMs run (0 = one stream: every kernel on all SMs)
@@ -709,10 +710,18 @@ int run_expert_mlp(bool pair, const MegaLayout& l, uint8_t* base, const void* l1
 // The two grouped GEMMs of the layer over this rank's expert-sorted rows (shared by the single-rank and the
 // expert-parallel paths): L1 writes quantised activations + scales (FP8/UE8M0 or NVFP4/UE4M3), L2 writes BF16 rows
 // into l2_out in the same row order.
+// Where the down GEMM of the expert-parallel layer may send its output rows instead of writing them to l2_out: row r goes
+// to row src_of_row[r] % entries_per_rank of the `returned` buffer of rank src_of_row[r] / entries_per_rank.
+struct ReturnSpec {
+    const int* src_of_row;
+    int entries_per_rank;
+    unsigned long long returned_base[kMaxRanks];
+};
+
 int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
                     const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
                     cudaStream_t stream, int stage_event_base, long long expected_rows_per_expert, int group_begin = 0,
-                    int group_end = 0) {
+                    int group_end = 0, const ReturnSpec* ret = nullptr, bool* returned_by_gemm = nullptr) {
     const int E = l.num_local_experts + quant.guest_slots;  // guest slots follow the rank's own experts, in the plan and in the weights
     // [group_begin, group_end): the expert slots this call computes ({0, 0} = all of them)
     const int first_expert = (group_begin == 0 && group_end == 0) ? 0 : group_begin;
@@ -865,6 +874,16 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.a_scale = quant.act_scale;
         p.b_scales = quant.l2_scales;
         p.sf_transposed = 1;
+        // GEMM and return transfer in one kernel: only the 256-wide tokens-on-M kernel of the FP8 x FP4 kind has the
+        // epilogue for it; otherwise the caller sends the rows of l2_out with a kernel of its own
+        const bool fuse_return = ret != nullptr && orient == kOrientM && !nvfp4 && !bf16 && hidden % 256 == 0 &&
+                                 (tuning().block_n == 0 || tuning().block_n == 256);
+        if (fuse_return) {
+            p.ret_src = ret->src_of_row;
+            p.ret_entries_per_rank = ret->entries_per_rank;
+            for (int r = 0; r < kMaxRanks; ++r) p.ret_base[r] = ret->returned_base[r];
+        }
+        if (returned_by_gemm != nullptr) *returned_by_gemm = fuse_return;
         if ((rc = run_split(c))) return rc;
     }
     return record_stage(stage_event_base + 1, stream);
@@ -1083,8 +1102,18 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         dgb200_ep_fetch_guest_weights_kernel<<<dim3(overlap ? std::max(1, comm_sms / std::max(1, G)) : 74, G), 256, 0, on>>>(
             reinterpret_cast<const int*>(base + l.guest_expert), E, guest_tables);
     };
+    // With balanced loads on one stream the down GEMM sends its output rows to their source ranks from its epilogue
+    // ("fused_return" tuning knob, on by default), so the transfer runs under the GEMM's own MMAs tile by tile; where the
+    // GEMM variant in use has no such epilogue, or on the second stream, a kernel of its own sends the rows of l2_out.
+    ReturnSpec return_spec{};
+    return_spec.src_of_row = reinterpret_cast<const int*>(base + l.src_of_row);
+    return_spec.entries_per_rank = entries_per_rank;
+    for (int r = 0; r < num_ranks; ++r) return_spec.returned_base[r] = peers.p[r] + static_cast<unsigned long long>(l.returned);
+    const bool fuse_return_into_gemm = spill && !overlap && tuning().fused_return != 0;
+    bool returned_by_gemm = false;
     auto gemms = [&](int q) -> int {
         const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
+        returned_by_gemm = false;
         if (g1 == g0) return 0;
         // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
         if (sf_per_row > 0)
@@ -1096,7 +1125,8 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         return run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream,
                                kNumStageEvents /* no stage events inside the loop */,
                                static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts,
-                               phases == 1 ? 0 : g0, phases == 1 ? 0 : g1);
+                               phases == 1 ? 0 : g0, phases == 1 ? 0 : g1, fuse_return_into_gemm ? &return_spec : nullptr,
+                               &returned_by_gemm);
     };
 
     // the BF16 output rows of phase q's expert slots back to the ranks their tokens came from
@@ -1132,7 +1162,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         for (int q = 0; q < phases; ++q) {
             flag(1 + q, 0, 1);
             if ((rc = gemms(q))) return rc;
-            if (spill) return_rows(q, stream, false);
+            if (spill && !returned_by_gemm) return_rows(q, stream, false);
             flag(1 + kMaxEpPhases + q, 1, 0);
         }
         if ((rc = record_stage(3, stream))) return rc;  // both GEMMs of all phases lie before this point
@@ -1369,6 +1399,9 @@ int dgb200_set_tuning(const char* name, int32_t value) {
     } else if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
+    } else if (std::strcmp(name, "fused_return") == 0) {
+        DGB_REQUIRE(value == 0 || value == 1, "fused_return must be 0 or 1");
+        tuning().fused_return = value;
     } else if (std::strcmp(name, "pdl") == 0) {
         DGB_REQUIRE(value == 0 || value == 1, "pdl must be 0 or 1");
         tuning().pdl = value;

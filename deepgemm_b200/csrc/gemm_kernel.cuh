@@ -104,6 +104,13 @@ struct GemmParams {
     int accumulate;  // kEpiF32 only: d += accumulator instead of d = accumulator (the dense GEMMs' input c, already in d)
     int kg_psum;     // kModeKGrouped: layout[g] is the end K row of group g (groups start at multiples of `alignment`,
                      // the gap rows are zero) instead of its K extent
+    // kEpiBF16, BLOCK_N = 256, expert-parallel down GEMM only: the epilogue does not write d but sends every output row
+    // straight to the rank its token came from (GEMM and return transfer in one kernel, tile by tile):
+    // ret_src[row] = source rank * ret_entries_per_rank + entry (written by the dispatch push), the row goes to
+    // ret_base[source rank] + entry * n * 2 bytes. Null = write d.
+    const int* ret_src;
+    int ret_entries_per_rank;
+    unsigned long long ret_base[kMaxRanks];  // each rank's buffer of returned rows as mapped into this process
 };
 
 // K rows [start, start + len) of group `g` of a K-grouped operand; `prev_end` carries the running end between calls
@@ -760,7 +767,46 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                 }
             }
             if constexpr (L::kStageBytesPerWarp != 0 && EPI == kEpiBF16) {
-                if (via_tma && warp_has_rows) {
+                if (p.ret_src != nullptr) {
+                    // Fused return: this warp's 32 rows x 128 columns (256 bytes of BF16 per row) go to 32 different places
+                    // in other ranks' memory. A thread holds a whole row segment in registers, but 32 threads storing 16
+                    // bytes each into 32 rows make the worst pattern for NVLink, so the warp turns its slab through the
+                    // 2 KB staging buffer eight rows at a time: the eight owners write their 256 bytes (XOR-swizzled
+                    // chunks), then every store instruction of the warp writes two complete 256-byte segments.
+                    if (warp_has_rows) {
+                        unsigned long long my_dst = 0;
+                        if (store) {
+                            const int src = __ldg(p.ret_src + row);
+                            const int src_rank = src / p.ret_entries_per_rank;
+                            my_dst = p.ret_base[src_rank] +
+                                     (static_cast<unsigned long long>(src - src_rank * p.ret_entries_per_rank) * p.n +
+                                      static_cast<unsigned long long>(t.n_block * BLOCK_N + static_cast<int>(half) * kCols)) * 2ull;
+                        }
+#pragma unroll 1
+                        for (int pass = 0; pass < 4; ++pass) {
+                            __syncwarp();
+                            if (static_cast<int>(lane >> 3) == pass) {
+                                uint8_t* mine = stage_buf + (lane & 7) * 256;
+#pragma unroll
+                                for (int c = 0; c < kCols / 8; ++c)
+                                    *reinterpret_cast<uint4*>(mine + ((c ^ static_cast<int>(lane & 7)) << 4)) = make_uint4(
+                                        pack_bf16x2(__uint_as_float(acc[c * 8 + 0]), __uint_as_float(acc[c * 8 + 1])),
+                                        pack_bf16x2(__uint_as_float(acc[c * 8 + 2]), __uint_as_float(acc[c * 8 + 3])),
+                                        pack_bf16x2(__uint_as_float(acc[c * 8 + 4]), __uint_as_float(acc[c * 8 + 5])),
+                                        pack_bf16x2(__uint_as_float(acc[c * 8 + 6]), __uint_as_float(acc[c * 8 + 7])));
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int slab_row = static_cast<int>(lane >> 4) + 2 * j;  // 0..7: two rows per instruction
+                                const int chunk = static_cast<int>(lane & 15);
+                                const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + slab_row * 256 + ((chunk ^ slab_row) << 4));
+                                const unsigned long long dst = __shfl_sync(0xffffffffu, my_dst, pass * 8 + slab_row);
+                                if (dst != 0) st_global_v4(reinterpret_cast<void*>(dst + chunk * 16), v.x, v.y, v.z, v.w);
+                            }
+                        }
+                    }
+                } else if (via_tma && warp_has_rows) {
                     // 32 columns (64 bytes of BF16 per row) per TMA store; rows past rows_store hold whatever the MMA
                     // produced from the tile's padding rows and land in padding rows of D
                     const int x0 = t.n_block * BLOCK_N + static_cast<int>(half) * kCols;
@@ -882,7 +928,7 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                             for (int i = 0; i < kCols / 4; ++i)
                                 st_global_v4(dst + i * 4, acc[i * 4 + 0], acc[i * 4 + 1], acc[i * 4 + 2], acc[i * 4 + 3]);
                         }
-                    } else if (!via_tma) {
+                    } else if (!via_tma && p.ret_src == nullptr) {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + row * p.d_row_stride + col0;
 #pragma unroll
                         for (int i = 0; i < kCols / 8; ++i)

@@ -45,6 +45,9 @@ int dgb200_get_num_sms(void);
  *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
  *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
  *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
+ *   "fused_return"       expert-parallel layer with guest experts: 1 (default) = the down GEMM sends every output row to
+ *                        the rank its token came from straight from its epilogue (GEMM and transfer in one kernel, tile by
+ *                        tile); 0 = the GEMM writes its rows locally and a kernel of its own sends them afterwards.
  *   "pdl"                1 (default) = the kernels of the single-rank layer and of the GEMM entry points are launched
  *                        with programmatic stream serialization: a kernel may start while its predecessor in the
  *                        stream still runs and waits (griddepcontrol.wait) before it touches memory. 0 = plain

@@ -195,6 +195,16 @@ def _worker_spill(rank, world, port, results):
             assert status[0] == 0, status
             out['y_' + name] = y.cpu()
             out['stats_' + name] = stats.cpu()
+        # the down GEMM writes its rows locally and a separate kernel sends them back (the default sends them from the GEMM's
+        # epilogue): same rows, same local combine, same bits
+        _lib.check(_lib.lib().dgb200_set_tuning(b'fused_return', 0))
+        try:
+            y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+            dg.fp8_fp4_mega_moe(y, l1s, l2s, buf)
+            assert _lib.device_status()[0] == 0
+            out['y_separate_return'] = y.cpu()
+        finally:
+            _lib.check(_lib.lib().dgb200_set_tuning(b'fused_return', 1))
         # the same calls with the row-moving kernels on the library's second stream, beside the GEMMs of four expert phases
         _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', 16))
         try:
@@ -248,6 +258,7 @@ def test_two_rank_hot_expert_spill_matches_oracle():
         # a row's arithmetic does not depend on the rank that computes it; the tile orientation the layer picks for an
         # expert by its row count may, in the last bits of the FP32 sums
         assert quant.calc_diff(got['y_spill'], got['y_plain']) <= 1e-6
+        assert torch.equal(got['y_separate_return'], got['y_spill']), 'returning rows from the GEMM epilogue must not change them'
         assert quant.calc_diff(got['y_two_streams'], got['y_spill']) <= 1e-6
         assert quant.calc_diff(got['y_two_streams_plain'], got['y_spill']) <= 1e-6
         assert torch.equal(got['y_two_streams'], got['y_two_streams_again'])
