@@ -407,7 +407,19 @@ def _worker_full(rank, world, port, results):
                 q2, s2 = dg.utils.per_token_cast_to_fp4(w2, use_ue8m0=True, gran_k=32)
                 rows.append((q1.cpu(), s1.cpu(), q2.cpu(), s2.cpu()))
             samples[t] = dict(x_q=x_q[t:t + 1].cpu(), x_sf=x_sf[t:t + 1].cpu(), rows=rows, w=buf.topk_weights[t].cpu(), y=y[t].cpu())
-        results[rank] = dict(idx=idx, all_idx=[a.cpu() for a in all_idx], dest=dest, end=end, logits=logits.cpu(), samples=samples)
+        # the same batch with guest experts: rows of hot experts move to the other rank, whose down GEMM (like everyone's)
+        # sends its output rows back from its epilogue; compared with the run above over ALL tokens
+        from oracle import quant
+        l1s, l2s = dg.share_weights_for_mega_moe(dist.group.WORLD, l1, l2, num_guest_experts=4)
+        y_spill = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+        dg.fp8_fp4_mega_moe_bf16_input(y_spill, x, l1s, l2s, buf, logits=logits, fast_math=False)
+        assert _lib.device_status()[0] == 0
+        take = lambda key, n: buf.buffer[lay[key]:lay[key] + n * 4].view(torch.int32).cpu().clone()
+        spill = dict(diff=float(quant.calc_diff(y_spill.cpu(), y.cpu())), same_rows=int((y_spill == y).all(dim=1).sum()),
+                     dest=take('dest_row', tokens * topk), start=take('expert_start', per_rank + 4), end=take('expert_end', per_rank + 4),
+                     my_dest=take('my_dest', experts), my_slot=take('my_slot', experts), guest=take('guest_expert', 4))
+        results[rank] = dict(idx=idx, all_idx=[a.cpu() for a in all_idx], dest=dest, end=end, logits=logits.cpu(), samples=samples,
+                             spill=spill)
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -440,6 +452,16 @@ def test_two_rank_full_size_plan_and_sampled_tokens():
                 a2 = quant.dequantize_fp8(a2_q, a2_sf, 32) @ quant.dequantize_fp4(q2, s2, 32).T
                 acc += a2.bfloat16().float()[0]
             assert quant.calc_diff(s['y'], acc.bfloat16()) <= 2e-3
+        # guest experts at full size: the plan is the oracle's, rows were moved, and all 8192 outputs agree with the run
+        # that kept every expert's rows on its owner (most of them bit for bit: only the tile orientation chosen for an
+        # expert whose row count changed can alter the last bits of an FP32 sum)
+        sp = got['spill']
+        my_base, my_dest, my_slot, start, end, guest = omoe.ep_plan_with_spill(all_counts, rank, 128, 4)
+        assert torch.equal(sp['my_dest'].long(), my_dest) and torch.equal(sp['my_slot'].long(), my_slot)
+        assert torch.equal(sp['guest'].long(), guest) and torch.equal(sp['start'].long(), start) and torch.equal(sp['end'].long(), end)
+        assert torch.equal(sp['dest'].long(), omoe.ep_dest_rows(got['idx'], my_base, experts))
+        assert sp['diff'] <= 1e-6 and sp['same_rows'] >= 8192 * 9 // 10, sp
+    assert sum(int((results[r]['spill']['guest'] >= 0).sum()) for r in range(world)) > 0
 
 
 # ---- the BF16 layer on 2 ranks: the same push / barrier / pull protocol with BF16 rows and no scale factors
