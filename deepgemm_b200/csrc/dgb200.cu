@@ -977,14 +977,17 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                     int32_t* stats, uint8_t* base, const uint64_t* peer_buffer_ptrs, int rank, int num_ranks, int num_tokens,
                     int num_max_tokens_per_rank, int num_experts, int num_topk, int hidden, int intermediate_hidden,
                     float activation_clamp, int fast_math, cudaStream_t stream) {
-    // Expert-parallel layer, every step a kernel on the caller's stream. The local experts of every rank are cut into
-    // up to kMaxEpPhases phases; dispatch, GEMMs and combine run phase by phase behind per-phase flags, so that the
-    // NVLink traffic of one phase overlaps the GEMMs of the others (on the rank that receives the most rows: rows of later
-    // phases arrive while it computes earlier ones, and its peers pull finished phases while it computes the rest):
-    //   count -> publish counts -> flag row 0 (signal + wait) -> plan -> assign
-    //   for each phase q: push the entries of phase-q experts to their owners -> signal "dispatch q"
+    // Expert-parallel layer. The expert slots of every rank (own experts, then guest slots) are cut into `phases` phases:
+    //   count -> publish counts -> flag row 0 (signal + wait) -> plan (every rank derives the same one) -> assign
+    //   for each phase q: push the entries routed to phase-q slots to the ranks that compute them -> signal "dispatch q"
     //   for each phase q: wait "dispatch q" of all ranks -> scale reorder -> L1(q) -> L2(q) -> signal "outputs q"
-    //   for each phase q: wait "outputs q" of all ranks -> combine phase q (pull rows, FP32 running sums; last phase writes y)
+    //   wait "outputs q" of all ranks -> combine
+    // Three arrangements, chosen below:
+    //   guest experts (balanced loads), one stream: a single phase; the down GEMM sends its output rows to their source
+    //     ranks from its epilogue (or a return-push kernel does, where the GEMM variant cannot); the combine is a local sum;
+    //   rows stay on their owners, one stream: up to kMaxEpPhases phases, and the combine pulls the rows of each finished
+    //     phase while the most loaded rank still computes the next;
+    //   ep_comm_sms > 0: pushes and return pushes on a second stream, on SMs the GEMMs leave free.
     // Reference: the fused kernel overlaps the same traffic tile by tile (sm100_fp8_fp4_mega_moe.cuh:533-556, :1274-1300)
     // behind three barriers (comm/barrier.cuh:47-89).
     PeerTable peers{};
