@@ -1042,34 +1042,40 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     const long long* topk_idx = reinterpret_cast<const long long*>(base + l.topk_idx);
     const float* topk_weights = reinterpret_cast<const float*>(base + l.topk_weights);
     const long long peer_budget = tuning().peer_wait_cycles;
+    // On one stream the kernels follow each other with programmatic dependent launch (every one of them starts with
+    // pdl_prologue()); on two streams events sit between them and the launches are plain.
+    const bool pdl = use_pdl();
     auto flag = [&](int row, int do_signal, int do_wait) {
-        dgb200_ep_flag_kernel<<<1, 32, 0, stream>>>(peers, l.flags, row, rank, num_ranks, do_signal, do_wait, peer_budget);
+        launch_kernel(dgb200_ep_flag_kernel, dim3(1), dim3(32), 0, stream, pdl, peers, l.flags, row, rank, num_ranks, do_signal, do_wait,
+                      peer_budget);
     };
     auto phase_begin = [&](int q) { return static_cast<int>(static_cast<long long>(q) * V / phases); };
     int rc = 0;
     if ((rc = record_stage(0, stream))) return rc;
 
     // count this rank's entries per (global) expert and publish the totals to every rank
-    dgb200_moe_count_kernel<<<chunks, kPlanChunk, num_experts * sizeof(int), stream>>>(topk_idx, entries, 0, num_experts, chunk_hist);
-    dgb200_ep_share_counts_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, num_experts, rank, num_ranks, peers, l.all_counts);
+    launch_kernel(dgb200_moe_count_kernel, dim3(chunks), dim3(kPlanChunk), num_experts * sizeof(int), stream, pdl, topk_idx, entries, 0,
+                  num_experts, chunk_hist);
+    launch_kernel(dgb200_ep_share_counts_kernel, dim3(1), dim3(1024), 0, stream, pdl, chunk_hist, chunks, num_experts, rank, num_ranks, peers,
+                  l.all_counts);
     flag(0, 1, 1);
     // the same global plan on every rank
     if (spill)
-        dgb200_ep_spill_plan_kernel<<<1, 1024, static_cast<size_t>(num_ranks) * num_experts * 6, stream>>>(
+        launch_kernel(dgb200_ep_spill_plan_kernel, dim3(1), dim3(1024), static_cast<size_t>(num_ranks) * num_experts * 6, stream, pdl,
             reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank, kSegmentAlignment, G,
             reinterpret_cast<int*>(base + l.my_base), reinterpret_cast<int*>(base + l.my_dest), reinterpret_cast<int*>(base + l.my_slot),
             reinterpret_cast<int*>(base + l.expert_start), reinterpret_cast<int*>(base + l.expert_end),
             reinterpret_cast<int*>(base + l.total_rows), reinterpret_cast<int*>(base + l.guest_expert),
             reinterpret_cast<int*>(base + l.rank_rows), stats);
     else
-        dgb200_ep_plan_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
+        launch_kernel(dgb200_ep_plan_kernel, dim3(1), dim3(1024), 0, stream, pdl, reinterpret_cast<const int*>(base + l.all_counts), num_experts, num_ranks, rank,
                                                        kSegmentAlignment, reinterpret_cast<int*>(base + l.my_base),
                                                        reinterpret_cast<int*>(base + l.expert_start),
                                                        reinterpret_cast<int*>(base + l.expert_end),
                                                        reinterpret_cast<int*>(base + l.total_rows), stats);
     if (entries > 0)
-        dgb200_ep_assign_kernel<<<chunks, kPlanChunk, 32 * num_experts, stream>>>(topk_idx, entries, num_experts, chunk_hist,
-                                                                              reinterpret_cast<const int*>(base + l.my_base), dest_row);
+        launch_kernel(dgb200_ep_assign_kernel, dim3(chunks), dim3(kPlanChunk), 32 * num_experts, stream, pdl, topk_idx, entries, num_experts,
+                      chunk_hist, reinterpret_cast<const int*>(base + l.my_base), dest_row);
     DGB_CUDA(cudaGetLastError());
     if ((rc = record_stage(1, stream))) return rc;
 
@@ -1095,15 +1101,15 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     auto push = [&](int q, cudaStream_t on, bool few_sms) {
         if (entries <= 0) return;
         const RowMoverLaunch shape = row_mover_launch(push_slot_bytes, few_sms);
-        dgb200_ep_push_kernel<<<few_sms ? comm_sms : all_sms, shape.warps * 32, shape.smem_bytes, on>>>(
+        launch_kernel(dgb200_ep_push_kernel, dim3(few_sms ? comm_sms : all_sms), dim3(shape.warps * 32), shape.smem_bytes, on, pdl && !overlap,
             base + l.x, reinterpret_cast<const unsigned*>(base + l.x_sf), topk_idx, topk_weights, dest_row, entries, num_topk,
             static_cast<int>(act_row_bytes(quant.kind, hidden)), sf_per_row, E, rank, entries_per_rank, peers, l.l1_acts,
             l.l1_sf_stage, l.row_weight, l.src_of_row, phase_begin(q), phase_begin(q + 1), my_dest, my_slot);
     };
     auto fetch_guests = [&](cudaStream_t on) {
         // the weights of the experts this rank hosts as a guest, from their owners
-        dgb200_ep_fetch_guest_weights_kernel<<<dim3(overlap ? std::max(1, comm_sms / std::max(1, G)) : 74, G), 256, 0, on>>>(
-            reinterpret_cast<const int*>(base + l.guest_expert), E, guest_tables);
+        launch_kernel(dgb200_ep_fetch_guest_weights_kernel, dim3(overlap ? std::max(1, comm_sms / std::max(1, G)) : 74, G), dim3(256), 0, on,
+                      pdl && !overlap, reinterpret_cast<const int*>(base + l.guest_expert), E, guest_tables);
     };
     // With balanced loads on one stream the down GEMM sends its output rows to their source ranks from its epilogue
     // ("fused_return" tuning knob, on by default), so the transfer runs under the GEMM's own MMAs tile by tile; where the
@@ -1120,7 +1126,8 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         if (g1 == g0) return 0;
         // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
         if (sf_per_row > 0)
-            dgb200_sf_rows_to_cp_order_kernel<<<static_cast<int>(l.max_rows / 32), 256, sf_per_row * 33 * sizeof(unsigned), stream>>>(
+            launch_kernel(dgb200_sf_rows_to_cp_order_kernel, dim3(static_cast<int>(l.max_rows / 32)), dim3(256),
+                sf_per_row * 33 * sizeof(unsigned), stream, pdl && !overlap,
                 reinterpret_cast<const unsigned*>(base + l.l1_sf_stage), static_cast<int>(l.max_rows), sf_per_row,
                 reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows, reinterpret_cast<const int*>(base + l.total_rows),
                 expert_start + g0, expert_end + g1 - 1);
@@ -1137,14 +1144,14 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
         if (g1 == g0) return;
         const RowMoverLaunch shape = row_mover_launch(hidden * 2ll, few_sms);
-        dgb200_ep_return_rows_kernel<<<few_sms ? comm_sms : all_sms, shape.warps * 32, shape.smem_bytes, on>>>(
-            reinterpret_cast<const __nv_bfloat16*>(base + l.l2_out), reinterpret_cast<const int*>(base + l.src_of_row), expert_start,
+        launch_kernel(dgb200_ep_return_rows_kernel, dim3(few_sms ? comm_sms : all_sms), dim3(shape.warps * 32), shape.smem_bytes, on,
+            pdl && !overlap, reinterpret_cast<const __nv_bfloat16*>(base + l.l2_out), reinterpret_cast<const int*>(base + l.src_of_row), expert_start,
             expert_end, g0, g1, hidden, entries_per_rank, peers, l.returned);
     };
     // once every rank's rows of every phase have arrived: a local sum per token, in slot order
     auto combine = [&]() {
         if (num_tokens > 0)
-            dgb200_moe_combine_returned_kernel<<<num_tokens, 128, 0, stream>>>(
+            launch_kernel(dgb200_moe_combine_returned_kernel, dim3(num_tokens), dim3(128), 0, stream, pdl && !overlap,
                 reinterpret_cast<const __nv_bfloat16*>(base + l.returned), dest_row, num_topk, hidden,
                 with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr, static_cast<__nv_bfloat16*>(y));
     };
@@ -1177,7 +1184,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         for (int q = 0; q < phases; ++q) {
             flag(1 + kMaxEpPhases + q, 0, 1);
             if (!spill && num_tokens > 0)
-                dgb200_moe_combine_phase_kernel<<<num_tokens, 128, num_topk * sizeof(unsigned long long), stream>>>(
+                launch_kernel(dgb200_moe_combine_phase_kernel, dim3(num_tokens), dim3(128), num_topk * sizeof(unsigned long long), stream, pdl,
                     peers, l.l2_out, topk_idx, dest_row, num_topk, E, hidden,
                     with_shared ? reinterpret_cast<const __nv_bfloat16*>(base + l.shared_out) : nullptr,
                     reinterpret_cast<float*>(base + l.combine_partial), static_cast<__nv_bfloat16*>(y), phase_begin(q), phase_begin(q + 1),

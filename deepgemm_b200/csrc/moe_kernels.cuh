@@ -283,6 +283,7 @@ dgb200_moe_combine_kernel(const PeerTable peers, long long rows_offset, const lo
 __global__ void __launch_bounds__(1024)
 dgb200_ep_share_counts_kernel(int* __restrict__ chunk_hist, int num_chunks, int num_experts, int my_rank, int num_ranks,
                               const PeerTable peers, long long all_counts_offset) {
+    pdl_prologue();
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
         int count = 0;
         for (int c = 0; c < num_chunks; ++c) {
@@ -315,6 +316,7 @@ constexpr int kEpFlagRows = 1 + 2 * kMaxEpPhases + 4;  // 9 flag rows, then 2 + 
 __global__ void __launch_bounds__(32)
 dgb200_ep_flag_kernel(const PeerTable peers, long long flags_offset, int row, int my_rank, int num_ranks, int do_signal,
                       int do_wait, long long budget_cycles) {
+    pdl_prologue();
     const int lane = threadIdx.x;
     int* local = reinterpret_cast<int*>(peers.p[my_rank] + flags_offset);
     int* sent = local + (kEpFlagRows - 4) * kMaxEpRanks + row;
@@ -364,6 +366,7 @@ __global__ void __launch_bounds__(1024)
 dgb200_ep_plan_kernel(const int* __restrict__ all_counts, int num_experts, int num_ranks, int my_rank, int alignment,
                       int* __restrict__ my_base, int* __restrict__ expert_start, int* __restrict__ expert_end,
                       int* __restrict__ total_rows, int* __restrict__ cumulative_stats) {
+    pdl_prologue();
     __shared__ int warp_sums[32];
     __shared__ int carry;
     const int per_rank = num_experts / num_ranks;
@@ -429,6 +432,7 @@ dgb200_moe_combine_phase_kernel(const PeerTable peers, long long rows_offset, co
                                 const __nv_bfloat16* __restrict__ shared_rows, float* __restrict__ partial,
                                 __nv_bfloat16* __restrict__ y, int local_expert_begin, int local_expert_end, int first, int last,
                                 const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
+    pdl_prologue();
     const int t = blockIdx.x;
     extern __shared__ unsigned long long slot_rows[];  // address of each slot's row of this phase, 0 = skip
     __shared__ int any;
@@ -521,6 +525,7 @@ dgb200_ep_spill_plan_kernel(const int* __restrict__ all_counts, int num_experts,
                             int guest_slots, int* __restrict__ my_base, int* __restrict__ my_dest, int* __restrict__ my_slot,
                             int* __restrict__ slot_start, int* __restrict__ slot_end, int* __restrict__ total_rows,
                             int* __restrict__ guest_expert, int* __restrict__ rank_rows, int* __restrict__ cumulative_stats) {
+    pdl_prologue();
     extern __shared__ int spill_smem[];
     int* counts = spill_smem;                                                              // [ranks][experts]
     unsigned char* dest = reinterpret_cast<unsigned char*>(counts + num_ranks * num_experts);  // [experts][ranks]
@@ -662,6 +667,7 @@ struct GuestWeightTables {
 };
 __global__ void __launch_bounds__(256)
 dgb200_ep_fetch_guest_weights_kernel(const int* __restrict__ guest_expert, int experts_per_rank, const GuestWeightTables t) {
+    pdl_prologue();
     const int e = guest_expert[blockIdx.y];
     if (e < 0) return;
     const int owner = e / experts_per_rank, local_expert = e - owner * experts_per_rank;
@@ -689,6 +695,7 @@ dgb200_ep_fetch_guest_weights_kernel(const int* __restrict__ guest_expert, int e
 __global__ void __launch_bounds__(kPlanChunk)
 dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries, int num_experts,
                         const int* __restrict__ chunk_hist, const int* __restrict__ my_base, int* __restrict__ dest_row) {
+    pdl_prologue();
     extern __shared__ unsigned char warp_hist[];  // [32 warps][num_experts]
     for (int i = threadIdx.x; i < 32 * num_experts; i += blockDim.x) warp_hist[i] = 0;
     __syncthreads();
@@ -776,6 +783,7 @@ dgb200_ep_push_kernel(const unsigned char* __restrict__ x, const unsigned* __res
                       long long acts_offset, long long sf_offset, long long weight_offset,
                       long long src_offset, int local_expert_begin, int local_expert_end,
                       const int* __restrict__ my_dest, const int* __restrict__ my_slot) {
+    pdl_prologue();
     extern __shared__ __align__(16) unsigned char mover_smem[];
     __shared__ uint32_t abort_flag;
     const int sf_bytes = sf_per_row * 4;
@@ -835,6 +843,7 @@ __global__ void __launch_bounds__(1024)
 dgb200_ep_return_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ src_of_row,
                              const int* __restrict__ slot_start, const int* __restrict__ slot_end_rows, int slot_begin,
                              int slot_end, int hidden, int entries_per_rank, const PeerTable peers, long long returned_offset) {
+    pdl_prologue();
     extern __shared__ __align__(16) unsigned char mover_smem[];
     __shared__ uint32_t abort_flag;
     const int row_bytes = hidden * 2;
@@ -864,6 +873,7 @@ dgb200_ep_return_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* 
 __global__ void __launch_bounds__(128)
 dgb200_moe_combine_returned_kernel(const __nv_bfloat16* __restrict__ returned, const int* __restrict__ dest_row, int topk,
                                    int hidden, const __nv_bfloat16* __restrict__ shared_rows, __nv_bfloat16* __restrict__ y) {
+    pdl_prologue();
     const int t = blockIdx.x;
     __shared__ int valid[32];
     if (threadIdx.x < 32) valid[threadIdx.x] = static_cast<int>(threadIdx.x) < topk && dest_row[static_cast<long long>(t) * topk + threadIdx.x] >= 0;
