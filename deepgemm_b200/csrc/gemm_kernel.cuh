@@ -778,7 +778,10 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                         if (store) {
                             const int src = __ldg(p.ret_src + row);
                             const int src_rank = src / p.ret_entries_per_rank;
-                            my_dst = p.ret_base[src_rank] +
+                            // a row whose push never arrived (a rank that timed out) carries a stale source id: never
+                            // index past the table or store through a null base
+                            if (src >= 0 && src_rank < kMaxRanks && p.ret_base[src_rank] != 0)
+                                my_dst = p.ret_base[src_rank] +
                                      (static_cast<unsigned long long>(src - src_rank * p.ret_entries_per_rank) * p.n +
                                       static_cast<unsigned long long>(t.n_block * BLOCK_N + static_cast<int>(half) * kCols)) * 2ull;
                         }

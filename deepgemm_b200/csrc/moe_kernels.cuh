@@ -858,6 +858,8 @@ dgb200_ep_return_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* 
         for (int r = slot_start[v] + warp; r < end && ok; r += num_warps) {
             const int src = src_of_row[r];
             const int rank = src / entries_per_rank, entry = src - rank * entries_per_rank;
+            // a row whose push never arrived (a rank that timed out) carries a stale source id: skip what cannot be a rank
+            if (src < 0 || rank >= kMaxEpRanks || peers.p[rank] == 0) continue;
             ok = row_mover_copy(mover, rows + static_cast<long long>(r) * hidden,
                                 reinterpret_cast<void*>(peers.p[rank] + returned_offset + static_cast<long long>(entry) * row_bytes),
                                 static_cast<uint32_t>(row_bytes), nullptr, nullptr, 0u);
