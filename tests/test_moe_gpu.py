@@ -302,6 +302,45 @@ def test_programmatic_dependent_launch_on_and_off(dg):
         assert all(torch.equal(a, b) for a, b in zip(plan, plans[0]))
 
 
+def test_layer_inside_a_cuda_graph(dg):
+    """The single-rank layer captured into a CUDA graph (after one eager call, which creates the library's side stream and
+    sets the kernels' attributes) and replayed on new inputs: the fork / join of the split GEMMs, the memset of the plan and
+    the programmatic dependent launches must all be capturable, and a replay must give the bits of an eager call."""
+    tokens, hidden, inter, experts, topk = 300, 512, 256, 4, 2  # about 150 rows per expert: the GEMMs split by expert size
+    c = moe_case(tokens, hidden, inter, experts, topk, seed=71)
+    c2 = moe_case(tokens, hidden, inter, experts, topk, seed=72)
+    for k in ('l1_q', 'l1_sf', 'l2_q', 'l2_sf'):
+        c2[k] = c[k]
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    l1, l2 = _device_weights(dg, c)
+    y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+
+    def load(case):
+        buf.x[:tokens].copy_(case['x_q'].cuda())
+        buf.x_sf[:tokens].copy_(quant.pack_ue8m0(case['x_sf']).cuda())
+        buf.topk_idx[:tokens].copy_(case['topk_idx'].cuda())
+        buf.topk_weights[:tokens].copy_(case['topk_weights'].cuda())
+
+    from deepgemm_b200 import _lib
+    load(c)
+    dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+    assert _lib.device_status()[0] == 0
+    eager = y.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+    y.fill_(float('nan'))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, eager), 'a replay on the same inputs gives the eager bits'
+    load(c2)
+    y.fill_(float('nan'))
+    graph.replay()
+    assert _lib.device_status()[0] == 0
+    want = omoe.moe_layer(c2['x_q'], c2['x_sf'], c2['topk_idx'], c2['topk_weights'], c2['l1_q'], c2['l1_sf'], c2['l2_q'], c2['l2_sf'])
+    assert quant.calc_diff(y.cpu(), want) <= FP4_TOL
+
+
 def test_peer_wait_runs_out_and_the_library_stays_usable(dg):
     """Failure detection of the expert-parallel barrier, on one GPU and without faulting it: the layer is called as rank 0
     of 2 with both entries of the peer table pointing at this process's own buffer, so the flag "rank 1" should write
