@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument('--comm-sms', type=int, default=-1,
                     help='expert-parallel runs: SMs kept for the kernels that move rows while the GEMMs run (the library\'s '
                          '"ep_comm_sms" knob; -1 = its default, 0 = one stream without overlap)')
+    ap.add_argument('--fused-dispatch', type=int, default=-1,
+                    help='expert-parallel runs: the library\'s "fused_dispatch" knob (-1 = its default)')
     ap.add_argument('--fused-return', type=int, default=-1,
                     help='expert-parallel runs: the library\'s "fused_return" knob (-1 = its default)')
     ap.add_argument('--pdl', type=int, default=-1, help='programmatic dependent launch: 0 / 1 (-1 = the library\'s default)')
@@ -1025,6 +1027,9 @@ def main():
     if args.fused_return >= 0:
         from deepgemm_b200 import _lib
         _lib.check(_lib.lib().dgb200_set_tuning(b'fused_return', args.fused_return))
+    if args.fused_dispatch >= 0:
+        from deepgemm_b200 import _lib
+        _lib.check(_lib.lib().dgb200_set_tuning(b'fused_dispatch', args.fused_dispatch))
     rc = run_ours(args, cfg, rank, world, local_rank)
     if world > 1:
         import torch.distributed as dist

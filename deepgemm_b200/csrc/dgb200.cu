@@ -89,6 +89,7 @@ struct Tuning {
                           // 1 = the fused expert-MLP kernel on single CTAs, 2 = on CTA pairs; -1 = not yet read from
                           // the environment (DGB200_MLP_KERNEL, default below)
     int fused_return = 1;  // expert-parallel layer with guest experts: the down GEMM's epilogue sends the output rows back
+    int fused_dispatch = 0;  // ... and the gate/up GEMM of expert phase q pushes the dispatch rows of phase q + 1
     int pdl = 1;  // programmatic dependent launch between the kernels of the single-rank layer (set_pdl)
     int ep_comm_sms = 0;  // expert-parallel layer: SMs kept free of GEMM CTAs for kernels that move rows over NVLink on a
                           // second stream while the GEMMs run (0 = one stream: every kernel on all SMs)
@@ -298,7 +299,9 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
     switch (c.epilogue) {
         case kEpiBF16: DGB_LAUNCH(kEpiBF16, kKindFp8Fp4);
         case kEpiF32: DGB_LAUNCH(kEpiF32, kKindFp8Fp4);
-        case kEpiSwiGLU: DGB_LAUNCH(kEpiSwiGLU, kKindFp8Fp4);
+        case kEpiSwiGLU:
+            if (p.push.list != nullptr) return launch_gemm<256, 4, kEpiSwiGLUPush, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
+            DGB_LAUNCH(kEpiSwiGLU, kKindFp8Fp4);
         default: return fail(DGB200_EINVAL, "unknown epilogue %d", c.epilogue);
     }
 #undef DGB_LAUNCH
@@ -493,6 +496,8 @@ struct MegaLayout {
     long long l1_sf_stage;  // expert parallel: row-major landing area of pushed scale ints [max_rows][ints per row]
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
     long long combine_partial;  // expert parallel, pull combine: fp32 [max tokens, hidden], the running sums between phases
+    long long push_lists;  // expert parallel: [kMaxEpPhases] entry lists (max tokens * topk ints each) of the dispatch that rides on the
+                           // gate/up GEMMs, then kMaxEpPhases counters
     long long returned;  // expert parallel, return push: bf16 [max tokens * topk, hidden], the output rows the computing ranks sent back
     long long tile_done;  // FP8 kind: one counter per token tile of the fused expert-MLP kernel (max_rows / 128 + local experts)
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
@@ -582,6 +587,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_slots) * 4) : 0;
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.combine_partial = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * hidden * 4) : 0;
+    l.push_lists = num_ranks > 1 ? take(kMaxEpPhases * (static_cast<long long>(max_tokens) * topk * 4 + 64)) : 0;
     l.returned = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * topk * hidden * 2) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
@@ -710,6 +716,19 @@ int run_expert_mlp(bool pair, const MegaLayout& l, uint8_t* base, const void* l1
 // The two grouped GEMMs of the layer over this rank's expert-sorted rows (shared by the single-rank and the
 // expert-parallel paths): L1 writes quantised activations + scales (FP8/UE8M0 or NVFP4/UE4M3), L2 writes BF16 rows
 // into l2_out in the same row order.
+// Which tile orientation serves the layer's two GEMMs (the reasons are in run_layer_gemms).
+enum LayerOrientation { kOrientM, kOrientSplit, kOrientSwapAll };
+
+LayerOrientation layer_orientation(int kind, int num_groups, int hidden, int intermediate_hidden, long long expected_rows_per_expert) {
+    if (kind == kKindFp8Fp4 && num_groups <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
+        if (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= 40)) return kOrientSwapAll;
+        if (tuning().swap_ab == 2 ||
+            (tuning().swap_ab == -1 && expected_rows_per_expert >= 100 && expected_rows_per_expert <= kSwapMaxTok + 16))
+            return kOrientSplit;
+    }
+    return kOrientM;
+}
+
 // Where the down GEMM of the expert-parallel layer may send its output rows instead of writing them to l2_out: row r goes
 // to row src_of_row[r] % entries_per_rank of the `returned` buffer of rank src_of_row[r] / entries_per_rank.
 struct ReturnSpec {
@@ -721,7 +740,8 @@ struct ReturnSpec {
 int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base, const void* l1_w, const void* l1_w_sf, const void* l2_w,
                     const void* l2_w_sf, int hidden, int intermediate_hidden, float activation_clamp, int fast_math,
                     cudaStream_t stream, int stage_event_base, long long expected_rows_per_expert, int group_begin = 0,
-                    int group_end = 0, const ReturnSpec* ret = nullptr, bool* returned_by_gemm = nullptr) {
+                    int group_end = 0, const ReturnSpec* ret = nullptr, bool* returned_by_gemm = nullptr,
+                    const PushWork* push = nullptr) {
     const int E = l.num_local_experts + quant.guest_slots;  // guest slots follow the rank's own experts, in the plan and in the weights
     // [group_begin, group_end): the expert slots this call computes ({0, 0} = all of them)
     const int first_expert = (group_begin == 0 && group_end == 0) ? 0 : group_begin;
@@ -749,14 +769,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         const int rc_ev = record_stage(stage_event_base, stream);  // one launch: the down stage's share is inside the first interval
         return rc_ev ? rc_ev : record_stage(stage_event_base + 1, stream);
     }
-    enum { kOrientM, kOrientSplit, kOrientSwapAll } orient = kOrientM;
-    if (!nvfp4 && !bf16 && E <= kMaxCachedGroups && (2 * intermediate_hidden) % 256 == 0 && hidden % 256 == 0) {
-        if (tuning().swap_ab == 1 || (tuning().swap_ab == -1 && expected_rows_per_expert <= 40))
-            orient = kOrientSwapAll;
-        else if (tuning().swap_ab == 2 ||
-                 (tuning().swap_ab == -1 && expected_rows_per_expert >= 100 && expected_rows_per_expert <= kSwapMaxTok + 16))
-            orient = kOrientSplit;
-    }
+    const LayerOrientation orient = layer_orientation(quant.kind, E, hidden, intermediate_hidden, expected_rows_per_expert);
     int rc = 0;
     auto run_split = [&](GemmCall& c) -> int {
         if (orient == kOrientM) return run_gemm(c, stream);
@@ -836,6 +849,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
         p.fast_math = fast_math;
+        if (push != nullptr && orient == kOrientM && !nvfp4 && !bf16) p.push = *push;  // the caller checked that this variant runs
         if ((rc = run_split(c))) return rc;
     }
     if ((rc = record_stage(stage_event_base, stream))) return rc;
@@ -1034,7 +1048,13 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     // (ep_comm_sms > 0) or behind the most loaded rank's GEMMs when rows stay on their owners; with balanced loads on one
     // stream a single phase (fewer launches, larger GEMMs).
     const int comm_sms = tuning().ep_comm_sms;
-    const int phases = fused_mlp ? 1 : std::min((spill && comm_sms == 0) ? 1 : kMaxEpPhases, V);
+    const long long expected_rows = static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts;
+    // "fused_dispatch": with balanced loads on one stream, several phases again, and the gate/up GEMM of phase q carries the
+    // dispatch rows of phase q + 1 in its epilogue warps (only the tokens-on-M variant of the FP8 x FP4 kind can)
+    const bool ride = spill && comm_sms == 0 && tuning().fused_dispatch != 0 && !fused_mlp && V >= 2 &&
+                      layer_orientation(quant.kind, V, hidden, intermediate_hidden, expected_rows) == kOrientM;
+    const int ride_phases = tuning().fused_dispatch >= 2 ? tuning().fused_dispatch : kMaxEpPhases;
+    const int phases = fused_mlp ? 1 : std::min(ride ? ride_phases : ((spill && comm_sms == 0) ? 1 : kMaxEpPhases), V);
     int* chunk_hist = reinterpret_cast<int*>(base + l.chunk_hist);
     int* dest_row = reinterpret_cast<int*>(base + l.dest_row);
     const int* expert_start = reinterpret_cast<const int*>(base + l.expert_start);
@@ -1120,9 +1140,44 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     for (int r = 0; r < num_ranks; ++r) return_spec.returned_base[r] = peers.p[r] + static_cast<unsigned long long>(l.returned);
     const bool fuse_return_into_gemm = spill && !overlap && tuning().fused_return != 0;
     bool returned_by_gemm = false;
+    // the dispatch rows of phase q + 1 that the gate/up GEMM of phase q pushes ("fused_dispatch")
+    const long long list_stride = static_cast<long long>(entries_per_rank);
+    int* push_lists = reinterpret_cast<int*>(base + l.push_lists);
+    int* push_counts = push_lists + kMaxEpPhases * list_stride;
+    auto push_work_for = [&](int phase) {
+        PushWork w{};
+        w.list = push_lists + phase * list_stride;
+        w.count = push_counts + phase;
+        w.x = base + l.x;
+        w.x_sf = reinterpret_cast<const unsigned*>(base + l.x_sf);
+        w.topk_weights = topk_weights;
+        w.topk_idx = topk_idx;
+        w.dest_row = dest_row;
+        w.my_dest = my_dest;
+        w.experts_per_rank = E;
+        w.topk = num_topk;
+        w.row_bytes = static_cast<int>(act_row_bytes(quant.kind, hidden));
+        w.sf_per_row = sf_per_row;
+        w.my_rank = rank;
+        w.entries_per_rank = entries_per_rank;
+        for (int r = 0; r < num_ranks; ++r) {
+            w.acts_base[r] = peers.p[r] + static_cast<unsigned long long>(l.l1_acts);
+            w.sf_base[r] = peers.p[r] + static_cast<unsigned long long>(l.l1_sf_stage);
+            w.weight_base[r] = peers.p[r] + static_cast<unsigned long long>(l.row_weight);
+            w.src_base[r] = peers.p[r] + static_cast<unsigned long long>(l.src_of_row);
+        }
+        return w;
+    };
     auto gemms = [&](int q) -> int {
         const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
         returned_by_gemm = false;
+        PushWork next_phase{};
+        if (ride && q + 1 < phases && entries > 0) next_phase = push_work_for(q + 1);
+        if (g1 == g0 && next_phase.list != nullptr) {
+            // nothing to compute in this phase on this rank: the rows still have to leave
+            push(q + 1, stream, false);
+            return 0;
+        }
         if (g1 == g0) return 0;
         // the scale ints every rank pushed row by row -> the GEMM's MN-major tcgen05.cp order (local, a few microseconds)
         if (sf_per_row > 0)
@@ -1133,10 +1188,9 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
                 expert_start + g0, expert_end + g1 - 1);
         DGB_CUDA(cudaGetLastError());
         return run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream,
-                               kNumStageEvents /* no stage events inside the loop */,
-                               static_cast<long long>(num_max_tokens_per_rank) * num_ranks * num_topk / num_experts,
+                               kNumStageEvents /* no stage events inside the loop */, expected_rows,
                                phases == 1 ? 0 : g0, phases == 1 ? 0 : g1, fuse_return_into_gemm ? &return_spec : nullptr,
-                               &returned_by_gemm);
+                               &returned_by_gemm, next_phase.list != nullptr ? &next_phase : nullptr);
     };
 
     // the BF16 output rows of phase q's expert slots back to the ranks their tokens came from
@@ -1157,7 +1211,12 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
     };
 
     if (!overlap) {
-        for (int q = 0; q < phases; ++q) {
+        if (ride && entries > 0) {
+            DGB_CUDA(cudaMemsetAsync(push_counts, 0, kMaxEpPhases * sizeof(int), stream));
+            launch_kernel(dgb200_ep_phase_lists_kernel, dim3((entries + 255) / 256), dim3(256), 0, stream, false, topk_idx, dest_row, entries, E,
+                          my_slot, phases, V, push_lists, static_cast<int>(list_stride), push_counts);
+        }
+        for (int q = 0; q < (ride ? 1 : phases); ++q) {
             push(q, stream, false);
             flag(1 + q, 1, 0);
         }
@@ -1172,6 +1231,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         for (int q = 0; q < phases; ++q) {
             flag(1 + q, 0, 1);
             if ((rc = gemms(q))) return rc;
+            if (ride && q + 1 < phases) flag(1 + q + 1, 1, 0);  // the next phase's rows left with this phase's gate/up GEMM
             if (spill && !returned_by_gemm) return_rows(q, stream, false);
             flag(1 + kMaxEpPhases + q, 1, 0);
         }
@@ -1409,6 +1469,9 @@ int dgb200_set_tuning(const char* name, int32_t value) {
     } else if (std::strcmp(name, "block_n") == 0) {
         DGB_REQUIRE(value == 0 || value == 128 || value == 256, "block_n must be 0 (automatic), 128 or 256");
         tuning().block_n = value;
+    } else if (std::strcmp(name, "fused_dispatch") == 0) {
+        DGB_REQUIRE(value >= 0 && value <= kMaxEpPhases, "fused_dispatch must be 0 (off), 1 (on, %d phases) or a phase count up to %d", kMaxEpPhases, kMaxEpPhases);
+        tuning().fused_dispatch = value;
     } else if (std::strcmp(name, "fused_return") == 0) {
         DGB_REQUIRE(value == 0 || value == 1, "fused_return must be 0 or 1");
         tuning().fused_return = value;

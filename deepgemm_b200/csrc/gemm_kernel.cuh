@@ -51,6 +51,8 @@ enum EpilogueKind : int {
     kEpiSwiGLUNvfp4 = 3,  // gate/up -> silu(gate)*up*row_weight -> NVFP4 (per-16 UE4M3 scales, given per-tensor scale)
     kEpiSwiGLUBf16 = 4,   // gate/up -> silu(gate)*up*row_weight -> BF16 rows (the BF16 layer)
     kEpiF32Acc = 5,       // D fp32 = C + accumulator; selects the K-grouped form of the kernel (kModeKGrouped)
+    kEpiSwiGLUPush = 6,   // kEpiSwiGLU whose epilogue warps also push dispatch rows of the next expert phase (GemmParams::push):
+                          // an instantiation of its own, so that the plain kernel's register allocation stays as it is
 };
 
 enum MmaKind : int {
@@ -61,6 +63,20 @@ enum MmaKind : int {
 };
 
 constexpr int kMaxRanks = 8;
+
+// Rows the gate/up GEMM's epilogue warps push to other ranks between tiles (see GemmParams::push).
+struct PushWork {
+    const int* list;             // entries (token * topk + k) of the next phase, in any order
+    const int* count;            // their number
+    const unsigned char* x;      // this rank's quantised rows [tokens, row_bytes]
+    const unsigned* x_sf;        // their packed scale ints [tokens, sf_per_row]
+    const float* topk_weights;   // [tokens * topk]
+    const long long* topk_idx;   // [tokens * topk]
+    const int* dest_row;         // row of each entry on the rank that computes it
+    const int* my_dest;          // computing rank per expert (spill plan), or null: expert / experts_per_rank
+    int experts_per_rank, topk, row_bytes, sf_per_row, my_rank, entries_per_rank;
+    unsigned long long acts_base[kMaxRanks], sf_base[kMaxRanks], weight_base[kMaxRanks], src_base[kMaxRanks];  // per rank
+};
 
 struct GemmParams {
     // Scale factors are read through tensor maps over int32 [groups * packed_k, aligned MN] (packed UE8M0, MN-major):
@@ -111,6 +127,10 @@ struct GemmParams {
     const int* ret_src;
     int ret_entries_per_rank;
     unsigned long long ret_base[kMaxRanks];  // each rank's buffer of returned rows as mapped into this process
+    // kEpiSwiGLU, expert-parallel gate/up GEMM only: between its tiles every epilogue warp also pushes some of the rows this
+    // rank routes to the NEXT expert phase into the buffers of the ranks that compute them (the dispatch of phase q + 1
+    // rides on the GEMM of phase q, whose epilogue warps are idle most of a tile). push.list == nullptr: nothing to push.
+    PushWork push;
 };
 
 // K rows [start, start + len) of group `g` of a K-grouped operand; `prev_end` carries the running end between calls
@@ -304,11 +324,13 @@ constexpr int kGemmThreads = 384;       // warps 0-3: loaders / MMA / transposer
 constexpr int kRegsControlWarps = 96;   // after setmaxnreg: the control warpgroup gives registers away ...
 constexpr int kRegsEpilogueWarps = 200; // ... to the two epilogue warpgroups, which hold a drained accumulator
 
-template <int BLOCK_N, int kStages, int EPI, int kKind = kKindFp8Fp4>
+template <int BLOCK_N, int kStages, int kEpilogue, int kKind = kKindFp8Fp4>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                            const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ GemmParams p) {
+    constexpr bool kPushes = kEpilogue == kEpiSwiGLUPush;
+    constexpr int EPI = kPushes ? static_cast<int>(kEpiSwiGLU) : kEpilogue;
     using L = GemmSmem<BLOCK_N, kStages, kKind, EPI == kEpiF32Acc>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N must be 128 or 256");
     static_assert(L::kDynamicBytes <= 232448, "shared memory budget");
@@ -717,6 +739,42 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         const uint32_t q = warp & 3, half = (warp - 4) >> 2;
         const int r = static_cast<int>(q * 32 + lane);
         bool ok = true;
+        // rows of the next expert phase this warp pushes between its tiles: entries cursor, cursor + all epilogue warps, ...
+        int push_cursor = static_cast<int>(blockIdx.x * 8 + (warp - 4)), push_count = 0;
+        if constexpr (kPushes) {
+            if (p.push.list != nullptr) push_count = __ldg(p.push.count);
+        }
+        auto push_rows = [&](int max_rows) {
+            if constexpr (kPushes) {
+                const PushWork& w = p.push;
+                for (int n = 0; n < max_rows && push_cursor < push_count; ++n, push_cursor += static_cast<int>(gridDim.x) * 8) {
+                    const int entry = __ldg(w.list + push_cursor);
+                    const int token = entry / w.topk;
+                    const int expert = static_cast<int>(__ldg(w.topk_idx + entry));
+                    const int owner = w.my_dest != nullptr ? __ldg(w.my_dest + expert) : expert / w.experts_per_rank;
+                    const long long dest = __ldg(w.dest_row + entry);
+                    const uint4* from = reinterpret_cast<const uint4*>(w.x + static_cast<long long>(token) * w.row_bytes);
+                    uint4* to = reinterpret_cast<uint4*>(w.acts_base[owner] + dest * w.row_bytes);
+                    const int vecs = w.row_bytes / 16;
+                    for (int c0 = static_cast<int>(lane); c0 < vecs; c0 += 32 * 7) {
+                        uint4 v[7];
+#pragma unroll
+                        for (int j = 0; j < 7; ++j)
+                            if (c0 + 32 * j < vecs) v[j] = ld_global_nc_v4(from + c0 + 32 * j);
+#pragma unroll
+                        for (int j = 0; j < 7; ++j)
+                            if (c0 + 32 * j < vecs) st_global_v4(to + c0 + 32 * j, v[j].x, v[j].y, v[j].z, v[j].w);
+                    }
+                    unsigned* sf_to = reinterpret_cast<unsigned*>(w.sf_base[owner]) + dest * w.sf_per_row;
+                    for (int c = static_cast<int>(lane); c < w.sf_per_row; c += 32)
+                        sf_to[c] = __ldg(w.x_sf + static_cast<long long>(token) * w.sf_per_row + c);
+                    if (lane == 0) {
+                        reinterpret_cast<float*>(w.weight_base[owner])[dest] = __ldg(w.topk_weights + entry);
+                        reinterpret_cast<int*>(w.src_base[owner])[dest] = w.my_rank * w.entries_per_rank + entry;
+                    }
+                }
+            }
+        };
         while (ok && sched.next(t)) {
             if (t.group < 0) continue;
             const uint32_t as = iter % kNumAccum, aphase = (iter / kNumAccum) & 1;
@@ -1060,7 +1118,9 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                     }
                 }
             }
+            if constexpr (kPushes) push_rows(2);  // a couple of rows of the next phase's dispatch per tile
         }
+        if constexpr (kPushes) push_rows(0x7fffffff);  // whatever is left of this warp's share
         if (L::kStageBytesPerWarp != 0 && lane == 0) bulk_wait_group_all();  // stores still in flight read this CTA's shared memory
     }
 

@@ -720,6 +720,24 @@ dgb200_ep_assign_kernel(const long long* __restrict__ topk_idx, int num_entries,
     dest_row[i] = my_base[e] + chunk_hist[static_cast<long long>(blockIdx.x) * num_experts + e] + before + rank_in_warp;
 }
 
+// Entry lists of the dispatch that rides on the gate/up GEMMs (GemmParams::push): every valid entry (token, k) of this
+// rank whose expert slot belongs to phase q >= 1 is appended to list q (any order: an entry's destination row is fixed
+// by the plan). Phase 0 is sent by dgb200_ep_push_kernel before the first GEMM. counts must be zero on entry.
+__global__ void __launch_bounds__(256)
+dgb200_ep_phase_lists_kernel(const long long* __restrict__ topk_idx, const int* __restrict__ dest_row, int num_entries,
+                             int experts_per_rank, const int* __restrict__ my_slot, int num_phases, int num_slots,
+                             int* __restrict__ lists, int list_stride, int* __restrict__ counts) {
+    pdl_prologue();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_entries || dest_row[i] < 0) return;
+    const int expert = static_cast<int>(topk_idx[i]);
+    const int slot = my_slot != nullptr ? my_slot[expert] : expert % experts_per_rank;
+    int phase = 0;
+    while (phase + 1 < num_phases && slot >= static_cast<int>(static_cast<long long>(phase + 1) * num_slots / num_phases)) ++phase;
+    if (phase == 0) return;
+    lists[static_cast<long long>(phase) * list_stride + atomicAdd(&counts[phase], 1)] = i;
+}
+
 // ---- rows between ranks through the bulk-copy unit --------------------------------------------------------------------------
 // The kernels that move rows between ranks (dispatch push, return push) read local memory and write a peer's. While GEMMs
 // hold most SMs they run on a handful of SMs, so what they move is bounded by the bytes each SM keeps in flight: every

@@ -45,6 +45,10 @@ int dgb200_get_num_sms(void);
  *                        rows per expert, tokens-on-M kernel otherwise), 0 = tokens-on-M kernel only, 1 = everything
  *                        through the swapped-operand kernel including its fused SwiGLU epilogue, 2 = the size split
  *                        with every expert of up to 160 rows on the swapped side (1 and 2: testing, experiments).
+ *   "fused_dispatch"     expert-parallel layer with guest experts: 0 (default) = the dispatch push is a kernel of its own;
+ *                        1 or a phase count 2..4 = several expert phases, and the epilogue warps of the gate/up GEMM of
+ *                        phase q also push the rows this rank routes to phase q + 1 (measured slower than the default:
+ *                        the guest experts balance a rank's total rows, not its rows per phase).
  *   "fused_return"       expert-parallel layer with guest experts: 1 (default) = the down GEMM sends every output row to
  *                        the rank its token came from straight from its epilogue (GEMM and transfer in one kernel, tile by
  *                        tile); 0 = the GEMM writes its rows locally and a kernel of its own sends them afterwards.

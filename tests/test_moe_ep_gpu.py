@@ -205,6 +205,17 @@ def _worker_spill(rank, world, port, results):
             out['y_separate_return'] = y.cpu()
         finally:
             _lib.check(_lib.lib().dgb200_set_tuning(b'fused_return', 1))
+        # four expert phases on one stream, the dispatch rows of phase q + 1 pushed by the epilogue warps of the gate/up GEMM of
+        # phase q: the same rows land in the same places
+        _lib.check(_lib.lib().dgb200_set_tuning(b'fused_dispatch', 1))
+        try:
+            for name in ('y_riding_dispatch', 'y_riding_dispatch_again'):
+                y = torch.full((t, HIDDEN), float('nan'), dtype=torch.bfloat16, device='cuda')
+                dg.fp8_fp4_mega_moe(y, l1s, l2s, buf)
+                assert _lib.device_status()[0] == 0
+                out[name] = y.cpu()
+        finally:
+            _lib.check(_lib.lib().dgb200_set_tuning(b'fused_dispatch', 0))
         # the same calls with the row-moving kernels on the library's second stream, beside the GEMMs of four expert phases
         _lib.check(_lib.lib().dgb200_set_tuning(b'ep_comm_sms', 16))
         try:
@@ -259,6 +270,8 @@ def test_two_rank_hot_expert_spill_matches_oracle():
         # expert by its row count may, in the last bits of the FP32 sums
         assert quant.calc_diff(got['y_spill'], got['y_plain']) <= 1e-6
         assert torch.equal(got['y_separate_return'], got['y_spill']), 'returning rows from the GEMM epilogue must not change them'
+        assert torch.equal(got['y_riding_dispatch'], got['y_spill']), 'rows pushed by the gate/up GEMM must give the same bits'
+        assert torch.equal(got['y_riding_dispatch'], got['y_riding_dispatch_again'])
         assert quant.calc_diff(got['y_two_streams'], got['y_spill']) <= 1e-6
         assert quant.calc_diff(got['y_two_streams_plain'], got['y_spill']) <= 1e-6
         assert torch.equal(got['y_two_streams'], got['y_two_streams_again'])
