@@ -1034,7 +1034,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         code = torch.tensor([rc], device='cuda')
-        dist.broadcast(code, 0)  # every rank leaves with rank 0's verdict on the parity check
+        dist.broadcast(code, 0)  # every rank leaves with rank 0's outcome of the parity check
         rc = int(code)
         dist.barrier()
         dist.destroy_process_group()
