@@ -897,6 +897,9 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         line['hot_expert_spill'] = {
             'guest_slots_per_rank': guests,
             'guest_slots_used': int(table[:, 11].sum()),
+            'routing': 'router logits biased by the log of a Zipf(1.0) popularity over a seeded permutation of the experts',
+            'return_transfer': ('inside the down GEMM (rows stored to their source ranks from its epilogue)' if guests and args.comm_sms <= 0
+                                and args.fused_return != 0 else 'a kernel of its own' if guests else 'pulled by the combine, phase by phase'),
             'load_imbalance_as_routed': (max(rows_before_spill) / (sum(rows_before_spill) / world)) if rows_before_spill else
             line['load_imbalance_max_over_mean'],
         }
