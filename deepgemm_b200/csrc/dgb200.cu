@@ -300,7 +300,7 @@ int run_gemm(GemmCall& c, cudaStream_t stream) {
         case kEpiBF16: DGB_LAUNCH(kEpiBF16, kKindFp8Fp4);
         case kEpiF32: DGB_LAUNCH(kEpiF32, kKindFp8Fp4);
         case kEpiSwiGLU:
-            if (p.push.list != nullptr) return launch_gemm<256, 4, kEpiSwiGLUPush, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
+            if (p.push != nullptr) return launch_gemm<256, 4, kEpiSwiGLUPush, kKindFp8Fp4>(tm_a, tm_b, tm_sfa, tm_sfb, tm_out, p, grid, stream);
             DGB_LAUNCH(kEpiSwiGLU, kKindFp8Fp4);
         default: return fail(DGB200_EINVAL, "unknown epilogue %d", c.epilogue);
     }
@@ -497,7 +497,7 @@ struct MegaLayout {
     long long l1_tmp;  // FP8 kind: bf16 [max_rows, 2 * inter], gate/up activations of the experts the swapped kernel serves
     long long combine_partial;  // expert parallel, pull combine: fp32 [max tokens, hidden], the running sums between phases
     long long push_lists;  // expert parallel: [kMaxEpPhases] entry lists (max tokens * topk ints each) of the dispatch that rides on the
-                           // gate/up GEMMs, then kMaxEpPhases counters
+                           // gate/up GEMMs, then kMaxEpPhases counters, then kMaxEpPhases PushWork descriptors
     long long returned;  // expert parallel, return push: bf16 [max tokens * topk, hidden], the output rows the computing ranks sent back
     long long tile_done;  // FP8 kind: one counter per token tile of the fused expert-MLP kernel (max_rows / 128 + local experts)
     // shared experts (token order, token_rows = capacity in rows): x scales in GEMM order, activations, output rows
@@ -587,7 +587,7 @@ int make_mega_layout(int kind, int num_ranks, int num_experts, int max_tokens, i
     l.tile_done = kind == kKindFp8Fp4 ? take((l.max_rows / 128 + l.num_slots) * 4) : 0;
     l.l1_sf_stage = num_ranks > 1 ? take(l.max_rows * sf_ints_per_row(kind, hidden) * 4) : 0;
     l.combine_partial = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * hidden * 4) : 0;
-    l.push_lists = num_ranks > 1 ? take(kMaxEpPhases * (static_cast<long long>(max_tokens) * topk * 4 + 64)) : 0;
+    l.push_lists = num_ranks > 1 ? take(kMaxEpPhases * (static_cast<long long>(max_tokens) * topk * 4 + 64 + static_cast<long long>(sizeof(PushWork)))) : 0;
     l.returned = num_ranks > 1 ? take(static_cast<long long>(max_tokens) * topk * hidden * 2) : 0;
     l.token_rows = (static_cast<long long>(max_tokens) + 127) / 128 * 128;
     if (shared_inter > 0) {
@@ -849,7 +849,7 @@ int run_layer_gemms(const LayerQuant& quant, const MegaLayout& l, uint8_t* base,
         p.row_weight = reinterpret_cast<const float*>(base + l.row_weight);
         p.clamp = (activation_clamp > 0.0f && activation_clamp < 3.0e38f) ? activation_clamp : 0.0f;
         p.fast_math = fast_math;
-        if (push != nullptr && orient == kOrientM && !nvfp4 && !bf16) p.push = *push;  // the caller checked that this variant runs
+        if (push != nullptr && orient == kOrientM && !nvfp4 && !bf16) p.push = push;  // device memory; the caller checked that this variant runs
         if ((rc = run_split(c))) return rc;
     }
     if ((rc = record_stage(stage_event_base, stream))) return rc;
@@ -1172,7 +1172,12 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         const int g0 = phase_begin(q), g1 = phase_begin(q + 1);
         returned_by_gemm = false;
         PushWork next_phase{};
-        if (ride && q + 1 < phases && entries > 0) next_phase = push_work_for(q + 1);
+        PushWork* next_phase_dev = nullptr;  // the descriptor as the kernel reads it
+        if (ride && q + 1 < phases && entries > 0) {
+            next_phase = push_work_for(q + 1);
+            next_phase_dev = reinterpret_cast<PushWork*>(push_counts + 16 * kMaxEpPhases) + (q + 1);
+            DGB_CUDA(cudaMemcpyAsync(next_phase_dev, &next_phase, sizeof(PushWork), cudaMemcpyHostToDevice, stream));
+        }
         if (g1 == g0 && next_phase.list != nullptr) {
             // nothing to compute in this phase on this rank: the rows still have to leave
             push(q + 1, stream, false);
@@ -1190,7 +1195,7 @@ int run_mega_moe_ep(const LayerQuant& quant, const MegaLayout& l, void* y, const
         return run_layer_gemms(quant, l, base, l1_w, l1_w_sf, l2_w, l2_w_sf, hidden, intermediate_hidden, activation_clamp, fast_math, stream,
                                kNumStageEvents /* no stage events inside the loop */, expected_rows,
                                phases == 1 ? 0 : g0, phases == 1 ? 0 : g1, fuse_return_into_gemm ? &return_spec : nullptr,
-                               &returned_by_gemm, next_phase.list != nullptr ? &next_phase : nullptr);
+                               &returned_by_gemm, next_phase_dev);
     };
 
     // the BF16 output rows of phase q's expert slots back to the ranks their tokens came from

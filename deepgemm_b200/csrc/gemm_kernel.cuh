@@ -64,7 +64,7 @@ enum MmaKind : int {
 
 constexpr int kMaxRanks = 8;
 
-// Rows the gate/up GEMM's epilogue warps push to other ranks between tiles (see GemmParams::push).
+// Rows the gate/up GEMM's epilogue warps push to other ranks between tiles (see GemmParams::push). Lives in device memory.
 struct PushWork {
     const int* list;             // entries (token * topk + k) of the next phase, in any order
     const int* count;            // their number
@@ -129,8 +129,9 @@ struct GemmParams {
     unsigned long long ret_base[kMaxRanks];  // each rank's buffer of returned rows as mapped into this process
     // kEpiSwiGLU, expert-parallel gate/up GEMM only: between its tiles every epilogue warp also pushes some of the rows this
     // rank routes to the NEXT expert phase into the buffers of the ranks that compute them (the dispatch of phase q + 1
-    // rides on the GEMM of phase q, whose epilogue warps are idle most of a tile). push.list == nullptr: nothing to push.
-    PushWork push;
+    // rides on the GEMM of phase q, whose epilogue warps are idle most of a tile). Null: nothing to push. A pointer to device
+    // memory, not a member: the descriptor is large and kernel parameters are copied at every launch of every variant.
+    const PushWork* push;
 };
 
 // K rows [start, start + len) of group `g` of a K-grouped operand; `prev_end` carries the running end between calls
@@ -742,11 +743,11 @@ dgb200_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // rows of the next expert phase this warp pushes between its tiles: entries cursor, cursor + all epilogue warps, ...
         int push_cursor = static_cast<int>(blockIdx.x * 8 + (warp - 4)), push_count = 0;
         if constexpr (kPushes) {
-            if (p.push.list != nullptr) push_count = __ldg(p.push.count);
+            if (p.push != nullptr) push_count = __ldg(p.push->count);
         }
         auto push_rows = [&](int max_rows) {
             if constexpr (kPushes) {
-                const PushWork& w = p.push;
+                const PushWork& w = *p.push;
                 for (int n = 0; n < max_rows && push_cursor < push_count; ++n, push_cursor += static_cast<int>(gridDim.x) * 8) {
                     const int entry = __ldg(w.list + push_cursor);
                     const int token = entry / w.topk;
