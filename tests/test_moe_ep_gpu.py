@@ -158,6 +158,9 @@ def _rank_inputs_spill(rank):
     logits = c['logits'].clone()
     logits[:, :3] += 4.0
     c['topk_idx'], c['topk_weights'] = omoe.route_sigmoid_topk(logits, SP_TOPK)
+    mask = torch.rand(c['topk_idx'].shape, generator=torch.Generator().manual_seed(710 + rank)) < 0.1  # masked slots
+    c['topk_idx'] = c['topk_idx'].masked_fill(mask, -1)
+    c['topk_weights'] = c['topk_weights'].masked_fill(mask, 0.0)
     w = moe_case(4, HIDDEN, INTER, SP_EXPERTS, SP_TOPK, seed=79)  # the same weights on every rank
     for k in ('l1_q', 'l1_sf', 'l2_q', 'l2_sf'):
         c[k] = w[k]
