@@ -709,7 +709,10 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
         if events is not None:
             arr = (ctypes.c_void_p * len(events))(*[None if ev is None else ev.cuda_event for ev in events])
             _lib.check(lib.dgb200_set_mega_moe_stage_events(ctypes.cast(arr, ctypes.c_void_p), len(events)))
-        if nvfp4:
+        if nvfp4 and world == 1:
+            # router -> dispatch plan -> BF16 rows quantised to NVFP4 while they are dispatched -> L1 -> L2 -> combine
+            dg.nvfp4_mega_moe_bf16_input(y_out, x_in, l1, l2, buf, x_scale, act_scale, logits=logits_in)
+        elif nvfp4:
             dg.route_sigmoid_topk(logits_in, k, buf.topk_idx, buf.topk_weights)
             dg.per_token_cast_to_nvfp4_into(x_in, x_scale, buf.x, buf.x_sf)
             dg.nvfp4_mega_moe(y_out, l1, l2, buf, x_scale, act_scale)
@@ -927,12 +930,12 @@ def layer_line(args, cfg, rank, world, local_rank, steps, warmup, with_e2e=True,
 def kernels_of_one_step(nvfp4, world, local_experts, guests=0, comm_sms=0):
     """Launches of this library's kernels in one pass of the layer (memsets are not kernels of ours). FP8 layer on one
     rank: router, count, scan, assign, quantise + dispatch, the two GEMMs each split over the two tile orientations
-    (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4 keeps a separate cast and gather. Expert parallel, P =
+    (2 + 2 launches) plus the SwiGLU finisher, combine; NVFP4: router, count, scan, assign, quantise + dispatch, two GEMMs, combine. Expert parallel, P =
     phases (one with guest experts on one stream, else min(4, expert slots)): router, count, publish counts, flag, plan, assign, quantise, then per phase push + flag,
     flag + scale reorder + L1 + L2, return push + flag, and at the end a flag wait per phase and the combine; with guest
     experts one more launch fetches their weights and the guest slots count as experts."""
     if world == 1:
-        return 9 if nvfp4 else 11
+        return 8 if nvfp4 else 11
     phases = 1 if (guests and comm_sms <= 0) else min(4, local_experts + guests)
     return 7 + 9 * phases + 1 + (1 if guests else 0)
 

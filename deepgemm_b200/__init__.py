@@ -42,6 +42,7 @@ from .mega import (  # noqa: F401
     get_symm_buffer_for_mega_moe,
     get_token_alignment_for_mega_moe,
     nvfp4_mega_moe,
+    nvfp4_mega_moe_bf16_input,
     route_sigmoid_topk,
     share_weights_for_mega_moe,
     transform_weights_for_mega_moe,

@@ -64,6 +64,9 @@ _SIGNATURES = {
     'dgb200_nvfp4_mega_moe': [
         _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
+    'dgb200_nvfp4_mega_moe_bf16_input': [
+        _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+        _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _i32, _ptr],
     'dgb200_get_symm_buffer_layout_for_bf16_mega_moe': [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr],
     'dgb200_bf16_mega_moe': [_ptr, _ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
                              _i32, ctypes.c_float, _i32, _ptr],

@@ -1374,7 +1374,11 @@ int run_mega_moe(const LayerQuant& quant, void* y, const void* l1_w, const void*
     const long long upper_rows = std::min<long long>(l.max_rows, static_cast<long long>(entries) + static_cast<long long>(E) * kSegmentAlignment);
     const int gather_blocks = static_cast<int>((upper_rows + 31) / 32);
     const int sf_per_row = sf_ints_per_row(quant.kind, hidden);
-    if (quant.x_bf16 != nullptr) {
+    if (quant.x_bf16 != nullptr && quant.kind == kKindNvfp4) {
+        DGB_CUDA(launch_kernel(dgb200_moe_quant_dispatch_nvfp4_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0, stream, pdl, quant.x_bf16,
+                               quant.x_bf16_row_stride, quant.x_scale, dest_row, num_tokens, num_topk, hidden, base + l.l1_acts,
+                               reinterpret_cast<unsigned*>(base + l.l1_sf), l.max_rows));
+    } else if (quant.x_bf16 != nullptr) {
         PeerTable self_table{};
         for (int r = 0; r < kMaxEpRanks; ++r) self_table.p[r] = reinterpret_cast<unsigned long long>(base);
         DGB_CUDA(launch_kernel(dgb200_moe_quant_dispatch_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0, stream, pdl, quant.x_bf16,
@@ -2112,6 +2116,40 @@ int dgb200_nvfp4_mega_moe(void* y, const void* l1_w, const void* l1_w_sf, const 
     return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, peer_buffer_ptrs, rank,
                         num_ranks, num_tokens, num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden,
                         activation_clamp, fast_math, static_cast<cudaStream_t>(stream));
+}
+
+int dgb200_nvfp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_stride, const float* logits, const void* l1_w,
+                                     const void* l1_w_sf, const float* l1_w_scales, const void* l2_w, const void* l2_w_sf,
+                                     const float* l2_w_scales, const float* x_scale, const float* act_scale,
+                                     int32_t* cumulative_local_expert_recv_stats, void* buffer, int32_t num_tokens,
+                                     int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
+                                     int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream) {
+    DGB_REQUIRE(l1_w_scales != nullptr && l2_w_scales != nullptr && x_scale != nullptr && act_scale != nullptr,
+                "null per-tensor scale pointer");
+    DGB_REQUIRE(x != nullptr && reinterpret_cast<uintptr_t>(x) % 16 == 0 && x_row_stride >= hidden && (x_row_stride * 2) % 16 == 0,
+                "x must be 16-byte aligned BF16 rows of at least `hidden` elements");
+    if (logits != nullptr && num_tokens > 0) {
+        MegaLayout l;
+        int rc = make_mega_layout(kKindNvfp4, 1, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, &l);
+        if (rc) return rc;
+        DGB_REQUIRE(buffer != nullptr && num_tokens <= num_max_tokens_per_rank, "bad buffer or token count");
+        uint8_t* base = static_cast<uint8_t*>(buffer);
+        rc = dgb200_route_sigmoid_topk(logits, num_tokens, num_experts, num_topk, reinterpret_cast<int64_t*>(base + l.topk_idx),
+                                       reinterpret_cast<float*>(base + l.topk_weights), stream);
+        if (rc) return rc;
+    }
+    LayerQuant quant;
+    quant.kind = kKindNvfp4;
+    quant.x_scale = x_scale;
+    quant.act_scale = act_scale;
+    quant.l1_scales = l1_w_scales;
+    quant.l2_scales = l2_w_scales;
+    quant.x_bf16 = static_cast<const __nv_bfloat16*>(x);
+    quant.x_bf16_row_stride = x_row_stride;
+    const uint64_t self = reinterpret_cast<uint64_t>(buffer);
+    return run_mega_moe(quant, y, l1_w, l1_w_sf, l2_w, l2_w_sf, cumulative_local_expert_recv_stats, buffer, &self, 0, 1, num_tokens,
+                        num_max_tokens_per_rank, num_experts, num_topk, hidden, intermediate_hidden, activation_clamp, fast_math,
+                        static_cast<cudaStream_t>(stream));
 }
 
 int dgb200_get_symm_buffer_layout_for_bf16_mega_moe(int32_t num_ranks, int32_t num_experts, int32_t num_max_tokens_per_rank,

@@ -1016,6 +1016,63 @@ dgb200_moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long 
     }
 }
 
+// The same fusion for the NVFP4 layer on a single rank: one warp per token reads the BF16 row once, quantises it to packed
+// E2M1 with one UE4M3 scale per 16 elements against the given per-tensor scale (the arithmetic of
+// dgb200_cast_rows_nvfp4_kernel, bit for bit: sf = e4m3_rn(amax / 6 / s_t), code = e2m1(v / (float(sf) * s_t)) with the
+// reference's tie-down thresholds) and writes the packed row and its scale ints (one per 64 elements, MN-major in
+// tcgen05.cp row order) into each of its top-k destination rows of the expert-sorted buffers. No reference counterpart.
+__global__ void __launch_bounds__(256)
+dgb200_moe_quant_dispatch_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long x_row_stride,
+                                       const float* __restrict__ tensor_scale, const int* __restrict__ dest_row, int tokens,
+                                       int topk, int hidden, unsigned char* __restrict__ acts, unsigned* __restrict__ acts_sf,
+                                       long long sf_k_stride) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (token >= tokens) return;
+    const int my_dest = lane < topk ? dest_row[token * topk + lane] : -1;
+    const float s_t = __ldg(tensor_scale);
+    const __nv_bfloat16* row = x + static_cast<long long>(token) * x_row_stride;
+    for (int col0 = 0; col0 < hidden; col0 += 512) {
+        const int col = col0 + lane * 16;  // one NVFP4 block per lane
+        const bool valid = col < hidden;   // hidden is a multiple of 64
+        float v[16];
+        float amax = 0.0f;
+        if (valid) {
+            const uint4* src = reinterpret_cast<const uint4*>(row + col);
+            const uint4 r0 = ld_global_nc_v4(src), r1 = ld_global_nc_v4(src + 1);
+            const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+        }
+        const uint32_t sf_byte = e4m3_byte(amax / 6.0f / s_t);
+        const float factor = e4m3_to_float(sf_byte) * s_t;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo |= (factor > 0.0f ? e2m1_code(v[i] / factor) : 0u) << (4 * i);
+            hi |= (factor > 0.0f ? e2m1_code(v[8 + i] / factor) : 0u) << (4 * i);
+        }
+        // packed scale int of 64 elements = the scale bytes of lanes L .. L + 3 (L a multiple of 4)
+        const uint32_t b1 = __shfl_down_sync(0xffffffffu, sf_byte, 1), b2 = __shfl_down_sync(0xffffffffu, sf_byte, 2),
+                       b3 = __shfl_down_sync(0xffffffffu, sf_byte, 3);
+        const uint32_t sf_int = sf_byte | (b1 << 8) | (b2 << 16) | (b3 << 24);
+        for (int k = 0; k < topk; ++k) {
+            const int d = __shfl_sync(0xffffffffu, my_dest, k);
+            if (d < 0 || !valid) continue;
+            *reinterpret_cast<uint2*>(acts + static_cast<long long>(d) * (hidden / 2) + col / 2) = make_uint2(lo, hi);
+            if ((lane & 3) == 0) acts_sf[static_cast<long long>(col >> 6) * sf_k_stride + sf_row_in_cp_order(d)] = sf_int;
+        }
+    }
+}
+
 // Token-major packed scale factors [tokens][ints_per_row] -> MN-major with every 128 rows in tcgen05.cp order
 // (out[c * k_stride + sf_row_in_cp_order(t)]): the form the GEMM reads when the activations stay in token order
 // (shared experts). 32 tokens per CTA through a padded shared-memory tile.

@@ -391,6 +391,43 @@ def nvfp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor
             _lib.current_stream_ptr()))
 
 
+def nvfp4_mega_moe_bf16_input(y: torch.Tensor, x: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor],
+                              l2_weights: Tuple[torch.Tensor, torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
+                              x_scale: torch.Tensor, act_scale: torch.Tensor, logits: Optional[torch.Tensor] = None,
+                              cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                              activation_clamp: Optional[float] = None, fast_math: bool = True) -> None:
+    """``nvfp4_mega_moe`` on a single rank with its prologue fused in (no reference counterpart): ``x`` is BF16
+    [num_tokens, hidden] and is quantised to NVFP4 against ``x_scale`` while it is dispatched; with ``logits`` the router
+    fills the buffer's ``topk_idx`` / ``topk_weights`` first, otherwise the caller has. Same bits as
+    ``per_token_cast_to_nvfp4_into`` + ``route_sigmoid_topk`` + ``nvfp4_mega_moe``."""
+    b = sym_buffer
+    if b.mma_type != 'nvfp4xnvfp4' or b.num_ranks != 1:
+        raise RuntimeError('needs a single-rank buffer created with mma_type=`nvfp4xnvfp4`')
+    _check_weight(l1_weights[0], l1_weights[1], b.num_experts, 2 * b.intermediate_hidden, b.hidden, 'l1_weights', 64)
+    _check_weight(l2_weights[0], l2_weights[1], b.num_experts, b.hidden, b.intermediate_hidden, 'l2_weights', 64)
+    for t, count, name in ((l1_weights[2], b.num_experts, 'l1 tensor scales'), (l2_weights[2], b.num_experts, 'l2 tensor scales'),
+                           (x_scale, 1, 'x_scale'), (act_scale, 1, 'act_scale')):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.numel() == count and t.is_contiguous()):
+            raise RuntimeError(f'{name} must be a contiguous CUDA float32 tensor of {count} element(s)')
+    if not (y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.size(1) == b.hidden and y.is_contiguous()):
+        raise RuntimeError('y must be a contiguous CUDA bfloat16 [num_tokens, hidden] tensor')
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and tuple(x.shape) == tuple(y.shape) and x.stride(1) == 1):
+        raise RuntimeError('x must be a CUDA bfloat16 [num_tokens, hidden] tensor with unit inner stride')
+    if logits is not None and not (logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous() and
+                                   tuple(logits.shape) == (y.size(0), b.num_experts)):
+        raise RuntimeError('logits must be a contiguous CUDA float32 [num_tokens, num_experts] tensor')
+    stats = cumulative_local_expert_recv_stats
+    if stats is not None and not (stats.dtype == torch.int32 and stats.numel() == b.num_experts and stats.is_contiguous()):
+        raise RuntimeError('cumulative_local_expert_recv_stats must be a contiguous int32 [num_experts] tensor')
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.lib().dgb200_nvfp4_mega_moe_bf16_input(
+            p(y), p(x), x.stride(0), p(logits), p(l1_weights[0]), p(l1_weights[1]), p(l1_weights[2]), p(l2_weights[0]),
+            p(l2_weights[1]), p(l2_weights[2]), p(x_scale), p(act_scale), p(stats), p(b.buffer), y.size(0),
+            b.num_max_tokens_per_rank, b.num_experts, b.num_topk, b.hidden, b.intermediate_hidden,
+            float(activation_clamp) if activation_clamp is not None else 0.0, int(fast_math), _lib.current_stream_ptr()))
+
+
 def bf16_mega_moe(y: torch.Tensor, l1_weights: torch.Tensor, l2_weights: torch.Tensor, sym_buffer: SymmBuffer,
                   shared_l1_weights: Optional[torch.Tensor] = None, shared_l2_weights: Optional[torch.Tensor] = None,
                   cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None, activation: str = 'swiglu',

@@ -424,6 +424,19 @@ int dgb200_ep_plan_with_guest_experts(const int32_t* all_counts, int32_t num_ran
                                       int32_t* my_slot, int32_t* slot_start, int32_t* slot_end, int32_t* guest_expert,
                                       int32_t* rank_rows, void* stream);
 
+/* dgb200_nvfp4_mega_moe on a single rank with its prologue fused in (no reference counterpart): x is BF16 [num_tokens,
+ * hidden] (row stride in elements) and is quantised to NVFP4 against x_scale while it is dispatched, so the buffer's
+ * x / x_sf views are not used; with `logits` (float [num_tokens, num_experts], may be NULL) the sigmoid / top-k /
+ * renormalise router fills topk_idx and topk_weights first. Results are bit-identical to dgb200_per_token_cast_to_nvfp4 +
+ * dgb200_route_sigmoid_topk + dgb200_nvfp4_mega_moe. The buffer is the one of
+ * dgb200_get_symm_buffer_layout_for_nvfp4_mega_moe with num_ranks = 1. */
+int dgb200_nvfp4_mega_moe_bf16_input(void* y, const void* x, int64_t x_row_stride, const float* logits, const void* l1_w,
+                                     const void* l1_w_sf, const float* l1_w_scales, const void* l2_w, const void* l2_w_sf,
+                                     const float* l2_w_scales, const float* x_scale, const float* act_scale,
+                                     int32_t* cumulative_local_expert_recv_stats, void* buffer, int32_t num_tokens,
+                                     int32_t num_max_tokens_per_rank, int32_t num_experts, int32_t num_topk, int32_t hidden,
+                                     int32_t intermediate_hidden, float activation_clamp, int32_t fast_math, void* stream);
+
 /* Dispatch plan for callers that cannot allocate device memory. It has no counterpart in the reference.
  * Some hosts of this library run it from places where cudaMalloc is off limits: inside a region whose memory is
  * owned by another allocator with a fixed pool, in a callback that must not synchronise the device, or in a service

@@ -185,6 +185,45 @@ def test_layer_matches_oracle(dg, tokens, hidden, inter, experts, topk, masked):
     assert (got[fully_masked] == 0).all()
 
 
+@pytest.mark.parametrize('tokens,hidden,inter,experts,topk,use_logits', [
+    (200, 512, 256, 8, 2, False),
+    (333, 1024, 256, 16, 4, True),
+    (1, 256, 256, 4, 1, True),
+])
+def test_fused_prologue_gives_the_same_bits(dg, tokens, hidden, inter, experts, topk, use_logits):
+    """nvfp4_mega_moe_bf16_input (BF16 rows quantised to NVFP4 while they are dispatched, router inside the call) against the
+    separate steps per_token_cast_to_nvfp4_into + route_sigmoid_topk + nvfp4_mega_moe: same plan, same output bits."""
+    c = moe_case_nvfp4(tokens, hidden, inter, experts, topk, seed=900 + tokens)
+    torch.manual_seed(tokens)
+    logits = torch.randn(tokens, experts).cuda()
+    x = c['x'].cuda()
+    x_scale, act_scale = c['x_scale'].cuda(), torch.tensor(2e-4).cuda()
+    l1 = (c['l1_q'].cuda(), dg.pack_nvfp4_sf_mn_major(c['l1_sf'].cuda()), c['l1_scales'].cuda())
+    l2 = (c['l2_q'].cuda(), dg.pack_nvfp4_sf_mn_major(c['l2_sf'].cuda()), c['l2_scales'].cuda())
+    l1, l2 = dg.transform_weights_for_mega_moe(l1, l2)
+    outs, plans = [], []
+    for fused in (False, True):
+        buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, mma_type='nvfp4xnvfp4')
+        if use_logits and not fused:
+            dg.route_sigmoid_topk(logits, topk, buf.topk_idx[:tokens], buf.topk_weights[:tokens])
+        elif not use_logits:
+            buf.topk_idx[:tokens].copy_(c['topk_idx'].cuda())
+            buf.topk_weights[:tokens].copy_(c['topk_weights'].cuda())
+        y = torch.full((tokens, hidden), float('nan'), dtype=torch.bfloat16, device='cuda')
+        if fused:
+            dg.nvfp4_mega_moe_bf16_input(y, x, l1, l2, buf, x_scale, act_scale, logits=logits if use_logits else None,
+                                         fast_math=False)
+        else:
+            dg.per_token_cast_to_nvfp4_into(x, x_scale, buf.x, buf.x_sf)
+            dg.nvfp4_mega_moe(y, l1, l2, buf, x_scale, act_scale, fast_math=False)
+        _status_ok()
+        lay = buf.layout
+        outs.append(y.cpu())
+        plans.append(buf.buffer[lay['dest_row']:lay['dest_row'] + tokens * topk * 4].view(torch.int32).cpu())
+    assert not torch.isnan(outs[0].float()).any()
+    assert torch.equal(plans[0], plans[1]) and torch.equal(outs[0], outs[1])
+
+
 def test_layer_with_clamp_and_saturating_act_scale(dg):
     """An activation scale 8x too small makes block scales saturate at 448; kernel and oracle must clip alike."""
     tokens, hidden, inter, experts, topk = 96, 512, 256, 4, 2
